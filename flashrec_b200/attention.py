@@ -1,0 +1,178 @@
+"""KV pool, slot-index gather and the decode attention backend: mirrors of
+``TokenToKVPool`` (kvcache/pool.py:66-139), ``gather_kv_indices``
+(attention/kv_indices.py:63-132) and ``AttentionBackend`` (attention/flashinfer.py)
+for the FP8 decode path.
+"""
+
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Union
+
+import torch
+
+from flashrec_b200._lib import call, ptr, require_cuda, stream_ptr
+from flashrec_b200.kernel.sglops import store_kv_cache
+
+_FP8 = torch.float8_e4m3fn
+
+
+class TokenToKVPool:
+    """Physical KV: e4m3 ``[num_tokens, num_kv_heads, head_dim]`` per layer; slot 0 is
+    a dummy that is never handed out (kvcache/pool.py:66-114). ``page_size`` only
+    sets the allocation granularity (slot = page * page_size + offset); the byte
+    layout is the reference's page-size-1 layout."""
+
+    def __init__(self, num_layers, num_tokens, num_kv_heads, head_dim, dtype, device, page_size: int = 1):
+        if dtype != _FP8:
+            raise NotImplementedError("flashrec_b200 implements the float8_e4m3fn KV pool only")
+        self.num_layers = int(num_layers)
+        self.num_tokens = int(num_tokens)
+        self.num_kv_heads = int(num_kv_heads)
+        self.head_dim = int(head_dim)
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self.page_size = int(page_size)
+        self.row_dim = self.num_kv_heads * self.head_dim
+        shape = (self.num_tokens, self.num_kv_heads, self.head_dim)
+        self.k = [torch.zeros(shape, dtype=torch.uint8, device=device).view(_FP8) for _ in range(num_layers)]
+        self.v = [torch.zeros(shape, dtype=torch.uint8, device=device).view(_FP8) for _ in range(num_layers)]
+        first = self.page_size if self.page_size > 1 else 1  # page 0 / slot 0 reserved
+        self._free: List[int] = list(range(first, self.num_tokens))
+        self.last_alloc_cpu: List[int] = []
+
+    def available_size(self) -> int:
+        return len(self._free)
+
+    def alloc(self, n: int) -> Optional[torch.Tensor]:
+        n = int(n)
+        if n <= 0:
+            self.last_alloc_cpu = []
+            return torch.empty(0, dtype=torch.int64, device=self.device)
+        if n > len(self._free):
+            self.last_alloc_cpu = []
+            return None
+        idx = self._free[-n:]
+        del self._free[-n:]
+        self.last_alloc_cpu = idx
+        return torch.tensor(idx, dtype=torch.int64, device=self.device)
+
+    def free(self, indices) -> None:
+        ids = indices.tolist() if isinstance(indices, torch.Tensor) else list(indices)
+        self._free.extend(int(i) for i in ids if int(i) > 0)
+
+    def k_cache(self, layer_id: int) -> torch.Tensor:
+        return self.k[layer_id]
+
+    def v_cache(self, layer_id: int) -> torch.Tensor:
+        return self.v[layer_id]
+
+    def store(self, layer_id: int, k: torch.Tensor, v: torch.Tensor, loc: torch.Tensor) -> None:
+        n = int(loc.numel())
+        if n == 0:
+            return
+        store_kv_cache(
+            self.k[layer_id].view(-1, self.row_dim),
+            self.v[layer_id].view(-1, self.row_dim),
+            loc,
+            k.reshape(n, self.row_dim),
+            v.reshape(n, self.row_dim),
+        )
+
+
+def gather_kv_indices(
+    req_to_token: torch.Tensor,
+    rows: torch.Tensor,
+    seq_lens: Union[Sequence[int], torch.Tensor],
+    out: Optional[torch.Tensor] = None,
+    total: Optional[int] = None,
+    indptr_out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Concatenated slot ids of each row's ``[:seq_len]`` prefix (int32).
+
+    With ``out`` and ``indptr_out`` given and ``seq_lens`` an int32 device tensor,
+    nothing is allocated and nothing syncs (graph-capturable); otherwise ``total``
+    is obtained from the host copy of ``seq_lens`` as the reference does."""
+    require_cuda(req_to_token, rows)
+    device = req_to_token.device
+    if req_to_token.dtype != torch.int32:
+        raise TypeError("req_to_token must be int32")
+    rows = rows.reshape(-1).to(device=device, dtype=torch.int64)
+    n = int(rows.numel())
+    if n == 0:
+        return torch.empty(0, dtype=torch.int32, device=device) if out is None else out[:0]
+    if isinstance(seq_lens, torch.Tensor):
+        sl = seq_lens.reshape(-1)[:n].to(device=device, dtype=torch.int32).contiguous()
+        if total is None and out is None:
+            total = int(sl.sum().item())
+    else:
+        seq_list = [int(x) for x in seq_lens]
+        if len(seq_list) != n:
+            raise ValueError("rows and seq_lens length mismatch")
+        if total is None:
+            total = int(sum(seq_list))
+        sl = torch.tensor(seq_list, dtype=torch.int32, device=device)
+    if int(sl.numel()) != n:
+        raise ValueError("rows and seq_lens length mismatch")
+    if out is None:
+        out = torch.empty(max(int(total), 0), dtype=torch.int32, device=device)
+    elif out.dtype != torch.int32:
+        raise TypeError("out must be int32")
+    cap = int(out.numel()) if total is None else min(int(total), int(out.numel()))
+    if indptr_out is None:
+        indptr_out = torch.empty(n + 1, dtype=torch.int32, device=device)
+    call("fr_gather_kv_indices", ptr(req_to_token), req_to_token.stride(0), ptr(rows), ptr(sl), ptr(indptr_out),
+         ptr(out), n, cap, stream_ptr(device))
+    return out.reshape(-1)[:cap] if total is not None else out
+
+
+class AttentionBackend:
+    """Decode attention over the e4m3 pool. ``prepare`` plans (finds each group's
+    shared slot prefix on the device); ``forward`` stores nothing when
+    ``skip_store`` is set (the fused rope kernel already wrote K/V)."""
+
+    def __init__(self, kv_pool: TokenToKVPool, num_qo_heads: int, num_kv_heads: int, head_dim: int):
+        self.kv_pool = kv_pool
+        self.num_qo_heads = int(num_qo_heads)
+        self.num_kv_heads = int(num_kv_heads)
+        self.head_dim = int(head_dim)
+        self.n_rep = self.num_qo_heads // self.num_kv_heads
+        self._group_rows: Optional[torch.Tensor] = None
+        self._shared_len: Optional[torch.Tensor] = None
+        self._max_group_rows = 0
+        self._n_groups = 0
+
+    def set_groups(self, group_rows: torch.Tensor, max_group_rows: int) -> None:
+        """``group_rows`` int32 [n_groups + 1]: rows [g[i], g[i+1]) are the beams of one request."""
+        self._group_rows = group_rows.to(dtype=torch.int32).contiguous()
+        self._n_groups = int(group_rows.numel()) - 1
+        self._max_group_rows = int(max_group_rows)
+        if self._shared_len is None or self._shared_len.numel() < self._n_groups:
+            self._shared_len = torch.zeros(self._n_groups, dtype=torch.int32, device=group_rows.device)
+
+    def prepare(self, batch) -> None:
+        if batch.kv_indices is None or batch.kv_indptr is None:
+            return
+        if self._group_rows is None:
+            n = int(batch.kv_indptr.numel()) - 1
+            self.set_groups(torch.arange(n + 1, dtype=torch.int32, device=batch.kv_indptr.device), 1)
+        call("fr_decode_attn_plan", ptr(batch.kv_indptr), ptr(batch.kv_indices), ptr(self._group_rows),
+             self._n_groups, ptr(self._shared_len), stream_ptr(batch.kv_indptr.device))
+
+    def forward(self, q, k, v, layer_id: int, batch, skip_store: bool = False, out=None) -> torch.Tensor:
+        """q: [T, Hq, D] bf16 (may be a strided view); returns [T, Hq, D] bf16."""
+        require_cuda(q)
+        if not skip_store:
+            self.kv_pool.store(layer_id, k, v, batch.out_cache_loc)
+        if batch.is_prefill:
+            raise NotImplementedError("flashrec_b200 covers the decode step; prefill attention is out of scope")
+        t = int(q.shape[0])
+        if out is None:
+            out = torch.empty((t, self.num_qo_heads, self.head_dim), dtype=torch.bfloat16, device=q.device)
+        kc = self.kv_pool.k[layer_id]
+        vc = self.kv_pool.v[layer_id]
+        call("fr_decode_attn_fp8", ptr(q), q.stride(0), q.stride(1), ptr(kc), ptr(vc), kc.stride(0), kc.stride(1),
+             vc.stride(0), vc.stride(1), ptr(batch.kv_indptr), ptr(batch.kv_indices), ptr(self._group_rows),
+             ptr(self._shared_len), ptr(out), out.stride(0), t, self._n_groups, self.num_qo_heads,
+             self.num_kv_heads, self.head_dim, self._max_group_rows, self.kv_pool.num_tokens,
+             float(self.head_dim) ** -0.5, stream_ptr(q.device))
+        return out

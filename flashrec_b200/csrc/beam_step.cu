@@ -1,0 +1,641 @@
+// Trie-constrained beam step of the SID decode: masked scores -> sorted top-K
+// across all beams of a request -> token-row expand -> trie-node advance.
+//
+// Stands in for
+//   trie_mask_kernel / trie_advance(_batched)_kernel / beam_expand(_batched)_kernel
+//   / genrec_mask_topk_expand_kernel          (kernel/csrc/beam_trie.cuh:69-755)
+//   and their torch restatements              (kernel/beam_trie.py:82-246, 536-630)
+//   BeamValidPathTrie.mask_candidates / advance_node_ids / _csr_lookup
+//                                             (search/trie.py:345-368, 445-589)
+//   expand_step's no-EOS path                 (search/expand.py:351-372)
+//
+// Ordering rule (the reference CUDA kernel's, beam_trie.cuh:495-500): score
+// descending, ties broken by the smaller flat candidate index b * C + c. With
+// masking on, a candidate whose score is -inf is not a candidate at all; when
+// fewer than K remain the tail is filled with (-inf, parent 0, token of flat
+// index 0), as the reference does (beam_trie.cuh:664-683).
+//
+// Selection: one CTA per request runs a radix select on the 64-bit composite
+// (order-preserving score key << 32 | ~flat index) — 11/11/10-bit digits, each
+// pass re-enumerating the candidates and histogramming those that match the
+// prefix found so far, stopping as soon as the boundary bin is taken whole —
+// then collects the K winners into shared memory and bitonic-sorts them. This
+// replaces the reference's K serial block-wide arg-max rounds and has no 512
+// limit on beam width.
+#include "fr_common.cuh"
+#include "topk_select.cuh"
+
+namespace fr {
+namespace beam {
+
+constexpr int kThreads = 1024;
+constexpr int kMaxK = 4096;
+
+struct Trie {
+  int kind;  // FR_TRIE_NONE / DENSE / CSR / BITMAP
+  const uint8_t* allow;
+  const void* next;
+  int next_is_i32;
+  const int64_t* keys;
+  const int64_t* child;
+  int64_t n_edges;
+  const uint32_t* bitmap;
+  const int64_t* child_base;
+  const int32_t* level_off;
+  int words;
+  int64_t n_rows;
+  int64_t vsz;
+  int64_t token_base;
+  int64_t invalid_node;
+};
+
+__device__ __forceinline__ int64_t clamp64(int64_t x, int64_t lo, int64_t hi) { return x < lo ? lo : (x > hi ? hi : x); }
+
+// first position in keys[0, n) with keys[pos] >= key
+__device__ __forceinline__ int64_t lower_bound(const int64_t* __restrict__ keys, int64_t n, int64_t key) {
+  int64_t lo = 0, hi = n;
+  while (lo < hi) {
+    const int64_t mid = (lo + hi) >> 1;
+    if (__ldg(keys + mid) < key) lo = mid + 1; else hi = mid;
+  }
+  return lo;
+}
+
+// Is `tok` a legal continuation of trie node `node`? node < 0 = unconstrained.
+__device__ __forceinline__ bool trie_allowed(const Trie& tr, int64_t node, int64_t tok) {
+  if (node < 0) return true;
+  const int64_t rel = tok - tr.token_base;
+  if (rel < 0 || rel >= tr.vsz) return false;
+  if (tr.kind == FR_TRIE_DENSE) {
+    if (tr.n_rows <= 0) return false;
+    const int64_t safe = clamp64(node, 0, tr.n_rows - 1);
+    return __ldg(tr.allow + safe * tr.vsz + rel) != 0;
+  }
+  if (tr.kind == FR_TRIE_CSR) {
+    if (tr.n_edges <= 0) return false;
+    const int64_t key = node * tr.vsz + rel;
+    const int64_t pos = lower_bound(tr.keys, tr.n_edges, key);
+    return pos < tr.n_edges && __ldg(tr.keys + pos) == key;
+  }
+  if (tr.kind == FR_TRIE_BITMAP) {
+    if (tr.n_rows <= 0) return false;
+    const int64_t safe = clamp64(node, 0, tr.n_rows - 1);
+    const int64_t c = rel - __ldg(tr.level_off + safe);
+    if (c < 0 || c >= static_cast<int64_t>(tr.words) * 32) return false;
+    return (__ldg(tr.bitmap + safe * tr.words + (c >> 5)) >> (c & 31)) & 1u;
+  }
+  return true;
+}
+
+// Node reached from `old` by `tok`: old < 0 stays; unknown edge -> invalid_node.
+__device__ __forceinline__ int64_t trie_transition(const Trie& tr, int64_t old, int64_t tok) {
+  if (old < 0) return old;
+  const int64_t rel = tok - tr.token_base;
+  if (rel < 0 || rel >= tr.vsz) return tr.invalid_node;
+  if (tr.kind == FR_TRIE_DENSE) {
+    if (tr.n_rows <= 0) return tr.invalid_node;
+    const int64_t safe = clamp64(old, 0, tr.n_rows - 1);
+    return tr.next_is_i32 ? static_cast<int64_t>(__ldg(static_cast<const int32_t*>(tr.next) + safe * tr.vsz + rel))
+                          : __ldg(static_cast<const int64_t*>(tr.next) + safe * tr.vsz + rel);
+  }
+  if (tr.kind == FR_TRIE_CSR) {
+    if (tr.n_edges <= 0) return tr.invalid_node;
+    const int64_t key = old * tr.vsz + rel;
+    const int64_t pos = lower_bound(tr.keys, tr.n_edges, key);
+    if (pos < tr.n_edges && __ldg(tr.keys + pos) == key) return __ldg(tr.child + pos);
+    return tr.invalid_node;
+  }
+  if (tr.kind == FR_TRIE_BITMAP) {
+    if (tr.n_rows <= 0) return tr.invalid_node;
+    const int64_t safe = clamp64(old, 0, tr.n_rows - 1);
+    const int64_t c = rel - __ldg(tr.level_off + safe);
+    if (c < 0 || c >= static_cast<int64_t>(tr.words) * 32) return tr.invalid_node;
+    const uint32_t* bm = tr.bitmap + safe * tr.words;
+    const uint32_t w = __ldg(bm + (c >> 5));
+    if (!((w >> (c & 31)) & 1u)) return tr.invalid_node;
+    const int64_t base = __ldg(tr.child_base + safe);
+    if (base < 0) return -1;  // children are leaves: unconstrained from here on
+    int64_t rank = __popc(w & ((1u << (c & 31)) - 1u));
+    for (int i = 0; i < (c >> 5); ++i) rank += __popc(__ldg(bm + i));
+    return base + rank;
+  }
+  return old;
+}
+
+// ---------------------------------------------------------------------------
+// element-wise entry points
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(512) trie_mask_kernel(float* __restrict__ out, const float* __restrict__ in,
+                                                       const int64_t* __restrict__ tok,
+                                                       const int64_t* __restrict__ nodes, Trie tr, float neg_inf,
+                                                       int64_t rows, int64_t cols) {
+  const int64_t total = rows * cols;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / cols;
+    out[i] = trie_allowed(tr, nodes[r], tok[i]) ? in[i] : neg_inf;
+  }
+}
+
+// out[n, k] = transition(node_ids[n, clamp(parents[n, k])], tokens[n, k])
+__global__ void __launch_bounds__(512) trie_advance_kernel(int64_t* __restrict__ out,
+                                                          const int64_t* __restrict__ nodes,
+                                                          const int64_t* __restrict__ parents,
+                                                          const int64_t* __restrict__ tok, Trie tr, int N, int BW,
+                                                          int K) {
+  const int64_t total = static_cast<int64_t>(N) * K;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t n = i / K;
+    const int64_t p = clamp64(parents[i], 0, BW - 1);
+    out[i] = trie_transition(tr, nodes[n * BW + p], tok[i]);
+  }
+}
+
+// out[n, b, :] = token_ids[n, clamp(parents[n, b]), :]; out[n, b, col] = new_tokens[n, b]
+__global__ void __launch_bounds__(512) beam_expand_kernel(int64_t* __restrict__ out,
+                                                         const int64_t* __restrict__ token_ids,
+                                                         const int64_t* __restrict__ parents,
+                                                         const int64_t* __restrict__ new_tokens, int N, int BW, int L,
+                                                         int col) {
+  const int64_t total = static_cast<int64_t>(N) * BW * L;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t c = i % L;
+    const int64_t nb = i / L;
+    const int64_t n = nb / BW;
+    if (c == col) {
+      out[i] = new_tokens[nb];
+    } else {
+      const int64_t p = clamp64(parents[nb], 0, BW - 1);
+      out[i] = token_ids[(n * BW + p) * L + c];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// fused step
+// ---------------------------------------------------------------------------
+struct StepParams {
+  float* out_vals;         // [N, K]
+  int64_t* out_parents;    // [N, K]
+  int64_t* out_tokens;     // [N, K]
+  int64_t* out_indices;    // [N, K] flat index b * C + c
+  int64_t* out_child;      // [N, K] node after the step, or null
+  int64_t* token_ids_out;  // [N, BW, L] or null
+  int64_t* node_ids_out;   // [N, BW] or null
+  const float* cum;        // [N, BW]
+  const int64_t* node_in;  // [N, BW] or null
+  const int64_t* token_ids_in;
+  const uint8_t* do_expand;  // [N] or null (= all)
+  const int32_t* col_n;      // [N] or null (= 0)
+  // explicit candidates
+  const float* lp;     // [N, BW, C]
+  const int64_t* tok;  // [N, BW, C]
+  float* scratch;      // [N, BW * C] masked scores
+  // full-width candidates straight from the level's logits
+  const float* logits;  // [N * BW, ld]
+  int64_t ld;
+  const float* row_max;     // [N * BW]
+  const float* row_logsum;  // [N * BW]
+  int64_t level_tok_base;   // token id of code 0 of this level
+  int64_t idx_base;         // added to c when forming the flat index (token-range shards)
+  int64_t idx_width;        // C used in the flat index (whole level width)
+  Trie trie;
+  int N, BW, C, K, L;
+  int apply_mask, apply_expand, apply_advance;
+  float neg_inf;
+};
+
+using topk::compose;
+using topk::SelectSmem;
+
+// Candidate enumeration. Calls f(composite) for every live candidate of request n.
+template <bool FULL, class F>
+__device__ __forceinline__ void for_each_candidate(const StepParams& p, int n, bool masked, F&& f) {
+  if constexpr (!FULL) {
+    const uint32_t M = static_cast<uint32_t>(p.BW) * p.C;
+    const float* cum_n = p.cum + static_cast<size_t>(n) * p.BW;
+    if (masked) {
+      const float* sc = p.scratch + static_cast<size_t>(n) * M;
+      for (uint32_t i = threadIdx.x; i < M; i += kThreads) {
+        const float s = sc[i];
+        if (s != p.neg_inf) f(compose(s, i));
+      }
+    } else {
+      const float* lp_n = p.lp + static_cast<size_t>(n) * M;
+      for (uint32_t i = threadIdx.x; i < M; i += kThreads) f(compose(__fadd_rn(cum_n[i / p.C], lp_n[i]), i));
+    }
+  } else {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const Trie& tr = p.trie;
+    const int64_t first_tok = p.level_tok_base + p.idx_base;  // token of this shard's local code 0
+    const int64_t level_off = first_tok - tr.token_base;
+    for (int b = warp; b < p.BW; b += kThreads / 32) {
+      const size_t row = static_cast<size_t>(n) * p.BW + b;
+      const float cumb = p.cum[row];
+      if (cumb == p.neg_inf) continue;
+      const int64_t node = p.node_in ? p.node_in[row] : -1;
+      const float* lg = p.logits + row * p.ld;
+      const float mx = p.row_max[row], ls = p.row_logsum[row];
+      if (tr.kind == FR_TRIE_CSR && node >= 0) {
+        // only the node's own edges can be legal: walk its slice of the sorted key array
+        const int64_t k0 = node * tr.vsz + level_off;
+        const int64_t e0 = lower_bound(tr.keys, tr.n_edges, k0);
+        const int64_t e1 = lower_bound(tr.keys, tr.n_edges, k0 + p.C);
+        for (int64_t e = e0 + lane; e < e1; e += 32) {
+          const int64_t c = __ldg(tr.keys + e) - k0;
+          const float s = __fadd_rn(cumb, __fsub_rn(__fsub_rn(lg[c], mx), ls));
+          if (s != p.neg_inf)
+            f(compose(s, static_cast<uint32_t>(static_cast<int64_t>(b) * p.idx_width + p.idx_base + c)));
+        }
+      } else {
+        for (int c = lane; c < p.C; c += 32) {
+          if (!trie_allowed(tr, node, first_tok + c)) continue;
+          const float s = __fadd_rn(cumb, __fsub_rn(__fsub_rn(lg[c], mx), ls));
+          if (s != p.neg_inf)
+            f(compose(s, static_cast<uint32_t>(static_cast<int64_t>(b) * p.idx_width + p.idx_base + c)));
+        }
+      }
+    }
+  }
+}
+
+// Token-row expand and node advance for request n, given the K winners in
+// shared memory (sel_parent, sel_token) — same contract as the reference's tail
+// of genrec_mask_topk_expand_kernel (beam_trie.cuh:697-754).
+__device__ __forceinline__ void apply_winners(const StepParams& p, int n, const int32_t* sel_parent,
+                                              const int64_t* sel_token, const int64_t* sel_child) {
+  const bool expand_this = p.apply_expand && p.token_ids_in && p.token_ids_out && (!p.do_expand || p.do_expand[n] != 0);
+  if (!expand_this) return;
+  int64_t col = 0;
+  if (p.col_n) col = p.col_n[n] < 0 ? 0 : p.col_n[n];
+  const int64_t* tin = p.token_ids_in + static_cast<size_t>(n) * p.BW * p.L;
+  int64_t* tout = p.token_ids_out + static_cast<size_t>(n) * p.BW * p.L;
+  const int plane = p.BW * p.L;
+  for (int i = threadIdx.x; i < plane; i += kThreads) {
+    const int b = i / p.L, c = i - b * p.L;
+    if (b >= p.K) { tout[i] = tin[i]; continue; }
+    if (c == col) tout[i] = sel_token[b];
+    else tout[i] = tin[static_cast<size_t>(sel_parent[b]) * p.L + c];
+  }
+  if (p.apply_advance && p.node_in && p.node_ids_out) {
+    const int64_t* nin = p.node_in + static_cast<size_t>(n) * p.BW;
+    int64_t* nout = p.node_ids_out + static_cast<size_t>(n) * p.BW;
+    for (int b = threadIdx.x; b < p.BW; b += kThreads) nout[b] = b < p.K ? sel_child[b] : nin[b];
+  }
+}
+
+template <bool FULL>
+__global__ void __launch_bounds__(kThreads, 1) beam_step_kernel(StepParams p) {
+  extern __shared__ __align__(16) uint8_t dyn[];
+  __shared__ SelectSmem sm;
+  const int n = blockIdx.x;
+  int kp2 = 1;
+  while (kp2 < p.K) kp2 <<= 1;
+  uint64_t* win = reinterpret_cast<uint64_t*>(dyn);                    // [kp2]
+  int64_t* sel_token = reinterpret_cast<int64_t*>(win + kp2);          // [K]
+  int64_t* sel_child = sel_token + p.K;                                // [K]
+  int32_t* sel_parent = reinterpret_cast<int32_t*>(sel_child + p.K);   // [K]
+
+  const bool masked = FULL || (p.apply_mask && p.node_in && p.trie.kind != FR_TRIE_NONE);
+  const uint32_t M = static_cast<uint32_t>(p.BW) * p.C;
+
+  if constexpr (!FULL) {
+    if (masked) {
+      // pass 0: masked scores, kept in global scratch for the later passes
+      const float* cum_n = p.cum + static_cast<size_t>(n) * p.BW;
+      const float* lp_n = p.lp + static_cast<size_t>(n) * M;
+      const int64_t* tok_n = p.tok + static_cast<size_t>(n) * M;
+      const int64_t* nodes_n = p.node_in + static_cast<size_t>(n) * p.BW;
+      float* sc = p.scratch + static_cast<size_t>(n) * M;
+      for (uint32_t i = threadIdx.x; i < M; i += kThreads) {
+        const uint32_t b = i / p.C;
+        float s = __fadd_rn(cum_n[b], lp_n[i]);
+        if (!trie_allowed(p.trie, nodes_n[b], tok_n[i])) s = p.neg_inf;
+        sc[i] = s;
+      }
+      __syncthreads();  // same CTA re-reads what it wrote
+    }
+  }
+
+  // ---- select + sort ---------------------------------------------------------
+  const int nvalid = topk::radix_select_topk<kThreads>(
+      [&](auto&& f) { for_each_candidate<FULL>(p, n, masked, f); }, p.K, win, kp2, sm);
+
+  // ---- outputs ---------------------------------------------------------------
+  const int64_t* tok_n = FULL ? nullptr : p.tok + static_cast<size_t>(n) * M;
+  const int64_t* nodes_n = p.node_in ? p.node_in + static_cast<size_t>(n) * p.BW : nullptr;
+  const int64_t cdiv = FULL ? p.idx_width : p.C;
+  for (int k = threadIdx.x; k < p.K; k += kThreads) {
+    float v = p.neg_inf;
+    uint32_t idx = 0;
+    if (k < nvalid) {
+      const uint64_t ck = win[k];
+      v = topk::composite_score(ck);
+      idx = topk::composite_index(ck);
+    }
+    const int64_t parent = k < nvalid ? static_cast<int64_t>(idx) / cdiv : 0;
+    int64_t token;
+    if constexpr (FULL) token = p.level_tok_base + static_cast<int64_t>(idx) % cdiv;
+    else token = M > 0 ? tok_n[k < nvalid ? idx : 0] : 0;
+    const int64_t pc = clamp64(parent, 0, p.BW - 1);
+    int64_t child = 0;
+    if (nodes_n) child = trie_transition(p.trie, nodes_n[pc], token);
+    const size_t o = static_cast<size_t>(n) * p.K + k;
+    p.out_vals[o] = v;
+    p.out_parents[o] = parent;
+    p.out_tokens[o] = token;
+    p.out_indices[o] = k < nvalid ? static_cast<int64_t>(idx) : 0;
+    if (p.out_child) p.out_child[o] = child;
+    sel_parent[k] = static_cast<int32_t>(pc);
+    sel_token[k] = token;
+    sel_child[k] = child;
+  }
+  __syncthreads();
+  apply_winners(p, n, sel_parent, sel_token, sel_child);
+}
+
+// ---------------------------------------------------------------------------
+// merge of per-shard winners (token-range sharded lm_head): S sorted lists of K
+// records per request -> global sorted top-K, then expand / advance.
+// ---------------------------------------------------------------------------
+struct MergeParams {
+  const float* vals;       // [S, N, K]
+  const int64_t* indices;  // [S, N, K] flat index over the whole level
+  const int64_t* child;    // [S, N, K]
+  int S;
+  StepParams step;  // outputs + expand inputs; idx_width / level_tok_base / K / BW / L used
+};
+
+__global__ void __launch_bounds__(kThreads, 1) merge_shards_kernel(MergeParams mp) {
+  extern __shared__ __align__(16) uint8_t dyn[];
+  const StepParams& p = mp.step;
+  const int n = blockIdx.x;
+  const int total = mp.S * p.K;
+  int tp2 = 1;
+  while (tp2 < total) tp2 <<= 1;
+  uint64_t* win = reinterpret_cast<uint64_t*>(dyn);                    // [tp2]
+  int64_t* sel_token = reinterpret_cast<int64_t*>(win + tp2);          // [K]
+  int64_t* sel_child = sel_token + p.K;                                // [K]
+  int32_t* sel_parent = reinterpret_cast<int32_t*>(sel_child + p.K);   // [K]
+  for (int i = threadIdx.x; i < tp2; i += kThreads) {
+    uint64_t ck = 0;
+    if (i < total) {
+      const int s = i / p.K, k = i - s * p.K;
+      const size_t o = (static_cast<size_t>(s) * p.N + n) * p.K + k;
+      const float v = mp.vals[o];
+      if (v != p.neg_inf) ck = compose(v, static_cast<uint32_t>(mp.indices[o]));
+    }
+    win[i] = ck;
+  }
+  __syncthreads();
+  topk::bitonic_sort_desc<kThreads>(win, tp2);
+  for (int k = threadIdx.x; k < p.K; k += kThreads) {
+    const uint64_t ck = win[k];
+    const bool live = ck != 0;
+    float v = p.neg_inf;
+    uint32_t idx = 0;
+    if (live) {
+      v = topk::composite_score(ck);
+      idx = topk::composite_index(ck);
+    }
+    const int64_t parent = static_cast<int64_t>(idx) / p.idx_width;
+    const int64_t token = p.level_tok_base + static_cast<int64_t>(idx) % p.idx_width;
+    // find the record again in the shard lists to fetch its child node
+    int64_t child = 0;
+    if (live && mp.child) {
+      for (int s = 0; s < mp.S; ++s) {
+        const size_t base = (static_cast<size_t>(s) * p.N + n) * p.K;
+        // shard lists are sorted like the output: binary search on the composite
+        int lo = 0, hi = p.K;
+        while (lo < hi) {
+          const int mid = (lo + hi) >> 1;
+          const float mv = mp.vals[base + mid];
+          const uint64_t mk = mv != p.neg_inf ? compose(mv, static_cast<uint32_t>(mp.indices[base + mid])) : 0;
+          if (mk > ck) lo = mid + 1; else hi = mid;
+        }
+        if (lo < p.K && mp.vals[base + lo] != p.neg_inf &&
+            compose(mp.vals[base + lo], static_cast<uint32_t>(mp.indices[base + lo])) == ck) {
+          child = mp.child[base + lo];
+          break;
+        }
+      }
+    }
+    const int64_t pc = clamp64(parent, 0, p.BW - 1);
+    const size_t o = static_cast<size_t>(n) * p.K + k;
+    p.out_vals[o] = v;
+    p.out_parents[o] = live ? parent : 0;
+    p.out_tokens[o] = live ? token : p.level_tok_base;
+    p.out_indices[o] = live ? static_cast<int64_t>(idx) : 0;
+    if (p.out_child) p.out_child[o] = child;
+    sel_parent[k] = static_cast<int32_t>(live ? pc : 0);
+    sel_token[k] = live ? token : p.level_tok_base;
+    sel_child[k] = child;
+  }
+  __syncthreads();
+  apply_winners(p, n, sel_parent, sel_token, sel_child);
+}
+
+static int make_trie(const fr_trie* t, Trie* out) {
+  Trie tr{};
+  if (!t || t->kind == FR_TRIE_NONE) { tr.kind = FR_TRIE_NONE; *out = tr; return FR_OK; }
+  tr.kind = t->kind;
+  tr.allow = static_cast<const uint8_t*>(t->allow);
+  tr.next = t->next;
+  tr.next_is_i32 = t->next_is_i32;
+  tr.keys = static_cast<const int64_t*>(t->csr_keys);
+  tr.child = static_cast<const int64_t*>(t->csr_child);
+  tr.n_edges = t->n_edges;
+  tr.bitmap = static_cast<const uint32_t*>(t->bitmap);
+  tr.child_base = static_cast<const int64_t*>(t->child_base);
+  tr.level_off = static_cast<const int32_t*>(t->level_off);
+  tr.words = t->words_per_node;
+  tr.n_rows = t->n_rows;
+  tr.vsz = t->vsz;
+  tr.token_base = t->token_base;
+  tr.invalid_node = t->invalid_node;
+  if (tr.vsz <= 0) return FR_ERR_BAD_ARG;
+  switch (tr.kind) {
+    case FR_TRIE_DENSE: if (!tr.allow || tr.n_rows <= 0) return FR_ERR_BAD_ARG; break;
+    case FR_TRIE_CSR: if (tr.n_edges < 0 || (tr.n_edges > 0 && (!tr.keys || !tr.child))) return FR_ERR_BAD_ARG; break;
+    case FR_TRIE_BITMAP:
+      if (!tr.bitmap || !tr.child_base || !tr.level_off || tr.words <= 0 || tr.n_rows <= 0) return FR_ERR_BAD_ARG;
+      break;
+    default: return FR_ERR_BAD_ARG;
+  }
+  *out = tr;
+  return FR_OK;
+}
+
+static size_t step_smem(int K) {
+  int kp2 = 1;
+  while (kp2 < K) kp2 <<= 1;
+  return static_cast<size_t>(kp2) * 8 + static_cast<size_t>(K) * (8 + 8 + 4) + 16;
+}
+
+template <bool FULL>
+static int launch_step(const StepParams& p, cudaStream_t stream) {
+  const size_t smem = step_smem(p.K);
+  auto kern = beam_step_kernel<FULL>;
+  if (smem > 48 * 1024) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+      return FR_ERR_CUDA;
+  }
+  kern<<<p.N, kThreads, smem, stream>>>(p);
+  return launch_status();
+}
+
+static int grid_for(int64_t total, int threads) {
+  int64_t g = (total + threads - 1) / threads;
+  if (g > 148 * 8) g = 148 * 8;
+  return static_cast<int>(g < 1 ? 1 : g);
+}
+
+}  // namespace beam
+}  // namespace fr
+
+using namespace fr;
+using namespace fr::beam;
+
+extern "C" int fr_trie_mask(float* scores_out, const float* scores_in, const int64_t* cand_tokens,
+                            const int64_t* node_ids, const fr_trie* trie, float neg_inf, int64_t rows, int64_t cols,
+                            cudaStream_t stream) {
+  FR_CHECK_ARG(rows >= 0 && cols >= 0);
+  if (rows == 0 || cols == 0) return FR_OK;
+  FR_CHECK_ARG(scores_out && scores_in && cand_tokens && node_ids && trie);
+  Trie tr;
+  const int st = make_trie(trie, &tr);
+  if (st != FR_OK) return st;
+  trie_mask_kernel<<<grid_for(rows * cols, 512), 512, 0, stream>>>(scores_out, scores_in, cand_tokens, node_ids, tr,
+                                                                   neg_inf, rows, cols);
+  return launch_status();
+}
+
+extern "C" int fr_trie_advance(int64_t* out, const int64_t* node_ids, const int64_t* parents, const int64_t* tokens,
+                               const fr_trie* trie, int N, int BW, int K, cudaStream_t stream) {
+  FR_CHECK_ARG(N >= 0 && BW > 0 && K >= 0);
+  if (N == 0 || K == 0) return FR_OK;
+  FR_CHECK_ARG(out && node_ids && parents && tokens && trie);
+  Trie tr;
+  const int st = make_trie(trie, &tr);
+  if (st != FR_OK) return st;
+  trie_advance_kernel<<<grid_for(static_cast<int64_t>(N) * K, 512), 512, 0, stream>>>(out, node_ids, parents, tokens,
+                                                                                      tr, N, BW, K);
+  return launch_status();
+}
+
+extern "C" int fr_beam_expand(int64_t* out, const int64_t* token_ids, const int64_t* parents,
+                              const int64_t* new_tokens, int N, int BW, int L, int col, cudaStream_t stream) {
+  FR_CHECK_ARG(N >= 0 && BW > 0 && L > 0);
+  if (N == 0) return FR_OK;
+  FR_CHECK_ARG(out && token_ids && parents && new_tokens && out != token_ids);
+  FR_CHECK_ARG(col >= 0 && col < L);
+  beam_expand_kernel<<<grid_for(static_cast<int64_t>(N) * BW * L, 512), 512, 0, stream>>>(out, token_ids, parents,
+                                                                                         new_tokens, N, BW, L, col);
+  return launch_status();
+}
+
+static int check_step_common(const StepParams& p) {
+  FR_CHECK_ARG(p.N >= 0 && p.BW > 0 && p.C > 0 && p.K > 0 && p.L >= 0);
+  FR_CHECK_SUPPORTED(p.K <= kMaxK && p.K <= p.BW * static_cast<int64_t>(p.C));
+  FR_CHECK_SUPPORTED(static_cast<int64_t>(p.BW) * (p.idx_width > 0 ? p.idx_width : p.C) < (1ll << 32));
+  FR_CHECK_ARG(p.out_vals && p.out_parents && p.out_tokens && p.out_indices && p.cum);
+  if (p.apply_expand) {
+    FR_CHECK_ARG(p.token_ids_in && p.token_ids_out && p.token_ids_in != p.token_ids_out && p.L > 0);
+    FR_CHECK_SUPPORTED(p.K <= p.BW);
+  }
+  if (p.apply_advance) FR_CHECK_ARG(p.node_in && p.node_ids_out && p.node_in != p.node_ids_out);
+  return FR_OK;
+}
+
+extern "C" int fr_mask_topk_expand(float* out_vals, int64_t* out_parents, int64_t* out_tokens, int64_t* out_indices,
+                                   int64_t* out_child, float* scratch, const float* cum, const float* top_logprobs,
+                                   const int64_t* top_tokens, const int64_t* node_in, const int64_t* token_ids_in,
+                                   int64_t* token_ids_out, int64_t* node_ids_out, const uint8_t* do_expand,
+                                   const int32_t* col_n, const fr_trie* trie, int N, int BW, int C, int K, int L,
+                                   int apply_mask, int apply_expand, int apply_advance, cudaStream_t stream) {
+  StepParams p{};
+  p.out_vals = out_vals; p.out_parents = out_parents; p.out_tokens = out_tokens; p.out_indices = out_indices;
+  p.out_child = out_child; p.token_ids_out = token_ids_out; p.node_ids_out = node_ids_out;
+  p.cum = cum; p.node_in = node_in; p.token_ids_in = token_ids_in; p.do_expand = do_expand; p.col_n = col_n;
+  p.lp = top_logprobs; p.tok = top_tokens; p.scratch = scratch;
+  p.N = N; p.BW = BW; p.C = C; p.K = K; p.L = L;
+  p.apply_mask = apply_mask; p.apply_expand = apply_expand; p.apply_advance = apply_advance && apply_mask && apply_expand;
+  p.neg_inf = -INFINITY;
+  p.idx_width = C;
+  if (N == 0) return FR_OK;
+  int st = make_trie(trie, &p.trie);
+  if (st != FR_OK) return st;
+  if (!(apply_mask && node_in && p.trie.kind != FR_TRIE_NONE)) { p.apply_mask = 0; p.apply_advance = 0; }
+  st = check_step_common(p);
+  if (st != FR_OK) return st;
+  FR_CHECK_ARG(top_logprobs && top_tokens);
+  if (p.apply_mask) FR_CHECK_ARG(scratch);
+  return launch_step<false>(p, stream);
+}
+
+extern "C" int fr_sid_beam_step(float* out_vals, int64_t* out_parents, int64_t* out_tokens, int64_t* out_indices,
+                                int64_t* out_child, const float* cum, const float* logits, int64_t ld,
+                                const float* row_max, const float* row_logsum, const int64_t* node_in,
+                                const int64_t* token_ids_in, int64_t* token_ids_out, int64_t* node_ids_out,
+                                const uint8_t* do_expand, const int32_t* col_n, const fr_trie* trie,
+                                int64_t level_tok_base, int64_t idx_base, int64_t idx_width, int N, int BW,
+                                int level_width, int K, int L, int apply_expand, int apply_advance,
+                                cudaStream_t stream) {
+  StepParams p{};
+  p.out_vals = out_vals; p.out_parents = out_parents; p.out_tokens = out_tokens; p.out_indices = out_indices;
+  p.out_child = out_child; p.token_ids_out = token_ids_out; p.node_ids_out = node_ids_out;
+  p.cum = cum; p.node_in = node_in; p.token_ids_in = token_ids_in; p.do_expand = do_expand; p.col_n = col_n;
+  p.logits = logits; p.ld = ld; p.row_max = row_max; p.row_logsum = row_logsum;
+  p.level_tok_base = level_tok_base; p.idx_base = idx_base; p.idx_width = idx_width > 0 ? idx_width : level_width;
+  p.N = N; p.BW = BW; p.C = level_width; p.K = K; p.L = L;
+  p.apply_mask = 1; p.apply_expand = apply_expand; p.apply_advance = apply_advance && apply_expand;
+  p.neg_inf = -INFINITY;
+  if (N == 0) return FR_OK;
+  int st = make_trie(trie, &p.trie);
+  if (st != FR_OK) return st;
+  if (p.trie.kind == FR_TRIE_NONE) { p.trie.vsz = 1; p.trie.token_base = 0; }
+  st = check_step_common(p);
+  if (st != FR_OK) return st;
+  FR_CHECK_ARG(logits && row_max && row_logsum && ld >= level_width);
+  FR_CHECK_ARG(p.trie.kind == FR_TRIE_NONE || node_in);
+  return launch_step<true>(p, stream);
+}
+
+extern "C" int fr_topk_merge_shards(float* out_vals, int64_t* out_parents, int64_t* out_tokens, int64_t* out_indices,
+                                    int64_t* out_child, const float* shard_vals, const int64_t* shard_indices,
+                                    const int64_t* shard_child, const int64_t* node_in, const int64_t* token_ids_in,
+                                    int64_t* token_ids_out, int64_t* node_ids_out, const uint8_t* do_expand,
+                                    const int32_t* col_n, int64_t level_tok_base, int64_t idx_width, int S, int N,
+                                    int BW, int K, int L, int apply_expand, int apply_advance, cudaStream_t stream) {
+  FR_CHECK_ARG(S > 0 && N >= 0 && BW > 0 && K > 0 && idx_width > 0);
+  if (N == 0) return FR_OK;
+  FR_CHECK_ARG(out_vals && out_parents && out_tokens && out_indices && shard_vals && shard_indices);
+  FR_CHECK_SUPPORTED(K <= kMaxK && static_cast<int64_t>(S) * K <= 16384);
+  MergeParams mp{};
+  mp.vals = shard_vals; mp.indices = shard_indices; mp.child = shard_child; mp.S = S;
+  StepParams& p = mp.step;
+  p.out_vals = out_vals; p.out_parents = out_parents; p.out_tokens = out_tokens; p.out_indices = out_indices;
+  p.out_child = out_child; p.token_ids_out = token_ids_out; p.node_ids_out = node_ids_out;
+  p.node_in = node_in; p.token_ids_in = token_ids_in; p.do_expand = do_expand; p.col_n = col_n;
+  p.level_tok_base = level_tok_base; p.idx_width = idx_width;
+  p.N = N; p.BW = BW; p.C = 1; p.K = K; p.L = L;
+  p.apply_expand = apply_expand; p.apply_advance = apply_advance && apply_expand && shard_child != nullptr;
+  p.neg_inf = -INFINITY;
+  if (apply_expand) {
+    FR_CHECK_ARG(token_ids_in && token_ids_out && token_ids_in != token_ids_out && L > 0);
+    FR_CHECK_SUPPORTED(K <= BW);
+  }
+  if (p.apply_advance) FR_CHECK_ARG(node_in && node_ids_out && node_in != node_ids_out);
+  int tp2 = 1;
+  while (tp2 < S * K) tp2 <<= 1;
+  const size_t smem = static_cast<size_t>(tp2) * 8 + static_cast<size_t>(K) * 20 + 16;
+  if (smem > 48 * 1024) {
+    if (cudaFuncSetAttribute(merge_shards_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+      return FR_ERR_CUDA;
+  }
+  merge_shards_kernel<<<N, kThreads, smem, stream>>>(mp);
+  return launch_status();
+}

@@ -1,0 +1,121 @@
+// Shared helpers for the sm_100a kernels of the quantized SID decode step.
+//
+// Conventions used by every kernel in this directory:
+//   * entry points are extern "C", take raw device pointers + sizes + a
+//     cudaStream_t, allocate nothing, and return an int status (0 = ok);
+//   * floating-point steps whose result is later compared bit-for-bit with
+//     the CPU oracle use the explicit round-to-nearest intrinsics
+//     (__fmul_rn, __fadd_rn, __fdiv_rn, __fsqrt_rn) so that nvcc can neither
+//     contract them into FMAs nor replace them by approximations;
+//   * sums of squares are accumulated in fp64 and rounded once to fp32, which
+//     makes the result independent of the reduction order.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/flashrec_b200.h"
+
+namespace fr {
+
+constexpr float kFp8Max = 448.0f;
+constexpr float kAmaxFloor = 1e-12f;  // clamp(min=1e-12) of the per-row amax
+
+#define FR_CHECK_ARG(cond)                \
+  do {                                    \
+    if (!(cond)) return FR_ERR_BAD_ARG;   \
+  } while (0)
+
+#define FR_CHECK_SUPPORTED(cond)            \
+  do {                                      \
+    if (!(cond)) return FR_ERR_UNSUPPORTED; \
+  } while (0)
+
+static inline int launch_status() {
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? FR_OK : FR_ERR_CUDA;
+}
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static inline int ceil_div(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
+
+// ---------------------------------------------------------------------------
+// device helpers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// bf16 <-> fp32 on raw bit patterns (a bf16 is the upper half of an fp32).
+__device__ __forceinline__ float bf16lo(uint32_t packed) { return __uint_as_float(packed << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
+
+// Round-to-nearest-even fp32 -> bf16, result returned as fp32 (lower 16 bits 0).
+__device__ __forceinline__ float round_bf16(float x) {
+  return __bfloat162float(__float2bfloat16_rn(x));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Two fp32 -> two e4m3 bytes (round to nearest even, saturating). `lo` lands in
+// the low byte.
+__device__ __forceinline__ uint16_t pack_e4m3x2(float lo, float hi) {
+  return static_cast<uint16_t>(__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3));
+}
+
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+  return static_cast<uint32_t>(pack_e4m3x2(a, b)) | (static_cast<uint32_t>(pack_e4m3x2(c, d)) << 16);
+}
+
+// clamp(y / scale, -448, 448): IEEE division, as torch does on fp32 tensors.
+__device__ __forceinline__ float quant_div(float y, float scale) {
+  float q = __fdiv_rn(y, scale);
+  return fminf(fmaxf(q, -kFp8Max), kFp8Max);
+}
+
+// scale = max(amax, 1e-12) / 448 in fp32.
+__device__ __forceinline__ float row_scale(float amax) {
+  return __fdiv_rn(fmaxf(amax, kAmaxFloor), kFp8Max);
+}
+
+// 1 / sqrt(x) as two correctly rounded fp32 operations (what a vectorised CPU
+// rsqrt computes); the hardware rsqrt approximation is deliberately avoided.
+__device__ __forceinline__ float rsqrt_rn(float x) { return __fdiv_rn(1.0f, __fsqrt_rn(x)); }
+
+// e4m3 byte -> fp32 (exact).
+__device__ __forceinline__ float e4m3_to_float(uint8_t b) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(b), __NV_E4M3);
+  return __half2float(*reinterpret_cast<__half*>(&h));
+}
+
+// Order-preserving map fp32 -> uint32 (larger float <=> larger key; -0 < +0).
+__device__ __forceinline__ uint32_t float_to_key(float f) {
+  uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_to_float(uint32_t k) {
+  uint32_t u = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
+  return __uint_as_float(u);
+}
+
+}  // namespace fr

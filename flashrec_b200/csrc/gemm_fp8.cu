@@ -1,0 +1,375 @@
+// W8A8 FP8 GEMM for the decode-step linear layers (qkv / o / gate_up / down and
+// the SID lm_head):
+//
+//     out[m, n] = cast( (sum_k a[m,k] * b[n,k]) * scale_a[m] * scale_b[n] ) (+ bias[n])
+//
+// a: e4m3 [M, K] row-major (per-token scales), b: e4m3 [N, K] row-major — the
+// reference keeps the weight as the `.t()` view of exactly this buffer
+// (layers/linear.py:104-110) — with per-output-channel scales. Stands in for
+// Linear.forward_fp8 -> fp8_scaled_mm (layers/linear.py:134-172,
+// kernel/sglops.py:99-140).
+//
+// sm_100a design: a persistent, warp-specialised kernel, one CTA per SM.
+//   warp 0      TMA producer: 128x128-byte A tile + BLOCK_N x128-byte B tile per
+//               stage, 128-byte swizzle, mbarrier complete_tx
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma
+//               (kind::f8f6f4, M=128, N=BLOCK_N, K=32 per instruction, both
+//               operands K-major straight from shared memory), accumulating
+//               fp32 in TMEM; tcgen05.commit frees the stage / publishes the tile
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp its own lane
+//               quadrant), apply per-token x per-channel scales in fp32, round
+//               once to bf16 (or keep fp32 for the lm_head logits), store
+// Two accumulator buffers in TMEM let the epilogue of tile i overlap the
+// main loop of tile i+1.
+#include "fr_common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace fr {
+
+int* device_status_ptr();  // capi.cu
+
+namespace gemm {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockK = 128;  // bytes == e4m3 elements: one 128-byte swizzle span
+constexpr int kUmmaK = 32;
+constexpr int kThreads = 192;
+constexpr int kEpiThreads = 128;
+
+template <int BLOCK_N>
+struct Cfg {
+  static constexpr int kStageA = kBlockM * kBlockK;
+  static constexpr int kStageB = BLOCK_N * kBlockK;
+  static constexpr int kStageBytes = kStageA + kStageB;
+  static constexpr int kStages = BLOCK_N == 256 ? 4 : (BLOCK_N == 128 ? 6 : 8);
+  static constexpr int kTmemCols = 2 * BLOCK_N;  // two accumulator buffers (power of two >= 32)
+  static constexpr int kScaleBytes = 2 * BLOCK_N * 4 * 2;  // scale_b and bias staging, double buffered
+  static constexpr int kBarBytes = (2 * kStages + 4) * 8 + 16;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kScaleBytes + kBarBytes;
+};
+
+template <typename OutT>
+__device__ __forceinline__ void store_chunk32(OutT* dst, const float (&v)[32], int ncols_valid);
+
+template <>
+__device__ __forceinline__ void store_chunk32<__nv_bfloat16>(__nv_bfloat16* dst, const float (&v)[32], int nvalid) {
+  if (nvalid >= 32) {
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 o;
+      o.x = pack_bf16(v[8 * i + 0], v[8 * i + 1]);
+      o.y = pack_bf16(v[8 * i + 2], v[8 * i + 3]);
+      o.z = pack_bf16(v[8 * i + 4], v[8 * i + 5]);
+      o.w = pack_bf16(v[8 * i + 6], v[8 * i + 7]);
+      d4[i] = o;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < nvalid) dst[i] = __float2bfloat16_rn(v[i]);
+  }
+}
+
+template <>
+__device__ __forceinline__ void store_chunk32<float>(float* dst, const float (&v)[32], int nvalid) {
+  if (nvalid >= 32) {
+    float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) d4[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < nvalid) dst[i] = v[i];
+  }
+}
+
+template <int BLOCK_N, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                OutT* __restrict__ out, int64_t ldo, const float* __restrict__ scale_a,
+                const float* __restrict__ scale_b, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
+                int* status) {
+  using C = Cfg<BLOCK_N>;
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte-swizzled operand tiles need a 1024-byte aligned base.
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+
+  float* sb_stage = reinterpret_cast<float*>(smem + C::kStages * C::kStageBytes);  // [2][BLOCK_N]
+  float* bias_stage = sb_stage + 2 * BLOCK_N;                                      // [2][BLOCK_N]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes + C::kScaleBytes);
+  const uint32_t bar_full = ptx::smem_u32(bars);                      // [kStages]
+  const uint32_t bar_empty = bar_full + 8 * C::kStages;               // [kStages]
+  const uint32_t bar_tfull = bar_empty + 8 * C::kStages;              // [2]
+  const uint32_t bar_tempty = bar_tfull + 16;                         // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_blocks = (M + kBlockM - 1) / kBlockM;
+  const int n_blocks = (N + BLOCK_N - 1) / BLOCK_N;
+  const int num_tiles = m_blocks * n_blocks;
+  const int num_kb = (K + kBlockK - 1) / kBlockK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      ptx::mbar_init(bar_full + 8 * s, 1);
+      ptx::mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(bar_tfull + 8 * b, 1);
+      ptx::mbar_init(bar_tempty + 8 * b, kEpiThreads / 32);
+    }
+    *abort_flag = 0;
+    ptx::mbar_init_fence();
+    ptx::prefetch_tmap(&tmap_a);
+    ptx::prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(tmem_slot), C::kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ---------------------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % m_blocks) * kBlockM;
+        const int n0 = (tile / m_blocks) * BLOCK_N;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = ptx::mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, status, 1);
+          if (!ok) break;
+          const uint32_t sa = base + stage * C::kStageBytes;
+          const uint32_t sbm = sa + C::kStageA;
+          ptx::mbar_expect_tx(bar_full + 8 * stage, C::kStageBytes);
+          ptx::tma_load_2d(sa, &tmap_a, kb * kBlockK, m0, bar_full + 8 * stage);
+          ptx::tma_load_2d(sbm, &tmap_b, kb * kBlockK, n0, bar_full + 8 * stage);
+          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer -----------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::make_idesc(0u, 0u, kBlockM, BLOCK_N);
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const uint32_t buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        ok = ptx::mbar_wait(bar_tempty + 8 * buf, acc_phase ^ 1u, abort_flag, status, 2);
+        if (!ok) break;
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BLOCK_N;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = ptx::mbar_wait(bar_full + 8 * stage, phase, abort_flag, status, 3);
+          if (!ok) break;
+          ptx::tc_fence_after();
+          const uint32_t sa = base + stage * C::kStageBytes;
+          const uint64_t a_desc = ptx::smem_desc_sw128(sa);
+          const uint64_t b_desc = ptx::smem_desc_sw128(sa + C::kStageA);
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            // +32 bytes along K inside the swizzled 128-byte row == +2 in the (addr >> 4) field
+            ptx::mma_f8f6f4(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          ptx::tc_commit(bar_empty + 8 * stage);  // stage reusable once these MMAs have read it
+          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) ptx::tc_commit(bar_tfull + 8 * buf);  // accumulator complete
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------ epilogue -------------------------------
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may access
+    const int epi_tid = threadIdx.x - 64;
+    bool ok = true;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      const int m0 = (tile % m_blocks) * kBlockM;
+      const int n0 = (tile / m_blocks) * BLOCK_N;
+      const uint32_t buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      float* sbs = sb_stage + buf * BLOCK_N;
+      float* bss = bias_stage + buf * BLOCK_N;
+      for (int i = epi_tid; i < BLOCK_N; i += kEpiThreads) {
+        const int n = n0 + i;
+        sbs[i] = n < N ? __ldg(scale_b + n) : 0.f;
+        bss[i] = (bias != nullptr && n < N) ? __bfloat162float(bias[n]) : 0.f;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+      const int row = m0 + quad * 32 + lane;
+      const float sa = row < M ? __ldg(scale_a + row) : 0.f;
+      int okw = 0;
+      if (lane == 0) okw = ptx::mbar_wait(bar_tfull + 8 * buf, acc_phase, abort_flag, status, 4) ? 1 : 0;
+      okw = __shfl_sync(0xffffffffu, okw, 0);
+      if (!okw) { ok = false; break; }
+      ptx::tc_fence_after();
+      const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BLOCK_N;
+      OutT* out_row = out + static_cast<int64_t>(row) * ldo + n0;
+#pragma unroll 1
+      for (int c = 0; c < BLOCK_N / 32; ++c) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(taddr_row + c * 32, r);
+        ptx::tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float t = __fmul_rn(__fmul_rn(__uint_as_float(r[j]), sa), sbs[c * 32 + j]);
+          if (bias != nullptr) t = __fadd_rn(round_bf16(t), bss[c * 32 + j]);
+          v[j] = t;
+        }
+        const int nvalid = N - (n0 + c * 32);
+        if (row < M && nvalid > 0) store_chunk32<OutT>(out_row + c * 32, v, nvalid);
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(bar_tempty + 8 * buf);
+    }
+  }
+
+  // common exit: all roles converge, then the allocating warp frees TMEM
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // an aborted pipeline may still have TMA tiles in flight towards this
+    // CTA's shared memory: give them (bounded) time to land before exiting
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) return nullptr;
+    if (q != cudaDriverEntryPointSuccess) return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// e4m3 matrix [rows, cols] with row pitch `ld` bytes; box = 128 bytes x box_rows, 128-byte swizzle.
+static int make_tmap_u8(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return FR_ERR_CUDA;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockK), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FR_OK : FR_ERR_CUDA;
+}
+
+static int sm_count() {
+  static int n = []() {
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
+    return v;
+  }();
+  return n;
+}
+
+// Tile-width choice: whole waves of 128 x BLOCK_N tiles over the SMs, discounted
+// by how far a narrower tile falls below the tensor-pipe rate (a 128x64 tile
+// needs 192 B/clk of shared-memory operand reads against 128 B/clk available).
+static int pick_block_n(int M, int N) {
+  const int sms = sm_count();
+  const int cand[3] = {256, 128, 64};
+  const double rate[3] = {1.0, 0.95, 0.65};
+  double best = -1.0;
+  int best_n = 128;
+  for (int i = 0; i < 3; ++i) {
+    const int64_t tiles = static_cast<int64_t>(ceil_div(M, kBlockM)) * ceil_div(N, cand[i]);
+    const int64_t waves = (tiles + sms - 1) / sms;
+    const double useful = static_cast<double>(N) / (static_cast<double>(ceil_div(N, cand[i])) * cand[i]);
+    const double eff = static_cast<double>(tiles) / static_cast<double>(waves * sms) * rate[i] * useful;
+    if (eff > best + 1e-9) { best = eff; best_n = cand[i]; }
+  }
+  return best_n;
+}
+
+template <int BLOCK_N, typename OutT>
+static int launch(const void* a, const void* b, const float* sa, const float* sb, const void* bias, void* out,
+                  int64_t ldo, int M, int N, int K, int64_t lda, int64_t ldb, cudaStream_t stream) {
+  using C = Cfg<BLOCK_N>;
+  CUtensorMap ta, tb;
+  int st = make_tmap_u8(&ta, a, M, K, lda, kBlockM);
+  if (st != FR_OK) return st;
+  st = make_tmap_u8(&tb, b, N, K, ldb, BLOCK_N);
+  if (st != FR_OK) return st;
+  auto kern = gemm_fp8_kernel<BLOCK_N, OutT>;
+  static bool attr_done = false;  // per template instantiation
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
+      return FR_ERR_CUDA;
+    attr_done = true;
+  }
+  int* status = device_status_ptr();
+  if (!status) return FR_ERR_CUDA;
+  const int tiles = ceil_div(M, kBlockM) * ceil_div(N, BLOCK_N);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(ta, tb, static_cast<OutT*>(out), ldo, sa, sb,
+                                                  static_cast<const __nv_bfloat16*>(bias), M, N, K, status);
+  return launch_status();
+}
+
+}  // namespace gemm
+}  // namespace fr
+
+using namespace fr;
+
+extern "C" int fr_gemm_fp8_w8a8(const void* a, const void* b, const float* scale_a, const float* scale_b,
+                                const void* bias, void* out, int out_is_f32, int M, int N, int K, int64_t lda,
+                                int64_t ldb, int64_t ldo, int block_n_hint, cudaStream_t stream) {
+  FR_CHECK_ARG(M >= 0 && N > 0 && K > 0);
+  if (M == 0) return FR_OK;
+  FR_CHECK_ARG(a && b && scale_a && scale_b && out);
+  // TMA: 16-byte aligned base and row pitch; vector stores: 16-byte aligned output rows
+  FR_CHECK_ARG(aligned16(a) && aligned16(b) && aligned16(out));
+  FR_CHECK_ARG(lda >= K && ldb >= K && ldo >= N && lda % 16 == 0 && ldb % 16 == 0);
+  FR_CHECK_ARG(out_is_f32 ? (ldo % 4 == 0) : (ldo % 8 == 0));
+  FR_CHECK_ARG(K % 16 == 0);
+  FR_CHECK_SUPPORTED(out_is_f32 ? (bias == nullptr) : true);
+  int bn = block_n_hint;
+  if (bn != 64 && bn != 128 && bn != 256) bn = gemm::pick_block_n(M, N);
+#define FR_GEMM_CASE(BN)                                                                                          \
+  case BN:                                                                                                        \
+    return out_is_f32 ? gemm::launch<BN, float>(a, b, scale_a, scale_b, bias, out, ldo, M, N, K, lda, ldb, stream) \
+                      : gemm::launch<BN, __nv_bfloat16>(a, b, scale_a, scale_b, bias, out, ldo, M, N, K, lda, ldb, stream)
+  switch (bn) {
+    FR_GEMM_CASE(256);
+    FR_GEMM_CASE(128);
+    FR_GEMM_CASE(64);
+    default: break;
+  }
+#undef FR_GEMM_CASE
+  return FR_ERR_UNSUPPORTED;
+}

@@ -1,0 +1,289 @@
+// Data-movement kernels around the attention of one decode step:
+//
+//   fr_qk_norm_rope_kv_fp8   per-head RMSNorm of Q and K, NeoX RoPE, Q written
+//                            back in place (bf16), K -> bf16 -> e4m3 and V -> e4m3
+//                            scattered to their KV-pool slots. Stands in for
+//                            fused_qk_norm_rope_store_fp8 (kernel/qk_rope_kv.py:28-250).
+//   fr_store_kv_fp8          plain bf16 -> e4m3 scatter of K and V
+//                            (TokenToKVPool.store, kvcache/pool.py:121-139).
+//   fr_gather_kv_indices     ragged copy req_to_token[row, :seq_len] -> flat slot
+//                            list + indptr (gather_kv_indices, attention/kv_indices.py:20-132).
+//   fr_embedding_bf16        token-embedding row gather (models/qwen3.py:266).
+//
+// All are HBM-bound; a group of D/8 lanes owns one (token, head) pair and moves
+// 8 bf16 per lane (4 from each rotary half) with 8-byte accesses.
+#include "fr_common.cuh"
+
+namespace fr {
+
+template <int LPH>
+__device__ __forceinline__ double group_sum(double v) {
+#pragma unroll
+  for (int o = LPH / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+struct RopeArgs {
+  __nv_bfloat16* q;
+  const __nv_bfloat16* k;
+  const __nv_bfloat16* v;
+  int64_t q_t, q_h, k_t, k_h, v_t, v_h;
+  const int64_t* pos;
+  const int64_t* loc;
+  const __nv_bfloat16* qw;
+  const __nv_bfloat16* kw;
+  float eps;
+  const float* cs;
+  int max_pos;
+  uint8_t* kc;
+  uint8_t* vc;
+  int64_t ck_s, ck_h, cv_s, cv_h;
+  int T, n_q, n_kv, num_slots;
+};
+
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&x)[4]) {
+  uint2 u = *reinterpret_cast<const uint2*>(p);
+  x[0] = bf16lo(u.x); x[1] = bf16hi(u.x); x[2] = bf16lo(u.y); x[3] = bf16hi(u.y);
+}
+
+// ROPE == false: plain conversion of K and V (no norm / rotation), used by fr_store_kv_fp8.
+template <int D, bool ROPE>
+__global__ void __launch_bounds__(256) qk_rope_kv_kernel(RopeArgs a) {
+  constexpr int LPH = D / 8;        // lanes per head
+  constexpr int HPW = 32 / LPH;     // heads per warp
+  constexpr int HALF = D / 2;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane % LPH;
+  const int heads_all = a.n_q + 2 * a.n_kv;
+  const int64_t item = (static_cast<int64_t>(blockIdx.x) * (256 / 32) + (threadIdx.x >> 5)) * HPW + lane / LPH;
+  const bool live = item < static_cast<int64_t>(a.T) * heads_all;
+  // dead groups still take part in the shuffles below
+  const int t = live ? static_cast<int>(item / heads_all) : 0;
+  const int hs = live ? static_cast<int>(item % heads_all) : 0;
+  const bool is_q = hs < a.n_q;
+  const bool is_k = !is_q && hs < a.n_q + a.n_kv;
+  const int h = is_q ? hs : (is_k ? hs - a.n_q : hs - a.n_q - a.n_kv);
+
+  const __nv_bfloat16* src = is_q ? (a.q + t * a.q_t + h * a.q_h)
+                                  : (is_k ? (a.k + t * a.k_t + h * a.k_h) : (a.v + t * a.v_t + h * a.v_h));
+  float lo[4] = {0.f, 0.f, 0.f, 0.f}, hi[4] = {0.f, 0.f, 0.f, 0.f};
+  if (live) {
+    load4(src + 4 * sub, lo);
+    load4(src + HALF + 4 * sub, hi);
+  }
+  double ss = 0.0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    ss += static_cast<double>(lo[i] * lo[i]);
+    ss += static_cast<double>(hi[i] * hi[i]);
+  }
+  ss = group_sum<LPH>(ss);  // all 32 lanes execute the shuffles
+  if (!live) return;
+
+  int64_t slot = 0;
+  if (!is_q) {
+    slot = a.loc[t];
+    if (slot < 0 || slot >= a.num_slots) return;  // never write outside the pool
+  }
+
+  if (ROPE && (is_q || is_k)) {
+    int64_t p = a.pos[t];
+    p = p < 0 ? 0 : (p >= a.max_pos ? a.max_pos - 1 : p);
+    const float4 c4 = *reinterpret_cast<const float4*>(a.cs + p * D + 4 * sub);
+    const float4 s4 = *reinterpret_cast<const float4*>(a.cs + p * D + HALF + 4 * sub);
+    const float cosv[4] = {c4.x, c4.y, c4.z, c4.w};
+    const float sinv[4] = {s4.x, s4.y, s4.z, s4.w};
+    const __nv_bfloat16* wsrc = is_q ? a.qw : a.kw;
+    float wlo[4], whi[4];
+    load4(wsrc + 4 * sub, wlo);
+    load4(wsrc + HALF + 4 * sub, whi);
+    const float var = static_cast<float>(ss / static_cast<double>(D));
+    const float rstd = rsqrt_rn(__fadd_rn(var, a.eps));
+    float y1[4], y2[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float x1 = __fmul_rn(__fmul_rn(lo[i], rstd), wlo[i]);
+      const float x2 = __fmul_rn(__fmul_rn(hi[i], rstd), whi[i]);
+      y1[i] = __fsub_rn(__fmul_rn(x1, cosv[i]), __fmul_rn(x2, sinv[i]));
+      y2[i] = __fadd_rn(__fmul_rn(x2, cosv[i]), __fmul_rn(x1, sinv[i]));
+    }
+    if (is_q) {
+      __nv_bfloat16* dst = a.q + t * a.q_t + h * a.q_h;
+      uint2 o1, o2;
+      o1.x = pack_bf16(y1[0], y1[1]); o1.y = pack_bf16(y1[2], y1[3]);
+      o2.x = pack_bf16(y2[0], y2[1]); o2.y = pack_bf16(y2[2], y2[3]);
+      *reinterpret_cast<uint2*>(dst + 4 * sub) = o1;
+      *reinterpret_cast<uint2*>(dst + HALF + 4 * sub) = o2;
+      return;
+    }
+    // K: round to bf16 first, as the reference does before the e4m3 cast
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      lo[i] = round_bf16(y1[i]);
+      hi[i] = round_bf16(y2[i]);
+    }
+  } else if (is_q) {
+    return;  // ROPE == false never has Q work
+  }
+  uint8_t* dst = is_k ? (a.kc + slot * a.ck_s + h * a.ck_h) : (a.vc + slot * a.cv_s + h * a.cv_h);
+  *reinterpret_cast<uint32_t*>(dst + 4 * sub) = pack_e4m3x4(lo[0], lo[1], lo[2], lo[3]);
+  *reinterpret_cast<uint32_t*>(dst + HALF + 4 * sub) = pack_e4m3x4(hi[0], hi[1], hi[2], hi[3]);
+}
+
+template <bool ROPE>
+static int launch_rope(const RopeArgs& a, int D, cudaStream_t stream) {
+  const int heads_all = a.n_q + 2 * a.n_kv;
+  const int64_t items = static_cast<int64_t>(a.T) * heads_all;
+  if (items == 0) return FR_OK;
+  if (D == 128) {
+    const int per_cta = 8 * 2;
+    qk_rope_kv_kernel<128, ROPE><<<ceil_div(items, per_cta), 256, 0, stream>>>(a);
+  } else if (D == 64) {
+    const int per_cta = 8 * 4;
+    qk_rope_kv_kernel<64, ROPE><<<ceil_div(items, per_cta), 256, 0, stream>>>(a);
+  } else {
+    return FR_ERR_UNSUPPORTED;
+  }
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// kv index gather
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) seq_scan_kernel(const int32_t* __restrict__ seq_lens,
+                                                       int32_t* __restrict__ indptr, int n) {
+  __shared__ int32_t warp_tot[32];
+  __shared__ int32_t carry_s;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) { carry_s = 0; indptr[0] = 0; }
+  __syncthreads();
+  for (int base = 0; base < n; base += 1024) {
+    const int i = base + threadIdx.x;
+    int32_t v = i < n ? max(seq_lens[i], 0) : 0;
+    int32_t x = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int32_t y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
+    }
+    if (lane == 31) warp_tot[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+      int32_t w = warp_tot[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int32_t y = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += y;
+      }
+      warp_tot[lane] = w;  // inclusive
+    }
+    __syncthreads();
+    const int32_t carry = carry_s;
+    const int32_t incl = carry + x + (warp > 0 ? warp_tot[warp - 1] : 0);
+    if (i < n) indptr[i + 1] = incl;
+    __syncthreads();
+    if (threadIdx.x == 1023) carry_s = incl;
+    __syncthreads();
+  }
+}
+
+__global__ void __launch_bounds__(256) gather_kv_kernel(const int32_t* __restrict__ table, int64_t stride,
+                                                       const int64_t* __restrict__ rows,
+                                                       const int32_t* __restrict__ seq_lens,
+                                                       const int32_t* __restrict__ indptr, int32_t* __restrict__ out,
+                                                       int n, int capacity) {
+  const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (r >= n) return;
+  const int lane = threadIdx.x & 31;
+  const int32_t sl = max(seq_lens[r], 0);
+  const int32_t off = indptr[r];
+  const int32_t* src = table + rows[r] * stride;
+  for (int i = lane; i < sl; i += 32) {
+    if (off + i < capacity) out[off + i] = __ldg(src + i);
+  }
+}
+
+__global__ void __launch_bounds__(256) embedding_kernel(const uint4* __restrict__ table, const int64_t* __restrict__ ids,
+                                                       uint4* __restrict__ out, int T, int vec_per_row, int vocab) {
+  const int64_t total = static_cast<int64_t>(T) * vec_per_row;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(i / vec_per_row);
+    const int c = static_cast<int>(i % vec_per_row);
+    int64_t id = ids[t];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    out[i] = __ldg(table + id * vec_per_row + c);
+  }
+}
+
+}  // namespace fr
+
+using namespace fr;
+
+static bool aligned8(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 7u) == 0; }
+static bool aligned4(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 3u) == 0; }
+
+extern "C" int fr_qk_norm_rope_kv_fp8(void* q, const void* k, const void* v, int64_t q_t, int64_t q_h, int64_t k_t,
+                                      int64_t k_h, int64_t v_t, int64_t v_h, const int64_t* positions,
+                                      const int64_t* loc, const void* q_weight, const void* k_weight, float eps,
+                                      const float* cos_sin, int max_pos, void* k_cache, void* v_cache, int64_t ck_s,
+                                      int64_t ck_h, int64_t cv_s, int64_t cv_h, int T, int n_q, int n_kv, int D,
+                                      int num_slots, cudaStream_t stream) {
+  FR_CHECK_ARG(T >= 0 && n_q >= 0 && n_kv >= 0 && D > 0 && max_pos > 0 && num_slots > 0);
+  if (T == 0) return FR_OK;
+  FR_CHECK_ARG(q && k && v && positions && loc && q_weight && k_weight && cos_sin && k_cache && v_cache);
+  FR_CHECK_SUPPORTED(D == 128 || D == 64);
+  FR_CHECK_ARG(aligned8(q) && aligned8(k) && aligned8(v) && aligned8(q_weight) && aligned8(k_weight));
+  FR_CHECK_ARG(q_t % 4 == 0 && q_h % 4 == 0 && k_t % 4 == 0 && k_h % 4 == 0 && v_t % 4 == 0 && v_h % 4 == 0);
+  FR_CHECK_ARG(aligned16(cos_sin) && aligned4(k_cache) && aligned4(v_cache));
+  FR_CHECK_ARG(ck_s % 4 == 0 && ck_h % 4 == 0 && cv_s % 4 == 0 && cv_h % 4 == 0);
+  RopeArgs a{static_cast<__nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v),
+             q_t, q_h, k_t, k_h, v_t, v_h, positions, loc, static_cast<const __nv_bfloat16*>(q_weight),
+             static_cast<const __nv_bfloat16*>(k_weight), eps, cos_sin, max_pos, static_cast<uint8_t*>(k_cache),
+             static_cast<uint8_t*>(v_cache), ck_s, ck_h, cv_s, cv_h, T, n_q, n_kv, num_slots};
+  return launch_rope<true>(a, D, stream);
+}
+
+extern "C" int fr_store_kv_fp8(const void* k, const void* v, int64_t k_t, int64_t k_h, int64_t v_t, int64_t v_h,
+                               const int64_t* loc, void* k_cache, void* v_cache, int64_t ck_s, int64_t ck_h,
+                               int64_t cv_s, int64_t cv_h, int T, int n_kv, int D, int num_slots,
+                               cudaStream_t stream) {
+  FR_CHECK_ARG(T >= 0 && n_kv >= 0 && D > 0 && num_slots > 0);
+  if (T == 0) return FR_OK;
+  FR_CHECK_ARG(k && v && loc && k_cache && v_cache);
+  FR_CHECK_SUPPORTED(D == 128 || D == 64);
+  FR_CHECK_ARG(aligned8(k) && aligned8(v) && k_t % 4 == 0 && k_h % 4 == 0 && v_t % 4 == 0 && v_h % 4 == 0);
+  FR_CHECK_ARG(aligned4(k_cache) && aligned4(v_cache) && ck_s % 4 == 0 && ck_h % 4 == 0 && cv_s % 4 == 0 && cv_h % 4 == 0);
+  RopeArgs a{nullptr, static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), 0, 0, k_t, k_h, v_t,
+             v_h, nullptr, loc, nullptr, nullptr, 0.f, nullptr, 1, static_cast<uint8_t*>(k_cache),
+             static_cast<uint8_t*>(v_cache), ck_s, ck_h, cv_s, cv_h, T, 0, n_kv, num_slots};
+  return launch_rope<false>(a, D, stream);
+}
+
+extern "C" int fr_gather_kv_indices(const int32_t* req_to_token, int64_t row_stride, const int64_t* rows,
+                                    const int32_t* seq_lens, int32_t* indptr_out, int32_t* out, int n,
+                                    int out_capacity, cudaStream_t stream) {
+  FR_CHECK_ARG(n >= 0 && out_capacity >= 0);
+  if (n == 0) return FR_OK;
+  FR_CHECK_ARG(req_to_token && rows && seq_lens && indptr_out && (out || out_capacity == 0));
+  seq_scan_kernel<<<1, 1024, 0, stream>>>(seq_lens, indptr_out, n);
+  if (launch_status() != FR_OK) return FR_ERR_CUDA;
+  if (out_capacity == 0) return FR_OK;
+  gather_kv_kernel<<<ceil_div(n, 8), 256, 0, stream>>>(req_to_token, row_stride, rows, seq_lens, indptr_out, out, n,
+                                                      out_capacity);
+  return launch_status();
+}
+
+extern "C" int fr_embedding_bf16(const void* table, const int64_t* ids, void* out, int T, int hidden, int vocab,
+                                 cudaStream_t stream) {
+  FR_CHECK_ARG(T >= 0 && hidden > 0 && hidden % 8 == 0 && vocab > 0);
+  if (T == 0) return FR_OK;
+  FR_CHECK_ARG(table && ids && out && aligned16(table) && aligned16(out));
+  const int vec = hidden / 8;
+  const int64_t total = static_cast<int64_t>(T) * vec;
+  int grid = ceil_div(total, 256);
+  if (grid > 148 * 16) grid = 148 * 16;
+  embedding_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint4*>(table), ids, static_cast<uint4*>(out), T, vec,
+                                            vocab);
+  return launch_status();
+}

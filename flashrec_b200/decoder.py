@@ -1,0 +1,168 @@
+"""Host-side call order of one Qwen3 decode step on the FP8 path — a mirror of
+``Qwen3Attention / Qwen3MLP / Qwen3DecoderLayer / Qwen3ForCausalLM``
+(models/qwen3.py:36-273) and of ``ForwardBatch`` (core.py:81-101). Every
+arithmetic step is one call into the sm_100a library; this file only sequences
+them and owns the weights.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+
+from flashrec_b200._lib import call, ptr, stream_ptr
+from flashrec_b200.attention import AttentionBackend, TokenToKVPool
+from flashrec_b200.kernel.qk_rope_kv import fused_qk_norm_rope_store_fp8
+from flashrec_b200.kernel.silu_fp8 import silu_and_mul_per_token_quant_fp8
+from flashrec_b200.layers import Linear, RMSNorm, RotaryEmbedding
+
+
+@dataclass
+class Qwen3Config:
+    hidden_size: int = 2048
+    num_attention_heads: int = 16
+    num_key_value_heads: int = 8
+    head_dim: int = 128
+    intermediate_size: int = 6144
+    num_hidden_layers: int = 28
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 1e6
+    max_position_embeddings: int = 8192
+    vocab_size: int = 151936 + 24576
+
+
+@dataclass
+class ForwardBatch:
+    """One decode forward; ``n_rows`` = total beam rows (core.py:81-101)."""
+
+    input_ids: torch.Tensor
+    req_pool_indices: Optional[torch.Tensor]
+    seq_lens: torch.Tensor
+    positions: torch.Tensor
+    out_cache_loc: torch.Tensor
+    is_prefill: bool = False
+    kv_indices: Optional[torch.Tensor] = None
+    kv_indptr: Optional[torch.Tensor] = None
+
+    @property
+    def n_rows(self) -> int:
+        return int(self.seq_lens.numel())
+
+
+class Qwen3Attention:
+    def __init__(self, cfg: Qwen3Config, layer_id: int, attn: AttentionBackend, rotary: RotaryEmbedding, device=None):
+        self.layer_id = layer_id
+        self.head_dim = cfg.head_dim
+        self.num_qo = cfg.num_attention_heads
+        self.num_kv = cfg.num_key_value_heads
+        self.qkv_proj = Linear(cfg.hidden_size, (self.num_qo + 2 * self.num_kv) * cfg.head_dim)
+        self.o_proj = Linear(self.num_qo * cfg.head_dim, cfg.hidden_size)
+        self.q_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, device=device)
+        self.k_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, device=device)
+        self.attn = attn
+        self.rotary = rotary
+
+    def forward(self, x, batch: ForwardBatch, *, q_fp8, a_scale) -> torch.Tensor:
+        t = int(q_fp8.shape[0])
+        qkv = self.qkv_proj.forward_fp8(q_fp8, a_scale, (t, self.qkv_proj.in_features), torch.bfloat16)
+        heads = qkv.view(t, self.num_qo + 2 * self.num_kv, self.head_dim)
+        q = heads[:, : self.num_qo]
+        k = heads[:, self.num_qo : self.num_qo + self.num_kv]
+        v = heads[:, self.num_qo + self.num_kv :]
+        pool = self.attn.kv_pool
+        fused_qk_norm_rope_store_fp8(
+            q, k, v, batch.positions, batch.out_cache_loc, self.q_norm.weight, self.k_norm.weight,
+            self.q_norm.eps, self.rotary.cos_sin_cache, pool.k[self.layer_id], pool.v[self.layer_id],
+        )
+        # the attention kernel reads the strided q view directly (no .contiguous() copy)
+        o = self.attn.forward(q, k, v, self.layer_id, batch, skip_store=True)
+        return self.o_proj(o.reshape(t, -1))
+
+
+class Qwen3MLP:
+    def __init__(self, cfg: Qwen3Config):
+        self.gate_up_proj = Linear(cfg.hidden_size, 2 * cfg.intermediate_size)
+        self.down_proj = Linear(cfg.intermediate_size, cfg.hidden_size)
+
+    def forward(self, x, *, q_fp8, a_scale) -> torch.Tensor:
+        rows = int(q_fp8.shape[0])
+        gu = self.gate_up_proj.forward_fp8(q_fp8, a_scale, (rows, self.gate_up_proj.in_features), torch.bfloat16)
+        y_fp8, y_scale = silu_and_mul_per_token_quant_fp8(gu)
+        return self.down_proj.forward_fp8(y_fp8, y_scale, (rows, self.down_proj.in_features), torch.bfloat16)
+
+
+class Qwen3DecoderLayer:
+    def __init__(self, cfg: Qwen3Config, layer_id: int, attn: AttentionBackend, rotary: RotaryEmbedding, device=None):
+        self.self_attn = Qwen3Attention(cfg, layer_id, attn, rotary, device=device)
+        self.mlp = Qwen3MLP(cfg)
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, device=device)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, device=device)
+
+    def forward(self, x, residual, batch: ForwardBatch):
+        """FP8 branch of Qwen3DecoderLayer.forward (models/qwen3.py:198-215)."""
+        if residual is None:
+            residual = x
+            q_fp8, a_scale = self.input_layernorm.quant_fp8(x)
+        else:
+            q_fp8, a_scale, residual = self.input_layernorm.quant_fp8(x, residual)
+        hidden = self.self_attn.forward(x, batch, q_fp8=q_fp8, a_scale=a_scale)
+        q_fp8, a_scale, residual = self.post_attention_layernorm.quant_fp8(hidden, residual)
+        hidden = self.mlp.forward(hidden, q_fp8=q_fp8, a_scale=a_scale)
+        return hidden, residual
+
+
+class Qwen3ForCausalLM:
+    """Embedding -> layers -> final (add+)RMSNorm; returns the normalised hidden
+    states, which the SID head consumes (models/qwen3.py:227-273)."""
+
+    def __init__(self, cfg: Qwen3Config, attn: AttentionBackend, device):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.rotary = RotaryEmbedding(cfg.head_dim, cfg.max_position_embeddings, cfg.rope_theta, device=device)
+        self.layers: List[Qwen3DecoderLayer] = [
+            Qwen3DecoderLayer(cfg, i, attn, self.rotary, device=device) for i in range(cfg.num_hidden_layers)
+        ]
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, device=device)
+        self.embed_tokens: Optional[torch.Tensor] = None  # bf16 [vocab, hidden]
+        self.attn = attn
+
+    def embed(self, input_ids: torch.Tensor) -> torch.Tensor:
+        ids = input_ids.reshape(-1).to(torch.int64)
+        out = torch.empty((ids.numel(), self.cfg.hidden_size), dtype=torch.bfloat16, device=ids.device)
+        call("fr_embedding_bf16", ptr(self.embed_tokens), ptr(ids), ptr(out), ids.numel(), self.cfg.hidden_size,
+             int(self.embed_tokens.shape[0]), stream_ptr(ids.device))
+        return out
+
+    def forward(self, batch: ForwardBatch) -> torch.Tensor:
+        x = self.embed(batch.input_ids)
+        residual = None
+        for layer in self.layers:
+            x, residual = layer.forward(x, residual, batch)
+        if residual is None:
+            return self.norm(x)
+        x, _ = self.norm(x, residual)
+        return x
+
+    # -- random initialisation used by the benchmark / tests --------------------
+    def init_random(self, seed: int = 0, std: float = 0.02, embed: bool = True) -> None:
+        """N(0, std) weights quantised per channel; norm weights = 1."""
+        g = torch.Generator(device=self.device)
+        g.manual_seed(seed)
+        cfg = self.cfg
+
+        def rnd(n, k):
+            return torch.randn((n, k), generator=g, device=self.device, dtype=torch.float32) * std
+
+        for layer in self.layers:
+            a = layer.self_attn
+            a.qkv_proj.load(rnd(a.qkv_proj.out_features, cfg.hidden_size), quantize_fp8=True)
+            a.o_proj.load(rnd(cfg.hidden_size, a.o_proj.in_features), quantize_fp8=True)
+            layer.mlp.gate_up_proj.load(rnd(2 * cfg.intermediate_size, cfg.hidden_size), quantize_fp8=True)
+            layer.mlp.down_proj.load(rnd(cfg.hidden_size, cfg.intermediate_size), quantize_fp8=True)
+        if embed:
+            self.embed_tokens = (
+                torch.randn((cfg.vocab_size, cfg.hidden_size), generator=g, device=self.device, dtype=torch.float32)
+                * std
+            ).to(torch.bfloat16)

@@ -1,0 +1,159 @@
+"""Element-wise / GEMM wrappers with the reference's ``flashrec.kernel.sglops``
+signatures (kernel/sglops.py:34-222), backed by the sm_100a library.
+
+Unlike the reference there is no torch branch: inputs must be CUDA tensors.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from flashrec_b200 import _lib
+from flashrec_b200._lib import call, ptr, require_cuda, stream_ptr
+
+_FP8 = torch.float8_e4m3fn
+
+
+def _rows2d(x: torch.Tensor, hidden: int) -> torch.Tensor:
+    x2 = x.reshape(-1, hidden)
+    return x2 if x2.is_contiguous() else x2.contiguous()
+
+
+def _bf16(x: torch.Tensor, what: str) -> None:
+    if x.dtype != torch.bfloat16:
+        raise TypeError(f"{what}: expected bfloat16, got {x.dtype}")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMSNorm, bf16 in/out (kernel/sglops.py:34-45)."""
+    require_cuda(x, weight)
+    _bf16(x, "rmsnorm x")
+    hidden = int(weight.numel())
+    x2 = _rows2d(x, hidden)
+    w = weight.reshape(-1).to(device=x.device, dtype=x.dtype).contiguous()
+    out = torch.empty_like(x2)
+    call("fr_rmsnorm_bf16", ptr(x2), None, ptr(w), float(eps), ptr(out), x2.shape[0], hidden, stream_ptr(x.device))
+    return out.view(x.shape)
+
+
+def fused_add_rmsnorm(
+    x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """``residual += x`` (in place) then RMSNorm(residual) (kernel/sglops.py:48-61)."""
+    require_cuda(x, residual, weight)
+    _bf16(x, "fused_add_rmsnorm x")
+    _bf16(residual, "fused_add_rmsnorm residual")
+    hidden = int(weight.numel())
+    x2 = _rows2d(x, hidden)
+    r2 = residual.reshape(-1, hidden)
+    copy_back = not r2.is_contiguous()
+    r2c = r2.contiguous() if copy_back else r2
+    w = weight.reshape(-1).to(device=x.device, dtype=x.dtype).contiguous()
+    out = torch.empty_like(x2)
+    call("fr_rmsnorm_bf16", ptr(x2), ptr(r2c), ptr(w), float(eps), ptr(out), x2.shape[0], hidden,
+         stream_ptr(x.device))
+    if copy_back:
+        residual.copy_(r2c.view(residual.shape))
+        return out.view(x.shape), residual
+    return out.view(x.shape), r2c.view(residual.shape)
+
+
+def per_token_quant_fp8(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per-row e4m3 quantisation; returns (q [rows, hidden], scale [rows, 1]) (kernel/sglops.py:84-96)."""
+    require_cuda(x)
+    hidden = int(x.shape[-1])
+    x2 = _rows2d(x, hidden)
+    if x2.dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError(f"per_token_quant_fp8: expected bfloat16 or float32, got {x2.dtype}")
+    rows = int(x2.shape[0])
+    q = torch.empty((rows, hidden), dtype=_FP8, device=x.device)
+    s = torch.empty((rows, 1), dtype=torch.float32, device=x.device)
+    call("fr_token_quant_fp8", ptr(x2), int(x2.dtype == torch.float32), ptr(q), ptr(s), rows, hidden,
+         stream_ptr(x.device))
+    return q, s
+
+
+def fp8_scaled_mm(
+    a_fp8: torch.Tensor,
+    b_fp8: torch.Tensor,
+    scale_a: torch.Tensor,
+    scale_b: torch.Tensor,
+    out_dtype: torch.dtype,
+    bias: Optional[torch.Tensor] = None,
+    *,
+    block_n: int = 0,
+) -> torch.Tensor:
+    """a: [M,K] e4m3 row-major, b: [K,N] e4m3 column-major (the ``.t()`` view of an
+    [N,K] weight), scale_a: [M,1] or [M], scale_b: [N] (kernel/sglops.py:99-140).
+    ``out_dtype`` is bfloat16, or float32 (no bias) for the lm_head logits."""
+    require_cuda(a_fp8, b_fp8, scale_a, scale_b, bias)
+    if a_fp8.dtype != _FP8 or b_fp8.dtype != _FP8:
+        raise TypeError("fp8_scaled_mm: operands must be float8_e4m3fn")
+    if b_fp8.dim() != 2 or b_fp8.stride(0) != 1:
+        raise ValueError("fp8_scaled_mm: b must be the column-major [K,N] view of an [N,K] weight")
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError(f"fp8_scaled_mm: unsupported out_dtype {out_dtype}")
+    m, k = int(a_fp8.shape[0]), int(a_fp8.shape[1])
+    n = int(b_fp8.shape[1])
+    if int(b_fp8.shape[0]) != k:
+        raise ValueError("fp8_scaled_mm: inner dimensions differ")
+    a = a_fp8 if a_fp8.stride(1) == 1 else a_fp8.contiguous()
+    sa = scale_a.reshape(-1).to(torch.float32)
+    sb = scale_b.reshape(-1).to(torch.float32)
+    if sa.numel() == 1:
+        sa = sa.expand(m)
+    if sb.numel() == 1:
+        sb = sb.expand(n)
+    sa = sa.contiguous()
+    sb = sb.contiguous()
+    if sa.numel() != m or sb.numel() != n:
+        raise ValueError("fp8_scaled_mm: scale shapes do not match [M] / [N]")
+    bias_c = None
+    if bias is not None:
+        bias_c = bias.to(dtype=torch.bfloat16).contiguous()
+    out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    call("fr_gemm_fp8_w8a8", ptr(a), ptr(b_fp8), ptr(sa), ptr(sb), ptr(bias_c), ptr(out),
+         int(out_dtype == torch.float32), m, n, k, a.stride(0), b_fp8.stride(1), out.stride(0), int(block_n),
+         stream_ptr(a.device))
+    return out
+
+
+def silu_and_mul(x: torch.Tensor) -> torch.Tensor:
+    """SwiGLU ``silu(x[..., :d]) * x[..., d:]`` in bf16 (kernel/sglops.py:143-151)."""
+    require_cuda(x)
+    _bf16(x, "silu_and_mul x")
+    last = int(x.shape[-1])
+    d = last // 2
+    x2 = _rows2d(x, last)
+    out = torch.empty((x2.shape[0], d), dtype=x.dtype, device=x.device)
+    call("fr_silu_mul_bf16", ptr(x2), ptr(out), x2.shape[0], d, stream_ptr(x.device))
+    return out.view(*x.shape[:-1], d)
+
+
+def store_kv_cache(
+    k_cache: torch.Tensor, v_cache: torch.Tensor, loc: torch.Tensor, k: torch.Tensor, v: torch.Tensor
+) -> None:
+    """k_cache[loc] = k; v_cache[loc] = v with bf16 -> e4m3 conversion.
+    Caches are [slots, H*D] (or [slots, H, D]) e4m3; k/v are [n, H*D] bf16 (kernel/sglops.py:207-222)."""
+    require_cuda(k_cache, v_cache, loc, k, v)
+    if k_cache.dtype != _FP8:
+        raise TypeError("store_kv_cache: only the float8_e4m3fn pool is supported")
+    n = int(loc.numel())
+    if n == 0:
+        return
+    row = int(k.numel() // n)
+    d = 128 if row % 128 == 0 else 64
+    h = row // d
+    k2 = k.reshape(n, h, d)
+    v2 = v.reshape(n, h, d)
+    if k2.stride(-1) != 1:
+        k2 = k2.contiguous()
+    if v2.stride(-1) != 1:
+        v2 = v2.contiguous()
+    loc64 = loc.reshape(-1).to(torch.int64).contiguous()
+    kc = k_cache.view(k_cache.shape[0], -1)
+    vc = v_cache.view(v_cache.shape[0], -1)
+    call("fr_store_kv_fp8", ptr(k2), ptr(v2), k2.stride(0), k2.stride(1), v2.stride(0), v2.stride(1), ptr(loc64),
+         ptr(kc), ptr(vc), kc.stride(0), d, vc.stride(0), d, n, h, d, int(kc.shape[0]), stream_ptr(k.device))

@@ -1,0 +1,260 @@
+/*
+ * flashrec_b200 — C ABI of the sm_100a kernels for the quantized SID decode step.
+ *
+ * Every entry point takes raw DEVICE pointers, explicit sizes/strides and the
+ * cudaStream_t to launch on; none allocates, synchronises or throws (unless its
+ * comment says otherwise). The return value is a status code: 0 on success,
+ * negative otherwise. Row-major contiguous layouts unless a stride is given.
+ * "e4m3" is float8_e4m3fn (max 448). Each declaration names the function of the
+ * reference engine (path inside its `python/flashrec/` tree) that it stands in
+ * for.
+ */
+#ifndef FLASHREC_B200_H_
+#define FLASHREC_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef __CUDA_RUNTIME_H__
+typedef struct CUstream_st* cudaStream_t;
+#endif
+
+enum fr_status {
+  FR_OK = 0,
+  FR_ERR_BAD_ARG = -1,     /* null / misaligned pointer, negative size, shape mismatch */
+  FR_ERR_UNSUPPORTED = -2, /* shape outside what the kernel was built for */
+  FR_ERR_CUDA = -3,        /* a CUDA runtime / driver call or the launch failed */
+  FR_ERR_TIMEOUT = -4      /* a bounded device-side wait gave up (see fr_device_status) */
+};
+
+/* Library / build identification: returns a static string. */
+const char* fr_version(void);
+
+/* Reads and clears the sticky device-side status word on the current device
+ * (0 = clean, otherwise the FR_ERR_* code and site recorded by a kernel whose
+ * bounded wait ran out). Synchronises the device; meant for tests and error
+ * paths, not the step loop. */
+int fr_device_status(int* status_out, int* site_out);
+
+/* ---- activation quantisers (HBM bound) ---------------------------------- */
+
+/* RMSNorm -> per-row e4m3. If `residual` is non-null it is updated in place
+ * (residual += x, rounded to bf16) and the norm runs on the updated residual.
+ * x, residual: bf16 [rows, hidden]; weight: bf16 [hidden]; q_out: e4m3
+ * [rows, hidden]; scale_out: f32 [rows]. hidden % 8 == 0.
+ * Reference: RMSNorm.quant_fp8 (layers/norm.py:28-42) ->
+ * rmsnorm_per_token_quant_fp8 / fused_add_rmsnorm_per_token_quant_fp8
+ * (kernel/rms_fp8.py:120-145). */
+int fr_rms_quant_fp8(const void* x, void* residual, const void* weight, float eps, void* q_out, float* scale_out,
+                     int rows, int hidden, cudaStream_t stream);
+
+/* bf16 RMSNorm (optionally residual += x first). y_out: bf16 [rows, hidden].
+ * Reference: rmsnorm / fused_add_rmsnorm (kernel/sglops.py:34-61). */
+int fr_rmsnorm_bf16(const void* x, void* residual, const void* weight, float eps, void* y_out, int rows, int hidden,
+                    cudaStream_t stream);
+
+/* Per-row e4m3 quantisation, scale = max(amax,1e-12)/448. x is bf16
+ * (x_is_f32 == 0, hidden % 8 == 0) or f32 (x_is_f32 != 0, hidden % 4 == 0).
+ * Reference: per_token_quant_fp8 (kernel/sglops.py:84-96) and
+ * quantize_weight_fp8 (layers/linear.py:26-32). */
+int fr_token_quant_fp8(const void* x, int x_is_f32, void* q_out, float* scale_out, int rows, int hidden,
+                       cudaStream_t stream);
+
+/* silu(x[:, :d]) * x[:, d:] -> per-row e4m3. x: bf16 [rows, 2d]; q_out: e4m3
+ * [rows, d]; scale_out: f32 [rows]. d % 8 == 0, d <= 16384.
+ * Reference: silu_and_mul_per_token_quant_fp8 (kernel/silu_fp8.py:86-119). */
+int fr_silu_mul_quant_fp8(const void* x, void* q_out, float* scale_out, int rows, int d, cudaStream_t stream);
+
+/* Unquantised SwiGLU, bf16 out [rows, d].
+ * Reference: silu_and_mul (kernel/sglops.py:143-151). */
+int fr_silu_mul_bf16(const void* x, void* y_out, int rows, int d, cudaStream_t stream);
+
+/* ---- W8A8 FP8 GEMM (tensor-core bound) ----------------------------------- */
+
+/* out[m,n] = cast((sum_k a[m,k] b[n,k]) * scale_a[m] * scale_b[n]) (+ bias[n]).
+ * a: e4m3 [M,K] pitch lda; b: e4m3 [N,K] pitch ldb (the weight as stored; the
+ * reference passes its `.t()` view); scale_a f32 [M]; scale_b f32 [N]; bias
+ * bf16 [N] or NULL; out: bf16 (out_is_f32 == 0) or f32 [M,N] pitch ldo
+ * (elements). K % 16 == 0; pitches in elements, multiples of 16 for a/b.
+ * block_n_hint: 0 = choose, else 64 / 128 / 256. Reports FR_ERR_TIMEOUT
+ * through fr_device_status if a pipeline wait gives up.
+ * Reference: Linear.forward_fp8 -> fp8_scaled_mm (layers/linear.py:134-172,
+ * kernel/sglops.py:99-140). */
+int fr_gemm_fp8_w8a8(const void* a, const void* b, const float* scale_a, const float* scale_b, const void* bias,
+                     void* out, int out_is_f32, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldo,
+                     int block_n_hint, cudaStream_t stream);
+
+/* ---- attention-side data movement (HBM bound) ---------------------------- */
+
+/* Per-head RMSNorm of Q and K + NeoX RoPE; Q is rewritten in place (bf16), K is
+ * rounded to bf16 then e4m3 and V to e4m3, both scattered to slot loc[t] of the
+ * KV pool (unscaled). q/k/v: bf16 views [T, heads, D] with element strides
+ * (token, head), D contiguous; positions, loc: int64 [T]; weights bf16 [D];
+ * cos_sin: f32 [max_pos, D] = [cos(0..D/2) | sin(0..D/2)]; caches e4m3 with
+ * byte strides (slot, head). D in {64, 128}. Slots outside [0, num_slots) are
+ * skipped, positions are clamped.
+ * Reference: fused_qk_norm_rope_store_fp8 (kernel/qk_rope_kv.py:165-250). */
+int fr_qk_norm_rope_kv_fp8(void* q, const void* k, const void* v, int64_t q_t, int64_t q_h, int64_t k_t, int64_t k_h,
+                           int64_t v_t, int64_t v_h, const int64_t* positions, const int64_t* loc,
+                           const void* q_weight, const void* k_weight, float eps, const float* cos_sin, int max_pos,
+                           void* k_cache, void* v_cache, int64_t ck_s, int64_t ck_h, int64_t cv_s, int64_t cv_h, int T,
+                           int n_q, int n_kv, int D, int num_slots, cudaStream_t stream);
+
+/* bf16 K/V -> e4m3 scatter into the pool.
+ * Reference: TokenToKVPool.store (kvcache/pool.py:121-139). */
+int fr_store_kv_fp8(const void* k, const void* v, int64_t k_t, int64_t k_h, int64_t v_t, int64_t v_h,
+                    const int64_t* loc, void* k_cache, void* v_cache, int64_t ck_s, int64_t ck_h, int64_t cv_s,
+                    int64_t cv_h, int T, int n_kv, int D, int num_slots, cudaStream_t stream);
+
+/* indptr_out[0..n] = exclusive scan of seq_lens; out[indptr[i] + j] =
+ * req_to_token[rows[i], j] for j < seq_lens[i]. req_to_token int32 with element
+ * row stride; rows int64 [n]; seq_lens int32 [n]; out int32 [out_capacity].
+ * Reference: gather_kv_indices (attention/kv_indices.py:63-132). */
+int fr_gather_kv_indices(const int32_t* req_to_token, int64_t row_stride, const int64_t* rows, const int32_t* seq_lens,
+                         int32_t* indptr_out, int32_t* out, int n, int out_capacity, cudaStream_t stream);
+
+/* out[t, :] = table[ids[t], :] (bf16, hidden % 8 == 0).
+ * Reference: nn.Embedding in Qwen3ForCausalLM.forward (models/qwen3.py:266). */
+int fr_embedding_bf16(const void* table, const int64_t* ids, void* out, int T, int hidden, int vocab,
+                      cudaStream_t stream);
+
+/* ---- decode attention over the e4m3 KV pool ------------------------------ */
+
+/* shared_len_out[g] = longest slot-list prefix common to all rows of group g,
+ * rows [group_rows[g], group_rows[g+1]). indptr int32 [n_rows+1], indices int32.
+ * Reference: takes the place of AttentionBackend.prepare / _plan_decode
+ * (attention/flashinfer.py:201-209, 262-349); runs on the device, capturable. */
+int fr_decode_attn_plan(const int32_t* indptr, const int32_t* indices, const int32_t* group_rows, int n_groups,
+                        int32_t* shared_len_out, cudaStream_t stream);
+
+/* out[r,h,:] = softmax(q[r,h,:] . K^T * sm_scale) . V over the row's slot list.
+ * q: bf16 [n_rows, hq, 128] (element strides token/head); caches e4m3 with byte
+ * strides (slot, kv head), 16-byte aligned rows; out: bf16 [n_rows, hq, 128]
+ * with token stride o_t. hq / hkv in {1,2,4,8}. Slots are clamped to the pool.
+ * Reference: AttentionBackend.forward decode branch (attention/flashinfer.py:
+ * 212-238) / _sdpa (:380-431). */
+int fr_decode_attn_fp8(const void* q, int64_t q_t, int64_t q_h, const void* k_cache, const void* v_cache,
+                       int64_t ck_s, int64_t ck_h, int64_t cv_s, int64_t cv_h, const int32_t* indptr,
+                       const int32_t* indices, const int32_t* group_rows, const int32_t* shared_len, void* out,
+                       int64_t o_t, int n_rows, int n_groups, int hq, int hkv, int head_dim, int max_group_rows,
+                       int num_slots, float sm_scale, cudaStream_t stream);
+
+/* ---- trie-constrained SID head ------------------------------------------- */
+
+enum fr_trie_kind { FR_TRIE_NONE = 0, FR_TRIE_DENSE = 1, FR_TRIE_CSR = 2, FR_TRIE_BITMAP = 3 };
+
+/* Device-resident catalog trie (all pointers are DEVICE pointers; the struct
+ * itself is read on the host). Node -1 = unconstrained, invalid_node = no legal
+ * continuation. Token t maps to column rel = t - token_base in [0, vsz).
+ *   DENSE : allow u8 [n_rows, vsz], next i32/i64 [n_rows, vsz] — the layout of
+ *           BeamValidPathTrie._allow_table/_next_node (search/trie.py:211-266).
+ *   CSR   : csr_keys i64 [n_edges] sorted (node * vsz + rel), csr_child i64
+ *           [n_edges] — BeamValidPathTrie._csr_keys/_csr_child (search/trie.py:292-343).
+ *   BITMAP: bitmap u32 [n_rows, words_per_node] over the codes of the node's own
+ *           level, level_off i32 [n_rows] = rel of that level's code 0, child_base
+ *           i64 [n_rows] = id of the node's first child (children are numbered
+ *           consecutively in code order) or -1 when the children are leaves. */
+typedef struct fr_trie {
+  int32_t kind;
+  int32_t next_is_i32;
+  const void* allow;
+  const void* next;
+  const void* csr_keys;
+  const void* csr_child;
+  int64_t n_edges;
+  const void* bitmap;
+  const void* child_base;
+  const void* level_off;
+  int32_t words_per_node;
+  int32_t reserved_;
+  int64_t n_rows;
+  int64_t vsz;
+  int64_t token_base;
+  int64_t invalid_node;
+} fr_trie;
+
+/* Row statistics of fp32 logits [rows, cols] (pitch ld): row_max, row_logsum =
+ * log(sum exp(x - max)); if logprobs_out is non-null also writes
+ * (x - max) - logsum with pitch ldo.
+ * Reference: F.log_softmax in RestrictedLMHead.compute_level (logits.py:118-138). */
+int fr_logsumexp_rows(const float* logits, int64_t ld, float* row_max, float* row_logsum, float* logprobs_out,
+                      int64_t ldo, int rows, int cols, cudaStream_t stream);
+
+/* Per-row sorted top-k (value descending, ties: smaller index). If row_max /
+ * row_logsum are given the values are the log-probs (x - max) - logsum.
+ * vals_out f32 [rows, k], idx_out i64 [rows, k]; cols * 4 bytes must fit in
+ * shared memory (cols <= 49152).
+ * Reference: torch.topk(..., sorted=True) in the expand path
+ * (scheduler/scheduler.py:1476-1482, engine/graph.py:185-194). */
+int fr_topk_rows(const float* x, int64_t ld, const float* row_max, const float* row_logsum, float* vals_out,
+                 int64_t* idx_out, int rows, int cols, int k, cudaStream_t stream);
+
+/* scores_out = allowed(node_ids[r], cand_tokens[r,c]) ? scores_in : neg_inf.
+ * Reference: trie_mask_candidates (kernel/beam_trie.py:82-117) and the CSR
+ * branch of BeamValidPathTrie.mask_candidates (search/trie.py:491-500). */
+int fr_trie_mask(float* scores_out, const float* scores_in, const int64_t* cand_tokens, const int64_t* node_ids,
+                 const fr_trie* trie, float neg_inf, int64_t rows, int64_t cols, cudaStream_t stream);
+
+/* out[n,k] = next(node_ids[n, clamp(parents[n,k])], tokens[n,k]).
+ * Reference: trie_advance_nodes(_batched) (kernel/beam_trie.py:120-197),
+ * BeamValidPathTrie.advance_node_ids (search/trie.py:531-589). */
+int fr_trie_advance(int64_t* out, const int64_t* node_ids, const int64_t* parents, const int64_t* tokens,
+                    const fr_trie* trie, int N, int BW, int K, cudaStream_t stream);
+
+/* out[n,b,:] = token_ids[n, clamp(parents[n,b]), :]; out[n,b,col] = new_tokens[n,b].
+ * Reference: beam_expand_token_ids (kernel/beam_trie.py:200-232). */
+int fr_beam_expand(int64_t* out, const int64_t* token_ids, const int64_t* parents, const int64_t* new_tokens, int N,
+                   int BW, int L, int col, cudaStream_t stream);
+
+/* Fused mask + sorted top-K over BW*C explicit candidates + token-row expand +
+ * node advance, one request per CTA; K <= 4096 (K <= BW when expanding).
+ * scratch: f32 [N, BW*C], required when masking. In/out planes must not alias.
+ * out_child (optional): node after the step for each winner.
+ * Reference: genrec_mask_topk_expand / call_genrec_cuda (kernel/beam_trie.py:
+ * 536-684, kernel/csrc/beam_trie.cuh:548-936). */
+int fr_mask_topk_expand(float* out_vals, int64_t* out_parents, int64_t* out_tokens, int64_t* out_indices,
+                        int64_t* out_child, float* scratch, const float* cum, const float* top_logprobs,
+                        const int64_t* top_tokens, const int64_t* node_in, const int64_t* token_ids_in,
+                        int64_t* token_ids_out, int64_t* node_ids_out, const uint8_t* do_expand, const int32_t* col_n,
+                        const fr_trie* trie, int N, int BW, int C, int K, int L, int apply_mask, int apply_expand,
+                        int apply_advance, cudaStream_t stream);
+
+/* The same step with the candidates taken straight from the level's fp32
+ * logits [N*BW, level_width] and their row statistics: every code of the level
+ * is a candidate (score = cum + (logit - max) - logsum), so no legal SID is
+ * lost to a per-beam pre-selection. token = level_tok_base + idx_base + c;
+ * flat index = b * idx_width + idx_base + c (idx_base / idx_width describe a
+ * token-range shard of a wider level; 0 / level_width otherwise). With a CSR
+ * trie only the node's own edges are visited.
+ * Reference: RestrictedLMHead.compute_level + expand_step (logits.py:118-138,
+ * search/expand.py:240-372) with the candidate width set to the level width. */
+int fr_sid_beam_step(float* out_vals, int64_t* out_parents, int64_t* out_tokens, int64_t* out_indices,
+                     int64_t* out_child, const float* cum, const float* logits, int64_t ld, const float* row_max,
+                     const float* row_logsum, const int64_t* node_in, const int64_t* token_ids_in,
+                     int64_t* token_ids_out, int64_t* node_ids_out, const uint8_t* do_expand, const int32_t* col_n,
+                     const fr_trie* trie, int64_t level_tok_base, int64_t idx_base, int64_t idx_width, int N, int BW,
+                     int level_width, int K, int L, int apply_expand, int apply_advance, cudaStream_t stream);
+
+/* Merge S per-shard sorted winner lists ([S, N, K] values / flat indices /
+ * child nodes, e.g. after an all-gather) into the global sorted top-K, then
+ * expand / advance as above. S * K <= 16384. No counterpart in the reference
+ * (it has no multi-GPU path); the ordering rule is the one above. */
+int fr_topk_merge_shards(float* out_vals, int64_t* out_parents, int64_t* out_tokens, int64_t* out_indices,
+                         int64_t* out_child, const float* shard_vals, const int64_t* shard_indices,
+                         const int64_t* shard_child, const int64_t* node_in, const int64_t* token_ids_in,
+                         int64_t* token_ids_out, int64_t* node_ids_out, const uint8_t* do_expand, const int32_t* col_n,
+                         int64_t level_tok_base, int64_t idx_width, int S, int N, int BW, int K, int L,
+                         int apply_expand, int apply_advance, cudaStream_t stream);
+
+/* Combine per-shard row statistics [S, rows] (max, logsum) into the statistics
+ * of the concatenated row. No counterpart in the reference. */
+int fr_lse_combine_shards(const float* shard_max, const float* shard_logsum, float* row_max, float* row_logsum, int S,
+                          int rows, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHREC_B200_H_ */

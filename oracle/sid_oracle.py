@@ -1,0 +1,356 @@
+"""CPU oracle for the quantized SID decode-step hot path.
+
+TEST INFRASTRUCTURE ONLY. This module restates, in plain torch-CPU / numpy, the
+arithmetic of the reference engine's decode path so that the CUDA kernels can
+be checked against it. Nothing in the product package imports it; only
+``tests/``, ``__graft_entry__.smoke()`` and ``bench.py``'s CPU-baseline legs do.
+
+Each function names the reference code it follows (paths inside the
+reference's ``python/flashrec`` tree). Pinning: ``tests/golden/*.npz`` holds
+inputs and outputs produced by importing the reference itself
+(``tests/golden/make_golden.py``); ``tests/test_oracle_golden.py`` checks this
+module against them. Two pieces have no runnable reference on a CPU and are
+therefore "parity unpinned" beyond their building blocks: the fused
+QK-norm+RoPE arithmetic (the reference's implementation is a Triton kernel and
+its torch fallback multiplies 64-wide cos/sin into 128-wide heads, which
+raises) and the FP8 lm_head (the reference's head is bf16).
+
+Deliberate, documented deviations from the literal torch path:
+  * sums of squares are accumulated in float64 and rounded once to float32
+    (torch reduces in float32 in an order that depends on build and thread
+    count); everything after that follows torch's float32 / bfloat16 roundings;
+  * silu is evaluated in float64 and rounded to float32 then bfloat16 (torch
+    evaluates exp in float32 with a vectorised polynomial).
+Both make the result independent of reduction order so that a GPU can match it
+bit for bit; the golden tests report how many bytes differ from the literal
+reference (none on the committed fixtures except where stated).
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import numpy as np
+import torch
+
+FP8 = torch.float8_e4m3fn
+FP8_MAX = 448.0
+
+
+# ---------------------------------------------------------------------------
+# quantisers
+# ---------------------------------------------------------------------------
+def per_token_quant_fp8(x: torch.Tensor):
+    """kernel/sglops.py:84-96 (torch branch)."""
+    x2 = x.reshape(-1, x.shape[-1])
+    x_f = x2.float()
+    amax = x_f.abs().amax(dim=-1, keepdim=True).clamp(min=1e-12)
+    scale = (amax / FP8_MAX).to(torch.float32)
+    q = (x_f / scale).clamp(-FP8_MAX, FP8_MAX).to(FP8)
+    return q, scale
+
+
+def quantize_weight_fp8(w: torch.Tensor):
+    """layers/linear.py:26-32."""
+    wf = w.float()
+    amax = wf.abs().amax(dim=-1).clamp(min=1e-12)
+    scale = (amax / FP8_MAX).to(torch.float32)
+    q = (wf / scale.unsqueeze(-1)).clamp(-FP8_MAX, FP8_MAX).to(FP8)
+    return q, scale
+
+
+def _rstd(x_f: torch.Tensor, eps: float) -> torch.Tensor:
+    """1/sqrt(mean(x^2)+eps): float64 sum rounded once to float32, then float32
+    add, sqrt and divide (each correctly rounded), cf. kernel/sglops.py:36-38."""
+    ss = (x_f.double() * x_f.double()).sum(dim=-1, keepdim=True)
+    var = (ss / x_f.shape[-1]).float()
+    return 1.0 / torch.sqrt(var + torch.tensor(eps, dtype=torch.float32))
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """kernel/sglops.py:34-39: (x_f * rstd) * w -> x.dtype."""
+    x_f = x.float()
+    y = x_f * _rstd(x_f, eps)
+    return (y * weight.float()).to(x.dtype)
+
+
+def fused_add_rmsnorm(x, residual, weight, eps):
+    """kernel/sglops.py:48-55: residual = residual + x (in bf16), then rmsnorm."""
+    residual = residual + x
+    return rmsnorm(residual, weight, eps), residual
+
+
+def rmsnorm_quant_fp8(x, weight, eps, residual: Optional[torch.Tensor] = None):
+    """RMSNorm.quant_fp8 on the torch path (kernel/rms_fp8.py:120-145 fallbacks):
+    rmsnorm -> bf16 -> per_token_quant_fp8. Returns (q, scale[, residual])."""
+    if residual is None:
+        q, s = per_token_quant_fp8(rmsnorm(x, weight.to(x.dtype), eps))
+        return q, s
+    h, residual = fused_add_rmsnorm(x, residual, weight.to(x.dtype), eps)
+    q, s = per_token_quant_fp8(h)
+    return q, s, residual
+
+
+def silu_bf16(g: torch.Tensor) -> torch.Tensor:
+    """F.silu on a bf16 tensor: x / (1 + exp(-x)) rounded to fp32 then bf16."""
+    gd = g.double()
+    return (gd / (1.0 + torch.exp(-gd))).float().to(torch.bfloat16)
+
+
+def silu_and_mul(x: torch.Tensor) -> torch.Tensor:
+    """kernel/sglops.py:143-151 on bf16: silu (-> bf16) times up (-> bf16)."""
+    d = x.shape[-1] // 2
+    return silu_bf16(x[..., :d]) * x[..., d:]
+
+
+def silu_mul_quant_fp8(x: torch.Tensor):
+    """kernel/silu_fp8.py:79-83 (fallback): per_token_quant_fp8(silu_and_mul(x))."""
+    return per_token_quant_fp8(silu_and_mul(x))
+
+
+# ---------------------------------------------------------------------------
+# GEMM
+# ---------------------------------------------------------------------------
+def fp8_gemm_acc(a_q: torch.Tensor, b_q_nk: torch.Tensor) -> torch.Tensor:
+    """Exact-ish fp32 accumulator sum_k a*b from the e4m3 bytes (products of two
+    e4m3 values are exact in fp32; the float64 matmul makes the sum order-free)."""
+    return (a_q.float().double() @ b_q_nk.float().double().t()).float()
+
+
+def fp8_scaled_mm(a_q, b_q_nk, scale_a, scale_b, out_dtype=torch.bfloat16, bias=None):
+    """kernel/sglops.py:99-140 (torch branch): _scaled_mm with unit scales -> out
+    dtype, then * scale_a * scale_b in fp32 -> out dtype (two roundings)."""
+    acc = fp8_gemm_acc(a_q, b_q_nk).to(out_dtype)
+    out = (acc.float() * scale_a.reshape(-1, 1).float() * scale_b.reshape(1, -1).float()).to(out_dtype)
+    if bias is not None:
+        out = out + bias.to(out_dtype)
+    return out
+
+
+def fp8_logits_f32(a_q, b_q_nk, scale_a, scale_b) -> torch.Tensor:
+    """fp32 logits of the FP8 lm_head: (acc * scale_a) * scale_b, no bf16 rounding."""
+    acc = fp8_gemm_acc(a_q, b_q_nk)
+    return (acc * scale_a.reshape(-1, 1).float()) * scale_b.reshape(1, -1).float()
+
+
+# ---------------------------------------------------------------------------
+# QK-norm + RoPE + KV write
+# ---------------------------------------------------------------------------
+def build_cos_sin_cache(head_dim: int, max_position: int, base: float) -> torch.Tensor:
+    """layers/rotary.py:21-34."""
+    inv_freq = 1.0 / (base ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
+    t = torch.arange(max_position, dtype=torch.float32)
+    freqs = torch.einsum("i,j->ij", t, inv_freq)
+    return torch.cat((freqs.cos(), freqs.sin()), dim=-1)
+
+
+def _norm_rope(x: torch.Tensor, w: torch.Tensor, eps: float, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """kernel/qk_rope_kv.py:64-98: fp32 x*rstd*w, NeoX halves, separate roundings.
+    x: [T, H, D] float32; cos/sin: [T, 1, D/2]. Returns float32 [T, H, D]."""
+    half = x.shape[-1] // 2
+    rstd = _rstd(x, eps)
+    xn = (x * rstd) * w.float()
+    x1, x2 = xn[..., :half], xn[..., half:]
+    y1 = x1 * cos - x2 * sin
+    y2 = x2 * cos + x1 * sin
+    return torch.cat((y1, y2), dim=-1)
+
+
+def qk_norm_rope_store_fp8(q, k, v, positions, loc, q_weight, k_weight, eps, cos_sin_cache, k_cache, v_cache):
+    """kernel/qk_rope_kv.py:28-155. q/k/v: bf16 [T, H, D]; returns the new q (bf16)
+    and writes k_cache[loc] / v_cache[loc] (e4m3 [slots, Hkv, D]) in place."""
+    d = q.shape[-1]
+    cs = cos_sin_cache[positions.long()].float()
+    cos, sin = cs[:, None, : d // 2], cs[:, None, d // 2 :]
+    q_new = _norm_rope(q.float(), q_weight.to(q.dtype), eps, cos, sin).to(q.dtype)
+    k_new = _norm_rope(k.float(), k_weight.to(k.dtype), eps, cos, sin).to(torch.bfloat16).to(FP8)
+    k_cache[loc.long()] = k_new
+    v_cache[loc.long()] = v.to(FP8)
+    return q_new
+
+
+def store_kv(k_cache, v_cache, loc, k, v):
+    """kvcache/pool.py:121-139 + kernel/sglops.py:207-222 (index_put of converted rows)."""
+    k_cache[loc.long()] = k.to(FP8)
+    v_cache[loc.long()] = v.to(FP8)
+
+
+# ---------------------------------------------------------------------------
+# attention
+# ---------------------------------------------------------------------------
+def gather_kv_indices(req_to_token: torch.Tensor, rows: torch.Tensor, seq_lens) -> torch.Tensor:
+    """attention/kv_indices.py:122-131 (torch branch)."""
+    out = [req_to_token[int(r), : int(s)].to(torch.int32) for r, s in zip(rows.tolist(), list(seq_lens))]
+    return torch.cat(out) if out else torch.empty(0, dtype=torch.int32)
+
+
+def decode_attention(q, k_cache, v_cache, kv_indptr, kv_indices, n_rep: int) -> torch.Tensor:
+    """attention/flashinfer.py:380-431 (_sdpa, decode branch), evaluated in fp32:
+    per row softmax(q K^T / sqrt(D)) V over the row's slot list, GQA by repeat."""
+    t, hq, d = q.shape
+    out = torch.zeros((t, hq, d), dtype=torch.float32)
+    scale = d ** -0.5
+    kf, vf = k_cache.float(), v_cache.float()
+    for i in range(t):
+        idx = kv_indices[int(kv_indptr[i]) : int(kv_indptr[i + 1])].long()
+        if idx.numel() == 0:
+            continue
+        k = kf[idx].repeat_interleave(n_rep, dim=1)  # [L, Hq, D]
+        v = vf[idx].repeat_interleave(n_rep, dim=1)
+        s = torch.einsum("hd,lhd->hl", q[i].float(), k) * scale
+        p = torch.softmax(s, dim=-1)
+        out[i] = torch.einsum("hl,lhd->hd", p, v)
+    return out.to(q.dtype)
+
+
+# ---------------------------------------------------------------------------
+# SID head + beam step
+# ---------------------------------------------------------------------------
+def log_softmax_rows(logits: torch.Tensor) -> torch.Tensor:
+    """logits.py:119-120: F.log_softmax(logits.float(), dim=-1)."""
+    return torch.log_softmax(logits.float(), dim=-1)
+
+
+def row_stats(logits: torch.Tensor):
+    mx = logits.float().amax(dim=-1)
+    ls = torch.log(torch.exp(logits.float() - mx[:, None]).sum(dim=-1))
+    return mx, ls
+
+
+def logprobs_from_stats(logits, mx, ls):
+    return (logits.float() - mx[:, None]) - ls[:, None]
+
+
+def topk_rows(x: torch.Tensor, k: int):
+    """Sorted top-k with the deterministic tie rule (value desc, index asc)."""
+    xs = x.float()
+    order = np.lexsort((np.arange(xs.shape[-1])[None, :].repeat(xs.shape[0], 0), -xs.numpy().astype(np.float64)), axis=-1)
+    idx = torch.from_numpy(order[:, :k].copy())
+    return torch.gather(xs, 1, idx), idx
+
+
+class OracleTrie:
+    """Dense tables / sorted-key CSR with the reference's sentinels
+    (search/trie.py:160-343): node -1 unconstrained, invalid_node all-false."""
+
+    def __init__(self, keys: np.ndarray, child: np.ndarray, vsz: int, token_base: int, invalid_node: int):
+        self.keys = np.asarray(keys, dtype=np.int64)
+        self.child = np.asarray(child, dtype=np.int64)
+        self.vsz = int(vsz)
+        self.token_base = int(token_base)
+        self.invalid_node = int(invalid_node)
+
+    def lookup(self, nodes: np.ndarray, toks: np.ndarray):
+        """search/trie.py:345-368 (_csr_lookup) + range / sentinel handling of
+        mask_candidates (:491-500) and advance_node_ids (:541-558)."""
+        nodes = np.asarray(nodes, dtype=np.int64)
+        rel = np.asarray(toks, dtype=np.int64) - self.token_base
+        in_range = (rel >= 0) & (rel < self.vsz)
+        key = np.clip(nodes, 0, None) * self.vsz + np.clip(rel, 0, self.vsz - 1)
+        e = self.keys.shape[0]
+        if e == 0:
+            found = np.zeros(key.shape, dtype=bool)
+            child = np.full(key.shape, self.invalid_node, dtype=np.int64)
+        else:
+            pos = np.searchsorted(self.keys, key)
+            posc = np.clip(pos, 0, e - 1)
+            found = (pos < e) & (self.keys[posc] == key)
+            child = np.where(found, self.child[posc], self.invalid_node)
+        found = found & in_range
+        child = np.where(found, child, self.invalid_node)
+        return found, child
+
+    def allowed(self, nodes, toks):
+        found, _ = self.lookup(nodes, toks)
+        return found | (np.asarray(nodes) < 0)
+
+    def transition(self, old, toks):
+        _, child = self.lookup(old, toks)
+        old = np.asarray(old, dtype=np.int64)
+        return np.where(old < 0, old, child)
+
+
+def trie_mask(scores, cand_tokens, node_ids, trie: OracleTrie):
+    """kernel/beam_trie.py:104-117."""
+    ok = trie.allowed(node_ids.numpy()[:, None].repeat(cand_tokens.shape[1], 1), cand_tokens.numpy())
+    return scores.masked_fill(~torch.from_numpy(ok), float("-inf"))
+
+
+def select_topk_flat(scores: np.ndarray, k: int, masked: bool):
+    """Deterministic sorted top-k over a flat score vector: score desc, index asc.
+    With ``masked`` a -inf score is not a candidate; missing winners are filled
+    with (-inf, index 0) (kernel/csrc/beam_trie.cuh:640-683)."""
+    s = scores.astype(np.float32)
+    idx_all = np.arange(s.shape[0])
+    live = s != -np.inf if masked else np.ones_like(s, dtype=bool)
+    cand = idx_all[live]
+    order = cand[np.lexsort((cand, -s[cand].astype(np.float64)))]
+    take = order[:k]
+    vals = np.full(k, -np.inf, dtype=np.float32)
+    idx = np.zeros(k, dtype=np.int64)
+    vals[: take.shape[0]] = s[take]
+    idx[: take.shape[0]] = take
+    return vals, idx, int(take.shape[0])
+
+
+def mask_topk_expand(cum, top_logprobs, top_tokens, select_k, node_ids=None, trie: Optional[OracleTrie] = None,
+                     token_ids=None, col=0, do_expand=None, apply_mask=True, apply_expand=True, apply_advance=True):
+    """genrec_mask_topk_expand (kernel/beam_trie.py:536-630, csrc/beam_trie.cuh:548-755)
+    with the CUDA kernel's deterministic ordering. All tensors on CPU.
+    Returns dict(vals, parents, tokens, indices, token_ids, node_ids, child)."""
+    n, bw, c = top_logprobs.shape
+    k = int(select_k)
+    masked = bool(apply_mask and node_ids is not None and trie is not None)
+    out = dict(
+        vals=torch.empty((n, k)), parents=torch.empty((n, k), dtype=torch.int64),
+        tokens=torch.empty((n, k), dtype=torch.int64), indices=torch.empty((n, k), dtype=torch.int64),
+        token_ids=None, node_ids=None, child=None,
+    )
+    do_exp = bool(apply_expand and token_ids is not None)
+    do_adv = bool(apply_advance and masked and do_exp)
+    if do_exp:
+        out["token_ids"] = token_ids.clone()
+    if do_adv:
+        out["node_ids"] = node_ids.clone()
+    if node_ids is not None and trie is not None:
+        out["child"] = torch.zeros((n, k), dtype=torch.int64)
+    cols = col if isinstance(col, torch.Tensor) else torch.full((n,), int(col))
+    for i in range(n):
+        scores = (cum[i].float()[:, None] + top_logprobs[i].float())
+        if masked:
+            ok = trie.allowed(node_ids[i].numpy()[:, None].repeat(c, 1), top_tokens[i].numpy())
+            scores = scores.masked_fill(~torch.from_numpy(ok), float("-inf"))
+        vals, idx, _ = select_topk_flat(scores.reshape(-1).numpy(), k, masked)
+        parents = idx // c
+        toks = top_tokens[i].reshape(-1).numpy()[idx]
+        out["vals"][i] = torch.from_numpy(vals)
+        out["indices"][i] = torch.from_numpy(idx)
+        out["parents"][i] = torch.from_numpy(parents)
+        out["tokens"][i] = torch.from_numpy(toks)
+        child = None
+        if node_ids is not None and trie is not None:
+            child = trie.transition(node_ids[i].numpy()[np.clip(parents, 0, bw - 1)], toks)
+            out["child"][i] = torch.from_numpy(child)
+        if do_exp and (do_expand is None or bool(do_expand[i])):
+            rows = token_ids[i][torch.from_numpy(np.clip(parents, 0, bw - 1))].clone()
+            cc = int(cols[i])
+            if 0 <= cc < rows.shape[1]:
+                rows[:, cc] = torch.from_numpy(toks)
+            out["token_ids"][i, :k] = rows
+            if do_adv:
+                out["node_ids"][i, :k] = torch.from_numpy(child)
+    return out
+
+
+def sid_beam_step(cum, logits, node_ids, trie: Optional[OracleTrie], level_tok_base: int, select_k: int,
+                  token_ids=None, col=0):
+    """Full-width step: every code of the level is a candidate of every beam;
+    score = cum + ((logit - max) - logsum); -inf scores are not candidates.
+    cum [N,BW], logits [N*BW, K_l] fp32, node_ids [N,BW]."""
+    n, bw = cum.shape
+    kl = logits.shape[1]
+    mx, ls = row_stats(logits)
+    lp = logprobs_from_stats(logits, mx, ls).view(n, bw, kl)
+    toks = (level_tok_base + torch.arange(kl, dtype=torch.int64))[None, None, :].expand(n, bw, kl)
+    return mask_topk_expand(cum, lp, toks, select_k, node_ids=node_ids, trie=trie, token_ids=token_ids, col=col,
+                            apply_mask=True)
