@@ -1,0 +1,394 @@
+"""Benchmark of the quantized SID decode step (see DESIGN.md for the workload).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One "step" is one decode wave of the hot path: 32 concurrent requests x 512
+beams = 16384 beam rows through a 28-layer Qwen3-1.7B-shaped FP8 model, the
+SID head and the trie-constrained beam step, for each of the 3 SID levels.
+Metric: beam rows decoded per second (rows x levels / time), whole job.
+
+  value  device-timed (CUDA events), inputs resident in HBM, CUDA-graph replay
+  e2e    same wave driven from pinned host buffers: per-step slot ids copied
+         host->device, final beams (scores + SID tokens) copied device->host
+  roofline      the FP8 GEMM (dominant kernel), timed alone in this process
+  cpu_baseline  the CPU oracle port of the same ops on a bounded sample
+
+With --gpus N > 1 (launched by torch.distributed.run) every rank runs its own
+replica on its own requests (requests never interact): weak scaling, no
+data-path collective; the time is the max over ranks.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "sid_decode_beam_rows_per_s"
+UNIT = "beam-rows/s"
+WORKLOAD = dict(
+    workload="qwen3-1.7b-shaped 28-layer FP8 W8A8 decode, fp8 KV, 3-level SID (3x8192), 1M-item CSR trie",
+    requests=32, beam_width=512, levels=3, prompt_len="uniform[128,1024]", shared_prefix=64,
+    l2_policy="working set (1.4 GB weights + activations) far larger than the 126 MB L2",
+)
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--requests", type=int, default=32)
+    ap.add_argument("--beam", type=int, default=512)
+    ap.add_argument("--layers", type=int, default=28)
+    ap.add_argument("--items", type=int, default=1_000_000)
+    ap.add_argument("--trie", default="csr", choices=["csr", "bitmap"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+# ---------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self._stop = threading.Event()
+        self._thr = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits"],
+                    capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([x.strip() for x in out.split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._thr.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._thr.join(timeout=10)
+
+    def summary(self):
+        sm = [int(s[0]) for s in self.samples if s and s[0].isdigit()]
+        mx = [int(s[1]) for s in self.samples if len(s) > 1 and s[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for s in self.samples if len(s) >= 6 for i in range(4) if s[2 + i] == "Active"})
+        return {"sm_mhz": int(statistics.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------
+# workload construction (seeded, synthetic)
+# ---------------------------------------------------------------------------
+def make_catalog(items: int, sizes, seed=0):
+    import numpy as np
+
+    rng = np.random.default_rng(seed)
+    return np.stack([rng.integers(0, s, items) for s in sizes], axis=1)
+
+
+def prompt_lengths(n: int, seed: int):
+    import numpy as np
+
+    rng = np.random.default_rng(1000 + seed)
+    return [int(x) for x in rng.integers(128, 1025, n)]
+
+
+# ---------------------------------------------------------------------------
+# CPU baseline (oracle port) — also the --impl reference arm
+# ---------------------------------------------------------------------------
+def cpu_baseline(beam: int, sizes, items: int, layers: int, budget_rows: int = 64):
+    """Times the oracle's restatement of one decode step on the host cores for a
+    bounded sample: `budget_rows` beam rows of one request (prompt 256) through ONE
+    decoder layer, one SID head level and one beam step; the layer time is
+    multiplied by the layer count. Returns (beam_rows_per_s, cores, description)."""
+    import numpy as np
+    import torch
+
+    from oracle import sid_oracle as O
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    g = torch.Generator().manual_seed(0)
+    H, HQ, HKV, D, I = 2048, 16, 8, 128, 6144
+    rows, plen = budget_rows, 256
+    w = {k: O.quantize_weight_fp8(0.02 * torch.randn(n, kk, generator=g))
+         for k, (n, kk) in dict(qkv=(4096, H), o=(H, H), gate_up=(2 * I, H), down=(H, I), head=(sizes[0], H)).items()}
+    norms = dict(input=torch.ones(H, dtype=torch.bfloat16), post=torch.ones(H, dtype=torch.bfloat16),
+                 q=torch.ones(D, dtype=torch.bfloat16), k=torch.ones(D, dtype=torch.bfloat16))
+    cs = O.build_cos_sin_cache(D, plen + 8, 1e6)
+    slots = plen + rows + 1
+    kc = torch.randn(slots, HKV, D, generator=g).bfloat16().to(O.FP8)
+    vc = torch.randn(slots, HKV, D, generator=g).bfloat16().to(O.FP8)
+    x = torch.randn(rows, H, generator=g).bfloat16()
+    pos = torch.full((rows,), plen)
+    loc = torch.arange(plen + 1, plen + 1 + rows)
+    indptr = torch.arange(rows + 1, dtype=torch.int32) * (plen + 1)
+    indices = torch.cat([torch.cat((torch.arange(1, plen + 1), loc[i:i + 1])) for i in range(rows)]).to(torch.int32)
+    from flashrec_b200.trie import build_trie_arrays  # host-side numpy builder, no GPU involved
+
+    arrays = build_trie_arrays(make_catalog(min(items, 200_000), sizes), list(sizes), 151_936)
+    otr = O.OracleTrie(arrays.csr_keys, arrays.edge_child, arrays.vsz, arrays.token_base, arrays.invalid_node)
+
+    def layer(x, residual):
+        return O.decoder_layer(x, residual, w, norms, pos, loc, cs, kc, vc, indptr, indices, HQ, HKV, D)
+
+    def head_and_step(h):
+        hq, hs = O.per_token_quant_fp8(h)
+        logits = O.fp8_logits_f32(hq, w["head"][0], hs, w["head"][1])
+        cum = torch.zeros(1, rows)
+        nodes = torch.zeros(1, rows, dtype=torch.int64)
+        return O.sid_beam_step(cum, logits, nodes, otr, arrays.token_base, rows)
+
+    layer(x, x.clone())  # warm-up
+    t0 = time.perf_counter()
+    h, r = layer(x, x.clone())
+    t_layer = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    head_and_step(h)
+    t_head = time.perf_counter() - t0
+    per_step = t_layer * layers + t_head
+    desc = (f"{rows} beam rows of one request (prompt 256): 1 decoder layer timed {t_layer:.3f}s x {layers} layers "
+            f"(extrapolated) + head level and beam step {t_head:.3f}s; float64-accumulating oracle port")
+    return rows / per_step, cores, desc
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sizes = [8192] * 3
+    vals = []
+    for _ in range(max(1, min(args.steps, 3))):
+        v, cores, desc = cpu_baseline(args.beam, sizes, args.items, args.layers)
+        vals.append(v)
+    v = statistics.median(vals)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp8_e4m3 x fp8_e4m3 -> f32", "data": "synthetic", "config": WORKLOAD,
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------
+def time_gemms(torch, rows: int, iters: int = 10):
+    """FP8 GEMM roofline: the four linear-layer shapes of one decoder layer at the
+    wave's row count, timed back to back with CUDA events on the launch stream."""
+    from flashrec_b200.kernel.sglops import fp8_scaled_mm
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    shapes = [("qkv", 4096, 2048), ("o", 2048, 2048), ("gate_up", 12288, 2048), ("down", 2048, 6144)]
+    ops, flops = [], 0.0
+    for name, n, k in shapes:
+        a = torch.randn(rows, k, device=dev).to(torch.float8_e4m3fn)
+        b = torch.randn(n, k, device=dev).to(torch.float8_e4m3fn)
+        sa = torch.rand(rows, 1, device=dev) + 0.5
+        sb = torch.rand(n, device=dev) + 0.5
+        ops.append((a, b, sa, sb))
+        flops += 2.0 * rows * n * k
+    for a, b, sa, sb in ops:  # warm-up
+        fp8_scaled_mm(a, b.t(), sa, sb, torch.bfloat16)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        for a, b, sa, sb in ops:
+            fp8_scaled_mm(a, b.t(), sa, sb, torch.bfloat16)
+    e1.record()
+    torch.cuda.synchronize()
+    sec = e0.elapsed_time(e1) / 1e3 / iters
+    lib = None
+    try:  # cuBLASLt FP8 on the same shapes, for orientation only
+        one = torch.ones((), device=dev)
+        for a, b, sa, sb in ops:
+            torch._scaled_mm(a, b.t(), scale_a=sa, scale_b=sb.view(1, -1), out_dtype=torch.bfloat16)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(iters):
+            for a, b, sa, sb in ops:
+                torch._scaled_mm(a, b.t(), scale_a=sa, scale_b=sb.view(1, -1), out_dtype=torch.bfloat16)
+        e1.record()
+        torch.cuda.synchronize()
+        lib = flops / (e0.elapsed_time(e1) / 1e3 / iters) / 1e12
+        del one
+    except Exception:
+        lib = None
+    return flops, sec, lib
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+    import numpy as np
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+
+    from flashrec_b200 import _lib, device_status
+    from flashrec_b200.decoder import Qwen3Config
+    from flashrec_b200.sid_decode import SidDecodeEngine
+    from flashrec_b200.trie import build_trie_arrays, trie_to_device
+
+    _lib.load()  # fails loudly if the CUDA library is missing
+    sizes = [8192] * 3
+    token_base = 151_936
+    cfg = Qwen3Config(num_hidden_layers=args.layers)
+    arrays = build_trie_arrays(make_catalog(args.items, sizes), sizes, token_base)
+    trie = trie_to_device(arrays, args.trie, dev)
+    eng = SidDecodeEngine(cfg, args.requests, args.beam, prompt_lengths(args.requests, rank), sizes, token_base, trie,
+                          dev, shared_prefix=64, page_size=16, seed=rank)
+    # count this library's kernel launches in one eager wave
+    counter = {"n": 0}
+    orig_call = _lib.call
+    two_kernels = {"fr_gather_kv_indices"}
+
+    def counting_call(name, *a):
+        counter["n"] += 2 if name in two_kernels else 1
+        return orig_call(name, *a)
+
+    import flashrec_b200.attention as m_att
+    import flashrec_b200.decoder as m_dec
+    import flashrec_b200.kernel.qk_rope_kv as m_rope
+    import flashrec_b200.kernel.rms_fp8 as m_rms
+    import flashrec_b200.kernel.sglops as m_sgl
+    import flashrec_b200.kernel.silu_fp8 as m_silu
+    import flashrec_b200.logits as m_log
+    import flashrec_b200.sid_decode as m_sid
+
+    mods = [m_att, m_dec, m_rope, m_rms, m_sgl, m_silu, m_log, m_sid]
+    for m in mods:
+        m.call = counting_call
+    eng.run(host_io=False, _eager=True)
+    torch.cuda.synchronize()
+    launches_per_wave = counter["n"]
+    for m in mods:
+        m.call = orig_call
+    eng.capture()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(host_io: bool, k: int) -> float:
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(k):
+            eng.run(host_io=host_io)
+        e1.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        sec = e0.elapsed_time(e1) / 1e3
+        if host_io:
+            sec = max(sec, wall)  # the wave ends with a host-visible result
+        if dist is not None:
+            t = torch.tensor([sec], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            sec = float(t.item())
+        return sec
+
+    for _ in range(max(args.warmup, 3)):
+        eng.run(host_io=False)
+    with ClockSampler(local) as clk:
+        sec = timed(False, args.steps)
+        sec_e2e = timed(True, args.steps)
+    barrier()
+    code, site = device_status()
+    rows_levels = args.requests * args.beam * len(sizes)
+    value = world * rows_levels * args.steps / sec
+    e2e_value = world * rows_levels * args.steps / sec_e2e
+    h2d = eng.rows * 8 * eng.steps
+    d2h = eng.h_vals.numel() * 4 + eng.h_tokens.numel() * 8
+
+    # legality of the produced beams (illegal-SID rate must be 0)
+    nodes = eng.final_nodes
+    live = torch.isfinite(eng.cum)
+    illegal = int(((nodes != -1) & live).sum().item())
+
+    line = None
+    if rank == 0:
+        flops, gsec, lib_tf = time_gemms(torch, eng.rows)
+        peaks = {}
+        pk = ROOT / "MEASURED_PEAKS.json"
+        if pk.exists():
+            peaks = json.loads(pk.read_text())
+        bf16_burst = float(peaks.get("bf16_tflops", 1590.0))
+        peak_fp8 = 2.0 * bf16_burst
+        achieved = flops / gsec / 1e12
+        roof = {
+            "bound": "tensor", "achieved": achieved, "peak": peak_fp8, "unit": "TFLOP/s",
+            "frac": achieved / peak_fp8, "traffic": None,
+            "kernel": "gemm_fp8_kernel (qkv+o+gate_up+down at M=%d, 4 launches)" % eng.rows,
+            "peak_source": ("2 x measured bf16 burst (MEASURED_PEAKS.json)" if peaks else "2 x fallback 1.59 PFLOP/s")
+            + "; nominal dense FP8 4500",
+            "cublaslt_fp8_tflops_same_shapes": lib_tf,
+        }
+        cpu = None
+        if not args.no_cpu_baseline:
+            v, cores, desc = cpu_baseline(args.beam, sizes, args.items, args.layers)
+            cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc}
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": sec / args.steps * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> f32 (bf16 activations)",
+            "data": "synthetic",
+            "config": dict(WORKLOAD, requests=args.requests, beam_width=args.beam, layers=args.layers,
+                           catalog_items=int(arrays.n_items), trie=args.trie, parallelism=f"dp{world}",
+                           rows_per_gpu=eng.rows, value_per_gpu=value / world),
+            "clocks": clk.summary(),
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": sec_e2e / args.steps * 1e3},
+            "gpu_launches": launches_per_wave * args.steps,
+            "roofline": roof,
+            "cpu_baseline": cpu,
+            "illegal_sid_beams": illegal,
+            "device_status": [code, site],
+        }
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -63,7 +63,7 @@ __device__ __forceinline__ int64_t lower_bound(const int64_t* __restrict__ keys,
 
 // Is `tok` a legal continuation of trie node `node`? node < 0 = unconstrained.
 __device__ __forceinline__ bool trie_allowed(const Trie& tr, int64_t node, int64_t tok) {
-  if (node < 0) return true;
+  if (node < 0 || tr.kind == FR_TRIE_NONE) return true;
   const int64_t rel = tok - tr.token_base;
   if (rel < 0 || rel >= tr.vsz) return false;
   if (tr.kind == FR_TRIE_DENSE) {
@@ -478,7 +478,7 @@ template <bool FULL>
 static int launch_step(const StepParams& p, cudaStream_t stream) {
   const size_t smem = step_smem(p.K);
   auto kern = beam_step_kernel<FULL>;
-  if (smem > 48 * 1024) {
+  if (smem > 32 * 1024) {  // static shared memory counts towards the 48 KiB default limit
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
       return FR_ERR_CUDA;
   }
@@ -631,7 +631,7 @@ extern "C" int fr_topk_merge_shards(float* out_vals, int64_t* out_parents, int64
   int tp2 = 1;
   while (tp2 < S * K) tp2 <<= 1;
   const size_t smem = static_cast<size_t>(tp2) * 8 + static_cast<size_t>(K) * 20 + 16;
-  if (smem > 48 * 1024) {
+  if (smem > 32 * 1024) {
     if (cudaFuncSetAttribute(merge_shards_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
       return FR_ERR_CUDA;

@@ -345,7 +345,7 @@ static int launch_rows(const void* x, void* resid, const void* w, float eps, voi
   const size_t smem = static_cast<size_t>(hidden) * 2;
   FR_CHECK_SUPPORTED(smem <= 200 * 1024);
   auto kern = row_block_kernel<NORM, RESID, QUANT>;
-  if (smem > 48 * 1024) {
+  if (smem > 40 * 1024) {  // leave room for the kernel's static shared memory
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
       return FR_ERR_CUDA;
   }

@@ -127,7 +127,7 @@ extern "C" int fr_topk_rows(const float* x, int64_t ld, const float* row_max, co
   while (kp2 < k) kp2 <<= 1;
   const size_t smem = static_cast<size_t>(kp2) * 8 + static_cast<size_t>(cols) * 4;
   FR_CHECK_SUPPORTED(smem <= 200 * 1024);
-  if (smem > 48 * 1024) {
+  if (smem > 32 * 1024) {  // static shared memory of the kernel counts towards the 48 KiB default limit
     if (cudaFuncSetAttribute(head::topk_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
       return FR_ERR_CUDA;

@@ -16,7 +16,9 @@ namespace topk {
 
 constexpr int kBins = 2048;
 
+// (-0.0 is folded into +0.0 first: the two compare equal and must tie on the index.)
 __device__ __forceinline__ uint64_t compose(float s, uint32_t idx) {
+  s = __fadd_rn(s, 0.0f);
   return (static_cast<uint64_t>(float_to_key(s)) << 32) | static_cast<uint64_t>(0xffffffffu - idx);
 }
 __device__ __forceinline__ float composite_score(uint64_t ck) { return key_to_float(static_cast<uint32_t>(ck >> 32)); }

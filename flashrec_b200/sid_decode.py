@@ -1,0 +1,287 @@
+"""Decode-side driver of trie-constrained SID beam search: the device work of
+one engine tick in the reference (``BeamRecEngine._forward_decode`` and
+``_expand_decode_body``, scheduler/scheduler.py:1261-1456; ``DecodeGraphRunner``,
+engine/graph.py:85-517), sequenced for a fixed wave of requests.
+
+Per step and per beam row: append a KV slot to the row's slot table, gather
+the flat slot lists, run the model body, the SID head of the step's level and
+the fused beam step, then re-parent the per-row decode tails of the slot table.
+Each step is captured once in a CUDA graph (rows = requests x beam width, a
+multiple of the beam width as in ``resolved_cuda_graph_sizes``, config.py:220-238)
+and replayed.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import torch
+
+from flashrec_b200._lib import call, ptr, stream_ptr
+from flashrec_b200.attention import AttentionBackend, TokenToKVPool, gather_kv_indices
+from flashrec_b200.decoder import ForwardBatch, Qwen3Config, Qwen3ForCausalLM
+from flashrec_b200.kernel.beam_trie import GenrecFusedResult
+from flashrec_b200.logits import RestrictedLMHead
+
+_FP8 = torch.float8_e4m3fn
+
+
+@dataclass
+class BeamStepOut:
+    vals: torch.Tensor      # [N, K] f32 cumulative scores, sorted descending
+    parents: torch.Tensor   # [N, K] i64 beam index of the parent
+    tokens: torch.Tensor    # [N, K] i64 chosen token
+    indices: torch.Tensor   # [N, K] i64 flat candidate index b * width + code
+    child: torch.Tensor     # [N, K] i64 trie node after the step
+
+
+def sid_beam_step(
+    cum: torch.Tensor,
+    logits: torch.Tensor,
+    row_max: torch.Tensor,
+    row_logsum: torch.Tensor,
+    node_ids: Optional[torch.Tensor],
+    trie,
+    level_tok_base: int,
+    select_k: int,
+    *,
+    token_ids_in: Optional[torch.Tensor] = None,
+    token_ids_out: Optional[torch.Tensor] = None,
+    node_ids_out: Optional[torch.Tensor] = None,
+    col: Optional[torch.Tensor] = None,
+    out: Optional[BeamStepOut] = None,
+    idx_base: int = 0,
+    idx_width: int = 0,
+) -> BeamStepOut:
+    """One full-width beam step straight from the level's fp32 logits.
+
+    ``cum`` [N,BW] f32; ``logits`` [N*BW, K_l] f32 with row statistics;
+    ``node_ids`` [N,BW] i64; ``trie`` a DeviceTrie (or None = unconstrained).
+    If the token planes are given (distinct in/out, [N,BW,L] i64) the winners'
+    token rows are expanded and ``node_ids_out`` receives the advanced nodes."""
+    n, bw = int(cum.shape[0]), int(cum.shape[1])
+    kl = int(logits.shape[1])
+    k = int(select_k)
+    dev = cum.device
+    if out is None:
+        out = BeamStepOut(
+            vals=torch.empty((n, k), dtype=torch.float32, device=dev),
+            parents=torch.empty((n, k), dtype=torch.int64, device=dev),
+            tokens=torch.empty((n, k), dtype=torch.int64, device=dev),
+            indices=torch.empty((n, k), dtype=torch.int64, device=dev),
+            child=torch.empty((n, k), dtype=torch.int64, device=dev),
+        )
+    tr = trie.descriptor() if trie is not None else None
+    do_exp = token_ids_in is not None and token_ids_out is not None
+    do_adv = do_exp and node_ids is not None and node_ids_out is not None and trie is not None
+    call("fr_sid_beam_step", ptr(out.vals), ptr(out.parents), ptr(out.tokens), ptr(out.indices), ptr(out.child),
+         ptr(cum), ptr(logits), logits.stride(0), ptr(row_max), ptr(row_logsum), ptr(node_ids), ptr(token_ids_in),
+         ptr(token_ids_out), ptr(node_ids_out), None, ptr(col), ctypes.byref(tr) if tr is not None else None,
+         int(level_tok_base), int(idx_base), int(idx_width), n, bw, kl, k,
+         int(token_ids_in.shape[2]) if do_exp else 0, int(do_exp), int(do_adv), stream_ptr(dev))
+    return out
+
+
+class SidDecodeEngine:
+    """A wave of ``n_requests`` requests x ``beam_width`` beams decoding ``len(sizes)``
+    SID levels with a Qwen3-shaped FP8 model. Weights are random (N(0, 0.02)), the
+    prompt KV is synthetic e4m3 data laid out as a prefill would have left it:
+    requests share the slots of a common prompt prefix (a radix-cache hit), every
+    beam of a request shares the request's prompt slots."""
+
+    def __init__(
+        self,
+        cfg: Qwen3Config,
+        n_requests: int,
+        beam_width: int,
+        prompt_lens: Sequence[int],
+        sizes: Sequence[int],
+        token_base: int,
+        trie,
+        device,
+        *,
+        shared_prefix: int = 0,
+        page_size: int = 16,
+        seed: int = 0,
+        use_graphs: bool = True,
+    ):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.n = int(n_requests)
+        self.bw = int(beam_width)
+        self.rows = self.n * self.bw
+        self.sizes = [int(s) for s in sizes]
+        self.steps = len(self.sizes)
+        self.token_base = int(token_base)
+        self.trie = trie
+        self.use_graphs = bool(use_graphs)
+        self.prompt_lens = [int(p) for p in prompt_lens]
+        assert len(self.prompt_lens) == self.n
+        dev = self.device
+        g = torch.Generator(device=dev)
+        g.manual_seed(seed)
+
+        # ---- KV pool: [page 0 dummy][shared prefix][per-request prompts][decode slots] ----
+        uniq_prompt = shared_prefix + sum(max(p - shared_prefix, 0) for p in self.prompt_lens)
+        decode_slots = self.rows * self.steps
+        num_tokens = page_size + uniq_prompt + decode_slots
+        num_tokens = (num_tokens + page_size - 1) // page_size * page_size
+        self.pool = TokenToKVPool(cfg.num_hidden_layers, num_tokens, cfg.num_key_value_heads, cfg.head_dim, _FP8, dev,
+                                  page_size=page_size)
+        n_prompt_slots = uniq_prompt
+        for layer in range(cfg.num_hidden_layers):  # synthetic "prefill" contents
+            for cache in (self.pool.k[layer], self.pool.v[layer]):
+                blk = torch.randn((n_prompt_slots, cfg.num_key_value_heads, cfg.head_dim), generator=g, device=dev,
+                                  dtype=torch.float32)
+                cache[page_size: page_size + n_prompt_slots].copy_(blk.to(torch.bfloat16).to(_FP8))
+        # slot table: row -> slot ids, like ReqToTokenPool.req_to_token (kvcache/pool.py:142-183)
+        self.max_seq = max(self.prompt_lens) + self.steps
+        table = torch.zeros((self.rows, self.max_seq), dtype=torch.int32)
+        shared = torch.arange(page_size, page_size + shared_prefix, dtype=torch.int32)
+        cursor = page_size + shared_prefix
+        for r, plen in enumerate(self.prompt_lens):
+            own = torch.arange(cursor, cursor + max(plen - shared_prefix, 0), dtype=torch.int32)
+            cursor += int(own.numel())
+            slots = torch.cat((shared[: min(plen, shared_prefix)], own))
+            table[r * self.bw: (r + 1) * self.bw, :plen] = slots[None, :]
+        self.req_to_token = table.to(dev)
+        self.decode_slot_base = page_size + uniq_prompt
+        plen_rows = torch.tensor(self.prompt_lens, dtype=torch.int64).repeat_interleave(self.bw)
+        self.prompt_len_rows = plen_rows.to(dev)
+        self.tail_cols = (plen_rows[:, None] + torch.arange(self.steps)[None, :]).to(dev)  # [rows, steps]
+        self.rows_idx = torch.arange(self.rows, dtype=torch.int64, device=dev)
+        self.row_base = (torch.arange(self.n, dtype=torch.int64, device=dev) * self.bw)[:, None]
+
+        # ---- model + head ----------------------------------------------------------------
+        self.attn = AttentionBackend(self.pool, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim)
+        self.attn.set_groups(torch.arange(self.n + 1, dtype=torch.int32, device=dev) * self.bw, self.bw)
+        self.model = Qwen3ForCausalLM(cfg, self.attn, dev)
+        self.model.init_random(seed=seed + 1)
+        sid_total = sum(self.sizes)
+        sid_w = torch.randn((sid_total, cfg.hidden_size), generator=g, device=dev, dtype=torch.float32) * 0.02
+        self.head = RestrictedLMHead(list(range(self.token_base, self.token_base + sid_total)))
+        from flashrec_b200.layers import quantize_weight_fp8
+
+        self.head.bind_quantized(*quantize_weight_fp8(sid_w))
+        self.head.bind_codebook(self.sizes)
+        self.level_tok_base = [self.token_base + sum(self.sizes[:l]) for l in range(self.steps)]
+
+        # ---- static step buffers ------------------------------------------------------------
+        i64 = dict(dtype=torch.int64, device=dev)
+        self.input_ids = torch.zeros(self.rows, **i64)
+        self.positions = torch.zeros(self.rows, **i64)
+        self.out_cache_loc = torch.zeros(self.rows, **i64)
+        self.seq_lens = torch.zeros(self.rows, dtype=torch.int32, device=dev)
+        total_idx = sum(self.prompt_lens) * self.bw + self.rows * self.steps
+        self.kv_indices = torch.zeros(total_idx, dtype=torch.int32, device=dev)
+        self.kv_indptr = torch.zeros(self.rows + 1, dtype=torch.int32, device=dev)
+        self.cum = torch.zeros((self.n, self.bw), dtype=torch.float32, device=dev)
+        self.node_planes = [torch.zeros((self.n, self.bw), **i64) for _ in range(2)]
+        self.tok_planes = [torch.zeros((self.n, self.bw, self.steps), **i64) for _ in range(2)]
+        self.col = torch.zeros(self.n, dtype=torch.int32, device=dev)
+        self.outs = [
+            BeamStepOut(
+                vals=torch.empty((self.n, self.bw), dtype=torch.float32, device=dev),
+                parents=torch.empty((self.n, self.bw), **i64), tokens=torch.empty((self.n, self.bw), **i64),
+                indices=torch.empty((self.n, self.bw), **i64), child=torch.empty((self.n, self.bw), **i64))
+            for _ in range(self.steps)
+        ]
+        # pinned host staging for the per-step inputs and the final result
+        self.h_loc = torch.empty((self.steps, self.rows), dtype=torch.int64).pin_memory()
+        for s in range(self.steps):
+            self.h_loc[s] = self.decode_slot_base + s * self.rows + torch.arange(self.rows)
+        self.d_loc = self.h_loc.to(dev)  # device-resident copy for runs that exclude host traffic
+        self.h_vals = torch.empty((self.n, self.bw), dtype=torch.float32).pin_memory()
+        self.h_tokens = torch.empty((self.n, self.bw, self.steps), dtype=torch.int64).pin_memory()
+        self.graphs: List[Optional[torch.cuda.CUDAGraph]] = [None] * self.steps
+        self.kernel_launches_per_step: List[int] = [0] * self.steps
+        self.reset()
+
+    # ------------------------------------------------------------------------------------
+    def reset(self) -> None:
+        """Beam state before the first step: one live beam per request at the trie root."""
+        self.cum.fill_(float("-inf"))
+        self.cum[:, 0] = 0.0
+        self.node_planes[0].zero_()
+        self.tok_planes[0].zero_()
+        self.input_ids.fill_(self.token_base)  # stand-in for the last prompt token
+        self.positions.copy_(self.prompt_len_rows)
+        self.seq_lens.copy_((self.prompt_len_rows + 1).to(torch.int32))
+
+    def _step_body(self, s: int) -> None:
+        """Device work of decode step ``s`` (level ``s``); allocation-stable, capturable."""
+        src, dst = s & 1, (s & 1) ^ 1
+        # KV slot of this step's input token goes into the row's slot table
+        self.req_to_token[self.rows_idx, self.positions] = self.out_cache_loc.to(torch.int32)
+        gather_kv_indices(self.req_to_token, self.rows_idx, self.seq_lens, out=self.kv_indices,
+                          indptr_out=self.kv_indptr)
+        batch = ForwardBatch(input_ids=self.input_ids, req_pool_indices=self.rows_idx, seq_lens=self.seq_lens,
+                             positions=self.positions, out_cache_loc=self.out_cache_loc, kv_indices=self.kv_indices,
+                             kv_indptr=self.kv_indptr)
+        self.attn.prepare(batch)
+        hidden = self.model.forward(batch)
+        logits, mx, ls, _ = self.head.logits_level(hidden, s)
+        self.col.fill_(s)
+        out = sid_beam_step(self.cum, logits, mx, ls, self.node_planes[src], self.trie, self.level_tok_base[s],
+                            self.bw, token_ids_in=self.tok_planes[src], token_ids_out=self.tok_planes[dst],
+                            node_ids_out=self.node_planes[dst], col=self.col, out=self.outs[s])
+        # bookkeeping for the next step (scheduler/kv_remap.py:30-66, scheduler.py:1594-1608)
+        self.cum.copy_(out.vals)
+        if self.trie is None:
+            self.node_planes[dst].fill_(-1)
+        self.input_ids.copy_(out.tokens.reshape(-1))
+        parent_rows = (self.row_base + out.parents).reshape(-1)
+        tails = self.req_to_token.gather(1, self.tail_cols)
+        self.req_to_token.scatter_(1, self.tail_cols, tails.index_select(0, parent_rows))
+        self.positions.add_(1)
+        self.seq_lens.add_(1)
+
+    def capture(self) -> None:
+        """Warm up and capture one CUDA graph per step."""
+        if not self.use_graphs:
+            return
+        stream = torch.cuda.Stream(device=self.device)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(stream):
+            self.run(host_io=False, _eager=True)  # warm-up: module loading, attribute setting
+        torch.cuda.current_stream(self.device).wait_stream(stream)
+        torch.cuda.synchronize(self.device)
+        self.reset()
+        for s in range(self.steps):
+            self.out_cache_loc.copy_(self.h_loc[s], non_blocking=True)
+            gph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gph):
+                self._step_body(s)
+            self.graphs[s] = gph
+        torch.cuda.synchronize(self.device)
+        self.reset()
+
+    def run(self, host_io: bool = True, _eager: bool = False) -> None:
+        """One wave: all decode steps. With ``host_io`` the per-step slot ids come
+        from pinned host memory and the final beams are read back to the host."""
+        self.reset()
+        for s in range(self.steps):
+            if host_io:
+                self.out_cache_loc.copy_(self.h_loc[s], non_blocking=True)
+            else:
+                self.out_cache_loc.copy_(self.d_loc[s])
+            if self.graphs[s] is not None and not _eager:
+                self.graphs[s].replay()
+            else:
+                self._step_body(s)
+        if host_io:
+            last = self.steps & 1
+            self.h_vals.copy_(self.cum, non_blocking=True)
+            self.h_tokens.copy_(self.tok_planes[last], non_blocking=True)
+            torch.cuda.current_stream(self.device).synchronize()
+
+    # results of the last run (device tensors)
+    @property
+    def final_tokens(self) -> torch.Tensor:
+        return self.tok_planes[self.steps & 1]
+
+    @property
+    def final_nodes(self) -> torch.Tensor:
+        return self.node_planes[self.steps & 1]

@@ -203,6 +203,44 @@ def decode_attention(q, k_cache, v_cache, kv_indptr, kv_indices, n_rep: int) -> 
     return out.to(q.dtype)
 
 
+def decoder_layer(x, residual, w, norms, positions, loc, cos_sin_cache, k_cache, v_cache, kv_indptr, kv_indices,
+                  hq: int, hkv: int, d: int, eps: float = 1e-6, trace: Optional[dict] = None):
+    """FP8 branch of Qwen3DecoderLayer.forward (models/qwen3.py:198-215) with
+    Qwen3Attention.forward (:62-134) and Qwen3MLP.forward (:144-172) inlined.
+    ``w`` maps qkv / o / gate_up / down to (e4m3 [N,K], scale [N]); ``norms`` maps
+    input / post / q / k to bf16 weights. residual None = first layer. If ``trace``
+    is a dict, every intermediate tensor is stored in it."""
+    t = trace if trace is not None else {}
+    rows = x.shape[0]
+    if residual is None:
+        residual = x
+        q, s = rmsnorm_quant_fp8(x, norms["input"], eps)
+    else:
+        q, s, residual = rmsnorm_quant_fp8(x, norms["input"], eps, residual=residual)
+    t.update(q1=q, s1=s, res1=residual)
+    qkv = fp8_scaled_mm(q, w["qkv"][0], s, w["qkv"][1])
+    t["qkv"] = qkv.clone()
+    qkv = qkv.view(rows, hq + 2 * hkv, d)
+    qn = qk_norm_rope_store_fp8(qkv[:, :hq], qkv[:, hq:hq + hkv], qkv[:, hq + hkv:], positions, loc, norms["q"],
+                                norms["k"], eps, cos_sin_cache, k_cache, v_cache)
+    t["qn"] = qn
+    a = decode_attention(qn, k_cache, v_cache, kv_indptr, kv_indices, hq // hkv).reshape(rows, -1)
+    t["attn"] = a
+    aq, asc = per_token_quant_fp8(a)
+    t.update(aq=aq, asc=asc)
+    h = fp8_scaled_mm(aq, w["o"][0], asc, w["o"][1])
+    t["o"] = h
+    q, s, residual = rmsnorm_quant_fp8(h, norms["post"], eps, residual=residual)
+    t.update(q2=q, s2=s, res2=residual)
+    gu = fp8_scaled_mm(q, w["gate_up"][0], s, w["gate_up"][1])
+    t["gu"] = gu
+    yq, ys = silu_mul_quant_fp8(gu)
+    t.update(yq=yq, ys=ys)
+    out = fp8_scaled_mm(yq, w["down"][0], ys, w["down"][1])
+    t["out"] = out
+    return out, residual
+
+
 # ---------------------------------------------------------------------------
 # SID head + beam step
 # ---------------------------------------------------------------------------
@@ -343,14 +381,17 @@ def mask_topk_expand(cum, top_logprobs, top_tokens, select_k, node_ids=None, tri
 
 
 def sid_beam_step(cum, logits, node_ids, trie: Optional[OracleTrie], level_tok_base: int, select_k: int,
-                  token_ids=None, col=0):
+                  token_ids=None, col=0, stats=None):
     """Full-width step: every code of the level is a candidate of every beam;
     score = cum + ((logit - max) - logsum); -inf scores are not candidates.
     cum [N,BW], logits [N*BW, K_l] fp32, node_ids [N,BW]."""
     n, bw = cum.shape
     kl = logits.shape[1]
-    mx, ls = row_stats(logits)
+    mx, ls = row_stats(logits) if stats is None else stats
     lp = logprobs_from_stats(logits, mx, ls).view(n, bw, kl)
+    if trie is None:  # unconstrained: every node id behaves like -1, -inf scores are still dropped
+        trie = OracleTrie(np.zeros(0, np.int64), np.zeros(0, np.int64), 1, 0, 0)
+        node_ids = torch.full((n, bw), -1, dtype=torch.int64)
     toks = (level_tok_base + torch.arange(kl, dtype=torch.int64))[None, None, :].expand(n, bw, kl)
     return mask_topk_expand(cum, lp, toks, select_k, node_ids=node_ids, trie=trie, token_ids=token_ids, col=col,
                             apply_mask=True)

@@ -1,0 +1,433 @@
+"""GPU parity: QK-norm+RoPE+KV write, slot gather, decode attention, SID head,
+trie mask / advance / expand and the fused beam step, against the CPU oracle and
+the reference's golden outputs."""
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import bf16_from_bits, bits8, bits16, fp8_from_bits, load_golden
+from oracle import sid_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+FP8 = torch.float8_e4m3fn
+
+
+def _zeros_fp8(*shape, device="cpu"):
+    return torch.zeros(shape, dtype=torch.uint8, device=device).view(FP8)
+
+
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("t,nq,nkv,d", [(7, 16, 8, 128), (33, 4, 2, 128), (5, 8, 8, 64), (1, 2, 1, 128)])
+def test_qk_norm_rope_kv(t, nq, nkv, d):
+    from flashrec_b200.kernel.qk_rope_kv import fused_qk_norm_rope_store_fp8
+
+    g = torch.Generator().manual_seed(t * 17 + nq)
+    qkv = torch.randn(t, nq + 2 * nkv, d, generator=g).bfloat16()
+    qw = (1 + 0.1 * torch.randn(d, generator=g)).bfloat16()
+    kw = (1 + 0.1 * torch.randn(d, generator=g)).bfloat16()
+    cs = O.build_cos_sin_cache(d, 300, 1e6)
+    pos = torch.randint(0, 300, (t,), generator=g)
+    slots = 64
+    loc = torch.randperm(slots - 1, generator=g)[:t] + 1
+    kc_ref, vc_ref = _zeros_fp8(slots, nkv, d), _zeros_fp8(slots, nkv, d)
+    q_ref = O.qk_norm_rope_store_fp8(qkv[:, :nq], qkv[:, nq:nq + nkv], qkv[:, nq + nkv:], pos, loc, qw, kw, 1e-6, cs,
+                                     kc_ref, vc_ref)
+    dev = qkv.to(DEV)
+    kc, vc = _zeros_fp8(slots, nkv, d, device=DEV), _zeros_fp8(slots, nkv, d, device=DEV)
+    ok = fused_qk_norm_rope_store_fp8(dev[:, :nq], dev[:, nq:nq + nkv], dev[:, nq + nkv:], pos.to(DEV), loc.to(DEV),
+                                      qw.to(DEV), kw.to(DEV), 1e-6, cs.to(DEV), kc, vc)
+    assert ok is True
+    assert np.array_equal(bits8(kc), bits8(kc_ref))  # K: bf16 then e4m3, bit exact
+    assert np.array_equal(bits8(vc), bits8(vc_ref))
+    assert np.array_equal(bits16(dev[:, :nq]), bits16(q_ref))  # Q rewritten in place inside the fused buffer
+    assert np.array_equal(bits16(dev[:, nq:]), bits16(qkv[:, nq:]))  # K/V inputs untouched
+
+
+def test_kv_store_and_rope_cache_golden():
+    from flashrec_b200.attention import TokenToKVPool
+    from flashrec_b200.layers import build_cos_sin_cache
+
+    g = load_golden("rope_kv")
+    assert np.array_equal(build_cos_sin_cache(128, 64, 1e6, device=DEV).cpu().numpy(), g["cos_sin"])
+    pool = TokenToKVPool(1, 40, 2, 128, FP8, DEV)
+    pool.store(0, bf16_from_bits(g["k"]).to(DEV), bf16_from_bits(g["v"]).to(DEV), torch.from_numpy(g["loc"]).to(DEV))
+    assert np.array_equal(bits8(pool.k[0]), g["k_cache"]) and np.array_equal(bits8(pool.v[0]), g["v_cache"])
+
+
+def test_gather_kv_indices_golden_and_ragged():
+    from flashrec_b200.attention import gather_kv_indices
+
+    g = load_golden("attention")
+    out = gather_kv_indices(torch.from_numpy(g["table"]).to(DEV), torch.from_numpy(g["rows"]).to(DEV),
+                            g["seq_lens"].tolist())
+    assert np.array_equal(out.cpu().numpy(), g["kv_indices"])
+    # the reference's own test vector (tests/test_kv_pool.py:9-25)
+    table = torch.arange(40, dtype=torch.int32, device=DEV).view(4, 10)
+    out = gather_kv_indices(table, torch.tensor([0, 1, 1], device=DEV), [3, 1, 4])
+    assert out.cpu().tolist() == [0, 1, 2, 10, 10, 11, 12, 13]
+    # many rows, zero-length rows, device seq_lens + preallocated outputs (no sync)
+    rng = np.random.default_rng(0)
+    n = 3000
+    table = torch.from_numpy(rng.integers(0, 1 << 20, (64, 300)).astype(np.int32)).to(DEV)
+    rows = torch.from_numpy(rng.integers(0, 64, n)).to(DEV)
+    sl = rng.integers(0, 301, n).astype(np.int32)
+    indptr = torch.empty(n + 1, dtype=torch.int32, device=DEV)
+    buf = torch.full((int(sl.sum()) + 5,), -7, dtype=torch.int32, device=DEV)
+    gather_kv_indices(table, rows, torch.from_numpy(sl).to(DEV), out=buf, indptr_out=indptr)
+    ref = O.gather_kv_indices(table.cpu(), rows.cpu(), sl.tolist())
+    assert np.array_equal(buf[: ref.numel()].cpu().numpy(), ref.numpy())
+    assert buf[ref.numel():].eq(-7).all()
+    assert np.array_equal(indptr.cpu().numpy(), np.concatenate([[0], np.cumsum(sl)]))
+
+
+# ---------------------------------------------------------------------------
+def _attn_case(n_groups, bw, prefix_lens, tails, hq, hkv, seed, slots=4096):
+    """Beams of each group share a prompt prefix and own `tails[g]` private slots."""
+    rng = np.random.default_rng(seed)
+    d = 128
+    kc = torch.from_numpy(rng.standard_normal((slots, hkv, d)).astype(np.float32)).bfloat16().to(FP8)
+    vc = torch.from_numpy(rng.standard_normal((slots, hkv, d)).astype(np.float32)).bfloat16().to(FP8)
+    free = list(rng.permutation(np.arange(1, slots)))
+    lists, group_rows = [], [0]
+    for gi in range(n_groups):
+        prefix = [int(free.pop()) for _ in range(prefix_lens[gi])]
+        for _ in range(bw[gi]):
+            lists.append(prefix + [int(free.pop()) for _ in range(tails[gi])])
+        group_rows.append(group_rows[-1] + bw[gi])
+    indptr = np.concatenate([[0], np.cumsum([len(x) for x in lists])]).astype(np.int32)
+    indices = np.concatenate([np.asarray(x, dtype=np.int32) for x in lists]) if lists else np.zeros(0, np.int32)
+    t = group_rows[-1]
+    q = torch.from_numpy(rng.standard_normal((t, hq, d)).astype(np.float32)).bfloat16()
+    return q, kc, vc, torch.from_numpy(indptr), torch.from_numpy(indices), torch.tensor(group_rows, dtype=torch.int32)
+
+
+def _run_attn(q, kc, vc, indptr, indices, group_rows, hq, hkv, expect_shared=None):
+    from flashrec_b200.attention import AttentionBackend, TokenToKVPool
+    from flashrec_b200.decoder import ForwardBatch
+
+    slots = kc.shape[0]
+    pool = TokenToKVPool(1, slots, hkv, 128, FP8, DEV)
+    pool.k[0].copy_(kc.to(DEV))
+    pool.v[0].copy_(vc.to(DEV))
+    be = AttentionBackend(pool, hq, hkv, 128)
+    gr = group_rows.to(DEV)
+    be.set_groups(gr, int((group_rows[1:] - group_rows[:-1]).max()))
+    t = q.shape[0]
+    batch = ForwardBatch(input_ids=torch.zeros(t, dtype=torch.int64, device=DEV), req_pool_indices=None,
+                         seq_lens=(indptr[1:] - indptr[:-1]).to(DEV), positions=torch.zeros(t, dtype=torch.int64),
+                         out_cache_loc=torch.zeros(t, dtype=torch.int64), kv_indices=indices.to(DEV),
+                         kv_indptr=indptr.to(DEV))
+    be.prepare(batch)
+    if expect_shared is not None:
+        assert be._shared_len[: len(expect_shared)].cpu().tolist() == expect_shared
+    return be.forward(q.to(DEV), None, None, 0, batch, skip_store=True)
+
+
+@pytest.mark.parametrize("hq,hkv", [(16, 8), (8, 8), (8, 2), (8, 1)])
+def test_decode_attention_shared_prefix(hq, hkv):
+    bw, pre, tails = [40, 3, 1], [257, 64, 5], [1, 3, 0]
+    q, kc, vc, indptr, indices, gr = _attn_case(3, bw, pre, tails, hq, hkv, seed=hq * 10 + hkv)
+    out = _run_attn(q, kc, vc, indptr, indices, gr, hq, hkv, expect_shared=[257, 64, 5])
+    ref = O.decode_attention(q, kc, vc, indptr, indices, hq // hkv).float()
+    err = (out.float().cpu() - ref).abs().max() / ref.abs().max()
+    assert err < 2e-2, err
+
+
+def test_decode_attention_no_sharing_and_empty_rows():
+    # per-row groups (the reference's flat interface): every list is its own prefix
+    q, kc, vc, indptr, indices, _ = _attn_case(1, [6], [0], [9], 16, 8, seed=5)
+    gr = torch.arange(7, dtype=torch.int32)
+    out = _run_attn(q, kc, vc, indptr, indices, gr, 16, 8)
+    ref = O.decode_attention(q, kc, vc, indptr, indices, 2).float()
+    assert (out.float().cpu() - ref).abs().max() / ref.abs().max() < 2e-2
+    # one group, nothing shared: all tokens go through the per-row tail path
+    out2 = _run_attn(q, kc, vc, indptr, indices, torch.tensor([0, 6], dtype=torch.int32), 16, 8, expect_shared=[0])
+    assert (out2.float().cpu() - ref).abs().max() / ref.abs().max() < 2e-2
+    # a row with an empty slot list yields zeros
+    indptr2 = indptr.clone()
+    indptr2[1:] = indptr[1:] - 9
+    indptr2[1] = 0
+    out3 = _run_attn(q, kc, vc, indptr2, indices[9:], gr, 16, 8)
+    assert out3[0].abs().max() == 0
+
+
+def test_decode_attention_golden_reference():
+    g = load_golden("attention")
+    q = bf16_from_bits(g["q"])
+    kc, vc = fp8_from_bits(g["k_cache"]), fp8_from_bits(g["v_cache"])
+    gr = torch.arange(5, dtype=torch.int32)
+    out = _run_attn(q, kc, vc, torch.from_numpy(g["indptr"]), torch.from_numpy(g["kv_indices"]), gr, 4, 2)
+    ref = bf16_from_bits(g["out"]).float()
+    assert torch.allclose(out.float().cpu(), ref, rtol=2e-2, atol=2e-2)
+
+
+# ---------------------------------------------------------------------------
+def test_head_logprobs_and_topk():
+    from flashrec_b200.logits import RestrictedLMHead, topk_rows
+
+    g = load_golden("head")
+    sizes, base = g["sizes"].tolist(), int(g["base"])
+    head = RestrictedLMHead(list(range(base, base + sum(sizes))))
+    head.bind_quantized(fp8_from_bits(g["sid_q"]).to(DEV), torch.from_numpy(g["sid_s"]).to(DEV))
+    head.bind_codebook(sizes)
+    h = bf16_from_bits(g["h"])
+    lp, ids = head.compute(h.to(DEV))
+    hq, hs = O.per_token_quant_fp8(h)
+    logits = O.fp8_logits_f32(hq, fp8_from_bits(g["sid_q"]), hs, torch.from_numpy(g["sid_s"]))
+    assert torch.allclose(lp.cpu(), O.log_softmax_rows(logits), atol=2e-5)
+    assert torch.allclose(lp.cpu(), torch.from_numpy(g["lp_all"]), atol=6e-2)  # reference bf16 head
+    assert np.array_equal(ids.cpu().numpy(), g["ids_all"])
+    lp1, ids1 = head.compute_level(h.to(DEV), 1)
+    assert torch.allclose(lp1.cpu(), O.log_softmax_rows(logits[:, 32:64]), atol=2e-5)
+    assert np.array_equal(ids1.cpu().numpy(), g["ids1"])
+    out = torch.empty_like(lp)
+    head.compute_into(h.to(DEV), None, out)
+    assert torch.equal(out, lp)
+    # fused statistics path
+    lg, mx, ls, _ = head.logits_level(h.to(DEV), 2)
+    assert torch.allclose(((lg - mx[:, None]) - ls[:, None]).cpu(), O.log_softmax_rows(logits[:, 64:]), atol=2e-5)
+    # per-row top-k: sorted, deterministic ties
+    vals, idx = topk_rows(lp1, 10)
+    rv, ri = O.topk_rows(lp1.cpu(), 10)
+    assert torch.equal(vals.cpu(), rv) and torch.equal(idx.cpu(), ri)
+
+
+@pytest.mark.parametrize("rows,cols,k", [(5, 8192, 1024), (3, 100, 100), (4, 4096, 1), (2, 777, 300)])
+def test_topk_rows_with_ties(rows, cols, k):
+    from flashrec_b200.logits import topk_rows
+
+    g = torch.Generator().manual_seed(cols)
+    x = torch.randn(rows, cols, generator=g)
+    x[0] = torch.round(x[0] * 2) / 2  # heavy ties
+    x[-1, :] = -1.5  # all equal
+    vals, idx = topk_rows(x.to(DEV), k)
+    rv, ri = O.topk_rows(x, k)
+    assert torch.equal(vals.cpu(), rv) and torch.equal(idx.cpu(), ri)
+
+
+# ---------------------------------------------------------------------------
+def _golden_trie_dev(layout):
+    from flashrec_b200.trie import build_trie_arrays, trie_to_device
+
+    g = load_golden("trie")
+    arrays = build_trie_arrays(g["items"], g["sizes"].tolist(), int(g["base"]))
+    return g, trie_to_device(arrays, layout, DEV)
+
+
+@pytest.mark.parametrize("layout", ["dense", "csr", "bitmap"])
+def test_trie_mask_advance_golden(layout):
+    from flashrec_b200.kernel.beam_trie import trie_advance_nodes, trie_mask_candidates
+
+    g, tr = _golden_trie_dev(layout)
+    masked = trie_mask_candidates(torch.from_numpy(g["scores"]).to(DEV), torch.from_numpy(g["toks"]).to(DEV),
+                                  torch.from_numpy(g["nodes"]).to(DEV), tr, int(g["base"]))
+    assert np.array_equal(masked.cpu().numpy(), g["masked"])
+    adv = trie_advance_nodes(torch.from_numpy(g["nodes"]).to(DEV), torch.from_numpy(g["parents"]).to(DEV),
+                             torch.from_numpy(g["atoks"]).to(DEV), tr, int(g["base"]), int(g["invalid"]))
+    assert np.array_equal(adv.cpu().numpy(), g["adv"])
+
+
+def test_trie_dense_tensor_interface_and_expand():
+    """The reference's tensor signatures: dense allow/next tables passed directly."""
+    from flashrec_b200.kernel.beam_trie import beam_expand_token_ids, trie_advance_nodes, trie_mask_candidates
+
+    g = load_golden("trie")
+    allow = torch.from_numpy(g["allow"]).to(DEV)
+    nxt = torch.from_numpy(g["next"]).to(DEV)
+    masked = trie_mask_candidates(torch.from_numpy(g["scores"]).to(DEV), torch.from_numpy(g["toks"]).to(DEV),
+                                  torch.from_numpy(g["nodes"]).to(DEV), allow, int(g["base"]))
+    assert np.array_equal(masked.cpu().numpy(), g["masked"])
+    for table in (nxt, nxt.to(torch.int64)):
+        adv = trie_advance_nodes(torch.from_numpy(g["nodes"]).to(DEV), torch.from_numpy(g["parents"]).to(DEV),
+                                 torch.from_numpy(g["atoks"]).to(DEV), table, int(g["base"]), int(g["invalid"]))
+        assert np.array_equal(adv.cpu().numpy(), g["adv"])
+    tid = torch.arange(24, dtype=torch.int64, device=DEV).view(6, 4)
+    par = torch.tensor([5, 0, 0, 3, 9, -2], device=DEV)  # out-of-range parents are clamped
+    new = torch.arange(100, 106, device=DEV)
+    out = beam_expand_token_ids(tid, par, new, 2)
+    ref = tid[par.clamp(0, 5)].clone()
+    ref[:, 2] = new
+    assert torch.equal(out, ref)
+
+
+@pytest.mark.parametrize("layout", ["dense", "csr", "bitmap"])
+def test_mask_topk_expand_golden(layout):
+    from flashrec_b200.kernel.beam_trie import genrec_mask_topk_expand
+
+    g, tr = _golden_trie_dev(layout)
+    b = load_golden("beam_step")
+    res = genrec_mask_topk_expand(torch.from_numpy(b["cum"]).to(DEV), torch.from_numpy(b["lp"]).to(DEV),
+                                  torch.from_numpy(b["tok"]).to(DEV), select_k=16,
+                                  node_ids=torch.from_numpy(b["node_in"]).to(DEV), allow_table=tr,
+                                  token_base=int(g["base"]), token_ids=torch.from_numpy(b["token_ids"]).to(DEV),
+                                  col=1, invalid_node=int(g["invalid"]))
+    live = np.isfinite(b["vals"])
+    assert np.array_equal(np.isfinite(res.vals.cpu().numpy()), live)
+    assert np.array_equal(res.vals.cpu().numpy()[live], b["vals"][live])
+    assert np.array_equal(res.parents.cpu().numpy()[live], b["parents"][live])
+    assert np.array_equal(res.tokens.cpu().numpy()[live], b["tokens"][live])
+    assert np.array_equal(res.indices.cpu().numpy()[live], b["indices"][live])
+    assert np.array_equal(res.token_ids.cpu().numpy()[live], b["token_ids_out"][live])
+    assert np.array_equal(res.node_ids.cpu().numpy()[live], b["node_out"][live])
+
+
+def _random_step(seed, n, bw, c, k, L, n_items=400, sizes=(16, 16, 16), ties=False):
+    from flashrec_b200.trie import build_trie_arrays
+
+    rng = np.random.default_rng(seed)
+    base = 5000
+    items = np.stack([rng.integers(0, s, n_items) for s in sizes], axis=1)
+    arrays = build_trie_arrays(items, list(sizes), base)
+    cum = torch.from_numpy(rng.standard_normal((n, bw)).astype(np.float32))
+    cum[0, bw // 2:] = float("-inf")  # dead beams
+    lp = torch.from_numpy(rng.standard_normal((n, bw, c)).astype(np.float32))
+    if ties:
+        lp = torch.round(lp * 2) / 2
+        cum = torch.round(cum)
+        cum[0, bw // 2:] = float("-inf")
+    lp = torch.sort(lp, dim=-1, descending=True).values
+    tok = torch.from_numpy(rng.integers(base + sizes[0], base + sizes[0] + sizes[1], (n, bw, c)))
+    n1 = int(arrays.level_start[2] - arrays.level_start[1])
+    nodes = torch.from_numpy(rng.integers(1, 1 + n1, (n, bw)))
+    nodes[-1, 0] = -1  # unconstrained beam
+    nodes[-1, 1] = arrays.invalid_node
+    token_ids = torch.from_numpy(rng.integers(base, base + 16, (n, bw, L)))
+    return arrays, cum, lp, tok, nodes, token_ids
+
+
+@pytest.mark.parametrize("layout", ["dense", "csr", "bitmap"])
+@pytest.mark.parametrize("n,bw,c,k,ties", [(3, 64, 32, 64, False), (2, 512, 64, 512, False), (2, 33, 7, 20, True),
+                                           (1, 2048, 16, 2048, False), (2, 16, 8, 16, True)])
+def test_mask_topk_expand_vs_oracle(layout, n, bw, c, k, ties):
+    from flashrec_b200.kernel.beam_trie import genrec_mask_topk_expand
+    from flashrec_b200.trie import trie_to_device
+
+    arrays, cum, lp, tok, nodes, token_ids = _random_step(n * 1000 + bw + c, n, bw, c, k, 4, ties=ties)
+    tr = trie_to_device(arrays, layout, DEV)
+    otr = O.OracleTrie(arrays.csr_keys, arrays.edge_child, arrays.vsz, arrays.token_base, arrays.invalid_node)
+    col = torch.tensor([1, 2, 3][:n], dtype=torch.int32)
+    ref = O.mask_topk_expand(cum, lp, tok, k, node_ids=nodes, trie=otr, token_ids=token_ids, col=col)
+    res = genrec_mask_topk_expand(cum.to(DEV), lp.to(DEV), tok.to(DEV), select_k=k, node_ids=nodes.to(DEV),
+                                  allow_table=tr, token_base=arrays.token_base, token_ids=token_ids.to(DEV),
+                                  col=col.to(DEV), invalid_node=arrays.invalid_node)
+    assert torch.equal(res.vals.cpu(), ref["vals"])  # same fp32 adds, bit exact
+    assert torch.equal(res.parents.cpu(), ref["parents"])
+    assert torch.equal(res.tokens.cpu(), ref["tokens"])
+    assert torch.equal(res.indices.cpu(), ref["indices"])
+    assert torch.equal(res.token_ids.cpu(), ref["token_ids"])
+    assert torch.equal(res.node_ids.cpu(), ref["node_ids"])
+    # unmasked variant: -inf candidates are ordinary candidates, ordered by index
+    ref_u = O.mask_topk_expand(cum, lp, tok, k, apply_mask=False, token_ids=token_ids, col=col)
+    res_u = genrec_mask_topk_expand(cum.to(DEV), lp.to(DEV), tok.to(DEV), select_k=k, apply_mask=False,
+                                    token_ids=token_ids.to(DEV), col=col.to(DEV))
+    assert torch.equal(res_u.vals.cpu(), ref_u["vals"])
+    assert torch.equal(res_u.indices.cpu(), ref_u["indices"])
+    assert torch.equal(res_u.token_ids.cpu(), ref_u["token_ids"])
+    assert res_u.node_ids is None
+
+
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("layout", ["dense", "csr", "bitmap", None])
+@pytest.mark.parametrize("n,bw,kl", [(3, 48, 64), (2, 512, 256)])
+def test_sid_beam_step_full_width(layout, n, bw, kl):
+    """Every code of the level is a candidate; the three trie layouts agree with
+    the oracle (and hence with each other) bit for bit."""
+    from flashrec_b200._lib import call, ptr, stream_ptr
+    from flashrec_b200.sid_decode import sid_beam_step
+    from flashrec_b200.trie import build_trie_arrays, trie_to_device
+
+    rng = np.random.default_rng(n * 100 + bw)
+    sizes, base = [kl, kl, kl], 7000
+    items = np.stack([rng.integers(0, kl, 3000) for _ in sizes], axis=1)
+    arrays = build_trie_arrays(items, sizes, base)
+    otr = O.OracleTrie(arrays.csr_keys, arrays.edge_child, arrays.vsz, base, arrays.invalid_node)
+    tr = trie_to_device(arrays, layout, DEV) if layout else None
+    level = 1
+    n1 = int(arrays.level_start[2] - arrays.level_start[1])
+    nodes = torch.from_numpy(rng.integers(1, 1 + n1, (n, bw)))
+    nodes[0, 0] = -1
+    nodes[0, 1] = arrays.invalid_node
+    cum = torch.from_numpy(rng.standard_normal((n, bw)).astype(np.float32))
+    cum[-1, bw // 3:] = float("-inf")
+    logits = torch.from_numpy((3 * rng.standard_normal((n * bw, kl))).astype(np.float32))
+    token_ids = torch.from_numpy(rng.integers(base, base + kl, (n, bw, 3)))
+    lg = logits.to(DEV)
+    mx = torch.empty(n * bw, device=DEV)
+    ls = torch.empty(n * bw, device=DEV)
+    call("fr_logsumexp_rows", ptr(lg), lg.stride(0), ptr(mx), ptr(ls), None, 0, n * bw, kl, stream_ptr(lg.device))
+    rmx, rls = O.row_stats(logits)
+    assert torch.allclose(mx.cpu(), rmx) and torch.allclose(ls.cpu(), rls, atol=1e-5)
+    tok_out = torch.zeros_like(token_ids).to(DEV)
+    node_out = torch.zeros_like(nodes).to(DEV)
+    col = torch.full((n,), level, dtype=torch.int32, device=DEV)
+    out = sid_beam_step(cum.to(DEV), lg, mx, ls, nodes.to(DEV), tr, base + kl * level, bw,
+                        token_ids_in=token_ids.to(DEV), token_ids_out=tok_out, node_ids_out=node_out, col=col)
+    ref = O.sid_beam_step(cum, logits, nodes, otr if layout else None, base + kl * level, bw, token_ids=token_ids,
+                          col=level, stats=(mx.cpu(), ls.cpu()))
+    assert torch.equal(out.vals.cpu(), ref["vals"])
+    assert torch.equal(out.indices.cpu(), ref["indices"])
+    assert torch.equal(out.parents.cpu(), ref["parents"])
+    assert torch.equal(out.tokens.cpu(), ref["tokens"])
+    assert torch.equal(tok_out.cpu(), ref["token_ids"])
+    if layout:
+        assert torch.equal(out.child.cpu(), ref["child"])
+        assert torch.equal(node_out.cpu(), ref["node_ids"])
+        live = torch.isfinite(ref["vals"])
+        legal = otr.allowed(nodes.numpy()[np.arange(n)[:, None], ref["parents"].numpy()], ref["tokens"].numpy())
+        assert legal[live.numpy()].all()  # illegal-SID rate 0
+
+
+def test_merge_shards_equals_unsharded():
+    """Token-range sharded head: per-shard steps + merge == one unsharded step."""
+    import ctypes
+
+    from flashrec_b200._lib import call, ptr, stream_ptr
+    from flashrec_b200.sid_decode import BeamStepOut, sid_beam_step
+    from flashrec_b200.trie import build_trie_arrays, trie_to_device
+
+    rng = np.random.default_rng(11)
+    n, bw, kl, S = 2, 64, 256, 4
+    sizes, base = [kl, kl], 100
+    arrays = build_trie_arrays(np.stack([rng.integers(0, kl, 5000) for _ in sizes], axis=1), sizes, base)
+    tr = trie_to_device(arrays, "csr", DEV)
+    n1 = int(arrays.level_start[2] - arrays.level_start[1])
+    nodes = torch.from_numpy(rng.integers(1, 1 + n1, (n, bw))).to(DEV)
+    cum = torch.from_numpy(rng.standard_normal((n, bw)).astype(np.float32)).to(DEV)
+    logits = torch.from_numpy(rng.standard_normal((n * bw, kl)).astype(np.float32)).to(DEV)
+    token_ids = torch.from_numpy(rng.integers(base, base + kl, (n, bw, 2))).to(DEV)
+    mx = torch.empty(n * bw, device=DEV)
+    ls = torch.empty(n * bw, device=DEV)
+    call("fr_logsumexp_rows", ptr(logits), logits.stride(0), ptr(mx), ptr(ls), None, 0, n * bw, kl, stream_ptr(logits.device))
+    col = torch.ones(n, dtype=torch.int32, device=DEV)
+    tok_ref, node_ref = torch.zeros_like(token_ids), torch.zeros_like(nodes)
+    full = sid_beam_step(cum, logits, mx, ls, nodes, tr, base + kl, bw, token_ids_in=token_ids, token_ids_out=tok_ref,
+                         node_ids_out=node_ref, col=col)
+    # shard statistics -> combined statistics
+    w = kl // S
+    smx = torch.empty((S, n * bw), device=DEV)
+    sls = torch.empty((S, n * bw), device=DEV)
+    for s in range(S):
+        part = logits[:, s * w:(s + 1) * w]
+        call("fr_logsumexp_rows", ptr(part), part.stride(0), ptr(smx[s]), ptr(sls[s]), None, 0, n * bw, w,
+             stream_ptr(logits.device))
+    gmx, gls = torch.empty_like(mx), torch.empty_like(ls)
+    call("fr_lse_combine_shards", ptr(smx), ptr(sls), ptr(gmx), ptr(gls), S, n * bw, stream_ptr(logits.device))
+    assert torch.allclose(gmx, mx) and torch.allclose(gls, ls, atol=1e-5)
+    vals = torch.empty((S, n, bw), device=DEV)
+    idx = torch.empty((S, n, bw), dtype=torch.int64, device=DEV)
+    child = torch.empty((S, n, bw), dtype=torch.int64, device=DEV)
+    for s in range(S):
+        part = logits[:, s * w:(s + 1) * w]
+        o = sid_beam_step(cum, part, mx, ls, nodes, tr, base + kl, bw, idx_base=s * w, idx_width=kl)
+        vals[s], idx[s], child[s] = o.vals, o.indices, o.child
+    m = BeamStepOut(*(torch.empty((n, bw), dtype=dt, device=DEV)
+                      for dt in (torch.float32, torch.int64, torch.int64, torch.int64, torch.int64)))
+    tok_out, node_out = torch.zeros_like(token_ids), torch.zeros_like(nodes)
+    call("fr_topk_merge_shards", ptr(m.vals), ptr(m.parents), ptr(m.tokens), ptr(m.indices), ptr(m.child), ptr(vals),
+         ptr(idx), ptr(child), ptr(nodes), ptr(token_ids), ptr(tok_out), ptr(node_out), None, ptr(col), base + kl, kl,
+         S, n, bw, bw, 2, 1, 1, stream_ptr(logits.device))
+    for a, b in ((m.vals, full.vals), (m.parents, full.parents), (m.tokens, full.tokens), (m.indices, full.indices),
+                 (m.child, full.child), (tok_out, tok_ref), (node_out, node_ref)):
+        assert torch.equal(a, b)

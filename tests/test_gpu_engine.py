@@ -1,0 +1,160 @@
+"""GPU parity of the sequenced path: one decoder layer against the oracle's
+restatement of the reference layer, and the decode engine (eager vs CUDA-graph
+replay, legality of the produced SIDs)."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import sid_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+FP8 = torch.float8_e4m3fn
+
+
+@pytest.mark.parametrize("rows,prompt", [(48, 70), (130, 257)])
+def test_decoder_layer_vs_oracle(rows, prompt):
+    """Config-2 geometry scaled down in width only where the kernels allow any width
+    (hidden 512, 4 q heads / 2 kv heads x 128, intermediate 1024)."""
+    from flashrec_b200.attention import AttentionBackend, TokenToKVPool
+    from flashrec_b200.decoder import ForwardBatch, Qwen3Config, Qwen3DecoderLayer
+    from flashrec_b200.layers import RotaryEmbedding
+
+    cfg = Qwen3Config(hidden_size=512, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+                      intermediate_size=1024, num_hidden_layers=1, max_position_embeddings=512)
+    g = torch.Generator().manual_seed(rows)
+    H, HQ, HKV, D, I = 512, 4, 2, 128, 1024
+    wf = dict(qkv=0.02 * torch.randn((HQ + 2 * HKV) * D, H, generator=g), o=0.02 * torch.randn(H, HQ * D, generator=g),
+              gate_up=0.02 * torch.randn(2 * I, H, generator=g), down=0.02 * torch.randn(H, I, generator=g))
+    w = {k: O.quantize_weight_fp8(v) for k, v in wf.items()}
+    norms = {k: (1 + 0.1 * torch.randn(n, generator=g)).bfloat16() for k, n in dict(input=H, post=H, q=D, k=D).items()}
+    cs = O.build_cos_sin_cache(D, 512, 1e6)
+    page = 16
+    slots = page + prompt + rows * page + page
+    kc = torch.zeros(slots, HKV, D, dtype=torch.uint8).view(FP8)
+    vc = torch.zeros(slots, HKV, D, dtype=torch.uint8).view(FP8)
+    kc[page:page + prompt] = torch.randn(prompt, HKV, D, generator=g).bfloat16().to(FP8)
+    vc[page:page + prompt] = torch.randn(prompt, HKV, D, generator=g).bfloat16().to(FP8)
+    x = torch.randn(rows, H, generator=g).bfloat16()
+    res = torch.randn(rows, H, generator=g).bfloat16()
+    pos = torch.full((rows,), prompt)
+    loc = page * (1 + (prompt + page - 1) // page + torch.arange(rows))  # every row writes into its own page
+    lists = [torch.cat((torch.arange(page, page + prompt), loc[i:i + 1])) for i in range(rows)]
+    indptr = torch.arange(rows + 1, dtype=torch.int32) * (prompt + 1)
+    indices = torch.cat(lists).to(torch.int32)
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    tr = {}
+    out_ref, res_ref = O.decoder_layer(x, res.clone(), w, norms, pos, loc, cs, kc_ref, vc_ref, indptr, indices, HQ, HKV, D,
+                                       trace=tr)
+
+    pool = TokenToKVPool(1, slots, HKV, D, FP8, DEV, page_size=page)
+    pool.k[0].copy_(kc.to(DEV))
+    pool.v[0].copy_(vc.to(DEV))
+    attn = AttentionBackend(pool, HQ, HKV, D)
+    attn.set_groups(torch.tensor([0, rows], dtype=torch.int32, device=DEV), rows)
+    layer = Qwen3DecoderLayer(cfg, 0, attn, RotaryEmbedding(D, 512, 1e6, device=DEV), device=DEV)
+    sa, mlp = layer.self_attn, layer.mlp
+    sa.qkv_proj.load(wf["qkv"].to(DEV), quantize_fp8=True)
+    sa.o_proj.load(wf["o"].to(DEV), quantize_fp8=True)
+    mlp.gate_up_proj.load(wf["gate_up"].to(DEV), quantize_fp8=True)
+    mlp.down_proj.load(wf["down"].to(DEV), quantize_fp8=True)
+    layer.input_layernorm.weight = norms["input"].to(DEV)
+    layer.post_attention_layernorm.weight = norms["post"].to(DEV)
+    sa.q_norm.weight = norms["q"].to(DEV)
+    sa.k_norm.weight = norms["k"].to(DEV)
+    batch = ForwardBatch(input_ids=torch.zeros(rows, dtype=torch.int64, device=DEV), req_pool_indices=None,
+                         seq_lens=torch.full((rows,), prompt + 1, dtype=torch.int32, device=DEV), positions=pos.to(DEV),
+                         out_cache_loc=loc.to(DEV), kv_indices=indices.to(DEV), kv_indptr=indptr.to(DEV))
+    attn.prepare(batch)
+    assert attn._shared_len.cpu().tolist() == [prompt]
+
+    def rel(a, b):
+        return float((a.float().cpu() - b.float()).abs().max() / b.float().abs().max())
+
+    def same_bytes(a, b):
+        return np.array_equal(a.cpu().contiguous().view(torch.uint8).numpy(), b.contiguous().view(torch.uint8).numpy())
+
+    # ---- stage by stage, every stage fed with the ORACLE's inputs ----------------------
+    from flashrec_b200.kernel.qk_rope_kv import fused_qk_norm_rope_store_fp8
+    from flashrec_b200.kernel.sglops import per_token_quant_fp8
+    from flashrec_b200.kernel.silu_fp8 import silu_and_mul_per_token_quant_fp8
+
+    bf = torch.bfloat16
+    q1, s1, r1 = layer.input_layernorm.quant_fp8(x.to(DEV), res.to(DEV))
+    assert same_bytes(q1, tr["q1"]) and torch.equal(s1.cpu(), tr["s1"]) and same_bytes(r1, tr["res1"])
+    qkv = sa.qkv_proj.forward_fp8(tr["q1"].to(DEV), tr["s1"].to(DEV), (rows, H), bf)
+    assert rel(qkv, tr["qkv"]) < 2e-2
+    heads = tr["qkv"].to(DEV).view(rows, HQ + 2 * HKV, D)
+    fused_qk_norm_rope_store_fp8(heads[:, :HQ], heads[:, HQ:HQ + HKV], heads[:, HQ + HKV:], pos.to(DEV), loc.to(DEV),
+                                 sa.q_norm.weight, sa.k_norm.weight, 1e-6, sa.rotary.cos_sin_cache, pool.k[0], pool.v[0])
+    assert same_bytes(pool.k[0], kc_ref) and same_bytes(pool.v[0], vc_ref)  # KV pool bytes incl. the new slots
+    assert same_bytes(heads[:, :HQ], tr["qn"])
+    o_attn = attn.forward(tr["qn"].to(DEV), None, None, 0, batch, skip_store=True)
+    assert rel(o_attn.reshape(rows, -1), tr["attn"]) < 2e-2
+    aq, asc = per_token_quant_fp8(tr["attn"].to(DEV))
+    assert same_bytes(aq, tr["aq"]) and torch.equal(asc.cpu(), tr["asc"])
+    o = sa.o_proj.forward_fp8(tr["aq"].to(DEV), tr["asc"].to(DEV), (rows, HQ * D), bf)
+    assert rel(o, tr["o"]) < 2e-2
+    q2, s2, r2 = layer.post_attention_layernorm.quant_fp8(tr["o"].to(DEV), tr["res1"].to(DEV))
+    assert same_bytes(q2, tr["q2"]) and torch.equal(s2.cpu(), tr["s2"]) and same_bytes(r2, tr["res2"])
+    gu = mlp.gate_up_proj.forward_fp8(tr["q2"].to(DEV), tr["s2"].to(DEV), (rows, H), bf)
+    assert rel(gu, tr["gu"]) < 2e-2
+    yq, ys = silu_and_mul_per_token_quant_fp8(tr["gu"].to(DEV))
+    assert same_bytes(yq, tr["yq"]) and torch.equal(ys.cpu(), tr["ys"])
+    down = mlp.down_proj.forward_fp8(tr["yq"].to(DEV), tr["ys"].to(DEV), (rows, I), bf)
+    assert rel(down, tr["out"]) < 2e-2
+
+    # ---- the layer as the host code sequences it (errors of six quantised stages compound) ----
+    pool.k[0].copy_(kc.to(DEV))
+    pool.v[0].copy_(vc.to(DEV))
+    out, res_out = layer.forward(x.to(DEV), res.to(DEV), batch)
+    cos = torch.nn.functional.cosine_similarity(out.float().cpu().flatten(), out_ref.float().flatten(), dim=0)
+    assert cos > 0.999 and rel(out, out_ref) < 0.1
+    assert rel(res_out, res_ref) < 2e-2
+    # V bytes come straight from the qkv GEMM output: a 1-ulp bf16 difference rarely survives the e4m3 cast
+    vdiff = pool.v[0].cpu().view(torch.uint8) != vc_ref.view(torch.uint8)
+    assert vdiff.float().mean() < 0.02
+    page_table = (indices.view(rows, -1) // page)
+    assert page_table[:, -1].unique().numel() == rows  # KV-page indices: one private page per row
+
+
+def test_engine_graph_equals_eager_and_sids_are_legal():
+    from flashrec_b200 import device_status
+    from flashrec_b200.decoder import Qwen3Config
+    from flashrec_b200.sid_decode import SidDecodeEngine
+    from flashrec_b200.trie import build_trie_arrays, trie_to_device
+
+    cfg = Qwen3Config(hidden_size=256, num_attention_heads=2, num_key_value_heads=1, head_dim=128,
+                      intermediate_size=512, num_hidden_layers=2, max_position_embeddings=128, vocab_size=1000 + 96)
+    rng = np.random.default_rng(3)
+    sizes, base = [32, 32, 32], 1000
+    items = np.stack([rng.integers(0, 32, 700) for _ in sizes], 1)
+    arrays = build_trie_arrays(items, sizes, base)
+    results = {}
+    for layout in ("csr", "bitmap"):
+        trie = trie_to_device(arrays, layout, DEV)
+        eng = SidDecodeEngine(cfg, 3, 16, [20, 33, 17], sizes, base, trie, DEV, shared_prefix=8, seed=1)
+        eng.run(host_io=False, _eager=True)
+        eager = (eng.cum.clone(), eng.final_tokens.clone(), eng.final_nodes.clone())
+        eng.capture()
+        eng.run(host_io=True)
+        assert torch.equal(eng.cum, eager[0]) and torch.equal(eng.final_tokens, eager[1])
+        assert torch.equal(eng.final_nodes, eager[2])
+        assert torch.equal(eng.h_tokens, eager[1].cpu()) and torch.equal(eng.h_vals, eager[0].cpu())
+        eng.run(host_io=False)  # replay is repeatable
+        assert torch.equal(eng.final_tokens, eager[1])
+        live = torch.isfinite(eng.cum)
+        assert live.any()
+        assert (eng.final_nodes[live] == -1).all()  # a complete SID was reached: leaf
+        codes = (eng.final_tokens - torch.tensor([base, base + 32, base + 64], device=DEV)).cpu().numpy()
+        legal = {tuple(r) for r in items.tolist()}
+        lv = live.cpu().numpy()
+        assert all(tuple(c) in legal for c in codes[lv])  # illegal-SID rate 0
+        for r in range(3):  # beams of a request are distinct items
+            rows = [tuple(c) for c in codes[r][lv[r]]]
+            assert len(rows) == len(set(rows))
+        assert (eng.cum[:, :-1] >= eng.cum[:, 1:]).all()  # sorted scores
+        results[layout] = eager
+    assert torch.equal(results["csr"][1], results["bitmap"][1])  # layouts agree bit for bit
+    assert device_status() == (0, 0)

@@ -1,0 +1,195 @@
+"""GPU parity: quantisers and the FP8 GEMM against the CPU oracle and the
+reference's golden outputs. Bit-exact for e4m3 bytes / scales / bf16 residuals;
+GEMM within 2e-2 relative (bf16 output)."""
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import bf16_from_bits, bits8, bits16, fp8_from_bits, load_golden
+from oracle import sid_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _eq_bytes(a: torch.Tensor, b: torch.Tensor):
+    assert np.array_equal(bits8(a), bits8(b))
+
+
+@pytest.mark.parametrize("rows,hidden", [(8, 2048), (5, 384), (33, 1024), (3, 4096), (1, 8), (17, 6144)])
+def test_rms_quant_bit_exact(rows, hidden):
+    from flashrec_b200.kernel.rms_fp8 import fused_add_rmsnorm_per_token_quant_fp8, rmsnorm_per_token_quant_fp8
+
+    g = torch.Generator().manual_seed(rows * 131 + hidden)
+    x = torch.randn(rows, hidden, generator=g).bfloat16()
+    r = torch.randn(rows, hidden, generator=g).bfloat16()
+    w = (1 + 0.1 * torch.randn(hidden, generator=g)).bfloat16()
+    q_ref, s_ref = O.rmsnorm_quant_fp8(x, w, 1e-6)
+    q, s = rmsnorm_per_token_quant_fp8(x.to(DEV), w.to(DEV), 1e-6)
+    _eq_bytes(q, q_ref)
+    assert torch.equal(s.cpu(), s_ref)
+    q2_ref, s2_ref, r2_ref = O.rmsnorm_quant_fp8(x, w, 1e-6, residual=r.clone())
+    r_dev = r.to(DEV)
+    q2, s2, r2 = fused_add_rmsnorm_per_token_quant_fp8(x.to(DEV), r_dev, w.to(DEV), 1e-6)
+    _eq_bytes(q2, q2_ref)
+    assert torch.equal(s2.cpu(), s2_ref)
+    assert np.array_equal(bits16(r2), bits16(r2_ref))
+    assert r2.data_ptr() == r_dev.data_ptr()  # updated in place
+
+
+def test_rms_quant_golden_reference_bytes():
+    from flashrec_b200.kernel.rms_fp8 import fused_add_rmsnorm_per_token_quant_fp8, rmsnorm_per_token_quant_fp8
+    from flashrec_b200.kernel.sglops import fused_add_rmsnorm, rmsnorm
+
+    g = load_golden("rms_quant")
+    for tag in ("a", "b"):
+        x, r, w = (bf16_from_bits(g[f"{tag}_{n}"]).to(DEV) for n in ("x", "r", "w"))
+        q, s = rmsnorm_per_token_quant_fp8(x, w, 1e-6)
+        assert np.array_equal(bits8(q), g[f"{tag}_q"]) and np.array_equal(s.cpu().numpy(), g[f"{tag}_s"])
+        assert np.array_equal(bits16(rmsnorm(x, w, 1e-6)), g[f"{tag}_y"])
+        q2, s2, r2 = fused_add_rmsnorm_per_token_quant_fp8(x, r.clone(), w, 1e-6)
+        assert np.array_equal(bits8(q2), g[f"{tag}_q_res"]) and np.array_equal(s2.cpu().numpy(), g[f"{tag}_s_res"])
+        assert np.array_equal(bits16(r2), g[f"{tag}_r_out"])
+        y3, r3 = fused_add_rmsnorm(x, r.clone(), w, 1e-6)
+        assert np.array_equal(bits16(r3), g[f"{tag}_r_out"])
+
+
+@pytest.mark.parametrize("rows,hidden", [(6, 2048), (7, 72), (2, 12288)])
+def test_token_quant_bit_exact(rows, hidden):
+    from flashrec_b200.kernel.sglops import per_token_quant_fp8
+
+    g = torch.Generator().manual_seed(hidden)
+    x = (3 * torch.randn(rows, hidden, generator=g)).bfloat16()
+    x[0, :] = 0  # all-zero row: amax clamps to 1e-12
+    q_ref, s_ref = O.per_token_quant_fp8(x)
+    q, s = per_token_quant_fp8(x.to(DEV))
+    _eq_bytes(q, q_ref)
+    assert torch.equal(s.cpu(), s_ref)
+    assert s.shape == (rows, 1)
+    # fp32 input (weight quantisation)
+    wf = 0.02 * torch.randn(rows, hidden, generator=g)
+    qw_ref, sw_ref = O.quantize_weight_fp8(wf)
+    from flashrec_b200.layers import quantize_weight_fp8
+
+    qw, sw = quantize_weight_fp8(wf.to(DEV))
+    _eq_bytes(qw, qw_ref)
+    assert torch.equal(sw.cpu(), sw_ref)
+
+
+def test_empty_inputs():
+    from flashrec_b200.kernel.sglops import per_token_quant_fp8
+    from flashrec_b200.kernel.silu_fp8 import silu_and_mul_per_token_quant_fp8
+
+    q, s = per_token_quant_fp8(torch.empty(0, 256, dtype=torch.bfloat16, device=DEV))
+    assert q.shape == (0, 256) and s.shape == (0, 1)
+    q, s = silu_and_mul_per_token_quant_fp8(torch.empty(0, 512, dtype=torch.bfloat16, device=DEV))
+    assert q.shape == (0, 256)
+
+
+@pytest.mark.parametrize("rows,d", [(4, 6144), (9, 1024), (3, 136), (2, 16384)])
+def test_silu_quant_bit_exact(rows, d):
+    from flashrec_b200.kernel.sglops import silu_and_mul
+    from flashrec_b200.kernel.silu_fp8 import silu_and_mul_per_token_quant_fp8
+
+    g = torch.Generator().manual_seed(d)
+    x = (2 * torch.randn(rows, 2 * d, generator=g)).bfloat16()
+    x[0, :8] = torch.tensor([-100.0, -88.0, 88.0, 1e-30, -1e-30, 0.0, 30.0, -30.0]).bfloat16()
+    q_ref, s_ref = O.silu_mul_quant_fp8(x)
+    q, s = silu_and_mul_per_token_quant_fp8(x.to(DEV))
+    _eq_bytes(q, q_ref)
+    assert torch.equal(s.cpu(), s_ref)
+    assert np.array_equal(bits16(silu_and_mul(x.to(DEV))), bits16(O.silu_and_mul(x)))
+
+
+def test_silu_quant_golden_close_to_reference():
+    from flashrec_b200.kernel.silu_fp8 import silu_and_mul_per_token_quant_fp8
+
+    g = load_golden("quant_silu")
+    q, s = silu_and_mul_per_token_quant_fp8(bf16_from_bits(g["gu"]).to(DEV))
+    assert (bits8(q) != g["q_silu"]).mean() < 1e-3  # torch's float32 exp vs exact silu
+    assert np.allclose(s.cpu().numpy(), g["s_silu"], rtol=1e-2)
+
+
+GEMM_SHAPES = [
+    # M, N, K, block_n
+    (128, 256, 128, 256),
+    (128, 128, 256, 128),
+    (128, 64, 384, 64),
+    (24, 96, 256, 0),
+    (512, 512, 2048, 0),
+    (200, 1000, 1040, 128),
+    (300, 328, 144, 256),
+    (1, 8, 16, 64),
+]
+
+
+@pytest.mark.parametrize("m,n,k,bn", GEMM_SHAPES)
+def test_gemm_fp8_vs_oracle(m, n, k, bn):
+    from flashrec_b200 import device_status
+    from flashrec_b200.kernel.sglops import fp8_scaled_mm
+
+    g = torch.Generator().manual_seed(m * 7 + n * 3 + k)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    w = 0.02 * torch.randn(n, k, generator=g)
+    aq, asc = O.per_token_quant_fp8(a)
+    wq, wsc = O.quantize_weight_fp8(w)
+    ref = O.fp8_scaled_mm(aq, wq, asc, wsc).float()
+    out = fp8_scaled_mm(aq.to(DEV), wq.to(DEV).t(), asc.to(DEV), wsc.to(DEV), torch.bfloat16, block_n=bn)
+    torch.cuda.synchronize()
+    assert device_status() == (0, 0)
+    got = out.float().cpu()
+    denom = ref.abs().max().clamp(min=1e-6)
+    assert ((got - ref).abs().max() / denom) < 2e-2
+    # fp32 output (lm_head logits): one rounding only, much tighter
+    ref32 = O.fp8_logits_f32(aq, wq, asc, wsc)
+    out32 = fp8_scaled_mm(aq.to(DEV), wq.to(DEV).t(), asc.to(DEV), wsc.to(DEV), torch.float32, block_n=bn)
+    assert torch.allclose(out32.cpu(), ref32, rtol=1e-5, atol=1e-6 * float(ref32.abs().max()))
+
+
+def test_gemm_exact_accumulation_small_integers():
+    """Operands that are small integers make every partial sum exact, so the
+    tensor-core result must equal the integer matmul exactly."""
+    from flashrec_b200.kernel.sglops import fp8_scaled_mm
+
+    g = torch.Generator().manual_seed(1)
+    m, n, k = 256, 384, 512
+    a = torch.randint(-3, 4, (m, k), generator=g).float()
+    b = torch.randint(-3, 4, (n, k), generator=g).float()
+    ref = a @ b.t()
+    ones_m = torch.ones(m, 1, device=DEV)
+    ones_n = torch.ones(n, device=DEV)
+    for bn in (64, 128, 256):
+        out = fp8_scaled_mm(a.to(torch.float8_e4m3fn).to(DEV), b.to(torch.float8_e4m3fn).to(DEV).t(), ones_m, ones_n,
+                            torch.float32, block_n=bn)
+        assert torch.equal(out.cpu(), ref), f"block_n={bn}"
+
+
+def test_linear_golden_and_bias():
+    from flashrec_b200.layers import Linear
+
+    g = load_golden("linear_fp8")
+    lin = Linear(256, 96)
+    lin.load(torch.from_numpy(g["w"]).to(DEV), quantize_fp8=True)
+    assert np.array_equal(bits8(lin._fp8_weight.t()), g["wq"])
+    assert np.array_equal(lin._fp8_scale.cpu().numpy(), g["wscale"])
+    y = lin.forward_fp8(fp8_from_bits(g["xq"]).to(DEV), torch.from_numpy(g["xs"]).to(DEV), (24, 256), torch.bfloat16)
+    ref = bf16_from_bits(g["y"]).float()
+    assert ((y.float().cpu() - ref).abs().max() / ref.abs().max()) < 2e-2
+    y2 = lin(bf16_from_bits(g["x"]).to(DEV))  # dynamic activation quantisation path
+    assert torch.equal(y2, y)
+    lin.bias = torch.randn(96, device=DEV).bfloat16()
+    yb = lin(bf16_from_bits(g["x"]).to(DEV))
+    assert torch.allclose(yb.float(), (y + lin.bias).float(), atol=1e-2)
+
+
+def test_bad_arguments_raise():
+    from flashrec_b200 import FlashRecKernelError
+    from flashrec_b200.kernel.sglops import fp8_scaled_mm, per_token_quant_fp8
+
+    with pytest.raises(FlashRecKernelError):
+        per_token_quant_fp8(torch.zeros(4, 64, dtype=torch.bfloat16))  # CPU tensor: no fallback
+    a = torch.zeros(8, 24, device=DEV).to(torch.float8_e4m3fn)  # K % 16 != 0
+    b = torch.zeros(16, 24, device=DEV).to(torch.float8_e4m3fn)
+    with pytest.raises(FlashRecKernelError):
+        fp8_scaled_mm(a, b.t(), torch.ones(8, 1, device=DEV), torch.ones(16, device=DEV), torch.bfloat16)
