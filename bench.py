@@ -55,6 +55,9 @@ def parse():
     ap.add_argument("--items", type=int, default=1_000_000)
     ap.add_argument("--trie", default="csr", choices=["csr", "bitmap"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-wave", action="store_true",
+                    help="run one eager (non-graph) wave between cudaProfilerStart/Stop and exit (for ncu "
+                         "--profile-from-start off)")
     return ap.parse_args()
 
 
@@ -301,6 +304,15 @@ def main():
     launches_per_wave = counter["n"]
     for m in mods:
         m.call = orig_call
+    if args.profile_wave:
+        eng.run(host_io=False, _eager=True)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        eng.run(host_io=False, _eager=True)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print(json.dumps({"profiled_wave_launches": launches_per_wave}))
+        return
     eng.capture()
 
     def barrier():

@@ -81,8 +81,10 @@ _SIGNATURES = {
     "fr_store_kv_fp8": [P, P, _L, _L, _L, _L, P, P, P, _L, _L, _L, _L, _I, _I, _I, _I, P],
     "fr_gather_kv_indices": [P, _L, P, P, P, P, _I, _I, P],
     "fr_embedding_bf16": [P, P, P, _I, _I, _I, P],
-    "fr_decode_attn_plan": [P, P, P, _I, P, P],
-    "fr_decode_attn_fp8": [P, _L, _L, P, P, _L, _L, _L, _L, P, P, P, P, P, _L, _I, _I, _I, _I, _I, _I, _I, _F, P],
+    "fr_decode_attn_plan": [P, P, P, _I, _I, P, P],
+    "fr_decode_attn_scratch_bytes": [_I, _I, _I],
+    "fr_decode_attn_fp8": [P, _L, _L, P, P, _L, _L, _L, _L, P, P, P, P, P, _L, _I, _I, _I, _I, _I, _I, _I, _F, P, _L,
+                           _I, P],
     "fr_logsumexp_rows": [P, _L, P, P, P, _L, _I, _I, P],
     "fr_topk_rows": [P, _L, P, P, P, P, _I, _I, _I, P],
     "fr_lse_combine_shards": [P, P, P, P, _I, _I, P],
@@ -93,7 +95,7 @@ _SIGNATURES = {
     "fr_sid_beam_step": [P] * 7 + [_L] + [P] * 9 + [_L] * 3 + [_I] * 7 + [P],
     "fr_topk_merge_shards": [P] * 14 + [_L] * 2 + [_I] * 7 + [P],
 }
-_RESTYPES = {"fr_version": c_char_p}
+_RESTYPES = {"fr_version": c_char_p, "fr_decode_attn_scratch_bytes": c_int64}
 
 
 def lib_path() -> Path:

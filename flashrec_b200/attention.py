@@ -10,6 +10,7 @@ from typing import List, Optional, Sequence, Union
 
 import torch
 
+from flashrec_b200 import _lib
 from flashrec_b200._lib import call, ptr, require_cuda, stream_ptr
 from flashrec_b200.kernel.sglops import store_kv_cache
 
@@ -130,7 +131,8 @@ class AttentionBackend:
     shared slot prefix on the device); ``forward`` stores nothing when
     ``skip_store`` is set (the fused rope kernel already wrote K/V)."""
 
-    def __init__(self, kv_pool: TokenToKVPool, num_qo_heads: int, num_kv_heads: int, head_dim: int):
+    def __init__(self, kv_pool: TokenToKVPool, num_qo_heads: int, num_kv_heads: int, head_dim: int,
+                 max_shared_len: int = 0):
         self.kv_pool = kv_pool
         self.num_qo_heads = int(num_qo_heads)
         self.num_kv_heads = int(num_kv_heads)
@@ -140,6 +142,9 @@ class AttentionBackend:
         self._shared_len: Optional[torch.Tensor] = None
         self._max_group_rows = 0
         self._n_groups = 0
+        # longest shared prefix the tensor-core path should cover (0 = use the kernel without scratch)
+        self.max_shared_len = int(max_shared_len)
+        self._scratch: Optional[torch.Tensor] = None
 
     def set_groups(self, group_rows: torch.Tensor, max_group_rows: int) -> None:
         """``group_rows`` int32 [n_groups + 1]: rows [g[i], g[i+1]) are the beams of one request."""
@@ -148,6 +153,10 @@ class AttentionBackend:
         self._max_group_rows = int(max_group_rows)
         if self._shared_len is None or self._shared_len.numel() < self._n_groups:
             self._shared_len = torch.zeros(self._n_groups, dtype=torch.int32, device=group_rows.device)
+        if self.max_shared_len > 0:
+            need = int(_lib.load().fr_decode_attn_scratch_bytes(self._n_groups, self.num_kv_heads, self.max_shared_len))
+            if self._scratch is None or self._scratch.numel() < need:
+                self._scratch = torch.empty(need, dtype=torch.uint8, device=group_rows.device)
 
     def prepare(self, batch) -> None:
         if batch.kv_indices is None or batch.kv_indptr is None:
@@ -156,7 +165,7 @@ class AttentionBackend:
             n = int(batch.kv_indptr.numel()) - 1
             self.set_groups(torch.arange(n + 1, dtype=torch.int32, device=batch.kv_indptr.device), 1)
         call("fr_decode_attn_plan", ptr(batch.kv_indptr), ptr(batch.kv_indices), ptr(self._group_rows),
-             self._n_groups, ptr(self._shared_len), stream_ptr(batch.kv_indptr.device))
+             self._n_groups, self._max_group_rows, ptr(self._shared_len), stream_ptr(batch.kv_indptr.device))
 
     def forward(self, q, k, v, layer_id: int, batch, skip_store: bool = False, out=None) -> torch.Tensor:
         """q: [T, Hq, D] bf16 (may be a strided view); returns [T, Hq, D] bf16."""
@@ -174,5 +183,7 @@ class AttentionBackend:
              vc.stride(0), vc.stride(1), ptr(batch.kv_indptr), ptr(batch.kv_indices), ptr(self._group_rows),
              ptr(self._shared_len), ptr(out), out.stride(0), t, self._n_groups, self.num_qo_heads,
              self.num_kv_heads, self.head_dim, self._max_group_rows, self.kv_pool.num_tokens,
-             float(self.head_dim) ** -0.5, stream_ptr(q.device))
+             float(self.head_dim) ** -0.5, ptr(self._scratch),
+             int(self._scratch.numel()) if self._scratch is not None else 0, self.max_shared_len,
+             stream_ptr(q.device))
         return out

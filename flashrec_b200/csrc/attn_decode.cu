@@ -304,23 +304,31 @@ __global__ void __launch_bounds__(kThreads) decode_attn_kernel(Params p) {
   }
 }
 
-// Longest slot prefix shared by all rows of each group.
+// Longest slot prefix shared by all rows of each group. grid = (row chunks, groups):
+// every CTA compares its chunk of rows with the group's first row and lowers
+// out[group] with an atomicMin (out is pre-set to the first row's length).
+constexpr int kPlanRowsPerCta = 32;
+
+__global__ void plan_init_kernel(const int32_t* __restrict__ indptr, const int32_t* __restrict__ group_rows,
+                                 int32_t* __restrict__ out, int n_groups) {
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= n_groups) return;
+  const int row0 = group_rows[g], row1 = group_rows[g + 1];
+  out[g] = row1 > row0 ? indptr[row0 + 1] - indptr[row0] : 0;
+}
+
 __global__ void __launch_bounds__(256) plan_kernel(const int32_t* __restrict__ indptr,
                                                   const int32_t* __restrict__ indices,
                                                   const int32_t* __restrict__ group_rows, int32_t* __restrict__ out) {
-  __shared__ int32_t best;
-  const int grp = blockIdx.x;
+  const int grp = blockIdx.y;
   const int row0 = group_rows[grp], row1 = group_rows[grp + 1];
+  const int first = row0 + 1 + blockIdx.x * kPlanRowsPerCta;
+  if (first >= row1) return;
+  const int last = min(first + kPlanRowsPerCta, row1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (row1 <= row0) {
-    if (threadIdx.x == 0) out[grp] = 0;
-    return;
-  }
   const int32_t* ref = indices + indptr[row0];
   const int ref_len = indptr[row0 + 1] - indptr[row0];
-  if (threadIdx.x == 0) best = ref_len;
-  __syncthreads();
-  for (int r = row0 + 1 + warp; r < row1; r += 8) {
+  for (int r = first + warp; r < last; r += 8) {
     const int32_t* cur = indices + indptr[r];
     const int len = min(ref_len, indptr[r + 1] - indptr[r]);
     int lcp = len;
@@ -328,33 +336,47 @@ __global__ void __launch_bounds__(256) plan_kernel(const int32_t* __restrict__ i
       const bool diff = (i + lane < len) && (cur[i + lane] != ref[i + lane]);
       const uint32_t bal = __ballot_sync(0xffffffffu, diff);
       if (bal) { lcp = i + __ffs(bal) - 1; break; }
-      if (i >= best) break;  // cannot lower the minimum any further
     }
-    if (lane == 0) atomicMin(&best, lcp);
+    if (lane == 0) atomicMin(out + grp, lcp);
   }
-  __syncthreads();
-  if (threadIdx.x == 0) out[grp] = best;
 }
 
 }  // namespace attn
+
+int decode_attn_tc(const void* q, int64_t q_t, int64_t q_h, const void* k_cache, const void* v_cache, int64_t ck_s,
+                   int64_t ck_h, int64_t cv_s, int64_t cv_h, const int32_t* indptr, const int32_t* indices,
+                   const int32_t* group_rows, const int32_t* shared_len, void* out, int64_t o_t, int n_rows,
+                   int n_groups, int hq, int hkv, int max_group_rows, int num_slots, float sm_scale, void* scratch,
+                   int lcap, cudaStream_t stream);  // attn_tc.cu
 }  // namespace fr
 
 using namespace fr;
 
 extern "C" int fr_decode_attn_plan(const int32_t* indptr, const int32_t* indices, const int32_t* group_rows,
-                                   int n_groups, int32_t* shared_len_out, cudaStream_t stream) {
+                                   int n_groups, int max_group_rows, int32_t* shared_len_out, cudaStream_t stream) {
   FR_CHECK_ARG(n_groups >= 0);
   if (n_groups == 0) return FR_OK;
   FR_CHECK_ARG(indptr && indices && group_rows && shared_len_out);
-  attn::plan_kernel<<<n_groups, 256, 0, stream>>>(indptr, indices, group_rows, shared_len_out);
+  attn::plan_init_kernel<<<ceil_div(n_groups, 128), 128, 0, stream>>>(indptr, group_rows, shared_len_out, n_groups);
+  if (launch_status() != FR_OK) return FR_ERR_CUDA;
+  if (max_group_rows <= 1) return FR_OK;
+  dim3 grid(ceil_div(max_group_rows - 1, attn::kPlanRowsPerCta), n_groups);
+  attn::plan_kernel<<<grid, 256, 0, stream>>>(indptr, indices, group_rows, shared_len_out);
   return launch_status();
+}
+
+extern "C" int64_t fr_decode_attn_scratch_bytes(int n_groups, int hkv, int max_shared_len) {
+  if (n_groups <= 0 || hkv <= 0 || max_shared_len <= 0) return 0;
+  const int64_t lcap = (static_cast<int64_t>(max_shared_len) + 63) / 64 * 64;
+  return static_cast<int64_t>(n_groups) * hkv * lcap * attn::kD * 2 /* bf16 */ * 2 /* K and V^T */;
 }
 
 extern "C" int fr_decode_attn_fp8(const void* q, int64_t q_t, int64_t q_h, const void* k_cache, const void* v_cache,
                                   int64_t ck_s, int64_t ck_h, int64_t cv_s, int64_t cv_h, const int32_t* indptr,
                                   const int32_t* indices, const int32_t* group_rows, const int32_t* shared_len,
                                   void* out, int64_t o_t, int n_rows, int n_groups, int hq, int hkv, int head_dim,
-                                  int max_group_rows, int num_slots, float sm_scale, cudaStream_t stream) {
+                                  int max_group_rows, int num_slots, float sm_scale, void* scratch,
+                                  int64_t scratch_bytes, int max_shared_len, cudaStream_t stream) {
   FR_CHECK_ARG(n_rows >= 0 && n_groups >= 0 && hq > 0 && hkv > 0 && max_group_rows >= 0 && num_slots > 0);
   if (n_rows == 0 || n_groups == 0 || max_group_rows == 0) return FR_OK;
   FR_CHECK_ARG(q && k_cache && v_cache && indptr && indices && group_rows && shared_len && out);
@@ -365,6 +387,14 @@ extern "C" int fr_decode_attn_fp8(const void* q, int64_t q_t, int64_t q_h, const
   FR_CHECK_ARG(aligned16(k_cache) && aligned16(v_cache) && ck_s % 16 == 0 && ck_h % 16 == 0 && cv_s % 16 == 0 &&
                cv_h % 16 == 0);
   FR_CHECK_ARG((reinterpret_cast<uintptr_t>(out) & 3u) == 0 && o_t % 2 == 0);
+  if (scratch != nullptr && max_shared_len > 0) {
+    // tensor-core path: the shared prefix of every group is widened once into the scratch buffer
+    const int lcap = (max_shared_len + 63) / 64 * 64;
+    FR_CHECK_ARG(scratch_bytes >= fr_decode_attn_scratch_bytes(n_groups, hkv, max_shared_len));
+    return decode_attn_tc(q, q_t, q_h, k_cache, v_cache, ck_s, ck_h, cv_s, cv_h, indptr, indices, group_rows,
+                          shared_len, out, o_t, n_rows, n_groups, hq, hkv, max_group_rows, num_slots, sm_scale,
+                          scratch, lcap, stream);
+  }
   attn::Params p{static_cast<const __nv_bfloat16*>(q), q_t, q_h, static_cast<const uint8_t*>(k_cache),
                  static_cast<const uint8_t*>(v_cache), ck_s, ck_h, cv_s, cv_h, indptr, indices, group_rows,
                  shared_len, static_cast<__nv_bfloat16*>(out), o_t, n_rows, n_groups, hq, hkv, num_slots,

@@ -93,6 +93,19 @@ __device__ __forceinline__ float quant_div(float y, float scale) {
   return fminf(fmaxf(q, -kFp8Max), kFp8Max);
 }
 
+// Same value as quant_div(y, scale) AFTER the e4m3 cast, at the cost of one
+// multiply: q ~= y * inv (inv = 1 / scale, correctly rounded) is within 2 fp32 ulp
+// of the IEEE quotient, so both round to the same e4m3 byte unless q lies within
+// a few ulp of an e4m3 rounding midpoint (20 low mantissa bits == 0x80000) or in
+// the e4m3 subnormal range; only those (about 1 in 10^4) take the true division.
+__device__ __forceinline__ float quant_div_fast(float y, float scale, float inv) {
+  float q = __fmul_rn(y, inv);
+  const uint32_t low = __float_as_uint(q) & 0xfffffu;
+  const bool hard = (low - (0x80000u - 8u) <= 16u) || !(fabsf(q) >= 0.015625f);
+  if (hard) q = __fdiv_rn(y, scale);
+  return fminf(fmaxf(q, -kFp8Max), kFp8Max);
+}
+
 // scale = max(amax, 1e-12) / 448 in fp32.
 __device__ __forceinline__ float row_scale(float amax) {
   return __fdiv_rn(fmaxf(amax, kAmaxFloor), kFp8Max);

@@ -246,7 +246,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   if (*abort_flag) {
     // an aborted pipeline may still have TMA tiles in flight towards this
     // CTA's shared memory: give them (bounded) time to land before exiting
-    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
     __syncthreads();
   }
   if (warp == 1) {

@@ -98,15 +98,16 @@ row_warp_kernel(const uint4* __restrict__ x, uint4* __restrict__ resid, const ui
     }
     amax = warp_max(amax);
     const float s = row_scale(amax);
+    const float inv = __fdiv_rn(1.0f, s);
     uint2* qr = q + static_cast<size_t>(row) * kVecPerRow;
 #pragma unroll
     for (int j = 0; j < VPL; ++j) {
       const uint32_t* xv = reinterpret_cast<const uint32_t*>(&v[j]);
       uint2 o;
-      o.x = pack_e4m3x4(quant_div(bf16lo(xv[0]), s), quant_div(bf16hi(xv[0]), s), quant_div(bf16lo(xv[1]), s),
-                        quant_div(bf16hi(xv[1]), s));
-      o.y = pack_e4m3x4(quant_div(bf16lo(xv[2]), s), quant_div(bf16hi(xv[2]), s), quant_div(bf16lo(xv[3]), s),
-                        quant_div(bf16hi(xv[3]), s));
+      o.x = pack_e4m3x4(quant_div_fast(bf16lo(xv[0]), s, inv), quant_div_fast(bf16hi(xv[0]), s, inv), quant_div_fast(bf16lo(xv[1]), s, inv),
+                        quant_div_fast(bf16hi(xv[1]), s, inv));
+      o.y = pack_e4m3x4(quant_div_fast(bf16lo(xv[2]), s, inv), quant_div_fast(bf16hi(xv[2]), s, inv), quant_div_fast(bf16lo(xv[3]), s, inv),
+                        quant_div_fast(bf16hi(xv[3]), s, inv));
       qr[j * 32 + lane] = o;
     }
     if (lane == 0) scale[row] = s;
@@ -205,15 +206,16 @@ row_block_kernel(const uint4* __restrict__ x, uint4* __restrict__ resid, const u
   if constexpr (QUANT) {
     amax = block_max(amax, red_f);
     const float s = row_scale(amax);
+    const float inv = __fdiv_rn(1.0f, s);
     uint2* qr = q + static_cast<size_t>(row) * nvec;
     for (int i = threadIdx.x; i < nvec; i += kBlockRowThreads) {
       uint4 v = row_smem[i];
       const uint32_t* xv = reinterpret_cast<const uint32_t*>(&v);
       uint2 o;
-      o.x = pack_e4m3x4(quant_div(bf16lo(xv[0]), s), quant_div(bf16hi(xv[0]), s), quant_div(bf16lo(xv[1]), s),
-                        quant_div(bf16hi(xv[1]), s));
-      o.y = pack_e4m3x4(quant_div(bf16lo(xv[2]), s), quant_div(bf16hi(xv[2]), s), quant_div(bf16lo(xv[3]), s),
-                        quant_div(bf16hi(xv[3]), s));
+      o.x = pack_e4m3x4(quant_div_fast(bf16lo(xv[0]), s, inv), quant_div_fast(bf16hi(xv[0]), s, inv), quant_div_fast(bf16lo(xv[1]), s, inv),
+                        quant_div_fast(bf16hi(xv[1]), s, inv));
+      o.y = pack_e4m3x4(quant_div_fast(bf16lo(xv[2]), s, inv), quant_div_fast(bf16hi(xv[2]), s, inv), quant_div_fast(bf16lo(xv[3]), s, inv),
+                        quant_div_fast(bf16hi(xv[3]), s, inv));
       qr[i] = o;
     }
     if (threadIdx.x == 0) scale[row] = s;
@@ -234,10 +236,11 @@ row_quant_f32_kernel(const float4* __restrict__ x, uint32_t* __restrict__ q, flo
   }
   amax = block_max(amax, red_f);
   const float s = row_scale(amax);
+    const float inv = __fdiv_rn(1.0f, s);
   uint32_t* qr = q + static_cast<size_t>(row) * nvec;
   for (int i = threadIdx.x; i < nvec; i += kBlockRowThreads) {
     float4 v = __ldg(xr + i);
-    qr[i] = pack_e4m3x4(quant_div(v.x, s), quant_div(v.y, s), quant_div(v.z, s), quant_div(v.w, s));
+    qr[i] = pack_e4m3x4(quant_div_fast(v.x, s, inv), quant_div_fast(v.y, s, inv), quant_div_fast(v.z, s, inv), quant_div_fast(v.w, s, inv));
   }
   if (threadIdx.x == 0) scale[row] = s;
 }
@@ -245,16 +248,15 @@ row_quant_f32_kernel(const float4* __restrict__ x, uint32_t* __restrict__ q, flo
 // ---------------------------------------------------------------------------
 // SwiGLU: silu(gate) * up, both rounded to bf16 as the torch bf16 path does.
 // ---------------------------------------------------------------------------
-// silu(g) = g / (1 + exp(-g)) correctly rounded to fp32, then to bf16. The fp32
-// evaluation is within a few ulp of the exact value; only results that land
-// within 16 fp32 ulp of a bf16 rounding midpoint (or extreme / tiny ones) are
-// re-evaluated in fp64, so the bf16 result equals the one obtained from an
-// exact evaluation.
+// silu(g) = g / (1 + exp(-g)) correctly rounded to fp32, then to bf16. The fast
+// path (ex2.approx + approximate divide) is within ~40 fp32 ulp of the exact
+// value for |g| <= 16; only results that land within 128 ulp of a bf16 rounding
+// midpoint (0.4 % of them), large |g| and tiny results are re-evaluated in fp64,
+// so the bf16 value always equals the one obtained from an exact evaluation.
 __device__ __forceinline__ float silu_bf16(float g) {
-  float e = expf(-g);
-  float s = __fdiv_rn(g, __fadd_rn(1.0f, e));
+  float s = __fdividef(g, 1.0f + __expf(-g));
   const uint32_t low = __float_as_uint(s) & 0xffffu;
-  const bool hard = (low >= 0x8000u - 16u && low <= 0x8000u + 16u) || !(fabsf(g) <= 80.f) || !(fabsf(s) >= 1e-30f);
+  const bool hard = (low - (0x8000u - 128u) <= 256u) || !(fabsf(g) <= 16.f) || !(fabsf(s) >= 1e-30f);
   if (hard) {
     const double gd = static_cast<double>(g);
     s = static_cast<float>(gd / (1.0 + exp(-gd)));
@@ -277,38 +279,48 @@ silu_mul_kernel(const uint4* __restrict__ x, uint2* __restrict__ q, float* __res
   const int nvec = d >> 3;
   const uint4* gate = x + static_cast<size_t>(row) * nvec * 2;
   const uint4* up = gate + nvec;
-  uint4 y[NV];
-  float amax = 0.f;
+  // all loads of the row are issued before any arithmetic (2 * NV 16-byte loads in flight per thread)
+  uint4 g[NV], u[NV];
 #pragma unroll
   for (int j = 0; j < NV; ++j) {
     const int i = j * kBlockRowThreads + threadIdx.x;
+    g[j] = make_uint4(0, 0, 0, 0);
+    u[j] = make_uint4(0, 0, 0, 0);
     if (i < nvec) {
-      uint4 g = __ldg(gate + i), u = __ldg(up + i);
-      uint32_t* yv = reinterpret_cast<uint32_t*>(&y[j]);
-      const uint32_t* gv = reinterpret_cast<const uint32_t*>(&g);
-      const uint32_t* uv = reinterpret_cast<const uint32_t*>(&u);
+      g[j] = __ldcs(gate + i);  // streamed once
+      u[j] = __ldcs(up + i);
+    }
+  }
+  float amax = 0.f;
 #pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        yv[t] = silu_mul_pack(gv[t], uv[t]);
-        amax = fmaxf(amax, fmaxf(fabsf(bf16lo(yv[t])), fabsf(bf16hi(yv[t]))));
-      }
-      if constexpr (!QUANT) y_out[static_cast<size_t>(row) * nvec + i] = y[j];
+  for (int j = 0; j < NV; ++j) {
+    uint32_t* yv = reinterpret_cast<uint32_t*>(&g[j]);  // the product overwrites the gate registers
+    const uint32_t* uv = reinterpret_cast<const uint32_t*>(&u[j]);
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      yv[t] = silu_mul_pack(yv[t], uv[t]);
+      amax = fmaxf(amax, fmaxf(fabsf(bf16lo(yv[t])), fabsf(bf16hi(yv[t]))));
+    }
+    if constexpr (!QUANT) {
+      const int i = j * kBlockRowThreads + threadIdx.x;
+      if (i < nvec) y_out[static_cast<size_t>(row) * nvec + i] = g[j];
     }
   }
   if constexpr (QUANT) {
     amax = block_max(amax, red_f);
     const float s = row_scale(amax);
+    const float inv = __fdiv_rn(1.0f, s);
     uint2* qr = q + static_cast<size_t>(row) * nvec;
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
       const int i = j * kBlockRowThreads + threadIdx.x;
       if (i < nvec) {
-        const uint32_t* xv = reinterpret_cast<const uint32_t*>(&y[j]);
+        const uint32_t* xv = reinterpret_cast<const uint32_t*>(&g[j]);
         uint2 o;
-        o.x = pack_e4m3x4(quant_div(bf16lo(xv[0]), s), quant_div(bf16hi(xv[0]), s), quant_div(bf16lo(xv[1]), s),
-                          quant_div(bf16hi(xv[1]), s));
-        o.y = pack_e4m3x4(quant_div(bf16lo(xv[2]), s), quant_div(bf16hi(xv[2]), s), quant_div(bf16lo(xv[3]), s),
-                          quant_div(bf16hi(xv[3]), s));
+        o.x = pack_e4m3x4(quant_div_fast(bf16lo(xv[0]), s, inv), quant_div_fast(bf16hi(xv[0]), s, inv),
+                          quant_div_fast(bf16lo(xv[1]), s, inv), quant_div_fast(bf16hi(xv[1]), s, inv));
+        o.y = pack_e4m3x4(quant_div_fast(bf16lo(xv[2]), s, inv), quant_div_fast(bf16hi(xv[2]), s, inv),
+                          quant_div_fast(bf16lo(xv[3]), s, inv), quant_div_fast(bf16hi(xv[3]), s, inv));
         qr[i] = o;
       }
     }

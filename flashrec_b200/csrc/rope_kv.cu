@@ -47,37 +47,51 @@ __device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&x)[4]) {
 }
 
 // ROPE == false: plain conversion of K and V (no norm / rotation), used by fr_store_kv_fp8.
-template <int D, bool ROPE>
+// Each group of D/8 lanes handles HPG consecutive heads of one token; all of their
+// loads are issued before any arithmetic. HPG > 1 requires n_q and n_kv to be
+// multiples of HPG so that a group never mixes Q, K and V heads.
+template <int D, bool ROPE, int HPG>
 __global__ void __launch_bounds__(256) qk_rope_kv_kernel(RopeArgs a) {
   constexpr int LPH = D / 8;        // lanes per head
-  constexpr int HPW = 32 / LPH;     // heads per warp
+  constexpr int GPW = 32 / LPH;     // lane groups per warp
   constexpr int HALF = D / 2;
   const int lane = threadIdx.x & 31;
   const int sub = lane % LPH;
   const int heads_all = a.n_q + 2 * a.n_kv;
-  const int64_t item = (static_cast<int64_t>(blockIdx.x) * (256 / 32) + (threadIdx.x >> 5)) * HPW + lane / LPH;
-  const bool live = item < static_cast<int64_t>(a.T) * heads_all;
+  const int groups_per_tok = heads_all / HPG;
+  const int64_t item = (static_cast<int64_t>(blockIdx.x) * (256 / 32) + (threadIdx.x >> 5)) * GPW + lane / LPH;
+  const bool live = item < static_cast<int64_t>(a.T) * groups_per_tok;
   // dead groups still take part in the shuffles below
-  const int t = live ? static_cast<int>(item / heads_all) : 0;
-  const int hs = live ? static_cast<int>(item % heads_all) : 0;
-  const bool is_q = hs < a.n_q;
-  const bool is_k = !is_q && hs < a.n_q + a.n_kv;
-  const int h = is_q ? hs : (is_k ? hs - a.n_q : hs - a.n_q - a.n_kv);
+  const int t = live ? static_cast<int>(item / groups_per_tok) : 0;
+  const int hs0 = live ? static_cast<int>(item % groups_per_tok) * HPG : 0;
+  const bool is_q = hs0 < a.n_q;
+  const bool is_k = !is_q && hs0 < a.n_q + a.n_kv;
+  const int h0 = is_q ? hs0 : (is_k ? hs0 - a.n_q : hs0 - a.n_q - a.n_kv);
 
-  const __nv_bfloat16* src = is_q ? (a.q + t * a.q_t + h * a.q_h)
-                                  : (is_k ? (a.k + t * a.k_t + h * a.k_h) : (a.v + t * a.v_t + h * a.v_h));
-  float lo[4] = {0.f, 0.f, 0.f, 0.f}, hi[4] = {0.f, 0.f, 0.f, 0.f};
-  if (live) {
-    load4(src + 4 * sub, lo);
-    load4(src + HALF + 4 * sub, hi);
-  }
-  double ss = 0.0;
+  const __nv_bfloat16* src0 = is_q ? (a.q + t * a.q_t + h0 * a.q_h)
+                                   : (is_k ? (a.k + t * a.k_t + h0 * a.k_h) : (a.v + t * a.v_t + h0 * a.v_h));
+  const int64_t hstride = is_q ? a.q_h : (is_k ? a.k_h : a.v_h);
+  float lo[HPG][4], hi[HPG][4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    ss += static_cast<double>(lo[i] * lo[i]);
-    ss += static_cast<double>(hi[i] * hi[i]);
+  for (int j = 0; j < HPG; ++j) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) lo[j][i] = hi[j][i] = 0.f;
+    if (live) {
+      load4(src0 + j * hstride + 4 * sub, lo[j]);
+      load4(src0 + j * hstride + HALF + 4 * sub, hi[j]);
+    }
   }
-  ss = group_sum<LPH>(ss);  // all 32 lanes execute the shuffles
+  double ss[HPG];
+#pragma unroll
+  for (int j = 0; j < HPG; ++j) {
+    double acc = 0.0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc += static_cast<double>(lo[j][i] * lo[j][i]);
+      acc += static_cast<double>(hi[j][i] * hi[j][i]);
+    }
+    ss[j] = group_sum<LPH>(acc);  // all 32 lanes execute the shuffles
+  }
   if (!live) return;
 
   int64_t slot = 0;
@@ -86,61 +100,70 @@ __global__ void __launch_bounds__(256) qk_rope_kv_kernel(RopeArgs a) {
     if (slot < 0 || slot >= a.num_slots) return;  // never write outside the pool
   }
 
-  if (ROPE && (is_q || is_k)) {
+  float cosv[4] = {1.f, 1.f, 1.f, 1.f}, sinv[4] = {0.f, 0.f, 0.f, 0.f}, wlo[4], whi[4];
+  const bool rotate = ROPE && (is_q || is_k);
+  if (rotate) {
     int64_t p = a.pos[t];
     p = p < 0 ? 0 : (p >= a.max_pos ? a.max_pos - 1 : p);
     const float4 c4 = *reinterpret_cast<const float4*>(a.cs + p * D + 4 * sub);
     const float4 s4 = *reinterpret_cast<const float4*>(a.cs + p * D + HALF + 4 * sub);
-    const float cosv[4] = {c4.x, c4.y, c4.z, c4.w};
-    const float sinv[4] = {s4.x, s4.y, s4.z, s4.w};
+    cosv[0] = c4.x; cosv[1] = c4.y; cosv[2] = c4.z; cosv[3] = c4.w;
+    sinv[0] = s4.x; sinv[1] = s4.y; sinv[2] = s4.z; sinv[3] = s4.w;
     const __nv_bfloat16* wsrc = is_q ? a.qw : a.kw;
-    float wlo[4], whi[4];
     load4(wsrc + 4 * sub, wlo);
     load4(wsrc + HALF + 4 * sub, whi);
-    const float var = static_cast<float>(ss / static_cast<double>(D));
-    const float rstd = rsqrt_rn(__fadd_rn(var, a.eps));
-    float y1[4], y2[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float x1 = __fmul_rn(__fmul_rn(lo[i], rstd), wlo[i]);
-      const float x2 = __fmul_rn(__fmul_rn(hi[i], rstd), whi[i]);
-      y1[i] = __fsub_rn(__fmul_rn(x1, cosv[i]), __fmul_rn(x2, sinv[i]));
-      y2[i] = __fadd_rn(__fmul_rn(x2, cosv[i]), __fmul_rn(x1, sinv[i]));
-    }
-    if (is_q) {
-      __nv_bfloat16* dst = a.q + t * a.q_t + h * a.q_h;
-      uint2 o1, o2;
-      o1.x = pack_bf16(y1[0], y1[1]); o1.y = pack_bf16(y1[2], y1[3]);
-      o2.x = pack_bf16(y2[0], y2[1]); o2.y = pack_bf16(y2[2], y2[3]);
-      *reinterpret_cast<uint2*>(dst + 4 * sub) = o1;
-      *reinterpret_cast<uint2*>(dst + HALF + 4 * sub) = o2;
-      return;
-    }
-    // K: round to bf16 first, as the reference does before the e4m3 cast
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      lo[i] = round_bf16(y1[i]);
-      hi[i] = round_bf16(y2[i]);
-    }
   } else if (is_q) {
     return;  // ROPE == false never has Q work
   }
-  uint8_t* dst = is_k ? (a.kc + slot * a.ck_s + h * a.ck_h) : (a.vc + slot * a.cv_s + h * a.cv_h);
-  *reinterpret_cast<uint32_t*>(dst + 4 * sub) = pack_e4m3x4(lo[0], lo[1], lo[2], lo[3]);
-  *reinterpret_cast<uint32_t*>(dst + HALF + 4 * sub) = pack_e4m3x4(hi[0], hi[1], hi[2], hi[3]);
+#pragma unroll
+  for (int j = 0; j < HPG; ++j) {
+    if (rotate) {
+      const float var = static_cast<float>(ss[j] / static_cast<double>(D));
+      const float rstd = rsqrt_rn(__fadd_rn(var, a.eps));
+      float y1[4], y2[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float x1 = __fmul_rn(__fmul_rn(lo[j][i], rstd), wlo[i]);
+        const float x2 = __fmul_rn(__fmul_rn(hi[j][i], rstd), whi[i]);
+        y1[i] = __fsub_rn(__fmul_rn(x1, cosv[i]), __fmul_rn(x2, sinv[i]));
+        y2[i] = __fadd_rn(__fmul_rn(x2, cosv[i]), __fmul_rn(x1, sinv[i]));
+      }
+      if (is_q) {
+        __nv_bfloat16* dst = a.q + t * a.q_t + (h0 + j) * a.q_h;
+        uint2 o1, o2;
+        o1.x = pack_bf16(y1[0], y1[1]); o1.y = pack_bf16(y1[2], y1[3]);
+        o2.x = pack_bf16(y2[0], y2[1]); o2.y = pack_bf16(y2[2], y2[3]);
+        *reinterpret_cast<uint2*>(dst + 4 * sub) = o1;
+        *reinterpret_cast<uint2*>(dst + HALF + 4 * sub) = o2;
+        continue;
+      }
+      // K: round to bf16 first, as the reference does before the e4m3 cast
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        lo[j][i] = round_bf16(y1[i]);
+        hi[j][i] = round_bf16(y2[i]);
+      }
+    }
+    uint8_t* dst = is_k ? (a.kc + slot * a.ck_s + (h0 + j) * a.ck_h) : (a.vc + slot * a.cv_s + (h0 + j) * a.cv_h);
+    *reinterpret_cast<uint32_t*>(dst + 4 * sub) = pack_e4m3x4(lo[j][0], lo[j][1], lo[j][2], lo[j][3]);
+    *reinterpret_cast<uint32_t*>(dst + HALF + 4 * sub) = pack_e4m3x4(hi[j][0], hi[j][1], hi[j][2], hi[j][3]);
+  }
 }
 
 template <bool ROPE>
 static int launch_rope(const RopeArgs& a, int D, cudaStream_t stream) {
   const int heads_all = a.n_q + 2 * a.n_kv;
-  const int64_t items = static_cast<int64_t>(a.T) * heads_all;
-  if (items == 0) return FR_OK;
+  if (static_cast<int64_t>(a.T) * heads_all == 0) return FR_OK;
+  const bool four = (a.n_q % 4 == 0) && (a.n_kv % 4 == 0);
+  const int64_t items = static_cast<int64_t>(a.T) * (four ? heads_all / 4 : heads_all);
   if (D == 128) {
     const int per_cta = 8 * 2;
-    qk_rope_kv_kernel<128, ROPE><<<ceil_div(items, per_cta), 256, 0, stream>>>(a);
+    if (four) qk_rope_kv_kernel<128, ROPE, 4><<<ceil_div(items, per_cta), 256, 0, stream>>>(a);
+    else qk_rope_kv_kernel<128, ROPE, 1><<<ceil_div(items, per_cta), 256, 0, stream>>>(a);
   } else if (D == 64) {
     const int per_cta = 8 * 4;
-    qk_rope_kv_kernel<64, ROPE><<<ceil_div(items, per_cta), 256, 0, stream>>>(a);
+    if (four) qk_rope_kv_kernel<64, ROPE, 4><<<ceil_div(items, per_cta), 256, 0, stream>>>(a);
+    else qk_rope_kv_kernel<64, ROPE, 1><<<ceil_div(items, per_cta), 256, 0, stream>>>(a);
   } else {
     return FR_ERR_UNSUPPORTED;
   }

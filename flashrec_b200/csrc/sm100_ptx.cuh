@@ -3,7 +3,7 @@
 // allocation, tcgen05.mma / commit / ld, and the shared-memory matrix
 // descriptor for K-major 128-byte-swizzled operand tiles.
 //
-// Every wait in here is bounded: after kSpinLimit unsuccessful polls the wait
+// Every wait in here is bounded (one second of wall-clock time): after that the wait
 // records an error in the global status word, raises the CTA-wide abort flag
 // and returns false; callers leave their loops, fall through to the common
 // exit and free TMEM, so a mistake shows up as FR_ERR_TIMEOUT, not a hang.
@@ -47,15 +47,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait. `abort_flag` lives in shared memory and is shared by the CTA;
-// `status` is the global sticky status word {code, site}.
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait: gives up after kWaitLimitNs of wall-clock time (an
+// mbarrier.try_wait may itself suspend the thread for an unspecified while, so
+// the bound is on time, not on the number of polls). `abort_flag` lives in shared
+// memory and is shared by the CTA; `status` is the global sticky word {code, site}.
+constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s
+
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
                                           int site) {
+  for (uint32_t i = 0; i < 64u; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (i > 1024u) {
-      __nanosleep(64);
-      if ((i & 255u) == 0u && *abort_flag) return false;
+    __nanosleep(32);
+    if ((i & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) break;
     }
   }
   *abort_flag = 1;
@@ -72,6 +86,18 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
       "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(bar)
       : "memory");
 }
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap* tmap, int c0, int c1, int c2,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+          dst_smem),
+      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
+}
+
+// Make generic-proxy shared-memory writes visible to the async proxy (TMA / tcgen05.mma reads).
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
@@ -133,6 +159,20 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Store counterpart of tmem_ld_32x32: thread t writes 32 consecutive fp32 columns of lane (taddr.lane + t).
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor for a K-major operand tile stored as rows of
 // 128 bytes with the 128-byte swizzle (what a TMA load with

@@ -155,7 +155,8 @@ class SidDecodeEngine:
         self.row_base = (torch.arange(self.n, dtype=torch.int64, device=dev) * self.bw)[:, None]
 
         # ---- model + head ----------------------------------------------------------------
-        self.attn = AttentionBackend(self.pool, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim)
+        self.attn = AttentionBackend(self.pool, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
+                                     max_shared_len=max(self.prompt_lens) + self.steps)
         self.attn.set_groups(torch.arange(self.n + 1, dtype=torch.int32, device=dev) * self.bw, self.bw)
         self.model = Qwen3ForCausalLM(cfg, self.attn, dev)
         self.model.init_random(seed=seed + 1)

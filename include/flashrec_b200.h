@@ -124,23 +124,35 @@ int fr_embedding_bf16(const void* table, const int64_t* ids, void* out, int T, i
 /* ---- decode attention over the e4m3 KV pool ------------------------------ */
 
 /* shared_len_out[g] = longest slot-list prefix common to all rows of group g,
- * rows [group_rows[g], group_rows[g+1]). indptr int32 [n_rows+1], indices int32.
+ * rows [group_rows[g], group_rows[g+1]) (at most max_group_rows of them).
+ * indptr int32 [n_rows+1], indices int32.
  * Reference: takes the place of AttentionBackend.prepare / _plan_decode
  * (attention/flashinfer.py:201-209, 262-349); runs on the device, capturable. */
 int fr_decode_attn_plan(const int32_t* indptr, const int32_t* indices, const int32_t* group_rows, int n_groups,
-                        int32_t* shared_len_out, cudaStream_t stream);
+                        int max_group_rows, int32_t* shared_len_out, cudaStream_t stream);
+
+/* Bytes of scratch fr_decode_attn_fp8 needs for its tensor-core path: bf16
+ * copies of K and of V transposed for the shared prefix (at most max_shared_len
+ * tokens) of every group and kv head. */
+int64_t fr_decode_attn_scratch_bytes(int n_groups, int hkv, int max_shared_len);
 
 /* out[r,h,:] = softmax(q[r,h,:] . K^T * sm_scale) . V over the row's slot list.
  * q: bf16 [n_rows, hq, 128] (element strides token/head); caches e4m3 with byte
  * strides (slot, kv head), 16-byte aligned rows; out: bf16 [n_rows, hq, 128]
  * with token stride o_t. hq / hkv in {1,2,4,8}. Slots are clamped to the pool.
+ * scratch (optional, caller-owned, 16-byte aligned, at least
+ * fr_decode_attn_scratch_bytes(...) bytes; contents need not be preserved
+ * between calls): when given, the groups' shared prefixes (capped at
+ * max_shared_len tokens) run on tcgen05 tensor cores; when NULL, a kernel
+ * without scratch (mma.sync) is used. Results agree within the bf16 tolerance.
  * Reference: AttentionBackend.forward decode branch (attention/flashinfer.py:
  * 212-238) / _sdpa (:380-431). */
 int fr_decode_attn_fp8(const void* q, int64_t q_t, int64_t q_h, const void* k_cache, const void* v_cache,
                        int64_t ck_s, int64_t ck_h, int64_t cv_s, int64_t cv_h, const int32_t* indptr,
                        const int32_t* indices, const int32_t* group_rows, const int32_t* shared_len, void* out,
                        int64_t o_t, int n_rows, int n_groups, int hq, int hkv, int head_dim, int max_group_rows,
-                       int num_slots, float sm_scale, cudaStream_t stream);
+                       int num_slots, float sm_scale, void* scratch, int64_t scratch_bytes, int max_shared_len,
+                       cudaStream_t stream);
 
 /* ---- trie-constrained SID head ------------------------------------------- */
 

@@ -12,7 +12,7 @@ def _declared():
     text = (ROOT / "include" / "flashrec_b200.h").read_text()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     decls = {}
-    for m in re.finditer(r"\b(?:int|const char\*)\s+(fr_\w+)\s*\(([^;]*?)\)\s*;", text, flags=re.S):
+    for m in re.finditer(r"\b(?:int|int64_t|const char\*)\s+(fr_\w+)\s*\(([^;]*?)\)\s*;", text, flags=re.S):
         args = m.group(2).strip()
         n = 0 if args in ("", "void") else args.count(",") + 1
         decls[m.group(1)] = n

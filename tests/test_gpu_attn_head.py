@@ -103,7 +103,7 @@ def _attn_case(n_groups, bw, prefix_lens, tails, hq, hkv, seed, slots=4096):
     return q, kc, vc, torch.from_numpy(indptr), torch.from_numpy(indices), torch.tensor(group_rows, dtype=torch.int32)
 
 
-def _run_attn(q, kc, vc, indptr, indices, group_rows, hq, hkv, expect_shared=None):
+def _run_attn(q, kc, vc, indptr, indices, group_rows, hq, hkv, expect_shared=None, tc=False):
     from flashrec_b200.attention import AttentionBackend, TokenToKVPool
     from flashrec_b200.decoder import ForwardBatch
 
@@ -111,7 +111,8 @@ def _run_attn(q, kc, vc, indptr, indices, group_rows, hq, hkv, expect_shared=Non
     pool = TokenToKVPool(1, slots, hkv, 128, FP8, DEV)
     pool.k[0].copy_(kc.to(DEV))
     pool.v[0].copy_(vc.to(DEV))
-    be = AttentionBackend(pool, hq, hkv, 128)
+    # tc=True: tcgen05 path with caller scratch; tc=False: the kernel without scratch
+    be = AttentionBackend(pool, hq, hkv, 128, max_shared_len=int((indptr[1:] - indptr[:-1]).max()) if tc else 0)
     gr = group_rows.to(DEV)
     be.set_groups(gr, int((group_rows[1:] - group_rows[:-1]).max()))
     t = q.shape[0]
@@ -125,40 +126,54 @@ def _run_attn(q, kc, vc, indptr, indices, group_rows, hq, hkv, expect_shared=Non
     return be.forward(q.to(DEV), None, None, 0, batch, skip_store=True)
 
 
+@pytest.mark.parametrize("tc", [False, True])
 @pytest.mark.parametrize("hq,hkv", [(16, 8), (8, 8), (8, 2), (8, 1)])
-def test_decode_attention_shared_prefix(hq, hkv):
+def test_decode_attention_shared_prefix(hq, hkv, tc):
     bw, pre, tails = [40, 3, 1], [257, 64, 5], [1, 3, 0]
     q, kc, vc, indptr, indices, gr = _attn_case(3, bw, pre, tails, hq, hkv, seed=hq * 10 + hkv)
-    out = _run_attn(q, kc, vc, indptr, indices, gr, hq, hkv, expect_shared=[257, 64, 5])
+    out = _run_attn(q, kc, vc, indptr, indices, gr, hq, hkv, expect_shared=[257, 64, 5], tc=tc)
     ref = O.decode_attention(q, kc, vc, indptr, indices, hq // hkv).float()
     err = (out.float().cpu() - ref).abs().max() / ref.abs().max()
     assert err < 2e-2, err
 
 
-def test_decode_attention_no_sharing_and_empty_rows():
+@pytest.mark.parametrize("tc", [False, True])
+def test_decode_attention_wide_groups_long_prefix(tc):
+    """Beam width 200 (two 64-beam CTA tiles + a ragged one), prefix 700 (11 KV tiles), longer tails."""
+    q, kc, vc, indptr, indices, gr = _attn_case(2, [200, 70], [700, 129], [3, 6], 16, 8, seed=77, slots=8192)
+    out = _run_attn(q, kc, vc, indptr, indices, gr, 16, 8, expect_shared=[700, 129], tc=tc)
+    ref = O.decode_attention(q, kc, vc, indptr, indices, 2).float()
+    err = (out.float().cpu() - ref).abs().max() / ref.abs().max()
+    assert err < 2e-2, err
+
+
+@pytest.mark.parametrize("tc", [False, True])
+def test_decode_attention_no_sharing_and_empty_rows(tc):
     # per-row groups (the reference's flat interface): every list is its own prefix
     q, kc, vc, indptr, indices, _ = _attn_case(1, [6], [0], [9], 16, 8, seed=5)
     gr = torch.arange(7, dtype=torch.int32)
-    out = _run_attn(q, kc, vc, indptr, indices, gr, 16, 8)
+    out = _run_attn(q, kc, vc, indptr, indices, gr, 16, 8, tc=tc)
     ref = O.decode_attention(q, kc, vc, indptr, indices, 2).float()
     assert (out.float().cpu() - ref).abs().max() / ref.abs().max() < 2e-2
     # one group, nothing shared: all tokens go through the per-row tail path
-    out2 = _run_attn(q, kc, vc, indptr, indices, torch.tensor([0, 6], dtype=torch.int32), 16, 8, expect_shared=[0])
+    out2 = _run_attn(q, kc, vc, indptr, indices, torch.tensor([0, 6], dtype=torch.int32), 16, 8, expect_shared=[0],
+                     tc=tc)
     assert (out2.float().cpu() - ref).abs().max() / ref.abs().max() < 2e-2
     # a row with an empty slot list yields zeros
     indptr2 = indptr.clone()
     indptr2[1:] = indptr[1:] - 9
     indptr2[1] = 0
-    out3 = _run_attn(q, kc, vc, indptr2, indices[9:], gr, 16, 8)
+    out3 = _run_attn(q, kc, vc, indptr2, indices[9:], gr, 16, 8, tc=tc)
     assert out3[0].abs().max() == 0
 
 
-def test_decode_attention_golden_reference():
+@pytest.mark.parametrize("tc", [False, True])
+def test_decode_attention_golden_reference(tc):
     g = load_golden("attention")
     q = bf16_from_bits(g["q"])
     kc, vc = fp8_from_bits(g["k_cache"]), fp8_from_bits(g["v_cache"])
     gr = torch.arange(5, dtype=torch.int32)
-    out = _run_attn(q, kc, vc, torch.from_numpy(g["indptr"]), torch.from_numpy(g["kv_indices"]), gr, 4, 2)
+    out = _run_attn(q, kc, vc, torch.from_numpy(g["indptr"]), torch.from_numpy(g["kv_indices"]), gr, 4, 2, tc=tc)
     ref = bf16_from_bits(g["out"]).float()
     assert torch.allclose(out.float().cpu(), ref, rtol=2e-2, atol=2e-2)
 
