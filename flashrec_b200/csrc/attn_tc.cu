@@ -11,7 +11,7 @@
 // widened e4m3 -> bf16 into a scratch buffer [group, kv head, token, 128] and V is
 // widened and TRANSPOSED into [group, kv head, 128, token], once per group instead
 // of once per CTA. Both layouts are K-major for their MMA, so plain TMA tile
-// loads (128-byte swizzle, no multicast) feed tcgen05.mma directly.
+// loads (128-byte swizzle, one CTA per tile) feed tcgen05.mma directly.
 // Step 2 (decode_attn_tc_kernel): one CTA per (64/G-beam tile... 128 query vectors,
 // kv head, group). warp 0 = TMA producer, warp 1 = TMEM allocation + MMA issue,
 // warps 2-5 = softmax / correction / tail / epilogue, one query vector per

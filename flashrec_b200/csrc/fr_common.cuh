@@ -103,7 +103,7 @@ __device__ __forceinline__ float quant_div_fast(float y, float scale, float inv)
   const uint32_t low = __float_as_uint(q) & 0xfffffu;
   const bool hard = (low - (0x80000u - 8u) <= 16u) || !(fabsf(q) >= 0.015625f);
   if (hard) q = __fdiv_rn(y, scale);
-  return fminf(fmaxf(q, -kFp8Max), kFp8Max);
+  return q;  // |q| <= 448 (1 + 2^-22); the saturating e4m3 conversion does the clamp
 }
 
 // scale = max(amax, 1e-12) / 448 in fp32.
@@ -114,6 +114,42 @@ __device__ __forceinline__ float row_scale(float amax) {
 // 1 / sqrt(x) as two correctly rounded fp32 operations (what a vectorised CPU
 // rsqrt computes); the hardware rsqrt approximation is deliberately avoided.
 __device__ __forceinline__ float rsqrt_rn(float x) { return __fdiv_rn(1.0f, __fsqrt_rn(x)); }
+
+// silu(g) = g / (1 + exp(-g)) correctly rounded to fp32, then to bf16. Fast path:
+// exp(-g) = 2^(th + tl) with th + tl = -g * log2(e) carried in two floats (the
+// product's rounding error is recovered with an FMA), ex2.approx on th and a
+// first-order correction for tl, then an approximate divide: within ~6 fp32 ulp
+// of the exact value for |g| <= 80. Only results that land within 24 ulp of a
+// bf16 rounding midpoint (0.07 %), huge |g| and tiny results are re-evaluated in
+// fp64, so the bf16 value always equals the one obtained from an exact evaluation.
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ float silu_bf16(float g) {
+  constexpr float kL2eHi = 1.44269502162933349609375f;  // fp32(log2 e)
+  constexpr float kL2eLo = 1.925963033500e-8f;          // log2 e - fp32(log2 e)
+  const float th = __fmul_rn(g, -kL2eHi);
+  const float tl = __fmaf_rn(g, -kL2eLo, __fmaf_rn(g, -kL2eHi, -th));
+  float e = ex2_approx(th);
+  e = __fmaf_rn(e, tl * 0.693147182f, e);
+  float s = __fdividef(g, 1.0f + e);
+  const uint32_t low = __float_as_uint(s) & 0xffffu;
+  const bool hard = (low - (0x8000u - 24u) <= 48u) || !(fabsf(g) <= 80.f) || !(fabsf(s) >= 1e-30f);
+  if (hard) {
+    const double gd = static_cast<double>(g);
+    s = static_cast<float>(gd / (1.0 + exp(-gd)));
+  }
+  return round_bf16(s);
+}
+
+__device__ __forceinline__ uint32_t silu_mul_pack(uint32_t g, uint32_t u) {
+  float a = __fmul_rn(silu_bf16(bf16lo(g)), bf16lo(u));
+  float b = __fmul_rn(silu_bf16(bf16hi(g)), bf16hi(u));
+  return pack_bf16(a, b);
+}
 
 // e4m3 byte -> fp32 (exact).
 __device__ __forceinline__ float e4m3_to_float(uint8_t b) {

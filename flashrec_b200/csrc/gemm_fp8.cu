@@ -21,6 +21,8 @@
 //               once to bf16 (or keep fp32 for the lm_head logits), store
 // Two accumulator buffers in TMEM let the epilogue of tile i overlap the
 // main loop of tile i+1.
+#include <stdlib.h>
+
 #include "fr_common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -33,8 +35,15 @@ namespace gemm {
 constexpr int kBlockM = 128;
 constexpr int kBlockK = 128;  // bytes == e4m3 elements: one 128-byte swizzle span
 constexpr int kUmmaK = 32;
-constexpr int kThreads = 192;
-constexpr int kEpiThreads = 128;
+// 2 control warps (TMA, MMA) + epilogue warps. The plain epilogue uses one warp per TMEM lane
+// quadrant; the SwiGLU epilogue does ~40 instructions per element and gets four warps per quadrant
+// (each takes one 32-column chunk) so that it still hides under the main loop.
+template <int EPI>
+struct EpiCfg {
+  static constexpr int kWarps = EPI == 1 ? 16 : 4;
+  static constexpr int kEpiThreads = kWarps * 32;
+  static constexpr int kThreads = 64 + kEpiThreads;
+};
 
 template <int BLOCK_N>
 struct Cfg {
@@ -84,13 +93,21 @@ __device__ __forceinline__ void store_chunk32<float>(float* dst, const float (&v
   }
 }
 
-template <int BLOCK_N, typename OutT>
-__global__ void __launch_bounds__(kThreads, 1)
+// EPI == 0: plain scaled output. EPI == 1 (BLOCK_N == 256, bf16 out): the weight rows
+// are interleaved per tile as [128 gate channels | the 128 matching up channels];
+// the epilogue rounds both to bf16 (exactly what the unfused GEMM would have
+// stored), applies silu(gate) * up with the bf16 roundings of the unfused SwiGLU
+// kernel, stores y [M, N/2] and folds max|y| of every row into row_amax (float
+// bits, atomicMax on non-negative values).
+template <int BLOCK_N, typename OutT, int EPI>
+__global__ void __launch_bounds__(EpiCfg<EPI>::kThreads, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 OutT* __restrict__ out, int64_t ldo, const float* __restrict__ scale_a,
                 const float* __restrict__ scale_b, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
-                int* status) {
+                unsigned int* __restrict__ row_amax, int* status) {
   using C = Cfg<BLOCK_N>;
+  constexpr int kEpiThreads = EpiCfg<EPI>::kEpiThreads;
+  constexpr int kSplit = EpiCfg<EPI>::kWarps / 4;  // epilogue warps per lane quadrant
   extern __shared__ uint8_t smem_raw[];
   // 128-byte-swizzled operand tiles need a 1024-byte aligned base.
   const uint32_t raw = ptx::smem_u32(smem_raw);
@@ -195,6 +212,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     // ------------------------------ epilogue -------------------------------
     const int quad = warp & 3;  // TMEM lane quadrant this warp may access
     const int epi_tid = threadIdx.x - 64;
+    const int part = (warp - 2) >> 2;  // which share of the column chunks this warp takes
     bool ok = true;
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
@@ -218,21 +236,44 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       if (!okw) { ok = false; break; }
       ptx::tc_fence_after();
       const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BLOCK_N;
-      OutT* out_row = out + static_cast<int64_t>(row) * ldo + n0;
+      if constexpr (EPI == 0) {
+        OutT* out_row = out + static_cast<int64_t>(row) * ldo + n0;
 #pragma unroll 1
-      for (int c = 0; c < BLOCK_N / 32; ++c) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32(taddr_row + c * 32, r);
-        ptx::tmem_ld_wait();
-        float v[32];
+        for (int c = part; c < BLOCK_N / 32; c += kSplit) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(taddr_row + c * 32, r);
+          ptx::tmem_ld_wait();
+          float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float t = __fmul_rn(__fmul_rn(__uint_as_float(r[j]), sa), sbs[c * 32 + j]);
-          if (bias != nullptr) t = __fadd_rn(round_bf16(t), bss[c * 32 + j]);
-          v[j] = t;
+          for (int j = 0; j < 32; ++j) {
+            float t = __fmul_rn(__fmul_rn(__uint_as_float(r[j]), sa), sbs[c * 32 + j]);
+            if (bias != nullptr) t = __fadd_rn(round_bf16(t), bss[c * 32 + j]);
+            v[j] = t;
+          }
+          const int nvalid = N - (n0 + c * 32);
+          if (row < M && nvalid > 0) store_chunk32<OutT>(out_row + c * 32, v, nvalid);
         }
-        const int nvalid = N - (n0 + c * 32);
-        if (row < M && nvalid > 0) store_chunk32<OutT>(out_row + c * 32, v, nvalid);
+      } else {
+        __nv_bfloat16* out_row = reinterpret_cast<__nv_bfloat16*>(out) + static_cast<int64_t>(row) * ldo + n0 / 2;
+        float amax = 0.f;
+#pragma unroll 1
+        for (int c = part; c < BLOCK_N / 64; c += kSplit) {
+          uint32_t rg[32], ru[32];
+          ptx::tmem_ld_32x32(taddr_row + c * 32, rg);                 // gate channels
+          ptx::tmem_ld_32x32(taddr_row + BLOCK_N / 2 + c * 32, ru);   // matching up channels
+          ptx::tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float g = round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(rg[j]), sa), sbs[c * 32 + j]));
+            const float u = round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(ru[j]), sa), sbs[BLOCK_N / 2 + c * 32 + j]));
+            const float y = round_bf16(__fmul_rn(silu_bf16(g), u));
+            v[j] = y;
+            amax = fmaxf(amax, fabsf(y));
+          }
+          if (row < M) store_chunk32<__nv_bfloat16>(out_row + c * 32, v, 32);
+        }
+        if (row < M) atomicMax(row_amax + row, __float_as_uint(amax));
       }
       ptx::tc_fence_before();
       __syncwarp();
@@ -252,6 +293,235 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   if (warp == 1) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// CTA-pair variant: cluster of 2 CTAs, pair tile 256 (M) x 256 (N).
+// CTA r of the pair owns accumulator rows [m0 + 128 r, +128) and loads, per
+// 128-byte k-block, its own 128 rows of A and rows [n0 + 128 r, +128) of B (32 KB
+// per stage instead of 48 KB for the same tensor work per SM). The even CTA
+// issues tcgen05.mma.cta_group::2 (M = 256, N = 256) for both SMs.
+//   full[s]    lives in CTA 0; both CTAs' TMA loads credit their bytes to it
+//   empty[s]   one per CTA; CTA 0's MMA thread commits to both
+//   tfull[b]   one per CTA (accumulator buffer b complete); committed to both
+//   tempty[b]  lives in CTA 0; the epilogue warps of both CTAs arrive on it
+// ---------------------------------------------------------------------------
+struct PairCfg {
+  static constexpr int kBlockN = 256;
+  static constexpr int kStageA = kBlockM * kBlockK;           // 16 KB
+  static constexpr int kStageB = (kBlockN / 2) * kBlockK;     // 16 KB: this CTA's half of the B rows
+  static constexpr int kStageBytes = kStageA + kStageB;
+  static constexpr int kStages = 6;
+  static constexpr int kTmemCols = 2 * kBlockN;
+  static constexpr int kScaleBytes = 2 * kBlockN * 4 * 2;
+  static constexpr int kBarBytes = (2 * kStages + 4) * 8 + 16;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kScaleBytes + kBarBytes;
+};
+
+template <typename OutT, int EPI>
+__global__ void __launch_bounds__(EpiCfg<EPI>::kThreads, 1)
+gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                     OutT* __restrict__ out, int64_t ldo, const float* __restrict__ scale_a,
+                     const float* __restrict__ scale_b, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
+                     unsigned int* __restrict__ row_amax, int* status) {
+  using C = PairCfg;
+  constexpr int BLOCK_N = C::kBlockN;
+  constexpr int kEpiThreads = EpiCfg<EPI>::kEpiThreads;
+  constexpr int kEpiWarps = EpiCfg<EPI>::kWarps;
+  constexpr int kSplit = kEpiWarps / 4;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+
+  float* sb_stage = reinterpret_cast<float*>(smem + C::kStages * C::kStageBytes);
+  float* bias_stage = sb_stage + 2 * BLOCK_N;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes + C::kScaleBytes);
+  const uint32_t bar_full = ptx::smem_u32(bars);
+  const uint32_t bar_empty = bar_full + 8 * C::kStages;
+  const uint32_t bar_tfull = bar_empty + 8 * C::kStages;
+  const uint32_t bar_tempty = bar_tfull + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_ctarank();
+  const int pair = blockIdx.x >> 1;
+  const int n_pairs = gridDim.x >> 1;
+  const int m_blocks = (M + 2 * kBlockM - 1) / (2 * kBlockM);  // pair tiles along M
+  const int n_blocks = (N + BLOCK_N - 1) / BLOCK_N;
+  const int num_tiles = m_blocks * n_blocks;
+  const int num_kb = (K + kBlockK - 1) / kBlockK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      ptx::mbar_init(bar_full + 8 * s, 1);
+      ptx::mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(bar_tfull + 8 * b, 1);
+      ptx::mbar_init(bar_tempty + 8 * b, 2 * kEpiWarps);  // epilogue warps of both CTAs
+    }
+    *abort_flag = 0;
+    ptx::mbar_init_fence();
+    ptx::prefetch_tmap(&tmap_a);
+    ptx::prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), C::kTmemCols);
+    ptx::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  // neither CTA may signal the other's barriers before they are initialised
+  ptx::cluster_arrive();
+  ptx::cluster_wait();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ---------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
+        const int m0 = (tile % m_blocks) * (2 * kBlockM) + static_cast<int>(rank) * kBlockM;
+        const int n0 = (tile / m_blocks) * BLOCK_N + static_cast<int>(rank) * (BLOCK_N / 2);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = ptx::mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, status, 21);
+          if (!ok) break;
+          const uint32_t sa = base + stage * C::kStageBytes;
+          const uint32_t full0 = ptx::mapa(bar_full + 8 * stage, 0);  // CTA 0 collects both CTAs' bytes
+          if (rank == 0) ptx::mbar_expect_tx(bar_full + 8 * stage, 2 * C::kStageBytes);
+          ptx::tma_load_2d_pair(sa, &tmap_a, kb * kBlockK, m0, full0);
+          ptx::tma_load_2d_pair(sa + C::kStageA, &tmap_b, kb * kBlockK, n0, full0);
+          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (CTA 0 only) ----------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = ptx::make_idesc(0u, 0u, 2 * kBlockM, BLOCK_N);
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int tile = pair; tile < num_tiles && ok; tile += n_pairs, ++it) {
+        const uint32_t buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        ok = ptx::mbar_wait(bar_tempty + 8 * buf, acc_phase ^ 1u, abort_flag, status, 22);
+        if (!ok) break;
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BLOCK_N;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = ptx::mbar_wait(bar_full + 8 * stage, phase, abort_flag, status, 23);
+          if (!ok) break;
+          ptx::tc_fence_after();
+          const uint32_t sa = base + stage * C::kStageBytes;
+          const uint64_t a_desc = ptx::smem_desc_sw128(sa);
+          const uint64_t b_desc = ptx::smem_desc_sw128(sa + C::kStageA);
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k)
+            ptx::mma_f8f6f4_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          ptx::tc_commit_pair(ptx::mapa(bar_empty + 8 * stage, 0));  // stage reusable in both CTAs
+          ptx::tc_commit_pair(ptx::mapa(bar_empty + 8 * stage, 1));
+          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) {
+          ptx::tc_commit_pair(ptx::mapa(bar_tfull + 8 * buf, 0));  // accumulator complete in both CTAs
+          ptx::tc_commit_pair(ptx::mapa(bar_tfull + 8 * buf, 1));
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------ epilogue (both CTAs) -------------------
+    const int quad = warp & 3;
+    const int epi_tid = threadIdx.x - 64;
+    const int part = (warp - 2) >> 2;
+    bool ok = true;
+    int it = 0;
+    for (int tile = pair; tile < num_tiles && ok; tile += n_pairs, ++it) {
+      const int m0 = (tile % m_blocks) * (2 * kBlockM) + static_cast<int>(rank) * kBlockM;
+      const int n0 = (tile / m_blocks) * BLOCK_N;
+      const uint32_t buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      float* sbs = sb_stage + buf * BLOCK_N;
+      float* bss = bias_stage + buf * BLOCK_N;
+      for (int i = epi_tid; i < BLOCK_N; i += kEpiThreads) {
+        const int n = n0 + i;
+        sbs[i] = n < N ? __ldg(scale_b + n) : 0.f;
+        bss[i] = (bias != nullptr && n < N) ? __bfloat162float(bias[n]) : 0.f;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+      const int row = m0 + quad * 32 + lane;
+      const float sa = row < M ? __ldg(scale_a + row) : 0.f;
+      int okw = 0;
+      if (lane == 0) okw = ptx::mbar_wait(bar_tfull + 8 * buf, acc_phase, abort_flag, status, 24) ? 1 : 0;
+      okw = __shfl_sync(0xffffffffu, okw, 0);
+      if (!okw) { ok = false; break; }
+      ptx::tc_fence_after();
+      const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BLOCK_N;
+      if constexpr (EPI == 0) {
+        OutT* out_row = out + static_cast<int64_t>(row) * ldo + n0;
+#pragma unroll 1
+        for (int c = part; c < BLOCK_N / 32; c += kSplit) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(taddr_row + c * 32, r);
+          ptx::tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float t = __fmul_rn(__fmul_rn(__uint_as_float(r[j]), sa), sbs[c * 32 + j]);
+            if (bias != nullptr) t = __fadd_rn(round_bf16(t), bss[c * 32 + j]);
+            v[j] = t;
+          }
+          const int nvalid = N - (n0 + c * 32);
+          if (row < M && nvalid > 0) store_chunk32<OutT>(out_row + c * 32, v, nvalid);
+        }
+      } else {
+        __nv_bfloat16* out_row = reinterpret_cast<__nv_bfloat16*>(out) + static_cast<int64_t>(row) * ldo + n0 / 2;
+        float amax = 0.f;
+#pragma unroll 1
+        for (int c = part; c < BLOCK_N / 64; c += kSplit) {
+          uint32_t rg[32], ru[32];
+          ptx::tmem_ld_32x32(taddr_row + c * 32, rg);
+          ptx::tmem_ld_32x32(taddr_row + BLOCK_N / 2 + c * 32, ru);
+          ptx::tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float g = round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(rg[j]), sa), sbs[c * 32 + j]));
+            const float u = round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(ru[j]), sa), sbs[BLOCK_N / 2 + c * 32 + j]));
+            const float y = round_bf16(__fmul_rn(silu_bf16(g), u));
+            v[j] = y;
+            amax = fmaxf(amax, fabsf(y));
+          }
+          if (row < M) store_chunk32<__nv_bfloat16>(out_row + c * 32, v, 32);
+        }
+        if (row < M) atomicMax(row_amax + row, __float_as_uint(amax));
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa(bar_tempty + 8 * buf, 0));
+    }
+  }
+
+  // common exit: both CTAs of the pair converge before either frees TMEM or leaves
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  ptx::cluster_arrive();
+  ptx::cluster_wait();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc_pair(tmem_base, C::kTmemCols);
   }
 }
 
@@ -316,16 +586,17 @@ static int pick_block_n(int M, int N) {
   return best_n;
 }
 
-template <int BLOCK_N, typename OutT>
+template <int BLOCK_N, typename OutT, int EPI = 0>
 static int launch(const void* a, const void* b, const float* sa, const float* sb, const void* bias, void* out,
-                  int64_t ldo, int M, int N, int K, int64_t lda, int64_t ldb, cudaStream_t stream) {
+                  int64_t ldo, int M, int N, int K, int64_t lda, int64_t ldb, cudaStream_t stream,
+                  unsigned int* row_amax = nullptr) {
   using C = Cfg<BLOCK_N>;
   CUtensorMap ta, tb;
   int st = make_tmap_u8(&ta, a, M, K, lda, kBlockM);
   if (st != FR_OK) return st;
   st = make_tmap_u8(&tb, b, N, K, ldb, BLOCK_N);
   if (st != FR_OK) return st;
-  auto kern = gemm_fp8_kernel<BLOCK_N, OutT>;
+  auto kern = gemm_fp8_kernel<BLOCK_N, OutT, EPI>;
   static bool attr_done = false;  // per template instantiation
   if (!attr_done) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
@@ -336,9 +607,61 @@ static int launch(const void* a, const void* b, const float* sa, const float* sb
   if (!status) return FR_ERR_CUDA;
   const int tiles = ceil_div(M, kBlockM) * ceil_div(N, BLOCK_N);
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(ta, tb, static_cast<OutT*>(out), ldo, sa, sb,
-                                                  static_cast<const __nv_bfloat16*>(bias), M, N, K, status);
+  kern<<<grid, EpiCfg<EPI>::kThreads, C::kSmemBytes, stream>>>(ta, tb, static_cast<OutT*>(out), ldo, sa, sb,
+                                                  static_cast<const __nv_bfloat16*>(bias), M, N, K, row_amax, status);
   return launch_status();
+}
+
+template <typename OutT, int EPI>
+static int launch_pair(const void* a, const void* b, const float* sa, const float* sb, const void* bias, void* out,
+                       int64_t ldo, int M, int N, int K, int64_t lda, int64_t ldb, cudaStream_t stream,
+                       unsigned int* row_amax = nullptr) {
+  using C = PairCfg;
+  CUtensorMap ta, tb;
+  int st = make_tmap_u8(&ta, a, M, K, lda, kBlockM);
+  if (st != FR_OK) return st;
+  st = make_tmap_u8(&tb, b, N, K, ldb, C::kBlockN / 2);
+  if (st != FR_OK) return st;
+  auto kern = gemm_fp8_pair_kernel<OutT, EPI>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
+      return FR_ERR_CUDA;
+    attr_done = true;
+  }
+  int* status = device_status_ptr();
+  if (!status) return FR_ERR_CUDA;
+  const int tiles = ceil_div(M, 2 * kBlockM) * ceil_div(N, C::kBlockN);
+  const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(EpiCfg<EPI>::kThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, static_cast<OutT*>(out), ldo, sa, sb,
+                         static_cast<const __nv_bfloat16*>(bias), M, N, K, row_amax, status) != cudaSuccess) {
+    cudaGetLastError();
+    return FR_ERR_CUDA;
+  }
+  return FR_OK;
+}
+
+// CTA pairs pay off once there are several waves of 256 x 256 tiles; FR_GEMM_PAIR=0/1 overrides.
+static bool use_pair(int M, int N) {
+  static int forced = []() {
+    const char* e = getenv("FR_GEMM_PAIR");
+    return e ? (e[0] == '0' ? 0 : 1) : -1;
+  }();
+  if (forced >= 0) return forced == 1;
+  const int64_t tiles = static_cast<int64_t>(ceil_div(M, 2 * kBlockM)) * ceil_div(N, PairCfg::kBlockN);
+  return tiles >= 3 * (sm_count() / 2);
 }
 
 }  // namespace gemm
@@ -358,6 +681,11 @@ extern "C" int fr_gemm_fp8_w8a8(const void* a, const void* b, const float* scale
   FR_CHECK_ARG(out_is_f32 ? (ldo % 4 == 0) : (ldo % 8 == 0));
   FR_CHECK_ARG(K % 16 == 0);
   FR_CHECK_SUPPORTED(out_is_f32 ? (bias == nullptr) : true);
+  if (block_n_hint == 512 || (block_n_hint == 0 && gemm::use_pair(M, N))) {
+    return out_is_f32 ? gemm::launch_pair<float, 0>(a, b, scale_a, scale_b, bias, out, ldo, M, N, K, lda, ldb, stream)
+                      : gemm::launch_pair<__nv_bfloat16, 0>(a, b, scale_a, scale_b, bias, out, ldo, M, N, K, lda, ldb,
+                                                            stream);
+  }
   int bn = block_n_hint;
   if (bn != 64 && bn != 128 && bn != 256) bn = gemm::pick_block_n(M, N);
 #define FR_GEMM_CASE(BN)                                                                                          \
@@ -372,4 +700,20 @@ extern "C" int fr_gemm_fp8_w8a8(const void* a, const void* b, const float* scale
   }
 #undef FR_GEMM_CASE
   return FR_ERR_UNSUPPORTED;
+}
+
+extern "C" int fr_gemm_fp8_silu_mul(const void* a, const void* b_interleaved, const float* scale_a,
+                                    const float* scale_b_interleaved, void* y_out, float* row_amax, int M, int N,
+                                    int K, int64_t lda, int64_t ldb, int64_t ldo, int mode, cudaStream_t stream) {
+  FR_CHECK_ARG(M >= 0 && N > 0 && K > 0);
+  if (M == 0) return FR_OK;
+  FR_CHECK_ARG(a && b_interleaved && scale_a && scale_b_interleaved && y_out && row_amax);
+  FR_CHECK_SUPPORTED(N % 256 == 0);
+  FR_CHECK_ARG(aligned16(a) && aligned16(b_interleaved) && aligned16(y_out));
+  FR_CHECK_ARG(lda >= K && ldb >= K && ldo >= N / 2 && lda % 16 == 0 && ldb % 16 == 0 && ldo % 8 == 0 && K % 16 == 0);
+  if (mode == 2 || (mode == 0 && gemm::use_pair(M, N)))
+    return gemm::launch_pair<__nv_bfloat16, 1>(a, b_interleaved, scale_a, scale_b_interleaved, nullptr, y_out, ldo, M,
+                                               N, K, lda, ldb, stream, reinterpret_cast<unsigned int*>(row_amax));
+  return gemm::launch<256, __nv_bfloat16, 1>(a, b_interleaved, scale_a, scale_b_interleaved, nullptr, y_out, ldo, M, N,
+                                             K, lda, ldb, stream, reinterpret_cast<unsigned int*>(row_amax));
 }

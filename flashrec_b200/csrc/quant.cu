@@ -40,18 +40,23 @@ row_warp_kernel(const uint4* __restrict__ x, uint4* __restrict__ resid, const ui
 
   if constexpr (RESID) {
     uint4* rr = resid + static_cast<size_t>(row) * kVecPerRow;
+    // every residual load is issued before the first store to the same array (the
+    // compiler cannot reorder them itself), so the row costs one memory round trip
+    uint4 r[VPL];
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) r[j] = rr[j * 32 + lane];
 #pragma unroll
     for (int j = 0; j < VPL; ++j) {
-      uint4 r = rr[j * 32 + lane];
       uint32_t* xv = reinterpret_cast<uint32_t*>(&v[j]);
-      const uint32_t* rv = reinterpret_cast<const uint32_t*>(&r);
+      const uint32_t* rv = reinterpret_cast<const uint32_t*>(&r[j]);
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
         // residual + x in bf16: fp32 add, one rounding to bf16
         xv[t] = pack_bf16(__fadd_rn(bf16lo(rv[t]), bf16lo(xv[t])), __fadd_rn(bf16hi(rv[t]), bf16hi(xv[t])));
       }
-      rr[j * 32 + lane] = v[j];
     }
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) rr[j * 32 + lane] = v[j];
   }
 
   float amax = 0.f;
@@ -248,28 +253,6 @@ row_quant_f32_kernel(const float4* __restrict__ x, uint32_t* __restrict__ q, flo
 // ---------------------------------------------------------------------------
 // SwiGLU: silu(gate) * up, both rounded to bf16 as the torch bf16 path does.
 // ---------------------------------------------------------------------------
-// silu(g) = g / (1 + exp(-g)) correctly rounded to fp32, then to bf16. The fast
-// path (ex2.approx + approximate divide) is within ~40 fp32 ulp of the exact
-// value for |g| <= 16; only results that land within 128 ulp of a bf16 rounding
-// midpoint (0.4 % of them), large |g| and tiny results are re-evaluated in fp64,
-// so the bf16 value always equals the one obtained from an exact evaluation.
-__device__ __forceinline__ float silu_bf16(float g) {
-  float s = __fdividef(g, 1.0f + __expf(-g));
-  const uint32_t low = __float_as_uint(s) & 0xffffu;
-  const bool hard = (low - (0x8000u - 128u) <= 256u) || !(fabsf(g) <= 16.f) || !(fabsf(s) >= 1e-30f);
-  if (hard) {
-    const double gd = static_cast<double>(g);
-    s = static_cast<float>(gd / (1.0 + exp(-gd)));
-  }
-  return round_bf16(s);
-}
-
-__device__ __forceinline__ uint32_t silu_mul_pack(uint32_t g, uint32_t u) {
-  float a = __fmul_rn(silu_bf16(bf16lo(g)), bf16lo(u));
-  float b = __fmul_rn(silu_bf16(bf16hi(g)), bf16hi(u));
-  return pack_bf16(a, b);
-}
-
 template <int NV, bool QUANT>
 __global__ void __launch_bounds__(kBlockRowThreads)
 silu_mul_kernel(const uint4* __restrict__ x, uint2* __restrict__ q, float* __restrict__ scale,
@@ -326,6 +309,40 @@ silu_mul_kernel(const uint4* __restrict__ x, uint2* __restrict__ q, float* __res
     }
     if (threadIdx.x == 0) scale[row] = s;
   }
+}
+
+// Rows whose max|y| is already known (written by the fused GEMM epilogue):
+// pure streaming quantiser, 16-byte loads / 8-byte stores, grid-stride.
+template <int NV>
+__global__ void __launch_bounds__(256)
+quant_known_amax_kernel(const uint4* __restrict__ y, const float* __restrict__ row_amax, uint2* __restrict__ q,
+                        float* __restrict__ scale, int vec_per_row) {
+  const int row = blockIdx.x;
+  const uint4* yr = y + static_cast<size_t>(row) * vec_per_row;
+  uint4 v[NV];
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int i = j * 256 + threadIdx.x;
+    v[j] = make_uint4(0, 0, 0, 0);
+    if (i < vec_per_row) v[j] = __ldcs(yr + i);
+  }
+  const float s = row_scale(__ldg(row_amax + row));
+  const float inv = __fdiv_rn(1.0f, s);
+  uint2* qr = q + static_cast<size_t>(row) * vec_per_row;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int i = j * 256 + threadIdx.x;
+    if (i < vec_per_row) {
+      const uint32_t xv[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+      uint2 o;
+      o.x = pack_e4m3x4(quant_div_fast(bf16lo(xv[0]), s, inv), quant_div_fast(bf16hi(xv[0]), s, inv),
+                        quant_div_fast(bf16lo(xv[1]), s, inv), quant_div_fast(bf16hi(xv[1]), s, inv));
+      o.y = pack_e4m3x4(quant_div_fast(bf16lo(xv[2]), s, inv), quant_div_fast(bf16hi(xv[2]), s, inv),
+                        quant_div_fast(bf16lo(xv[3]), s, inv), quant_div_fast(bf16hi(xv[3]), s, inv));
+      qr[i] = o;
+    }
+  }
+  if (threadIdx.x == 0) scale[row] = s;
 }
 
 // ---------------------------------------------------------------------------
@@ -435,4 +452,24 @@ extern "C" int fr_silu_mul_bf16(const void* x, void* y_out, int rows, int d, cud
   if (rows == 0) return FR_OK;
   FR_CHECK_ARG(x && y_out && aligned16(x) && aligned16(y_out));
   return launch_silu<false>(x, nullptr, nullptr, y_out, rows, d, stream);
+}
+
+extern "C" int fr_quant_known_amax_fp8(const void* y, const float* row_amax, void* q_out, float* scale_out, int rows,
+                                       int d, cudaStream_t stream) {
+  FR_CHECK_ARG(rows >= 0 && d > 0 && d % 8 == 0);
+  if (rows == 0) return FR_OK;
+  FR_CHECK_ARG(y && row_amax && q_out && scale_out && aligned16(y) && aligned16(q_out));
+  const uint4* yp = static_cast<const uint4*>(y);
+  uint2* qp = static_cast<uint2*>(q_out);
+  const int vec = d / 8;
+  switch (ceil_div(vec, 256)) {
+    case 1: quant_known_amax_kernel<1><<<rows, 256, 0, stream>>>(yp, row_amax, qp, scale_out, vec); break;
+    case 2: quant_known_amax_kernel<2><<<rows, 256, 0, stream>>>(yp, row_amax, qp, scale_out, vec); break;
+    case 3: quant_known_amax_kernel<3><<<rows, 256, 0, stream>>>(yp, row_amax, qp, scale_out, vec); break;
+    case 4: quant_known_amax_kernel<4><<<rows, 256, 0, stream>>>(yp, row_amax, qp, scale_out, vec); break;
+    case 5: case 6: case 7: case 8:
+      quant_known_amax_kernel<8><<<rows, 256, 0, stream>>>(yp, row_amax, qp, scale_out, vec); break;
+    default: return FR_ERR_UNSUPPORTED;  // d > 16384
+  }
+  return launch_status();
 }

@@ -15,6 +15,7 @@ import torch
 from flashrec_b200._lib import call, ptr, stream_ptr
 from flashrec_b200.attention import AttentionBackend, TokenToKVPool
 from flashrec_b200.kernel.qk_rope_kv import fused_qk_norm_rope_store_fp8
+from flashrec_b200.kernel.sglops import fp8_scaled_mm_silu_mul, interleave_gate_up, quant_known_amax_fp8
 from flashrec_b200.kernel.silu_fp8 import silu_and_mul_per_token_quant_fp8
 from flashrec_b200.layers import Linear, RMSNorm, RotaryEmbedding
 
@@ -82,12 +83,34 @@ class Qwen3Attention:
 
 
 class Qwen3MLP:
-    def __init__(self, cfg: Qwen3Config):
+    """``fuse_silu_gemm``: run SwiGLU inside the gate_up GEMM epilogue (weight rows
+    interleaved once at load time); the result is bit-identical to the reference's
+    call order gate_up GEMM -> silu_and_mul_per_token_quant_fp8, which is kept
+    as the unfused branch."""
+
+    def __init__(self, cfg: Qwen3Config, fuse_silu_gemm: bool = True):
         self.gate_up_proj = Linear(cfg.hidden_size, 2 * cfg.intermediate_size)
         self.down_proj = Linear(cfg.intermediate_size, cfg.hidden_size)
+        self.fuse_silu_gemm = bool(fuse_silu_gemm) and cfg.intermediate_size % 128 == 0
+        self._gu_w: Optional[torch.Tensor] = None
+        self._gu_s: Optional[torch.Tensor] = None
+
+    def prepare_fused(self, free_unfused: bool = False) -> None:
+        """Build the interleaved gate_up weight from the loaded ``gate_up_proj``."""
+        if not self.fuse_silu_gemm:
+            return
+        w_nk = self.gate_up_proj._fp8_weight.t()
+        self._gu_w, self._gu_s = interleave_gate_up(w_nk, self.gate_up_proj._fp8_scale)
+        if free_unfused:
+            self.gate_up_proj._fp8_weight = None
+            self.gate_up_proj._fp8_scale = None
 
     def forward(self, x, *, q_fp8, a_scale) -> torch.Tensor:
         rows = int(q_fp8.shape[0])
+        if self.fuse_silu_gemm and self._gu_w is not None:
+            y, amax = fp8_scaled_mm_silu_mul(q_fp8, self._gu_w, a_scale, self._gu_s)
+            y_fp8, y_scale = quant_known_amax_fp8(y, amax)
+            return self.down_proj.forward_fp8(y_fp8, y_scale, (rows, self.down_proj.in_features), torch.bfloat16)
         gu = self.gate_up_proj.forward_fp8(q_fp8, a_scale, (rows, self.gate_up_proj.in_features), torch.bfloat16)
         y_fp8, y_scale = silu_and_mul_per_token_quant_fp8(gu)
         return self.down_proj.forward_fp8(y_fp8, y_scale, (rows, self.down_proj.in_features), torch.bfloat16)
@@ -161,6 +184,7 @@ class Qwen3ForCausalLM:
             a.o_proj.load(rnd(cfg.hidden_size, a.o_proj.in_features), quantize_fp8=True)
             layer.mlp.gate_up_proj.load(rnd(2 * cfg.intermediate_size, cfg.hidden_size), quantize_fp8=True)
             layer.mlp.down_proj.load(rnd(cfg.hidden_size, cfg.intermediate_size), quantize_fp8=True)
+            layer.mlp.prepare_fused(free_unfused=True)
         if embed:
             self.embed_tokens = (
                 torch.randn((cfg.vocab_size, cfg.hidden_size), generator=g, device=self.device, dtype=torch.float32)

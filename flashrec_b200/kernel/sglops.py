@@ -120,6 +120,45 @@ def fp8_scaled_mm(
     return out
 
 
+def interleave_gate_up(weight_nk: torch.Tensor, scale: torch.Tensor, block: int = 128):
+    """Regroup the rows of a merged gate_up weight ``[2d, K]`` (gate rows first, then
+    up rows, as ``merge_gate_up`` in the reference's models/weight.py lays them out)
+    so that every 2*block rows hold ``block`` gate channels followed by the matching
+    ``block`` up channels — the layout ``fp8_scaled_mm_silu_mul`` expects."""
+    two_d = int(weight_nk.shape[0])
+    d = two_d // 2
+    if two_d % 2 or d % block:
+        raise ValueError(f"intermediate size {d} must be a multiple of {block}")
+    idx = torch.arange(d, device=weight_nk.device).view(d // block, block)
+    perm = torch.cat((idx, idx + d), dim=1).reshape(-1)
+    return weight_nk.index_select(0, perm).contiguous(), scale.reshape(-1).index_select(0, perm).contiguous()
+
+
+def fp8_scaled_mm_silu_mul(a_fp8, b_interleaved_nk, scale_a, scale_b_interleaved, *, mode: int = 0):
+    """gate_up GEMM with SwiGLU in the epilogue: returns ``(y bf16 [M, d], row_amax f32 [M])``,
+    bit-identical to ``silu_and_mul(fp8_scaled_mm(...))`` on the un-interleaved weight."""
+    require_cuda(a_fp8, b_interleaved_nk, scale_a, scale_b_interleaved)
+    m, k = int(a_fp8.shape[0]), int(a_fp8.shape[1])
+    n = int(b_interleaved_nk.shape[0])
+    y = torch.empty((m, n // 2), dtype=torch.bfloat16, device=a_fp8.device)
+    amax = torch.zeros(m, dtype=torch.float32, device=a_fp8.device)
+    sa = scale_a.reshape(-1).to(torch.float32).contiguous()
+    call("fr_gemm_fp8_silu_mul", ptr(a_fp8), ptr(b_interleaved_nk), ptr(sa), ptr(scale_b_interleaved), ptr(y),
+         ptr(amax), m, n, k, a_fp8.stride(0), b_interleaved_nk.stride(0), y.stride(0), int(mode),
+         stream_ptr(a_fp8.device))
+    return y, amax
+
+
+def quant_known_amax_fp8(y: torch.Tensor, row_amax: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per-row e4m3 quantisation when max|y| per row is already known."""
+    require_cuda(y, row_amax)
+    rows, d = int(y.shape[0]), int(y.shape[1])
+    q = torch.empty((rows, d), dtype=_FP8, device=y.device)
+    s = torch.empty((rows, 1), dtype=torch.float32, device=y.device)
+    call("fr_quant_known_amax_fp8", ptr(y), ptr(row_amax), ptr(q), ptr(s), rows, d, stream_ptr(y.device))
+    return q, s
+
+
 def silu_and_mul(x: torch.Tensor) -> torch.Tensor:
     """SwiGLU ``silu(x[..., :d]) * x[..., d:]`` in bf16 (kernel/sglops.py:143-151)."""
     require_cuda(x)

@@ -79,13 +79,35 @@ int fr_silu_mul_bf16(const void* x, void* y_out, int rows, int d, cudaStream_t s
  * reference passes its `.t()` view); scale_a f32 [M]; scale_b f32 [N]; bias
  * bf16 [N] or NULL; out: bf16 (out_is_f32 == 0) or f32 [M,N] pitch ldo
  * (elements). K % 16 == 0; pitches in elements, multiples of 16 for a/b.
- * block_n_hint: 0 = choose, else 64 / 128 / 256. Reports FR_ERR_TIMEOUT
+ * block_n_hint: 0 = choose, 64 / 128 / 256 = one CTA per 128 x block_n tile,
+ * 512 = CTA pairs (cluster of 2, tcgen05 cta_group::2) on 256 x 256 tiles. Reports FR_ERR_TIMEOUT
  * through fr_device_status if a pipeline wait gives up.
  * Reference: Linear.forward_fp8 -> fp8_scaled_mm (layers/linear.py:134-172,
  * kernel/sglops.py:99-140). */
 int fr_gemm_fp8_w8a8(const void* a, const void* b, const float* scale_a, const float* scale_b, const void* bias,
                      void* out, int out_is_f32, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldo,
                      int block_n_hint, cudaStream_t stream);
+
+/* gate_up GEMM with SwiGLU fused into the epilogue. b_interleaved / its scales:
+ * the [2d, K] gate_up weight with rows regrouped per 256-row tile as
+ * [gate rows 128t .. 128t+127 | up rows 128t .. 128t+127] (N = 2d, d % 128 == 0).
+ * y_out: bf16 [M, d] = bf16(silu(bf16 gate) * bf16 up), identical to what
+ * fr_gemm_fp8_w8a8 followed by fr_silu_mul_bf16 produces; row_amax: f32 [M],
+ * must be ZERO on entry, receives max|y| per row (then feed
+ * fr_quant_known_amax_fp8). Together they reproduce fr_gemm_fp8_w8a8 +
+ * fr_silu_mul_quant_fp8 bit for bit while moving half the bytes. mode: 0 = choose,
+ * 1 = one CTA per 128 x 256 tile, 2 = CTA pairs on 256 x 256 tiles.
+ * Reference: Qwen3MLP.forward (models/qwen3.py:144-172). */
+int fr_gemm_fp8_silu_mul(const void* a, const void* b_interleaved, const float* scale_a,
+                         const float* scale_b_interleaved, void* y_out, float* row_amax, int M, int N, int K,
+                         int64_t lda, int64_t ldb, int64_t ldo, int mode, cudaStream_t stream);
+
+/* Per-row e4m3 quantisation of bf16 rows whose max|y| is already known:
+ * scale = max(row_amax, 1e-12) / 448. q_out e4m3 [rows, d], scale_out f32 [rows].
+ * Reference: the quantisation half of silu_and_mul_per_token_quant_fp8
+ * (kernel/silu_fp8.py:57-71). */
+int fr_quant_known_amax_fp8(const void* y, const float* row_amax, void* q_out, float* scale_out, int rows, int d,
+                            cudaStream_t stream);
 
 /* ---- attention-side data movement (HBM bound) ---------------------------- */
 

@@ -121,6 +121,11 @@ GEMM_SHAPES = [
     (200, 1000, 1040, 128),
     (300, 328, 144, 256),
     (1, 8, 16, 64),
+    # 512 = CTA pairs (cluster of 2) on 256 x 256 tiles
+    (512, 512, 2048, 512),
+    (300, 328, 144, 512),
+    (1000, 768, 256, 512),
+    (130, 2048, 6144, 512),
 ]
 
 
@@ -159,7 +164,7 @@ def test_gemm_exact_accumulation_small_integers():
     ref = a @ b.t()
     ones_m = torch.ones(m, 1, device=DEV)
     ones_n = torch.ones(n, device=DEV)
-    for bn in (64, 128, 256):
+    for bn in (64, 128, 256, 512):
         out = fp8_scaled_mm(a.to(torch.float8_e4m3fn).to(DEV), b.to(torch.float8_e4m3fn).to(DEV).t(), ones_m, ones_n,
                             torch.float32, block_n=bn)
         assert torch.equal(out.cpu(), ref), f"block_n={bn}"
@@ -193,3 +198,30 @@ def test_bad_arguments_raise():
     b = torch.zeros(16, 24, device=DEV).to(torch.float8_e4m3fn)
     with pytest.raises(FlashRecKernelError):
         fp8_scaled_mm(a, b.t(), torch.ones(8, 1, device=DEV), torch.ones(16, device=DEV), torch.bfloat16)
+
+
+@pytest.mark.parametrize("m,d,k", [(200, 256, 512), (128, 1024, 256), (37, 128, 2048)])
+def test_gemm_silu_epilogue_equals_unfused_bit_for_bit(m, d, k):
+    """gate_up GEMM with SwiGLU in the epilogue + known-amax quantiser == GEMM -> fused SwiGLU quantiser."""
+    from flashrec_b200.kernel.sglops import (fp8_scaled_mm, fp8_scaled_mm_silu_mul, interleave_gate_up,
+                                             quant_known_amax_fp8, silu_and_mul)
+    from flashrec_b200.kernel.silu_fp8 import silu_and_mul_per_token_quant_fp8
+
+    g = torch.Generator().manual_seed(m + d)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    w = 0.05 * torch.randn(2 * d, k, generator=g)
+    aq, asc = O.per_token_quant_fp8(a)
+    wq, wsc = O.quantize_weight_fp8(w)
+    aq, asc, wq, wsc = aq.to(DEV), asc.to(DEV), wq.to(DEV), wsc.to(DEV)
+    gu = fp8_scaled_mm(aq, wq.t(), asc, wsc, torch.bfloat16, block_n=256)
+    q_ref, s_ref = silu_and_mul_per_token_quant_fp8(gu)
+    wi, si = interleave_gate_up(wq, wsc)
+    y, amax = fp8_scaled_mm_silu_mul(aq, wi, asc, si, mode=1)
+    assert np.array_equal(bits16(y), bits16(silu_and_mul(gu)))
+    y2, amax2 = fp8_scaled_mm_silu_mul(aq, wi, asc, si, mode=2)  # CTA pairs
+    assert torch.equal(y2, y) and torch.equal(amax2, amax)
+    q, s = quant_known_amax_fp8(y, amax)
+    assert np.array_equal(bits8(q), bits8(q_ref)) and torch.equal(s, s_ref)
+    # and against the CPU oracle of the unfused reference order
+    qo, so = O.silu_mul_quant_fp8(gu.cpu())
+    assert np.array_equal(bits8(q), bits8(qo)) and torch.equal(s.cpu(), so)
