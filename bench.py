@@ -58,6 +58,9 @@ def parse():
     ap.add_argument("--profile-wave", action="store_true",
                     help="run one eager (non-graph) wave between cudaProfilerStart/Stop and exit (for ncu "
                          "--profile-from-start off)")
+    ap.add_argument("--profile-kernels", action="store_true",
+                    help="launch each hot kernel once at the wave's shapes (random inputs) between "
+                         "cudaProfilerStart/Stop and exit (for ncu --set full --profile-from-start off)")
     return ap.parse_args()
 
 
@@ -245,10 +248,66 @@ def time_gemms(torch, rows: int, iters: int = 10):
     return flops, sec, lib
 
 
+def profile_kernels(rows: int):
+    """One launch of every hot kernel at the bench shapes, for a small ncu capture
+    (about 1.5 GB resident, each kernel a fraction of a millisecond)."""
+    import torch
+
+    from flashrec_b200.kernel.qk_rope_kv import fused_qk_norm_rope_store_fp8
+    from flashrec_b200.kernel.rms_fp8 import fused_add_rmsnorm_per_token_quant_fp8
+    from flashrec_b200.kernel.sglops import (fp8_scaled_mm, fp8_scaled_mm_silu_mul, per_token_quant_fp8,
+                                             quant_known_amax_fp8)
+    from flashrec_b200.kernel.silu_fp8 import silu_and_mul_per_token_quant_fp8
+    from flashrec_b200.layers import build_cos_sin_cache
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    fp8 = torch.float8_e4m3fn
+    a = torch.randn(rows, 2048, device=dev).to(fp8)
+    b = torch.randn(12288, 2048, device=dev).mul_(0.05).to(fp8)
+    sa = torch.rand(rows, 1, device=dev) * 0.02 + 0.01
+    sb = torch.rand(12288, device=dev) * 0.02 + 0.01
+    h = torch.randn(rows, 2048, device=dev).bfloat16()
+    r = torch.randn(rows, 2048, device=dev).bfloat16()
+    w = torch.ones(2048, device=dev).bfloat16()
+    gu = torch.randn(rows, 12288, device=dev).bfloat16()
+    qkv = torch.randn(rows, 32, 128, device=dev).bfloat16()
+    cs = build_cos_sin_cache(128, 2048, 1e6, device=dev)
+    pos = torch.randint(0, 2048, (rows,), device=dev)
+    loc = torch.arange(1, rows + 1, device=dev)
+    kc = torch.zeros(rows + 16, 8, 128, dtype=torch.uint8, device=dev).view(fp8)
+    vc = torch.zeros_like(kc)
+    hw = torch.ones(128, device=dev).bfloat16()
+
+    def once():
+        y, am = fp8_scaled_mm_silu_mul(a, b, sa, sb)                      # gate_up GEMM + SwiGLU epilogue
+        quant_known_amax_fp8(y, am)
+        fp8_scaled_mm(a, b.t(), sa, sb, torch.bfloat16)                   # plain GEMM, CTA pairs
+        fp8_scaled_mm(a, b.t(), sa, sb, torch.bfloat16, block_n=256)      # plain GEMM, one CTA per tile
+        fused_add_rmsnorm_per_token_quant_fp8(h, r, w, 1e-6)
+        per_token_quant_fp8(h)
+        silu_and_mul_per_token_quant_fp8(gu)                              # unfused SwiGLU quantiser
+        fused_qk_norm_rope_store_fp8(qkv[:, :16], qkv[:, 16:24], qkv[:, 24:], pos, loc, hw, hw, 1e-6, cs, kc, vc)
+
+    for _ in range(2):
+        once()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    once()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    print(json.dumps({"profiled": "kernels", "rows": rows}))
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.profile_kernels:
+        import torch
+
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        profile_kernels(args.requests * args.beam)
         return
     import numpy as np
     import torch

@@ -191,7 +191,8 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 
   if (warp == 0) {
     // ------------------------------ TMA producer ---------------------------
-    if (lane == 0 && n_tiles > 0) {
+    if (lane == 0) {
+      // Q is needed by the MMAs and, from shared memory, by the per-row tails
       ptx::mbar_expect_tx(bar_q, kSmemQ);
       ptx::tma_load_3d(sm_q, &tmap_q, 0, kvh * G, row0 + beam0, bar_q);
       ptx::tma_load_3d(sm_q + kSmemQ / 2, &tmap_q, 64, kvh * G, row0 + beam0, bar_q);
@@ -204,7 +205,7 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         ptx::tma_load_3d(sm_k + st * kSmemK + kSmemK / 2, &tmap_k, 64, jj * kTileN, gh, bar_kfull + 8 * st);
         return true;
       };
-      ok = load_k(0);
+      if (n_tiles > 0) ok = load_k(0);
       for (int j = 0; j < n_tiles && ok; ++j) {
         // K runs one tile ahead of V so that S of tile j+1 can be issued during the softmax of tile j
         if (j + 1 < n_tiles) {
@@ -363,8 +364,14 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       int max_len = t_len;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) max_len = max(max_len, __shfl_xor_sync(0xffffffffu, max_len, o));
-      const __nv_bfloat16* qp = p.q + row * p.q_t + head * p.q_h;
       bool o_valid = n_tiles > 0;
+      if (max_len > 0) {  // warp-uniform; Q tile in shared memory (row r, 128-byte swizzle)
+        int okq = 0;
+        if (lane == 0) okq = ptx::mbar_wait(bar_q, 0, abort_flag, status, 20) ? 1 : 0;
+        okq = __shfl_sync(0xffffffffu, okq, 0);
+        if (!okq) max_len = 0;
+      }
+      const uint8_t* q_row = smem + r * 128;  // + k-block * 16 KB + (chunk ^ (r & 7)) * 16
       constexpr int kBatch = 4;
       for (int t0 = 0; t0 < max_len; t0 += kBatch) {
         float sc[kBatch];
@@ -377,14 +384,23 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
             int64_t s = p.indices[t_beg + t0 + b];
             s = s < 0 ? 0 : (s >= p.num_slots ? p.num_slots - 1 : s);
             slot[b] = s;
-            const uint8_t* kp = p.kc + s * p.ck_s + kvh * p.ck_h;
+          }
+        }
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+          if (t0 + b < t_len) {
+            const uint8_t* kp = p.kc + slot[b] * p.ck_s + kvh * p.ck_h;
+            uint4 kk[kD / 16];
+#pragma unroll
+            for (int c = 0; c < kD / 16; ++c) kk[c] = __ldg(reinterpret_cast<const uint4*>(kp + c * 16));  // all in flight
             float dot = 0.f;
-#pragma unroll 2
+#pragma unroll
             for (int c = 0; c < kD / 16; ++c) {
-              const uint4 kk = __ldg(reinterpret_cast<const uint4*>(kp + c * 16));
-              const uint4 q0 = __ldg(reinterpret_cast<const uint4*>(qp + c * 16));
-              const uint4 q1 = __ldg(reinterpret_cast<const uint4*>(qp + c * 16 + 8));
-              const uint32_t kw[4] = {kk.x, kk.y, kk.z, kk.w};
+              const uint8_t* qb = q_row + (c >> 2) * (kSmemQ / 2);
+              const int ch = (c & 3) * 2;
+              const uint4 q0 = *reinterpret_cast<const uint4*>(qb + (((ch) ^ (r & 7)) << 4));
+              const uint4 q1 = *reinterpret_cast<const uint4*>(qb + (((ch + 1) ^ (r & 7)) << 4));
+              const uint32_t kw[4] = {kk[c].x, kk[c].y, kk[c].z, kk[c].w};
               const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
@@ -421,13 +437,21 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           }
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * c_old);
+          uint4 vv[kBatch][2];
+#pragma unroll
+          for (int b = 0; b < kBatch; ++b) {
+            vv[b][0] = vv[b][1] = make_uint4(0, 0, 0, 0);
+            if (pr[b] != 0.f) {
+              const uint8_t* vp = p.vc + slot[b] * p.cv_s + kvh * p.cv_h + c * 32;
+              vv[b][0] = __ldg(reinterpret_cast<const uint4*>(vp));
+              vv[b][1] = __ldg(reinterpret_cast<const uint4*>(vp + 16));
+            }
+          }
 #pragma unroll
           for (int b = 0; b < kBatch; ++b) {
             if (pr[b] != 0.f) {
-              const uint8_t* vp = p.vc + slot[b] * p.cv_s + kvh * p.cv_h + c * 32;
-              const uint4 v0 = __ldg(reinterpret_cast<const uint4*>(vp));
-              const uint4 v1 = __ldg(reinterpret_cast<const uint4*>(vp + 16));
-              const uint32_t vw[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+              const uint32_t vw[8] = {vv[b][0].x, vv[b][0].y, vv[b][0].z, vv[b][0].w,
+                                      vv[b][1].x, vv[b][1].y, vv[b][1].z, vv[b][1].w};
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
                 const float2 va = e4m3x2_to_float2(static_cast<uint16_t>(vw[i] & 0xffffu));

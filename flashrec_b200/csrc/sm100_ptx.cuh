@@ -143,6 +143,18 @@ __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64
       : "memory");
 }
 
+// Same with the A operand read from tensor memory (M = 128: lane = row; 16-bit elements packed two
+// per 32-bit column, K = 16 elements = 8 columns per instruction).
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // 32 lanes x 32 consecutive fp32 columns: thread t of the warp receives lane
 // (taddr.lane + t), columns taddr.col .. +31. A warp may only touch the lane
 // quadrant 32 * (warp_id % 4).
