@@ -94,6 +94,7 @@ _SIGNATURES = {
     "fr_trie_advance": [P, P, P, P, P, _I, _I, _I, P],
     "fr_beam_expand": [P, P, P, P, _I, _I, _I, _I, P],
     "fr_mask_topk_expand": [P] * 16 + [_I] * 8 + [P],
+    "fr_mask_topk_expand_static": [P] * 15 + [_I] * 8 + [P],
     "fr_sid_beam_step": [P] * 7 + [_L] + [P] * 9 + [_L] * 3 + [_I] * 7 + [P],
     "fr_topk_merge_shards": [P] * 14 + [_L] * 2 + [_I] * 7 + [P],
 }

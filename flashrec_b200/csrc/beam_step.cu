@@ -639,3 +639,52 @@ extern "C" int fr_topk_merge_shards(float* out_vals, int64_t* out_parents, int64
   merge_shards_kernel<<<N, kThreads, smem, stream>>>(mp);
   return launch_status();
 }
+
+// ---------------------------------------------------------------------------
+// fr_mask_topk_expand without a caller-provided workspace.
+//
+// Who needs it: a host that binds this C ABI from a decode worker which owns no
+// allocator of its own. In the serving engine this library plugs into, device
+// memory is carved up once at start-up (weights, then the KV pool takes what is
+// left), so by the time a decode tick runs there is nothing to cudaMalloc from,
+// and a tick must not stall on the allocator anyway. Such a caller still passes
+// its inputs and outputs, but the masked-score workspace comes from the fixed
+// array below, which every GPU that loads the library holds until exit.
+//
+// Limits and rules:
+//   * N * BW * C <= FR_STATIC_SCRATCH_FLOATS (2 Mi floats = 8 MiB); larger
+//     requests are refused with FR_ERR_UNSUPPORTED, nothing is launched.
+//   * The first call on a device looks up the array's device address
+//     (cudaGetSymbolAddress with that device current) and caches it; make that
+//     first call before starting any stream capture.
+//   * All calls on a device share the one array. The kernel rewrites every
+//     workspace entry it later reads, so nothing has to be cleared between
+//     calls, but two calls that overlap on the GPU (different streams) race on it.
+// ---------------------------------------------------------------------------
+#define FR_STATIC_SCRATCH_FLOATS (2u << 20)
+static __device__ __align__(256) float g_static_scratch[FR_STATIC_SCRATCH_FLOATS];
+
+extern "C" int fr_mask_topk_expand_static(float* out_vals, int64_t* out_parents, int64_t* out_tokens,
+                                          int64_t* out_indices, int64_t* out_child, const float* cum,
+                                          const float* top_logprobs, const int64_t* top_tokens, const int64_t* node_in,
+                                          const int64_t* token_ids_in, int64_t* token_ids_out, int64_t* node_ids_out,
+                                          const uint8_t* do_expand, const int32_t* col_n, const fr_trie* trie, int N,
+                                          int BW, int C, int K, int L, int apply_mask, int apply_expand,
+                                          int apply_advance, cudaStream_t stream) {
+  FR_CHECK_ARG(N >= 0 && BW > 0 && C > 0);
+  if (static_cast<int64_t>(N) * BW * C > static_cast<int64_t>(FR_STATIC_SCRATCH_FLOATS)) return FR_ERR_UNSUPPORTED;
+  // In host code `g_static_scratch` is only a handle for the symbol, not a device
+  // address: resolve it once per device, with that device current.
+  constexpr int kMaxDev = 64;
+  static float* dev_ptr[kMaxDev] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return FR_ERR_CUDA;
+  if (dev_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) return FR_ERR_CUDA;
+    dev_ptr[dev] = static_cast<float*>(p);
+  }
+  return fr_mask_topk_expand(out_vals, out_parents, out_tokens, out_indices, out_child, dev_ptr[dev], cum,
+                             top_logprobs, top_tokens, node_in, token_ids_in, token_ids_out, node_ids_out, do_expand,
+                             col_n, trie, N, BW, C, K, L, apply_mask, apply_expand, apply_advance, stream);
+}

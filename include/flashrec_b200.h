@@ -256,6 +256,21 @@ int fr_mask_topk_expand(float* out_vals, int64_t* out_parents, int64_t* out_toke
                         const fr_trie* trie, int N, int BW, int C, int K, int L, int apply_mask, int apply_expand,
                         int apply_advance, cudaStream_t stream);
 
+/* fr_mask_topk_expand for callers that cannot hand over a workspace (a decode
+ * worker in a server whose device memory was fully carved up at start-up and
+ * that may not call the allocator during a tick): same arguments minus
+ * `scratch`; the masked scores go to a fixed 8 MiB array inside the library.
+ * N * BW * C must not exceed 2 * 1024 * 1024 (FR_ERR_UNSUPPORTED otherwise).
+ * The first call on a device resolves the array's address; make it before any
+ * stream capture. Calls on one device share the array: do not let two of them
+ * overlap on the GPU. No counterpart in the reference. */
+int fr_mask_topk_expand_static(float* out_vals, int64_t* out_parents, int64_t* out_tokens, int64_t* out_indices,
+                               int64_t* out_child, const float* cum, const float* top_logprobs,
+                               const int64_t* top_tokens, const int64_t* node_in, const int64_t* token_ids_in,
+                               int64_t* token_ids_out, int64_t* node_ids_out, const uint8_t* do_expand,
+                               const int32_t* col_n, const fr_trie* trie, int N, int BW, int C, int K, int L,
+                               int apply_mask, int apply_expand, int apply_advance, cudaStream_t stream);
+
 /* The same step with the candidates taken straight from the level's fp32
  * logits [N*BW, level_width] and their row statistics: every code of the level
  * is a candidate (score = cum + (logit - max) - logsum), so no legal SID is
