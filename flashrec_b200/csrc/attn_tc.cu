@@ -5,7 +5,8 @@
 // of two tcgen05 contractions per KV tile:
 //
 //     S = Q . K^T        kind::f16 (bf16 x bf16 -> fp32 in TMEM), M=128, N=64 tokens, K=128 dims
-//     O += P . V         P = exp2(S*scale - m) rounded to bf16, written to shared memory
+//     O += P . V         P = exp2(S*scale - m) rounded to bf16, written back into TMEM over S
+//                        and consumed from there as the A operand (no shared-memory round trip)
 //
 // Step 1 (shared_kv_prepare_kernel): per layer, the group's shared K rows are
 // widened e4m3 -> bf16 into a scratch buffer [group, kv head, token, 128] and V is
@@ -43,8 +44,7 @@ constexpr float kRescaleThreshold = 8.0f;
 constexpr int kSmemQ = kM * kD * 2;             // 32 KB: two k-blocks of [128 rows x 128 B]
 constexpr int kSmemK = kTileN * kD * 2;         // 16 KB per stage: two k-blocks of [64 rows x 128 B]
 constexpr int kSmemV = kD * kTileN * 2;         // 16 KB: [128 dims x 128 B (64 tokens)]
-constexpr int kSmemP = kM * kTileN * 2;         // 16 KB: [128 rows x 128 B (64 tokens)]
-constexpr int kSmemBytes = 1024 + kSmemQ + 2 * kSmemK + kSmemV + kSmemP + 256;
+constexpr int kSmemBytes = 1024 + kSmemQ + 2 * kSmemK + 2 * kSmemV + 256;  // K and V double buffered
 
 struct Params {
   const __nv_bfloat16* q;
@@ -134,20 +134,18 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   uint8_t* smem = smem_raw + (base - raw);
   const uint32_t sm_q = base;
   const uint32_t sm_k = sm_q + kSmemQ;       // 2 stages
-  const uint32_t sm_v = sm_k + 2 * kSmemK;
-  const uint32_t sm_p = sm_v + kSmemV;
-  uint8_t* p_smem = smem + kSmemQ + 2 * kSmemK + kSmemV;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemQ + 2 * kSmemK + kSmemV + kSmemP);
+  const uint32_t sm_v = sm_k + 2 * kSmemK;   // 2 stages
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemQ + 2 * kSmemK + 2 * kSmemV);
   const uint32_t bar0 = ptx::smem_u32(bars);
   const uint32_t bar_q = bar0;              // Q landed
   const uint32_t bar_kfull = bar0 + 8;      // [2]
   const uint32_t bar_kempty = bar0 + 24;    // [2]
-  const uint32_t bar_vfull = bar0 + 40;
-  const uint32_t bar_vempty = bar0 + 48;
-  const uint32_t bar_sfull = bar0 + 56;     // [2] S tile complete in TMEM buffer (tile & 1)
-  const uint32_t bar_pfull = bar0 + 72;     // P tile written (128 arrivals)
-  const uint32_t bar_ofull = bar0 + 80;     // P.V accumulated
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  const uint32_t bar_vfull = bar0 + 40;     // [2]
+  const uint32_t bar_vempty = bar0 + 56;    // [2]
+  const uint32_t bar_sfull = bar0 + 72;     // [2] S tile complete in TMEM buffer (tile & 1)
+  const uint32_t bar_pfull = bar0 + 88;     // P tile written into TMEM (128 arrivals)
+  const uint32_t bar_ofull = bar0 + 96;     // P.V accumulated
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   constexpr int kBeams = kM / G;
@@ -168,8 +166,10 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       ptx::mbar_init(bar_kfull + 8 * i, 1);
       ptx::mbar_init(bar_kempty + 8 * i, 1);
     }
-    ptx::mbar_init(bar_vfull, 1);
-    ptx::mbar_init(bar_vempty, 1);
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(bar_vfull + 8 * i, 1);
+      ptx::mbar_init(bar_vempty + 8 * i, 1);
+    }
     ptx::mbar_init(bar_sfull, 1);
     ptx::mbar_init(bar_sfull + 8, 1);
     ptx::mbar_init(bar_pfull, 128);
@@ -212,10 +212,11 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           ok = load_k(j + 1);
           if (!ok) break;
         }
-        ok = ptx::mbar_wait(bar_vempty, (j & 1) ^ 1u, abort_flag, status, 12);
+        const uint32_t st = j & 1, ph = (j >> 1) & 1;
+        ok = ptx::mbar_wait(bar_vempty + 8 * st, ph ^ 1u, abort_flag, status, 12);
         if (!ok) break;
-        ptx::mbar_expect_tx(bar_vfull, kSmemV);
-        ptx::tma_load_3d(sm_v, &tmap_v, j * kTileN, 0, gh, bar_vfull);
+        ptx::mbar_expect_tx(bar_vfull + 8 * st, kSmemV);
+        ptx::tma_load_3d(sm_v + st * kSmemV, &tmap_v, j * kTileN, 0, gh, bar_vfull + 8 * st);
       }
     }
     __syncwarp();
@@ -254,18 +255,19 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         }
         ok = ptx::mbar_wait(bar_pfull, j & 1, abort_flag, status, 15);
         if (!ok) break;
-        ok = ptx::mbar_wait(bar_vfull, j & 1, abort_flag, status, 16);
+        ok = ptx::mbar_wait(bar_vfull + 8 * (j & 1), (j >> 1) & 1, abort_flag, status, 16);
         if (!ok) break;
         ptx::tc_fence_after();
-        // O (+)= P V: one k-block of 64 tokens x 4 instructions of K = 16
+        // O (+)= P V: A = P straight from TMEM (bf16 pairs in the first 32 columns of the S
+        // buffer of this tile: 16 tokens = 8 columns per instruction), B = V^T tile in shared memory
         {
-          const uint64_t a_desc = ptx::smem_desc_sw128(sm_p);
-          const uint64_t b_desc = ptx::smem_desc_sw128(sm_v);
+          const uint32_t a_tmem = tmem_base + kColS + (j & 1) * kTileN;
+          const uint64_t b_desc = ptx::smem_desc_sw128(sm_v + (j & 1) * kSmemV);
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            ptx::mma_f16(tmem_base + kColO, a_desc + 2u * k, b_desc + 2u * k, idesc_o, (j | k) != 0 ? 1u : 0u);
+            ptx::mma_f16_ts(tmem_base + kColO, a_tmem + 8u * k, b_desc + 2u * k, idesc_o, (j | k) != 0 ? 1u : 0u);
         }
-        ptx::tc_commit(bar_vempty);
+        ptx::tc_commit(bar_vempty + 8 * (j & 1));
         ptx::tc_commit(bar_ofull);
       }
     }
@@ -310,43 +312,38 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         m_used = tmax;
       }
       l_sum *= factor;
-      // P (and O) may only be touched once the previous P.V has completed
-      if (j > 0) {
+      // O may only be rescaled once the previous P.V has completed (rare: the maximum is raised lazily)
+      if (j > 0 && __any_sync(0xffffffffu, factor != 1.0f)) {
         if (lane == 0) okw = ptx::mbar_wait(bar_ofull, (j - 1) & 1, abort_flag, status, 18) ? 1 : 0;
         okw = __shfl_sync(0xffffffffu, okw, 0);
         if (!okw) { ok = false; break; }
         ptx::tc_fence_after();
-        if (__any_sync(0xffffffffu, factor != 1.0f)) {
 #pragma unroll 1
-          for (int c = 0; c < kD / 32; ++c) {
-            uint32_t o[32];
-            ptx::tmem_ld_32x32(t_lane + kColO + c * 32, o);
-            ptx::tmem_ld_wait();
+        for (int c = 0; c < kD / 32; ++c) {
+          uint32_t o[32];
+          ptx::tmem_ld_32x32(t_lane + kColO + c * 32, o);
+          ptx::tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
-            ptx::tmem_st_32x32(t_lane + kColO + c * 32, o);
-          }
-          ptx::tmem_st_wait();
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+          ptx::tmem_st_32x32(t_lane + kColO + c * 32, o);
         }
+        ptx::tmem_st_wait();
       }
-      // P = exp2(S - m) as bf16 into the swizzled A-operand tile: row r, 8 chunks of 16 bytes
+      // P = exp2(S - m) as bf16 pairs, written over the first 32 columns of this tile's S buffer
+      // (S has just been read into registers; the next S for this buffer is issued after this P.V)
       float psum = 0.f;
-      uint8_t* prow = p_smem + r * 128;
+      uint32_t w[32];
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        uint32_t w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int c = ch * 8 + 2 * i;  // token index within the tile
-          const float a = exp2f(__uint_as_float(c < 32 ? s0[c & 31] : s1[c & 31]) - m_used);
-          const float b = exp2f(__uint_as_float(c + 1 < 32 ? s0[(c + 1) & 31] : s1[(c + 1) & 31]) - m_used);
-          w[i] = pack_bf16(a, b);
-          psum += bf16lo(w[i]) + bf16hi(w[i]);
-        }
-        *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      for (int i = 0; i < 32; ++i) {
+        const int c = 2 * i;  // token index within the tile
+        const float a = exp2f(__uint_as_float(c < 32 ? s0[c & 31] : s1[c & 31]) - m_used);
+        const float b = exp2f(__uint_as_float(c + 1 < 32 ? s0[(c + 1) & 31] : s1[(c + 1) & 31]) - m_used);
+        w[i] = pack_bf16(a, b);
+        psum += bf16lo(w[i]) + bf16hi(w[i]);
       }
       l_sum += psum;
-      ptx::fence_proxy_async_smem();
+      ptx::tmem_st_32x32(t_lane + kColS + (j & 1) * kTileN, w);
+      ptx::tmem_st_wait();
       ptx::tc_fence_before();
       ptx::mbar_arrive(bar_pfull);
     }

@@ -93,6 +93,27 @@ __device__ __forceinline__ void store_chunk32<float>(float* dst, const float (&v
   }
 }
 
+// Tile order: groups of kRasterGroup row blocks, column block slowest inside a
+// group, so the tiles in flight at any time (one per SM or SM pair) cover a
+// roughly square patch: each A row block is streamed from HBM once and the B
+// column blocks of the patch stay in L2, also when A alone is larger than L2
+// (the long-K down projection).
+constexpr int kRasterGroup = 8;
+struct TileCoord {
+  int mb, nb;
+};
+__device__ __forceinline__ TileCoord tile_coord(int tile, int m_blocks, int n_blocks) {
+  const int per_group = kRasterGroup * n_blocks;
+  const int group = tile / per_group;
+  const int first = group * kRasterGroup;
+  const int rows = min(kRasterGroup, m_blocks - first);
+  const int t = tile - group * per_group;
+  TileCoord c;
+  c.mb = first + t % rows;
+  c.nb = t / rows;
+  return c;
+}
+
 // EPI == 0: plain scaled output. EPI == 1 (BLOCK_N == 256, bf16 out): the weight rows
 // are interleaved per tile as [128 gate channels | the 128 matching up channels];
 // the epilogue rounds both to bf16 (exactly what the unfused GEMM would have
@@ -160,8 +181,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % m_blocks) * kBlockM;
-        const int n0 = (tile / m_blocks) * BLOCK_N;
+        const TileCoord tc = tile_coord(tile, m_blocks, n_blocks);
+        const int m0 = tc.mb * kBlockM;
+        const int n0 = tc.nb * BLOCK_N;
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = ptx::mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, status, 1);
           if (!ok) break;
@@ -216,8 +238,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     bool ok = true;
     int it = 0;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
-      const int m0 = (tile % m_blocks) * kBlockM;
-      const int n0 = (tile / m_blocks) * BLOCK_N;
+      const TileCoord tc = tile_coord(tile, m_blocks, n_blocks);
+      const int m0 = tc.mb * kBlockM;
+      const int n0 = tc.nb * BLOCK_N;
       const uint32_t buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       float* sbs = sb_stage + buf * BLOCK_N;
@@ -306,23 +329,28 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 //   empty[s]   one per CTA; CTA 0's MMA thread commits to both
 //   tfull[b]   one per CTA (accumulator buffer b complete); committed to both
 //   tempty[b]  lives in CTA 0; the epilogue warps of both CTAs arrive on it
+// Epilogue: every warp converts its 32 accumulator rows chunk by chunk, writes
+// the chunk into a swizzled shared-memory staging tile and hands it to a TMA
+// store (full 128-byte lines, clipped at the matrix edge by the hardware), so
+// the output leaves the SM as bulk copies instead of per-thread 16-byte stores.
 // ---------------------------------------------------------------------------
 struct PairCfg {
   static constexpr int kBlockN = 256;
   static constexpr int kStageA = kBlockM * kBlockK;           // 16 KB
   static constexpr int kStageB = (kBlockN / 2) * kBlockK;     // 16 KB: this CTA's half of the B rows
   static constexpr int kStageBytes = kStageA + kStageB;
-  static constexpr int kStages = 6;
+  static constexpr int kStages = 5;
   static constexpr int kTmemCols = 2 * kBlockN;
+  static constexpr int kOutStageBytes = 32 * 1024;  // epilogue staging tiles for the TMA stores
   static constexpr int kScaleBytes = 2 * kBlockN * 4 * 2;
   static constexpr int kBarBytes = (2 * kStages + 4) * 8 + 16;
-  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kScaleBytes + kBarBytes;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kOutStageBytes + kScaleBytes + kBarBytes;
 };
 
 template <typename OutT, int EPI>
 __global__ void __launch_bounds__(EpiCfg<EPI>::kThreads, 1)
 gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                     OutT* __restrict__ out, int64_t ldo, const float* __restrict__ scale_a,
+                     const __grid_constant__ CUtensorMap tmap_out, const float* __restrict__ scale_a,
                      const float* __restrict__ scale_b, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
                      unsigned int* __restrict__ row_amax, int* status) {
   using C = PairCfg;
@@ -335,9 +363,10 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw);
 
-  float* sb_stage = reinterpret_cast<float*>(smem + C::kStages * C::kStageBytes);
+  uint8_t* out_stage = smem + C::kStages * C::kStageBytes;  // 1024-byte aligned
+  float* sb_stage = reinterpret_cast<float*>(out_stage + C::kOutStageBytes);
   float* bias_stage = sb_stage + 2 * BLOCK_N;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes + C::kScaleBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + C::kOutStageBytes + C::kScaleBytes);
   const uint32_t bar_full = ptx::smem_u32(bars);
   const uint32_t bar_empty = bar_full + 8 * C::kStages;
   const uint32_t bar_tfull = bar_empty + 8 * C::kStages;
@@ -368,6 +397,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     ptx::mbar_init_fence();
     ptx::prefetch_tmap(&tmap_a);
     ptx::prefetch_tmap(&tmap_b);
+    ptx::prefetch_tmap(&tmap_out);
   }
   if (warp == 1) {
     ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), C::kTmemCols);
@@ -387,8 +417,9 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += n_pairs) {
-        const int m0 = (tile % m_blocks) * (2 * kBlockM) + static_cast<int>(rank) * kBlockM;
-        const int n0 = (tile / m_blocks) * BLOCK_N + static_cast<int>(rank) * (BLOCK_N / 2);
+        const TileCoord tc = tile_coord(tile, m_blocks, n_blocks);
+        const int m0 = tc.mb * (2 * kBlockM) + static_cast<int>(rank) * kBlockM;
+        const int n0 = tc.nb * BLOCK_N + static_cast<int>(rank) * (BLOCK_N / 2);
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = ptx::mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, status, 21);
           if (!ok) break;
@@ -445,8 +476,9 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     bool ok = true;
     int it = 0;
     for (int tile = pair; tile < num_tiles && ok; tile += n_pairs, ++it) {
-      const int m0 = (tile % m_blocks) * (2 * kBlockM) + static_cast<int>(rank) * kBlockM;
-      const int n0 = (tile / m_blocks) * BLOCK_N;
+      const TileCoord tc = tile_coord(tile, m_blocks, n_blocks);
+      const int m0 = tc.mb * (2 * kBlockM) + static_cast<int>(rank) * kBlockM;
+      const int n0 = tc.nb * BLOCK_N;
       const uint32_t buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       float* sbs = sb_stage + buf * BLOCK_N;
@@ -465,42 +497,85 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       if (!okw) { ok = false; break; }
       ptx::tc_fence_after();
       const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BLOCK_N;
+      const int ewarp = warp - 2;
+      const int row_base = m0 + quad * 32;  // first output row of this warp
       if constexpr (EPI == 0) {
-        OutT* out_row = out + static_cast<int64_t>(row) * ldo + n0;
+        // chunk = 128 bytes of output per row (64 bf16 or 32 f32 columns); two staging tiles per warp
+        constexpr int kChunkCols = 128 / static_cast<int>(sizeof(OutT));
+        constexpr int kLoads = kChunkCols / 32;
+        uint8_t* stage0 = out_stage + ewarp * 8192;
 #pragma unroll 1
-        for (int c = part; c < BLOCK_N / 32; c += kSplit) {
-          uint32_t r[32];
-          ptx::tmem_ld_32x32(taddr_row + c * 32, r);
-          ptx::tmem_ld_wait();
-          float v[32];
+        for (int c = 0; c < BLOCK_N / kChunkCols; ++c) {
+          uint8_t* st = stage0 + (c & 1) * 4096;
+          if (lane == 0) ptx::bulk_wait_read<1>();  // the store that last used this tile has read it
+          __syncwarp();
+          uint32_t w[32];  // 128 bytes of this thread's row
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float t = __fmul_rn(__fmul_rn(__uint_as_float(r[j]), sa), sbs[c * 32 + j]);
-            if (bias != nullptr) t = __fadd_rn(round_bf16(t), bss[c * 32 + j]);
-            v[j] = t;
+          for (int h = 0; h < kLoads; ++h) {
+            uint32_t r[32];
+            ptx::tmem_ld_32x32(taddr_row + c * kChunkCols + h * 32, r);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int col = c * kChunkCols + h * 32 + j;
+              float t = __fmul_rn(__fmul_rn(__uint_as_float(r[j]), sa), sbs[col]);
+              if (bias != nullptr) t = __fadd_rn(round_bf16(t), bss[col]);
+              r[j] = __float_as_uint(t);
+            }
+            if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) w[j] = r[j];
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                w[h * 16 + j] = pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+            }
           }
-          const int nvalid = N - (n0 + c * 32);
-          if (row < M && nvalid > 0) store_chunk32<OutT>(out_row + c * 32, v, nvalid);
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch)  // 128-byte swizzle: 16-byte chunk index ^ (row & 7)
+            *reinterpret_cast<uint4*>(st + lane * 128 + ((ch ^ (lane & 7)) << 4)) =
+                make_uint4(w[4 * ch], w[4 * ch + 1], w[4 * ch + 2], w[4 * ch + 3]);
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && row_base < M && n0 + c * kChunkCols < N) {
+            ptx::tma_store_2d(&tmap_out, ptx::smem_u32(st), n0 + c * kChunkCols, row_base);
+            ptx::bulk_commit();
+          }
         }
       } else {
-        __nv_bfloat16* out_row = reinterpret_cast<__nv_bfloat16*>(out) + static_cast<int64_t>(row) * ldo + n0 / 2;
+        // one 32-column chunk of y per warp and tile: 64-byte rows, 64-byte swizzle
+        uint8_t* st = out_stage + ewarp * 2048;
         float amax = 0.f;
-#pragma unroll 1
-        for (int c = part; c < BLOCK_N / 64; c += kSplit) {
-          uint32_t rg[32], ru[32];
-          ptx::tmem_ld_32x32(taddr_row + c * 32, rg);
-          ptx::tmem_ld_32x32(taddr_row + BLOCK_N / 2 + c * 32, ru);
-          ptx::tmem_ld_wait();
-          float v[32];
+        const int c = part;
+        if (lane == 0) ptx::bulk_wait_read<0>();
+        __syncwarp();
+        uint32_t rg[32], ru[32];
+        ptx::tmem_ld_32x32(taddr_row + c * 32, rg);
+        ptx::tmem_ld_32x32(taddr_row + BLOCK_N / 2 + c * 32, ru);
+        ptx::tmem_ld_wait();
+        uint32_t w[16];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float g = round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(rg[j]), sa), sbs[c * 32 + j]));
-            const float u = round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(ru[j]), sa), sbs[BLOCK_N / 2 + c * 32 + j]));
-            const float y = round_bf16(__fmul_rn(silu_bf16(g), u));
-            v[j] = y;
-            amax = fmaxf(amax, fabsf(y));
+        for (int j = 0; j < 16; ++j) {
+          float y2[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int jj = 2 * j + e;
+            const float g = round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(rg[jj]), sa), sbs[c * 32 + jj]));
+            const float u = round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(ru[jj]), sa), sbs[BLOCK_N / 2 + c * 32 + jj]));
+            y2[e] = __fmul_rn(silu_bf16(g), u);
           }
-          if (row < M) store_chunk32<__nv_bfloat16>(out_row + c * 32, v, 32);
+          w[j] = pack_bf16(y2[0], y2[1]);
+          amax = fmaxf(amax, fmaxf(fabsf(bf16lo(w[j])), fabsf(bf16hi(w[j]))));
+        }
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch)  // 64-byte swizzle: 16-byte chunk index ^ ((row >> 1) & 3)
+          *reinterpret_cast<uint4*>(st + lane * 64 + ((ch ^ ((lane >> 1) & 3)) << 4)) =
+              make_uint4(w[4 * ch], w[4 * ch + 1], w[4 * ch + 2], w[4 * ch + 3]);
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && row_base < M) {
+          ptx::tma_store_2d(&tmap_out, ptx::smem_u32(st), n0 / 2 + c * 32, row_base);
+          ptx::bulk_commit();
         }
         if (row < M) atomicMax(row_amax + row, __float_as_uint(amax));
       }
@@ -510,6 +585,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     }
   }
 
+  if (warp >= 2 && lane == 0) ptx::bulk_wait_all();  // this warp's output tiles have been written
   // common exit: both CTAs of the pair converge before either frees TMEM or leaves
   ptx::tc_fence_before();
   __syncthreads();
@@ -554,6 +630,23 @@ static int make_tmap_u8(CUtensorMap* map, const void* ptr, int64_t rows, int64_t
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FR_OK : FR_ERR_CUDA;
+}
+
+// Output matrix [rows, cols] of 2- or 4-byte elements, row pitch `ld` elements; box = box_cols x 32 rows.
+static int make_tmap_out(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t ld, int elem_bytes,
+                         int box_cols) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return FR_ERR_CUDA;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * elem_bytes};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), 32};
+  cuuint32_t estr[2] = {1, 1};
+  const int inner = box_cols * elem_bytes;
+  const CUtensorMapSwizzle sw = inner == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  CUresult r = fn(map, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? FR_OK : FR_ERR_CUDA;
 }
 
@@ -622,6 +715,10 @@ static int launch_pair(const void* a, const void* b, const float* sa, const floa
   if (st != FR_OK) return st;
   st = make_tmap_u8(&tb, b, N, K, ldb, C::kBlockN / 2);
   if (st != FR_OK) return st;
+  CUtensorMap to;
+  if (EPI == 1) st = make_tmap_out(&to, out, M, N / 2, ldo, 2, 32);
+  else st = make_tmap_out(&to, out, M, N, ldo, static_cast<int>(sizeof(OutT)), 128 / static_cast<int>(sizeof(OutT)));
+  if (st != FR_OK) return st;
   auto kern = gemm_fp8_pair_kernel<OutT, EPI>;
   static bool attr_done = false;
   if (!attr_done) {
@@ -645,8 +742,8 @@ static int launch_pair(const void* a, const void* b, const float* sa, const floa
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, static_cast<OutT*>(out), ldo, sa, sb,
-                         static_cast<const __nv_bfloat16*>(bias), M, N, K, row_amax, status) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, to, sa, sb, static_cast<const __nv_bfloat16*>(bias), M, N, K, row_amax,
+                         status) != cudaSuccess) {
     cudaGetLastError();
     return FR_ERR_CUDA;
   }
