@@ -294,17 +294,18 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       ptx::tmem_ld_32x32(t_lane + kColS + (j & 1) * kTileN + 32, s1);
       ptx::tmem_ld_wait();
       const int ntok = min(kTileN, ls - j * kTileN);
-      float tmax = -INFINITY;
+      if (ntok < kTileN) {  // last tile of the prefix (uniform over the CTA): mask the columns past its end
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        float a = __uint_as_float(s0[c]) * p.scale_log2;
-        float b = __uint_as_float(s1[c]) * p.scale_log2;
-        if (c >= ntok) a = -INFINITY;
-        if (c + 32 >= ntok) b = -INFINITY;
-        s0[c] = __float_as_uint(a);
-        s1[c] = __float_as_uint(b);
-        tmax = fmaxf(tmax, fmaxf(a, b));
+        for (int c = 0; c < 32; ++c) {
+          if (c >= ntok) s0[c] = 0xff800000u;       // -inf
+          if (c + 32 >= ntok) s1[c] = 0xff800000u;
+        }
       }
+      // maximum of the raw scores on four independent chains; the softmax scale (> 0) is applied once
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < 32; ++c) mx[c & 3] = fmaxf(mx[c & 3], fmaxf(__uint_as_float(s0[c]), __uint_as_float(s1[c])));
+      const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
       // raise the reference maximum only when the tile exceeds it by a margin
       float factor = 1.0f;
       if (tmax > m_used + kRescaleThreshold) {
@@ -331,16 +332,21 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       }
       // P = exp2(S - m) as bf16 pairs, written over the first 32 columns of this tile's S buffer
       // (S has just been read into registers; the next S for this buffer is issued after this P.V)
-      float psum = 0.f;
+      // exp2(s * scale - m): one FMA and one ex2.approx per score (the argument is at most the
+      // rescale threshold, far from overflow; -inf gives 0), sums on four independent chains
+      float ps[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t w[32];
+      const float neg_m = -m_used;
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
         const int c = 2 * i;  // token index within the tile
-        const float a = exp2f(__uint_as_float(c < 32 ? s0[c & 31] : s1[c & 31]) - m_used);
-        const float b = exp2f(__uint_as_float(c + 1 < 32 ? s0[(c + 1) & 31] : s1[(c + 1) & 31]) - m_used);
+        const float a = ex2_approx(__fmaf_rn(__uint_as_float(c < 32 ? s0[c & 31] : s1[c & 31]), p.scale_log2, neg_m));
+        const float b =
+            ex2_approx(__fmaf_rn(__uint_as_float(c + 1 < 32 ? s0[(c + 1) & 31] : s1[(c + 1) & 31]), p.scale_log2, neg_m));
         w[i] = pack_bf16(a, b);
-        psum += bf16lo(w[i]) + bf16hi(w[i]);
+        ps[i & 3] += a + b;
       }
+      const float psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
       l_sum += psum;
       ptx::tmem_st_32x32(t_lane + kColS + (j & 1) * kTileN, w);
       ptx::tmem_st_wait();

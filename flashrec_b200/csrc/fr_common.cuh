@@ -38,6 +38,10 @@ static inline int launch_status() {
   return e == cudaSuccess ? FR_OK : FR_ERR_CUDA;
 }
 
+// Device table silu(bf16) -> bf16 over all 65536 inputs for the current device, built on first use
+// (capi.cu). nullptr on a CUDA error.
+const uint16_t* silu_table_ptr(cudaStream_t stream);
+
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 static inline int ceil_div(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
@@ -115,41 +119,55 @@ __device__ __forceinline__ float row_scale(float amax) {
 // rsqrt computes); the hardware rsqrt approximation is deliberately avoided.
 __device__ __forceinline__ float rsqrt_rn(float x) { return __fdiv_rn(1.0f, __fsqrt_rn(x)); }
 
-// silu(g) = g / (1 + exp(-g)) correctly rounded to fp32, then to bf16. Fast path:
-// exp(-g) = 2^(th + tl) with th + tl = -g * log2(e) carried in two floats (the
-// product's rounding error is recovered with an FMA), ex2.approx on th and a
-// first-order correction for tl, then an approximate divide: within ~6 fp32 ulp
-// of the exact value. Only results that land within 24 ulp of a bf16 rounding
-// midpoint (0.07 %) and tiny / non-finite results are re-evaluated in fp64, so the
-// bf16 value always equals the one obtained from an exact evaluation.
+// silu(g) = g / (1 + exp(-g)) correctly rounded to fp32, then to bf16, for a bf16-valued g.
+// Fast path: exp(-g) = 2^(th + tl) with th + tl = -g * log2(e) carried in two floats (the
+// product's rounding error is recovered with an FMA), ex2.approx on th and a first-order
+// correction for tl, then an approximate divide: within ~6 fp32 ulp of the exact value.
+// Results that land within 24 ulp of a bf16 rounding midpoint, and tiny / non-finite ones,
+// cannot be trusted to round the right way; for those the answer is read from a table of the
+// exactly evaluated function over all 65536 bf16 inputs (silu_table_ptr), so the bf16 value
+// always equals the one obtained from an exact evaluation and no thread ever runs fp64 code.
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 
-__device__ __forceinline__ float silu_bf16(float g) {
+// Fast path only: returns the approximate silu(g) and sets `hard` when its bf16 rounding cannot
+// be trusted. Branch-free.
+__device__ __forceinline__ float silu_fast(float g, bool& hard) {
   constexpr float kL2eHi = 1.44269502162933349609375f;  // fp32(log2 e)
   constexpr float kL2eLo = 1.925963033500e-8f;          // log2 e - fp32(log2 e)
   const float th = __fmul_rn(g, -kL2eHi);
   const float tl = __fmaf_rn(g, -kL2eLo, __fmaf_rn(g, -kL2eHi, -th));
   float e = ex2_approx(th);
   e = __fmaf_rn(e, tl * 0.693147182f, e);
-  float s = __fdividef(g, 1.0f + e);
+  const float s = __fdividef(g, 1.0f + e);
   const uint32_t low = __float_as_uint(s) & 0xffffu;
   // (huge |g|: exp underflows to 0 and s == g exactly, or the quotient collapses to 0 / NaN and
-  //  is caught by the magnitude test)
-  const bool hard = (low - (0x8000u - 24u) <= 48u) || !(fabsf(s) >= 1e-30f);
-  if (hard) {
-    const double gd = static_cast<double>(g);
-    s = static_cast<float>(gd / (1.0 + exp(-gd)));
-  }
-  return round_bf16(s);
+  //  is caught by the magnitude test; silu(+-0) = +-0 is exact)
+  hard = (low - (0x8000u - 24u) <= 48u) || (!(fabsf(s) >= 1e-30f) && g != 0.f);
+  return s;
 }
 
-__device__ __forceinline__ uint32_t silu_mul_pack(uint32_t g, uint32_t u) {
-  float a = __fmul_rn(silu_bf16(bf16lo(g)), bf16lo(u));
-  float b = __fmul_rn(silu_bf16(bf16hi(g)), bf16hi(u));
+// fp64 evaluation rounded once to fp32: only the kernel that fills the table runs this.
+__device__ __forceinline__ float silu_exact(float g) {
+  const double gd = static_cast<double>(g);
+  return static_cast<float>(gd / (1.0 + exp(-gd)));
+}
+
+// g must be exactly representable in bf16 (its upper 16 bits index the table).
+__device__ __forceinline__ float silu_bf16(float g, const uint16_t* __restrict__ table) {
+  bool hard;
+  const float s = silu_fast(g, hard);
+  float r = round_bf16(s);
+  if (hard) r = __uint_as_float(static_cast<uint32_t>(__ldg(table + (__float_as_uint(g) >> 16))) << 16);
+  return r;
+}
+
+__device__ __forceinline__ uint32_t silu_mul_pack(uint32_t g, uint32_t u, const uint16_t* __restrict__ table) {
+  float a = __fmul_rn(silu_bf16(bf16lo(g), table), bf16lo(u));
+  float b = __fmul_rn(silu_bf16(bf16hi(g), table), bf16hi(u));
   return pack_bf16(a, b);
 }
 

@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(EpiCfg<EPI>::kThreads, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 OutT* __restrict__ out, int64_t ldo, const float* __restrict__ scale_a,
                 const float* __restrict__ scale_b, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
-                unsigned int* __restrict__ row_amax, int* status) {
+                unsigned int* __restrict__ row_amax, const uint16_t* __restrict__ silu_table, int* status) {
   using C = Cfg<BLOCK_N>;
   constexpr int kEpiThreads = EpiCfg<EPI>::kEpiThreads;
   constexpr int kSplit = EpiCfg<EPI>::kWarps / 4;  // epilogue warps per lane quadrant
@@ -290,7 +290,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           for (int j = 0; j < 32; ++j) {
             const float g = round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(rg[j]), sa), sbs[c * 32 + j]));
             const float u = round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(ru[j]), sa), sbs[BLOCK_N / 2 + c * 32 + j]));
-            const float y = round_bf16(__fmul_rn(silu_bf16(g), u));
+            const float y = round_bf16(__fmul_rn(silu_bf16(g, silu_table), u));
             v[j] = y;
             amax = fmaxf(amax, fabsf(y));
           }
@@ -317,6 +317,46 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, C::kTmemCols);
   }
+}
+
+// SwiGLU on 16 gate / 16 up accumulator columns of one row (one thread): returns max|y| and
+// hands back the 16 bf16 results as two 16-byte pieces. Branch-free (inputs whose fast silu
+// cannot be trusted take a predicated table load), so the 16 instruction chains interleave.
+// sbg / sbu: the 16 per-channel scales of the gate / up columns in global memory (16-byte
+// aligned; every thread reads the same addresses, so they come from L1).
+__device__ __forceinline__ float swiglu16(uint32_t taddr_g, uint32_t taddr_u, const float* __restrict__ sbg,
+                                          const float* __restrict__ sbu, float sa,
+                                          const uint16_t* __restrict__ silu_table, uint4& out0, uint4& out1) {
+  uint32_t rg[16], ru[16];
+  ptx::tmem_ld_32x16(taddr_g, rg);
+  ptx::tmem_ld_32x16(taddr_u, ru);
+  float sg[16], su[16];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(sbg) + q);
+    const float4 b = __ldg(reinterpret_cast<const float4*>(sbu) + q);
+    sg[4 * q] = a.x, sg[4 * q + 1] = a.y, sg[4 * q + 2] = a.z, sg[4 * q + 3] = a.w;
+    su[4 * q] = b.x, su[4 * q + 1] = b.y, su[4 * q + 2] = b.z, su[4 * q + 3] = b.w;
+  }
+  ptx::tmem_ld_wait();
+  uint32_t w[8];
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float y2[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int jj = 2 * j + e;
+      const float g = round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(rg[jj]), sa), sg[jj]));
+      const float u = round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(ru[jj]), sa), su[jj]));
+      y2[e] = __fmul_rn(silu_bf16(g, silu_table), u);
+    }
+    w[j] = pack_bf16(y2[0], y2[1]);
+    amax = fmaxf(amax, fmaxf(fabsf(bf16lo(w[j])), fabsf(bf16hi(w[j]))));
+  }
+  out0 = make_uint4(w[0], w[1], w[2], w[3]);
+  out1 = make_uint4(w[4], w[5], w[6], w[7]);
+  return amax;
 }
 
 // ---------------------------------------------------------------------------
@@ -352,7 +392,7 @@ __global__ void __launch_bounds__(EpiCfg<EPI>::kThreads, 1)
 gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_out, const float* __restrict__ scale_a,
                      const float* __restrict__ scale_b, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
-                     unsigned int* __restrict__ row_amax, int* status) {
+                     unsigned int* __restrict__ row_amax, const uint16_t* __restrict__ silu_table, int* status) {
   using C = PairCfg;
   constexpr int BLOCK_N = C::kBlockN;
   constexpr int kEpiThreads = EpiCfg<EPI>::kEpiThreads;
@@ -483,14 +523,16 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       const uint32_t acc_phase = (it >> 1) & 1;
       float* sbs = sb_stage + buf * BLOCK_N;
       float* bss = bias_stage + buf * BLOCK_N;
-      for (int i = epi_tid; i < BLOCK_N; i += kEpiThreads) {
-        const int n = n0 + i;
-        sbs[i] = n < N ? __ldg(scale_b + n) : 0.f;
-        bss[i] = (bias != nullptr && n < N) ? __bfloat162float(bias[n]) : 0.f;
-      }
-      asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
       const int row = m0 + quad * 32 + lane;
       const float sa = row < M ? __ldg(scale_a + row) : 0.f;
+      if constexpr (EPI == 0) {  // the SwiGLU epilogue reads its few scales straight from global memory
+        for (int i = epi_tid; i < BLOCK_N; i += kEpiThreads) {
+          const int n = n0 + i;
+          sbs[i] = n < N ? __ldg(scale_b + n) : 0.f;
+          bss[i] = (bias != nullptr && n < N) ? __bfloat162float(bias[n]) : 0.f;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+      }
       int okw = 0;
       if (lane == 0) okw = ptx::mbar_wait(bar_tfull + 8 * buf, acc_phase, abort_flag, status, 24) ? 1 : 0;
       okw = __shfl_sync(0xffffffffu, okw, 0);
@@ -507,8 +549,6 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll 1
         for (int c = 0; c < BLOCK_N / kChunkCols; ++c) {
           uint8_t* st = stage0 + (c & 1) * 4096;
-          if (lane == 0) ptx::bulk_wait_read<1>();  // the store that last used this tile has read it
-          __syncwarp();
           uint32_t w[32];  // 128 bytes of this thread's row
 #pragma unroll
           for (int h = 0; h < kLoads; ++h) {
@@ -531,6 +571,8 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 w[h * 16 + j] = pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
             }
           }
+          if (lane == 0) ptx::bulk_wait_read<1>();  // the store that last used this staging tile has read it
+          __syncwarp();
 #pragma unroll
           for (int ch = 0; ch < 8; ++ch)  // 128-byte swizzle: 16-byte chunk index ^ (row & 7)
             *reinterpret_cast<uint4*>(st + lane * 128 + ((ch ^ (lane & 7)) << 4)) =
@@ -547,30 +589,21 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         uint8_t* st = out_stage + ewarp * 2048;
         float amax = 0.f;
         const int c = part;
-        if (lane == 0) ptx::bulk_wait_read<0>();
-        __syncwarp();
-        uint32_t rg[32], ru[32];
-        ptx::tmem_ld_32x32(taddr_row + c * 32, rg);
-        ptx::tmem_ld_32x32(taddr_row + BLOCK_N / 2 + c * 32, ru);
-        ptx::tmem_ld_wait();
-        uint32_t w[16];
+        // two halves of 16 columns (register budget: 18 warps leave 96 registers per thread)
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          float y2[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int jj = 2 * j + e;
-            const float g = round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(rg[jj]), sa), sbs[c * 32 + jj]));
-            const float u = round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(ru[jj]), sa), sbs[BLOCK_N / 2 + c * 32 + jj]));
-            y2[e] = __fmul_rn(silu_bf16(g), u);
+        for (int half = 0; half < 2; ++half) {
+          const int col = c * 32 + half * 16;
+          uint4 o0, o1;
+          amax = fmaxf(amax, swiglu16(taddr_row + col, taddr_row + BLOCK_N / 2 + col, scale_b + n0 + col,
+                                      scale_b + n0 + BLOCK_N / 2 + col, sa, silu_table, o0, o1));
+          if (half == 0) {  // the previous tile's store must have read the staging tile; by now it has
+            if (lane == 0) ptx::bulk_wait_read<0>();
+            __syncwarp();
           }
-          w[j] = pack_bf16(y2[0], y2[1]);
-          amax = fmaxf(amax, fmaxf(fabsf(bf16lo(w[j])), fabsf(bf16hi(w[j]))));
+          // 64-byte swizzle: 16-byte chunk index ^ ((row >> 1) & 3)
+          *reinterpret_cast<uint4*>(st + lane * 64 + (((half * 2) ^ ((lane >> 1) & 3)) << 4)) = o0;
+          *reinterpret_cast<uint4*>(st + lane * 64 + (((half * 2 + 1) ^ ((lane >> 1) & 3)) << 4)) = o1;
         }
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch)  // 64-byte swizzle: 16-byte chunk index ^ ((row >> 1) & 3)
-          *reinterpret_cast<uint4*>(st + lane * 64 + ((ch ^ ((lane >> 1) & 3)) << 4)) =
-              make_uint4(w[4 * ch], w[4 * ch + 1], w[4 * ch + 2], w[4 * ch + 3]);
         ptx::fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0 && row_base < M) {
@@ -698,10 +731,12 @@ static int launch(const void* a, const void* b, const float* sa, const float* sb
   }
   int* status = device_status_ptr();
   if (!status) return FR_ERR_CUDA;
+  const uint16_t* table = EPI == 1 ? silu_table_ptr(stream) : nullptr;
+  if (EPI == 1 && !table) return FR_ERR_CUDA;
   const int tiles = ceil_div(M, kBlockM) * ceil_div(N, BLOCK_N);
   const int grid = tiles < sm_count() ? tiles : sm_count();
   kern<<<grid, EpiCfg<EPI>::kThreads, C::kSmemBytes, stream>>>(ta, tb, static_cast<OutT*>(out), ldo, sa, sb,
-                                                  static_cast<const __nv_bfloat16*>(bias), M, N, K, row_amax, status);
+                                                  static_cast<const __nv_bfloat16*>(bias), M, N, K, row_amax, table, status);
   return launch_status();
 }
 
@@ -728,6 +763,8 @@ static int launch_pair(const void* a, const void* b, const float* sa, const floa
   }
   int* status = device_status_ptr();
   if (!status) return FR_ERR_CUDA;
+  const uint16_t* table = EPI == 1 ? silu_table_ptr(stream) : nullptr;
+  if (EPI == 1 && !table) return FR_ERR_CUDA;
   const int tiles = ceil_div(M, 2 * kBlockM) * ceil_div(N, C::kBlockN);
   const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
   cudaLaunchConfig_t cfg = {};
@@ -743,7 +780,7 @@ static int launch_pair(const void* a, const void* b, const float* sa, const floa
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   if (cudaLaunchKernelEx(&cfg, kern, ta, tb, to, sa, sb, static_cast<const __nv_bfloat16*>(bias), M, N, K, row_amax,
-                         status) != cudaSuccess) {
+                         table, status) != cudaSuccess) {
     cudaGetLastError();
     return FR_ERR_CUDA;
   }
@@ -806,7 +843,7 @@ extern "C" int fr_gemm_fp8_silu_mul(const void* a, const void* b_interleaved, co
   if (M == 0) return FR_OK;
   FR_CHECK_ARG(a && b_interleaved && scale_a && scale_b_interleaved && y_out && row_amax);
   FR_CHECK_SUPPORTED(N % 256 == 0);
-  FR_CHECK_ARG(aligned16(a) && aligned16(b_interleaved) && aligned16(y_out));
+  FR_CHECK_ARG(aligned16(a) && aligned16(b_interleaved) && aligned16(y_out) && aligned16(scale_b_interleaved));
   FR_CHECK_ARG(lda >= K && ldb >= K && ldo >= N / 2 && lda % 16 == 0 && ldb % 16 == 0 && ldo % 8 == 0 && K % 16 == 0);
   if (mode == 2 || (mode == 0 && gemm::use_pair(M, N)))
     return gemm::launch_pair<__nv_bfloat16, 1>(a, b_interleaved, scale_a, scale_b_interleaved, nullptr, y_out, ldo, M,

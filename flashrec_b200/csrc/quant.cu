@@ -256,7 +256,7 @@ row_quant_f32_kernel(const float4* __restrict__ x, uint32_t* __restrict__ q, flo
 template <int NV, bool QUANT>
 __global__ void __launch_bounds__(kBlockRowThreads)
 silu_mul_kernel(const uint4* __restrict__ x, uint2* __restrict__ q, float* __restrict__ scale,
-                uint4* __restrict__ y_out, int d) {
+                uint4* __restrict__ y_out, int d, const uint16_t* __restrict__ silu_table) {
   __shared__ float red_f[kBlockRowThreads / 32];
   const int row = blockIdx.x;
   const int nvec = d >> 3;
@@ -281,7 +281,7 @@ silu_mul_kernel(const uint4* __restrict__ x, uint2* __restrict__ q, float* __res
     const uint32_t* uv = reinterpret_cast<const uint32_t*>(&u[j]);
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
-      yv[t] = silu_mul_pack(yv[t], uv[t]);
+      yv[t] = silu_mul_pack(yv[t], uv[t], silu_table);
       amax = fmaxf(amax, fmaxf(fabsf(bf16lo(yv[t])), fabsf(bf16hi(yv[t]))));
     }
     if constexpr (!QUANT) {
@@ -427,13 +427,15 @@ static int launch_silu(const void* x, void* q, float* scale, void* y, int rows, 
   uint2* qp = static_cast<uint2*>(q);
   uint4* yp = static_cast<uint4*>(y);
   const int nv = ceil_div(d >> 3, kBlockRowThreads);
+  const uint16_t* table = silu_table_ptr(stream);
+  if (!table) return FR_ERR_CUDA;
   switch (nv) {
-    case 1: silu_mul_kernel<1, QUANT><<<rows, kBlockRowThreads, 0, stream>>>(xp, qp, scale, yp, d); break;
-    case 2: silu_mul_kernel<2, QUANT><<<rows, kBlockRowThreads, 0, stream>>>(xp, qp, scale, yp, d); break;
-    case 3: silu_mul_kernel<3, QUANT><<<rows, kBlockRowThreads, 0, stream>>>(xp, qp, scale, yp, d); break;
-    case 4: silu_mul_kernel<4, QUANT><<<rows, kBlockRowThreads, 0, stream>>>(xp, qp, scale, yp, d); break;
-    case 5: case 6: silu_mul_kernel<6, QUANT><<<rows, kBlockRowThreads, 0, stream>>>(xp, qp, scale, yp, d); break;
-    case 7: case 8: silu_mul_kernel<8, QUANT><<<rows, kBlockRowThreads, 0, stream>>>(xp, qp, scale, yp, d); break;
+    case 1: silu_mul_kernel<1, QUANT><<<rows, kBlockRowThreads, 0, stream>>>(xp, qp, scale, yp, d, table); break;
+    case 2: silu_mul_kernel<2, QUANT><<<rows, kBlockRowThreads, 0, stream>>>(xp, qp, scale, yp, d, table); break;
+    case 3: silu_mul_kernel<3, QUANT><<<rows, kBlockRowThreads, 0, stream>>>(xp, qp, scale, yp, d, table); break;
+    case 4: silu_mul_kernel<4, QUANT><<<rows, kBlockRowThreads, 0, stream>>>(xp, qp, scale, yp, d, table); break;
+    case 5: case 6: silu_mul_kernel<6, QUANT><<<rows, kBlockRowThreads, 0, stream>>>(xp, qp, scale, yp, d, table); break;
+    case 7: case 8: silu_mul_kernel<8, QUANT><<<rows, kBlockRowThreads, 0, stream>>>(xp, qp, scale, yp, d, table); break;
     default: return FR_ERR_UNSUPPORTED;  // d > 16384
   }
   return launch_status();

@@ -225,3 +225,38 @@ def test_gemm_silu_epilogue_equals_unfused_bit_for_bit(m, d, k):
     # and against the CPU oracle of the unfused reference order
     qo, so = O.silu_mul_quant_fp8(gu.cpu())
     assert np.array_equal(bits8(q), bits8(qo)) and torch.equal(s.cpu(), so)
+
+
+@pytest.mark.parametrize("case", ["zero_rows", "wide_gates", "tiny_channel_scales", "huge_row_scales"])
+def test_gemm_silu_epilogue_corner_inputs(case):
+    """The SwiGLU epilogue keeps bit parity with GEMM -> SwiGLU where its shortcuts do not apply: all-zero
+    rows, gates far into both tails, and scales outside the range its FMA-pipe bf16 rounding covers."""
+    from flashrec_b200.kernel.sglops import fp8_scaled_mm, fp8_scaled_mm_silu_mul, interleave_gate_up, silu_and_mul
+
+    m, d, k = 300, 256, 512
+    g = torch.Generator().manual_seed(7)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    w = 0.05 * torch.randn(2 * d, k, generator=g)
+    if case == "zero_rows":
+        a[5:40] = 0
+        a[257:] = 0
+    if case == "wide_gates":
+        w = 2.0 * torch.randn(2 * d, k, generator=g)  # gate values of a few tens, both signs
+    aq, asc = O.per_token_quant_fp8(a)
+    wq, wsc = O.quantize_weight_fp8(w)
+    if case == "tiny_channel_scales":
+        wsc[::7] = 1e-30
+        wsc[3::11] = 1e-41  # subnormal scale: subnormal gate / up values
+    if case == "huge_row_scales":
+        asc[::5] = 3e30
+        wsc[::3] = 1e6
+    aq, asc, wq, wsc = aq.to(DEV), asc.to(DEV), wq.to(DEV), wsc.to(DEV)
+    gu = fp8_scaled_mm(aq, wq.t(), asc, wsc, torch.bfloat16, block_n=256)
+    ref = silu_and_mul(gu)
+    wi, si = interleave_gate_up(wq, wsc)
+    for mode in (1, 2):
+        y, amax = fp8_scaled_mm_silu_mul(aq, wi, asc, si, mode=mode)
+        assert np.array_equal(bits16(y), bits16(ref)), (case, mode)
+        finite = torch.isfinite(ref.float()).all(dim=1)
+        want = ref.float().abs().amax(dim=1)
+        assert torch.equal(amax.flatten()[finite], want[finite]), (case, mode)
