@@ -81,6 +81,22 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// a + b on two packed bf16 pairs, each sum rounded once to bf16. Equal to the fp32 sum rounded to
+// bf16: the fp32 sum of two bf16 values is exact unless their exponents differ by more than 16,
+// and then either rounding returns the larger operand.
+__device__ __forceinline__ uint32_t add_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+// max(acc, |x|) on two packed bf16 lanes (acc >= 0 in both lanes). A NaN lane of x is ignored, as fmaxf does.
+__device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t acc, uint32_t x) {
+  uint32_t d;
+  asm("max.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(acc), "r"(x & 0x7fff7fffu));
+  return d;
+}
+
 // Two fp32 -> two e4m3 bytes (round to nearest even, saturating). `lo` lands in
 // the low byte.
 __device__ __forceinline__ uint16_t pack_e4m3x2(float lo, float hi) {
@@ -97,17 +113,20 @@ __device__ __forceinline__ float quant_div(float y, float scale) {
   return fminf(fmaxf(q, -kFp8Max), kFp8Max);
 }
 
-// Same value as quant_div(y, scale) AFTER the e4m3 cast, at the cost of one
-// multiply: q ~= y * inv (inv = 1 / scale, correctly rounded) is within 2 fp32 ulp
-// of the IEEE quotient, so both round to the same e4m3 byte unless q lies within
-// a few ulp of an e4m3 rounding midpoint (20 low mantissa bits == 0x80000) or in
-// the e4m3 subnormal range; only those (about 1 in 10^4) take the true division.
-__device__ __forceinline__ float quant_div_fast(float y, float scale, float inv) {
-  float q = __fmul_rn(y, inv);
-  const uint32_t low = __float_as_uint(q) & 0xfffffu;
-  const bool hard = (low - (0x80000u - 8u) <= 16u) || !(fabsf(q) >= 0.015625f);
-  if (hard) q = __fdiv_rn(y, scale);
-  return q;  // |q| <= 448 (1 + 2^-22); the saturating e4m3 conversion does the clamp
+// The correctly rounded fp32 quotient y / scale without a division and without a branch:
+// q0 = y * inv (inv = the correctly rounded 1 / scale), the exact remainder r = y - q0 * scale
+// from one FMA, and q0 + r * inv rounded once (Markstein's correction step) equals the IEEE
+// quotient. `scale_or_zero` is the scale, or 0 when the scale is not finite (a row that holds an
+// infinity): inv is 0 there and the sequence then returns 0 for finite y and NaN for infinite y,
+// as the division would. |q| <= 448 (1 + 2^-22) for |y| <= amax: the saturating e4m3 conversion
+// does the clamp. The sign is taken from y at the end (the scale is positive): the correction
+// step alone would turn the quotient of y = -0 into +0, which is a different e4m3 byte.
+__device__ __forceinline__ float finite_or_zero(float s) { return s <= 3.402823466e38f ? s : 0.f; }
+__device__ __forceinline__ float quant_div_fast(float y, float scale_or_zero, float inv) {
+  const float q0 = __fmul_rn(y, inv);
+  const float r = __fmaf_rn(-q0, scale_or_zero, y);
+  const float q1 = __fmaf_rn(r, inv, q0);
+  return __uint_as_float((__float_as_uint(q1) & 0x7fffffffu) | (__float_as_uint(y) & 0x80000000u));
 }
 
 // scale = max(amax, 1e-12) / 448 in fp32.

@@ -50,10 +50,7 @@ row_warp_kernel(const uint4* __restrict__ x, uint4* __restrict__ resid, const ui
       uint32_t* xv = reinterpret_cast<uint32_t*>(&v[j]);
       const uint32_t* rv = reinterpret_cast<const uint32_t*>(&r[j]);
 #pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        // residual + x in bf16: fp32 add, one rounding to bf16
-        xv[t] = pack_bf16(__fadd_rn(bf16lo(rv[t]), bf16lo(xv[t])), __fadd_rn(bf16hi(rv[t]), bf16hi(xv[t])));
-      }
+      for (int t = 0; t < 4; ++t) xv[t] = add_bf16x2(rv[t], xv[t]);  // residual + x, rounded to bf16
     }
 #pragma unroll
     for (int j = 0; j < VPL; ++j) rr[j * 32 + lane] = v[j];
@@ -67,9 +64,9 @@ row_warp_kernel(const uint4* __restrict__ x, uint4* __restrict__ resid, const ui
       const uint32_t* xv = reinterpret_cast<const uint32_t*>(&v[j]);
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
-        float a = bf16lo(xv[t]), b = bf16hi(xv[t]);
-        ss += static_cast<double>(a * a);  // exact in fp32: 8-bit significands
-        ss += static_cast<double>(b * b);
+        const double a = static_cast<double>(bf16lo(xv[t])), b = static_cast<double>(bf16hi(xv[t]));
+        ss = fma(a, a, ss);  // the squares are exact (8-bit significands)
+        ss = fma(b, b, ss);
       }
     }
     ss = warp_sum(ss);
@@ -95,24 +92,26 @@ row_warp_kernel(const uint4* __restrict__ x, uint4* __restrict__ resid, const ui
     for (int j = 0; j < VPL; ++j) yr[j * 32 + lane] = v[j];
     return;
   } else {
+    uint32_t am2 = 0;  // running max |.| of both bf16 lanes
 #pragma unroll
     for (int j = 0; j < VPL; ++j) {
       const uint32_t* xv = reinterpret_cast<const uint32_t*>(&v[j]);
 #pragma unroll
-      for (int t = 0; t < 4; ++t) amax = fmaxf(amax, fmaxf(fabsf(bf16lo(xv[t])), fabsf(bf16hi(xv[t]))));
+      for (int t = 0; t < 4; ++t) am2 = absmax_bf16x2(am2, xv[t]);
     }
-    amax = warp_max(amax);
+    amax = warp_max(fmaxf(bf16lo(am2), bf16hi(am2)));
     const float s = row_scale(amax);
     const float inv = __fdiv_rn(1.0f, s);
+    const float sf = finite_or_zero(s);
     uint2* qr = q + static_cast<size_t>(row) * kVecPerRow;
 #pragma unroll
     for (int j = 0; j < VPL; ++j) {
       const uint32_t* xv = reinterpret_cast<const uint32_t*>(&v[j]);
       uint2 o;
-      o.x = pack_e4m3x4(quant_div_fast(bf16lo(xv[0]), s, inv), quant_div_fast(bf16hi(xv[0]), s, inv), quant_div_fast(bf16lo(xv[1]), s, inv),
-                        quant_div_fast(bf16hi(xv[1]), s, inv));
-      o.y = pack_e4m3x4(quant_div_fast(bf16lo(xv[2]), s, inv), quant_div_fast(bf16hi(xv[2]), s, inv), quant_div_fast(bf16lo(xv[3]), s, inv),
-                        quant_div_fast(bf16hi(xv[3]), s, inv));
+      o.x = pack_e4m3x4(quant_div_fast(bf16lo(xv[0]), sf, inv), quant_div_fast(bf16hi(xv[0]), sf, inv), quant_div_fast(bf16lo(xv[1]), sf, inv),
+                        quant_div_fast(bf16hi(xv[1]), sf, inv));
+      o.y = pack_e4m3x4(quant_div_fast(bf16lo(xv[2]), sf, inv), quant_div_fast(bf16hi(xv[2]), sf, inv), quant_div_fast(bf16lo(xv[3]), sf, inv),
+                        quant_div_fast(bf16hi(xv[3]), sf, inv));
       qr[j * 32 + lane] = o;
     }
     if (lane == 0) scale[row] = s;
@@ -212,15 +211,16 @@ row_block_kernel(const uint4* __restrict__ x, uint4* __restrict__ resid, const u
     amax = block_max(amax, red_f);
     const float s = row_scale(amax);
     const float inv = __fdiv_rn(1.0f, s);
+    const float sf = finite_or_zero(s);
     uint2* qr = q + static_cast<size_t>(row) * nvec;
     for (int i = threadIdx.x; i < nvec; i += kBlockRowThreads) {
       uint4 v = row_smem[i];
       const uint32_t* xv = reinterpret_cast<const uint32_t*>(&v);
       uint2 o;
-      o.x = pack_e4m3x4(quant_div_fast(bf16lo(xv[0]), s, inv), quant_div_fast(bf16hi(xv[0]), s, inv), quant_div_fast(bf16lo(xv[1]), s, inv),
-                        quant_div_fast(bf16hi(xv[1]), s, inv));
-      o.y = pack_e4m3x4(quant_div_fast(bf16lo(xv[2]), s, inv), quant_div_fast(bf16hi(xv[2]), s, inv), quant_div_fast(bf16lo(xv[3]), s, inv),
-                        quant_div_fast(bf16hi(xv[3]), s, inv));
+      o.x = pack_e4m3x4(quant_div_fast(bf16lo(xv[0]), sf, inv), quant_div_fast(bf16hi(xv[0]), sf, inv), quant_div_fast(bf16lo(xv[1]), sf, inv),
+                        quant_div_fast(bf16hi(xv[1]), sf, inv));
+      o.y = pack_e4m3x4(quant_div_fast(bf16lo(xv[2]), sf, inv), quant_div_fast(bf16hi(xv[2]), sf, inv), quant_div_fast(bf16lo(xv[3]), sf, inv),
+                        quant_div_fast(bf16hi(xv[3]), sf, inv));
       qr[i] = o;
     }
     if (threadIdx.x == 0) scale[row] = s;
@@ -242,10 +242,11 @@ row_quant_f32_kernel(const float4* __restrict__ x, uint32_t* __restrict__ q, flo
   amax = block_max(amax, red_f);
   const float s = row_scale(amax);
     const float inv = __fdiv_rn(1.0f, s);
+    const float sf = finite_or_zero(s);
   uint32_t* qr = q + static_cast<size_t>(row) * nvec;
   for (int i = threadIdx.x; i < nvec; i += kBlockRowThreads) {
     float4 v = __ldg(xr + i);
-    qr[i] = pack_e4m3x4(quant_div_fast(v.x, s, inv), quant_div_fast(v.y, s, inv), quant_div_fast(v.z, s, inv), quant_div_fast(v.w, s, inv));
+    qr[i] = pack_e4m3x4(quant_div_fast(v.x, sf, inv), quant_div_fast(v.y, sf, inv), quant_div_fast(v.z, sf, inv), quant_div_fast(v.w, sf, inv));
   }
   if (threadIdx.x == 0) scale[row] = s;
 }
@@ -293,6 +294,7 @@ silu_mul_kernel(const uint4* __restrict__ x, uint2* __restrict__ q, float* __res
     amax = block_max(amax, red_f);
     const float s = row_scale(amax);
     const float inv = __fdiv_rn(1.0f, s);
+    const float sf = finite_or_zero(s);
     uint2* qr = q + static_cast<size_t>(row) * nvec;
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
@@ -300,10 +302,10 @@ silu_mul_kernel(const uint4* __restrict__ x, uint2* __restrict__ q, float* __res
       if (i < nvec) {
         const uint32_t* xv = reinterpret_cast<const uint32_t*>(&g[j]);
         uint2 o;
-        o.x = pack_e4m3x4(quant_div_fast(bf16lo(xv[0]), s, inv), quant_div_fast(bf16hi(xv[0]), s, inv),
-                          quant_div_fast(bf16lo(xv[1]), s, inv), quant_div_fast(bf16hi(xv[1]), s, inv));
-        o.y = pack_e4m3x4(quant_div_fast(bf16lo(xv[2]), s, inv), quant_div_fast(bf16hi(xv[2]), s, inv),
-                          quant_div_fast(bf16lo(xv[3]), s, inv), quant_div_fast(bf16hi(xv[3]), s, inv));
+        o.x = pack_e4m3x4(quant_div_fast(bf16lo(xv[0]), sf, inv), quant_div_fast(bf16hi(xv[0]), sf, inv),
+                          quant_div_fast(bf16lo(xv[1]), sf, inv), quant_div_fast(bf16hi(xv[1]), sf, inv));
+        o.y = pack_e4m3x4(quant_div_fast(bf16lo(xv[2]), sf, inv), quant_div_fast(bf16hi(xv[2]), sf, inv),
+                          quant_div_fast(bf16lo(xv[3]), sf, inv), quant_div_fast(bf16hi(xv[3]), sf, inv));
         qr[i] = o;
       }
     }
@@ -328,6 +330,7 @@ quant_known_amax_kernel(const uint4* __restrict__ y, const float* __restrict__ r
   }
   const float s = row_scale(__ldg(row_amax + row));
   const float inv = __fdiv_rn(1.0f, s);
+  const float sf = finite_or_zero(s);
   uint2* qr = q + static_cast<size_t>(row) * vec_per_row;
 #pragma unroll
   for (int j = 0; j < NV; ++j) {
@@ -335,10 +338,10 @@ quant_known_amax_kernel(const uint4* __restrict__ y, const float* __restrict__ r
     if (i < vec_per_row) {
       const uint32_t xv[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
       uint2 o;
-      o.x = pack_e4m3x4(quant_div_fast(bf16lo(xv[0]), s, inv), quant_div_fast(bf16hi(xv[0]), s, inv),
-                        quant_div_fast(bf16lo(xv[1]), s, inv), quant_div_fast(bf16hi(xv[1]), s, inv));
-      o.y = pack_e4m3x4(quant_div_fast(bf16lo(xv[2]), s, inv), quant_div_fast(bf16hi(xv[2]), s, inv),
-                        quant_div_fast(bf16lo(xv[3]), s, inv), quant_div_fast(bf16hi(xv[3]), s, inv));
+      o.x = pack_e4m3x4(quant_div_fast(bf16lo(xv[0]), sf, inv), quant_div_fast(bf16hi(xv[0]), sf, inv),
+                        quant_div_fast(bf16lo(xv[1]), sf, inv), quant_div_fast(bf16hi(xv[1]), sf, inv));
+      o.y = pack_e4m3x4(quant_div_fast(bf16lo(xv[2]), sf, inv), quant_div_fast(bf16hi(xv[2]), sf, inv),
+                        quant_div_fast(bf16lo(xv[3]), sf, inv), quant_div_fast(bf16hi(xv[3]), sf, inv));
       qr[i] = o;
     }
   }

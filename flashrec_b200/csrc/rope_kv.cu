@@ -81,16 +81,23 @@ __global__ void __launch_bounds__(256) qk_rope_kv_kernel(RopeArgs a) {
       load4(src0 + j * hstride + HALF + 4 * sub, hi[j]);
     }
   }
+  // sums of squares only where some lane of the warp normalises (Q / K heads); the decision is
+  // warp-uniform because all 32 lanes execute the shuffles
   double ss[HPG];
+  const bool any_norm = ROPE && __any_sync(0xffffffffu, live && (is_q || is_k));
 #pragma unroll
   for (int j = 0; j < HPG; ++j) {
-    double acc = 0.0;
+    ss[j] = 0.0;
+    if (any_norm) {
+      double acc = 0.0;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      acc += static_cast<double>(lo[j][i] * lo[j][i]);
-      acc += static_cast<double>(hi[j][i] * hi[j][i]);
+      for (int i = 0; i < 4; ++i) {
+        const double l = static_cast<double>(lo[j][i]), h = static_cast<double>(hi[j][i]);
+        acc = fma(l, l, acc);  // the squares are exact (8-bit significands)
+        acc = fma(h, h, acc);
+      }
+      ss[j] = group_sum<LPH>(acc);
     }
-    ss[j] = group_sum<LPH>(acc);  // all 32 lanes execute the shuffles
   }
   if (!live) return;
 
