@@ -59,11 +59,36 @@ struct Params {
   __nv_bfloat16* out;
   int64_t o_t;
   __nv_bfloat16* kb;  // [groups, hkv, lcap, 128]
-  __nv_bfloat16* vt;  // [groups, hkv, 128, lcap]
+  __half* vt;         // [groups, hkv, 128, lcap], fp16 (e4m3 values are exact in fp16)
   int lcap;
   int n_rows, n_groups, hq, hkv, num_slots;
   float scale_log2;
 };
+
+__device__ __forceinline__ __half2 e4m3x2_to_half2(uint16_t v) {
+  __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(v), __NV_E4M3);
+  return *reinterpret_cast<__half2*>(&h);
+}
+
+// exp2 of two fp32 arguments, evaluated as one packed fp16 operation: {2^lo, 2^hi} as an fp16 pair
+// (lo in the low half). The arguments are at most the rescale threshold, so 2^x <= 256; arguments
+// below -16 lose relative accuracy but their terms are below 2^-16 of the row maximum.
+__device__ __forceinline__ uint32_t ex2_f16x2(float lo, float hi) {
+  uint32_t packed, r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(hi), "f"(lo));
+  asm("ex2.approx.f16x2 %0, %1;" : "=r"(r) : "r"(packed));
+  return r;
+}
+__device__ __forceinline__ uint32_t add_f16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ float sum_f16x2(uint32_t v) {
+  const __half2 h = *reinterpret_cast<const __half2*>(&v);
+  const float2 f = __half22float2(h);
+  return f.x + f.y;
+}
 
 __device__ __forceinline__ float2 e4m3x2_to_float2(uint16_t v) {
   __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(v), __NV_E4M3);
@@ -83,7 +108,7 @@ __global__ void __launch_bounds__(256) shared_kv_prepare_kernel(Params p) {
   const int32_t* idx = p.indices + p.indptr[row0];
   const size_t gh = static_cast<size_t>(grp) * p.hkv + kvh;
   __nv_bfloat16* kb = p.kb + gh * p.lcap * kD;
-  __nv_bfloat16* vt = p.vt + gh * kD * p.lcap;
+  __half* vt = p.vt + gh * kD * p.lcap;
   // 32 tokens x 8 chunks of 16 dims; token fastest across lanes so that the
   // transposed V stores of a warp hit consecutive addresses
   const int tok = tok0 + (threadIdx.x & 31);
@@ -111,13 +136,13 @@ __global__ void __launch_bounds__(256) shared_kv_prepare_kernel(Params p) {
   kdst[1] = make_uint4(ko[4], ko[5], ko[6], ko[7]);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const float2 a = e4m3x2_to_float2(static_cast<uint16_t>(vw[i] & 0xffffu));
-    const float2 b = e4m3x2_to_float2(static_cast<uint16_t>(vw[i] >> 16));
+    const __half2 a = e4m3x2_to_half2(static_cast<uint16_t>(vw[i] & 0xffffu));
+    const __half2 b = e4m3x2_to_half2(static_cast<uint16_t>(vw[i] >> 16));
     const int d = ch * 16 + 4 * i;
-    vt[static_cast<size_t>(d + 0) * p.lcap + tok] = __float2bfloat16_rn(a.x);
-    vt[static_cast<size_t>(d + 1) * p.lcap + tok] = __float2bfloat16_rn(a.y);
-    vt[static_cast<size_t>(d + 2) * p.lcap + tok] = __float2bfloat16_rn(b.x);
-    vt[static_cast<size_t>(d + 3) * p.lcap + tok] = __float2bfloat16_rn(b.y);
+    vt[static_cast<size_t>(d + 0) * p.lcap + tok] = __low2half(a);
+    vt[static_cast<size_t>(d + 1) * p.lcap + tok] = __high2half(a);
+    vt[static_cast<size_t>(d + 2) * p.lcap + tok] = __low2half(b);
+    vt[static_cast<size_t>(d + 3) * p.lcap + tok] = __high2half(b);
   }
 }
 
@@ -224,7 +249,7 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     // ------------------------------ MMA issuer -----------------------------
     if (lane == 0 && n_tiles > 0) {
       constexpr uint32_t idesc_s = ptx::make_idesc(1u, 1u, kM, kTileN);  // bf16 x bf16, N = 64 tokens
-      constexpr uint32_t idesc_o = ptx::make_idesc(1u, 1u, kM, kD);      // N = 128 dims
+      constexpr uint32_t idesc_o = ptx::make_idesc(0u, 0u, kM, kD);      // fp16 x fp16, N = 128 dims
       bool ok = ptx::mbar_wait(bar_q, 0, abort_flag, status, 13);
       // S = Q K^T for tile jj into TMEM buffer (jj & 1): 2 k-blocks (64 dims) x 4 instructions of K = 16
       auto issue_s = [&](int jj) -> bool {
@@ -330,23 +355,23 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         }
         ptx::tmem_st_wait();
       }
-      // P = exp2(S - m) as bf16 pairs, written over the first 32 columns of this tile's S buffer
+      // P is written as fp16 pairs over the first 32 columns of this tile's S buffer
       // (S has just been read into registers; the next S for this buffer is issued after this P.V)
-      // exp2(s * scale - m): one FMA and one ex2.approx per score (the argument is at most the
-      // rescale threshold, far from overflow; -inf gives 0), sums on four independent chains
-      float ps[4] = {0.f, 0.f, 0.f, 0.f};
+      // P = exp2(s * scale - m) as fp16 pairs: one FMA per score, one conversion and one packed
+      // ex2.approx per pair; the row sum runs on four packed fp16 chains of 8 terms each (terms
+      // <= 256, relative error of the sum below 2^-10) and is widened to fp32 per tile
+      uint32_t ps[4] = {0u, 0u, 0u, 0u};
       uint32_t w[32];
       const float neg_m = -m_used;
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
         const int c = 2 * i;  // token index within the tile
-        const float a = ex2_approx(__fmaf_rn(__uint_as_float(c < 32 ? s0[c & 31] : s1[c & 31]), p.scale_log2, neg_m));
-        const float b =
-            ex2_approx(__fmaf_rn(__uint_as_float(c + 1 < 32 ? s0[(c + 1) & 31] : s1[(c + 1) & 31]), p.scale_log2, neg_m));
-        w[i] = pack_bf16(a, b);
-        ps[i & 3] += a + b;
+        const float a = __fmaf_rn(__uint_as_float(c < 32 ? s0[c & 31] : s1[c & 31]), p.scale_log2, neg_m);
+        const float b = __fmaf_rn(__uint_as_float(c + 1 < 32 ? s0[(c + 1) & 31] : s1[(c + 1) & 31]), p.scale_log2, neg_m);
+        w[i] = ex2_f16x2(a, b);
+        ps[i & 3] = add_f16x2(ps[i & 3], w[i]);
       }
-      const float psum = (ps[0] + ps[1]) + (ps[2] + ps[3]);
+      const float psum = (sum_f16x2(ps[0]) + sum_f16x2(ps[1])) + (sum_f16x2(ps[2]) + sum_f16x2(ps[3]));
       l_sum += psum;
       ptx::tmem_st_32x32(t_lane + kColS + (j & 1) * kTileN, w);
       ptx::tmem_st_wait();
@@ -530,14 +555,14 @@ static EncodeTiledFn encode_fn() {
 
 // bf16 3-D tensor, 128-byte swizzle; dims / box innermost first; strides in bytes for dims 1 and 2.
 static int make_tmap_bf16_3d(CUtensorMap* map, const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1,
-                             uint64_t s2, uint32_t b0, uint32_t b1, uint32_t b2) {
+                             uint64_t s2, uint32_t b0, uint32_t b1, uint32_t b2, bool fp16 = false) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return FR_ERR_CUDA;
   cuuint64_t dims[3] = {d0, d1, d2};
   cuuint64_t strides[2] = {s1, s2};
   cuuint32_t box[3] = {b0, b1, b2};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+  CUresult r = fn(map, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? FR_OK : FR_ERR_CUDA;
@@ -553,7 +578,7 @@ static int launch(const Params& p, int max_group_rows, cudaStream_t stream) {
   st = make_tmap_bf16_3d(&tk, p.kb, kD, p.lcap, gh, kD * 2, static_cast<uint64_t>(p.lcap) * kD * 2, 64, kTileN, 1);
   if (st != FR_OK) return st;
   st = make_tmap_bf16_3d(&tv, p.vt, p.lcap, kD, gh, static_cast<uint64_t>(p.lcap) * 2,
-                         static_cast<uint64_t>(p.lcap) * kD * 2, kTileN, kD, 1);
+                         static_cast<uint64_t>(p.lcap) * kD * 2, kTileN, kD, 1, true);
   if (st != FR_OK) return st;
   auto kern = decode_attn_tc_kernel<G>;
   static bool attr_done = false;
@@ -590,7 +615,7 @@ int decode_attn_tc(const void* q, int64_t q_t, int64_t q_h, const void* k_cache,
                     hkv, num_slots, sm_scale * 1.4426950408889634f};
   const size_t half = static_cast<size_t>(n_groups) * hkv * lcap * attn_tc::kD;
   p.kb = static_cast<__nv_bfloat16*>(scratch);
-  p.vt = p.kb + half;
+  p.vt = reinterpret_cast<__half*>(p.kb + half);
   switch (G) {
     case 1: return attn_tc::launch<1>(p, max_group_rows, stream);
     case 2: return attn_tc::launch<2>(p, max_group_rows, stream);

@@ -71,6 +71,12 @@ __global__ void __launch_bounds__(256) qk_rope_kv_kernel(RopeArgs a) {
   const __nv_bfloat16* src0 = is_q ? (a.q + t * a.q_t + h0 * a.q_h)
                                    : (is_k ? (a.k + t * a.k_t + h0 * a.k_h) : (a.v + t * a.v_t + h0 * a.v_h));
   const int64_t hstride = is_q ? a.q_h : (is_k ? a.k_h : a.v_h);
+  const bool rotate = ROPE && (is_q || is_k);
+  // The position / slot lookups and the cos / sin row they lead to are independent of the head
+  // data: issue them first so that their two dependent round trips overlap the loads of the heads.
+  int64_t p = 0, slot = 0;
+  if (live && rotate) p = __ldg(a.pos + t);
+  if (live && !is_q) slot = __ldg(a.loc + t);
   float lo[HPG][4], hi[HPG][4];
 #pragma unroll
   for (int j = 0; j < HPG; ++j) {
@@ -80,6 +86,18 @@ __global__ void __launch_bounds__(256) qk_rope_kv_kernel(RopeArgs a) {
       load4(src0 + j * hstride + 4 * sub, lo[j]);
       load4(src0 + j * hstride + HALF + 4 * sub, hi[j]);
     }
+  }
+  float cosv[4] = {1.f, 1.f, 1.f, 1.f}, sinv[4] = {0.f, 0.f, 0.f, 0.f};
+  float wlo[4] = {0.f, 0.f, 0.f, 0.f}, whi[4] = {0.f, 0.f, 0.f, 0.f};
+  if (live && rotate) {
+    p = p < 0 ? 0 : (p >= a.max_pos ? a.max_pos - 1 : p);
+    const float4 c4 = __ldg(reinterpret_cast<const float4*>(a.cs + p * D + 4 * sub));
+    const float4 s4 = __ldg(reinterpret_cast<const float4*>(a.cs + p * D + HALF + 4 * sub));
+    cosv[0] = c4.x; cosv[1] = c4.y; cosv[2] = c4.z; cosv[3] = c4.w;
+    sinv[0] = s4.x; sinv[1] = s4.y; sinv[2] = s4.z; sinv[3] = s4.w;
+    const __nv_bfloat16* wsrc = is_q ? a.qw : a.kw;
+    load4(wsrc + 4 * sub, wlo);
+    load4(wsrc + HALF + 4 * sub, whi);
   }
   // sums of squares only where some lane of the warp normalises (Q / K heads); the decision is
   // warp-uniform because all 32 lanes execute the shuffles
@@ -100,28 +118,8 @@ __global__ void __launch_bounds__(256) qk_rope_kv_kernel(RopeArgs a) {
     }
   }
   if (!live) return;
-
-  int64_t slot = 0;
-  if (!is_q) {
-    slot = a.loc[t];
-    if (slot < 0 || slot >= a.num_slots) return;  // never write outside the pool
-  }
-
-  float cosv[4] = {1.f, 1.f, 1.f, 1.f}, sinv[4] = {0.f, 0.f, 0.f, 0.f}, wlo[4], whi[4];
-  const bool rotate = ROPE && (is_q || is_k);
-  if (rotate) {
-    int64_t p = a.pos[t];
-    p = p < 0 ? 0 : (p >= a.max_pos ? a.max_pos - 1 : p);
-    const float4 c4 = *reinterpret_cast<const float4*>(a.cs + p * D + 4 * sub);
-    const float4 s4 = *reinterpret_cast<const float4*>(a.cs + p * D + HALF + 4 * sub);
-    cosv[0] = c4.x; cosv[1] = c4.y; cosv[2] = c4.z; cosv[3] = c4.w;
-    sinv[0] = s4.x; sinv[1] = s4.y; sinv[2] = s4.z; sinv[3] = s4.w;
-    const __nv_bfloat16* wsrc = is_q ? a.qw : a.kw;
-    load4(wsrc + 4 * sub, wlo);
-    load4(wsrc + HALF + 4 * sub, whi);
-  } else if (is_q) {
-    return;  // ROPE == false never has Q work
-  }
+  if (!is_q && (slot < 0 || slot >= a.num_slots)) return;  // never write outside the pool
+  if (!ROPE && is_q) return;                               // plain KV store never has Q work
 #pragma unroll
   for (int j = 0; j < HPG; ++j) {
     if (rotate) {
