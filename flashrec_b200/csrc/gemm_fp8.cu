@@ -323,10 +323,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 // hands back the 16 bf16 results as two 16-byte pieces. Branch-free (inputs whose fast silu
 // cannot be trusted take a predicated table load), so the 16 instruction chains interleave.
 // sbg / sbu: the 16 per-channel scales of the gate / up columns in global memory (16-byte
-// aligned; every thread reads the same addresses, so they come from L1).
+// aligned; every thread reads the same addresses, so they come from L1). release_bar: 0, or the
+// cluster address of the barrier to arrive on once the accumulator columns are in registers.
 __device__ __forceinline__ float swiglu16(uint32_t taddr_g, uint32_t taddr_u, const float* __restrict__ sbg,
                                           const float* __restrict__ sbu, float sa,
-                                          const uint16_t* __restrict__ silu_table, uint4& out0, uint4& out1) {
+                                          const uint16_t* __restrict__ silu_table, uint32_t release_bar, uint4& out0,
+                                          uint4& out1) {
   uint32_t rg[16], ru[16];
   ptx::tmem_ld_32x16(taddr_g, rg);
   ptx::tmem_ld_32x16(taddr_u, ru);
@@ -339,6 +341,11 @@ __device__ __forceinline__ float swiglu16(uint32_t taddr_g, uint32_t taddr_u, co
     su[4 * q] = b.x, su[4 * q + 1] = b.y, su[4 * q + 2] = b.z, su[4 * q + 3] = b.w;
   }
   ptx::tmem_ld_wait();
+  if (release_bar != 0u) {  // last read of this accumulator buffer by this warp: hand it back now
+    ptx::tc_fence_before();
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) ptx::mbar_arrive_cluster(release_bar);
+  }
   uint32_t w[8];
   float amax = 0.f;
 #pragma unroll
@@ -541,6 +548,10 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BLOCK_N;
       const int ewarp = warp - 2;
       const int row_base = m0 + quad * 32;  // first output row of this warp
+      // The accumulator buffer goes back to the MMA warp as soon as its last column is in
+      // registers, before any store or atomic of this tile is issued: the arrive has release
+      // semantics and would otherwise wait for those to complete.
+      const uint32_t tempty_remote = ptx::mapa(bar_tempty + 8 * buf, 0);
       if constexpr (EPI == 0) {
         // chunk = 128 bytes of output per row (64 bf16 or 32 f32 columns); two staging tiles per warp
         constexpr int kChunkCols = 128 / static_cast<int>(sizeof(OutT));
@@ -571,6 +582,11 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                 w[h * 16 + j] = pack_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
             }
           }
+          if (c == BLOCK_N / kChunkCols - 1) {
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(tempty_remote);
+          }
           if (lane == 0) ptx::bulk_wait_read<1>();  // the store that last used this staging tile has read it
           __syncwarp();
 #pragma unroll
@@ -595,7 +611,8 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           const int col = c * 32 + half * 16;
           uint4 o0, o1;
           amax = fmaxf(amax, swiglu16(taddr_row + col, taddr_row + BLOCK_N / 2 + col, scale_b + n0 + col,
-                                      scale_b + n0 + BLOCK_N / 2 + col, sa, silu_table, o0, o1));
+                                      scale_b + n0 + BLOCK_N / 2 + col, sa, silu_table,
+                                      half == 1 ? tempty_remote : 0u, o0, o1));
           if (half == 0) {  // the previous tile's store must have read the staging tile; by now it has
             if (lane == 0) ptx::bulk_wait_read<0>();
             __syncwarp();
@@ -612,9 +629,6 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         }
         if (row < M) atomicMax(row_amax + row, __float_as_uint(amax));
       }
-      ptx::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa(bar_tempty + 8 * buf, 0));
     }
   }
 
