@@ -10,7 +10,7 @@ Metric: beam rows decoded per second (rows x levels / time), whole job.
   value  device-timed (CUDA events), inputs resident in HBM, CUDA-graph replay
   e2e    same wave driven from pinned host buffers: per-step slot ids copied
          host->device, final beams (scores + SID tokens) copied device->host
-  roofline      the FP8 GEMM (dominant kernel), timed alone in this process
+  roofline      the gate_up FP8 GEMM with the SwiGLU epilogue (dominant kernel), timed alone
   cpu_baseline  the CPU oracle port of the same ops on a bounded sample
 
 With --gpus N > 1 (launched by torch.distributed.run) every rank runs its own
@@ -204,9 +204,12 @@ def run_reference_arm(args):
 
 # ---------------------------------------------------------------------------
 def time_gemms(torch, rows: int, iters: int = 10):
-    """FP8 GEMM roofline: the four linear-layer shapes of one decoder layer at the
-    wave's row count, timed back to back with CUDA events on the launch stream."""
-    from flashrec_b200.kernel.sglops import fp8_scaled_mm
+    """FP8 GEMM roofline figures, timed alone with CUDA events on the launch stream:
+    (a) the dominant kernel of the wave, the gate_up GEMM with the SwiGLU epilogue, at the
+    wave's row count; (b) the four linear-layer shapes of one decoder layer back to back
+    (plain GEMMs), with cuBLASLt on the same shapes beside it. Between timed launches of (a)
+    a 256 MB buffer is rewritten, so its operands come from HBM, not from L2."""
+    from flashrec_b200.kernel.sglops import fp8_scaled_mm, fp8_scaled_mm_silu_mul, interleave_gate_up
 
     dev = torch.device("cuda", torch.cuda.current_device())
     shapes = [("qkv", 4096, 2048), ("o", 2048, 2048), ("gate_up", 12288, 2048), ("down", 2048, 6144)]
@@ -214,14 +217,33 @@ def time_gemms(torch, rows: int, iters: int = 10):
     for name, n, k in shapes:
         a = torch.randn(rows, k, device=dev).to(torch.float8_e4m3fn)
         b = torch.randn(n, k, device=dev).to(torch.float8_e4m3fn)
-        sa = torch.rand(rows, 1, device=dev) + 0.5
+        sa = (torch.rand(rows, 1, device=dev) + 0.5) / 45.0  # gate / up values of order 1
         sb = torch.rand(n, device=dev) + 0.5
         ops.append((a, b, sa, sb))
         flops += 2.0 * rows * n * k
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # (a) dominant kernel
+    a, b, sa, sb = ops[2]
+    wi, si = interleave_gate_up(b, sb)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for _ in range(3):
+        fp8_scaled_mm_silu_mul(a, wi, sa, si)
+    torch.cuda.synchronize()
+    fused_ms = []
+    for _ in range(iters):
+        flush.zero_()
+        e0.record()
+        fp8_scaled_mm_silu_mul(a, wi, sa, si)
+        e1.record()
+        torch.cuda.synchronize()
+        fused_ms.append(e0.elapsed_time(e1))
+    fused_sec = sum(fused_ms) / len(fused_ms) / 1e3
+    fused_flops = 2.0 * rows * 12288 * 2048
+    del flush, wi, si
+    # (b) the four layer shapes
     for a, b, sa, sb in ops:  # warm-up
         fp8_scaled_mm(a, b.t(), sa, sb, torch.bfloat16)
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(iters):
         for a, b, sa, sb in ops:
@@ -245,7 +267,7 @@ def time_gemms(torch, rows: int, iters: int = 10):
         del one
     except Exception:
         lib = None
-    return flops, sec, lib
+    return fused_flops, fused_sec, flops, sec, lib
 
 
 def profile_kernels(rows: int):
@@ -418,20 +440,29 @@ def main():
 
     line = None
     if rank == 0:
-        flops, gsec, lib_tf = time_gemms(torch, eng.rows)
+        fused_flops, fused_sec, flops, gsec, lib_tf = time_gemms(torch, eng.rows)
         peaks = {}
         pk = ROOT / "MEASURED_PEAKS.json"
         if pk.exists():
             peaks = json.loads(pk.read_text())
         bf16_burst = float(peaks.get("bf16_tflops", 1590.0))
         peak_fp8 = 2.0 * bf16_burst
-        achieved = flops / gsec / 1e12
+        achieved = fused_flops / fused_sec / 1e12
+        # DRAM bytes of one launch of this kernel at M = 16384 from the ncu capture summarised in
+        # profiles/gemm_fp8_gate_up_M16384.md (68.0 MB read + 166.7 MB written), scaled by the rows
+        traffic = (68.0e6 + 166.7e6) * eng.rows / 16384.0
         roof = {
             "bound": "tensor", "achieved": achieved, "peak": peak_fp8, "unit": "TFLOP/s",
-            "frac": achieved / peak_fp8, "traffic": None,
-            "kernel": "gemm_fp8_kernel (qkv+o+gate_up+down at M=%d, 4 launches)" % eng.rows,
+            "frac": achieved / peak_fp8, "traffic": traffic,
+            "kernel": "gemm_fp8_pair_kernel<bf16, EPI=1> (gate_up GEMM + SwiGLU epilogue, M=%d N=12288 K=2048; "
+                      "31 %% of the wave)" % eng.rows,
+            "us_per_launch": fused_sec * 1e6,
             "peak_source": ("2 x measured bf16 burst (MEASURED_PEAKS.json)" if peaks else "2 x fallback 1.59 PFLOP/s")
             + "; nominal dense FP8 4500",
+            "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch at M=16384 "
+                              "(profiles/gemm_fp8_gate_up_M16384.md), scaled to this row count",
+            "layer_gemms_tflops": flops / gsec / 1e12,
+            "layer_gemms": "plain qkv+o+gate_up+down at M=%d, 4 launches back to back" % eng.rows,
             "cublaslt_fp8_tflops_same_shapes": lib_tf,
         }
         cpu = None

@@ -87,6 +87,8 @@ _SIGNATURES = {
     "fr_decode_attn_scratch_bytes": [_I, _I, _I],
     "fr_decode_attn_fp8": [P, _L, _L, P, P, _L, _L, _L, _L, P, P, P, P, P, _L, _I, _I, _I, _I, _I, _I, _I, _F, P, _L,
                            _I, P],
+    "fr_decode_attn_reuse_fp8": [P, _L, _L, P, P, _L, _L, _L, _L, P, P, P, P, P, _L, _I, _I, _I, _I, _I, _I, _I, _F, P,
+                                 _L, _I, P, P],
     "fr_logsumexp_rows": [P, _L, P, P, P, _L, _I, _I, P],
     "fr_topk_rows": [P, _L, P, P, P, P, _I, _I, _I, P],
     "fr_lse_combine_shards": [P, P, P, P, _I, _I, P],

@@ -132,7 +132,7 @@ class AttentionBackend:
     ``skip_store`` is set (the fused rope kernel already wrote K/V)."""
 
     def __init__(self, kv_pool: TokenToKVPool, num_qo_heads: int, num_kv_heads: int, head_dim: int,
-                 max_shared_len: int = 0):
+                 max_shared_len: int = 0, keep_prefix: bool = False):
         self.kv_pool = kv_pool
         self.num_qo_heads = int(num_qo_heads)
         self.num_kv_heads = int(num_kv_heads)
@@ -145,6 +145,14 @@ class AttentionBackend:
         # longest shared prefix the tensor-core path should cover (0 = use the kernel without scratch)
         self.max_shared_len = int(max_shared_len)
         self._scratch: Optional[torch.Tensor] = None
+        # keep_prefix: one scratch buffer per layer, so that the widened shared prefix written at
+        # the first decode step of a set of requests is reused by their later steps
+        # (``prepare(batch, reuse_prefix=True)``) instead of being widened again every step
+        self.keep_prefix = bool(keep_prefix) and self.max_shared_len > 0
+        self._layer_scratch: dict = {}
+        self._scratch_bytes = 0
+        self._prepared_len: Optional[torch.Tensor] = None
+        self._reuse = False
 
     def set_groups(self, group_rows: torch.Tensor, max_group_rows: int) -> None:
         """``group_rows`` int32 [n_groups + 1]: rows [g[i], g[i+1]) are the beams of one request."""
@@ -155,12 +163,34 @@ class AttentionBackend:
             self._shared_len = torch.zeros(self._n_groups, dtype=torch.int32, device=group_rows.device)
         if self.max_shared_len > 0:
             need = int(_lib.load().fr_decode_attn_scratch_bytes(self._n_groups, self.num_kv_heads, self.max_shared_len))
-            if self._scratch is None or self._scratch.numel() < need:
+            if need > self._scratch_bytes:
+                self._layer_scratch.clear()
+            self._scratch_bytes = max(self._scratch_bytes, need)
+            if not self.keep_prefix and (self._scratch is None or self._scratch.numel() < need):
                 self._scratch = torch.empty(need, dtype=torch.uint8, device=group_rows.device)
+            if self.keep_prefix and (self._prepared_len is None or self._prepared_len.numel() < self._n_groups):
+                self._prepared_len = torch.zeros(self._n_groups, dtype=torch.int32, device=group_rows.device)
+        self._reuse = False
 
-    def prepare(self, batch) -> None:
+    def _scratch_for(self, layer_id: int, device) -> Optional[torch.Tensor]:
+        if not self.keep_prefix:
+            return self._scratch
+        buf = self._layer_scratch.get(layer_id)
+        if buf is None:
+            buf = torch.empty(self._scratch_bytes, dtype=torch.uint8, device=device)
+            self._layer_scratch[layer_id] = buf
+        return buf
+
+    def prepare(self, batch, reuse_prefix: bool = False) -> None:
+        """Plan the step. ``reuse_prefix`` (needs ``keep_prefix``): the rows are later decode steps
+        of the requests of the previous ``prepare``; their prompt slots and KV bytes are unchanged,
+        so each layer widens only the prefix tokens that call had not covered yet."""
         if batch.kv_indices is None or batch.kv_indptr is None:
             return
+        reuse = bool(reuse_prefix) and self.keep_prefix and self._shared_len is not None
+        if reuse:
+            self._prepared_len.copy_(self._shared_len[: self._prepared_len.numel()])
+        self._reuse = reuse
         if self._group_rows is None:
             n = int(batch.kv_indptr.numel()) - 1
             self.set_groups(torch.arange(n + 1, dtype=torch.int32, device=batch.kv_indptr.device), 1)
@@ -179,11 +209,15 @@ class AttentionBackend:
             out = torch.empty((t, self.num_qo_heads, self.head_dim), dtype=torch.bfloat16, device=q.device)
         kc = self.kv_pool.k[layer_id]
         vc = self.kv_pool.v[layer_id]
-        call("fr_decode_attn_fp8", ptr(q), q.stride(0), q.stride(1), ptr(kc), ptr(vc), kc.stride(0), kc.stride(1),
-             vc.stride(0), vc.stride(1), ptr(batch.kv_indptr), ptr(batch.kv_indices), ptr(self._group_rows),
-             ptr(self._shared_len), ptr(out), out.stride(0), t, self._n_groups, self.num_qo_heads,
-             self.num_kv_heads, self.head_dim, self._max_group_rows, self.kv_pool.num_tokens,
-             float(self.head_dim) ** -0.5, ptr(self._scratch),
-             int(self._scratch.numel()) if self._scratch is not None else 0, self.max_shared_len,
-             stream_ptr(q.device))
+        scratch = self._scratch_for(layer_id, q.device) if self.max_shared_len > 0 else None
+        args = (ptr(q), q.stride(0), q.stride(1), ptr(kc), ptr(vc), kc.stride(0), kc.stride(1),
+                vc.stride(0), vc.stride(1), ptr(batch.kv_indptr), ptr(batch.kv_indices), ptr(self._group_rows),
+                ptr(self._shared_len), ptr(out), out.stride(0), t, self._n_groups, self.num_qo_heads,
+                self.num_kv_heads, self.head_dim, self._max_group_rows, self.kv_pool.num_tokens,
+                float(self.head_dim) ** -0.5, ptr(scratch), int(scratch.numel()) if scratch is not None else 0,
+                self.max_shared_len)
+        if self._reuse:
+            call("fr_decode_attn_reuse_fp8", *args, ptr(self._prepared_len), stream_ptr(q.device))
+        else:
+            call("fr_decode_attn_fp8", *args, stream_ptr(q.device))
         return out

@@ -347,7 +347,7 @@ int decode_attn_tc(const void* q, int64_t q_t, int64_t q_h, const void* k_cache,
                    int64_t ck_h, int64_t cv_s, int64_t cv_h, const int32_t* indptr, const int32_t* indices,
                    const int32_t* group_rows, const int32_t* shared_len, void* out, int64_t o_t, int n_rows,
                    int n_groups, int hq, int hkv, int max_group_rows, int num_slots, float sm_scale, void* scratch,
-                   int lcap, cudaStream_t stream);  // attn_tc.cu
+                   int lcap, const int32_t* prepared_len, cudaStream_t stream);  // attn_tc.cu
 }  // namespace fr
 
 using namespace fr;
@@ -371,12 +371,12 @@ extern "C" int64_t fr_decode_attn_scratch_bytes(int n_groups, int hkv, int max_s
   return static_cast<int64_t>(n_groups) * hkv * lcap * attn::kD * 2 /* bf16 */ * 2 /* K and V^T */;
 }
 
-extern "C" int fr_decode_attn_fp8(const void* q, int64_t q_t, int64_t q_h, const void* k_cache, const void* v_cache,
-                                  int64_t ck_s, int64_t ck_h, int64_t cv_s, int64_t cv_h, const int32_t* indptr,
-                                  const int32_t* indices, const int32_t* group_rows, const int32_t* shared_len,
-                                  void* out, int64_t o_t, int n_rows, int n_groups, int hq, int hkv, int head_dim,
-                                  int max_group_rows, int num_slots, float sm_scale, void* scratch,
-                                  int64_t scratch_bytes, int max_shared_len, cudaStream_t stream) {
+static int decode_attn_entry(const void* q, int64_t q_t, int64_t q_h, const void* k_cache, const void* v_cache,
+                             int64_t ck_s, int64_t ck_h, int64_t cv_s, int64_t cv_h, const int32_t* indptr,
+                             const int32_t* indices, const int32_t* group_rows, const int32_t* shared_len, void* out,
+                             int64_t o_t, int n_rows, int n_groups, int hq, int hkv, int head_dim, int max_group_rows,
+                             int num_slots, float sm_scale, void* scratch, int64_t scratch_bytes, int max_shared_len,
+                             const int32_t* prepared_len, cudaStream_t stream) {
   FR_CHECK_ARG(n_rows >= 0 && n_groups >= 0 && hq > 0 && hkv > 0 && max_group_rows >= 0 && num_slots > 0);
   if (n_rows == 0 || n_groups == 0 || max_group_rows == 0) return FR_OK;
   FR_CHECK_ARG(q && k_cache && v_cache && indptr && indices && group_rows && shared_len && out);
@@ -393,7 +393,7 @@ extern "C" int fr_decode_attn_fp8(const void* q, int64_t q_t, int64_t q_h, const
     FR_CHECK_ARG(scratch_bytes >= fr_decode_attn_scratch_bytes(n_groups, hkv, max_shared_len));
     return decode_attn_tc(q, q_t, q_h, k_cache, v_cache, ck_s, ck_h, cv_s, cv_h, indptr, indices, group_rows,
                           shared_len, out, o_t, n_rows, n_groups, hq, hkv, max_group_rows, num_slots, sm_scale,
-                          scratch, lcap, stream);
+                          scratch, lcap, prepared_len, stream);
   }
   attn::Params p{static_cast<const __nv_bfloat16*>(q), q_t, q_h, static_cast<const uint8_t*>(k_cache),
                  static_cast<const uint8_t*>(v_cache), ck_s, ck_h, cv_s, cv_h, indptr, indices, group_rows,
@@ -409,4 +409,28 @@ extern "C" int fr_decode_attn_fp8(const void* q, int64_t q_t, int64_t q_h, const
     default: return FR_ERR_UNSUPPORTED;
   }
   return launch_status();
+}
+
+extern "C" int fr_decode_attn_fp8(const void* q, int64_t q_t, int64_t q_h, const void* k_cache, const void* v_cache,
+                                  int64_t ck_s, int64_t ck_h, int64_t cv_s, int64_t cv_h, const int32_t* indptr,
+                                  const int32_t* indices, const int32_t* group_rows, const int32_t* shared_len,
+                                  void* out, int64_t o_t, int n_rows, int n_groups, int hq, int hkv, int head_dim,
+                                  int max_group_rows, int num_slots, float sm_scale, void* scratch,
+                                  int64_t scratch_bytes, int max_shared_len, cudaStream_t stream) {
+  return decode_attn_entry(q, q_t, q_h, k_cache, v_cache, ck_s, ck_h, cv_s, cv_h, indptr, indices, group_rows,
+                           shared_len, out, o_t, n_rows, n_groups, hq, hkv, head_dim, max_group_rows, num_slots,
+                           sm_scale, scratch, scratch_bytes, max_shared_len, nullptr, stream);
+}
+
+extern "C" int fr_decode_attn_reuse_fp8(const void* q, int64_t q_t, int64_t q_h, const void* k_cache,
+                                        const void* v_cache, int64_t ck_s, int64_t ck_h, int64_t cv_s, int64_t cv_h,
+                                        const int32_t* indptr, const int32_t* indices, const int32_t* group_rows,
+                                        const int32_t* shared_len, void* out, int64_t o_t, int n_rows, int n_groups,
+                                        int hq, int hkv, int head_dim, int max_group_rows, int num_slots,
+                                        float sm_scale, void* scratch, int64_t scratch_bytes, int max_shared_len,
+                                        const int32_t* prepared_len, cudaStream_t stream) {
+  FR_CHECK_ARG(scratch != nullptr && max_shared_len > 0 && prepared_len != nullptr);
+  return decode_attn_entry(q, q_t, q_h, k_cache, v_cache, ck_s, ck_h, cv_s, cv_h, indptr, indices, group_rows,
+                           shared_len, out, o_t, n_rows, n_groups, hq, hkv, head_dim, max_group_rows, num_slots,
+                           sm_scale, scratch, scratch_bytes, max_shared_len, prepared_len, stream);
 }

@@ -63,6 +63,7 @@ struct Params {
   int lcap;
   int n_rows, n_groups, hq, hkv, num_slots;
   float scale_log2;
+  const int32_t* prepared_len;  // per group: tokens of the prefix already widened in scratch (or nullptr)
 };
 
 __device__ __forceinline__ __half2 e4m3x2_to_half2(uint16_t v) {
@@ -104,6 +105,9 @@ __global__ void __launch_bounds__(256) shared_kv_prepare_kernel(Params p) {
   const int padded = (ls + kTileN - 1) / kTileN * kTileN;  // tiles are read whole: zero-fill their tails
   const int tok0 = blockIdx.x * 32;
   if (tok0 >= padded) return;
+  // tokens below `done` were widened by an earlier call on the same scratch and are still valid
+  const int done = p.prepared_len != nullptr ? min(p.prepared_len[grp], ls) : 0;
+  if (tok0 + 32 <= done) return;
   const int row0 = p.group_rows[grp];
   const int32_t* idx = p.indices + p.indptr[row0];
   const size_t gh = static_cast<size_t>(grp) * p.hkv + kvh;
@@ -120,7 +124,7 @@ __global__ void __launch_bounds__(256) shared_kv_prepare_kernel(Params p) {
     kraw = __ldg(reinterpret_cast<const uint4*>(p.kc + s * p.ck_s + kvh * p.ck_h + ch * 16));
     vraw = __ldg(reinterpret_cast<const uint4*>(p.vc + s * p.cv_s + kvh * p.cv_h + ch * 16));
   }
-  if (tok >= padded) return;
+  if (tok >= padded || tok < done) return;
   const uint32_t kw[4] = {kraw.x, kraw.y, kraw.z, kraw.w};
   const uint32_t vw[4] = {vraw.x, vraw.y, vraw.z, vraw.w};
   uint32_t ko[8];
@@ -453,8 +457,30 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         l_sum = l_sum * c_old;
 #pragma unroll
         for (int b = 0; b < kBatch; ++b) l_sum += pr[b];
+        // V rows of the batch, 32 dims at a time; the loads of chunk c + 1 are issued before the
+        // arithmetic of chunk c so that their latency is paid once, not once per chunk
+        uint4 vnext[kBatch][2];
+        auto load_v = [&](int c) {
+#pragma unroll
+          for (int b = 0; b < kBatch; ++b) {
+            vnext[b][0] = vnext[b][1] = make_uint4(0, 0, 0, 0);
+            if (pr[b] != 0.f) {
+              const uint8_t* vp = p.vc + slot[b] * p.cv_s + kvh * p.cv_h + c * 32;
+              vnext[b][0] = __ldg(reinterpret_cast<const uint4*>(vp));
+              vnext[b][1] = __ldg(reinterpret_cast<const uint4*>(vp + 16));
+            }
+          }
+        };
+        load_v(0);
 #pragma unroll 1
         for (int c = 0; c < kD / 32; ++c) {
+          uint4 vv[kBatch][2];
+#pragma unroll
+          for (int b = 0; b < kBatch; ++b) {
+            vv[b][0] = vnext[b][0];
+            vv[b][1] = vnext[b][1];
+          }
+          if (c + 1 < kD / 32) load_v(c + 1);
           uint32_t o[32];
           if (o_valid) {
             ptx::tmem_ld_32x32(t_lane + kColO + c * 32, o);
@@ -465,16 +491,6 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           }
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * c_old);
-          uint4 vv[kBatch][2];
-#pragma unroll
-          for (int b = 0; b < kBatch; ++b) {
-            vv[b][0] = vv[b][1] = make_uint4(0, 0, 0, 0);
-            if (pr[b] != 0.f) {
-              const uint8_t* vp = p.vc + slot[b] * p.cv_s + kvh * p.cv_h + c * 32;
-              vv[b][0] = __ldg(reinterpret_cast<const uint4*>(vp));
-              vv[b][1] = __ldg(reinterpret_cast<const uint4*>(vp + 16));
-            }
-          }
 #pragma unroll
           for (int b = 0; b < kBatch; ++b) {
             if (pr[b] != 0.f) {
@@ -604,7 +620,7 @@ int decode_attn_tc(const void* q, int64_t q_t, int64_t q_h, const void* k_cache,
                    int64_t ck_h, int64_t cv_s, int64_t cv_h, const int32_t* indptr, const int32_t* indices,
                    const int32_t* group_rows, const int32_t* shared_len, void* out, int64_t o_t, int n_rows,
                    int n_groups, int hq, int hkv, int max_group_rows, int num_slots, float sm_scale, void* scratch,
-                   int lcap, cudaStream_t stream) {
+                   int lcap, const int32_t* prepared_len, cudaStream_t stream) {
   const int G = hq / hkv;
   // TMA: 16-byte aligned base and strides for the strided Q view
   FR_CHECK_ARG(aligned16(q) && (q_t * 2) % 16 == 0 && (q_h * 2) % 16 == 0 && aligned16(out) && (o_t * 2) % 16 == 0);
@@ -612,7 +628,7 @@ int decode_attn_tc(const void* q, int64_t q_t, int64_t q_h, const void* k_cache,
   attn_tc::Params p{static_cast<const __nv_bfloat16*>(q), q_t, q_h, static_cast<const uint8_t*>(k_cache),
                     static_cast<const uint8_t*>(v_cache), ck_s, ck_h, cv_s, cv_h, indptr, indices, group_rows,
                     shared_len, static_cast<__nv_bfloat16*>(out), o_t, nullptr, nullptr, lcap, n_rows, n_groups, hq,
-                    hkv, num_slots, sm_scale * 1.4426950408889634f};
+                    hkv, num_slots, sm_scale * 1.4426950408889634f, prepared_len};
   const size_t half = static_cast<size_t>(n_groups) * hkv * lcap * attn_tc::kD;
   p.kb = static_cast<__nv_bfloat16*>(scratch);
   p.vt = reinterpret_cast<__half*>(p.kb + half);

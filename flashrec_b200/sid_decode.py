@@ -106,6 +106,7 @@ class SidDecodeEngine:
         page_size: int = 16,
         seed: int = 0,
         use_graphs: bool = True,
+        keep_prefix: bool = True,
     ):
         self.cfg = cfg
         self.device = torch.device(device)
@@ -156,7 +157,7 @@ class SidDecodeEngine:
 
         # ---- model + head ----------------------------------------------------------------
         self.attn = AttentionBackend(self.pool, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
-                                     max_shared_len=max(self.prompt_lens) + self.steps)
+                                     max_shared_len=max(self.prompt_lens) + self.steps, keep_prefix=keep_prefix)
         self.attn.set_groups(torch.arange(self.n + 1, dtype=torch.int32, device=dev) * self.bw, self.bw)
         self.model = Qwen3ForCausalLM(cfg, self.attn, dev)
         self.model.init_random(seed=seed + 1)
@@ -221,7 +222,7 @@ class SidDecodeEngine:
         batch = ForwardBatch(input_ids=self.input_ids, req_pool_indices=self.rows_idx, seq_lens=self.seq_lens,
                              positions=self.positions, out_cache_loc=self.out_cache_loc, kv_indices=self.kv_indices,
                              kv_indptr=self.kv_indptr)
-        self.attn.prepare(batch)
+        self.attn.prepare(batch, reuse_prefix=s > 0)
         hidden = self.model.forward(batch)
         logits, mx, ls, _ = self.head.logits_level(hidden, s)
         self.col.fill_(s)

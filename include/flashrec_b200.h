@@ -176,6 +176,22 @@ int fr_decode_attn_fp8(const void* q, int64_t q_t, int64_t q_h, const void* k_ca
                        int num_slots, float sm_scale, void* scratch, int64_t scratch_bytes, int max_shared_len,
                        cudaStream_t stream);
 
+/* fr_decode_attn_fp8 for the later decode steps of the same requests: the scratch
+ * still holds the widened prefixes an earlier call (either entry) on the same
+ * scratch, groups and KV pool wrote, and only tokens [prepared_len[g],
+ * shared_len[g]) of group g are widened now (prepared_len: int32 [n_groups], the
+ * shared_len that earlier call saw). Valid while the first prepared_len[g] slots
+ * of every group are the slots that call saw and their KV bytes are unchanged
+ * (the prompt of a request during its decode steps). scratch and prepared_len
+ * are required. Has no counterpart in the reference, whose attention re-reads
+ * the e4m3 pool every step (attention/flashinfer.py:212-238). */
+int fr_decode_attn_reuse_fp8(const void* q, int64_t q_t, int64_t q_h, const void* k_cache, const void* v_cache,
+                       int64_t ck_s, int64_t ck_h, int64_t cv_s, int64_t cv_h, const int32_t* indptr,
+                       const int32_t* indices, const int32_t* group_rows, const int32_t* shared_len, void* out,
+                       int64_t o_t, int n_rows, int n_groups, int hq, int hkv, int head_dim, int max_group_rows,
+                       int num_slots, float sm_scale, void* scratch, int64_t scratch_bytes, int max_shared_len,
+                       const int32_t* prepared_len, cudaStream_t stream);
+
 /* ---- trie-constrained SID head ------------------------------------------- */
 
 enum fr_trie_kind { FR_TRIE_NONE = 0, FR_TRIE_DENSE = 1, FR_TRIE_CSR = 2, FR_TRIE_BITMAP = 3 };

@@ -446,3 +446,60 @@ def test_merge_shards_equals_unsharded():
     for a, b in ((m.vals, full.vals), (m.parents, full.parents), (m.tokens, full.tokens), (m.indices, full.indices),
                  (m.child, full.child), (tok_out, tok_ref), (node_out, node_ref)):
         assert torch.equal(a, b)
+
+
+def test_decode_attention_prefix_reused_across_steps():
+    """Later decode steps of the same requests reuse the prefix widened at the first step (one scratch per
+    layer), widen only the tokens the shared prefix grew by, and give the bits a fresh widening gives."""
+    from flashrec_b200.attention import AttentionBackend, TokenToKVPool
+    from flashrec_b200.decoder import ForwardBatch
+
+    hq, hkv, bw, pre = 16, 8, [70, 9], [300, 64]
+    rng = np.random.default_rng(11)
+    slots = 4096
+    kc = torch.from_numpy(rng.standard_normal((slots, hkv, 128)).astype(np.float32)).bfloat16().to(FP8)
+    vc = torch.from_numpy(rng.standard_normal((slots, hkv, 128)).astype(np.float32)).bfloat16().to(FP8)
+    free = list(rng.permutation(np.arange(1, slots)))
+    prefixes = [[int(free.pop()) for _ in range(p)] for p in pre]
+    group_rows = torch.tensor([0, bw[0], bw[0] + bw[1]], dtype=torch.int32)
+    t = int(group_rows[-1])
+    # step 0: prompt + own slot; step 1: prompt + one slot shared by the whole group + own slot (all beams
+    # descend from one parent); step 2: prompt + that slot + a parent's slot + own slot
+    shared_tok = [int(free.pop()) for _ in pre]
+    steps = []
+    for step in range(3):
+        lists = []
+        for gi in range(2):
+            for _ in range(bw[gi]):
+                own = [int(free.pop()) for _ in range(1 if step < 2 else 2)]
+                lists.append(prefixes[gi] + ([shared_tok[gi]] if step > 0 else []) + own)
+        steps.append(lists)
+    pools = [TokenToKVPool(2, slots, hkv, 128, FP8, DEV) for _ in range(2)]
+    for pool in pools:
+        for layer in range(2):
+            pool.k[layer].copy_(kc.to(DEV))
+            pool.v[layer].copy_(vc.to(DEV))
+    keep = AttentionBackend(pools[0], hq, hkv, 128, max_shared_len=320, keep_prefix=True)
+    fresh = AttentionBackend(pools[1], hq, hkv, 128, max_shared_len=320)
+    for be in (keep, fresh):
+        be.set_groups(group_rows.to(DEV), max(bw))
+    for step, lists in enumerate(steps):
+        indptr = torch.from_numpy(np.concatenate([[0], np.cumsum([len(x) for x in lists])]).astype(np.int32))
+        indices = torch.from_numpy(np.concatenate([np.asarray(x, dtype=np.int32) for x in lists]))
+        q = torch.from_numpy(rng.standard_normal((t, hq, 128)).astype(np.float32)).bfloat16()
+        batch = ForwardBatch(input_ids=torch.zeros(t, dtype=torch.int64, device=DEV), req_pool_indices=None,
+                             seq_lens=(indptr[1:] - indptr[:-1]).to(DEV), positions=torch.zeros(t, dtype=torch.int64),
+                             out_cache_loc=torch.zeros(t, dtype=torch.int64), kv_indices=indices.to(DEV),
+                             kv_indptr=indptr.to(DEV))
+        keep.prepare(batch, reuse_prefix=step > 0)
+        fresh.prepare(batch)
+        want_shared = [p + (1 if step > 0 else 0) for p in pre]
+        assert keep._shared_len.cpu().tolist() == want_shared
+        if step > 0:
+            assert keep._prepared_len.cpu().tolist() == [p + (1 if step > 1 else 0) for p in pre]
+        for layer in range(2):
+            a = keep.forward(q.to(DEV), None, None, layer, batch, skip_store=True)
+            b = fresh.forward(q.to(DEV), None, None, layer, batch, skip_store=True)
+            assert torch.equal(a, b), (step, layer)
+        ref = O.decode_attention(q, kc, vc, indptr, indices, hq // hkv).float()
+        assert (a.float().cpu() - ref).abs().max() / ref.abs().max() < 2e-2
