@@ -19,7 +19,7 @@
 
 namespace fr {
 
-constexpr int kWarpsPerCta = 8;
+constexpr int kWarpsPerCta = 4;  // 128-thread CTAs: at ~96 registers per thread five of them fit on an SM (20 warps) where two 256-thread CTAs give 16
 
 // ---------------------------------------------------------------------------
 // One warp per row, hidden = 256 * VPL, whole row held in registers.
