@@ -259,7 +259,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       if (!okw) { ok = false; break; }
       ptx::tc_fence_after();
       const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BLOCK_N;
-      if constexpr (EPI == 0) {
+      if constexpr (EPI == 0 || EPI == 2) {
         OutT* out_row = out + static_cast<int64_t>(row) * ldo + n0;
 #pragma unroll 1
         for (int c = part; c < BLOCK_N / 32; c += kSplit) {
@@ -274,6 +274,16 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             v[j] = t;
           }
           const int nvalid = N - (n0 + c * 32);
+          if constexpr (EPI == 2) {
+            // out is the residual stream, updated in place: bf16(bf16(x) + residual), as the
+            // reference's fused add does on the rounded GEMM output
+            if (row < M && nvalid > 0) {
+              const __nv_bfloat16* res = reinterpret_cast<const __nv_bfloat16*>(out_row) + c * 32;
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < nvalid) v[j] = __fadd_rn(round_bf16(v[j]), __bfloat162float(res[j]));
+            }
+          }
           if (row < M && nvalid > 0) store_chunk32<OutT>(out_row + c * 32, v, nvalid);
         }
       } else {
@@ -381,6 +391,7 @@ __device__ __forceinline__ float swiglu16(uint32_t taddr_g, uint32_t taddr_u, co
 // store (full 128-byte lines, clipped at the matrix edge by the hardware), so
 // the output leaves the SM as bulk copies instead of per-thread 16-byte stores.
 // ---------------------------------------------------------------------------
+template <int EPI>
 struct PairCfg {
   static constexpr int kBlockN = 256;
   static constexpr int kStageA = kBlockM * kBlockK;           // 16 KB
@@ -388,9 +399,11 @@ struct PairCfg {
   static constexpr int kStageBytes = kStageA + kStageB;
   static constexpr int kStages = 5;
   static constexpr int kTmemCols = 2 * kBlockN;
-  static constexpr int kOutStageBytes = 32 * 1024;  // epilogue staging tiles for the TMA stores
+  // epilogue staging tiles for the TMA stores (EPI 2: three per warp, they also receive the residual)
+  static constexpr int kOutStageBytes = (EPI == 2 ? 48 : 32) * 1024;
   static constexpr int kScaleBytes = 2 * kBlockN * 4 * 2;
-  static constexpr int kBarBytes = (2 * kStages + 4) * 8 + 16;
+  static constexpr int kResBars = 12;  // EPI 2: 4 epilogue warps x 3 staging tiles
+  static constexpr int kBarBytes = (2 * kStages + 4 + kResBars) * 8 + 16;
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kOutStageBytes + kScaleBytes + kBarBytes;
 };
 
@@ -400,7 +413,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                      const __grid_constant__ CUtensorMap tmap_out, const float* __restrict__ scale_a,
                      const float* __restrict__ scale_b, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
                      unsigned int* __restrict__ row_amax, const uint16_t* __restrict__ silu_table, int* status) {
-  using C = PairCfg;
+  using C = PairCfg<EPI>;
   constexpr int BLOCK_N = C::kBlockN;
   constexpr int kEpiThreads = EpiCfg<EPI>::kEpiThreads;
   constexpr int kEpiWarps = EpiCfg<EPI>::kWarps;
@@ -418,7 +431,8 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const uint32_t bar_empty = bar_full + 8 * C::kStages;
   const uint32_t bar_tfull = bar_empty + 8 * C::kStages;
   const uint32_t bar_tempty = bar_tfull + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::kStages + 4);
+  const uint32_t bar_res = bar_tempty + 16;  // [kResBars] residual tile landed (EPI 2)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::kStages + 4 + C::kResBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -440,6 +454,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       ptx::mbar_init(bar_tfull + 8 * b, 1);
       ptx::mbar_init(bar_tempty + 8 * b, 2 * kEpiWarps);  // epilogue warps of both CTAs
     }
+    for (int b = 0; b < C::kResBars; ++b) ptx::mbar_init(bar_res + 8 * b, 1);
     *abort_flag = 0;
     ptx::mbar_init_fence();
     ptx::prefetch_tmap(&tmap_a);
@@ -532,7 +547,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       float* bss = bias_stage + buf * BLOCK_N;
       const int row = m0 + quad * 32 + lane;
       const float sa = row < M ? __ldg(scale_a + row) : 0.f;
-      if constexpr (EPI == 0) {  // the SwiGLU epilogue reads its few scales straight from global memory
+      if constexpr (EPI != 1) {  // the SwiGLU epilogue reads its few scales straight from global memory
         for (int i = epi_tid; i < BLOCK_N; i += kEpiThreads) {
           const int n = n0 + i;
           sbs[i] = n < N ? __ldg(scale_b + n) : 0.f;
@@ -600,6 +615,71 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             ptx::bulk_commit();
           }
         }
+      } else if constexpr (EPI == 2) {
+        // out += : the output tile is the bf16 residual stream, updated in place. Chunk k of this
+        // warp (counted across tiles) uses staging tile k % 3: the residual chunk is brought in
+        // by a TMA load issued one chunk ahead, the sum goes back into the same tile and leaves
+        // by a TMA store.
+        constexpr int kChunkCols = 64;
+        constexpr int kChunks = BLOCK_N / kChunkCols;
+        uint8_t* stage0 = out_stage + ewarp * 12288;
+        const uint32_t bar_w = bar_res + 8 * (ewarp * 3);
+        auto issue_res = [&](int tile_i, int c, int kc) {  // lane 0 only
+          const TileCoord tcn = tile_coord(tile_i, m_blocks, n_blocks);
+          const int rb = tcn.mb * (2 * kBlockM) + static_cast<int>(rank) * kBlockM + quad * 32;
+          const int cb = tcn.nb * BLOCK_N + c * kChunkCols;
+          const uint32_t b = bar_w + 8 * (kc % 3);
+          ptx::mbar_expect_tx(b, 4096);
+          ptx::tma_load_2d(ptx::smem_u32(stage0 + (kc % 3) * 4096), &tmap_out, cb, rb, b);
+        };
+        if (it == 0 && lane == 0) issue_res(tile, 0, 0);
+#pragma unroll 1
+        for (int c = 0; c < kChunks; ++c) {
+          const int kc = it * kChunks + c;
+          uint8_t* st = stage0 + (kc % 3) * 4096;
+          if (lane == 0) {
+            // tile (kc + 1) % 3 was last used by chunk kc - 2: its store must have read it
+            ptx::bulk_wait_read<1>();
+            if (c + 1 < kChunks) issue_res(tile, c + 1, kc + 1);
+            else if (tile + n_pairs < num_tiles) issue_res(tile + n_pairs, 0, kc + 1);
+          }
+          uint32_t w[32];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t r[32];
+            ptx::tmem_ld_32x32(taddr_row + c * kChunkCols + h * 32, r);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int col = c * kChunkCols + h * 32 + 2 * j;
+              w[h * 16 + j] = pack_bf16(__fmul_rn(__fmul_rn(__uint_as_float(r[2 * j]), sa), sbs[col]),
+                                        __fmul_rn(__fmul_rn(__uint_as_float(r[2 * j + 1]), sa), sbs[col + 1]));
+            }
+          }
+          if (c == kChunks - 1) {
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(tempty_remote);
+          }
+          int okr = 0;
+          if (lane == 0) okr = ptx::mbar_wait(bar_w + 8 * (kc % 3), (kc / 3) & 1, abort_flag, status, 25) ? 1 : 0;
+          okr = __shfl_sync(0xffffffffu, okr, 0);
+          if (!okr) { ok = false; break; }
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {  // 128-byte swizzle: 16-byte chunk index ^ (row & 7)
+            uint4* cell = reinterpret_cast<uint4*>(st + lane * 128 + ((ch ^ (lane & 7)) << 4));
+            const uint4 rv = *cell;
+            *cell = make_uint4(add_bf16x2(w[4 * ch], rv.x), add_bf16x2(w[4 * ch + 1], rv.y),
+                               add_bf16x2(w[4 * ch + 2], rv.z), add_bf16x2(w[4 * ch + 3], rv.w));
+          }
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && row_base < M && n0 + c * kChunkCols < N) {
+            ptx::tma_store_2d(&tmap_out, ptx::smem_u32(st), n0 + c * kChunkCols, row_base);
+            ptx::bulk_commit();
+          }
+        }
+        if (!ok) break;
       } else {
         // one 32-column chunk of y per warp and tile: 64-byte rows, 64-byte swizzle
         uint8_t* st = out_stage + ewarp * 2048;
@@ -758,7 +838,7 @@ template <typename OutT, int EPI>
 static int launch_pair(const void* a, const void* b, const float* sa, const float* sb, const void* bias, void* out,
                        int64_t ldo, int M, int N, int K, int64_t lda, int64_t ldb, cudaStream_t stream,
                        unsigned int* row_amax = nullptr) {
-  using C = PairCfg;
+  using C = PairCfg<EPI>;
   CUtensorMap ta, tb;
   int st = make_tmap_u8(&ta, a, M, K, lda, kBlockM);
   if (st != FR_OK) return st;
@@ -808,7 +888,7 @@ static bool use_pair(int M, int N) {
     return e ? (e[0] == '0' ? 0 : 1) : -1;
   }();
   if (forced >= 0) return forced == 1;
-  const int64_t tiles = static_cast<int64_t>(ceil_div(M, 2 * kBlockM)) * ceil_div(N, PairCfg::kBlockN);
+  const int64_t tiles = static_cast<int64_t>(ceil_div(M, 2 * kBlockM)) * ceil_div(N, PairCfg<0>::kBlockN);
   return tiles >= 3 * (sm_count() / 2);
 }
 
@@ -864,4 +944,32 @@ extern "C" int fr_gemm_fp8_silu_mul(const void* a, const void* b_interleaved, co
                                                N, K, lda, ldb, stream, reinterpret_cast<unsigned int*>(row_amax));
   return gemm::launch<256, __nv_bfloat16, 1>(a, b_interleaved, scale_a, scale_b_interleaved, nullptr, y_out, ldo, M, N,
                                              K, lda, ldb, stream, reinterpret_cast<unsigned int*>(row_amax));
+}
+
+extern "C" int fr_gemm_fp8_w8a8_add(const void* a, const void* b, const float* scale_a, const float* scale_b,
+                                    void* residual_inout, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldr,
+                                    int block_n_hint, cudaStream_t stream) {
+  FR_CHECK_ARG(M >= 0 && N > 0 && K > 0);
+  if (M == 0) return FR_OK;
+  FR_CHECK_ARG(a && b && scale_a && scale_b && residual_inout);
+  FR_CHECK_ARG(aligned16(a) && aligned16(b) && aligned16(residual_inout));
+  FR_CHECK_ARG(lda >= K && ldb >= K && ldr >= N && lda % 16 == 0 && ldb % 16 == 0 && ldr % 8 == 0 && K % 16 == 0);
+  if (block_n_hint == 512 || (block_n_hint == 0 && gemm::use_pair(M, N)))
+    return gemm::launch_pair<__nv_bfloat16, 2>(a, b, scale_a, scale_b, nullptr, residual_inout, ldr, M, N, K, lda, ldb,
+                                               stream);
+  int bn = block_n_hint;
+  if (bn != 64 && bn != 128 && bn != 256) bn = gemm::pick_block_n(M, N);
+  switch (bn) {
+    case 256:
+      return gemm::launch<256, __nv_bfloat16, 2>(a, b, scale_a, scale_b, nullptr, residual_inout, ldr, M, N, K, lda,
+                                                 ldb, stream);
+    case 128:
+      return gemm::launch<128, __nv_bfloat16, 2>(a, b, scale_a, scale_b, nullptr, residual_inout, ldr, M, N, K, lda,
+                                                 ldb, stream);
+    case 64:
+      return gemm::launch<64, __nv_bfloat16, 2>(a, b, scale_a, scale_b, nullptr, residual_inout, ldr, M, N, K, lda,
+                                                ldb, stream);
+    default: break;
+  }
+  return FR_ERR_UNSUPPORTED;
 }

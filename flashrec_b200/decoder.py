@@ -15,7 +15,8 @@ import torch
 from flashrec_b200._lib import call, ptr, stream_ptr
 from flashrec_b200.attention import AttentionBackend, TokenToKVPool
 from flashrec_b200.kernel.qk_rope_kv import fused_qk_norm_rope_store_fp8
-from flashrec_b200.kernel.sglops import fp8_scaled_mm_silu_mul, interleave_gate_up, quant_known_amax_fp8
+from flashrec_b200.kernel.sglops import (fp8_scaled_mm_silu_mul, interleave_gate_up, per_token_quant_fp8,
+                                         quant_known_amax_fp8)
 from flashrec_b200.kernel.silu_fp8 import silu_and_mul_per_token_quant_fp8
 from flashrec_b200.layers import Linear, RMSNorm, RotaryEmbedding
 
@@ -65,7 +66,9 @@ class Qwen3Attention:
         self.attn = attn
         self.rotary = rotary
 
-    def forward(self, x, batch: ForwardBatch, *, q_fp8, a_scale) -> torch.Tensor:
+    def forward(self, x, batch: ForwardBatch, *, q_fp8, a_scale, residual_inout=None) -> torch.Tensor:
+        """``residual_inout``: the o_proj GEMM adds its output to this bf16 residual stream in place
+        (and returns it) instead of returning the projection."""
         t = int(q_fp8.shape[0])
         qkv = self.qkv_proj.forward_fp8(q_fp8, a_scale, (t, self.qkv_proj.in_features), torch.bfloat16)
         heads = qkv.view(t, self.num_qo + 2 * self.num_kv, self.head_dim)
@@ -79,6 +82,9 @@ class Qwen3Attention:
         )
         # the attention kernel reads the strided q view directly (no .contiguous() copy)
         o = self.attn.forward(q, k, v, self.layer_id, batch, skip_store=True)
+        if residual_inout is not None:
+            o_fp8, o_scale = per_token_quant_fp8(o.reshape(t, -1))
+            return self.o_proj.forward_fp8_add_(o_fp8, o_scale, residual_inout)
         return self.o_proj(o.reshape(t, -1))
 
 
@@ -105,14 +111,18 @@ class Qwen3MLP:
             self.gate_up_proj._fp8_weight = None
             self.gate_up_proj._fp8_scale = None
 
-    def forward(self, x, *, q_fp8, a_scale) -> torch.Tensor:
+    def forward(self, x, *, q_fp8, a_scale, residual_inout=None) -> torch.Tensor:
+        """``residual_inout``: the down_proj GEMM adds its output to this bf16 residual stream in
+        place (and returns it) instead of returning the projection."""
         rows = int(q_fp8.shape[0])
         if self.fuse_silu_gemm and self._gu_w is not None:
             y, amax = fp8_scaled_mm_silu_mul(q_fp8, self._gu_w, a_scale, self._gu_s)
             y_fp8, y_scale = quant_known_amax_fp8(y, amax)
-            return self.down_proj.forward_fp8(y_fp8, y_scale, (rows, self.down_proj.in_features), torch.bfloat16)
-        gu = self.gate_up_proj.forward_fp8(q_fp8, a_scale, (rows, self.gate_up_proj.in_features), torch.bfloat16)
-        y_fp8, y_scale = silu_and_mul_per_token_quant_fp8(gu)
+        else:
+            gu = self.gate_up_proj.forward_fp8(q_fp8, a_scale, (rows, self.gate_up_proj.in_features), torch.bfloat16)
+            y_fp8, y_scale = silu_and_mul_per_token_quant_fp8(gu)
+        if residual_inout is not None:
+            return self.down_proj.forward_fp8_add_(y_fp8, y_scale, residual_inout)
         return self.down_proj.forward_fp8(y_fp8, y_scale, (rows, self.down_proj.in_features), torch.bfloat16)
 
 
@@ -122,6 +132,17 @@ class Qwen3DecoderLayer:
         self.mlp = Qwen3MLP(cfg)
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, device=device)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, device=device)
+
+    def forward_fused_residual(self, residual, batch: ForwardBatch):
+        """The same layer with the residual adds folded into the o_proj and down_proj GEMM
+        epilogues: ``residual`` (bf16 [T, hidden]) holds x + residual of the unfused flow on entry
+        and on exit, is updated in place, and each norm reads it without an add. Bit-identical
+        to ``forward`` (the GEMM output is rounded to bf16 before the bf16 add in both)."""
+        q_fp8, a_scale = self.input_layernorm.quant_fp8(residual)
+        self.self_attn.forward(None, batch, q_fp8=q_fp8, a_scale=a_scale, residual_inout=residual)
+        q_fp8, a_scale = self.post_attention_layernorm.quant_fp8(residual)
+        self.mlp.forward(None, q_fp8=q_fp8, a_scale=a_scale, residual_inout=residual)
+        return residual
 
     def forward(self, x, residual, batch: ForwardBatch):
         """FP8 branch of Qwen3DecoderLayer.forward (models/qwen3.py:198-215)."""
@@ -140,9 +161,12 @@ class Qwen3ForCausalLM:
     """Embedding -> layers -> final (add+)RMSNorm; returns the normalised hidden
     states, which the SID head consumes (models/qwen3.py:227-273)."""
 
-    def __init__(self, cfg: Qwen3Config, attn: AttentionBackend, device):
+    def __init__(self, cfg: Qwen3Config, attn: AttentionBackend, device, fuse_residual: bool = True):
         self.cfg = cfg
         self.device = torch.device(device)
+        # fold the residual adds into the o_proj / down_proj GEMM epilogues (same bits, one HBM
+        # pass over the residual stream less per norm)
+        self.fuse_residual = bool(fuse_residual)
         self.rotary = RotaryEmbedding(cfg.head_dim, cfg.max_position_embeddings, cfg.rope_theta, device=device)
         self.layers: List[Qwen3DecoderLayer] = [
             Qwen3DecoderLayer(cfg, i, attn, self.rotary, device=device) for i in range(cfg.num_hidden_layers)
@@ -160,6 +184,11 @@ class Qwen3ForCausalLM:
 
     def forward(self, batch: ForwardBatch) -> torch.Tensor:
         x = self.embed(batch.input_ids)
+        if self.fuse_residual and self.layers:
+            residual = x  # the embedding output is this wave's residual stream, updated in place
+            for layer in self.layers:
+                layer.forward_fused_residual(residual, batch)
+            return self.norm(residual)
         residual = None
         for layer in self.layers:
             x, residual = layer.forward(x, residual, batch)

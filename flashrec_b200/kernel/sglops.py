@@ -120,6 +120,30 @@ def fp8_scaled_mm(
     return out
 
 
+def fp8_scaled_mm_add_(a_fp8: torch.Tensor, b_fp8: torch.Tensor, scale_a: torch.Tensor, scale_b: torch.Tensor,
+                       residual: torch.Tensor, block_n: int = 0) -> torch.Tensor:
+    """``residual += fp8_scaled_mm(a, b, ..., bf16)`` in place, with the reference's roundings (the
+    GEMM output rounded to bf16, then the bf16 sum): the add half of ``fused_add_rmsnorm`` that
+    follows the o_proj / down_proj GEMMs (models/qwen3.py:205-214) folded into the GEMM epilogue.
+    ``b_fp8`` is the ``[K, N]`` ``.t()`` view of the weight as for ``fp8_scaled_mm``."""
+    require_cuda(a_fp8, b_fp8, scale_a, scale_b, residual)
+    if b_fp8.dim() != 2 or b_fp8.stride(0) != 1:
+        raise ValueError("fp8_scaled_mm_add_: b must be the column-major [K,N] view of an [N,K] weight")
+    m, k = int(a_fp8.shape[0]), int(a_fp8.shape[1])
+    n = int(b_fp8.shape[1])
+    if residual.dtype != torch.bfloat16 or residual.dim() != 2 or tuple(residual.shape) != (m, n) or \
+            residual.stride(1) != 1:
+        raise ValueError("fp8_scaled_mm_add_: residual must be a bf16 [M, N] matrix with unit column stride")
+    a = a_fp8 if a_fp8.stride(1) == 1 else a_fp8.contiguous()
+    sa = scale_a.reshape(-1).to(torch.float32).contiguous()
+    sb = scale_b.reshape(-1).to(torch.float32).contiguous()
+    if sa.numel() != m or sb.numel() != n:
+        raise ValueError("fp8_scaled_mm_add_: scale shapes do not match [M] / [N]")
+    call("fr_gemm_fp8_w8a8_add", ptr(a), ptr(b_fp8), ptr(sa), ptr(sb), ptr(residual), m, n, k, a.stride(0),
+         b_fp8.stride(1), residual.stride(0), int(block_n), stream_ptr(a.device))
+    return residual
+
+
 def interleave_gate_up(weight_nk: torch.Tensor, scale: torch.Tensor, block: int = 128):
     """Regroup the rows of a merged gate_up weight ``[2d, K]`` (gate rows first, then
     up rows, as ``merge_gate_up`` in the reference's models/weight.py lays them out)

@@ -17,6 +17,7 @@ from flashrec_b200.kernel.rms_fp8 import (
 )
 from flashrec_b200.kernel.sglops import (
     fp8_scaled_mm,
+    fp8_scaled_mm_add_,
     fused_add_rmsnorm,
     per_token_quant_fp8,
     rmsnorm,
@@ -103,6 +104,14 @@ class Linear:
     def forward_fp8(self, q: torch.Tensor, a_scale: torch.Tensor, orig_shape: tuple, out_dtype: torch.dtype):
         """GEMM from a pre-quantised activation. ``q`` is [M, K] e4m3 (layers/linear.py:134-142)."""
         return self._fp8_mm(q, a_scale, orig_shape, out_dtype)
+
+    def forward_fp8_add_(self, q: torch.Tensor, a_scale: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+        """``residual += self(q)`` in place on the bf16 residual stream [M, out_features] (bias-free layers)."""
+        if not self._use_fp8:
+            raise RuntimeError("Linear.load() has not been called")
+        if self.bias is not None:
+            raise RuntimeError("forward_fp8_add_: layers with a bias are not supported")
+        return fp8_scaled_mm_add_(q, self._fp8_weight, a_scale, self._fp8_scale, residual)
 
     def _fp8_mm(self, q, a_scale, orig_shape, out_dtype):
         if not self._use_fp8:

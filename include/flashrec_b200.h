@@ -88,6 +88,17 @@ int fr_gemm_fp8_w8a8(const void* a, const void* b, const float* scale_a, const f
                      void* out, int out_is_f32, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldo,
                      int block_n_hint, cudaStream_t stream);
 
+/* residual_inout[m, n] = bf16( bf16( (sum_k a[m,k] b[n,k]) * scale_a[m] * scale_b[n] ) + residual_inout[m, n] ):
+ * the GEMM of fr_gemm_fp8_w8a8 (bf16 output, no bias) with the add half of the
+ * reference's fused add + RMSNorm folded into its epilogue, in place on the bf16
+ * residual stream [M, N] (row pitch ldr elements, 16-byte aligned rows). The
+ * caller then normalises residual_inout without an add (fr_rms_quant_fp8 with
+ * residual = NULL); the bits equal GEMM -> fused_add_rmsnorm
+ * (kernel/sglops.py:49-61, models/qwen3.py:205-214). */
+int fr_gemm_fp8_w8a8_add(const void* a, const void* b, const float* scale_a, const float* scale_b,
+                         void* residual_inout, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldr,
+                         int block_n_hint, cudaStream_t stream);
+
 /* gate_up GEMM with SwiGLU fused into the epilogue. b_interleaved / its scales:
  * the [2d, K] gate_up weight with rows regrouped per 256-row tile as
  * [gate rows 128t .. 128t+127 | up rows 128t .. 128t+127] (N = 2d, d % 128 == 0).

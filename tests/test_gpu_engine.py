@@ -158,3 +158,41 @@ def test_engine_graph_equals_eager_and_sids_are_legal():
         results[layout] = eager
     assert torch.equal(results["csr"][1], results["bitmap"][1])  # layouts agree bit for bit
     assert device_status() == (0, 0)
+
+
+def test_model_with_residual_adds_in_gemm_epilogues_equals_unfused_flow():
+    """Qwen3ForCausalLM(fuse_residual=True) (o_proj / down_proj GEMMs add into the residual stream, norms
+    without add) gives the bits of the reference's call order GEMM -> fused add + RMSNorm."""
+    from flashrec_b200.attention import AttentionBackend, TokenToKVPool
+    from flashrec_b200.decoder import ForwardBatch, Qwen3Config, Qwen3ForCausalLM
+
+    cfg = Qwen3Config(hidden_size=512, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+                      intermediate_size=1024, num_hidden_layers=3, max_position_embeddings=256, vocab_size=600)
+    rows, prompt = 300, 40
+    outs = []
+    for fuse in (False, True):
+        pool = TokenToKVPool(cfg.num_hidden_layers, 2048, cfg.num_key_value_heads, cfg.head_dim,
+                             torch.float8_e4m3fn, DEV)
+        g = torch.Generator(device=DEV).manual_seed(5)
+        for layer in range(cfg.num_hidden_layers):
+            pool.k[layer].copy_(torch.randn(pool.k[layer].shape, generator=g, device=DEV).to(torch.float8_e4m3fn))
+            pool.v[layer].copy_(torch.randn(pool.v[layer].shape, generator=g, device=DEV).to(torch.float8_e4m3fn))
+        attn = AttentionBackend(pool, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
+                                max_shared_len=prompt + 4)
+        attn.set_groups(torch.tensor([0, rows], dtype=torch.int32, device=DEV), rows)
+        model = Qwen3ForCausalLM(cfg, attn, DEV, fuse_residual=fuse)
+        model.init_random(seed=2)
+        shared = torch.arange(1, prompt + 1, dtype=torch.int32)
+        own = torch.arange(100, 100 + rows, dtype=torch.int32)
+        lists = torch.cat([shared.repeat(rows, 1), own[:, None]], dim=1)
+        indptr = torch.arange(rows + 1, dtype=torch.int32) * (prompt + 1)
+        ids = torch.randint(0, 600, (rows,), generator=torch.Generator().manual_seed(1))
+        batch = ForwardBatch(input_ids=ids.to(DEV), req_pool_indices=None,
+                             seq_lens=torch.full((rows,), prompt + 1, dtype=torch.int32, device=DEV),
+                             positions=torch.full((rows,), prompt, dtype=torch.int64, device=DEV),
+                             out_cache_loc=own.to(torch.int64).to(DEV), kv_indices=lists.reshape(-1).to(DEV),
+                             kv_indptr=indptr.to(DEV))
+        attn.prepare(batch)
+        outs.append(model.forward(batch))
+    assert torch.isfinite(outs[0].float()).all()
+    assert torch.equal(outs[0], outs[1])

@@ -260,3 +260,29 @@ def test_gemm_silu_epilogue_corner_inputs(case):
         finite = torch.isfinite(ref.float()).all(dim=1)
         want = ref.float().abs().amax(dim=1)
         assert torch.equal(amax.flatten()[finite], want[finite]), (case, mode)
+
+
+@pytest.mark.parametrize("m,n,k,block_n", [(300, 512, 256, 0), (37, 200, 128, 64), (128, 256, 2048, 256),
+                                           (700, 1024, 384, 512), (513, 200, 512, 512), (4100, 2048, 256, 0)])
+def test_gemm_add_into_residual_equals_gemm_then_bf16_add(m, n, k, block_n):
+    """fr_gemm_fp8_w8a8_add == GEMM (bf16 out) followed by the bf16 add of fused_add_rmsnorm, bit for bit,
+    through the single-CTA kernels (hint 64 / 256 / auto) and the CTA-pair kernel (hint 512, ragged edges)."""
+    from flashrec_b200.kernel.sglops import fp8_scaled_mm, fp8_scaled_mm_add_
+
+    g = torch.Generator().manual_seed(m + n + k)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    w = 0.05 * torch.randn(n, k, generator=g)
+    res = torch.randn(m, n, generator=g).bfloat16()
+    aq, asc = O.per_token_quant_fp8(a)
+    wq, wsc = O.quantize_weight_fp8(w)
+    aq, asc, wq, wsc = aq.to(DEV), asc.to(DEV), wq.to(DEV), wsc.to(DEV)
+    x = fp8_scaled_mm(aq, wq.t(), asc, wsc, torch.bfloat16, block_n=block_n)
+    want = (x.float() + res.to(DEV).float()).bfloat16()
+    # a padded residual matrix: row pitch larger than N, columns beyond N must stay untouched
+    pitch = (n + 15) // 8 * 8
+    buf = torch.full((m, pitch), 7.0, dtype=torch.bfloat16, device=DEV)
+    buf[:, :n] = res.to(DEV)
+    out = fp8_scaled_mm_add_(aq, wq.t(), asc, wsc, buf[:, :n], block_n=block_n)
+    assert out.data_ptr() == buf.data_ptr()
+    assert np.array_equal(bits16(buf[:, :n].contiguous()), bits16(want))
+    assert (buf[:, n:] == 7.0).all()
