@@ -729,6 +729,251 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 }
 
 // ---------------------------------------------------------------------------
+// Split-K variant for few rows (a decode step of one request: M = 512). With so few
+// row blocks the tiles of the kernels above cannot fill the GPU without re-reading A
+// once per column tile from L2, and every CTA runs the whole K loop serially. Here a
+// cluster of S CTAs (S in {1, 2, 4, 8}) owns one 128 x 256 output tile: every CTA
+// runs the TMA -> tcgen05 pipeline over its own 1/S of the k-blocks, then the partial
+// tiles are summed across the cluster through distributed shared memory: CTA q owns
+// rows [q 128/S, (q+1) 128/S) of the tile; every CTA stores each of its accumulator
+// rows (fp32) straight into the owner's shared memory (remote stores into the
+// operand stages, idle by then; slot = sender rank), one cluster barrier, and each
+// owner adds its S slots in rank order from local shared memory, scales, converts
+// and stores. Deterministic, no workspace, no atomics, nothing remote after the
+// barrier.
+// EPI 0: out = scaled product (bf16 or f32). EPI 2: bf16 out += (in place, residual).
+// ---------------------------------------------------------------------------
+struct SplitCfg {
+  static constexpr int kTileM = kBlockM;  // 128
+  static constexpr int kTileN = 256;
+  static constexpr int kStageA = kTileM * kBlockK;  // 16 KB
+  static constexpr int kStageB = kTileN * kBlockK;  // 32 KB
+  static constexpr int kStageBytes = kStageA + kStageB;
+  static constexpr int kStages = 4;      // 192 KB; the first 128 KB double as the reduction buffer
+  static constexpr int kTmemCols = 256;  // one 128 x 256 fp32 accumulator
+  static constexpr int kBarBytes = (2 * kStages + 1) * 8 + 16;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kBarBytes;
+  static constexpr int kThreads = 192;
+};
+
+template <typename OutT, int EPI, int S>
+__global__ void __launch_bounds__(SplitCfg::kThreads, 1)
+gemm_fp8_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                       OutT* __restrict__ out, int64_t ldo, const float* __restrict__ scale_a,
+                       const float* __restrict__ scale_b, int M, int N, int K, int* status) {
+  using C = SplitCfg;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+  const uint32_t bar_full = ptx::smem_u32(bars);
+  const uint32_t bar_empty = bar_full + 8 * C::kStages;
+  const uint32_t bar_tfull = bar_empty + 8 * C::kStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::kStages + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int rank = static_cast<int>(ptx::cluster_ctarank());
+  const int tile = blockIdx.x / S;
+  const int m_blocks = (M + C::kTileM - 1) / C::kTileM;
+  const int m0 = (tile % m_blocks) * C::kTileM;
+  const int n0 = (tile / m_blocks) * C::kTileN;
+  const int num_kb = (K + kBlockK - 1) / kBlockK;
+  const int per = num_kb / S;  // the host picks S that divides the k-blocks
+  const int kb0 = rank * per;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      ptx::mbar_init(bar_full + 8 * s, 1);
+      ptx::mbar_init(bar_empty + 8 * s, 1);
+    }
+    ptx::mbar_init(bar_tfull, 1);
+    *abort_flag = 0;
+    ptx::mbar_init_fence();
+    ptx::prefetch_tmap(&tmap_a);
+    ptx::prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(tmem_slot), C::kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      for (int i = 0; i < per; ++i) {
+        if (!ptx::mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, status, 31)) break;
+        const uint32_t sa = base + stage * C::kStageBytes;
+        const int kx = (kb0 + i) * kBlockK;
+        ptx::mbar_expect_tx(bar_full + 8 * stage, C::kStageBytes);
+        ptx::tma_load_2d(sa, &tmap_a, kx, m0, bar_full + 8 * stage);
+        ptx::tma_load_2d(sa + C::kStageA, &tmap_b, kx, n0, bar_full + 8 * stage);
+        if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::make_idesc(0u, 0u, kBlockM, C::kTileN);
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int i = 0; i < per; ++i) {
+        ok = ptx::mbar_wait(bar_full + 8 * stage, phase, abort_flag, status, 32);
+        if (!ok) break;
+        ptx::tc_fence_after();
+        const uint32_t sa = base + stage * C::kStageBytes;
+        const uint64_t a_desc = ptx::smem_desc_sw128(sa);
+        const uint64_t b_desc = ptx::smem_desc_sw128(sa + C::kStageA);
+#pragma unroll
+        for (int k = 0; k < kBlockK / kUmmaK; ++k)
+          ptx::mma_f8f6f4(tmem_base, a_desc + 2u * k, b_desc + 2u * k, idesc, (i | k) != 0 ? 1u : 0u);
+        ptx::tc_commit(bar_empty + 8 * stage);
+        if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+      }
+      if (ok) ptx::tc_commit(bar_tfull);
+    }
+    __syncwarp();
+  }
+
+  // ---- cluster-wide reduction. Every thread of every CTA takes part in the cluster barriers;
+  // the four epilogue warps do the work.
+  // No CTA may receive partial rows before its own pipeline has stopped using the stages:
+  // each CTA waits for its accumulator (all its MMAs, hence all its TMA loads, are done), then
+  // the first cluster barrier says so to the others.
+  const bool epi = warp >= 2;
+  const int quad = warp & 3;
+  const int epi_tid = threadIdx.x - 64;
+  constexpr int rows_per = kBlockM / S;  // rows of the tile this CTA reduces
+  if (epi) {
+    int okw = 0;
+    if (lane == 0) okw = ptx::mbar_wait(bar_tfull, 0, abort_flag, status, 33) ? 1 : 0;
+    okw = __shfl_sync(0xffffffffu, okw, 0);
+    (void)okw;  // on a time-out the status word is set; the barriers below are still honoured
+    ptx::tc_fence_after();
+  }
+  ptx::cluster_arrive();
+  ptx::cluster_wait();
+  if (epi) {
+    // accumulator row r -> owner CTA r / rows_per, slot `rank`, fp32 [rows_per][1024 bytes] per
+    // slot, 16-byte pieces XOR-swizzled by (row & 7) (conflict-free for the stores and the loads)
+    const int r = quad * 32 + lane;
+    const int owner = r / rows_per;
+    const int rl = r % rows_per;
+    const uint32_t dst_row = ptx::mapa(base + (rank * rows_per + rl) * 1024, owner);
+    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+#pragma unroll 1
+    for (int c = 0; c < C::kTileN / 32; ++c) {
+      uint32_t v[32];
+      ptx::tmem_ld_32x32(taddr + c * 32, v);
+      ptx::tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        ptx::st_cluster_u32x4(dst_row + (((c * 8 + j) ^ (rl & 7)) << 4), v[4 * j], v[4 * j + 1], v[4 * j + 2],
+                              v[4 * j + 3]);
+    }
+  }
+  ptx::cluster_arrive();  // release: the remote stores above; acquire: the other CTAs' into this one
+  ptx::cluster_wait();
+  if (epi) {
+    constexpr int kPieces = rows_per * (C::kTileN / 4) / 128;  // 16-byte pieces per thread: 64 / S
+    constexpr int kBatch = kPieces < 8 ? kPieces : 8;
+#pragma unroll 1
+    for (int b0 = 0; b0 < kPieces; b0 += kBatch) {
+      float sav[kBatch];
+      float4 sbv[kBatch];
+      uint2 resv[kBatch];  // EPI 2: the residual piece, fetched with the other loads
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b) {
+        const int idx = (b0 + b) * 128 + epi_tid;
+        const int rl = idx / (C::kTileN / 4);
+        const int ch = idx % (C::kTileN / 4);
+        const int row = m0 + rank * rows_per + rl;
+        const int col = n0 + ch * 4;
+        sav[b] = row < M ? __ldg(scale_a + row) : 0.f;
+        sbv[b].x = col + 0 < N ? __ldg(scale_b + col + 0) : 0.f;
+        sbv[b].y = col + 1 < N ? __ldg(scale_b + col + 1) : 0.f;
+        sbv[b].z = col + 2 < N ? __ldg(scale_b + col + 2) : 0.f;
+        sbv[b].w = col + 3 < N ? __ldg(scale_b + col + 3) : 0.f;
+        resv[b] = make_uint2(0u, 0u);
+        if constexpr (EPI == 2) {
+          if (row < M && col + 4 <= N)
+            resv[b] = *reinterpret_cast<const uint2*>(out + static_cast<int64_t>(row) * ldo + col);
+        }
+      }
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b) {
+        const int idx = (b0 + b) * 128 + epi_tid;
+        const int rl = idx / (C::kTileN / 4);
+        const int ch = idx % (C::kTileN / 4);
+        const uint8_t* src = smem + rl * 1024 + ((ch ^ (rl & 7)) << 4);
+        float4 sum = *reinterpret_cast<const float4*>(src);
+#pragma unroll
+        for (int pr = 1; pr < S; ++pr) {
+          const float4 v = *reinterpret_cast<const float4*>(src + pr * rows_per * 1024);
+          sum.x = __fadd_rn(sum.x, v.x);
+          sum.y = __fadd_rn(sum.y, v.y);
+          sum.z = __fadd_rn(sum.z, v.z);
+          sum.w = __fadd_rn(sum.w, v.w);
+        }
+        const int row = m0 + rank * rows_per + rl;
+        const int col = n0 + ch * 4;
+        if (row < M && col < N) {
+          const float sa = sav[b];
+          float o[4] = {__fmul_rn(__fmul_rn(sum.x, sa), sbv[b].x), __fmul_rn(__fmul_rn(sum.y, sa), sbv[b].y),
+                        __fmul_rn(__fmul_rn(sum.z, sa), sbv[b].z), __fmul_rn(__fmul_rn(sum.w, sa), sbv[b].w)};
+          OutT* dst = out + static_cast<int64_t>(row) * ldo + col;
+          if constexpr (EPI == 2) {
+            if (col + 4 <= N) {
+              o[0] = __fadd_rn(round_bf16(o[0]), bf16lo(resv[b].x));
+              o[1] = __fadd_rn(round_bf16(o[1]), bf16hi(resv[b].x));
+              o[2] = __fadd_rn(round_bf16(o[2]), bf16lo(resv[b].y));
+              o[3] = __fadd_rn(round_bf16(o[3]), bf16hi(resv[b].y));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                if (col + j < N)
+                  o[j] = __fadd_rn(round_bf16(o[j]), __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(dst)[j]));
+            }
+          }
+          if (col + 4 <= N) {
+            if constexpr (sizeof(OutT) == 4) {
+              *reinterpret_cast<float4*>(dst) = make_float4(o[0], o[1], o[2], o[3]);
+            } else {
+              *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (col + j < N) {
+                if constexpr (sizeof(OutT) == 4) dst[j] = o[j];
+                else dst[j] = __float2bfloat16_rn(o[j]);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -892,6 +1137,75 @@ static bool use_pair(int M, int N) {
   return tiles >= 3 * (sm_count() / 2);
 }
 
+// Split-K over a cluster: the largest S in {8, 4, 2} that divides the k-blocks, leaves each CTA
+// at least two of them and keeps tiles x S within the SM count; 1 when no such S exists, 0 when
+// the shape has too many rows or tiles for this kernel.
+static int pick_splits(int M, int N, int K) {
+  const int64_t tiles = static_cast<int64_t>(ceil_div(M, SplitCfg::kTileM)) * ceil_div(N, SplitCfg::kTileN);
+  const int num_kb = ceil_div(K, kBlockK);
+  if (M > 1024 || tiles > sm_count()) return 0;
+  for (int s = 8; s >= 2; s >>= 1)
+    if (num_kb % s == 0 && num_kb / s >= 2 && tiles * s <= sm_count()) return s;
+  return 1;
+}
+
+// Chosen by itself only for long reductions (K >= 4096: the down projection of a one-request
+// step), where the serial K loop of a lone CTA costs more than the exchange of partial tiles:
+// distributed shared memory moved only ~11 bytes per clock and SM in the measurements, so for
+// shorter K the kernels above are faster.
+static int auto_splits(int M, int N, int K) {
+  if (ceil_div(K, kBlockK) < 32) return 0;
+  const int s = pick_splits(M, N, K);
+  return s >= 2 ? s : 0;
+}
+
+template <typename OutT, int EPI>
+static int launch_splitk(const void* a, const void* b, const float* sa, const float* sb, void* out, int64_t ldo, int M,
+                         int N, int K, int64_t lda, int64_t ldb, int splits, cudaStream_t stream) {
+  using C = SplitCfg;
+  CUtensorMap ta, tb;
+  int st = make_tmap_u8(&ta, a, M, K, lda, kBlockM);
+  if (st != FR_OK) return st;
+  st = make_tmap_u8(&tb, b, N, K, ldb, C::kTileN);
+  if (st != FR_OK) return st;
+  using Kern = void (*)(const CUtensorMap, const CUtensorMap, OutT*, int64_t, const float*, const float*, int, int, int,
+                        int*);
+  Kern kern = nullptr;
+  switch (splits) {
+    case 1: kern = gemm_fp8_splitk_kernel<OutT, EPI, 1>; break;
+    case 2: kern = gemm_fp8_splitk_kernel<OutT, EPI, 2>; break;
+    case 4: kern = gemm_fp8_splitk_kernel<OutT, EPI, 4>; break;
+    case 8: kern = gemm_fp8_splitk_kernel<OutT, EPI, 8>; break;
+    default: return FR_ERR_UNSUPPORTED;
+  }
+  static bool attr_done[9] = {false};
+  if (!attr_done[splits]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
+      return FR_ERR_CUDA;
+    attr_done[splits] = true;
+  }
+  int* status = device_status_ptr();
+  if (!status) return FR_ERR_CUDA;
+  const int tiles = ceil_div(M, C::kTileM) * ceil_div(N, C::kTileN);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles * splits);
+  cfg.blockDim = dim3(C::kThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = splits;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, static_cast<OutT*>(out), ldo, sa, sb, M, N, K, status) != cudaSuccess) {
+    cudaGetLastError();
+    return FR_ERR_CUDA;
+  }
+  return FR_OK;
+}
+
 }  // namespace gemm
 }  // namespace fr
 
@@ -909,6 +1223,15 @@ extern "C" int fr_gemm_fp8_w8a8(const void* a, const void* b, const float* scale
   FR_CHECK_ARG(out_is_f32 ? (ldo % 4 == 0) : (ldo % 8 == 0));
   FR_CHECK_ARG(K % 16 == 0);
   FR_CHECK_SUPPORTED(out_is_f32 ? (bias == nullptr) : true);
+  if (bias == nullptr && (block_n_hint == 1024 || block_n_hint == 0)) {
+    int splits = block_n_hint == 1024 ? gemm::pick_splits(M, N, K) : gemm::auto_splits(M, N, K);
+    if (block_n_hint == 1024 && splits == 0) splits = 1;
+    if (splits >= 1)
+      return out_is_f32 ? gemm::launch_splitk<float, 0>(a, b, scale_a, scale_b, out, ldo, M, N, K, lda, ldb, splits,
+                                                        stream)
+                        : gemm::launch_splitk<__nv_bfloat16, 0>(a, b, scale_a, scale_b, out, ldo, M, N, K, lda, ldb,
+                                                                splits, stream);
+  }
   if (block_n_hint == 512 || (block_n_hint == 0 && gemm::use_pair(M, N))) {
     return out_is_f32 ? gemm::launch_pair<float, 0>(a, b, scale_a, scale_b, bias, out, ldo, M, N, K, lda, ldb, stream)
                       : gemm::launch_pair<__nv_bfloat16, 0>(a, b, scale_a, scale_b, bias, out, ldo, M, N, K, lda, ldb,
@@ -954,6 +1277,13 @@ extern "C" int fr_gemm_fp8_w8a8_add(const void* a, const void* b, const float* s
   FR_CHECK_ARG(a && b && scale_a && scale_b && residual_inout);
   FR_CHECK_ARG(aligned16(a) && aligned16(b) && aligned16(residual_inout));
   FR_CHECK_ARG(lda >= K && ldb >= K && ldr >= N && lda % 16 == 0 && ldb % 16 == 0 && ldr % 8 == 0 && K % 16 == 0);
+  if (block_n_hint == 1024 || block_n_hint == 0) {
+    int splits = block_n_hint == 1024 ? gemm::pick_splits(M, N, K) : gemm::auto_splits(M, N, K);
+    if (block_n_hint == 1024 && splits == 0) splits = 1;
+    if (splits >= 1)
+      return gemm::launch_splitk<__nv_bfloat16, 2>(a, b, scale_a, scale_b, residual_inout, ldr, M, N, K, lda, ldb, splits,
+                                                   stream);
+  }
   if (block_n_hint == 512 || (block_n_hint == 0 && gemm::use_pair(M, N)))
     return gemm::launch_pair<__nv_bfloat16, 2>(a, b, scale_a, scale_b, nullptr, residual_inout, ldr, M, N, K, lda, ldb,
                                                stream);
