@@ -58,6 +58,8 @@ def parse():
     ap.add_argument("--profile-wave", action="store_true",
                     help="run one eager (non-graph) wave between cudaProfilerStart/Stop and exit (for ncu "
                          "--profile-from-start off)")
+    ap.add_argument("--gemm-shapes", type=int, default=0, metavar="ROWS",
+                    help="time the FP8 GEMM of every layer shape at ROWS rows (this library and cuBLASLt) and exit")
     ap.add_argument("--profile-kernels", action="store_true",
                     help="launch each hot kernel once at the wave's shapes (random inputs) between "
                          "cudaProfilerStart/Stop and exit (for ncu --set full --profile-from-start off)")
@@ -270,6 +272,52 @@ def time_gemms(torch, rows: int, iters: int = 10):
     return fused_flops, fused_sec, flops, sec, lib
 
 
+def gemm_shapes(rows: int):
+    """FP8 GEMM time of every linear-layer shape of the step at ``rows`` rows (512 = the decode
+    step of a single request), this library and cuBLASLt (``torch._scaled_mm``) side by side:
+    20 launches per CUDA graph, two replays timed with CUDA events (weights stay L2-resident)."""
+    import torch
+
+    from flashrec_b200.kernel.sglops import fp8_scaled_mm
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    fp8 = torch.float8_e4m3fn
+    shapes = {"qkv": (4096, 2048), "o": (2048, 2048), "gate_up": (12288, 2048), "down": (2048, 6144),
+              "config1": (6144, 2048), "sid_head_level": (8192, 2048)}
+    out = {}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def graph_us(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(20):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        g.replay()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / 40
+
+    for name, (n, k) in shapes.items():
+        a = torch.randn(rows, k, device=dev).to(fp8)
+        b = torch.randn(n, k, device=dev).to(fp8)
+        sa = torch.rand(rows, 1, device=dev) + 0.5
+        sb = torch.rand(n, device=dev) + 0.5
+        flops = 2.0 * rows * n * k
+        us = graph_us(lambda: fp8_scaled_mm(a, b.t(), sa, sb, torch.bfloat16))
+        lib = graph_us(lambda: torch._scaled_mm(a, b.t(), scale_a=sa, scale_b=sb.view(1, -1),
+                                                out_dtype=torch.bfloat16))
+        out[name] = {"N": n, "K": k, "us": round(us, 2), "tflops": round(flops / us / 1e6, 1),
+                     "cublaslt_us": round(lib, 2), "cublaslt_tflops": round(flops / lib / 1e6, 1)}
+    print(json.dumps({"gemm_shapes_rows": rows, "shapes": out}))
+
+
 def profile_kernels(rows: int):
     """One launch of every hot kernel at the bench shapes, for a small ncu capture
     (about 1.5 GB resident, each kernel a fraction of a millisecond)."""
@@ -324,6 +372,12 @@ def main():
     args = parse()
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.gemm_shapes:
+        import torch
+
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        gemm_shapes(args.gemm_shapes)
         return
     if args.profile_kernels:
         import torch
