@@ -211,8 +211,11 @@ using topk::compose;
 using topk::SelectSmem;
 
 // Candidate enumeration. Calls f(composite) for every live candidate of request n.
+// `rng` (FULL + CSR trie): per beam the [first, last) positions of its node's edges in the sorted
+// key array, found once per launch; a negative first position means "no range, scan the level".
 template <bool FULL, class F>
-__device__ __forceinline__ void for_each_candidate(const StepParams& p, int n, bool masked, F&& f) {
+__device__ __forceinline__ void for_each_candidate(const StepParams& p, int n, bool masked, const int64_t* rng,
+                                                   F&& f) {
   if constexpr (!FULL) {
     const uint32_t M = static_cast<uint32_t>(p.BW) * p.C;
     const float* cum_n = p.cum + static_cast<size_t>(n) * p.BW;
@@ -241,8 +244,7 @@ __device__ __forceinline__ void for_each_candidate(const StepParams& p, int n, b
       if (tr.kind == FR_TRIE_CSR && node >= 0) {
         // only the node's own edges can be legal: walk its slice of the sorted key array
         const int64_t k0 = node * tr.vsz + level_off;
-        const int64_t e0 = lower_bound(tr.keys, tr.n_edges, k0);
-        const int64_t e1 = lower_bound(tr.keys, tr.n_edges, k0 + p.C);
+        const int64_t e0 = rng[2 * b], e1 = rng[2 * b + 1];
         for (int64_t e = e0 + lane; e < e1; e += 32) {
           const int64_t c = __ldg(tr.keys + e) - k0;
           const float s = __fadd_rn(cumb, __fsub_rn(__fsub_rn(lg[c], mx), ls));
@@ -297,6 +299,7 @@ __global__ void __launch_bounds__(kThreads, 1) beam_step_kernel(StepParams p) {
   int64_t* sel_token = reinterpret_cast<int64_t*>(win + kp2);          // [K]
   int64_t* sel_child = sel_token + p.K;                                // [K]
   int32_t* sel_parent = reinterpret_cast<int32_t*>(sel_child + p.K);   // [K]
+  int64_t* rng = reinterpret_cast<int64_t*>(dyn + ((kp2 * 8 + p.K * 20 + 15) & ~15));  // [2 * BW], FULL + CSR only
 
   const bool masked = FULL || (p.apply_mask && p.node_in && p.trie.kind != FR_TRIE_NONE);
   const uint32_t M = static_cast<uint32_t>(p.BW) * p.C;
@@ -319,9 +322,30 @@ __global__ void __launch_bounds__(kThreads, 1) beam_step_kernel(StepParams p) {
     }
   }
 
+  if constexpr (FULL) {
+    if (p.trie.kind == FR_TRIE_CSR) {
+      // every enumeration pass below walks the beams' edge lists: find each list once (one
+      // binary-search pair per thread, all beams in parallel) instead of once per pass and warp
+      const int64_t level_off = p.level_tok_base + p.idx_base - p.trie.token_base;
+      for (int b = threadIdx.x; b < p.BW; b += kThreads) {
+        const size_t row = static_cast<size_t>(n) * p.BW + b;
+        const int64_t node = p.node_in ? p.node_in[row] : -1;
+        int64_t e0 = -1, e1 = -1;
+        if (node >= 0 && p.cum[row] != p.neg_inf) {
+          const int64_t k0 = node * p.trie.vsz + level_off;
+          e0 = lower_bound(p.trie.keys, p.trie.n_edges, k0);
+          e1 = lower_bound(p.trie.keys, p.trie.n_edges, k0 + p.C);
+        }
+        rng[2 * b] = e0;
+        rng[2 * b + 1] = e1;
+      }
+      __syncthreads();
+    }
+  }
+
   // ---- select + sort ---------------------------------------------------------
   const int nvalid = topk::radix_select_topk<kThreads>(
-      [&](auto&& f) { for_each_candidate<FULL>(p, n, masked, f); }, p.K, win, kp2, sm);
+      [&](auto&& f) { for_each_candidate<FULL>(p, n, masked, rng, f); }, p.K, win, kp2, sm);
 
   // ---- outputs ---------------------------------------------------------------
   const int64_t* tok_n = FULL ? nullptr : p.tok + static_cast<size_t>(n) * M;
@@ -468,15 +492,17 @@ static int make_trie(const fr_trie* t, Trie* out) {
   return FR_OK;
 }
 
-static size_t step_smem(int K) {
+static size_t step_smem(int K, int BW, bool edge_ranges) {
   int kp2 = 1;
   while (kp2 < K) kp2 <<= 1;
-  return static_cast<size_t>(kp2) * 8 + static_cast<size_t>(K) * (8 + 8 + 4) + 16;
+  size_t b = (static_cast<size_t>(kp2) * 8 + static_cast<size_t>(K) * (8 + 8 + 4) + 15) & ~static_cast<size_t>(15);
+  if (edge_ranges) b += static_cast<size_t>(BW) * 16;
+  return b + 16;
 }
 
 template <bool FULL>
 static int launch_step(const StepParams& p, cudaStream_t stream) {
-  const size_t smem = step_smem(p.K);
+  const size_t smem = step_smem(p.K, p.BW, FULL && p.trie.kind == FR_TRIE_CSR);
   auto kern = beam_step_kernel<FULL>;
   if (smem > 32 * 1024) {  // static shared memory counts towards the 48 KiB default limit
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)

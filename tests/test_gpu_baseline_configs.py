@@ -1,0 +1,106 @@
+"""GPU parity at the sizes the baseline configurations name (through the C ABI).
+
+Config 1: RMSNorm -> FP8 then one W8A8 linear, 512 rows x 2048 -> 6144, seed-0 inputs.
+Config 3: trie-constrained SID head, 512 beams, 3 levels x 8192 codes, a catalog of uniform random
+3-tuples (200k here: the catalog size changes the trie, not the kernels), CSR and bitmap tries, three
+decode steps: every step against the CPU oracle bit for bit, and the properties the step must have
+at any size (legal SIDs only, sorted scores, distinct beams, layouts agree).
+Config 2 at full size is the last case of tests/test_gpu_engine.py::test_decoder_layer_vs_oracle.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import sid_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+FP8 = torch.float8_e4m3fn
+
+
+def _bytes(t):
+    return t.detach().cpu().contiguous().view(torch.uint8).numpy()
+
+
+def test_config1_rmsnorm_fp8_linear_512x2048x6144():
+    from flashrec_b200.kernel.rms_fp8 import rmsnorm_per_token_quant_fp8
+    from flashrec_b200.kernel.sglops import fp8_scaled_mm
+    from flashrec_b200.layers import quantize_weight_fp8
+
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(512, 2048, generator=g).bfloat16()
+    gamma = (1 + 0.1 * torch.randn(2048, generator=g)).bfloat16()
+    w = 0.02 * torch.randn(6144, 2048, generator=g)
+    q_ref, s_ref = O.rmsnorm_quant_fp8(x, gamma, 1e-6)
+    wq_ref, ws_ref = O.quantize_weight_fp8(w)
+    out_ref = O.fp8_scaled_mm(q_ref, wq_ref, s_ref, ws_ref).float()
+
+    q, s = rmsnorm_per_token_quant_fp8(x.to(DEV), gamma.to(DEV), 1e-6)
+    assert np.array_equal(_bytes(q), _bytes(q_ref)) and torch.equal(s.cpu(), s_ref)  # FP8 bytes and scales: bit-exact
+    wq, ws = quantize_weight_fp8(w.to(DEV))
+    assert np.array_equal(_bytes(wq), _bytes(wq_ref)) and torch.equal(ws.cpu().reshape(-1), ws_ref.reshape(-1))
+    out = fp8_scaled_mm(q, wq.t(), s, ws, torch.bfloat16)
+    assert out.shape == (512, 6144) and out.dtype == torch.bfloat16
+    err = (out.float().cpu() - out_ref).abs().max() / out_ref.abs().max()
+    assert err < 2e-2, err  # bf16 GEMM output: 2e-2 relative
+    # every kernel that can take this shape stays within the same bound
+    for hint in (64, 128, 256, 512, 1024):
+        o2 = fp8_scaled_mm(q, wq.t(), s, ws, torch.bfloat16, block_n=hint)
+        assert (o2.float().cpu() - out_ref).abs().max() / out_ref.abs().max() < 2e-2, hint
+
+
+@pytest.mark.parametrize("catalog", [200_000])
+def test_config3_trie_constrained_head_three_steps(catalog):
+    from flashrec_b200.logits import RestrictedLMHead
+    from flashrec_b200.sid_decode import sid_beam_step
+    from flashrec_b200.trie import build_trie_arrays, trie_to_device
+
+    bw, kl, hidden, base = 512, 8192, 2048, 151_936
+    sizes = [kl, kl, kl]
+    items = np.unique(np.random.default_rng(0).integers(0, kl, (catalog, 3)), axis=0)
+    arrays = build_trie_arrays(items, sizes, base)
+    otr = O.OracleTrie(arrays.csr_keys, arrays.edge_child, arrays.vsz, base, arrays.invalid_node)
+    legal = {tuple(r) for r in items.tolist()}
+
+    g = torch.Generator().manual_seed(3)
+    w = 0.02 * torch.randn(3 * kl, hidden, generator=g)
+    wq, ws = O.quantize_weight_fp8(w)
+    head = RestrictedLMHead(list(range(base, base + 3 * kl)))
+    head.bind_quantized(wq.to(DEV), ws.reshape(-1).to(DEV))
+    head.bind_codebook(sizes)
+    hs = [torch.randn(bw, hidden, generator=torch.Generator().manual_seed(lv)).bfloat16() for lv in range(3)]
+
+    results = {}
+    for layout in ("csr", "bitmap"):
+        trie = trie_to_device(arrays, layout, DEV)
+        cum = torch.full((1, bw), float("-inf"))
+        cum[0, 0] = 0.0  # step 0: one live beam at the root
+        nodes = torch.zeros((1, bw), dtype=torch.int64)
+        toks = torch.zeros((1, bw, 3), dtype=torch.int64)
+        cum_d, nodes_d, toks_d = cum.to(DEV), nodes.to(DEV), toks.to(DEV)
+        for lv in range(3):
+            lg, mx, ls, _ = head.logits_level(hs[lv].to(DEV), lv)
+            tok_out = torch.zeros_like(toks_d)
+            node_out = torch.zeros_like(nodes_d)
+            col = torch.full((1,), lv, dtype=torch.int32, device=DEV)
+            out = sid_beam_step(cum_d, lg, mx, ls, nodes_d, trie, base + kl * lv, bw, token_ids_in=toks_d,
+                                token_ids_out=tok_out, node_ids_out=node_out, col=col)
+            # the CPU oracle on the device's own logits and statistics (the head GEMM has its own test)
+            ref = O.sid_beam_step(cum_d.cpu(), lg.cpu(), nodes_d.cpu(), otr, base + kl * lv, bw,
+                                  token_ids=toks_d.cpu(), col=lv, stats=(mx.cpu(), ls.cpu()))
+            assert torch.equal(out.vals.cpu(), ref["vals"]), (layout, lv)
+            assert torch.equal(out.parents.cpu(), ref["parents"]) and torch.equal(out.tokens.cpu(), ref["tokens"])
+            assert torch.equal(tok_out.cpu(), ref["token_ids"]) and torch.equal(node_out.cpu(), ref["node_ids"])
+            v = out.vals[0]
+            assert (v[:-1] >= v[1:]).all()  # sorted scores
+            cum_d, nodes_d, toks_d = out.vals.clone(), node_out, tok_out
+        live = torch.isfinite(cum_d[0]).cpu().numpy()
+        assert live.sum() == bw  # a 200k-item catalog keeps all 512 beams alive after three levels
+        codes = (toks_d[0].cpu() - torch.tensor([base, base + kl, base + 2 * kl])).numpy()
+        rows = [tuple(c) for c in codes[live]]
+        assert all(r in legal for r in rows)  # illegal-SID rate 0
+        assert len(set(rows)) == len(rows)  # beams are distinct items
+        assert (nodes_d[0].cpu().numpy()[live] == -1).all()  # complete SIDs: leaves reached
+        results[layout] = (cum_d.cpu(), toks_d.cpu())
+    assert torch.equal(results["csr"][0], results["bitmap"][0]) and torch.equal(results["csr"][1], results["bitmap"][1])

@@ -13,18 +13,24 @@ DEV = "cuda:0"
 FP8 = torch.float8_e4m3fn
 
 
-@pytest.mark.parametrize("rows,prompt", [(48, 70), (130, 257)])
-def test_decoder_layer_vs_oracle(rows, prompt):
-    """Config-2 geometry scaled down in width only where the kernels allow any width
-    (hidden 512, 4 q heads / 2 kv heads x 128, intermediate 1024)."""
+@pytest.mark.parametrize("rows,prompt,H,HQ,HKV,I,tc", [
+    (48, 70, 512, 4, 2, 1024, False),
+    (130, 257, 512, 4, 2, 1024, True),
+    # BASELINE config 2 at full size: Qwen3-1.7B layer geometry, 512 beam rows, 256-token shared prefix
+    (512, 256, 2048, 16, 8, 6144, True),
+])
+def test_decoder_layer_vs_oracle(rows, prompt, H, HQ, HKV, I, tc):
+    """One decoder layer at one decode step against the oracle, stage by stage: config-2 geometry scaled
+    down in width (the kernels allow any width) and at its full size; ``tc`` selects the tcgen05 attention
+    path (caller scratch) instead of the kernel without scratch."""
     from flashrec_b200.attention import AttentionBackend, TokenToKVPool
     from flashrec_b200.decoder import ForwardBatch, Qwen3Config, Qwen3DecoderLayer
     from flashrec_b200.layers import RotaryEmbedding
 
-    cfg = Qwen3Config(hidden_size=512, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
-                      intermediate_size=1024, num_hidden_layers=1, max_position_embeddings=512)
+    D = 128
+    cfg = Qwen3Config(hidden_size=H, num_attention_heads=HQ, num_key_value_heads=HKV, head_dim=D,
+                      intermediate_size=I, num_hidden_layers=1, max_position_embeddings=512)
     g = torch.Generator().manual_seed(rows)
-    H, HQ, HKV, D, I = 512, 4, 2, 128, 1024
     wf = dict(qkv=0.02 * torch.randn((HQ + 2 * HKV) * D, H, generator=g), o=0.02 * torch.randn(H, HQ * D, generator=g),
               gate_up=0.02 * torch.randn(2 * I, H, generator=g), down=0.02 * torch.randn(H, I, generator=g))
     w = {k: O.quantize_weight_fp8(v) for k, v in wf.items()}
@@ -51,7 +57,7 @@ def test_decoder_layer_vs_oracle(rows, prompt):
     pool = TokenToKVPool(1, slots, HKV, D, FP8, DEV, page_size=page)
     pool.k[0].copy_(kc.to(DEV))
     pool.v[0].copy_(vc.to(DEV))
-    attn = AttentionBackend(pool, HQ, HKV, D)
+    attn = AttentionBackend(pool, HQ, HKV, D, max_shared_len=prompt + 1 if tc else 0)
     attn.set_groups(torch.tensor([0, rows], dtype=torch.int32, device=DEV), rows)
     layer = Qwen3DecoderLayer(cfg, 0, attn, RotaryEmbedding(D, 512, 1e6, device=DEV), device=DEV)
     sa, mlp = layer.self_attn, layer.mlp
