@@ -1,4 +1,4 @@
-"""Benchmark of the quantized SID decode step (see DESIGN.md for the workload).
+"""Benchmark of the quantized SID decode step.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 

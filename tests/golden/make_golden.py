@@ -195,7 +195,10 @@ def main() -> None:
 
 
 if __name__ == "__main__":
-    ref = os.environ.get("FLASHREC_REFERENCE", "/root/reference/python")
+    # the reference checkout's `python/` directory: argument 1 or $FLASHREC_REFERENCE
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FLASHREC_REFERENCE")
+    if not ref:
+        sys.exit("usage: make_golden.py <reference checkout>/python   (or set FLASHREC_REFERENCE)")
     if ref not in sys.path:
         sys.path.insert(0, ref)
     main()
