@@ -77,6 +77,8 @@ _SIGNATURES = {
     "fr_silu_mul_bf16": [P, P, _I, _I, P],
     "fr_gemm_fp8_w8a8": [P, P, P, P, P, P, _I, _I, _I, _I, _L, _L, _L, _I, P],
     "fr_gemm_fp8_w8a8_add": [P, P, P, P, P, _I, _I, _I, _L, _L, _L, _I, P],
+    "fr_gemm_fp8_qkv_rope": [P, P, P, P, P, _L, _I, _I, _I, _I, _I, _L, _L, P, P, P, P, _F, P, _I, P, P, _L, _L, _L, _L, _I,
+                             P],
     "fr_gemm_fp8_silu_mul": [P, P, P, P, P, P, _I, _I, _I, _L, _L, _L, _I, P],
     "fr_quant_known_amax_fp8": [P, P, P, P, _I, _I, P],
     "fr_qk_norm_rope_kv_fp8": [P, P, P, _L, _L, _L, _L, _L, _L, P, P, P, P, _F, P, _I, P, P, _L, _L, _L, _L, _I,

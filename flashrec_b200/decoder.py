@@ -14,7 +14,7 @@ import torch
 
 from flashrec_b200._lib import call, ptr, stream_ptr
 from flashrec_b200.attention import AttentionBackend, TokenToKVPool
-from flashrec_b200.kernel.qk_rope_kv import fused_qk_norm_rope_store_fp8
+from flashrec_b200.kernel.qk_rope_kv import fp8_qkv_mm_norm_rope_store, fused_qk_norm_rope_store_fp8
 from flashrec_b200.kernel.sglops import (fp8_scaled_mm_silu_mul, interleave_gate_up, per_token_quant_fp8,
                                          quant_known_amax_fp8)
 from flashrec_b200.kernel.silu_fp8 import silu_and_mul_per_token_quant_fp8
@@ -65,17 +65,32 @@ class Qwen3Attention:
         self.k_norm = RMSNorm(cfg.head_dim, cfg.rms_norm_eps, device=device)
         self.attn = attn
         self.rotary = rotary
+        # run QK-norm + RoPE + the FP8 KV write inside the qkv GEMM's epilogue (same bits as the
+        # reference's call order qkv_proj -> fused_qk_norm_rope_store_fp8, which stays as the other branch)
+        self.fuse_rope_gemm = False
 
     def forward(self, x, batch: ForwardBatch, *, q_fp8, a_scale, residual_inout=None) -> torch.Tensor:
         """``residual_inout``: the o_proj GEMM adds its output to this bf16 residual stream in place
         (and returns it) instead of returning the projection."""
         t = int(q_fp8.shape[0])
+        pool = self.attn.kv_pool
+        if self.fuse_rope_gemm and self.head_dim == 128 and self.num_qo % 2 == 0 and self.num_kv % 2 == 0 \
+                and self.qkv_proj.bias is None:
+            # norm + RoPE + KV write in the qkv GEMM's epilogue: the qkv matrix is never materialised
+            q = fp8_qkv_mm_norm_rope_store(
+                q_fp8, self.qkv_proj._fp8_weight, a_scale, self.qkv_proj._fp8_scale, batch.positions,
+                batch.out_cache_loc, self.q_norm.weight, self.k_norm.weight, self.q_norm.eps,
+                self.rotary.cos_sin_cache, pool.k[self.layer_id], pool.v[self.layer_id], self.num_qo, self.num_kv)
+            o = self.attn.forward(q, None, None, self.layer_id, batch, skip_store=True)
+            if residual_inout is not None:
+                o_fp8, o_scale = per_token_quant_fp8(o.reshape(t, -1))
+                return self.o_proj.forward_fp8_add_(o_fp8, o_scale, residual_inout)
+            return self.o_proj(o.reshape(t, -1))
         qkv = self.qkv_proj.forward_fp8(q_fp8, a_scale, (t, self.qkv_proj.in_features), torch.bfloat16)
         heads = qkv.view(t, self.num_qo + 2 * self.num_kv, self.head_dim)
         q = heads[:, : self.num_qo]
         k = heads[:, self.num_qo : self.num_qo + self.num_kv]
         v = heads[:, self.num_qo + self.num_kv :]
-        pool = self.attn.kv_pool
         fused_qk_norm_rope_store_fp8(
             q, k, v, batch.positions, batch.out_cache_loc, self.q_norm.weight, self.k_norm.weight,
             self.q_norm.eps, self.rotary.cos_sin_cache, pool.k[self.layer_id], pool.v[self.layer_id],
@@ -161,7 +176,8 @@ class Qwen3ForCausalLM:
     """Embedding -> layers -> final (add+)RMSNorm; returns the normalised hidden
     states, which the SID head consumes (models/qwen3.py:227-273)."""
 
-    def __init__(self, cfg: Qwen3Config, attn: AttentionBackend, device, fuse_residual: bool = True):
+    def __init__(self, cfg: Qwen3Config, attn: AttentionBackend, device, fuse_residual: bool = True,
+                 fuse_rope_gemm: bool = False):
         self.cfg = cfg
         self.device = torch.device(device)
         # fold the residual adds into the o_proj / down_proj GEMM epilogues (same bits, one HBM
@@ -171,6 +187,8 @@ class Qwen3ForCausalLM:
         self.layers: List[Qwen3DecoderLayer] = [
             Qwen3DecoderLayer(cfg, i, attn, self.rotary, device=device) for i in range(cfg.num_hidden_layers)
         ]
+        for layer in self.layers:
+            layer.self_attn.fuse_rope_gemm = bool(fuse_rope_gemm)
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, device=device)
         self.embed_tokens: Optional[torch.Tensor] = None  # bf16 [vocab, hidden]
         self.attn = attn

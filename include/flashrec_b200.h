@@ -100,6 +100,22 @@ int fr_gemm_fp8_w8a8_add(const void* a, const void* b, const float* scale_a, con
                          void* residual_inout, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldr,
                          int block_n_hint, cudaStream_t stream);
 
+/* The qkv projection with fr_qk_norm_rope_kv_fp8 applied in the GEMM epilogue: the accumulator
+ * tile (two whole heads of 128 columns) is scaled and rounded to bf16 exactly as fr_gemm_fp8_w8a8
+ * would store it, then Q and K heads get the per-head RMSNorm and the NeoX rotation of the row's
+ * position; Q goes to q_out (bf16 [M, n_q * 128], row pitch ldq elements), K (rounded to bf16
+ * first) and V go as e4m3 to k_cache / v_cache[loc[m], head, :] (byte strides ck_*, cv_*; slots
+ * outside [0, num_slots) are skipped). The [M, (n_q + 2 n_kv) * 128] qkv matrix is never written.
+ * b: merged qkv weight e4m3 [(n_q + 2 n_kv) * 128, K]. head_dim == 128, n_q and n_kv even.
+ * Same bits as the two calls in sequence.
+ * Reference: Qwen3Attention.forward, qkv_proj followed by fused_qk_norm_rope_store_fp8
+ * (models/qwen3.py:76-108, kernel/qk_rope_kv.py:165-250). */
+int fr_gemm_fp8_qkv_rope(const void* a, const void* b, const float* scale_a, const float* scale_b, void* q_out,
+                         int64_t ldq, int M, int n_q, int n_kv, int head_dim, int K, int64_t lda, int64_t ldb,
+                         const int64_t* positions, const int64_t* loc, const void* q_weight, const void* k_weight,
+                         float eps, const float* cos_sin, int max_pos, void* k_cache, void* v_cache, int64_t ck_s,
+                         int64_t ck_h, int64_t cv_s, int64_t cv_h, int num_slots, cudaStream_t stream);
+
 /* gate_up GEMM with SwiGLU fused into the epilogue. b_interleaved / its scales:
  * the [2d, K] gate_up weight with rows regrouped per 256-row tile as
  * [gate rows 128t .. 128t+127 | up rows 128t .. 128t+127] (N = 2d, d % 128 == 0).

@@ -167,15 +167,16 @@ def test_engine_graph_equals_eager_and_sids_are_legal():
 
 
 def test_model_with_residual_adds_in_gemm_epilogues_equals_unfused_flow():
-    """Qwen3ForCausalLM(fuse_residual=True) (o_proj / down_proj GEMMs add into the residual stream, norms
-    without add) gives the bits of the reference's call order GEMM -> fused add + RMSNorm."""
+    """Qwen3ForCausalLM(fuse_residual=True, fuse_rope_gemm=True) (o_proj / down_proj GEMMs add into the
+    residual stream, norms without add; QK-norm + RoPE + KV write in the qkv GEMM's epilogue) gives the bits
+    of the reference's call order GEMM -> fused add + RMSNorm, qkv_proj -> fused_qk_norm_rope_store_fp8."""
     from flashrec_b200.attention import AttentionBackend, TokenToKVPool
     from flashrec_b200.decoder import ForwardBatch, Qwen3Config, Qwen3ForCausalLM
 
     cfg = Qwen3Config(hidden_size=512, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
                       intermediate_size=1024, num_hidden_layers=3, max_position_embeddings=256, vocab_size=600)
     rows, prompt = 300, 40
-    outs = []
+    outs, pools = [], []
     for fuse in (False, True):
         pool = TokenToKVPool(cfg.num_hidden_layers, 2048, cfg.num_key_value_heads, cfg.head_dim,
                              torch.float8_e4m3fn, DEV)
@@ -183,10 +184,11 @@ def test_model_with_residual_adds_in_gemm_epilogues_equals_unfused_flow():
         for layer in range(cfg.num_hidden_layers):
             pool.k[layer].copy_(torch.randn(pool.k[layer].shape, generator=g, device=DEV).to(torch.float8_e4m3fn))
             pool.v[layer].copy_(torch.randn(pool.v[layer].shape, generator=g, device=DEV).to(torch.float8_e4m3fn))
+        pools.append(pool)
         attn = AttentionBackend(pool, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
                                 max_shared_len=prompt + 4)
         attn.set_groups(torch.tensor([0, rows], dtype=torch.int32, device=DEV), rows)
-        model = Qwen3ForCausalLM(cfg, attn, DEV, fuse_residual=fuse)
+        model = Qwen3ForCausalLM(cfg, attn, DEV, fuse_residual=fuse, fuse_rope_gemm=fuse)
         model.init_random(seed=2)
         shared = torch.arange(1, prompt + 1, dtype=torch.int32)
         own = torch.arange(100, 100 + rows, dtype=torch.int32)
@@ -202,3 +204,6 @@ def test_model_with_residual_adds_in_gemm_epilogues_equals_unfused_flow():
         outs.append(model.forward(batch))
     assert torch.isfinite(outs[0].float()).all()
     assert torch.equal(outs[0], outs[1])
+    for layer in range(cfg.num_hidden_layers):  # and the KV pools hold the same bytes
+        assert torch.equal(pools[0].k[layer].view(torch.uint8), pools[1].k[layer].view(torch.uint8))
+        assert torch.equal(pools[0].v[layer].view(torch.uint8), pools[1].v[layer].view(torch.uint8))

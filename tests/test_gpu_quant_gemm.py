@@ -294,3 +294,42 @@ def test_gemm_add_into_residual_equals_gemm_then_bf16_add(m, n, k, block_n):
     assert out.data_ptr() == buf.data_ptr()
     assert np.array_equal(bits16(buf[:, :n].contiguous()), bits16(want))
     assert (buf[:, n:] == 7.0).all()
+
+
+@pytest.mark.parametrize("t,n_q,n_kv,k", [(300, 4, 2, 512), (37, 2, 2, 256), (1100, 16, 8, 2048)])
+def test_qkv_gemm_with_norm_rope_kv_epilogue_equals_the_two_calls(t, n_q, n_kv, k):
+    """fr_gemm_fp8_qkv_rope == qkv GEMM (bf16) -> fused_qk_norm_rope_store_fp8: Q bits, K / V pool bytes,
+    untouched slots; rows with out-of-range slots are skipped."""
+    from flashrec_b200.kernel.qk_rope_kv import fp8_qkv_mm_norm_rope_store, fused_qk_norm_rope_store_fp8
+    from flashrec_b200.kernel.sglops import fp8_scaled_mm
+
+    d = 128
+    g = torch.Generator().manual_seed(t + n_q)
+    a = torch.randn(t, k, generator=g).bfloat16()
+    w = 0.05 * torch.randn((n_q + 2 * n_kv) * d, k, generator=g)
+    aq, asc = O.per_token_quant_fp8(a)
+    wq, wsc = O.quantize_weight_fp8(w)
+    aq, asc, wq, wsc = aq.to(DEV), asc.to(DEV), wq.to(DEV), wsc.to(DEV)
+    qw = (1 + 0.1 * torch.randn(d, generator=g)).bfloat16().to(DEV)
+    kw = (1 + 0.1 * torch.randn(d, generator=g)).bfloat16().to(DEV)
+    cs = O.build_cos_sin_cache(d, 400, 1e6).to(DEV)
+    pos = torch.randint(0, 400, (t,), generator=g).to(DEV)
+    slots = t + 20
+    loc = (torch.randperm(slots - 1, generator=g)[:t] + 1)
+    loc[0] = -5          # outside the pool: no write
+    loc[t // 2] = slots  # outside the pool: no write
+    loc = loc.to(DEV)
+
+    def pools():
+        kc = torch.full((slots, n_kv, d), 0x11, dtype=torch.uint8, device=DEV).view(torch.float8_e4m3fn)
+        return kc, kc.clone()
+
+    qkv = fp8_scaled_mm(aq, wq.t(), asc, wsc, torch.bfloat16, block_n=256).view(t, n_q + 2 * n_kv, d)
+    kc_ref, vc_ref = pools()
+    fused_qk_norm_rope_store_fp8(qkv[:, :n_q], qkv[:, n_q:n_q + n_kv], qkv[:, n_q + n_kv:], pos, loc, qw, kw, 1e-6, cs,
+                                 kc_ref, vc_ref)
+    kc, vc = pools()
+    q = fp8_qkv_mm_norm_rope_store(aq, wq.t(), asc, wsc, pos, loc, qw, kw, 1e-6, cs, kc, vc, n_q, n_kv)
+    assert q.shape == (t, n_q, d)
+    assert np.array_equal(bits16(q), bits16(qkv[:, :n_q].contiguous()))
+    assert np.array_equal(bits8(kc), bits8(kc_ref)) and np.array_equal(bits8(vc), bits8(vc_ref))
