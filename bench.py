@@ -55,6 +55,8 @@ def parse():
     ap.add_argument("--items", type=int, default=1_000_000)
     ap.add_argument("--trie", default="csr", choices=["csr", "bitmap"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-fuse-rope-gemm", action="store_true",
+                    help="run QK-norm + RoPE + KV write as their own kernel instead of in the qkv GEMM's epilogue")
     ap.add_argument("--profile-wave", action="store_true",
                     help="run one eager (non-graph) wave between cudaProfilerStart/Stop and exit (for ncu "
                          "--profile-from-start off)")
@@ -412,7 +414,7 @@ def main():
     arrays = build_trie_arrays(make_catalog(args.items, sizes), sizes, token_base)
     trie = trie_to_device(arrays, args.trie, dev)
     eng = SidDecodeEngine(cfg, args.requests, args.beam, prompt_lengths(args.requests, rank), sizes, token_base, trie,
-                          dev, shared_prefix=64, page_size=16, seed=rank)
+                          dev, shared_prefix=64, page_size=16, seed=rank, fuse_rope_gemm=not args.no_fuse_rope_gemm)
     # count this library's kernel launches in one eager wave
     counter = {"n": 0}
     orig_call = _lib.call

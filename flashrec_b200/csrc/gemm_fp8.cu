@@ -555,7 +555,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     const int part = (warp - 2) >> 2;
     bool ok = true;
     int it = 0;
-    uint32_t quad_phase = 0;  // EPI 3: parity of the quadrant's exchange barrier
+    int xsel = 0;  // EPI 3: which exchange buffer the next sum-of-squares exchange uses
     if constexpr (EPI == 3) {
       // q- / k-norm weights as fp32 in shared memory, once per CTA
       float* wn = reinterpret_cast<float*>(out_stage);
@@ -573,7 +573,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       float* bss = bias_stage + buf * BLOCK_N;
       const int row = m0 + quad * 32 + lane;
       const float sa = row < M ? __ldg(scale_a + row) : 0.f;
-      if constexpr (EPI == 0 || EPI == 2) {  // the other epilogues read their scales straight from global memory
+      if constexpr (EPI != 1) {  // the SwiGLU epilogue reads its few scales straight from global memory
         for (int i = epi_tid; i < BLOCK_N; i += kEpiThreads) {
           const int n = n0 + i;
           sbs[i] = n < N ? __ldg(scale_b + n) : 0.f;
@@ -707,123 +707,123 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         }
         if (!ok) break;
       } else if constexpr (EPI == 3) {
-        // The tile is two whole heads of 128 columns. Warp part p of a lane quadrant takes
-        // columns [16p, 16p + 16) and their rotary partners [64 + 16p, +16) of both heads; the
-        // four parts of a quadrant add their sums of squares through shared memory (fp64, fixed
-        // order) behind a four-arrival mbarrier with a bounded wait.
-        const float* wn = reinterpret_cast<const float*>(out_stage);            // [q-norm 128 | k-norm 128]
-        double* xss = reinterpret_cast<double*>(out_stage + 1024);              // [2][4 quads][4 parts][32]
-        const uint32_t bar_q4 = bar_res + 8 * quad;
+        // The tile is two whole heads of 128 columns. Warp part p of a lane quadrant takes head
+        // p >> 1 of the tile: columns [32 s, 32 s + 32) and their rotary partners [64 + 32 s, +32),
+        // s = p & 1; the two warps of a (quadrant, head) add their sums of squares through shared
+        // memory (fp64, fixed order) behind a named barrier of their 64 threads. Each thread does
+        // one head per tile, so the two heads of a tile are worked on at the same time.
+        const float* wn = reinterpret_cast<const float*>(out_stage);  // [q-norm 128 | k-norm 128]
+        double* xss = reinterpret_cast<double*>(out_stage + 1024);    // [2][4 quads][4 parts][32]
         const int p = part;
+        const int hd = p >> 1, sh = p & 1;
         const bool row_ok = row < M;
-        const int head0 = n0 / 128;
-        const bool any_rot = head0 < rp.n_q + rp.n_kv;  // Q or K heads in this tile (both heads alike)
-        float cosv[16], sinv[16];
-        int64_t slot = -1;
-        if (row_ok && head0 >= rp.n_q) slot = __ldg(rp.loc + row);
-        if (any_rot) {
-          int64_t ps = row_ok ? __ldg(rp.pos + row) : 0;
-          ps = ps < 0 ? 0 : (ps >= rp.max_pos ? rp.max_pos - 1 : ps);
-          const float* cp = rp.cs + ps * 128 + 16 * p;
+        const int hg = n0 / 128 + hd;  // head index among [Q heads | K heads | V heads]
+        const bool is_q = hg < rp.n_q;
+        const bool is_k = !is_q && hg < rp.n_q + rp.n_kv;
+        const int c0 = hd * 128 + 32 * sh;
+        uint32_t a1[32], a2[32];
+        ptx::tmem_ld_32x32(taddr_row + c0, a1);
+        ptx::tmem_ld_32x32(taddr_row + c0 + 64, a2);
+        // independent of the accumulators: the row's position / slot (they lead to dependent loads)
+        int64_t ps = 0, slot = -1;
+        if (row_ok && (is_q || is_k)) ps = __ldg(rp.pos + row);
+        if (row_ok && !is_q) slot = __ldg(rp.loc + row);
+        ps = ps < 0 ? 0 : (ps >= rp.max_pos ? rp.max_pos - 1 : ps);
+        const float* cp = rp.cs + ps * 128 + 32 * sh;
+        ptx::tmem_ld_wait();
+        {  // last read of this accumulator buffer by this warp
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive_cluster(tempty_remote);
+        }
+        // the qkv GEMM's bf16 output values, in place
 #pragma unroll
-          for (int i = 0; i < 16; i += 4) {
-            const float4 c4 = __ldg(reinterpret_cast<const float4*>(cp + i));
-            const float4 s4 = __ldg(reinterpret_cast<const float4*>(cp + 64 + i));
-            cosv[i] = c4.x; cosv[i + 1] = c4.y; cosv[i + 2] = c4.z; cosv[i + 3] = c4.w;
-            sinv[i] = s4.x; sinv[i + 1] = s4.y; sinv[i + 2] = s4.z; sinv[i + 3] = s4.w;
+        for (int i = 0; i < 32; ++i) {
+          a1[i] = __float_as_uint(round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(a1[i]), sa), sbs[c0 + i])));
+          a2[i] = __float_as_uint(round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(a2[i]), sa), sbs[c0 + 64 + i])));
+        }
+        if (is_q || is_k) {
+          double sq[4] = {0.0, 0.0, 0.0, 0.0};  // four independent chains
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const double l = static_cast<double>(__uint_as_float(a1[i])), hh = static_cast<double>(__uint_as_float(a2[i]));
+            sq[i & 3] = fma(l, l, sq[i & 3]);
+            sq[i & 3] = fma(hh, hh, sq[i & 3]);
+          }
+          double* xs = xss + ((xsel * 16 + quad * 4 + hd * 2) * 32);
+          xsel ^= 1;  // alternate buffers per exchange: use n + 2 is separated from use n by barrier n + 1
+          xs[sh * 32 + lane] = (sq[0] + sq[1]) + (sq[2] + sq[3]);
+          // the two warps of this (quadrant, head) meet; both take the same path through every tile
+          asm volatile("bar.sync %0, 64;" ::"r"(2 + quad * 2 + hd) : "memory");
+          const double tot = xs[lane] + xs[32 + lane];
+          const float var = static_cast<float>(tot / 128.0);
+          const float rstd = rsqrt_rn(__fadd_rn(var, rp.eps));
+          const float* w = wn + (is_q ? 0 : 128) + 32 * sh;
+#pragma unroll
+          for (int i0 = 0; i0 < 32; i0 += 8) {
+            float cv[8], sv[8];
+#pragma unroll
+            for (int i = 0; i < 8; i += 4) {
+              const float4 c4 = __ldg(reinterpret_cast<const float4*>(cp + i0 + i));
+              const float4 s4 = __ldg(reinterpret_cast<const float4*>(cp + 64 + i0 + i));
+              cv[i] = c4.x; cv[i + 1] = c4.y; cv[i + 2] = c4.z; cv[i + 3] = c4.w;
+              sv[i] = s4.x; sv[i + 1] = s4.y; sv[i + 2] = s4.z; sv[i + 3] = s4.w;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float xa = __fmul_rn(__fmul_rn(__uint_as_float(a1[i0 + i]), rstd), w[i0 + i]);
+              const float xb = __fmul_rn(__fmul_rn(__uint_as_float(a2[i0 + i]), rstd), w[64 + i0 + i]);
+              a1[i0 + i] = __float_as_uint(__fsub_rn(__fmul_rn(xa, cv[i]), __fmul_rn(xb, sv[i])));
+              a2[i0 + i] = __float_as_uint(__fadd_rn(__fmul_rn(xb, cv[i]), __fmul_rn(xa, sv[i])));
+            }
           }
         }
-#pragma unroll 1
-        for (int h = 0; h < 2; ++h) {
-          const int hg = head0 + h;  // head index among [Q heads | K heads | V heads]
-          const int c0 = h * 128 + 16 * p;
-          uint32_t a1[16], a2[16];
-          ptx::tmem_ld_32x16(taddr_row + c0, a1);
-          ptx::tmem_ld_32x16(taddr_row + c0 + 64, a2);
-          ptx::tmem_ld_wait();
-          if (h == 1) {  // last read of this accumulator buffer by this warp
-            ptx::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive_cluster(tempty_remote);
-          }
-          float x1[16], x2[16];  // the qkv GEMM's bf16 output values
+        if (is_q) {
+          if (row_ok) {
+            __nv_bfloat16* dst = rp.q_out + static_cast<int64_t>(row) * rp.ldq + hg * 128 + 32 * sh;
+            uint4* d1 = reinterpret_cast<uint4*>(dst);
+            uint4* d2 = reinterpret_cast<uint4*>(dst + 64);
 #pragma unroll
-          for (int i = 0; i < 16; i += 4) {
-            const float4 b1 = __ldg(reinterpret_cast<const float4*>(scale_b + n0 + c0 + i));
-            const float4 b2 = __ldg(reinterpret_cast<const float4*>(scale_b + n0 + c0 + 64 + i));
-            x1[i] = round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(a1[i]), sa), b1.x));
-            x1[i + 1] = round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(a1[i + 1]), sa), b1.y));
-            x1[i + 2] = round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(a1[i + 2]), sa), b1.z));
-            x1[i + 3] = round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(a1[i + 3]), sa), b1.w));
-            x2[i] = round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(a2[i]), sa), b2.x));
-            x2[i + 1] = round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(a2[i + 1]), sa), b2.y));
-            x2[i + 2] = round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(a2[i + 2]), sa), b2.z));
-            x2[i + 3] = round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(a2[i + 3]), sa), b2.w));
-          }
-          const bool is_q = hg < rp.n_q;
-          const bool is_k = !is_q && hg < rp.n_q + rp.n_kv;
-          if (is_q || is_k) {
-            double ss = 0.0;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const double l = static_cast<double>(x1[i]), hh = static_cast<double>(x2[i]);
-              ss = fma(l, l, ss);
-              ss = fma(hh, hh, ss);
-            }
-            double* xs = xss + (((it * 2 + h) & 1) * 16 + quad * 4) * 32;
-            xs[p * 32 + lane] = ss;
-            __syncwarp();
-            int okq = 0;
-            if (lane == 0) {
-              ptx::mbar_arrive(bar_q4);
-              okq = ptx::mbar_wait(bar_q4, quad_phase, abort_flag, status, 26) ? 1 : 0;
-            }
-            okq = __shfl_sync(0xffffffffu, okq, 0);
-            quad_phase ^= 1u;
-            if (!okq) { ok = false; break; }
-            const double tot = ((xs[lane] + xs[32 + lane]) + xs[64 + lane]) + xs[96 + lane];
-            const float var = static_cast<float>(tot / 128.0);
-            const float rstd = rsqrt_rn(__fadd_rn(var, rp.eps));
-            const float* w = wn + (is_q ? 0 : 128) + 16 * p;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const float xa = __fmul_rn(__fmul_rn(x1[i], rstd), w[i]);
-              const float xb = __fmul_rn(__fmul_rn(x2[i], rstd), w[64 + i]);
-              x1[i] = __fsub_rn(__fmul_rn(xa, cosv[i]), __fmul_rn(xb, sinv[i]));
-              x2[i] = __fadd_rn(__fmul_rn(xb, cosv[i]), __fmul_rn(xa, sinv[i]));
+            for (int v = 0; v < 4; ++v) {
+              d1[v] = make_uint4(pack_bf16(__uint_as_float(a1[8 * v]), __uint_as_float(a1[8 * v + 1])),
+                                 pack_bf16(__uint_as_float(a1[8 * v + 2]), __uint_as_float(a1[8 * v + 3])),
+                                 pack_bf16(__uint_as_float(a1[8 * v + 4]), __uint_as_float(a1[8 * v + 5])),
+                                 pack_bf16(__uint_as_float(a1[8 * v + 6]), __uint_as_float(a1[8 * v + 7])));
+              d2[v] = make_uint4(pack_bf16(__uint_as_float(a2[8 * v]), __uint_as_float(a2[8 * v + 1])),
+                                 pack_bf16(__uint_as_float(a2[8 * v + 2]), __uint_as_float(a2[8 * v + 3])),
+                                 pack_bf16(__uint_as_float(a2[8 * v + 4]), __uint_as_float(a2[8 * v + 5])),
+                                 pack_bf16(__uint_as_float(a2[8 * v + 6]), __uint_as_float(a2[8 * v + 7])));
             }
           }
-          if (is_q) {
-            if (row_ok) {
-              __nv_bfloat16* dst = rp.q_out + static_cast<int64_t>(row) * rp.ldq + hg * 128 + 16 * p;
-              uint4* d1 = reinterpret_cast<uint4*>(dst);
-              uint4* d2 = reinterpret_cast<uint4*>(dst + 64);
-              d1[0] = make_uint4(pack_bf16(x1[0], x1[1]), pack_bf16(x1[2], x1[3]), pack_bf16(x1[4], x1[5]), pack_bf16(x1[6], x1[7]));
-              d1[1] = make_uint4(pack_bf16(x1[8], x1[9]), pack_bf16(x1[10], x1[11]), pack_bf16(x1[12], x1[13]), pack_bf16(x1[14], x1[15]));
-              d2[0] = make_uint4(pack_bf16(x2[0], x2[1]), pack_bf16(x2[2], x2[3]), pack_bf16(x2[4], x2[5]), pack_bf16(x2[6], x2[7]));
-              d2[1] = make_uint4(pack_bf16(x2[8], x2[9]), pack_bf16(x2[10], x2[11]), pack_bf16(x2[12], x2[13]), pack_bf16(x2[14], x2[15]));
-            }
-          } else {
-            if (is_k) {  // K: round to bf16 first, as the reference does before the e4m3 cast
+        } else {
+          if (is_k) {  // K: round to bf16 first, as the reference does before the e4m3 cast
 #pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                x1[i] = round_bf16(x1[i]);
-                x2[i] = round_bf16(x2[i]);
+            for (int i = 0; i < 32; ++i) {
+              a1[i] = __float_as_uint(round_bf16(__uint_as_float(a1[i])));
+              a2[i] = __float_as_uint(round_bf16(__uint_as_float(a2[i])));
+            }
+          }
+          if (row_ok && slot >= 0 && slot < rp.num_slots) {  // never write outside the pool
+            uint8_t* dst = is_k ? (rp.kc + slot * rp.ck_s + (hg - rp.n_q) * rp.ck_h)
+                                : (rp.vc + slot * rp.cv_s + (hg - rp.n_q - rp.n_kv) * rp.cv_h);
+            uint4* d1 = reinterpret_cast<uint4*>(dst + 32 * sh);
+            uint4* d2 = reinterpret_cast<uint4*>(dst + 64 + 32 * sh);
+#pragma unroll
+            for (int v = 0; v < 2; ++v) {
+              uint32_t w1[4], w2[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int i = 16 * v + 4 * j;
+                w1[j] = pack_e4m3x4(__uint_as_float(a1[i]), __uint_as_float(a1[i + 1]), __uint_as_float(a1[i + 2]),
+                                    __uint_as_float(a1[i + 3]));
+                w2[j] = pack_e4m3x4(__uint_as_float(a2[i]), __uint_as_float(a2[i + 1]), __uint_as_float(a2[i + 2]),
+                                    __uint_as_float(a2[i + 3]));
               }
-            }
-            if (row_ok && slot >= 0 && slot < rp.num_slots) {  // never write outside the pool
-              uint8_t* dst = is_k ? (rp.kc + slot * rp.ck_s + (hg - rp.n_q) * rp.ck_h)
-                                  : (rp.vc + slot * rp.cv_s + (hg - rp.n_q - rp.n_kv) * rp.cv_h);
-              *reinterpret_cast<uint4*>(dst + 16 * p) =
-                  make_uint4(pack_e4m3x4(x1[0], x1[1], x1[2], x1[3]), pack_e4m3x4(x1[4], x1[5], x1[6], x1[7]),
-                             pack_e4m3x4(x1[8], x1[9], x1[10], x1[11]), pack_e4m3x4(x1[12], x1[13], x1[14], x1[15]));
-              *reinterpret_cast<uint4*>(dst + 64 + 16 * p) =
-                  make_uint4(pack_e4m3x4(x2[0], x2[1], x2[2], x2[3]), pack_e4m3x4(x2[4], x2[5], x2[6], x2[7]),
-                             pack_e4m3x4(x2[8], x2[9], x2[10], x2[11]), pack_e4m3x4(x2[12], x2[13], x2[14], x2[15]));
+              d1[v] = make_uint4(w1[0], w1[1], w1[2], w1[3]);
+              d2[v] = make_uint4(w2[0], w2[1], w2[2], w2[3]);
             }
           }
         }
-        if (!ok) break;
       } else {
         // one 32-column chunk of y per warp and tile: 64-byte rows, 64-byte swizzle
         uint8_t* st = out_stage + ewarp * 2048;

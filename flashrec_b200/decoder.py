@@ -68,14 +68,16 @@ class Qwen3Attention:
         # run QK-norm + RoPE + the FP8 KV write inside the qkv GEMM's epilogue (same bits as the
         # reference's call order qkv_proj -> fused_qk_norm_rope_store_fp8, which stays as the other branch)
         self.fuse_rope_gemm = False
+        self.fuse_rope_min_rows = 2048
 
     def forward(self, x, batch: ForwardBatch, *, q_fp8, a_scale, residual_inout=None) -> torch.Tensor:
         """``residual_inout``: the o_proj GEMM adds its output to this bf16 residual stream in place
         (and returns it) instead of returning the projection."""
         t = int(q_fp8.shape[0])
         pool = self.attn.kv_pool
-        if self.fuse_rope_gemm and self.head_dim == 128 and self.num_qo % 2 == 0 and self.num_kv % 2 == 0 \
-                and self.qkv_proj.bias is None:
+        # (worth it from a few thousand rows on; below that the two separate kernels are faster)
+        if self.fuse_rope_gemm and t >= self.fuse_rope_min_rows and self.head_dim == 128 and self.num_qo % 2 == 0 \
+                and self.num_kv % 2 == 0 and self.qkv_proj.bias is None:
             # norm + RoPE + KV write in the qkv GEMM's epilogue: the qkv matrix is never materialised
             q = fp8_qkv_mm_norm_rope_store(
                 q_fp8, self.qkv_proj._fp8_weight, a_scale, self.qkv_proj._fp8_scale, batch.positions,
@@ -177,7 +179,7 @@ class Qwen3ForCausalLM:
     states, which the SID head consumes (models/qwen3.py:227-273)."""
 
     def __init__(self, cfg: Qwen3Config, attn: AttentionBackend, device, fuse_residual: bool = True,
-                 fuse_rope_gemm: bool = False):
+                 fuse_rope_gemm: bool = True):
         self.cfg = cfg
         self.device = torch.device(device)
         # fold the residual adds into the o_proj / down_proj GEMM epilogues (same bits, one HBM

@@ -107,6 +107,7 @@ class SidDecodeEngine:
         seed: int = 0,
         use_graphs: bool = True,
         keep_prefix: bool = True,
+        fuse_rope_gemm: bool = True,
     ):
         self.cfg = cfg
         self.device = torch.device(device)
@@ -159,7 +160,7 @@ class SidDecodeEngine:
         self.attn = AttentionBackend(self.pool, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
                                      max_shared_len=max(self.prompt_lens) + self.steps, keep_prefix=keep_prefix)
         self.attn.set_groups(torch.arange(self.n + 1, dtype=torch.int32, device=dev) * self.bw, self.bw)
-        self.model = Qwen3ForCausalLM(cfg, self.attn, dev)
+        self.model = Qwen3ForCausalLM(cfg, self.attn, dev, fuse_rope_gemm=fuse_rope_gemm)
         self.model.init_random(seed=seed + 1)
         sid_total = sum(self.sizes)
         sid_w = torch.randn((sid_total, cfg.hidden_size), generator=g, device=dev, dtype=torch.float32) * 0.02

@@ -189,6 +189,8 @@ def test_model_with_residual_adds_in_gemm_epilogues_equals_unfused_flow():
                                 max_shared_len=prompt + 4)
         attn.set_groups(torch.tensor([0, rows], dtype=torch.int32, device=DEV), rows)
         model = Qwen3ForCausalLM(cfg, attn, DEV, fuse_residual=fuse, fuse_rope_gemm=fuse)
+        for layer in model.layers:
+            layer.self_attn.fuse_rope_min_rows = 0  # take the fused qkv path at this small row count too
         model.init_random(seed=2)
         shared = torch.arange(1, prompt + 1, dtype=torch.int32)
         own = torch.arange(100, 100 + rows, dtype=torch.int32)
