@@ -85,6 +85,8 @@ _SIGNATURES = {
                                _I, _I, _I, _I, P],
     "fr_store_kv_fp8": [P, P, _L, _L, _L, _L, P, P, P, _L, _L, _L, _L, _I, _I, _I, _I, P],
     "fr_gather_kv_indices": [P, _L, P, P, P, P, _I, _I, P],
+    "fr_kv_table_step": [P, _L, _I, _I, P, P, _I, P, P, P, P, P, P, _I, _I, P],
+    "fr_kv_table_fanout": [P, _L, _I, P, P, _I, _I, _I, P],
     "fr_embedding_bf16": [P, P, P, _I, _I, _I, P],
     "fr_decode_attn_plan": [P, P, P, _I, _I, P, P],
     "fr_decode_attn_scratch_bytes": [_I, _I, _I],

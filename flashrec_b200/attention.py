@@ -1,6 +1,6 @@
-"""KV pool, slot-index gather and the decode attention backend: mirrors of
+"""KV pool, slot-table bookkeeping and the decode attention backend: mirrors of
 ``TokenToKVPool`` (kvcache/pool.py:66-139), ``gather_kv_indices``
-(attention/kv_indices.py:63-132) and ``AttentionBackend`` (attention/flashinfer.py)
+(attention/kv_indices.py:63-132), ``remap_by_parents`` (scheduler/kv_remap.py:30-66) and ``AttentionBackend`` (attention/flashinfer.py)
 for the FP8 decode path.
 """
 
@@ -124,6 +124,65 @@ def gather_kv_indices(
     call("fr_gather_kv_indices", ptr(req_to_token), req_to_token.stride(0), ptr(rows), ptr(sl), ptr(indptr_out),
          ptr(out), n, cap, stream_ptr(device))
     return out.reshape(-1)[:cap] if total is not None else out
+
+
+def kv_table_step(
+    req_to_token: torch.Tensor,
+    rows: torch.Tensor,
+    seq_lens: torch.Tensor,
+    out: torch.Tensor,
+    indptr_out: torch.Tensor,
+    *,
+    new_slot: Optional[torch.Tensor] = None,
+    parents_rel: Optional[torch.Tensor] = None,
+    prefix_len: Optional[torch.Tensor] = None,
+    group_indptr: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """The slot-table work of one decode tick for a whole wave, in one call:
+    ``remap_by_parents`` of every request (scheduler/kv_remap.py:30-66) with last
+    tick's ``parents_rel``, the batched ``write_decode`` of this tick's ``new_slot``
+    (scheduler/scheduler.py:1305-1310) and ``gather_kv_indices``
+    (attention/kv_indices.py:63-132). ``seq_lens`` (int32, device) are the lengths
+    after the tick; the decode window of a row is ``[prefix_len, seq_len - 1)``
+    (``[prefix_len, seq_len)`` without ``new_slot``). Everything is a device tensor
+    given by the caller: nothing allocates or syncs (graph-capturable)."""
+    require_cuda(req_to_token, rows, seq_lens, out, indptr_out)
+    if req_to_token.dtype != torch.int32 or seq_lens.dtype != torch.int32 or rows.dtype != torch.int64:
+        raise TypeError("req_to_token / seq_lens must be int32 and rows int64")
+    if out.dtype != torch.int32 or indptr_out.dtype != torch.int32:
+        raise TypeError("out / indptr_out must be int32")
+    n = int(rows.numel())
+    if int(seq_lens.numel()) != n or int(indptr_out.numel()) < n + 1:
+        raise ValueError("seq_lens / indptr_out do not match rows")
+    for name, t, dt in (("new_slot", new_slot, torch.int64), ("parents_rel", parents_rel, torch.int64),
+                        ("prefix_len", prefix_len, torch.int32)):
+        if t is not None and (t.dtype != dt or int(t.numel()) != n or not t.is_contiguous()):
+            raise TypeError(f"{name} must be a contiguous {dt} tensor of {n} elements")
+    n_groups = 0
+    if parents_rel is not None:
+        if group_indptr is None or prefix_len is None or group_indptr.dtype != torch.int32:
+            raise TypeError("parents_rel needs prefix_len and an int32 group_indptr")
+        n_groups = int(group_indptr.numel()) - 1
+    call("fr_kv_table_step", ptr(req_to_token), req_to_token.stride(0), int(req_to_token.shape[0]),
+         int(req_to_token.shape[1]), ptr(rows), ptr(group_indptr), n_groups, ptr(parents_rel), ptr(prefix_len),
+         ptr(seq_lens), ptr(new_slot), ptr(indptr_out), ptr(out), n, int(out.numel()), stream_ptr(req_to_token.device))
+    return out
+
+
+def copy_prefill_to_beams_many(req_to_token: torch.Tensor, srcs: torch.Tensor, beam_rows: torch.Tensor,
+                               m: int) -> None:
+    """``table[beam_rows[r, b], :m] = table[srcs[r], :m]``: a prefill row's slots handed
+    to all beams of its request (ModelEngine.copy_prefill_to_beams_many,
+    engine/engine.py:252-274; ``m`` is the reference's ``max(seq_lens)``)."""
+    require_cuda(req_to_token, srcs, beam_rows)
+    if req_to_token.dtype != torch.int32 or srcs.dtype != torch.int64 or beam_rows.dtype != torch.int64:
+        raise TypeError("req_to_token must be int32, srcs / beam_rows int64")
+    if beam_rows.dim() != 2 or int(beam_rows.shape[0]) != int(srcs.numel()) or not beam_rows.is_contiguous():
+        raise ValueError("beam_rows must be a contiguous [n_requests, beam_width] tensor")
+    if not 0 <= int(m) <= int(req_to_token.shape[1]):
+        raise ValueError("m exceeds the table width")
+    call("fr_kv_table_fanout", ptr(req_to_token), req_to_token.stride(0), int(req_to_token.shape[0]), ptr(srcs),
+         ptr(beam_rows), int(beam_rows.shape[0]), int(beam_rows.shape[1]), int(m), stream_ptr(req_to_token.device))
 
 
 class AttentionBackend:

@@ -1,0 +1,231 @@
+// Bookkeeping on the row -> slot table (`req_to_token`, int32 [pool rows, max_seq]) of the beam
+// scheduler: everything one decode tick does to it, without torch index ops.
+//
+//   fr_gather_kv_indices   ragged copy req_to_token[row, :seq_len] -> flat slot list + indptr
+//                          (gather_kv_indices, attention/kv_indices.py:20-132).
+//   fr_kv_table_step       the three table operations of a tick in one call: every request's
+//                          decode window gathered by last tick's parents (remap_by_parents,
+//                          scheduler/kv_remap.py:30-66), the new token's slot written at the end
+//                          of each row (scheduler/scheduler.py:1305-1310), and the flat slot list
+//                          of the attention call (gather_kv_indices).
+//   fr_kv_table_fanout     a prefill row's slots copied to all beam rows of its request
+//                          (ModelEngine.copy_prefill_to_beams_many, engine/engine.py:252-274).
+//
+// The window remap is an in-place gather across rows. It is made race-free without a snapshot
+// of the table: the first kernel only READS the table (each row takes its window from its
+// parent's row) and writes the flat list; the second kernel only reads the flat list and writes
+// the windows and the new column back into the table. Both move 4-byte words, one warp per row.
+#include "fr_common.cuh"
+
+namespace fr {
+
+// indptr[0] = 0, indptr[i + 1] = sum of max(seq_lens[..i], 0). One CTA; each thread owns kScanItems
+// consecutive rows of a chunk, so 16384 rows take two rounds of the block-wide scan.
+constexpr int kScanItems = 8;
+__global__ void __launch_bounds__(1024) seq_scan_kernel(const int32_t* __restrict__ seq_lens,
+                                                       int32_t* __restrict__ indptr, int n) {
+  __shared__ int32_t warp_tot[32];
+  __shared__ int32_t carry_s;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) { carry_s = 0; indptr[0] = 0; }
+  __syncthreads();
+  for (int base = 0; base < n; base += 1024 * kScanItems) {
+    const int i0 = base + threadIdx.x * kScanItems;
+    int32_t v[kScanItems];
+    int32_t x = 0;
+#pragma unroll
+    for (int j = 0; j < kScanItems; ++j) {
+      v[j] = i0 + j < n ? max(seq_lens[i0 + j], 0) : 0;
+      x += v[j];
+    }
+    const int32_t mine = x;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int32_t y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
+    }
+    if (lane == 31) warp_tot[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+      int32_t w = warp_tot[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int32_t y = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += y;
+      }
+      warp_tot[lane] = w;  // inclusive
+    }
+    __syncthreads();
+    const int32_t incl = carry_s + x + (warp > 0 ? warp_tot[warp - 1] : 0);
+    int32_t run = incl - mine;
+#pragma unroll
+    for (int j = 0; j < kScanItems; ++j) {
+      run += v[j];
+      if (i0 + j < n) indptr[i0 + j + 1] = run;
+    }
+    __syncthreads();
+    if (threadIdx.x == 1023) carry_s = incl;
+    __syncthreads();
+  }
+}
+
+// dst[c] = src[c] for c in [begin, end), c < limit, by one warp: four independent 128-byte rows of
+// loads in flight per lane before the stores.
+__device__ __forceinline__ void warp_copy_words(const int32_t* __restrict__ src, int32_t* __restrict__ dst, int begin,
+                                                int end, int limit, int lane) {
+  end = min(end, limit);
+  int c = begin + lane;
+  for (; c + 96 < end; c += 128) {
+    const int32_t v0 = __ldg(src + c), v1 = __ldg(src + c + 32), v2 = __ldg(src + c + 64), v3 = __ldg(src + c + 96);
+    dst[c] = v0; dst[c + 32] = v1; dst[c + 64] = v2; dst[c + 96] = v3;
+  }
+  for (; c < end; c += 32) dst[c] = __ldg(src + c);
+}
+
+__global__ void __launch_bounds__(256) gather_kv_kernel(const int32_t* __restrict__ table, int64_t stride,
+                                                       const int64_t* __restrict__ rows,
+                                                       const int32_t* __restrict__ seq_lens,
+                                                       const int32_t* __restrict__ indptr, int32_t* __restrict__ out,
+                                                       int n, int capacity) {
+  const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (r >= n) return;
+  const int lane = threadIdx.x & 31;
+  const int32_t sl = max(seq_lens[r], 0);
+  const int32_t off = indptr[r];
+  const int32_t* src = table + rows[r] * stride;
+  warp_copy_words(src, out + off, 0, sl, capacity - off, lane);
+}
+
+struct StepArgs {
+  int32_t* table;
+  int64_t stride;
+  int n_table_rows, n_cols;
+  const int64_t* rows;
+  const int32_t* group_indptr;
+  int n_groups;
+  const int64_t* parents_rel;
+  const int32_t* prefix_len;
+  const int32_t* seq_lens;
+  const int64_t* new_slot;
+  const int32_t* indptr;
+  int32_t* out;
+  int n, capacity;
+};
+
+// Length of row i after the tick, and where its window starts and ends.
+__device__ __forceinline__ void row_extent(const StepArgs& a, int i, int& sl, int& pre, int& keep) {
+  sl = min(max(a.seq_lens[i], 0), a.n_cols);
+  keep = max(sl - (a.new_slot ? 1 : 0), 0);
+  pre = a.prefix_len ? min(max(a.prefix_len[i], 0), keep) : keep;
+}
+
+// Phase 1: out[indptr[i] + c] = slot of column c of row i AFTER the tick, read from the table as it
+// was BEFORE the tick: prompt columns from the row itself, window columns from the parent's row,
+// the last column from new_slot.
+__global__ void __launch_bounds__(256) kv_step_gather_kernel(StepArgs a) {
+  const int i = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (i >= a.n) return;
+  const int lane = threadIdx.x & 31;
+  int sl, pre, keep;
+  row_extent(a, i, sl, pre, keep);
+  const int64_t own_row = a.rows[i];
+  int64_t par_row = own_row;
+  if (a.parents_rel && pre < keep) {
+    // request of batch row i: the last g with group_indptr[g] <= i
+    int lo = 0, hi = a.n_groups;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (a.group_indptr[mid] <= i) lo = mid; else hi = mid;
+    }
+    const int g0 = a.group_indptr[lo], k = a.group_indptr[lo + 1] - g0;
+    int64_t p = a.parents_rel[i];
+    p = p < 0 ? 0 : (p > k - 1 ? k - 1 : p);  // clamp(0, k - 1) as the reference does
+    par_row = a.rows[g0 + static_cast<int>(p)];
+  }
+  const bool own_ok = own_row >= 0 && own_row < a.n_table_rows;
+  const bool par_ok = par_row >= 0 && par_row < a.n_table_rows;
+  const int32_t off = a.indptr[i];
+  int32_t* dst = a.out + off;
+  const int limit = a.capacity - off;
+  // the table is only read by this kernel, the list only written
+  if (own_ok) warp_copy_words(a.table + own_row * a.stride, dst, 0, pre, limit, lane);
+  if (par_ok) warp_copy_words(a.table + par_row * a.stride, dst, pre, keep, limit, lane);
+  if (a.new_slot && lane == 0 && keep < sl && keep < limit) dst[keep] = static_cast<int32_t>(a.new_slot[i]);
+}
+
+// Phase 2: window and new column of every row written back from the flat list.
+__global__ void __launch_bounds__(256) kv_step_writeback_kernel(StepArgs a) {
+  const int i = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (i >= a.n) return;
+  const int lane = threadIdx.x & 31;
+  int sl, pre, keep;
+  row_extent(a, i, sl, pre, keep);
+  const int64_t own_row = a.rows[i];
+  if (own_row < 0 || own_row >= a.n_table_rows) return;
+  if (!a.parents_rel) pre = keep;  // no remap: only the new column changes
+  int32_t* dst = a.table + own_row * a.stride;
+  const int32_t off = a.indptr[i];
+  warp_copy_words(a.out + off, dst, pre, sl, a.capacity - off, lane);
+}
+
+// table[dst_rows[r * bw + b], :m] = table[src_rows[r], :m]
+__global__ void __launch_bounds__(256) kv_fanout_kernel(int32_t* table, int64_t stride, int n_table_rows,
+                                                       const int64_t* __restrict__ src_rows,
+                                                       const int64_t* __restrict__ dst_rows, int total, int bw, int m) {
+  const int i = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (i >= total) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t s = src_rows[i / bw], d = dst_rows[i];
+  if (s < 0 || s >= n_table_rows || d < 0 || d >= n_table_rows || s == d) return;
+  warp_copy_words(table + s * stride, table + d * stride, 0, m, m, lane);
+}
+
+}  // namespace fr
+
+using namespace fr;
+
+extern "C" int fr_gather_kv_indices(const int32_t* req_to_token, int64_t row_stride, const int64_t* rows,
+                                    const int32_t* seq_lens, int32_t* indptr_out, int32_t* out, int n,
+                                    int out_capacity, cudaStream_t stream) {
+  FR_CHECK_ARG(n >= 0 && out_capacity >= 0);
+  if (n == 0) return FR_OK;
+  FR_CHECK_ARG(req_to_token && rows && seq_lens && indptr_out && (out || out_capacity == 0));
+  seq_scan_kernel<<<1, 1024, 0, stream>>>(seq_lens, indptr_out, n);
+  if (launch_status() != FR_OK) return FR_ERR_CUDA;
+  if (out_capacity == 0) return FR_OK;
+  gather_kv_kernel<<<ceil_div(n, 8), 256, 0, stream>>>(req_to_token, row_stride, rows, seq_lens, indptr_out, out, n,
+                                                      out_capacity);
+  return launch_status();
+}
+
+extern "C" int fr_kv_table_step(int32_t* req_to_token, int64_t row_stride, int n_table_rows, int n_cols,
+                                const int64_t* rows, const int32_t* group_indptr, int n_groups,
+                                const int64_t* parents_rel, const int32_t* prefix_len, const int32_t* seq_lens,
+                                const int64_t* new_slot, int32_t* indptr_out, int32_t* out, int n, int out_capacity,
+                                cudaStream_t stream) {
+  FR_CHECK_ARG(n >= 0 && out_capacity >= 0 && n_table_rows >= 0 && n_cols >= 0 && n_groups >= 0);
+  if (n == 0) return FR_OK;
+  FR_CHECK_ARG(req_to_token && rows && seq_lens && indptr_out && out && row_stride >= n_cols);
+  FR_CHECK_ARG(!parents_rel || (group_indptr && n_groups > 0 && prefix_len));
+  seq_scan_kernel<<<1, 1024, 0, stream>>>(seq_lens, indptr_out, n);
+  if (launch_status() != FR_OK) return FR_ERR_CUDA;
+  StepArgs a{req_to_token, row_stride, n_table_rows, n_cols, rows, group_indptr, n_groups, parents_rel, prefix_len,
+             seq_lens, new_slot, indptr_out, out, n, out_capacity};
+  kv_step_gather_kernel<<<ceil_div(n, 8), 256, 0, stream>>>(a);
+  if (launch_status() != FR_OK) return FR_ERR_CUDA;
+  if (!parents_rel && !new_slot) return FR_OK;  // nothing to write back: a plain gather
+  kv_step_writeback_kernel<<<ceil_div(n, 8), 256, 0, stream>>>(a);
+  return launch_status();
+}
+
+extern "C" int fr_kv_table_fanout(int32_t* req_to_token, int64_t row_stride, int n_table_rows, const int64_t* src_rows,
+                                  const int64_t* dst_rows, int n_requests, int beam_width, int m,
+                                  cudaStream_t stream) {
+  FR_CHECK_ARG(n_requests >= 0 && beam_width >= 0 && m >= 0 && n_table_rows >= 0);
+  const int64_t total = static_cast<int64_t>(n_requests) * beam_width;
+  if (total == 0 || m == 0) return FR_OK;
+  FR_CHECK_ARG(req_to_token && src_rows && dst_rows && row_stride >= m && total <= INT32_MAX);
+  kv_fanout_kernel<<<ceil_div(total, 8), 256, 0, stream>>>(req_to_token, row_stride, n_table_rows, src_rows, dst_rows,
+                                                          static_cast<int>(total), beam_width, m);
+  return launch_status();
+}

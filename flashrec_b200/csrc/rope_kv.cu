@@ -6,8 +6,6 @@
 //                            fused_qk_norm_rope_store_fp8 (kernel/qk_rope_kv.py:28-250).
 //   fr_store_kv_fp8          plain bf16 -> e4m3 scatter of K and V
 //                            (TokenToKVPool.store, kvcache/pool.py:121-139).
-//   fr_gather_kv_indices     ragged copy req_to_token[row, :seq_len] -> flat slot
-//                            list + indptr (gather_kv_indices, attention/kv_indices.py:20-132).
 //   fr_embedding_bf16        token-embedding row gather (models/qwen3.py:266).
 //
 // All are HBM-bound; a group of D/8 lanes owns one (token, head) pair and moves
@@ -175,62 +173,6 @@ static int launch_rope(const RopeArgs& a, int D, cudaStream_t stream) {
   return launch_status();
 }
 
-// ---------------------------------------------------------------------------
-// kv index gather
-// ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024) seq_scan_kernel(const int32_t* __restrict__ seq_lens,
-                                                       int32_t* __restrict__ indptr, int n) {
-  __shared__ int32_t warp_tot[32];
-  __shared__ int32_t carry_s;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (threadIdx.x == 0) { carry_s = 0; indptr[0] = 0; }
-  __syncthreads();
-  for (int base = 0; base < n; base += 1024) {
-    const int i = base + threadIdx.x;
-    int32_t v = i < n ? max(seq_lens[i], 0) : 0;
-    int32_t x = v;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      int32_t y = __shfl_up_sync(0xffffffffu, x, o);
-      if (lane >= o) x += y;
-    }
-    if (lane == 31) warp_tot[warp] = x;
-    __syncthreads();
-    if (warp == 0) {
-      int32_t w = warp_tot[lane];
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        int32_t y = __shfl_up_sync(0xffffffffu, w, o);
-        if (lane >= o) w += y;
-      }
-      warp_tot[lane] = w;  // inclusive
-    }
-    __syncthreads();
-    const int32_t carry = carry_s;
-    const int32_t incl = carry + x + (warp > 0 ? warp_tot[warp - 1] : 0);
-    if (i < n) indptr[i + 1] = incl;
-    __syncthreads();
-    if (threadIdx.x == 1023) carry_s = incl;
-    __syncthreads();
-  }
-}
-
-__global__ void __launch_bounds__(256) gather_kv_kernel(const int32_t* __restrict__ table, int64_t stride,
-                                                       const int64_t* __restrict__ rows,
-                                                       const int32_t* __restrict__ seq_lens,
-                                                       const int32_t* __restrict__ indptr, int32_t* __restrict__ out,
-                                                       int n, int capacity) {
-  const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (r >= n) return;
-  const int lane = threadIdx.x & 31;
-  const int32_t sl = max(seq_lens[r], 0);
-  const int32_t off = indptr[r];
-  const int32_t* src = table + rows[r] * stride;
-  for (int i = lane; i < sl; i += 32) {
-    if (off + i < capacity) out[off + i] = __ldg(src + i);
-  }
-}
-
 __global__ void __launch_bounds__(256) embedding_kernel(const uint4* __restrict__ table, const int64_t* __restrict__ ids,
                                                        uint4* __restrict__ out, int T, int vec_per_row, int vocab) {
   const int64_t total = static_cast<int64_t>(T) * vec_per_row;
@@ -286,20 +228,6 @@ extern "C" int fr_store_kv_fp8(const void* k, const void* v, int64_t k_t, int64_
              v_h, nullptr, loc, nullptr, nullptr, 0.f, nullptr, 1, static_cast<uint8_t*>(k_cache),
              static_cast<uint8_t*>(v_cache), ck_s, ck_h, cv_s, cv_h, T, 0, n_kv, num_slots};
   return launch_rope<false>(a, D, stream);
-}
-
-extern "C" int fr_gather_kv_indices(const int32_t* req_to_token, int64_t row_stride, const int64_t* rows,
-                                    const int32_t* seq_lens, int32_t* indptr_out, int32_t* out, int n,
-                                    int out_capacity, cudaStream_t stream) {
-  FR_CHECK_ARG(n >= 0 && out_capacity >= 0);
-  if (n == 0) return FR_OK;
-  FR_CHECK_ARG(req_to_token && rows && seq_lens && indptr_out && (out || out_capacity == 0));
-  seq_scan_kernel<<<1, 1024, 0, stream>>>(seq_lens, indptr_out, n);
-  if (launch_status() != FR_OK) return FR_ERR_CUDA;
-  if (out_capacity == 0) return FR_OK;
-  gather_kv_kernel<<<ceil_div(n, 8), 256, 0, stream>>>(req_to_token, row_stride, rows, seq_lens, indptr_out, out, n,
-                                                      out_capacity);
-  return launch_status();
 }
 
 extern "C" int fr_embedding_bf16(const void* table, const int64_t* ids, void* out, int T, int hidden, int vocab,

@@ -3,9 +3,10 @@ one engine tick in the reference (``BeamRecEngine._forward_decode`` and
 ``_expand_decode_body``, scheduler/scheduler.py:1261-1456; ``DecodeGraphRunner``,
 engine/graph.py:85-517), sequenced for a fixed wave of requests.
 
-Per step and per beam row: append a KV slot to the row's slot table, gather
-the flat slot lists, run the model body, the SID head of the step's level and
-the fused beam step, then re-parent the per-row decode tails of the slot table.
+Per step: one slot-table call (the rows' decode windows re-parented by the
+previous step's parents, this step's KV slots appended, the flat slot lists
+gathered), the model body, the SID head of the step's level and the fused beam
+step. Before the first step every beam row receives its request's prompt slots.
 Each step is captured once in a CUDA graph (rows = requests x beam width, a
 multiple of the beam width as in ``resolved_cuda_graph_sizes``, config.py:220-238)
 and replayed.
@@ -20,7 +21,7 @@ from typing import List, Optional, Sequence
 import torch
 
 from flashrec_b200._lib import call, ptr, stream_ptr
-from flashrec_b200.attention import AttentionBackend, TokenToKVPool, gather_kv_indices
+from flashrec_b200.attention import AttentionBackend, TokenToKVPool, copy_prefill_to_beams_many, kv_table_step
 from flashrec_b200.decoder import ForwardBatch, Qwen3Config, Qwen3ForCausalLM
 from flashrec_b200.kernel.beam_trie import GenrecFusedResult
 from flashrec_b200.logits import RestrictedLMHead
@@ -138,28 +139,29 @@ class SidDecodeEngine:
                 blk = torch.randn((n_prompt_slots, cfg.num_key_value_heads, cfg.head_dim), generator=g, device=dev,
                                   dtype=torch.float32)
                 cache[page_size: page_size + n_prompt_slots].copy_(blk.to(torch.bfloat16).to(_FP8))
-        # slot table: row -> slot ids, like ReqToTokenPool.req_to_token (kvcache/pool.py:142-183)
+        # slot table: row -> slot ids, like ReqToTokenPool.req_to_token (kvcache/pool.py:142-183): the
+        # beam rows first, then one prefill row per request whose slots every wave hands to its beams
         self.max_seq = max(self.prompt_lens) + self.steps
-        table = torch.zeros((self.rows, self.max_seq), dtype=torch.int32)
+        table = torch.zeros((self.rows + self.n, self.max_seq), dtype=torch.int32)
         shared = torch.arange(page_size, page_size + shared_prefix, dtype=torch.int32)
         cursor = page_size + shared_prefix
         for r, plen in enumerate(self.prompt_lens):
             own = torch.arange(cursor, cursor + max(plen - shared_prefix, 0), dtype=torch.int32)
             cursor += int(own.numel())
-            slots = torch.cat((shared[: min(plen, shared_prefix)], own))
-            table[r * self.bw: (r + 1) * self.bw, :plen] = slots[None, :]
+            table[self.rows + r, :plen] = torch.cat((shared[: min(plen, shared_prefix)], own))
         self.req_to_token = table.to(dev)
+        self.prefill_rows = torch.arange(self.rows, self.rows + self.n, dtype=torch.int64, device=dev)
         self.decode_slot_base = page_size + uniq_prompt
         plen_rows = torch.tensor(self.prompt_lens, dtype=torch.int64).repeat_interleave(self.bw)
         self.prompt_len_rows = plen_rows.to(dev)
-        self.tail_cols = (plen_rows[:, None] + torch.arange(self.steps)[None, :]).to(dev)  # [rows, steps]
+        self.prefix_len_rows = self.prompt_len_rows.to(torch.int32)
         self.rows_idx = torch.arange(self.rows, dtype=torch.int64, device=dev)
-        self.row_base = (torch.arange(self.n, dtype=torch.int64, device=dev) * self.bw)[:, None]
+        self.group_indptr = torch.arange(self.n + 1, dtype=torch.int32, device=dev) * self.bw
 
         # ---- model + head ----------------------------------------------------------------
         self.attn = AttentionBackend(self.pool, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
                                      max_shared_len=max(self.prompt_lens) + self.steps, keep_prefix=keep_prefix)
-        self.attn.set_groups(torch.arange(self.n + 1, dtype=torch.int32, device=dev) * self.bw, self.bw)
+        self.attn.set_groups(self.group_indptr, self.bw)
         self.model = Qwen3ForCausalLM(cfg, self.attn, dev, fuse_rope_gemm=fuse_rope_gemm)
         self.model.init_random(seed=seed + 1)
         sid_total = sum(self.sizes)
@@ -204,7 +206,10 @@ class SidDecodeEngine:
 
     # ------------------------------------------------------------------------------------
     def reset(self) -> None:
-        """Beam state before the first step: one live beam per request at the trie root."""
+        """Beam state before the first step: one live beam per request at the trie root, every
+        beam row holding its request's prompt slots (engine/engine.py:252-274)."""
+        copy_prefill_to_beams_many(self.req_to_token, self.prefill_rows, self.rows_idx.view(self.n, self.bw),
+                                   max(self.prompt_lens))
         self.cum.fill_(float("-inf"))
         self.cum[:, 0] = 0.0
         self.node_planes[0].zero_()
@@ -216,10 +221,12 @@ class SidDecodeEngine:
     def _step_body(self, s: int) -> None:
         """Device work of decode step ``s`` (level ``s``); allocation-stable, capturable."""
         src, dst = s & 1, (s & 1) ^ 1
-        # KV slot of this step's input token goes into the row's slot table
-        self.req_to_token[self.rows_idx, self.positions] = self.out_cache_loc.to(torch.int32)
-        gather_kv_indices(self.req_to_token, self.rows_idx, self.seq_lens, out=self.kv_indices,
-                          indptr_out=self.kv_indptr)
+        # slot table: the windows follow last step's parents (scheduler/kv_remap.py:30-66), this step's
+        # slots go in (scheduler.py:1305-1310), the flat slot list of the attention call comes out
+        kv_table_step(self.req_to_token, self.rows_idx, self.seq_lens, self.kv_indices, self.kv_indptr,
+                      new_slot=self.out_cache_loc,
+                      parents_rel=self.outs[s - 1].parents.view(-1) if s > 0 else None,
+                      prefix_len=self.prefix_len_rows, group_indptr=self.group_indptr)
         batch = ForwardBatch(input_ids=self.input_ids, req_pool_indices=self.rows_idx, seq_lens=self.seq_lens,
                              positions=self.positions, out_cache_loc=self.out_cache_loc, kv_indices=self.kv_indices,
                              kv_indptr=self.kv_indptr)
@@ -230,14 +237,12 @@ class SidDecodeEngine:
         out = sid_beam_step(self.cum, logits, mx, ls, self.node_planes[src], self.trie, self.level_tok_base[s],
                             self.bw, token_ids_in=self.tok_planes[src], token_ids_out=self.tok_planes[dst],
                             node_ids_out=self.node_planes[dst], col=self.col, out=self.outs[s])
-        # bookkeeping for the next step (scheduler/kv_remap.py:30-66, scheduler.py:1594-1608)
+        # state of the next step (the window remap by out.parents is deferred to its table call, as
+        # scheduler.py:1590-1610 defers it)
         self.cum.copy_(out.vals)
         if self.trie is None:
             self.node_planes[dst].fill_(-1)
         self.input_ids.copy_(out.tokens.reshape(-1))
-        parent_rows = (self.row_base + out.parents).reshape(-1)
-        tails = self.req_to_token.gather(1, self.tail_cols)
-        self.req_to_token.scatter_(1, self.tail_cols, tails.index_select(0, parent_rows))
         self.positions.add_(1)
         self.seq_lens.add_(1)
 

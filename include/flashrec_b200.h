@@ -166,6 +166,34 @@ int fr_store_kv_fp8(const void* k, const void* v, int64_t k_t, int64_t k_h, int6
 int fr_gather_kv_indices(const int32_t* req_to_token, int64_t row_stride, const int64_t* rows, const int32_t* seq_lens,
                          int32_t* indptr_out, int32_t* out, int n, int out_capacity, cudaStream_t stream);
 
+/* One decode tick on the row -> slot table, for a whole wave of requests. Batch row i
+ * (table row rows[i]) belongs to request g with group_indptr[g] <= i < group_indptr[g+1];
+ * seq_lens[i] is the row's length AFTER the tick. In this order:
+ *  1. (parents_rel != NULL) the decode window, columns [prefix_len[i], seq_lens[i] - 1), is taken
+ *     from the row of parent p = clamp(parents_rel[i], 0, k-1) of the same request (k rows),
+ *     all rows reading the table as it was before the call:
+ *     remap_by_parents (scheduler/kv_remap.py:30-66), called per request at scheduler.py:1598-1610.
+ *  2. (new_slot != NULL) table[rows[i], seq_lens[i] - 1] = new_slot[i]: the batched write_decode
+ *     of scheduler/scheduler.py:1305-1310. With new_slot == NULL the window ends at seq_lens[i].
+ *  3. indptr_out = exclusive scan of seq_lens, out = the rows' slots [:seq_lens[i]] after 1 and 2:
+ *     gather_kv_indices (attention/kv_indices.py:63-132).
+ * rows, parents_rel, new_slot: int64 [n]; group_indptr: int32 [n_groups + 1]; prefix_len,
+ * seq_lens: int32 [n] (equal within a request); out: int32 [out_capacity], which must hold the
+ * whole list (entries past it are dropped from the list AND from the table update). rows must
+ * be distinct; rows outside [0, n_table_rows) are skipped; seq_lens are clamped to n_cols.
+ * No allocation, no host sync: graph-capturable. */
+int fr_kv_table_step(int32_t* req_to_token, int64_t row_stride, int n_table_rows, int n_cols, const int64_t* rows,
+                     const int32_t* group_indptr, int n_groups, const int64_t* parents_rel, const int32_t* prefix_len,
+                     const int32_t* seq_lens, const int64_t* new_slot, int32_t* indptr_out, int32_t* out, int n,
+                     int out_capacity, cudaStream_t stream);
+
+/* table[dst_rows[r * beam_width + b], :m] = table[src_rows[r], :m] for every request r and beam b.
+ * src_rows int64 [n_requests], dst_rows int64 [n_requests * beam_width]; a destination row must
+ * not be another request's source row.
+ * Reference: ModelEngine.copy_prefill_to_beams_many (engine/engine.py:252-274). */
+int fr_kv_table_fanout(int32_t* req_to_token, int64_t row_stride, int n_table_rows, const int64_t* src_rows,
+                       const int64_t* dst_rows, int n_requests, int beam_width, int m, cudaStream_t stream);
+
 /* out[t, :] = table[ids[t], :] (bf16, hidden % 8 == 0).
  * Reference: nn.Embedding in Qwen3ForCausalLM.forward (models/qwen3.py:266). */
 int fr_embedding_bf16(const void* table, const int64_t* ids, void* out, int T, int hidden, int vocab,

@@ -187,6 +187,46 @@ def gather_kv_indices(req_to_token: torch.Tensor, rows: torch.Tensor, seq_lens) 
     return torch.cat(out) if out else torch.empty(0, dtype=torch.int32)
 
 
+def remap_by_parents(table: torch.Tensor, beam_rows: torch.Tensor, parents_rel: torch.Tensor, prefix_len: int,
+                     seq_len: int) -> None:
+    """scheduler/kv_remap.py:30-66: columns [prefix_len, seq_len) of a request's rows, gathered in
+    place by (clamped) parent."""
+    seq_len = min(int(seq_len), int(table.shape[1]))
+    prefix_len = max(int(prefix_len), 0)
+    k = int(beam_rows.numel())
+    if prefix_len >= seq_len or k == 0 or int(parents_rel.numel()) != k:
+        return
+    rows = beam_rows.to(torch.int64)
+    parents = parents_rel.to(torch.int64).view(-1).clamp(0, k - 1)
+    window = table[rows, prefix_len:seq_len]
+    table[rows, prefix_len:seq_len] = window[parents]
+
+
+def kv_table_step(table, rows, group_indptr, seq_lens, new_slot=None, parents_rel=None, prefix_len=None):
+    """One tick on the slot table, the reference's three steps in its order: per-request
+    remap_by_parents of the window [prefix, seq_len - 1) (scheduler/scheduler.py:1598-1610), the
+    batched write_decode ``table[rows, col] = new_slot`` (scheduler/scheduler.py:1305-1310),
+    gather_kv_indices of ``[:seq_len]``. ``table`` is updated in place; returns (indptr, flat list)."""
+    n_new = 0 if new_slot is None else 1
+    if parents_rel is not None:
+        gi = [int(x) for x in group_indptr]
+        for g in range(len(gi) - 1):
+            a, b = gi[g], gi[g + 1]
+            if b > a:
+                remap_by_parents(table, rows[a:b], parents_rel[a:b], int(prefix_len[a]), int(seq_lens[a]) - n_new)
+    if new_slot is not None:
+        table[rows.to(torch.int64), seq_lens.to(torch.int64) - 1] = new_slot.to(table.dtype)
+    flat = gather_kv_indices(table, rows, seq_lens.tolist())
+    indptr = torch.zeros(len(seq_lens) + 1, dtype=torch.int32)
+    indptr[1:] = torch.cumsum(seq_lens.to(torch.int64), 0).to(torch.int32)
+    return indptr, flat
+
+
+def copy_prefill_to_beams_many(table, srcs, beam_rows, m: int) -> None:
+    """engine/engine.py:252-274: ``table[beam_rows, :m] = table[srcs, :m].unsqueeze(1)``."""
+    table[beam_rows.to(torch.int64), :m] = table[srcs.to(torch.int64), :m].unsqueeze(1)
+
+
 def decode_attention(q, k_cache, v_cache, kv_indptr, kv_indices, n_rep: int) -> torch.Tensor:
     """attention/flashinfer.py:380-431 (_sdpa, decode branch), evaluated in fp32:
     per row softmax(q K^T / sqrt(D)) V over the row's slot list, GQA by repeat."""

@@ -2,7 +2,9 @@
 
 Usage (only where the reference checkout is available):
 
-    PYTHONPATH=<reference>/python python tests/golden/make_golden.py
+    python tests/golden/make_golden.py <reference>/python [--only kv_table]
+
+(``--only kv_table`` writes just ``kv_table.npz``, leaving the other files as they are.)
 
 Every fixture holds seeded inputs and the outputs of the reference's own torch
 CPU code path (its ``sgl_kernel`` branch is absent, so each wrapper takes its
@@ -29,6 +31,51 @@ def bits16(t: torch.Tensor) -> np.ndarray:
 
 def bits8(t: torch.Tensor) -> np.ndarray:
     return t.contiguous().view(torch.uint8).numpy().copy()
+
+
+def kv_table_fixture() -> None:
+    """Three decode ticks on a small slot table with the reference's own functions:
+    copy_prefill_to_beams_many, then per tick the deferred remap_by_parents of every
+    request, the batched write_decode statement of the scheduler and gather_kv_indices."""
+    from flashrec.attention.kv_indices import gather_kv_indices
+    from flashrec.engine.engine import ModelEngine
+    from flashrec.scheduler.kv_remap import remap_by_parents
+
+    g = torch.Generator().manual_seed(7)
+    bws, plens, max_seq = [4, 6, 1, 5], [5, 9, 3, 7], 16
+    n_req, n_rows = len(bws), sum(bws)
+    table = torch.randint(1, 1000, (n_req + n_rows + 2, max_seq), generator=g, dtype=torch.int32)
+    out = {"table0": table.numpy().copy(), "bws": np.array(bws), "plens": np.array(plens)}
+    srcs = [1, 0, 3, 2]  # prefill rows
+    # beam rows of the requests: shuffled table rows above the prefill rows
+    perm = (torch.randperm(n_rows + 2, generator=g)[:n_rows] + n_req).to(torch.int64)
+    gi = np.concatenate(([0], np.cumsum(bws)))
+    out["rows"], out["group_indptr"], out["srcs"] = perm.numpy(), gi.astype(np.int32), np.array(srcs)
+    # fan-out: the batched call needs one beam width, so run it per width class as the engine does
+    fake = types.SimpleNamespace(req_pool=types.SimpleNamespace(req_to_token=table), _stage=None)
+    for r in range(n_req):
+        ModelEngine.copy_prefill_to_beams_many(fake, [srcs[r]], perm[gi[r]:gi[r + 1]].view(1, -1), [plens[r]])
+    out["table_fanout"] = table.numpy().copy()
+    next_slot = 2000
+    parents = None
+    for tick in range(3):
+        if parents is not None:  # remaps deferred from the previous tick (scheduler.py:1590-1610)
+            for r in range(n_req):
+                remap_by_parents(table, perm[gi[r]:gi[r + 1]], parents[gi[r]:gi[r + 1]], plens[r], plens[r] + tick)
+        out_cache = torch.arange(next_slot, next_slot + n_rows, dtype=torch.int64)
+        next_slot += n_rows
+        col_idx = torch.tensor(np.repeat(plens, bws)) + tick
+        table[perm, col_idx] = out_cache.to(dtype=table.dtype).view(-1)  # scheduler.py:1305-1310
+        seq_lens = (col_idx + 1).to(torch.int32)
+        flat = gather_kv_indices(table, perm, seq_lens.tolist())
+        out[f"new_slot{tick}"], out[f"seq_lens{tick}"] = out_cache.numpy(), seq_lens.numpy()
+        out[f"flat{tick}"], out[f"table{tick + 1}"] = flat.numpy(), table.numpy().copy()
+        if parents is not None:
+            out[f"parents{tick}"] = parents.numpy()
+        # parents chosen by this tick's expand: forks, permutations and out-of-range values (clamped)
+        parents = torch.cat([torch.randint(-1, bw + 1, (bw,), generator=g) for bw in bws]).to(torch.int64)
+    np.savez_compressed(HERE / "kv_table.npz", **out)
+    print("wrote kv_table.npz")
 
 
 def main() -> None:
@@ -191,6 +238,7 @@ def main() -> None:
                         node_in=node_in.numpy(), token_ids=token_ids.numpy(), vals=res.vals.numpy(),
                         parents=res.parents.numpy(), tokens=res.tokens.numpy(), indices=res.indices.numpy(),
                         token_ids_out=res.token_ids.numpy(), node_out=res.node_ids.numpy())
+    kv_table_fixture()
     print("wrote", sorted(p.name for p in HERE.glob("*.npz")))
 
 
@@ -201,4 +249,7 @@ if __name__ == "__main__":
         sys.exit("usage: make_golden.py <reference checkout>/python   (or set FLASHREC_REFERENCE)")
     if ref not in sys.path:
         sys.path.insert(0, ref)
-    main()
+    if sys.argv[2:4] == ["--only", "kv_table"]:
+        kv_table_fixture()
+    else:
+        main()

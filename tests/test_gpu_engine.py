@@ -143,6 +143,23 @@ def test_engine_graph_equals_eager_and_sids_are_legal():
         eng = SidDecodeEngine(cfg, 3, 16, [20, 33, 17], sizes, base, trie, DEV, shared_prefix=8, seed=1)
         eng.run(host_io=False, _eager=True)
         eager = (eng.cum.clone(), eng.final_tokens.clone(), eng.final_nodes.clone())
+        # the slot table and the last flat slot list are what the reference's torch bookkeeping gives
+        # for the parents this wave chose (fan-out, then per tick: deferred remap, write_decode, gather)
+        tab = eng.req_to_token.cpu()
+        exp = tab.clone()
+        exp[: eng.rows] = 0
+        O.copy_prefill_to_beams_many(exp, eng.prefill_rows.cpu(), eng.rows_idx.cpu().view(eng.n, eng.bw),
+                                     max(eng.prompt_lens))
+        pre = eng.prefix_len_rows.cpu()
+        for s in range(eng.steps):
+            par = eng.outs[s - 1].parents.cpu().view(-1) if s else None
+            indptr, flat = O.kv_table_step(exp, eng.rows_idx.cpu(), eng.group_indptr.cpu(), pre + s + 1,
+                                           eng.h_loc[s], par, pre)
+        n_flat = int(indptr[-1])
+        assert torch.equal(eng.kv_indptr.cpu(), indptr) and torch.equal(eng.kv_indices.cpu()[:n_flat], flat)
+        for r in range(eng.rows):  # columns a reader can reach: [:seq_len]
+            sl = int(pre[r]) + eng.steps
+            assert torch.equal(tab[r, :sl], exp[r, :sl]), r
         eng.capture()
         eng.run(host_io=True)
         assert torch.equal(eng.cum, eager[0]) and torch.equal(eng.final_tokens, eager[1])

@@ -132,3 +132,41 @@ def test_mask_topk_expand_matches_reference():
     rows_live = live  # [n, k] == [n, bw] here
     assert np.array_equal(res["token_ids"].numpy()[rows_live], b["token_ids_out"][rows_live])
     assert np.array_equal(res["node_ids"].numpy()[rows_live], b["node_out"][rows_live])
+
+
+def _kv_table_replay(g, step_fn, fanout_fn, table):
+    """Replay the fixture's three ticks with ``step_fn`` / ``fanout_fn``; yields what each produced."""
+    rows, gi = torch.from_numpy(g["rows"]), g["group_indptr"]
+    bws, plens = g["bws"].tolist(), g["plens"].tolist()
+    for r in range(len(bws)):
+        fanout_fn(table, torch.tensor([int(g["srcs"][r])]), rows[gi[r]:gi[r + 1]].view(1, -1), plens[r])
+    yield "fanout", table, None
+    prefix = torch.tensor(np.repeat(plens, bws), dtype=torch.int32)
+    for tick in range(3):
+        parents = torch.from_numpy(g[f"parents{tick}"]) if tick else None
+        flat = step_fn(table, rows, torch.from_numpy(gi), torch.from_numpy(g[f"seq_lens{tick}"]),
+                       torch.from_numpy(g[f"new_slot{tick}"]), parents, prefix)
+        yield tick, table, flat
+
+
+def test_kv_table_ticks_match_reference():
+    g = load_golden("kv_table")
+    table = torch.from_numpy(g["table0"].copy())
+    step = lambda t, rows, gi, sl, ns, par, pre: O.kv_table_step(t, rows, gi, sl, ns, par, pre)[1]
+    for tag, tab, flat in _kv_table_replay(g, step, O.copy_prefill_to_beams_many, table):
+        if tag == "fanout":
+            assert np.array_equal(tab.numpy(), g["table_fanout"])
+        else:
+            assert np.array_equal(tab.numpy(), g[f"table{tag + 1}"]), tag
+            assert np.array_equal(flat.numpy(), g[f"flat{tag}"]), tag
+
+
+def test_remap_by_parents_known_answer():
+    # the reference's own vector (tests/test_kv_remap.py:19-30): a fork gathers columns 2:4 by parent
+    table = torch.arange(20).view(4, 5).clone()
+    O.remap_by_parents(table, torch.arange(4), torch.tensor([0, 0, 1, 1]), 2, 4)
+    assert table[:, 2:4].tolist() == [[2, 3], [2, 3], [7, 8], [7, 8]]
+    assert table[:, :2].tolist() == [[0, 1], [5, 6], [10, 11], [15, 16]] and table[:, 4].tolist() == [4, 9, 14, 19]
+    before = table.clone()
+    O.remap_by_parents(table, torch.arange(4), torch.arange(4), 2, 4)  # identity parents change nothing
+    assert torch.equal(table, before)
