@@ -55,8 +55,12 @@ def parse():
     ap.add_argument("--items", type=int, default=1_000_000)
     ap.add_argument("--trie", default="csr", choices=["csr", "bitmap"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-prefill", action="store_true",
+                    help="leave the prompt K/V as the synthetic fill instead of running the prefill pass")
     ap.add_argument("--no-fuse-rope-gemm", action="store_true",
                     help="run QK-norm + RoPE + KV write as their own kernel instead of in the qkv GEMM's epilogue")
+    ap.add_argument("--profile-prefill", action="store_true",
+                    help="run one prefill pass between cudaProfilerStart/Stop and exit (for ncu --profile-from-start off)")
     ap.add_argument("--profile-wave", action="store_true",
                     help="run one eager (non-graph) wave between cudaProfilerStart/Stop and exit (for ncu "
                          "--profile-from-start off)")
@@ -415,6 +419,29 @@ def main():
     trie = trie_to_device(arrays, args.trie, dev)
     eng = SidDecodeEngine(cfg, args.requests, args.beam, prompt_lengths(args.requests, rank), sizes, token_base, trie,
                           dev, shared_prefix=64, page_size=16, seed=rank, fuse_rope_gemm=not args.no_fuse_rope_gemm)
+    # Prefill of the prompts (eager, one extend batch): the decode waves below then read real K/V. Timed on
+    # its own; it is not part of `value` (the metric is the decode step).
+    prefill = None
+    if not args.no_prefill:
+        eng.prefill()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        eng.prefill()
+        e1.record()
+        torch.cuda.synchronize()
+        pms = e0.elapsed_time(e1)
+        prefill = {"tokens": eng.prefill_tokens, "ms": pms, "tokens_per_s": eng.prefill_tokens / pms * 1e3,
+                   "note": "prompts U[128,1024], 64-token shared prefix computed once (cached prefix for the rest)"}
+    if args.profile_prefill:
+        eng.prefill()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        eng.prefill()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print(json.dumps({"profiled_prefill_tokens": eng.prefill_tokens}))
+        return
     # count this library's kernel launches in one eager wave
     counter = {"n": 0}
     orig_call = _lib.call
@@ -539,6 +566,7 @@ def main():
             "gpu_launches": launches_per_wave * args.steps,
             "roofline": roof,
             "cpu_baseline": cpu,
+            "prefill": prefill,
             "illegal_sid_beams": illegal,
             "device_status": [code, site],
         }

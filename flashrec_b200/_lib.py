@@ -92,6 +92,8 @@ _SIGNATURES = {
     "fr_decode_attn_scratch_bytes": [_I, _I, _I],
     "fr_decode_attn_fp8": [P, _L, _L, P, P, _L, _L, _L, _L, P, P, P, P, P, _L, _I, _I, _I, _I, _I, _I, _I, _F, P, _L,
                            _I, P],
+    "fr_prefill_attn_fp8": [P, _L, _L, P, P, _L, _L, _L, _L, P, P, P, P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _F, P, _L,
+                            P],
     "fr_decode_attn_reuse_fp8": [P, _L, _L, P, P, _L, _L, _L, _L, P, P, P, P, P, _L, _I, _I, _I, _I, _I, _I, _I, _F, P,
                                  _L, _I, P, P],
     "fr_logsumexp_rows": [P, _L, P, P, P, _L, _I, _I, P],

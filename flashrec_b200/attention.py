@@ -198,6 +198,7 @@ class AttentionBackend:
         self.head_dim = int(head_dim)
         self.n_rep = self.num_qo_heads // self.num_kv_heads
         self._group_rows: Optional[torch.Tensor] = None
+        self._prefill_scratch: Optional[torch.Tensor] = None
         self._shared_len: Optional[torch.Tensor] = None
         self._max_group_rows = 0
         self._n_groups = 0
@@ -256,18 +257,39 @@ class AttentionBackend:
         call("fr_decode_attn_plan", ptr(batch.kv_indptr), ptr(batch.kv_indices), ptr(self._group_rows),
              self._n_groups, self._max_group_rows, ptr(self._shared_len), stream_ptr(batch.kv_indptr.device))
 
+    def _forward_prefill(self, q, kc, vc, batch, out) -> torch.Tensor:
+        """Causal attention of the extend tokens over each request's slot list (the new tokens' K/V
+        are in the pool already): the prefill branch of ``AttentionBackend.forward``
+        (attention/flashinfer.py:351-378; mask of ``_sdpa``, attention/flashinfer.py:380-431)."""
+        ext = [int(x) for x in (batch.extend_seq_lens or [])]
+        n_req = len(ext)
+        if n_req == 0 or batch.qo_indptr is None or batch.kv_indptr is None or batch.kv_indices is None:
+            raise ValueError("a prefill batch needs extend_seq_lens, qo_indptr, kv_indptr and kv_indices")
+        pre = [int(x) for x in (batch.extend_prefix_lens or [0] * n_req)]
+        max_ext, max_kv = max(ext), max(e + p for e, p in zip(ext, pre))
+        need = int(_lib.load().fr_decode_attn_scratch_bytes(n_req, self.num_kv_heads, max_kv))
+        if self._prefill_scratch is None or self._prefill_scratch.numel() < need:
+            self._prefill_scratch = torch.empty(need, dtype=torch.uint8, device=q.device)
+        scratch = self._prefill_scratch
+        call("fr_prefill_attn_fp8", ptr(q), q.stride(0), q.stride(1), ptr(kc), ptr(vc), kc.stride(0), kc.stride(1),
+             vc.stride(0), vc.stride(1), ptr(batch.qo_indptr), ptr(batch.kv_indptr), ptr(batch.kv_indices), ptr(out),
+             out.stride(0), int(q.shape[0]), n_req, self.num_qo_heads, self.num_kv_heads, self.head_dim, max_ext,
+             max_kv, self.kv_pool.num_tokens, float(self.head_dim) ** -0.5, ptr(scratch), int(scratch.numel()),
+             stream_ptr(q.device))
+        return out
+
     def forward(self, q, k, v, layer_id: int, batch, skip_store: bool = False, out=None) -> torch.Tensor:
         """q: [T, Hq, D] bf16 (may be a strided view); returns [T, Hq, D] bf16."""
         require_cuda(q)
         if not skip_store:
             self.kv_pool.store(layer_id, k, v, batch.out_cache_loc)
-        if batch.is_prefill:
-            raise NotImplementedError("flashrec_b200 covers the decode step; prefill attention is out of scope")
         t = int(q.shape[0])
         if out is None:
             out = torch.empty((t, self.num_qo_heads, self.head_dim), dtype=torch.bfloat16, device=q.device)
         kc = self.kv_pool.k[layer_id]
         vc = self.kv_pool.v[layer_id]
+        if batch.is_prefill:
+            return self._forward_prefill(q, kc, vc, batch, out)
         scratch = self._scratch_for(layer_id, q.device) if self.max_shared_len > 0 else None
         args = (ptr(q), q.stride(0), q.stride(1), ptr(kc), ptr(vc), kc.stride(0), kc.stride(1),
                 vc.stride(0), vc.stride(1), ptr(batch.kv_indptr), ptr(batch.kv_indices), ptr(self._group_rows),

@@ -64,7 +64,22 @@ struct Params {
   int n_rows, n_groups, hq, hkv, num_slots;
   float scale_log2;
   const int32_t* prepared_len;  // per group: tokens of the prefix already widened in scratch (or nullptr)
+  // prefill (causal) use: the group's slot list is indices[kv_group_indptr[g] .. kv_group_indptr[g+1])
+  // and the group's rows are its last tokens, in order (nullptr for decode)
+  const int32_t* kv_group_indptr;
 };
+
+// Slot list and number of keys that all rows of group `grp` share (decode: the shared prefix found by the
+// plan; prefill: every key of the request).
+__device__ __forceinline__ int group_keys(const Params& p, int grp, int row0, const int32_t*& idx) {
+  if (p.kv_group_indptr != nullptr) {
+    const int b = p.kv_group_indptr[grp];
+    idx = p.indices + b;
+    return min(max(p.kv_group_indptr[grp + 1] - b, 0), p.lcap);
+  }
+  idx = p.indices + p.indptr[row0];
+  return min(p.shared_len[grp], p.lcap);
+}
 
 __device__ __forceinline__ __half2 e4m3x2_to_half2(uint16_t v) {
   __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(v), __NV_E4M3);
@@ -101,15 +116,15 @@ __device__ __forceinline__ float2 e4m3x2_to_float2(uint16_t v) {
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) shared_kv_prepare_kernel(Params p) {
   const int grp = blockIdx.z, kvh = blockIdx.y;
-  const int ls = min(p.shared_len[grp], p.lcap);
+  const int row0 = p.group_rows[grp];
+  const int32_t* idx;
+  const int ls = group_keys(p, grp, row0, idx);
   const int padded = (ls + kTileN - 1) / kTileN * kTileN;  // tiles are read whole: zero-fill their tails
   const int tok0 = blockIdx.x * 32;
   if (tok0 >= padded) return;
   // tokens below `done` were widened by an earlier call on the same scratch and are still valid
   const int done = p.prepared_len != nullptr ? min(p.prepared_len[grp], ls) : 0;
   if (tok0 + 32 <= done) return;
-  const int row0 = p.group_rows[grp];
-  const int32_t* idx = p.indices + p.indptr[row0];
   const size_t gh = static_cast<size_t>(grp) * p.hkv + kvh;
   __nv_bfloat16* kb = p.kb + gh * p.lcap * kD;
   __half* vt = p.vt + gh * kD * p.lcap;
@@ -153,7 +168,10 @@ __global__ void __launch_bounds__(256) shared_kv_prepare_kernel(Params p) {
 // ---------------------------------------------------------------------------
 // step 2
 // ---------------------------------------------------------------------------
-template <int G>
+// CAUSAL: prefill. The rows of a group are the request's last tokens (its extend tokens), row e sees the
+// keys [0, prefix + e] with prefix = keys - rows; tiles past the last row of the CTA are skipped, the
+// tiles on the diagonal are masked per row, and there is no per-row tail.
+template <int G, bool CAUSAL>
 __global__ void __launch_bounds__(kThreads, 2)
 decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                       const __grid_constant__ CUtensorMap tmap_v, Params p, int* status) {
@@ -183,8 +201,12 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   const int rows_in_group = p.group_rows[grp + 1] - row0;
   const int beam0 = blockIdx.x * kBeams;
   if (beam0 >= rows_in_group) return;
-  const int ls = min(p.shared_len[grp], p.lcap);
-  const int n_tiles = (ls + kTileN - 1) / kTileN;
+  const int32_t* idx_unused;
+  const int ls = group_keys(p, grp, row0, idx_unused);
+  const int pfx = CAUSAL ? max(ls - rows_in_group, 0) : 0;
+  // keys the last live row of this CTA sees (CTA-uniform: every role derives the same tile count)
+  const int vis = CAUSAL ? min(ls, pfx + min(beam0 + kBeams, rows_in_group)) : ls;
+  const int n_tiles = (vis + kTileN - 1) / kTileN;
   const int gh = grp * p.hkv + kvh;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -322,8 +344,12 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       ptx::tmem_ld_32x32(t_lane + kColS + (j & 1) * kTileN, s0);
       ptx::tmem_ld_32x32(t_lane + kColS + (j & 1) * kTileN + 32, s1);
       ptx::tmem_ld_wait();
-      const int ntok = min(kTileN, ls - j * kTileN);
-      if (ntok < kTileN) {  // last tile of the prefix (uniform over the CTA): mask the columns past its end
+      // decode: only the last tile of the prefix is short (uniform over the CTA); prefill: row e stops at
+      // key prefix + e, so the tiles on the diagonal are short by a different amount per row (never the
+      // first tile as a whole: key 0 is visible to every row, the running maximum is finite from tile 0 on)
+      const int row_keys = CAUSAL ? min(ls, pfx + (live ? beam : rows_in_group - 1) + 1) : ls;
+      const int ntok = min(kTileN, row_keys - j * kTileN);
+      if (ntok < kTileN) {
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
           if (c >= ntok) s0[c] = 0xff800000u;       // -inf
@@ -391,8 +417,8 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     }
     if (ok) {
       // ---- per-row tail: slots after the shared prefix ------------------------
-      const int t_beg = p.indptr[row] + ls;
-      const int t_len = live ? max(p.indptr[row + 1] - t_beg, 0) : 0;
+      const int t_beg = CAUSAL ? 0 : p.indptr[row] + ls;
+      const int t_len = (!CAUSAL && live) ? max(p.indptr[row + 1] - t_beg, 0) : 0;
       int max_len = t_len;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) max_len = max(max_len, __shfl_xor_sync(0xffffffffu, max_len, o));
@@ -584,7 +610,7 @@ static int make_tmap_bf16_3d(CUtensorMap* map, const void* ptr, uint64_t d0, uin
   return r == CUDA_SUCCESS ? FR_OK : FR_ERR_CUDA;
 }
 
-template <int G>
+template <int G, bool CAUSAL>
 static int launch(const Params& p, int max_group_rows, cudaStream_t stream) {
   CUtensorMap tq, tk, tv;
   int st = make_tmap_bf16_3d(&tq, p.q, kD, p.hq, p.n_rows, static_cast<uint64_t>(p.q_h) * 2,
@@ -596,7 +622,7 @@ static int launch(const Params& p, int max_group_rows, cudaStream_t stream) {
   st = make_tmap_bf16_3d(&tv, p.vt, p.lcap, kD, gh, static_cast<uint64_t>(p.lcap) * 2,
                          static_cast<uint64_t>(p.lcap) * kD * 2, kTileN, kD, 1, true);
   if (st != FR_OK) return st;
-  auto kern = decode_attn_tc_kernel<G>;
+  auto kern = decode_attn_tc_kernel<G, CAUSAL>;
   static bool attr_done = false;
   if (!attr_done) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
@@ -633,12 +659,50 @@ int decode_attn_tc(const void* q, int64_t q_t, int64_t q_h, const void* k_cache,
   p.kb = static_cast<__nv_bfloat16*>(scratch);
   p.vt = reinterpret_cast<__half*>(p.kb + half);
   switch (G) {
-    case 1: return attn_tc::launch<1>(p, max_group_rows, stream);
-    case 2: return attn_tc::launch<2>(p, max_group_rows, stream);
-    case 4: return attn_tc::launch<4>(p, max_group_rows, stream);
-    case 8: return attn_tc::launch<8>(p, max_group_rows, stream);
+    case 1: return attn_tc::launch<1, false>(p, max_group_rows, stream);
+    case 2: return attn_tc::launch<2, false>(p, max_group_rows, stream);
+    case 4: return attn_tc::launch<4, false>(p, max_group_rows, stream);
+    case 8: return attn_tc::launch<8, false>(p, max_group_rows, stream);
     default: return FR_ERR_UNSUPPORTED;
   }
 }
 
 }  // namespace fr
+
+using namespace fr;
+
+extern "C" int64_t fr_decode_attn_scratch_bytes(int n_groups, int hkv, int max_shared_len);
+
+extern "C" int fr_prefill_attn_fp8(const void* q, int64_t q_t, int64_t q_h, const void* k_cache, const void* v_cache,
+                                   int64_t ck_s, int64_t ck_h, int64_t cv_s, int64_t cv_h, const int32_t* qo_indptr,
+                                   const int32_t* kv_indptr, const int32_t* kv_indices, void* out, int64_t o_t,
+                                   int n_tokens, int n_requests, int hq, int hkv, int head_dim, int max_extend_len,
+                                   int max_kv_len, int num_slots, float sm_scale, void* scratch,
+                                   int64_t scratch_bytes, cudaStream_t stream) {
+  FR_CHECK_ARG(n_tokens >= 0 && n_requests >= 0 && hq > 0 && hkv > 0 && max_extend_len >= 0 && max_kv_len >= 0 &&
+               num_slots > 0);
+  if (n_tokens == 0 || n_requests == 0 || max_extend_len == 0 || max_kv_len == 0) return FR_OK;
+  FR_CHECK_ARG(q && k_cache && v_cache && qo_indptr && kv_indptr && kv_indices && out && scratch);
+  FR_CHECK_SUPPORTED(head_dim == attn_tc::kD && hq % hkv == 0);
+  const int G = hq / hkv;
+  FR_CHECK_SUPPORTED(G == 1 || G == 2 || G == 4 || G == 8);
+  FR_CHECK_ARG(aligned16(q) && (q_t * 2) % 16 == 0 && (q_h * 2) % 16 == 0 && aligned16(out) && (o_t * 2) % 16 == 0);
+  FR_CHECK_ARG(aligned16(k_cache) && aligned16(v_cache) && ck_s % 16 == 0 && ck_h % 16 == 0 && cv_s % 16 == 0 &&
+               cv_h % 16 == 0 && aligned16(scratch));
+  FR_CHECK_ARG(scratch_bytes >= fr_decode_attn_scratch_bytes(n_requests, hkv, max_kv_len));
+  const int lcap = (max_kv_len + attn_tc::kTileN - 1) / attn_tc::kTileN * attn_tc::kTileN;
+  attn_tc::Params p{static_cast<const __nv_bfloat16*>(q), q_t, q_h, static_cast<const uint8_t*>(k_cache),
+                    static_cast<const uint8_t*>(v_cache), ck_s, ck_h, cv_s, cv_h, nullptr, kv_indices, qo_indptr,
+                    nullptr, static_cast<__nv_bfloat16*>(out), o_t, nullptr, nullptr, lcap, n_tokens, n_requests, hq,
+                    hkv, num_slots, sm_scale * 1.4426950408889634f, nullptr, kv_indptr};
+  const size_t half = static_cast<size_t>(n_requests) * hkv * lcap * attn_tc::kD;
+  p.kb = static_cast<__nv_bfloat16*>(scratch);
+  p.vt = reinterpret_cast<__half*>(p.kb + half);
+  switch (G) {
+    case 1: return attn_tc::launch<1, true>(p, max_extend_len, stream);
+    case 2: return attn_tc::launch<2, true>(p, max_extend_len, stream);
+    case 4: return attn_tc::launch<4, true>(p, max_extend_len, stream);
+    case 8: return attn_tc::launch<8, true>(p, max_extend_len, stream);
+    default: return FR_ERR_UNSUPPORTED;
+  }
+}

@@ -37,7 +37,12 @@ class Qwen3Config:
 
 @dataclass
 class ForwardBatch:
-    """One decode forward; ``n_rows`` = total beam rows (core.py:81-101)."""
+    """One forward; ``n_rows`` = total beam rows (decode) or prompts (prefill) (core.py:81-101).
+
+    Prefill (``is_prefill``): ``input_ids`` / ``positions`` / ``out_cache_loc`` hold one entry per
+    extend token, ``seq_lens`` / ``kv_indptr`` one per request; ``extend_seq_lens`` and
+    ``extend_prefix_lens`` are the reference's host lists, ``qo_indptr`` (int32, device,
+    ``[n_rows + 1]``) is the running sum of ``extend_seq_lens`` that the attention kernel reads."""
 
     input_ids: torch.Tensor
     req_pool_indices: Optional[torch.Tensor]
@@ -47,6 +52,9 @@ class ForwardBatch:
     is_prefill: bool = False
     kv_indices: Optional[torch.Tensor] = None
     kv_indptr: Optional[torch.Tensor] = None
+    extend_prefix_lens: Optional[List[int]] = None
+    extend_seq_lens: Optional[List[int]] = None
+    qo_indptr: Optional[torch.Tensor] = None
 
     @property
     def n_rows(self) -> int:
@@ -216,6 +224,18 @@ class Qwen3ForCausalLM:
             return self.norm(x)
         x, _ = self.norm(x, residual)
         return x
+
+    def last_token_hidden(self, hidden: torch.Tensor, batch: ForwardBatch) -> torch.Tensor:
+        """Rows of ``hidden`` that feed the head: all of them for a decode batch, each request's
+        last extend token for a prefill batch (ModelEngine.last_token_hidden, engine/engine.py:286-303).
+        The offsets come from ``qo_indptr`` on the device; nothing is staged from the host."""
+        if not batch.is_prefill or not batch.extend_seq_lens:
+            return hidden
+        idx = (batch.qo_indptr[1:] - 1).to(torch.int64)
+        out = torch.empty((idx.numel(), hidden.shape[1]), dtype=torch.bfloat16, device=hidden.device)
+        call("fr_embedding_bf16", ptr(hidden), ptr(idx), ptr(out), idx.numel(), int(hidden.shape[1]),
+             int(hidden.shape[0]), stream_ptr(hidden.device))
+        return out
 
     # -- random initialisation used by the benchmark / tests --------------------
     def init_random(self, seed: int = 0, std: float = 0.02, embed: bool = True) -> None:

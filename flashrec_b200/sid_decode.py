@@ -122,6 +122,8 @@ class SidDecodeEngine:
         self.use_graphs = bool(use_graphs)
         self.prompt_lens = [int(p) for p in prompt_lens]
         assert len(self.prompt_lens) == self.n
+        self.shared_prefix = int(shared_prefix)
+        self.seed = int(seed)
         dev = self.device
         g = torch.Generator(device=dev)
         g.manual_seed(seed)
@@ -284,6 +286,43 @@ class SidDecodeEngine:
             self.h_vals.copy_(self.cum, non_blocking=True)
             self.h_tokens.copy_(self.tok_planes[last], non_blocking=True)
             torch.cuda.current_stream(self.device).synchronize()
+
+    def prefill(self) -> torch.Tensor:
+        """Run the model over the prompts (seeded random token ids) so that the pool holds their real
+        K/V instead of the synthetic fill, as one extend batch: request 0 computes the shared prefix,
+        the others take it as a cached prefix (a radix hit; ``extend_prefix_lens``, core.py:81-101) and
+        extend only their own tokens. Eager, like the reference's prefill. Returns the hidden state
+        of each request's last prompt token, ``[n_requests, hidden]`` (engine/engine.py:286-303)."""
+        dev = self.device
+        sp = self.shared_prefix
+        pre = [0 if r == 0 else min(sp, p) for r, p in enumerate(self.prompt_lens)]
+        ext = [p - q for p, q in zip(self.prompt_lens, pre)]
+        if min(ext) <= 0:
+            raise ValueError("every request needs at least one token of its own after the shared prefix")
+        g = torch.Generator().manual_seed(self.seed + 17)
+        shared_ids = torch.randint(0, self.token_base, (sp,), generator=g)
+        ids, pos = [], []
+        for r, plen in enumerate(self.prompt_lens):
+            own = torch.randint(0, self.token_base, (plen - min(sp, plen),), generator=g)
+            full = torch.cat((shared_ids[: min(sp, plen)], own))
+            ids.append(full[pre[r]:])
+            pos.append(torch.arange(pre[r], plen))
+        seq = torch.tensor(self.prompt_lens, dtype=torch.int32, device=dev)
+        n_idx = sum(self.prompt_lens)
+        kv_indices = torch.empty(n_idx, dtype=torch.int32, device=dev)
+        kv_indptr = torch.empty(self.n + 1, dtype=torch.int32, device=dev)
+        kv_table_step(self.req_to_token, self.prefill_rows, seq, kv_indices, kv_indptr)  # plain gather
+        table = self.req_to_token[self.rows:].cpu()
+        loc = torch.cat([table[r, pre[r]: self.prompt_lens[r]] for r in range(self.n)]).to(torch.int64)
+        qo = torch.zeros(self.n + 1, dtype=torch.int32)
+        qo[1:] = torch.cumsum(torch.tensor(ext), 0)
+        batch = ForwardBatch(input_ids=torch.cat(ids).to(dev), req_pool_indices=self.prefill_rows, seq_lens=seq,
+                             positions=torch.cat(pos).to(dev), out_cache_loc=loc.to(dev), is_prefill=True,
+                             kv_indices=kv_indices, kv_indptr=kv_indptr, extend_prefix_lens=pre,
+                             extend_seq_lens=ext, qo_indptr=qo.to(dev))
+        hidden = self.model.forward(batch)
+        self.prefill_tokens = int(qo[-1])
+        return self.model.last_token_hidden(hidden, batch)
 
     # results of the last run (device tensors)
     @property

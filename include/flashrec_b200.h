@@ -248,6 +248,22 @@ int fr_decode_attn_reuse_fp8(const void* q, int64_t q_t, int64_t q_h, const void
                        int num_slots, float sm_scale, void* scratch, int64_t scratch_bytes, int max_shared_len,
                        const int32_t* prepared_len, cudaStream_t stream);
 
+/* Causal attention of a prefill (extend) batch over the e4m3 pool, on the tensor cores.
+ * Request g owns query tokens [qo_indptr[g], qo_indptr[g+1]) of q / out and the slot list
+ * kv_indices[kv_indptr[g] .. kv_indptr[g+1]) (its cached prefix followed by the extend tokens'
+ * own slots, already written to the pool); token e of the request sees keys [0, prefix + e] with
+ * prefix = keys - extend tokens. q, out, caches, sm_scale as in fr_decode_attn_fp8; head_dim 128.
+ * scratch: fr_decode_attn_scratch_bytes(n_requests, hkv, max_kv_len) bytes; max_extend_len and
+ * max_kv_len bound the requests' extend and key counts (keys past max_kv_len would be ignored).
+ * Reference: AttentionBackend.forward prefill branch, FlashInfer BatchPrefillWithPagedKVCache
+ * planned causal with page_size 1 (attention/flashinfer.py:351-378), and its SDPA twin
+ * (_sdpa, attention/flashinfer.py:380-431: mask s <= prefix + e). */
+int fr_prefill_attn_fp8(const void* q, int64_t q_t, int64_t q_h, const void* k_cache, const void* v_cache,
+                        int64_t ck_s, int64_t ck_h, int64_t cv_s, int64_t cv_h, const int32_t* qo_indptr,
+                        const int32_t* kv_indptr, const int32_t* kv_indices, void* out, int64_t o_t, int n_tokens,
+                        int n_requests, int hq, int hkv, int head_dim, int max_extend_len, int max_kv_len,
+                        int num_slots, float sm_scale, void* scratch, int64_t scratch_bytes, cudaStream_t stream);
+
 /* ---- trie-constrained SID head ------------------------------------------- */
 
 enum fr_trie_kind { FR_TRIE_NONE = 0, FR_TRIE_DENSE = 1, FR_TRIE_CSR = 2, FR_TRIE_BITMAP = 3 };

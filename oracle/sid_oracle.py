@@ -246,6 +246,30 @@ def decode_attention(q, k_cache, v_cache, kv_indptr, kv_indices, n_rep: int) -> 
     return out.to(q.dtype)
 
 
+def prefill_attention(q, k_cache, v_cache, qo_indptr, kv_indptr, kv_indices, n_rep: int) -> torch.Tensor:
+    """attention/flashinfer.py:380-431 (_sdpa, prefill branch), evaluated in fp32: extend token e of a
+    request attends to the keys s <= prefix + e of the request's slot list, prefix = keys - extend
+    tokens (the mask ``s_idx <= pfx + e_idx``; ``is_causal`` when the prefix is empty)."""
+    t, hq, d = q.shape
+    out = torch.zeros((t, hq, d), dtype=torch.float32)
+    scale = d ** -0.5
+    kf, vf = k_cache.float(), v_cache.float()
+    for g in range(len(qo_indptr) - 1):
+        q0, q1 = int(qo_indptr[g]), int(qo_indptr[g + 1])
+        idx = kv_indices[int(kv_indptr[g]) : int(kv_indptr[g + 1])].long()
+        e, sl = q1 - q0, int(idx.numel())
+        if e == 0 or sl == 0:
+            continue
+        pfx = sl - e
+        k = kf[idx].repeat_interleave(n_rep, dim=1)  # [L, Hq, D]
+        v = vf[idx].repeat_interleave(n_rep, dim=1)
+        sc = torch.einsum("ehd,lhd->hel", q[q0:q1].float(), k) * scale
+        mask = torch.arange(sl)[None, :] <= (pfx + torch.arange(e)[:, None])
+        sc = sc.masked_fill(~mask[None], float("-inf"))
+        out[q0:q1] = torch.einsum("hel,lhd->ehd", torch.softmax(sc, dim=-1), v)
+    return out.to(q.dtype)
+
+
 def decoder_layer(x, residual, w, norms, positions, loc, cos_sin_cache, k_cache, v_cache, kv_indptr, kv_indices,
                   hq: int, hkv: int, d: int, eps: float = 1e-6, trace: Optional[dict] = None):
     """FP8 branch of Qwen3DecoderLayer.forward (models/qwen3.py:198-215) with

@@ -2,9 +2,9 @@
 
 Usage (only where the reference checkout is available):
 
-    python tests/golden/make_golden.py <reference>/python [--only kv_table]
+    python tests/golden/make_golden.py <reference>/python [--only kv_table | --only prefill_attention]
 
-(``--only kv_table`` writes just ``kv_table.npz``, leaving the other files as they are.)
+(``--only NAME`` writes just ``NAME.npz``, leaving the other files as they are.)
 
 Every fixture holds seeded inputs and the outputs of the reference's own torch
 CPU code path (its ``sgl_kernel`` branch is absent, so each wrapper takes its
@@ -76,6 +76,29 @@ def kv_table_fixture() -> None:
         parents = torch.cat([torch.randint(-1, bw + 1, (bw,), generator=g) for bw in bws]).to(torch.int64)
     np.savez_compressed(HERE / "kv_table.npz", **out)
     print("wrote kv_table.npz")
+
+
+def prefill_attention_fixture() -> None:
+    """The reference's SDPA attention in its prefill branch (causal with and without a cached prefix)."""
+    from flashrec.attention.flashinfer import AttentionBackend
+    from flashrec.kvcache.pool import TokenToKVPool
+
+    g = torch.Generator().manual_seed(11)
+    hq, hkv, d, slots = 2, 1, 128, 200
+    pool = TokenToKVPool(1, slots, hkv, d, torch.float8_e4m3fn, torch.device("cpu"))
+    pool.k[0].copy_(torch.randn(slots, hkv, d, generator=g).bfloat16().to(torch.float8_e4m3fn))
+    pool.v[0].copy_(torch.randn(slots, hkv, d, generator=g).bfloat16().to(torch.float8_e4m3fn))
+    ext, pre = [70, 1, 33, 66], [0, 5, 64, 17]
+    seq = [e + p for e, p in zip(ext, pre)]
+    kvi = torch.cat([torch.randperm(slots - 1, generator=g)[:s] + 1 for s in seq]).to(torch.int32)
+    q = torch.randn(sum(ext), hq, d, generator=g).bfloat16()
+    fake = types.SimpleNamespace(kv_pool=pool, n_rep=hq // hkv, head_dim=d)
+    batch = types.SimpleNamespace(n_rows=len(ext), seq_lens_cpu=torch.tensor(seq), extend_prefix_lens=pre,
+                                  extend_seq_lens=ext, is_prefill=True, kv_indices=kvi)
+    o = AttentionBackend._sdpa(fake, q, 0, batch)
+    np.savez_compressed(HERE / "prefill_attention.npz", ext=np.array(ext), pre=np.array(pre), kv_indices=kvi.numpy(),
+                        q=bits16(q), k_cache=bits8(pool.k[0]), v_cache=bits8(pool.v[0]), out=bits16(o))
+    print("wrote prefill_attention.npz")
 
 
 def main() -> None:
@@ -239,6 +262,7 @@ def main() -> None:
                         parents=res.parents.numpy(), tokens=res.tokens.numpy(), indices=res.indices.numpy(),
                         token_ids_out=res.token_ids.numpy(), node_out=res.node_ids.numpy())
     kv_table_fixture()
+    prefill_attention_fixture()
     print("wrote", sorted(p.name for p in HERE.glob("*.npz")))
 
 
@@ -251,5 +275,7 @@ if __name__ == "__main__":
         sys.path.insert(0, ref)
     if sys.argv[2:4] == ["--only", "kv_table"]:
         kv_table_fixture()
+    elif sys.argv[2:4] == ["--only", "prefill_attention"]:
+        prefill_attention_fixture()
     else:
         main()

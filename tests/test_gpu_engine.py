@@ -141,6 +141,12 @@ def test_engine_graph_equals_eager_and_sids_are_legal():
     for layout in ("csr", "bitmap"):
         trie = trie_to_device(arrays, layout, DEV)
         eng = SidDecodeEngine(cfg, 3, 16, [20, 33, 17], sizes, base, trie, DEV, shared_prefix=8, seed=1)
+        # real prompt K/V from a prefill instead of the synthetic fill
+        before = eng.pool.k[0][16:24].clone()
+        h = eng.prefill()
+        assert h.shape == (3, cfg.hidden_size) and torch.isfinite(h.float()).all()
+        assert eng.prefill_tokens == 20 + (33 - 8) + (17 - 8)  # the shared prefix is computed once
+        assert not torch.equal(eng.pool.k[0][16:24].view(torch.uint8), before.view(torch.uint8))
         eng.run(host_io=False, _eager=True)
         eager = (eng.cum.clone(), eng.final_tokens.clone(), eng.final_nodes.clone())
         # the slot table and the last flat slot list are what the reference's torch bookkeeping gives
