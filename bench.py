@@ -55,6 +55,9 @@ def parse():
     ap.add_argument("--items", type=int, default=1_000_000)
     ap.add_argument("--trie", default="csr", choices=["csr", "bitmap"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--level0-from-prefill", action="store_true",
+                    help="the reference's flow: level 0 from the prefill's last-token logits, decode steps for the "
+                         "other levels only (not the default workload, which runs all three levels as decode steps)")
     ap.add_argument("--no-prefill", action="store_true",
                     help="leave the prompt K/V as the synthetic fill instead of running the prefill pass")
     ap.add_argument("--no-fuse-rope-gemm", action="store_true",
@@ -418,11 +421,12 @@ def main():
     arrays = build_trie_arrays(make_catalog(args.items, sizes), sizes, token_base)
     trie = trie_to_device(arrays, args.trie, dev)
     eng = SidDecodeEngine(cfg, args.requests, args.beam, prompt_lengths(args.requests, rank), sizes, token_base, trie,
-                          dev, shared_prefix=64, page_size=16, seed=rank, fuse_rope_gemm=not args.no_fuse_rope_gemm)
+                          dev, shared_prefix=64, page_size=16, seed=rank, fuse_rope_gemm=not args.no_fuse_rope_gemm,
+                          level0_from_prefill=args.level0_from_prefill)
     # Prefill of the prompts (eager, one extend batch): the decode waves below then read real K/V. Timed on
     # its own; it is not part of `value` (the metric is the decode step).
     prefill = None
-    if not args.no_prefill:
+    if not args.no_prefill or args.level0_from_prefill:
         eng.prefill()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -510,7 +514,7 @@ def main():
         sec_e2e = timed(True, args.steps)
     barrier()
     code, site = device_status()
-    rows_levels = args.requests * args.beam * len(sizes)
+    rows_levels = args.requests * args.beam * (len(sizes) - eng.first_step)  # decode steps x rows
     value = world * rows_levels * args.steps / sec
     e2e_value = world * rows_levels * args.steps / sec_e2e
     h2d = eng.rows * 8 * eng.steps
@@ -559,7 +563,8 @@ def main():
             "data": "synthetic",
             "config": dict(WORKLOAD, requests=args.requests, beam_width=args.beam, layers=args.layers,
                            catalog_items=int(arrays.n_items), trie=args.trie, parallelism=f"dp{world}",
-                           rows_per_gpu=eng.rows, value_per_gpu=value / world),
+                           rows_per_gpu=eng.rows, value_per_gpu=value / world,
+                           decode_steps_per_wave=eng.steps - eng.first_step),
             "clocks": clk.summary(),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": sec_e2e / args.steps * 1e3},

@@ -182,8 +182,8 @@ struct StepParams {
   int64_t* out_tokens;     // [N, K]
   int64_t* out_indices;    // [N, K] flat index b * C + c
   int64_t* out_child;      // [N, K] node after the step, or null
-  int64_t* token_ids_out;  // [N, BW, L] or null
-  int64_t* node_ids_out;   // [N, BW] or null
+  int64_t* token_ids_out;  // [N, max(BW, K), L] or null
+  int64_t* node_ids_out;   // [N, max(BW, K)] or null
   const float* cum;        // [N, BW]
   const int64_t* node_in;  // [N, BW] or null
   const int64_t* token_ids_in;
@@ -272,9 +272,12 @@ __device__ __forceinline__ void apply_winners(const StepParams& p, int n, const 
   if (!expand_this) return;
   int64_t col = 0;
   if (p.col_n) col = p.col_n[n] < 0 ? 0 : p.col_n[n];
+  // the output planes hold max(BW, K) beams per request: K > BW when a request fans out from fewer
+  // input beams than it selects (level 0 from one prefill row)
+  const int obw = p.K > p.BW ? p.K : p.BW;
   const int64_t* tin = p.token_ids_in + static_cast<size_t>(n) * p.BW * p.L;
-  int64_t* tout = p.token_ids_out + static_cast<size_t>(n) * p.BW * p.L;
-  const int plane = p.BW * p.L;
+  int64_t* tout = p.token_ids_out + static_cast<size_t>(n) * obw * p.L;
+  const int plane = obw * p.L;
   for (int i = threadIdx.x; i < plane; i += kThreads) {
     const int b = i / p.L, c = i - b * p.L;
     if (b >= p.K) { tout[i] = tin[i]; continue; }
@@ -283,8 +286,8 @@ __device__ __forceinline__ void apply_winners(const StepParams& p, int n, const 
   }
   if (p.apply_advance && p.node_in && p.node_ids_out) {
     const int64_t* nin = p.node_in + static_cast<size_t>(n) * p.BW;
-    int64_t* nout = p.node_ids_out + static_cast<size_t>(n) * p.BW;
-    for (int b = threadIdx.x; b < p.BW; b += kThreads) nout[b] = b < p.K ? sel_child[b] : nin[b];
+    int64_t* nout = p.node_ids_out + static_cast<size_t>(n) * obw;
+    for (int b = threadIdx.x; b < obw; b += kThreads) nout[b] = b < p.K ? sel_child[b] : nin[b];
   }
 }
 
@@ -569,7 +572,6 @@ static int check_step_common(const StepParams& p) {
   FR_CHECK_ARG(p.out_vals && p.out_parents && p.out_tokens && p.out_indices && p.cum);
   if (p.apply_expand) {
     FR_CHECK_ARG(p.token_ids_in && p.token_ids_out && p.token_ids_in != p.token_ids_out && p.L > 0);
-    FR_CHECK_SUPPORTED(p.K <= p.BW);
   }
   if (p.apply_advance) FR_CHECK_ARG(p.node_in && p.node_ids_out && p.node_in != p.node_ids_out);
   return FR_OK;

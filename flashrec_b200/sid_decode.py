@@ -60,7 +60,7 @@ def sid_beam_step(
 
     ``cum`` [N,BW] f32; ``logits`` [N*BW, K_l] f32 with row statistics;
     ``node_ids`` [N,BW] i64; ``trie`` a DeviceTrie (or None = unconstrained).
-    If the token planes are given (distinct in/out, [N,BW,L] i64) the winners'
+    If the token planes are given (distinct; in [N,BW,L], out [N,max(BW,K),L] i64) the winners'
     token rows are expanded and ``node_ids_out`` receives the advanced nodes."""
     n, bw = int(cum.shape[0]), int(cum.shape[1])
     kl = int(logits.shape[1])
@@ -109,6 +109,7 @@ class SidDecodeEngine:
         use_graphs: bool = True,
         keep_prefix: bool = True,
         fuse_rope_gemm: bool = True,
+        level0_from_prefill: bool = False,
     ):
         self.cfg = cfg
         self.device = torch.device(device)
@@ -124,6 +125,10 @@ class SidDecodeEngine:
         assert len(self.prompt_lens) == self.n
         self.shared_prefix = int(shared_prefix)
         self.seed = int(seed)
+        # the reference's flow: level 0 is chosen from the prefill's last-token logits (one row per
+        # request, init_from_prefill_batch, search/expand.py:168-237) and only levels 1.. are decode steps
+        self.first_step = 1 if level0_from_prefill else 0
+        self.prefill_hidden: Optional[torch.Tensor] = None
         dev = self.device
         g = torch.Generator(device=dev)
         g.manual_seed(seed)
@@ -202,6 +207,9 @@ class SidDecodeEngine:
         self.d_loc = self.h_loc.to(dev)  # device-resident copy for runs that exclude host traffic
         self.h_vals = torch.empty((self.n, self.bw), dtype=torch.float32).pin_memory()
         self.h_tokens = torch.empty((self.n, self.bw, self.steps), dtype=torch.int64).pin_memory()
+        self._cum0 = torch.zeros((self.n, 1), dtype=torch.float32, device=dev)
+        self._node0 = torch.zeros((self.n, 1), **i64)
+        self._tok0 = torch.zeros((self.n, 1, self.steps), **i64)
         self.graphs: List[Optional[torch.cuda.CUDAGraph]] = [None] * self.steps
         self.kernel_launches_per_step: List[int] = [0] * self.steps
         self.reset()
@@ -220,6 +228,23 @@ class SidDecodeEngine:
         self.positions.copy_(self.prompt_len_rows)
         self.seq_lens.copy_((self.prompt_len_rows + 1).to(torch.int32))
 
+    def _level0_from_prefill(self) -> None:
+        """Level 0 from the last prompt token of every request: one logits row per request, the
+        top ``beam_width`` legal first codes become the request's beams (init_from_prefill_batch,
+        search/expand.py:168-237, with the candidate set widened to the whole level). Same kernels as
+        a decode step, with one input beam per request."""
+        if self.prefill_hidden is None:
+            raise RuntimeError("level0_from_prefill needs prefill() first")
+        logits, mx, ls, _ = self.head.logits_level(self.prefill_hidden, 0)
+        self.col.fill_(0)
+        out = sid_beam_step(self._cum0, logits, mx, ls, self._node0, self.trie, self.level_tok_base[0], self.bw,
+                            token_ids_in=self._tok0, token_ids_out=self.tok_planes[1],
+                            node_ids_out=self.node_planes[1], col=self.col, out=self.outs[0])
+        self.cum.copy_(out.vals)
+        if self.trie is None:
+            self.node_planes[1].fill_(-1)
+        self.input_ids.copy_(out.tokens.reshape(-1))
+
     def _step_body(self, s: int) -> None:
         """Device work of decode step ``s`` (level ``s``); allocation-stable, capturable."""
         src, dst = s & 1, (s & 1) ^ 1
@@ -232,7 +257,7 @@ class SidDecodeEngine:
         batch = ForwardBatch(input_ids=self.input_ids, req_pool_indices=self.rows_idx, seq_lens=self.seq_lens,
                              positions=self.positions, out_cache_loc=self.out_cache_loc, kv_indices=self.kv_indices,
                              kv_indptr=self.kv_indptr)
-        self.attn.prepare(batch, reuse_prefix=s > 0)
+        self.attn.prepare(batch, reuse_prefix=s > self.first_step)
         hidden = self.model.forward(batch)
         logits, mx, ls, _ = self.head.logits_level(hidden, s)
         self.col.fill_(s)
@@ -259,7 +284,7 @@ class SidDecodeEngine:
         torch.cuda.current_stream(self.device).wait_stream(stream)
         torch.cuda.synchronize(self.device)
         self.reset()
-        for s in range(self.steps):
+        for s in range(self.first_step, self.steps):
             self.out_cache_loc.copy_(self.h_loc[s], non_blocking=True)
             gph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(gph):
@@ -272,7 +297,9 @@ class SidDecodeEngine:
         """One wave: all decode steps. With ``host_io`` the per-step slot ids come
         from pinned host memory and the final beams are read back to the host."""
         self.reset()
-        for s in range(self.steps):
+        if self.first_step:
+            self._level0_from_prefill()
+        for s in range(self.first_step, self.steps):
             if host_io:
                 self.out_cache_loc.copy_(self.h_loc[s], non_blocking=True)
             else:
@@ -322,7 +349,8 @@ class SidDecodeEngine:
                              extend_seq_lens=ext, qo_indptr=qo.to(dev))
         hidden = self.model.forward(batch)
         self.prefill_tokens = int(qo[-1])
-        return self.model.last_token_hidden(hidden, batch)
+        self.prefill_hidden = self.model.last_token_hidden(hidden, batch)
+        return self.prefill_hidden
 
     # results of the last run (device tensors)
     @property

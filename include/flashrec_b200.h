@@ -332,7 +332,9 @@ int fr_beam_expand(int64_t* out, const int64_t* token_ids, const int64_t* parent
                    int BW, int L, int col, cudaStream_t stream);
 
 /* Fused mask + sorted top-K over BW*C explicit candidates + token-row expand +
- * node advance, one request per CTA; K <= 4096 (K <= BW when expanding).
+ * node advance, one request per CTA; K <= 4096. The input planes are [N, BW, ..], the output
+ * planes [N, max(BW, K), ..]: K > BW is a request fanning out from fewer input beams than it
+ * selects (level 0 from one prefill row, init_from_prefill_batch, search/expand.py:168-237).
  * scratch: f32 [N, BW*C], required when masking. In/out planes must not alias.
  * out_child (optional): node after the step for each winner.
  * Reference: genrec_mask_topk_expand / call_genrec_cuda (kernel/beam_trie.py:

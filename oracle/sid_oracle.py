@@ -413,10 +413,14 @@ def mask_topk_expand(cum, top_logprobs, top_tokens, select_k, node_ids=None, tri
     )
     do_exp = bool(apply_expand and token_ids is not None)
     do_adv = bool(apply_advance and masked and do_exp)
+    # output planes hold max(bw, k) beams: k > bw when a request fans out from fewer input beams than it
+    # selects (level 0 from one prefill row, search/expand.py:168-237); rows past k keep their input
     if do_exp:
-        out["token_ids"] = token_ids.clone()
+        out["token_ids"] = torch.zeros((n, max(bw, k), token_ids.shape[2]), dtype=token_ids.dtype)
+        out["token_ids"][:, :bw] = token_ids
     if do_adv:
-        out["node_ids"] = node_ids.clone()
+        out["node_ids"] = torch.zeros((n, max(bw, k)), dtype=node_ids.dtype)
+        out["node_ids"][:, :bw] = node_ids
     if node_ids is not None and trie is not None:
         out["child"] = torch.zeros((n, k), dtype=torch.int64)
     cols = col if isinstance(col, torch.Tensor) else torch.full((n,), int(col))

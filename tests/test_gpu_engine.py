@@ -189,6 +189,50 @@ def test_engine_graph_equals_eager_and_sids_are_legal():
     assert device_status() == (0, 0)
 
 
+def test_engine_level0_from_prefill():
+    """The reference's own flow: prefill, level 0 from the last prompt token's logits (one row per request,
+    init_from_prefill_batch), then one decode step per further level. Level 0 against the CPU oracle on the
+    device's logits, eager against graph replay, legality of the final SIDs."""
+    from flashrec_b200 import device_status
+    from flashrec_b200.decoder import Qwen3Config
+    from flashrec_b200.sid_decode import SidDecodeEngine
+    from flashrec_b200.trie import build_trie_arrays, trie_to_device
+
+    cfg = Qwen3Config(hidden_size=256, num_attention_heads=2, num_key_value_heads=1, head_dim=128,
+                      intermediate_size=512, num_hidden_layers=2, max_position_embeddings=128, vocab_size=1000 + 96)
+    rng = np.random.default_rng(5)
+    sizes, base = [32, 32, 32], 1000
+    items = np.stack([rng.integers(0, 32, 700) for _ in sizes], 1)
+    arrays = build_trie_arrays(items, sizes, base)
+    trie = trie_to_device(arrays, "csr", DEV)
+    eng = SidDecodeEngine(cfg, 3, 16, [20, 33, 17], sizes, base, trie, DEV, shared_prefix=8, seed=1,
+                          level0_from_prefill=True)
+    with pytest.raises(RuntimeError):
+        eng.run(host_io=False, _eager=True)  # no prefill yet
+    eng.prefill()
+    eng.run(host_io=False, _eager=True)
+    lg, mx, ls, _ = eng.head.logits_level(eng.prefill_hidden, 0)
+    otr = O.OracleTrie(arrays.csr_keys, arrays.edge_child, arrays.vsz, base, arrays.invalid_node)
+    ref = O.sid_beam_step(torch.zeros(3, 1), lg.cpu(), torch.zeros((3, 1), dtype=torch.int64), otr, base, 16,
+                          token_ids=torch.zeros((3, 1, 3), dtype=torch.int64), col=0, stats=(mx.cpu(), ls.cpu()))
+    o0 = eng.outs[0]
+    assert torch.equal(o0.vals.cpu(), ref["vals"]) and torch.equal(o0.tokens.cpu(), ref["tokens"])
+    assert (o0.parents == 0).all()  # every level-0 beam descends from the request's single prefill row
+    eager = (eng.cum.clone(), eng.final_tokens.clone(), eng.final_nodes.clone())
+    eng.capture()
+    assert eng.graphs[0] is None and eng.graphs[1] is not None  # level 0 is not a decode step
+    eng.run(host_io=True)
+    assert torch.equal(eng.cum, eager[0]) and torch.equal(eng.final_tokens, eager[1])
+    assert torch.equal(eng.final_nodes, eager[2]) and torch.equal(eng.h_tokens, eager[1].cpu())
+    live = torch.isfinite(eng.cum)
+    assert live.any() and (eng.final_nodes[live] == -1).all()
+    codes = (eng.final_tokens - torch.tensor([base, base + 32, base + 64], device=DEV)).cpu().numpy()
+    legal = {tuple(r) for r in items.tolist()}
+    lv = live.cpu().numpy()
+    assert all(tuple(c) in legal for c in codes[lv])
+    assert device_status() == (0, 0)
+
+
 def test_model_with_residual_adds_in_gemm_epilogues_equals_unfused_flow():
     """Qwen3ForCausalLM(fuse_residual=True, fuse_rope_gemm=True) (o_proj / down_proj GEMMs add into the
     residual stream, norms without add; QK-norm + RoPE + KV write in the qkv GEMM's epilogue) gives the bits
