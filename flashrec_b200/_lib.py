@@ -90,6 +90,8 @@ _SIGNATURES = {
     "fr_embedding_bf16": [P, P, P, _I, _I, _I, P],
     "fr_decode_attn_plan": [P, P, P, _I, _I, P, P],
     "fr_decode_attn_scratch_bytes": [_I, _I, _I],
+    "fr_trie_build_workspace_bytes": [_L],
+    "fr_trie_build_csr": [P, _L, _I, P, P, P, _L, P, P, _L, P],
     "fr_decode_attn_fp8": [P, _L, _L, P, P, _L, _L, _L, _L, P, P, P, P, P, _L, _I, _I, _I, _I, _I, _I, _I, _F, P, _L,
                            _I, P],
     "fr_prefill_attn_fp8": [P, _L, _L, P, P, _L, _L, _L, _L, P, P, P, P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _F, P, _L,
@@ -107,7 +109,8 @@ _SIGNATURES = {
     "fr_sid_beam_step": [P] * 7 + [_L] + [P] * 9 + [_L] * 3 + [_I] * 7 + [P],
     "fr_topk_merge_shards": [P] * 14 + [_L] * 2 + [_I] * 7 + [P],
 }
-_RESTYPES = {"fr_version": c_char_p, "fr_decode_attn_scratch_bytes": c_int64}
+_RESTYPES = {"fr_version": c_char_p, "fr_decode_attn_scratch_bytes": c_int64,
+             "fr_trie_build_workspace_bytes": c_int64}
 
 
 def lib_path() -> Path:

@@ -8,7 +8,9 @@ legal continuation), ``-1`` = unconstrained (a complete SID was reached); token
 of (level l, code c) = ``token_base + sum(sizes[:l]) + c``; CSR key =
 ``node * vsz + (token - token_base)``.
 
-The build itself is host-side numpy (sort / unique), not a Python dict walk.
+Two builders give the same arrays: ``build_trie_arrays`` (host-side numpy sort / unique, any
+layout afterwards) and ``build_trie_device`` (sort / unique / scan on the GPU, CSR layout only,
+for catalogs of tens of millions of items). Neither walks Python dicts.
 """
 
 from __future__ import annotations
@@ -209,3 +211,45 @@ def trie_to_device(arrays: TrieArrays, layout: str, device) -> DeviceTrie:
             },
         )
     raise ValueError(f"unknown trie layout {layout!r}")
+
+
+def build_trie_device(items: torch.Tensor, sizes: Sequence[int], token_base: int) -> DeviceTrie:
+    """CSR trie of the catalog ``items`` (int32 ``[n_items, depth]``, on the GPU) built on the GPU:
+    the device-side stand-in for ``BeamValidPathTrie._ensure_gpu_cache`` / ``_build_csr_cache``
+    (search/trie.py:222-251, 300-327). Same node numbering, keys and children as
+    ``build_trie_arrays`` + ``trie_to_device(.., "csr")``. One host read (the counts) at the end."""
+    import ctypes
+
+    from flashrec_b200._lib import call, load, ptr, require_cuda, stream_ptr
+
+    require_cuda(items)
+    if items.dim() != 2 or items.shape[1] != len(sizes) or items.dtype != torch.int32:
+        raise ValueError("items must be an int32 [n_items, len(sizes)] tensor")
+    items = items.contiguous()
+    dev = items.device
+    n, depth = int(items.shape[0]), len(sizes)
+    sizes = [int(x) for x in sizes]
+    need = int(load().fr_trie_build_workspace_bytes(n))
+    if need < 0:
+        raise ValueError("catalog too large for one build (n_items must be below 2^31)")
+    ws = torch.empty(need, dtype=torch.uint8, device=dev)
+    cap = max(n * depth, 1)
+    keys = torch.empty(cap, dtype=torch.int64, device=dev)
+    child = torch.empty(cap, dtype=torch.int64, device=dev)
+    counts = torch.zeros(3 + 2 * (depth + 1), dtype=torch.int64, device=dev)
+    c_sizes = (ctypes.c_int64 * depth)(*sizes)
+    call("fr_trie_build_csr", ptr(items), n, depth, ctypes.cast(c_sizes, ctypes.c_void_p), ptr(keys), ptr(child), cap,
+         ptr(counts), ptr(ws), need, stream_ptr(dev))
+    c = counts.cpu().numpy()
+    if c[0] < 0:
+        raise ValueError("item code out of range for its level")
+    n_edges = int(c[2])
+    level_start = c[3: 3 + depth + 1].copy()
+    if n == 0:
+        level_start[1:] = 1
+    empty = np.zeros(0, dtype=np.int64)
+    arrays = TrieArrays(sizes=sizes, token_base=int(token_base), vsz=int(sum(sizes)), n_nodes=int(c[1]),
+                        level_start=level_start, edge_parent=empty, edge_rel=empty, edge_child=empty,
+                        n_items=int(c[0]))
+    # trimmed copies so that the build's capacity-sized buffers are released
+    return DeviceTrie(_lib.FR_TRIE_CSR, arrays, dev, {"keys": keys[:n_edges].clone(), "child": child[:n_edges].clone()})

@@ -314,6 +314,23 @@ int fr_logsumexp_rows(const float* logits, int64_t ld, float* row_max, float* ro
 int fr_topk_rows(const float* x, int64_t ld, const float* row_max, const float* row_logsum, float* vals_out,
                  int64_t* idx_out, int rows, int cols, int k, cudaStream_t stream);
 
+/* Catalog trie built on the device, straight into the CSR layout (FR_TRIE_CSR) of `fr_trie`.
+ * items: int32 [n_items, depth] (device), items[i][l] in [0, sizes[l]); sizes: int64 [depth] (HOST).
+ * keys_out / child_out: int64 [edge_capacity] (device; n_items * depth always suffices): edges in
+ * ascending key order, key = node * vsz + (token - token_base) with vsz = sum(sizes), child = node
+ * id or -1 at the last level. counts_out: int64 [3 + 2 * (depth + 1)] (device): [0] distinct items
+ * (-1 if an item code was out of range: the outputs are then invalid), [1] internal nodes
+ * (= invalid_node), [2] edges, [3 + d] first node id of depth d (d = 0..depth), then the first
+ * edge of each depth. Node numbering as the reference: root 0, prefixes by (length, prefix) order.
+ * workspace: fr_trie_build_workspace_bytes(n_items) bytes, 16-byte aligned. depth <= 8,
+ * prod(sizes) < 2^62, n_items < 2^31. No host synchronisation.
+ * Reference: BeamValidPathTrie._ensure_gpu_cache / _build_csr_cache (search/trie.py:222-251,
+ * 300-327), which walk Python dicts. */
+int64_t fr_trie_build_workspace_bytes(int64_t n_items);
+int fr_trie_build_csr(const int32_t* items, int64_t n_items, int depth, const int64_t* sizes, int64_t* keys_out,
+                      int64_t* child_out, int64_t edge_capacity, int64_t* counts_out, void* workspace,
+                      int64_t workspace_bytes, cudaStream_t stream);
+
 /* scores_out = allowed(node_ids[r], cand_tokens[r,c]) ? scores_in : neg_inf.
  * Reference: trie_mask_candidates (kernel/beam_trie.py:82-117) and the CSR
  * branch of BeamValidPathTrie.mask_candidates (search/trie.py:491-500). */
