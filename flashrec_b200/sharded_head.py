@@ -109,3 +109,123 @@ class ShardedSidHead:
                                                lo, level_width)
         return self.ops.merge(self._all_gather(vals), self._all_gather(idx), self._all_gather(child), node_ids,
                               token_ids_in, token_ids_out, node_ids_out, col, level_tok_base, level_width)
+
+
+def _main() -> None:
+    """Self-check and timing of the sharded head on real GPUs, one rank per GPU:
+
+        python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \\
+            --master-port P -m flashrec_b200.sharded_head [--requests 16 --beam 2048 ...]
+
+    A wide-beam catalog search shaped like the largest baseline configuration (4 levels x 4096 codes,
+    Zipf-skewed 10M-item catalog, 2048 beams): every level is decoded through the sharded protocol and,
+    on the same inputs, through the unsharded beam step; all ranks must end in the unsharded result bit
+    for bit. Prints one JSON line (rank 0) with the step times (CUDA events, max over ranks)."""
+    import argparse
+    import json
+    import os
+
+    import numpy as np
+
+    from flashrec_b200.kernel.sglops import fp8_scaled_mm, per_token_quant_fp8
+    from flashrec_b200.layers import quantize_weight_fp8
+    from flashrec_b200.sid_decode import sid_beam_step
+    from flashrec_b200.trie import build_trie_device
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--requests", type=int, default=16)
+    ap.add_argument("--beam", type=int, default=2048)
+    ap.add_argument("--levels", type=int, default=4)
+    ap.add_argument("--width", type=int, default=4096)
+    ap.add_argument("--items", type=int, default=10_000_000)
+    ap.add_argument("--hidden", type=int, default=2048)
+    ap.add_argument("--reps", type=int, default=5)
+    args = ap.parse_args()
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    n, bw, L, kl, base = args.requests, args.beam, args.levels, args.width, 151_936
+    sizes = [kl] * L
+    rng = np.random.default_rng(0)  # the same catalog, weights and hidden states on every rank
+    cols = [np.minimum(rng.zipf(1.1, args.items) - 1, kl - 1) if l < 2 else rng.integers(0, kl, args.items)
+            for l in range(L)]
+    trie = build_trie_device(torch.from_numpy(np.stack(cols, 1).astype(np.int32)).to(dev), sizes, base)
+    g = torch.Generator(device=dev).manual_seed(1)
+    w = torch.randn((L * kl, args.hidden), generator=g, device=dev) * 0.02
+    wq, ws = quantize_weight_fp8(w)
+    del w
+    head = ShardedSidHead()
+    lo, hi = shard_range(kl, rank, world)
+
+    def planes():
+        cum = torch.full((n, bw), float("-inf"), device=dev)
+        cum[:, 0] = 0.0
+        return (cum, torch.zeros((n, bw), dtype=torch.int64, device=dev),
+                torch.zeros((n, bw, L), dtype=torch.int64, device=dev))
+
+    cum_s, node_s, tok_s = planes()
+    cum_u, node_u, tok_u = planes()
+    ok = True
+    t_sharded, t_unsharded = [], []
+    ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+    for lv in range(L):
+        hidden = (torch.randn((n * bw, args.hidden), generator=g, device=dev)).to(torch.bfloat16)
+        a_q, a_s = per_token_quant_fp8(hidden)
+        rows = slice(lv * kl + lo, lv * kl + hi)
+        local = fp8_scaled_mm(a_q, wq[rows].t(), a_s, ws.reshape(-1)[rows], torch.float32)  # this rank's columns
+        full = torch.empty((world, n * bw, hi - lo), dtype=torch.float32, device=dev)
+        dist.all_gather_into_tensor(full.view(-1, hi - lo), local)
+        full = full.permute(1, 0, 2).reshape(n * bw, kl).contiguous()
+        col = torch.full((n,), lv, dtype=torch.int32, device=dev)
+        for rep in range(args.reps + 1):  # the first repetition warms up
+            tok_o, node_o = torch.zeros_like(tok_s), torch.zeros_like(node_s)
+            dist.barrier()
+            e0, e1 = ev(), ev()
+            e0.record()
+            out_s = head.step(cum_s, local, node_s, trie, base + lv * kl, kl, bw, token_ids_in=tok_s,
+                              token_ids_out=tok_o, node_ids_out=node_o, col=col)
+            e1.record()
+            torch.cuda.synchronize()
+            if rep:
+                t_sharded.append(e0.elapsed_time(e1))
+        # unsharded on the same logits
+        ops = head.ops
+        for rep in range(args.reps + 1):
+            tok_r, node_r = torch.zeros_like(tok_u), torch.zeros_like(node_u)
+            e0, e1 = ev(), ev()
+            e0.record()
+            mx, ls = ops.local_stats(full)
+            out_u = sid_beam_step(cum_u, full, mx, ls, node_u, trie, base + lv * kl, bw, token_ids_in=tok_u,
+                                  token_ids_out=tok_r, node_ids_out=node_r, col=col)
+            e1.record()
+            torch.cuda.synchronize()
+            if rep:
+                t_unsharded.append(e0.elapsed_time(e1))
+        ok = ok and torch.equal(out_s.vals, out_u.vals) and torch.equal(out_s.tokens, out_u.tokens)
+        ok = ok and torch.equal(out_s.parents, out_u.parents) and torch.equal(tok_o, tok_r)
+        ok = ok and torch.equal(node_o, node_r)
+        cum_s, node_s, tok_s = out_s.vals.clone(), node_o, tok_o
+        cum_u, node_u, tok_u = out_u.vals.clone(), node_r, tok_r
+    live = torch.isfinite(cum_s)
+    flags = torch.tensor([int(ok), int((node_s[live] == -1).all())], device=dev)
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    t = torch.tensor([sum(t_sharded) / args.reps, sum(t_unsharded) / args.reps], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        print(json.dumps({
+            "check": "sharded SID head == unsharded, all ranks, all levels", "equal": bool(flags[0].item()),
+            "complete_sids_reached": bool(flags[1].item()), "n_gpus": world, "requests": n, "beam_width": bw,
+            "levels": L, "level_width": kl, "catalog_items": int(trie.arrays.n_items), "trie_nodes": trie.n_nodes,
+            "live_beams": int(live.sum().item()),
+            "ms_sharded_head_all_levels": float(t[0].item()), "ms_unsharded_head_all_levels": float(t[1].item()),
+            "note": "head step only (statistics, exchange, beam step, merge); logits GEMM excluded from both"}))
+    dist.barrier()
+    dist.destroy_process_group()
+    if not flags[0].item():
+        raise SystemExit(1)
+
+
+if __name__ == "__main__":
+    _main()

@@ -104,3 +104,77 @@ def test_config3_trie_constrained_head_three_steps(catalog):
         assert (nodes_d[0].cpu().numpy()[live] == -1).all()  # complete SIDs: leaves reached
         results[layout] = (cum_d.cpu(), toks_d.cpu())
     assert torch.equal(results["csr"][0], results["bitmap"][0]) and torch.equal(results["csr"][1], results["bitmap"][1])
+
+
+def test_config5_wide_beam_sharded_head_2048_beams_4x4096():
+    """Config 5 on one GPU: 2048 beams, 4 levels x 4096 codes, a Zipf-skewed catalog (2M items here; the
+    10M build has its own test) built on the device, head sharded by token range over 8 emulated ranks.
+    Every level: the unsharded step against the CPU oracle bit for bit, and statistics + per-shard steps +
+    merge against the unsharded step bit for bit; the final beams are distinct legal items."""
+    from flashrec_b200._lib import call, ptr, stream_ptr
+    from flashrec_b200.sid_decode import BeamStepOut, sid_beam_step
+    from flashrec_b200.trie import build_trie_arrays, build_trie_device
+
+    n, bw, L, kl, S, base, items_n = 2, 2048, 4, 4096, 8, 151_936, 2_000_000
+    sizes = [kl] * L
+    rng = np.random.default_rng(0)
+    cols = [np.minimum(rng.zipf(1.1, items_n) - 1, kl - 1) if l < 2 else rng.integers(0, kl, items_n)
+            for l in range(L)]
+    items = np.stack(cols, 1)
+    trie = build_trie_device(torch.from_numpy(items.astype(np.int32)).to(DEV), sizes, base)
+    host = build_trie_arrays(items, sizes, base)
+    otr = O.OracleTrie(host.csr_keys, host.edge_child, host.vsz, base, host.invalid_node)
+    assert np.array_equal(trie.tensors["keys"].cpu().numpy(), host.csr_keys)
+
+    cum = torch.full((n, bw), float("-inf"), device=DEV)
+    cum[:, 0] = 0.0
+    nodes = torch.zeros((n, bw), dtype=torch.int64, device=DEV)
+    toks = torch.zeros((n, bw, L), dtype=torch.int64, device=DEV)
+    w = kl // S
+    for lv in range(L):
+        g = torch.Generator().manual_seed(50 + lv)
+        logits = (3.0 * torch.randn(n * bw, kl, generator=g)).to(DEV)
+        mx, ls = torch.empty(n * bw, device=DEV), torch.empty(n * bw, device=DEV)
+        call("fr_logsumexp_rows", ptr(logits), logits.stride(0), ptr(mx), ptr(ls), None, 0, n * bw, kl, stream_ptr(DEV))
+        col = torch.full((n,), lv, dtype=torch.int32, device=DEV)
+        tok_ref, node_ref = torch.zeros_like(toks), torch.zeros_like(nodes)
+        full = sid_beam_step(cum, logits, mx, ls, nodes, trie, base + lv * kl, bw, token_ids_in=toks,
+                             token_ids_out=tok_ref, node_ids_out=node_ref, col=col)
+        ref = O.sid_beam_step(cum.cpu(), logits.cpu(), nodes.cpu(), otr, base + lv * kl, bw, token_ids=toks.cpu(),
+                              col=lv, stats=(mx.cpu(), ls.cpu()))
+        assert torch.equal(full.vals.cpu(), ref["vals"]) and torch.equal(full.tokens.cpu(), ref["tokens"]), lv
+        assert torch.equal(full.parents.cpu(), ref["parents"]) and torch.equal(tok_ref.cpu(), ref["token_ids"]), lv
+        assert torch.equal(node_ref.cpu(), ref["node_ids"]), lv
+        # the same step through 8 token-range shards
+        smx, sls = torch.empty((S, n * bw), device=DEV), torch.empty((S, n * bw), device=DEV)
+        for s in range(S):
+            part = logits[:, s * w:(s + 1) * w]
+            call("fr_logsumexp_rows", ptr(part), part.stride(0), ptr(smx[s]), ptr(sls[s]), None, 0, n * bw, w,
+                 stream_ptr(DEV))
+        gmx, gls = torch.empty_like(mx), torch.empty_like(ls)
+        call("fr_lse_combine_shards", ptr(smx), ptr(sls), ptr(gmx), ptr(gls), S, n * bw, stream_ptr(DEV))
+        vals = torch.empty((S, n, bw), device=DEV)
+        idx = torch.empty((S, n, bw), dtype=torch.int64, device=DEV)
+        child = torch.empty((S, n, bw), dtype=torch.int64, device=DEV)
+        for s in range(S):
+            o = sid_beam_step(cum, logits[:, s * w:(s + 1) * w], mx, ls, nodes, trie, base + lv * kl, bw,
+                              idx_base=s * w, idx_width=kl)
+            vals[s], idx[s], child[s] = o.vals, o.indices, o.child
+        m = BeamStepOut(*(torch.empty((n, bw), dtype=dt, device=DEV)
+                          for dt in (torch.float32, torch.int64, torch.int64, torch.int64, torch.int64)))
+        tok_out, node_out = torch.zeros_like(toks), torch.zeros_like(nodes)
+        call("fr_topk_merge_shards", ptr(m.vals), ptr(m.parents), ptr(m.tokens), ptr(m.indices), ptr(m.child),
+             ptr(vals), ptr(idx), ptr(child), ptr(nodes), ptr(toks), ptr(tok_out), ptr(node_out), None, ptr(col),
+             base + lv * kl, kl, S, n, bw, bw, L, 1, 1, stream_ptr(DEV))
+        for a, b in ((m.vals, full.vals), (m.parents, full.parents), (m.tokens, full.tokens),
+                     (m.indices, full.indices), (m.child, full.child), (tok_out, tok_ref), (node_out, node_ref)):
+            assert torch.equal(a, b), lv
+        cum, nodes, toks = full.vals.clone(), node_ref, tok_ref
+    live = torch.isfinite(cum).cpu().numpy()
+    assert live.all()
+    codes = (toks.cpu() - torch.tensor([base + l * kl for l in range(L)])).numpy()
+    legal = {tuple(r) for r in np.unique(items, axis=0).tolist()}
+    for r in range(n):
+        rows = [tuple(c) for c in codes[r]]
+        assert all(x in legal for x in rows) and len(set(rows)) == len(rows)
+    assert (nodes == -1).all()
