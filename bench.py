@@ -62,6 +62,9 @@ def parse():
                     help="leave the prompt K/V as the synthetic fill instead of running the prefill pass")
     ap.add_argument("--no-fuse-rope-gemm", action="store_true",
                     help="run QK-norm + RoPE + KV write as their own kernel instead of in the qkv GEMM's epilogue")
+    ap.add_argument("--attn-compare", action="store_true",
+                    help="time one layer's decode attention on the bench's slot lists beside FlashInfer's paged "
+                         "decode kernel (a library comparison) and exit")
     ap.add_argument("--profile-prefill", action="store_true",
                     help="run one prefill pass between cudaProfilerStart/Stop and exit (for ncu --profile-from-start off)")
     ap.add_argument("--profile-wave", action="store_true",
@@ -377,10 +380,93 @@ def profile_kernels(rows: int):
     print(json.dumps({"profiled": "kernels", "rows": rows}))
 
 
+def attn_compare(requests: int, beam: int, iters: int = 10):
+    """The decode attention of one layer on the bench's slot lists (requests x beam rows, prompts
+    U[128,1024] shared by a request's beams, one own slot per row), timed between L2 flushes: this
+    library's shared-prefix tcgen05 path (widening pass + attention kernel) beside FlashInfer's paged
+    decode kernel called the way the reference calls it (page_size 1, e4m3 KV, bf16 Q; library code, a
+    comparison only). Prints one JSON line."""
+    import numpy as np
+    import torch
+
+    from flashrec_b200.attention import AttentionBackend, TokenToKVPool
+    from flashrec_b200.decoder import ForwardBatch
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    hq, hkv, d = 16, 8, 128
+    plens = prompt_lengths(requests, 0)
+    rows = requests * beam
+    slots = 16 + sum(plens) + rows
+    pool = TokenToKVPool(1, slots, hkv, d, torch.float8_e4m3fn, dev)
+    g = torch.Generator(device=dev).manual_seed(0)
+    for c in (pool.k[0], pool.v[0]):
+        c.copy_(torch.randn(c.shape, generator=g, device=dev).to(torch.bfloat16).to(torch.float8_e4m3fn))
+    lists, cursor = [], 16
+    for r, p in enumerate(plens):
+        prefix = np.arange(cursor, cursor + p, dtype=np.int32)
+        cursor += p
+        own = np.arange(cursor, cursor + beam, dtype=np.int32)
+        cursor += beam
+        lists.append(np.concatenate([np.tile(prefix, (beam, 1)), own[:, None]], axis=1).reshape(-1))
+    lens = np.repeat(np.asarray(plens) + 1, beam)
+    indptr = torch.from_numpy(np.concatenate(([0], np.cumsum(lens))).astype(np.int32)).to(dev)
+    indices = torch.from_numpy(np.concatenate(lists)).to(dev)
+    q = torch.randn((rows, hq, d), generator=g, device=dev).to(torch.bfloat16)
+    be = AttentionBackend(pool, hq, hkv, d, max_shared_len=max(plens) + 1)
+    be.set_groups(torch.arange(requests + 1, dtype=torch.int32, device=dev) * beam, beam)
+    batch = ForwardBatch(input_ids=None, req_pool_indices=None, seq_lens=torch.from_numpy(lens.astype(np.int32)).to(dev),
+                         positions=None, out_cache_loc=None, kv_indices=indices, kv_indptr=indptr)
+    be.prepare(batch)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(fn):
+        for _ in range(3):
+            out = fn()
+        torch.cuda.synchronize()
+        ms = []
+        for _ in range(iters):
+            flush.zero_()
+            e0.record()
+            out = fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms.append(e0.elapsed_time(e1))
+        return out, statistics.median(ms) * 1e3
+
+    mine, us_mine = timed(lambda: be.forward(q, None, None, 0, batch, skip_store=True))
+    res = {"attn_compare": True, "rows": rows, "requests": requests, "beam_width": beam,
+           "keys_per_row_mean": float(lens.mean()), "this_library_us": us_mine,
+           "this_library": "shared_kv_prepare_kernel + decode_attn_tc_kernel (tcgen05, shared prefix once per request)"}
+    try:
+        from flashinfer import BatchDecodeWithPagedKVCacheWrapper
+
+        ws = torch.zeros(128 << 20, dtype=torch.uint8, device=dev)
+        kv = (pool.k[0].unsqueeze(1), pool.v[0].unsqueeze(1))
+        last = torch.ones(rows, dtype=torch.int32, device=dev)
+        for tc in (True, False):
+            w = BatchDecodeWithPagedKVCacheWrapper(ws, kv_layout="NHD", use_tensor_cores=tc)
+            w.plan(indptr, indices, last, hq, hkv, d, 1, pos_encoding_mode="NONE", q_data_type=torch.bfloat16,
+                   kv_data_type=torch.float8_e4m3fn)
+            ref, us = timed(lambda: w.run(q, kv))
+            key = "flashinfer_tensor_cores_us" if tc else "flashinfer_cuda_cores_us"
+            res[key] = us
+            res[key.replace("_us", "_max_abs_diff")] = float((ref.float() - mine.float()).abs().max().item())
+    except Exception as exc:  # the library may be unable to build or load its kernel here
+        res["flashinfer_unavailable"] = repr(exc)[:300]
+    print(json.dumps(res))
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.attn_compare:
+        import torch
+
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        attn_compare(args.requests, args.beam)
         return
     if args.gemm_shapes:
         import torch
