@@ -541,10 +541,13 @@ def main():
     # count this library's kernel launches in one eager wave
     counter = {"n": 0}
     orig_call = _lib.call
-    two_kernels = {"fr_gather_kv_indices"}
+    # entries that launch more than one kernel per call (scan + gather + write-back; widening + attention;
+    # plan initialisation + plan); every other entry launches one
+    kernels_per_call = {"fr_gather_kv_indices": 2, "fr_kv_table_step": 3, "fr_decode_attn_fp8": 2,
+                        "fr_decode_attn_reuse_fp8": 2, "fr_decode_attn_plan": 2}
 
     def counting_call(name, *a):
-        counter["n"] += 2 if name in two_kernels else 1
+        counter["n"] += kernels_per_call.get(name, 1)
         return orig_call(name, *a)
 
     import flashrec_b200.attention as m_att
