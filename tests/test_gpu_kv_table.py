@@ -121,3 +121,23 @@ def test_type_errors():
         kv_table_step(table, rows, sl, out, indptr, parents_rel=rows)
     with pytest.raises(ValueError):
         copy_prefill_to_beams_many(table, rows[:1], rows.view(1, 4), 9)
+
+
+def test_rows_outside_the_table_and_overlong_lengths_are_skipped_or_clamped():
+    from flashrec_b200.attention import kv_table_step
+
+    table = torch.arange(40, dtype=torch.int32).view(4, 10).to(DEV)
+    before = table.clone()
+    rows = torch.tensor([1, 99, -3, 2], device=DEV)          # two rows that do not exist
+    sl = torch.tensor([4, 3, 2, 25], dtype=torch.int32, device=DEV)  # the last one longer than the table is wide
+    out = torch.full((34,), -7, dtype=torch.int32, device=DEV)
+    indptr = torch.empty(5, dtype=torch.int32, device=DEV)
+    new_slot = torch.tensor([500, 501, 502, 503], device=DEV)
+    kv_table_step(table, rows, sl, out, indptr, new_slot=new_slot)
+    assert indptr.tolist() == [0, 4, 7, 9, 34]
+    t = table.cpu()
+    assert t[1, 3].item() == 500 and t[2, 9].item() == 503  # clamped to the last column of the table
+    t[1, 3], t[2, 9] = before[1, 3], before[2, 9]
+    assert torch.equal(t, before.cpu())                      # nothing else was touched
+    o = out.cpu()
+    assert o[:4].tolist() == [10, 11, 12, 500] and o[9:19].tolist() == list(range(20, 29)) + [503]

@@ -173,3 +173,21 @@ def test_extend_over_cached_prefix_equals_full_prefill():
     alone = run([(ids[1], 0, torch.arange(500, 500 + len(ids[1])))])
     d = (both[1].float() - alone[0].float()).abs()
     assert d.max() / alone.float().abs().max() < 1e-1 and d.mean() / alone.float().abs().mean() < 2e-2
+
+
+def test_prefill_attention_empty_request_and_unaligned_lengths():
+    """A request without extend tokens in the batch contributes nothing and disturbs nobody; key counts that
+    are not multiples of the 64-token tile and a query count that is not a multiple of the 64-row tile."""
+    hq, hkv = 16, 8
+    ext, pre = [5, 0, 67, 1], [59, 10, 62, 0]
+    rng = np.random.default_rng(1)
+    seq = [e + p for e, p in zip(ext, pre)]
+    slots = sum(seq) + 8
+    kc = torch.from_numpy(rng.standard_normal((slots, hkv, 128)).astype(np.float32)).bfloat16().to(FP8)
+    vc = torch.from_numpy(rng.standard_normal((slots, hkv, 128)).astype(np.float32)).bfloat16().to(FP8)
+    kvi = torch.from_numpy((rng.permutation(slots - 1)[: sum(seq)] + 1).astype(np.int32))
+    q = torch.from_numpy(rng.standard_normal((sum(ext), hq, 128)).astype(np.float32)).bfloat16()
+    out, qo, kv = _run_prefill(q, kc, vc, ext, pre, kvi, hq, hkv)
+    ref = O.prefill_attention(q, kc, vc, qo, kv, kvi, hq // hkv).float()
+    assert (out.float().cpu() - ref).abs().max() / ref.abs().max() < 2e-2
+    assert torch.isfinite(out.float()).all()
