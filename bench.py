@@ -498,20 +498,17 @@ def main():
     from flashrec_b200 import _lib, device_status
     from flashrec_b200.decoder import Qwen3Config
     from flashrec_b200.sid_decode import SidDecodeEngine
-    from flashrec_b200.trie import build_trie_arrays, build_trie_device, trie_to_device
+    from flashrec_b200.trie import build_trie_device
 
     _lib.load()  # fails loudly if the CUDA library is missing
     sizes = [8192] * 3
     token_base = 151_936
     cfg = Qwen3Config(num_hidden_layers=args.layers)
     catalog = make_catalog(args.items, sizes)
-    if args.trie == "csr":  # sort-based build on the GPU, straight into the CSR layout
-        trie = build_trie_device(torch.from_numpy(np.ascontiguousarray(catalog, dtype=np.int32)).to(dev), sizes,
-                                 token_base)
-        arrays = trie.arrays
-    else:
-        arrays = build_trie_arrays(catalog, sizes, token_base)
-        trie = trie_to_device(arrays, args.trie, dev)
+    # sort-based build on the GPU, straight into the layout the beam step reads
+    trie = build_trie_device(torch.from_numpy(np.ascontiguousarray(catalog, dtype=np.int32)).to(dev), sizes,
+                             token_base, layout=args.trie)
+    arrays = trie.arrays
     eng = SidDecodeEngine(cfg, args.requests, args.beam, prompt_lengths(args.requests, rank), sizes, token_base, trie,
                           dev, shared_prefix=64, page_size=16, seed=rank, fuse_rope_gemm=not args.no_fuse_rope_gemm,
                           level0_from_prefill=args.level0_from_prefill)

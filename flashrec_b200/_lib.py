@@ -92,6 +92,7 @@ _SIGNATURES = {
     "fr_decode_attn_scratch_bytes": [_I, _I, _I],
     "fr_trie_build_workspace_bytes": [_L],
     "fr_trie_build_csr": [P, _L, _I, P, P, P, _L, P, P, _L, P],
+    "fr_trie_csr_to_bitmap": [P, P, _L, _I, P, P, P, P, P, _I, P],
     "fr_decode_attn_fp8": [P, _L, _L, P, P, _L, _L, _L, _L, P, P, P, P, P, _L, _I, _I, _I, _I, _I, _I, _I, _F, P, _L,
                            _I, P],
     "fr_prefill_attn_fp8": [P, _L, _L, P, P, _L, _L, _L, _L, P, P, P, P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _F, P, _L,

@@ -251,6 +251,23 @@ __device__ __forceinline__ void for_each_candidate(const StepParams& p, int n, b
           if (s != p.neg_inf)
             f(compose(s, static_cast<uint32_t>(static_cast<int64_t>(b) * p.idx_width + p.idx_base + c)));
         }
+      } else if (tr.kind == FR_TRIE_BITMAP && node >= 0 && node < tr.n_rows) {
+        // only the set bits of the node's row can be legal: walk them word by word (a node deep in
+        // the trie has a handful of children among thousands of codes)
+        const int64_t delta = level_off - __ldg(tr.level_off + node);  // bit index of this shard's code 0
+        const uint32_t* bm = tr.bitmap + node * tr.words;
+        for (int w = lane; w < tr.words; w += 32) {
+          uint32_t bits = __ldg(bm + w);
+          while (bits) {
+            const int t = __ffs(bits) - 1;
+            bits &= bits - 1;
+            const int64_t c = static_cast<int64_t>(w) * 32 + t - delta;
+            if (c < 0 || c >= p.C) continue;
+            const float s = __fadd_rn(cumb, __fsub_rn(__fsub_rn(lg[c], mx), ls));
+            if (s != p.neg_inf)
+              f(compose(s, static_cast<uint32_t>(static_cast<int64_t>(b) * p.idx_width + p.idx_base + c)));
+          }
+        }
       } else {
         for (int c = lane; c < p.C; c += 32) {
           if (!trie_allowed(tr, node, first_tok + c)) continue;

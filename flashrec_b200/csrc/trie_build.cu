@@ -101,6 +101,43 @@ __global__ void __launch_bounds__(256) edge_kernel(const int64_t* __restrict__ k
   }
 }
 
+// Bitmap layout from the CSR arrays: one bit per (node, code of the node's own level), the id of the
+// node's first child (children are numbered consecutively in code order) and the token offset of the
+// node's level. One thread per edge / per node.
+struct BitmapArgs {
+  const int64_t* keys;
+  const int64_t* child;
+  int64_t n_edges, n_rows, vsz;
+  int depth, words;
+  int64_t node_start[kMaxDepth + 1];
+  int64_t off[kMaxDepth + 1];
+  uint32_t* bitmap;
+  int64_t* child_base;
+  int32_t* level_off;
+};
+
+__global__ void __launch_bounds__(256) bitmap_nodes_kernel(BitmapArgs a) {
+  const int64_t node = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (node >= a.n_rows) return;
+  int d = 0;
+  while (d + 1 < a.depth && node >= a.node_start[d + 1]) ++d;
+  if (node >= a.node_start[a.depth]) d = 0;  // the row of the invalid node
+  a.level_off[node] = static_cast<int32_t>(a.off[d]);
+  a.child_base[node] = -1;
+}
+
+__global__ void __launch_bounds__(256) bitmap_edges_kernel(BitmapArgs a) {
+  const int64_t e = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (e >= a.n_edges) return;
+  const int64_t key = a.keys[e];
+  const int64_t parent = key / a.vsz, rel = key - parent * a.vsz;
+  if (parent < 0 || parent >= a.n_rows) return;
+  const int64_t code = rel - a.level_off[parent];
+  if (code >= 0 && (code >> 5) < a.words)
+    atomicOr(a.bitmap + parent * a.words + (code >> 5), 1u << (code & 31));
+  if (e == 0 || a.keys[e - 1] / a.vsz != parent) a.child_base[parent] = a.child[e];
+}
+
 __global__ void mark_bad_kernel(const int* __restrict__ bad, int64_t* __restrict__ counts) {
   if (*bad) counts[0] = -1;
 }
@@ -224,5 +261,35 @@ extern "C" int fr_trie_build_csr(const int32_t* items, int64_t n_items, int dept
   // an item code outside its level makes the whole build invalid: reported through the counts
   // (counts[0] = -1) rather than by reading a flag back here
   mark_bad_kernel<<<1, 1, 0, stream>>>(bad, counts_out);
+  return launch_status();
+}
+
+extern "C" int fr_trie_csr_to_bitmap(const int64_t* keys, const int64_t* child, int64_t n_edges, int depth,
+                                     const int64_t* sizes, const int64_t* node_start, uint32_t* bitmap_out,
+                                     int64_t* child_base_out, int32_t* level_off_out, int words,
+                                     cudaStream_t stream) {
+  FR_CHECK_ARG(n_edges >= 0 && depth >= 1 && sizes && node_start && bitmap_out && child_base_out && level_off_out);
+  FR_CHECK_SUPPORTED(depth <= kMaxDepth);
+  FR_CHECK_ARG(n_edges == 0 || (keys && child));
+  BitmapArgs a{};
+  a.keys = keys; a.child = child; a.n_edges = n_edges; a.depth = depth; a.words = words;
+  a.bitmap = bitmap_out; a.child_base = child_base_out; a.level_off = level_off_out;
+  a.off[0] = 0;
+  int64_t widest = 0;
+  for (int l = 0; l < depth; ++l) {
+    FR_CHECK_ARG(sizes[l] > 0);
+    a.off[l + 1] = a.off[l] + sizes[l];
+    widest = sizes[l] > widest ? sizes[l] : widest;
+  }
+  for (int d = 0; d <= depth; ++d) a.node_start[d] = node_start[d];
+  a.vsz = a.off[depth];
+  a.n_rows = node_start[depth] + 1;  // internal nodes + the invalid node's empty row
+  FR_CHECK_ARG(words > 0 && static_cast<int64_t>(words) * 32 >= widest && a.n_rows > 0);
+  if (cudaMemsetAsync(bitmap_out, 0, static_cast<size_t>(a.n_rows) * words * sizeof(uint32_t), stream) != cudaSuccess)
+    return FR_ERR_CUDA;
+  bitmap_nodes_kernel<<<ceil_div(a.n_rows, 256), 256, 0, stream>>>(a);
+  if (launch_status() != FR_OK) return FR_ERR_CUDA;
+  if (n_edges == 0) return FR_OK;
+  bitmap_edges_kernel<<<ceil_div(n_edges, 256), 256, 0, stream>>>(a);
   return launch_status();
 }

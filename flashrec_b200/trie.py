@@ -213,8 +213,9 @@ def trie_to_device(arrays: TrieArrays, layout: str, device) -> DeviceTrie:
     raise ValueError(f"unknown trie layout {layout!r}")
 
 
-def build_trie_device(items: torch.Tensor, sizes: Sequence[int], token_base: int) -> DeviceTrie:
-    """CSR trie of the catalog ``items`` (int32 ``[n_items, depth]``, on the GPU) built on the GPU:
+def build_trie_device(items: torch.Tensor, sizes: Sequence[int], token_base: int, layout: str = "csr") -> DeviceTrie:
+    """Trie of the catalog ``items`` (int32 ``[n_items, depth]``, on the GPU) built on the GPU, in the
+    ``"csr"`` or the ``"bitmap"`` layout (the latter derived from the CSR arrays on the device):
     the device-side stand-in for ``BeamValidPathTrie._ensure_gpu_cache`` / ``_build_csr_cache``
     (search/trie.py:222-251, 300-327). Same node numbering, keys and children as
     ``build_trie_arrays`` + ``trie_to_device(.., "csr")``. One host read (the counts) at the end."""
@@ -251,5 +252,18 @@ def build_trie_device(items: torch.Tensor, sizes: Sequence[int], token_base: int
     arrays = TrieArrays(sizes=sizes, token_base=int(token_base), vsz=int(sum(sizes)), n_nodes=int(c[1]),
                         level_start=level_start, edge_parent=empty, edge_rel=empty, edge_child=empty,
                         n_items=int(c[0]))
+    if layout == "bitmap":
+        rows, words = arrays.n_nodes + 1, (max(sizes) + 31) // 32
+        bitmap = torch.empty((rows, words), dtype=torch.int32, device=dev)
+        child_base = torch.empty(rows, dtype=torch.int64, device=dev)
+        level_off = torch.empty(rows, dtype=torch.int32, device=dev)
+        c_start = (ctypes.c_int64 * (depth + 1))(*[int(x) for x in level_start])
+        call("fr_trie_csr_to_bitmap", ptr(keys), ptr(child), n_edges, depth, ctypes.cast(c_sizes, ctypes.c_void_p),
+             ctypes.cast(c_start, ctypes.c_void_p), ptr(bitmap), ptr(child_base), ptr(level_off), words,
+             stream_ptr(dev))
+        return DeviceTrie(_lib.FR_TRIE_BITMAP, arrays, dev,
+                          {"bitmap": bitmap, "child_base": child_base, "level_off": level_off})
+    if layout != "csr":
+        raise ValueError(f"unknown device-built trie layout {layout!r}")
     # trimmed copies so that the build's capacity-sized buffers are released
     return DeviceTrie(_lib.FR_TRIE_CSR, arrays, dev, {"keys": keys[:n_edges].clone(), "child": child[:n_edges].clone()})

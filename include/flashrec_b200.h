@@ -331,6 +331,16 @@ int fr_trie_build_csr(const int32_t* items, int64_t n_items, int depth, const in
                       int64_t* child_out, int64_t edge_capacity, int64_t* counts_out, void* workspace,
                       int64_t workspace_bytes, cudaStream_t stream);
 
+/* The bitmap layout (FR_TRIE_BITMAP) from the CSR arrays of fr_trie_build_csr: bitmap_out u32
+ * [n_nodes + 1, words] (bit c of row n = code c of node n's own level is a legal continuation),
+ * child_base_out int64 [n_nodes + 1] (id of the node's first child, children being consecutive in
+ * code order; -1 at the last level and for childless rows), level_off_out int32 [n_nodes + 1]
+ * (token offset of the node's level). sizes, node_start (= counts_out[3 ..] read back): HOST arrays
+ * of depth and depth + 1 entries; words * 32 >= max(sizes). */
+int fr_trie_csr_to_bitmap(const int64_t* keys, const int64_t* child, int64_t n_edges, int depth,
+                          const int64_t* sizes, const int64_t* node_start, uint32_t* bitmap_out,
+                          int64_t* child_base_out, int32_t* level_off_out, int words, cudaStream_t stream);
+
 /* scores_out = allowed(node_ids[r], cand_tokens[r,c]) ? scores_in : neg_inf.
  * Reference: trie_mask_candidates (kernel/beam_trie.py:82-117) and the CSR
  * branch of BeamValidPathTrie.mask_candidates (search/trie.py:491-500). */

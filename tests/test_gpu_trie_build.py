@@ -111,3 +111,16 @@ def test_device_builder_at_baseline_sizes(name, n, sizes, zipf):
         node = child[pos]
         assert bool((node >= 0).all()) if l + 1 < L else bool((node == -1).all())
     assert int(t.arrays.level_start[-1]) == t.n_nodes
+
+
+@pytest.mark.parametrize("n,sizes", [(50_000, [256, 256, 256]), (3000, [7, 300]), (0, [8, 8]), (200_000, [8192, 8192, 8192])])
+def test_device_bitmap_layout_equals_host_built_one(n, sizes):
+    from flashrec_b200.trie import build_trie_device, trie_to_device
+
+    rng = np.random.default_rng(n + 7)
+    items = np.stack([rng.integers(0, s, n) for s in sizes], 1).astype(np.int32).reshape(n, len(sizes))
+    host = trie_to_device(build_trie_arrays(items, sizes, 1000), "bitmap", DEV)
+    dev = build_trie_device(torch.from_numpy(items).to(DEV), sizes, 1000, layout="bitmap")
+    assert dev.n_nodes == host.n_nodes and dev.kind == host.kind
+    for name in ("bitmap", "child_base", "level_off"):
+        assert torch.equal(dev.tensors[name], host.tensors[name]), name
