@@ -191,7 +191,11 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   const uint32_t bar_vempty = bar0 + 56;    // [2]
   const uint32_t bar_sfull = bar0 + 72;     // [2] S tile complete in TMEM buffer (tile & 1)
   const uint32_t bar_pfull = bar0 + 88;     // P tile written into TMEM (128 arrivals)
-  const uint32_t bar_ofull = bar0 + 96;     // P.V accumulated
+  const uint32_t bar_ofull = bar0 + 96;     // P.V accumulated (one phase per tile; waited for by the rare O rescale)
+  // Last P.V accumulated. Its own one-phase barrier: the softmax of the last tile can finish while the
+  // P.V before the last is still pending (S of tile j + 1 is issued before P.V of tile j), and a parity
+  // wait on bar_ofull two phases ahead of the barrier would pass at once.
+  const uint32_t bar_done = bar0 + 112;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -225,6 +229,7 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     ptx::mbar_init(bar_sfull + 8, 1);
     ptx::mbar_init(bar_pfull, 128);
     ptx::mbar_init(bar_ofull, 1);
+    ptx::mbar_init(bar_done, 1);
     *abort_flag = 0;
     ptx::mbar_init_fence();
     ptx::prefetch_tmap(&tmap_q);
@@ -320,6 +325,7 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         }
         ptx::tc_commit(bar_vempty + 8 * (j & 1));
         ptx::tc_commit(bar_ofull);
+        if (j + 1 == n_tiles) ptx::tc_commit(bar_done);
       }
     }
     __syncwarp();
@@ -410,7 +416,7 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     }
     if (ok && n_tiles > 0) {
       int okw = 0;
-      if (lane == 0) okw = ptx::mbar_wait(bar_ofull, (n_tiles - 1) & 1, abort_flag, status, 19) ? 1 : 0;
+      if (lane == 0) okw = ptx::mbar_wait(bar_done, 0, abort_flag, status, 19) ? 1 : 0;
       okw = __shfl_sync(0xffffffffu, okw, 0);
       ok = okw != 0;
       ptx::tc_fence_after();

@@ -167,6 +167,23 @@ def test_decode_attention_no_sharing_and_empty_rows(tc):
     assert out3[0].abs().max() == 0
 
 
+@pytest.mark.parametrize("hq,hkv", [(16, 8), (8, 8), (8, 2)])
+@pytest.mark.parametrize("pre,tails", [([0, 0], [3, 8]), ([64, 130], [8, 2]), ([1, 63], [1, 5])])
+def test_decode_attention_private_slots_after_short_or_no_prefix(hq, hkv, pre, tails):
+    """tcgen05 path with 1..8 private slots per row, with and without a shared prefix in front of them
+    (no prefix: the rows' private slots are all they see), beam counts that do not fill a CTA tile, and a
+    group of one row."""
+    q, kc, vc, indptr, indices, gr = _attn_case(2, [150, 1], pre, tails, hq, hkv, seed=hq + hkv + sum(tails))
+    # (the one-row group shares its whole list with itself: its private slots count as prefix)
+    out = _run_attn(q, kc, vc, indptr, indices, gr, hq, hkv, tc=True)
+    ref = O.decode_attention(q, kc, vc, indptr, indices, hq // hkv).float()
+    err = (out.float().cpu() - ref).abs().max() / ref.abs().max()
+    assert err < 2e-2, err
+    assert torch.isfinite(out.float()).all()
+    if pre == [0, 0]:  # nothing but private slots in the 150-row group: tight against the oracle
+        assert torch.allclose(out.float().cpu()[:150], ref[:150], rtol=1e-2, atol=1e-2)
+
+
 @pytest.mark.parametrize("tc", [False, True])
 def test_decode_attention_golden_reference(tc):
     g = load_golden("attention")
