@@ -9,11 +9,12 @@ Each function names the reference code it follows (paths inside the
 reference's ``python/flashrec`` tree). Pinning: ``tests/golden/*.npz`` holds
 inputs and outputs produced by importing the reference itself
 (``tests/golden/make_golden.py``); ``tests/test_oracle_golden.py`` checks this
-module against them. Two pieces have no runnable reference on a CPU and are
-therefore "parity unpinned" beyond their building blocks: the fused
-QK-norm+RoPE arithmetic (the reference's implementation is a Triton kernel and
-its torch fallback multiplies 64-wide cos/sin into 128-wide heads, which
-raises) and the FP8 lm_head (the reference's head is bf16).
+module against them. The fused QK-norm+RoPE arithmetic has no torch path in the
+reference (its fallback multiplies 64-wide cos/sin into 128-wide heads, which raises);
+it is pinned by the reference's Triton kernel run under Triton's CPU interpreter,
+whose Q output equals this module's float32 result truncated to bfloat16, bit for
+bit (``rope_triton_interp.npz``). One piece stays "parity unpinned" beyond its
+building blocks: the FP8 lm_head (the reference's head is bf16).
 
 Deliberate, documented deviations from the literal torch path:
   * sums of squares are accumulated in float64 and rounded once to float32

@@ -2,9 +2,10 @@
 
 Usage (only where the reference checkout is available):
 
-    python tests/golden/make_golden.py <reference>/python [--only kv_table | --only prefill_attention]
+    python tests/golden/make_golden.py <reference>/python [--only kv_table | prefill_attention | rope_triton_interp]
 
-(``--only NAME`` writes just ``NAME.npz``, leaving the other files as they are.)
+(``--only NAME`` writes just ``NAME.npz``, leaving the other files as they are; ``rope_triton_interp`` is only
+written that way, in a process of its own.)
 
 Every fixture holds seeded inputs and the outputs of the reference's own torch
 CPU code path (its ``sgl_kernel`` branch is absent, so each wrapper takes its
@@ -99,6 +100,40 @@ def prefill_attention_fixture() -> None:
     np.savez_compressed(HERE / "prefill_attention.npz", ext=np.array(ext), pre=np.array(pre), kv_indices=kvi.numpy(),
                         q=bits16(q), k_cache=bits8(pool.k[0]), v_cache=bits8(pool.v[0]), out=bits16(o))
     print("wrote prefill_attention.npz")
+
+
+def rope_triton_interp_fixture() -> None:
+    """The reference's fused QK-norm + RoPE + KV-store Triton kernel (kernel/qk_rope_kv.py:28-155) run on
+    CPU tensors by Triton's interpreter (TRITON_INTERPRET=1, which must be set before triton is imported:
+    run this in a process of its own, ``--only rope_triton_interp``). The interpreter evaluates the
+    kernel's float32 arithmetic faithfully but its narrowing casts are not the hardware's (float32 ->
+    bfloat16 truncates, float32 -> e4m3 mis-rounds across exponent boundaries), so the fixture keeps the
+    in-place Q output, whose bits are the TRUNCATED float32 results, and drops the cache bytes."""
+    os.environ["TRITON_INTERPRET"] = "1"
+    import flashrec.kernel.qk_rope_kv as qk
+    from flashrec.layers.rotary import RotaryEmbedding
+
+    kernel = qk._try_triton()
+    assert type(kernel).__name__ == "InterpretedFunction", "triton was imported before TRITON_INTERPRET was set"
+    g = torch.Generator().manual_seed(21)
+    t, n_q, n_kv, d = 6, 4, 2, 128
+    qkv = torch.randn(t, n_q + 2 * n_kv, d, generator=g).bfloat16()  # strided views of one buffer, as the model has
+    q, k, v = qkv[:, :n_q], qkv[:, n_q:n_q + n_kv], qkv[:, n_q + n_kv:]
+    qw = (1 + 0.1 * torch.randn(d, generator=g)).bfloat16()
+    kw = (1 + 0.1 * torch.randn(d, generator=g)).bfloat16()
+    pos = torch.tensor([0, 1, 17, 100, 255, 4095])
+    loc = torch.tensor([4, 1, 7, 2, 9, 3])
+    rot = RotaryEmbedding(d, 4096, 1_000_000.0)
+    cs = rot.cos_sin_cache.float().contiguous()
+    kc = torch.zeros(12, n_kv, d, dtype=torch.uint8).view(torch.float8_e4m3fn)
+    vc = torch.zeros(12, n_kv, d, dtype=torch.uint8).view(torch.float8_e4m3fn)
+    q_in = q.clone()
+    kernel[(t,)](q, k, v, qw, kw, pos, loc, cs, kc, vc, q.stride(0), q.stride(1), k.stride(0), k.stride(1),
+                 v.stride(0), v.stride(1), kc.stride(0), kc.stride(1), vc.stride(0), vc.stride(1), n_q, n_kv, d, 1e-6,
+                 BLOCK=128, HALF=64, num_warps=4)
+    np.savez_compressed(HERE / "rope_triton_interp.npz", q=bits16(q_in), k=bits16(k.contiguous()), qw=bits16(qw),
+                        kw=bits16(kw), pos=pos.numpy(), cos_sin=cs.numpy()[pos.numpy()], q_out_truncated=bits16(q.contiguous()))
+    print("wrote rope_triton_interp.npz")
 
 
 def main() -> None:
@@ -277,5 +312,7 @@ if __name__ == "__main__":
         kv_table_fixture()
     elif sys.argv[2:4] == ["--only", "prefill_attention"]:
         prefill_attention_fixture()
+    elif sys.argv[2:4] == ["--only", "rope_triton_interp"]:
+        rope_triton_interp_fixture()
     else:
         main()

@@ -187,3 +187,20 @@ def test_prefill_attention_matches_reference():
     ref = bf16_from_bits(g["out"]).float()
     # the reference evaluates SDPA in bf16; this oracle in fp32
     assert torch.allclose(out.float(), ref, rtol=2e-2, atol=2e-2)
+
+
+def test_fused_qk_norm_rope_float32_arithmetic_matches_reference_triton_kernel():
+    """The reference's fused QK-norm + RoPE Triton kernel, executed by Triton's CPU interpreter, writes Q as
+    the TRUNCATED float32 result (the interpreter's float32 -> bfloat16 cast truncates; the hardware cast is
+    round-to-nearest). Truncating this oracle's float32 result gives the same bits: the float32 arithmetic
+    (norm, weight, NeoX pairing, cos/sin row) is the kernel's, bit for bit; the rounded result is within one
+    bfloat16 ulp of the fixture everywhere."""
+    g = load_golden("rope_triton_interp")
+    q = bf16_from_bits(g["q"])
+    cs = torch.from_numpy(g["cos_sin"]).float()
+    cos, sin = cs[:, None, :64], cs[:, None, 64:]
+    y = O._norm_rope(q.float(), bf16_from_bits(g["qw"]), 1e-6, cos, sin)
+    truncated = (y.contiguous().view(torch.int32) >> 16).to(torch.int16).numpy().view(np.uint16)
+    assert np.array_equal(truncated, g["q_out_truncated"])
+    rounded = bits16(y.to(torch.bfloat16)).astype(np.int32)
+    assert np.abs(rounded - g["q_out_truncated"].astype(np.int32)).max() <= 1
