@@ -629,12 +629,8 @@ static int launch(const Params& p, int max_group_rows, cudaStream_t stream) {
                          static_cast<uint64_t>(p.lcap) * kD * 2, kTileN, kD, 1, true);
   if (st != FR_OK) return st;
   auto kern = decode_attn_tc_kernel<G, CAUSAL>;
-  static bool attr_done = false;
-  if (!attr_done) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
-      return FR_ERR_CUDA;
-    attr_done = true;
-  }
+  static PerDeviceFlag attr_done;  // per template instantiation and device
+  if (ensure_dyn_smem(attr_done, kern, kSmemBytes) != FR_OK) return FR_ERR_CUDA;
   int* status = device_status_ptr();
   if (!status) return FR_ERR_CUDA;
   dim3 pgrid(ceil_div(p.lcap, 32), p.hkv, p.n_groups);

@@ -466,6 +466,10 @@ __global__ void __launch_bounds__(kThreads, 1) merge_shards_kernel(MergeParams m
         }
       }
     }
+    // a dead winner (fewer than K live candidates over all shards) is filled as the unsharded step
+    // fills it: parent 0, code 0 of the level, and the node that edge leads to
+    if (!live && p.node_in && p.trie.kind != FR_TRIE_NONE)
+      child = trie_transition(p.trie, p.node_in[static_cast<size_t>(n) * p.BW], p.level_tok_base);
     const int64_t pc = clamp64(parent, 0, p.BW - 1);
     const size_t o = static_cast<size_t>(n) * p.K + k;
     p.out_vals[o] = v;
@@ -652,8 +656,9 @@ extern "C" int fr_topk_merge_shards(float* out_vals, int64_t* out_parents, int64
                                     int64_t* out_child, const float* shard_vals, const int64_t* shard_indices,
                                     const int64_t* shard_child, const int64_t* node_in, const int64_t* token_ids_in,
                                     int64_t* token_ids_out, int64_t* node_ids_out, const uint8_t* do_expand,
-                                    const int32_t* col_n, int64_t level_tok_base, int64_t idx_width, int S, int N,
-                                    int BW, int K, int L, int apply_expand, int apply_advance, cudaStream_t stream) {
+                                    const int32_t* col_n, const fr_trie* trie, int64_t level_tok_base,
+                                    int64_t idx_width, int S, int N, int BW, int K, int L, int apply_expand,
+                                    int apply_advance, cudaStream_t stream) {
   FR_CHECK_ARG(S > 0 && N >= 0 && BW > 0 && K > 0 && idx_width > 0);
   if (N == 0) return FR_OK;
   FR_CHECK_ARG(out_vals && out_parents && out_tokens && out_indices && shard_vals && shard_indices);
@@ -661,6 +666,10 @@ extern "C" int fr_topk_merge_shards(float* out_vals, int64_t* out_parents, int64
   MergeParams mp{};
   mp.vals = shard_vals; mp.indices = shard_indices; mp.child = shard_child; mp.S = S;
   StepParams& p = mp.step;
+  {
+    const int st = make_trie(trie, &p.trie);
+    if (st != FR_OK) return st;
+  }
   p.out_vals = out_vals; p.out_parents = out_parents; p.out_tokens = out_tokens; p.out_indices = out_indices;
   p.out_child = out_child; p.token_ids_out = token_ids_out; p.node_ids_out = node_ids_out;
   p.node_in = node_in; p.token_ids_in = token_ids_in; p.do_expand = do_expand; p.col_n = col_n;
@@ -697,11 +706,15 @@ extern "C" int fr_topk_merge_shards(float* out_vals, int64_t* out_parents, int64
 // array below, which every GPU that loads the library holds until exit.
 //
 // Limits and rules:
-//   * N * BW * C <= FR_STATIC_SCRATCH_FLOATS (2 Mi floats = 8 MiB); larger
-//     requests are refused with FR_ERR_UNSUPPORTED, nothing is launched.
+//   * N * BW * C <= FR_STATIC_SCRATCH_FLOATS (2 Mi floats = 8 MiB) whenever the call masks
+//     (apply_mask with a trie and node_in: the only case that touches the array); larger
+//     requests are refused with FR_ERR_UNSUPPORTED, nothing is launched. Unmasked calls never
+//     use the array and have no such limit.
 //   * The first call on a device looks up the array's device address
 //     (cudaGetSymbolAddress with that device current) and caches it; make that
-//     first call before starting any stream capture.
+//     first call before starting any stream capture. The cache is keyed by device
+//     ordinal and filled without a lock (concurrent first calls store the same value);
+//     it does not survive cudaDeviceReset: do not reset a device this library has served.
 //   * All calls on a device share the one array. The kernel rewrites every
 //     workspace entry it later reads, so nothing has to be cleared between
 //     calls, but two calls that overlap on the GPU (different streams) race on it.
@@ -717,7 +730,10 @@ extern "C" int fr_mask_topk_expand_static(float* out_vals, int64_t* out_parents,
                                           int BW, int C, int K, int L, int apply_mask, int apply_expand,
                                           int apply_advance, cudaStream_t stream) {
   FR_CHECK_ARG(N >= 0 && BW > 0 && C > 0);
-  if (static_cast<int64_t>(N) * BW * C > static_cast<int64_t>(FR_STATIC_SCRATCH_FLOATS)) return FR_ERR_UNSUPPORTED;
+  // the array is only touched when the step masks (same condition as in fr_mask_topk_expand)
+  const bool uses_scratch = apply_mask && node_in != nullptr && trie != nullptr && trie->kind != FR_TRIE_NONE;
+  if (uses_scratch && static_cast<int64_t>(N) * BW * C > static_cast<int64_t>(FR_STATIC_SCRATCH_FLOATS))
+    return FR_ERR_UNSUPPORTED;
   // In host code `g_static_scratch` is only a handle for the symbol, not a device
   // address: resolve it once per device, with that device current.
   constexpr int kMaxDev = 64;

@@ -42,6 +42,43 @@ static inline int launch_status() {
 // (capi.cu). nullptr on a CUDA error.
 const uint16_t* silu_table_ptr(cudaStream_t stream);
 
+// Host-side state that belongs to a device, not to the process: a kernel's opt-in dynamic
+// shared-memory limit (cudaFuncSetAttribute applies to the device that is current when it is
+// called) and the SM count. One process may drive several GPUs through this library, so both are
+// kept per device ordinal. Filled without a lock: concurrent first calls store the same values.
+constexpr int kMaxDevices = 64;
+static inline int current_device() {
+  int d = 0;
+  if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= kMaxDevices) return -1;
+  return d;
+}
+struct PerDeviceFlag {
+  bool done[kMaxDevices] = {};
+};
+// Raise `kern`'s dynamic shared-memory limit to `bytes` on the current device, once per device.
+template <class Kernel>
+static inline int ensure_dyn_smem(PerDeviceFlag& flag, Kernel kern, int bytes) {
+  const int d = current_device();
+  if (d < 0) return FR_ERR_CUDA;
+  if (!flag.done[d]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return FR_ERR_CUDA;
+    flag.done[d] = true;
+  }
+  return FR_OK;
+}
+// SM count of the current device (148 when it cannot be read).
+static inline int device_sm_count() {
+  static int cache[kMaxDevices] = {};
+  const int d = current_device();
+  if (d < 0) return 148;
+  if (cache[d] == 0) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, d) != cudaSuccess || v <= 0) v = 148;
+    cache[d] = v;
+  }
+  return cache[d];
+}
+
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 static inline int ceil_div(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }

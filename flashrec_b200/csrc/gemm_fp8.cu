@@ -1166,15 +1166,7 @@ static int make_tmap_out(CUtensorMap* map, const void* ptr, int64_t rows, int64_
   return r == CUDA_SUCCESS ? FR_OK : FR_ERR_CUDA;
 }
 
-static int sm_count() {
-  static int n = []() {
-    int dev = 0, v = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
-    return v;
-  }();
-  return n;
-}
+static int sm_count() { return device_sm_count(); }
 
 // Tile-width choice: whole waves of 128 x BLOCK_N tiles over the SMs, discounted
 // by how far a narrower tile falls below the tensor-pipe rate (a 128x64 tile
@@ -1206,12 +1198,8 @@ static int launch(const void* a, const void* b, const float* sa, const float* sb
   st = make_tmap_u8(&tb, b, N, K, ldb, BLOCK_N);
   if (st != FR_OK) return st;
   auto kern = gemm_fp8_kernel<BLOCK_N, OutT, EPI>;
-  static bool attr_done = false;  // per template instantiation
-  if (!attr_done) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
-      return FR_ERR_CUDA;
-    attr_done = true;
-  }
+  static PerDeviceFlag attr_done;  // per template instantiation and device
+  if (ensure_dyn_smem(attr_done, kern, C::kSmemBytes) != FR_OK) return FR_ERR_CUDA;
   int* status = device_status_ptr();
   if (!status) return FR_ERR_CUDA;
   const uint16_t* table = EPI == 1 ? silu_table_ptr(stream) : nullptr;
@@ -1239,12 +1227,8 @@ static int launch_pair(const void* a, const void* b, const float* sa, const floa
                           128 / static_cast<int>(sizeof(OutT)));
   if (st != FR_OK) return st;
   auto kern = gemm_fp8_pair_kernel<OutT, EPI>;
-  static bool attr_done = false;
-  if (!attr_done) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
-      return FR_ERR_CUDA;
-    attr_done = true;
-  }
+  static PerDeviceFlag attr_done;  // per template instantiation and device
+  if (ensure_dyn_smem(attr_done, kern, C::kSmemBytes) != FR_OK) return FR_ERR_CUDA;
   int* status = device_status_ptr();
   if (!status) return FR_ERR_CUDA;
   const uint16_t* table = EPI == 1 ? silu_table_ptr(stream) : nullptr;
@@ -1323,12 +1307,8 @@ static int launch_splitk(const void* a, const void* b, const float* sa, const fl
     case 8: kern = gemm_fp8_splitk_kernel<OutT, EPI, 8>; break;
     default: return FR_ERR_UNSUPPORTED;
   }
-  static bool attr_done[9] = {false};
-  if (!attr_done[splits]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
-      return FR_ERR_CUDA;
-    attr_done[splits] = true;
-  }
+  static PerDeviceFlag attr_done[9];  // per split count and device
+  if (ensure_dyn_smem(attr_done[splits], kern, C::kSmemBytes) != FR_OK) return FR_ERR_CUDA;
   int* status = device_status_ptr();
   if (!status) return FR_ERR_CUDA;
   const int tiles = ceil_div(M, C::kTileM) * ceil_div(N, C::kTileN);

@@ -19,11 +19,16 @@
 
 namespace fr {
 
+int* device_status_ptr();  // capi.cu
+
 // indptr[0] = 0, indptr[i + 1] = sum of max(seq_lens[..i], 0). One CTA; each thread owns kScanItems
 // consecutive rows of a chunk, so 16384 rows take two rounds of the block-wide scan.
 constexpr int kScanItems = 8;
+// `status` (optional): the library's sticky status word; it receives {FR_ERR_BAD_ARG, site 41} when the
+// list is longer than `capacity`, since the caller cannot see that without a host read.
 __global__ void __launch_bounds__(1024) seq_scan_kernel(const int32_t* __restrict__ seq_lens,
-                                                       int32_t* __restrict__ indptr, int n) {
+                                                       int32_t* __restrict__ indptr, int n, int capacity = 0,
+                                                       int* status = nullptr) {
   __shared__ int32_t warp_tot[32];
   __shared__ int32_t carry_s;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -66,6 +71,9 @@ __global__ void __launch_bounds__(1024) seq_scan_kernel(const int32_t* __restric
     __syncthreads();
     if (threadIdx.x == 1023) carry_s = incl;
     __syncthreads();
+  }
+  if (status != nullptr && threadIdx.x == 0 && carry_s > capacity) {
+    if (atomicCAS(status, 0, FR_ERR_BAD_ARG) == 0) status[1] = 41;
   }
 }
 
@@ -138,11 +146,18 @@ __global__ void __launch_bounds__(256) kv_step_gather_kernel(StepArgs a) {
       if (a.group_indptr[mid] <= i) lo = mid; else hi = mid;
     }
     const int g0 = a.group_indptr[lo], k = a.group_indptr[lo + 1] - g0;
-    int64_t p = a.parents_rel[i];
-    p = p < 0 ? 0 : (p > k - 1 ? k - 1 : p);  // clamp(0, k - 1) as the reference does
-    par_row = a.rows[g0 + static_cast<int>(p)];
+    // a malformed group list (empty or reversed group, bounds outside the batch) leaves the row
+    // with its own window instead of reading outside `rows`
+    if (k > 0 && g0 >= 0 && g0 + k <= a.n) {
+      int64_t p = a.parents_rel[i];
+      p = p < 0 ? 0 : (p > k - 1 ? k - 1 : p);  // clamp(0, k - 1) as the reference does
+      par_row = a.rows[g0 + static_cast<int>(p)];
+    }
   }
   const bool own_ok = own_row >= 0 && own_row < a.n_table_rows;
+  // a parent whose table row does not exist: the row keeps its own window (identity), so the
+  // write-back never copies list entries that no one wrote
+  if (par_row < 0 || par_row >= a.n_table_rows) par_row = own_row;
   const bool par_ok = par_row >= 0 && par_row < a.n_table_rows;
   const int32_t off = a.indptr[i];
   int32_t* dst = a.out + off;
@@ -207,7 +222,7 @@ extern "C" int fr_kv_table_step(int32_t* req_to_token, int64_t row_stride, int n
   if (n == 0) return FR_OK;
   FR_CHECK_ARG(req_to_token && rows && seq_lens && indptr_out && out && row_stride >= n_cols);
   FR_CHECK_ARG(!parents_rel || (group_indptr && n_groups > 0 && prefix_len));
-  seq_scan_kernel<<<1, 1024, 0, stream>>>(seq_lens, indptr_out, n);
+  seq_scan_kernel<<<1, 1024, 0, stream>>>(seq_lens, indptr_out, n, out_capacity, device_status_ptr());
   if (launch_status() != FR_OK) return FR_ERR_CUDA;
   StepArgs a{req_to_token, row_stride, n_table_rows, n_cols, rows, group_indptr, n_groups, parents_rel, prefix_len,
              seq_lens, new_slot, indptr_out, out, n, out_capacity};

@@ -96,9 +96,12 @@ def trie_mask_candidates(
     if out is None:
         out = torch.empty_like(s_in)
     rows, cols = int(s_in.shape[0]), int(s_in.shape[1])
-    call("fr_trie_mask", ptr(out), ptr(s_in), ptr(_i64(cand_tokens)), ptr(_i64(node_ids)), ctypes.byref(tr),
+    # converted copies stay bound to names until the launch has been issued: a temporary freed
+    # before the call could be handed to the next conversion by the caching allocator
+    tok_c, nodes_c = _i64(cand_tokens), _i64(node_ids)
+    call("fr_trie_mask", ptr(out), ptr(s_in), ptr(tok_c), ptr(nodes_c), ctypes.byref(tr),
          float(neg_inf), rows, cols, stream_ptr(scores.device))
-    del keep
+    del keep, tok_c, nodes_c
     return out
 
 
@@ -317,12 +320,15 @@ def genrec_mask_topk_expand(
     node_out = None
     if do_adv:
         node_in, node_out = _pingpong_io(ws, "node", node_in, torch.int64, device)
+    # converted inputs stay bound to names until the launch has been issued (a temporary freed
+    # earlier could be reused by the next conversion before the kernel reads it)
+    cum_c, lp_c, tok_c = _f32(cum), _f32(top_logprobs), _i64(top_tokens)
     call("fr_mask_topk_expand", ptr(out_vals), ptr(out_parents), ptr(out_tokens), ptr(out_indices), None,
-         ptr(scratch), ptr(_f32(cum)), ptr(_f32(top_logprobs)), ptr(_i64(top_tokens)), ptr(node_in), ptr(tok_in),
+         ptr(scratch), ptr(cum_c), ptr(lp_c), ptr(tok_c), ptr(node_in), ptr(tok_in),
          ptr(tok_out), ptr(node_out), ptr(do_t), ptr(col_t), ctypes.byref(tr) if tr is not None else None,
          n, bw, c, k, int(tok_in.shape[2]) if do_exp else 0, int(do_mask), int(do_exp), int(do_adv),
          stream_ptr(device))
-    del keep
+    del keep, cum_c, lp_c, tok_c
     return GenrecFusedResult(
         vals=out_vals,
         parents=out_parents,

@@ -63,19 +63,21 @@ class CudaHeadOps:
         return o.vals, o.indices, o.child
 
     def merge(self, all_vals, all_idx, all_child, node_ids, token_ids_in, token_ids_out, node_ids_out, col,
-              level_tok_base, idx_width):
+              level_tok_base, idx_width, trie=None, beam_width=None):
         from flashrec_b200._lib import call, ptr, stream_ptr
         from flashrec_b200.sid_decode import BeamStepOut
 
         s, n, k = all_vals.shape
-        bw = int(node_ids.shape[1])
+        bw = int(beam_width) if beam_width is not None else int(node_ids.shape[1])
         dev = all_vals.device
+        tr = trie.descriptor() if trie is not None else None
         out = BeamStepOut(*(torch.empty((n, k), dtype=dt, device=dev)
                             for dt in (torch.float32, torch.int64, torch.int64, torch.int64, torch.int64)))
         do_exp = token_ids_in is not None
         call("fr_topk_merge_shards", ptr(out.vals), ptr(out.parents), ptr(out.tokens), ptr(out.indices),
              ptr(out.child), ptr(all_vals), ptr(all_idx), ptr(all_child), ptr(node_ids), ptr(token_ids_in),
-             ptr(token_ids_out), ptr(node_ids_out), None, ptr(col), int(level_tok_base), int(idx_width), s, n, bw, k,
+             ptr(token_ids_out), ptr(node_ids_out), None, ptr(col), ctypes.byref(tr) if tr is not None else None,
+             int(level_tok_base), int(idx_width), s, n, bw, k,
              int(token_ids_in.shape[2]) if do_exp else 0, int(do_exp), int(do_exp and node_ids_out is not None),
              stream_ptr(dev))
         return out
@@ -108,7 +110,8 @@ class ShardedSidHead:
         vals, idx, child = self.ops.local_step(cum, local_logits, mx, ls, node_ids, trie, level_tok_base, select_k,
                                                lo, level_width)
         return self.ops.merge(self._all_gather(vals), self._all_gather(idx), self._all_gather(child), node_ids,
-                              token_ids_in, token_ids_out, node_ids_out, col, level_tok_base, level_width)
+                              token_ids_in, token_ids_out, node_ids_out, col, level_tok_base, level_width,
+                              trie=trie, beam_width=int(cum.shape[1]))
 
 
 def _main() -> None:

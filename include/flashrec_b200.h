@@ -65,10 +65,17 @@ int fr_token_quant_fp8(const void* x, int x_is_f32, void* q_out, float* scale_ou
 
 /* silu(x[:, :d]) * x[:, d:] -> per-row e4m3. x: bf16 [rows, 2d]; q_out: e4m3
  * [rows, d]; scale_out: f32 [rows]. d % 8 == 0, d <= 16384.
+ * First use on a device (of this entry, fr_silu_mul_bf16 or fr_gemm_fp8_silu_mul, which share
+ * a 128 KB device table of exactly evaluated silu values): the table is filled by a kernel on
+ * `stream` and the call waits for that stream once. Make that first call outside any stream
+ * capture: under capture nothing can be waited for, so the fill is recorded into the graph (and
+ * into every later graph, until a call outside capture has completed the set-up).
  * Reference: silu_and_mul_per_token_quant_fp8 (kernel/silu_fp8.py:86-119). */
 int fr_silu_mul_quant_fp8(const void* x, void* q_out, float* scale_out, int rows, int d, cudaStream_t stream);
 
-/* Unquantised SwiGLU, bf16 out [rows, d].
+/* Unquantised SwiGLU, bf16 out [rows, d]. First use on a device fills the shared silu
+ * table and waits for `stream` once, as described for fr_silu_mul_quant_fp8: make that call
+ * outside stream capture.
  * Reference: silu_and_mul (kernel/sglops.py:143-151). */
 int fr_silu_mul_bf16(const void* x, void* y_out, int rows, int d, cudaStream_t stream);
 
@@ -125,6 +132,8 @@ int fr_gemm_fp8_qkv_rope(const void* a, const void* b, const float* scale_a, con
  * fr_quant_known_amax_fp8). Together they reproduce fr_gemm_fp8_w8a8 +
  * fr_silu_mul_quant_fp8 bit for bit while moving half the bytes. mode: 0 = choose,
  * 1 = one CTA per 128 x 256 tile, 2 = CTA pairs on 256 x 256 tiles.
+ * First use on a device fills the shared silu table and waits for `stream` once, as described
+ * for fr_silu_mul_quant_fp8: make that call outside stream capture.
  * Reference: Qwen3MLP.forward (models/qwen3.py:144-172). */
 int fr_gemm_fp8_silu_mul(const void* a, const void* b_interleaved, const float* scale_a,
                          const float* scale_b_interleaved, void* y_out, float* row_amax, int M, int N, int K,
@@ -179,8 +188,11 @@ int fr_gather_kv_indices(const int32_t* req_to_token, int64_t row_stride, const 
  *     gather_kv_indices (attention/kv_indices.py:63-132).
  * rows, parents_rel, new_slot: int64 [n]; group_indptr: int32 [n_groups + 1]; prefix_len,
  * seq_lens: int32 [n] (equal within a request); out: int32 [out_capacity], which must hold the
- * whole list (entries past it are dropped from the list AND from the table update). rows must
- * be distinct; rows outside [0, n_table_rows) are skipped; seq_lens are clamped to n_cols.
+ * whole list (entries past it are dropped from the list AND from the table update, and the status
+ * word read by fr_device_status is set to FR_ERR_BAD_ARG, site 41: size it from the host's own sum
+ * of seq_lens). rows must be distinct; rows outside [0, n_table_rows) are
+ * skipped; a parent whose row is outside the table, or a row whose group is empty or reaches
+ * outside the batch, keeps its own window; seq_lens are clamped to n_cols.
  * No allocation, no host sync: graph-capturable. */
 int fr_kv_table_step(int32_t* req_to_token, int64_t row_stride, int n_table_rows, int n_cols, const int64_t* rows,
                      const int32_t* group_indptr, int n_groups, const int64_t* parents_rel, const int32_t* prefix_len,
@@ -377,10 +389,13 @@ int fr_mask_topk_expand(float* out_vals, int64_t* out_parents, int64_t* out_toke
  * worker in a server whose device memory was fully carved up at start-up and
  * that may not call the allocator during a tick): same arguments minus
  * `scratch`; the masked scores go to a fixed 8 MiB array inside the library.
- * N * BW * C must not exceed 2 * 1024 * 1024 (FR_ERR_UNSUPPORTED otherwise).
- * The first call on a device resolves the array's address; make it before any
- * stream capture. Calls on one device share the array: do not let two of them
- * overlap on the GPU. No counterpart in the reference. */
+ * When the call masks (apply_mask, a trie and node_in given), N * BW * C must
+ * not exceed 2 * 1024 * 1024 (FR_ERR_UNSUPPORTED otherwise); unmasked calls do
+ * not use the array and have no such limit. The first call on a device
+ * resolves the array's address (cached per device ordinal, without a lock; the
+ * cache does not survive cudaDeviceReset); make it before any stream capture.
+ * Calls on one device share the array: do not let two of them overlap on the
+ * GPU. No counterpart in the reference. */
 int fr_mask_topk_expand_static(float* out_vals, int64_t* out_parents, int64_t* out_tokens, int64_t* out_indices,
                                int64_t* out_child, const float* cum, const float* top_logprobs,
                                const int64_t* top_tokens, const int64_t* node_in, const int64_t* token_ids_in,
@@ -406,14 +421,17 @@ int fr_sid_beam_step(float* out_vals, int64_t* out_parents, int64_t* out_tokens,
 
 /* Merge S per-shard sorted winner lists ([S, N, K] values / flat indices /
  * child nodes, e.g. after an all-gather) into the global sorted top-K, then
- * expand / advance as above. S * K <= 16384. No counterpart in the reference
- * (it has no multi-GPU path); the ordering rule is the one above. */
+ * expand / advance as above. S * K <= 16384. trie (optional): with it, the slots
+ * past the last live winner get the child node fr_sid_beam_step gives them (the
+ * edge of code 0 from beam 0's node), so sharded and unsharded node planes agree
+ * there too; NULL writes node 0. No counterpart in the reference (it has no
+ * multi-GPU path); the ordering rule is the one above. */
 int fr_topk_merge_shards(float* out_vals, int64_t* out_parents, int64_t* out_tokens, int64_t* out_indices,
                          int64_t* out_child, const float* shard_vals, const int64_t* shard_indices,
                          const int64_t* shard_child, const int64_t* node_in, const int64_t* token_ids_in,
                          int64_t* token_ids_out, int64_t* node_ids_out, const uint8_t* do_expand, const int32_t* col_n,
-                         int64_t level_tok_base, int64_t idx_width, int S, int N, int BW, int K, int L,
-                         int apply_expand, int apply_advance, cudaStream_t stream);
+                         const fr_trie* trie, int64_t level_tok_base, int64_t idx_width, int S, int N, int BW, int K,
+                         int L, int apply_expand, int apply_advance, cudaStream_t stream);
 
 /* Combine per-shard row statistics [S, rows] (max, logsum) into the statistics
  * of the concatenated row. No counterpart in the reference. */

@@ -457,9 +457,10 @@ def test_merge_shards_equals_unsharded():
     m = BeamStepOut(*(torch.empty((n, bw), dtype=dt, device=DEV)
                       for dt in (torch.float32, torch.int64, torch.int64, torch.int64, torch.int64)))
     tok_out, node_out = torch.zeros_like(token_ids), torch.zeros_like(nodes)
+    tr_desc = tr.descriptor()
     call("fr_topk_merge_shards", ptr(m.vals), ptr(m.parents), ptr(m.tokens), ptr(m.indices), ptr(m.child), ptr(vals),
-         ptr(idx), ptr(child), ptr(nodes), ptr(token_ids), ptr(tok_out), ptr(node_out), None, ptr(col), base + kl, kl,
-         S, n, bw, bw, 2, 1, 1, stream_ptr(logits.device))
+         ptr(idx), ptr(child), ptr(nodes), ptr(token_ids), ptr(tok_out), ptr(node_out), None, ptr(col),
+         ctypes.byref(tr_desc), base + kl, kl, S, n, bw, bw, 2, 1, 1, stream_ptr(logits.device))
     for a, b in ((m.vals, full.vals), (m.parents, full.parents), (m.tokens, full.tokens), (m.indices, full.indices),
                  (m.child, full.child), (tok_out, tok_ref), (node_out, node_ref)):
         assert torch.equal(a, b)

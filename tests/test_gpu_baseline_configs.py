@@ -8,6 +8,8 @@ at any size (legal SIDs only, sorted scores, distinct beams, layouts agree).
 Config 2 at full size is the last case of tests/test_gpu_engine.py::test_decoder_layer_vs_oracle.
 """
 
+import ctypes
+
 import numpy as np
 import pytest
 import torch
@@ -163,9 +165,10 @@ def test_config5_wide_beam_sharded_head_2048_beams_4x4096():
         m = BeamStepOut(*(torch.empty((n, bw), dtype=dt, device=DEV)
                           for dt in (torch.float32, torch.int64, torch.int64, torch.int64, torch.int64)))
         tok_out, node_out = torch.zeros_like(toks), torch.zeros_like(nodes)
+        trie_desc = trie.descriptor()
         call("fr_topk_merge_shards", ptr(m.vals), ptr(m.parents), ptr(m.tokens), ptr(m.indices), ptr(m.child),
              ptr(vals), ptr(idx), ptr(child), ptr(nodes), ptr(toks), ptr(tok_out), ptr(node_out), None, ptr(col),
-             base + lv * kl, kl, S, n, bw, bw, L, 1, 1, stream_ptr(DEV))
+             ctypes.byref(trie_desc), base + lv * kl, kl, S, n, bw, bw, L, 1, 1, stream_ptr(DEV))
         for a, b in ((m.vals, full.vals), (m.parents, full.parents), (m.tokens, full.tokens),
                      (m.indices, full.indices), (m.child, full.child), (tok_out, tok_ref), (node_out, node_ref)):
             assert torch.equal(a, b), lv

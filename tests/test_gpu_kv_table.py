@@ -104,8 +104,35 @@ def test_plain_gather_and_empty():
     # a list buffer that is too short drops the tail from the list and from the table update, nothing else
     table2 = before.clone()
     gi = torch.tensor([0, 3])
+    from flashrec_b200 import device_status
+
+    assert device_status() == (0, 0)
     _gpu_step(table2, rows, gi, sl, torch.tensor([7, 8, 9]), None, None, capacity=3)
     assert table2[4, 2].item() == 7 and table2[5, 9].item() == before[5, 9].item()
+    # ... and the overflow is reported through the status word (read-and-clear)
+    assert device_status() == (-1, 41)
+    assert device_status() == (0, 0)
+
+
+def test_parent_outside_the_table_keeps_the_rows_own_window():
+    from flashrec_b200.attention import kv_table_step
+
+    table = torch.arange(40, dtype=torch.int32).view(4, 10).to(DEV)
+    before = table.clone()
+    # batch rows 0, 1 are table rows 1 and 99 (99 does not exist); both name the other as parent
+    rows = torch.tensor([1, 99], device=DEV)
+    sl = torch.tensor([6, 6], dtype=torch.int32, device=DEV)
+    pre = torch.tensor([2, 2], dtype=torch.int32, device=DEV)
+    par = torch.tensor([1, 0], device=DEV)
+    gi = torch.tensor([0, 2], dtype=torch.int32, device=DEV)
+    out = torch.full((12,), -7, dtype=torch.int32, device=DEV)
+    indptr = torch.zeros(3, dtype=torch.int32, device=DEV)
+    kv_table_step(table, rows, sl, out, indptr, new_slot=torch.tensor([70, 71], device=DEV), parents_rel=par,
+                  prefix_len=pre, group_indptr=gi)
+    want = before.clone()
+    want[1, 5] = 70
+    assert torch.equal(table, want)  # row 1 kept its own window: its parent has no table row
+    assert out[:6].tolist() == [10, 11, 12, 13, 14, 70]
 
 
 def test_type_errors():

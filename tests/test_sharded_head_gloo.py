@@ -36,7 +36,7 @@ class OracleHeadOps:
         gidx = torch.where(torch.isfinite(r["vals"]), gidx, torch.zeros_like(gidx))
         return r["vals"], gidx, r["child"]
 
-    def merge(self, all_vals, all_idx, all_child, node_ids, tin, tout, nout, col, level_tok_base, idx_width):
+    def merge(self, all_vals, all_idx, all_child, node_ids, tin, tout, nout, col, level_tok_base, idx_width, **_):
         s, n, k = all_vals.shape
         out = dict(vals=torch.empty(n, k), idx=torch.empty(n, k, dtype=torch.int64),
                    child=torch.empty(n, k, dtype=torch.int64))

@@ -36,7 +36,7 @@ def _case(seed, n, bw, c, k, L):
     return trie, cum, lp, tok, nodes, token_ids, col
 
 
-def _run(entry, with_scratch, trie, cum, lp, tok, nodes, token_ids, col, k):
+def _run(entry, with_scratch, trie, cum, lp, tok, nodes, token_ids, col, k, masked=True):
     from flashrec_b200._lib import call, ptr, stream_ptr
 
     n, bw, c = lp.shape
@@ -49,7 +49,8 @@ def _run(entry, with_scratch, trie, cum, lp, tok, nodes, token_ids, col, k):
     head = [ptr(outs["vals"]), ptr(outs["parents"]), ptr(outs["tokens"]), ptr(outs["indices"]), ptr(outs["child"])]
     scratch = [ptr(torch.empty(n * bw * c, device=DEV))] if with_scratch else []
     call(entry, *head, *scratch, ptr(cum), ptr(lp), ptr(tok), ptr(nodes), ptr(token_ids), ptr(outs["tok_out"]),
-         ptr(outs["node_out"]), None, ptr(col), ctypes.byref(tr), n, bw, c, k, L, 1, 1, 1, stream_ptr(torch.device(DEV)))
+         ptr(outs["node_out"]), None, ptr(col), ctypes.byref(tr), n, bw, c, k, L, int(masked), 1, int(masked),
+         stream_ptr(torch.device(DEV)))
     torch.cuda.synchronize()
     return outs
 
@@ -76,3 +77,28 @@ def test_static_scratch_entry_refuses_oversized_requests():
         # claims N*BW*C = 4 * 2048 * 512 floats > 2 Mi: rejected before any pointer is touched
         call("fr_mask_topk_expand_static", None, None, None, None, None, ptr(cum), ptr(lp), ptr(tok), ptr(nodes), None,
              None, None, None, None, ctypes.byref(tr), 4, 2048, 512, 8, 0, 1, 0, 0, stream_ptr(torch.device(DEV)))
+
+
+def test_static_scratch_entry_unmasked_step_matches_and_has_no_size_limit():
+    """Without masking the fixed array is never touched: the two entries agree, and a step larger
+    than the array (N*BW*C = 2.25 Mi candidates) is served instead of refused."""
+    args = _case(4, 2, 64, 16, 48, 3)
+    ref = _run("fr_mask_topk_expand", True, *args, 48, masked=False)
+    got = _run("fr_mask_topk_expand_static", False, *args, 48, masked=False)
+    for name in ("vals", "parents", "tokens", "indices", "tok_out"):
+        assert torch.equal(ref[name], got[name]), name
+    n, bw, c, k = 9, 512, 512, 512
+    g = torch.Generator(device=DEV).manual_seed(5)
+    cum = torch.randn((n, bw), generator=g, device=DEV)
+    lp = torch.randn((n, bw, c), generator=g, device=DEV)
+    tok = torch.randint(0, 1000, (n, bw, c), generator=g, device=DEV)
+    trie = args[0]
+    big_ref = _run("fr_mask_topk_expand", True, trie, cum, lp, tok, torch.zeros((n, bw), dtype=torch.int64, device=DEV),
+                   torch.zeros((n, bw, 2), dtype=torch.int64, device=DEV),
+                   torch.zeros(n, dtype=torch.int32, device=DEV), k, masked=False)
+    big = _run("fr_mask_topk_expand_static", False, trie, cum, lp, tok,
+               torch.zeros((n, bw), dtype=torch.int64, device=DEV),
+               torch.zeros((n, bw, 2), dtype=torch.int64, device=DEV), torch.zeros(n, dtype=torch.int32, device=DEV), k,
+               masked=False)
+    for name in ("vals", "parents", "tokens", "indices"):
+        assert torch.equal(big_ref[name], big[name]), name
