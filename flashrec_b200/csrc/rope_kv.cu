@@ -37,6 +37,7 @@ struct RopeArgs {
   uint8_t* vc;
   int64_t ck_s, ck_h, cv_s, cv_h;
   int T, n_q, n_kv, num_slots;
+  __nv_bfloat16* k_out;  // NORM == false only: the rotated K is also written back here (bf16, strides k_t / k_h)
 };
 
 __device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&x)[4]) {
@@ -45,10 +46,12 @@ __device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&x)[4]) {
 }
 
 // ROPE == false: plain conversion of K and V (no norm / rotation), used by fr_store_kv_fp8.
+// NORM == false (with ROPE): rotation only, no per-head RMSNorm, K rewritten in place as well as Q
+// and the cache writes optional: fr_rope_neox_inplace.
 // Each group of D/8 lanes handles HPG consecutive heads of one token; all of their
 // loads are issued before any arithmetic. HPG > 1 requires n_q and n_kv to be
 // multiples of HPG so that a group never mixes Q, K and V heads.
-template <int D, bool ROPE, int HPG>
+template <int D, bool ROPE, int HPG, bool NORM = true>
 __global__ void __launch_bounds__(256) qk_rope_kv_kernel(RopeArgs a) {
   constexpr int LPH = D / 8;        // lanes per head
   constexpr int GPW = 32 / LPH;     // lane groups per warp
@@ -93,14 +96,16 @@ __global__ void __launch_bounds__(256) qk_rope_kv_kernel(RopeArgs a) {
     const float4 s4 = __ldg(reinterpret_cast<const float4*>(a.cs + p * D + HALF + 4 * sub));
     cosv[0] = c4.x; cosv[1] = c4.y; cosv[2] = c4.z; cosv[3] = c4.w;
     sinv[0] = s4.x; sinv[1] = s4.y; sinv[2] = s4.z; sinv[3] = s4.w;
-    const __nv_bfloat16* wsrc = is_q ? a.qw : a.kw;
-    load4(wsrc + 4 * sub, wlo);
-    load4(wsrc + HALF + 4 * sub, whi);
+    if constexpr (NORM) {
+      const __nv_bfloat16* wsrc = is_q ? a.qw : a.kw;
+      load4(wsrc + 4 * sub, wlo);
+      load4(wsrc + HALF + 4 * sub, whi);
+    }
   }
   // sums of squares only where some lane of the warp normalises (Q / K heads); the decision is
   // warp-uniform because all 32 lanes execute the shuffles
   double ss[HPG];
-  const bool any_norm = ROPE && __any_sync(0xffffffffu, live && (is_q || is_k));
+  const bool any_norm = ROPE && NORM && __any_sync(0xffffffffu, live && (is_q || is_k));
 #pragma unroll
   for (int j = 0; j < HPG; ++j) {
     ss[j] = 0.0;
@@ -116,18 +121,23 @@ __global__ void __launch_bounds__(256) qk_rope_kv_kernel(RopeArgs a) {
     }
   }
   if (!live) return;
-  if (!is_q && (slot < 0 || slot >= a.num_slots)) return;  // never write outside the pool
-  if (!ROPE && is_q) return;                               // plain KV store never has Q work
+  const bool to_cache = a.kc != nullptr && !is_q && slot >= 0 && slot < a.num_slots;  // never write outside the pool
+  if (NORM && !is_q && !to_cache) return;
+  if (!NORM && !is_q && !is_k && !to_cache) return;  // rotation only: V has work only when it is stored
+  if (!ROPE && is_q) return;                         // plain KV store never has Q work
 #pragma unroll
   for (int j = 0; j < HPG; ++j) {
     if (rotate) {
-      const float var = static_cast<float>(ss[j] / static_cast<double>(D));
-      const float rstd = rsqrt_rn(__fadd_rn(var, a.eps));
+      float rstd = 1.f;
+      if constexpr (NORM) {
+        const float var = static_cast<float>(ss[j] / static_cast<double>(D));
+        rstd = rsqrt_rn(__fadd_rn(var, a.eps));
+      }
       float y1[4], y2[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float x1 = __fmul_rn(__fmul_rn(lo[j][i], rstd), wlo[i]);
-        const float x2 = __fmul_rn(__fmul_rn(hi[j][i], rstd), whi[i]);
+        const float x1 = NORM ? __fmul_rn(__fmul_rn(lo[j][i], rstd), wlo[i]) : lo[j][i];
+        const float x2 = NORM ? __fmul_rn(__fmul_rn(hi[j][i], rstd), whi[i]) : hi[j][i];
         y1[i] = __fsub_rn(__fmul_rn(x1, cosv[i]), __fmul_rn(x2, sinv[i]));
         y2[i] = __fadd_rn(__fmul_rn(x2, cosv[i]), __fmul_rn(x1, sinv[i]));
       }
@@ -146,6 +156,17 @@ __global__ void __launch_bounds__(256) qk_rope_kv_kernel(RopeArgs a) {
         lo[j][i] = round_bf16(y1[i]);
         hi[j][i] = round_bf16(y2[i]);
       }
+      if constexpr (!NORM) {
+        if (a.k_out != nullptr) {  // rotation in place: the bf16 K goes back to where it came from
+          __nv_bfloat16* dst = a.k_out + t * a.k_t + (h0 + j) * a.k_h;
+          uint2 o1, o2;
+          o1.x = pack_bf16(lo[j][0], lo[j][1]); o1.y = pack_bf16(lo[j][2], lo[j][3]);
+          o2.x = pack_bf16(hi[j][0], hi[j][1]); o2.y = pack_bf16(hi[j][2], hi[j][3]);
+          *reinterpret_cast<uint2*>(dst + 4 * sub) = o1;
+          *reinterpret_cast<uint2*>(dst + HALF + 4 * sub) = o2;
+        }
+        if (!to_cache) continue;
+      }
     }
     uint8_t* dst = is_k ? (a.kc + slot * a.ck_s + (h0 + j) * a.ck_h) : (a.vc + slot * a.cv_s + (h0 + j) * a.cv_h);
     *reinterpret_cast<uint32_t*>(dst + 4 * sub) = pack_e4m3x4(lo[j][0], lo[j][1], lo[j][2], lo[j][3]);
@@ -153,7 +174,7 @@ __global__ void __launch_bounds__(256) qk_rope_kv_kernel(RopeArgs a) {
   }
 }
 
-template <bool ROPE>
+template <bool ROPE, bool NORM = true>
 static int launch_rope(const RopeArgs& a, int D, cudaStream_t stream) {
   const int heads_all = a.n_q + 2 * a.n_kv;
   if (static_cast<int64_t>(a.T) * heads_all == 0) return FR_OK;
@@ -161,12 +182,12 @@ static int launch_rope(const RopeArgs& a, int D, cudaStream_t stream) {
   const int64_t items = static_cast<int64_t>(a.T) * (four ? heads_all / 4 : heads_all);
   if (D == 128) {
     const int per_cta = 8 * 2;
-    if (four) qk_rope_kv_kernel<128, ROPE, 4><<<ceil_div(items, per_cta), 256, 0, stream>>>(a);
-    else qk_rope_kv_kernel<128, ROPE, 1><<<ceil_div(items, per_cta), 256, 0, stream>>>(a);
+    if (four) qk_rope_kv_kernel<128, ROPE, 4, NORM><<<ceil_div(items, per_cta), 256, 0, stream>>>(a);
+    else qk_rope_kv_kernel<128, ROPE, 1, NORM><<<ceil_div(items, per_cta), 256, 0, stream>>>(a);
   } else if (D == 64) {
     const int per_cta = 8 * 4;
-    if (four) qk_rope_kv_kernel<64, ROPE, 4><<<ceil_div(items, per_cta), 256, 0, stream>>>(a);
-    else qk_rope_kv_kernel<64, ROPE, 1><<<ceil_div(items, per_cta), 256, 0, stream>>>(a);
+    if (four) qk_rope_kv_kernel<64, ROPE, 4, NORM><<<ceil_div(items, per_cta), 256, 0, stream>>>(a);
+    else qk_rope_kv_kernel<64, ROPE, 1, NORM><<<ceil_div(items, per_cta), 256, 0, stream>>>(a);
   } else {
     return FR_ERR_UNSUPPORTED;
   }
@@ -210,8 +231,33 @@ extern "C" int fr_qk_norm_rope_kv_fp8(void* q, const void* k, const void* v, int
   RopeArgs a{static_cast<__nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v),
              q_t, q_h, k_t, k_h, v_t, v_h, positions, loc, static_cast<const __nv_bfloat16*>(q_weight),
              static_cast<const __nv_bfloat16*>(k_weight), eps, cos_sin, max_pos, static_cast<uint8_t*>(k_cache),
-             static_cast<uint8_t*>(v_cache), ck_s, ck_h, cv_s, cv_h, T, n_q, n_kv, num_slots};
+             static_cast<uint8_t*>(v_cache), ck_s, ck_h, cv_s, cv_h, T, n_q, n_kv, num_slots, nullptr};
   return launch_rope<true>(a, D, stream);
+}
+
+extern "C" int fr_rope_neox_inplace(void* q, void* k, const void* v, int64_t q_t, int64_t q_h, int64_t k_t, int64_t k_h,
+                                    int64_t v_t, int64_t v_h, const int64_t* positions, const int64_t* loc,
+                                    const float* cos_sin, int max_pos, void* k_cache, void* v_cache, int64_t ck_s,
+                                    int64_t ck_h, int64_t cv_s, int64_t cv_h, int T, int n_q, int n_kv, int D,
+                                    int num_slots, cudaStream_t stream) {
+  FR_CHECK_ARG(T >= 0 && n_q >= 0 && n_kv >= 0 && D > 0 && max_pos > 0);
+  if (T == 0) return FR_OK;
+  FR_CHECK_ARG(q && k && positions && cos_sin && aligned16(cos_sin));
+  FR_CHECK_SUPPORTED(D == 128 || D == 64);
+  FR_CHECK_ARG(aligned8(q) && aligned8(k) && q_t % 4 == 0 && q_h % 4 == 0 && k_t % 4 == 0 && k_h % 4 == 0);
+  const bool store = k_cache != nullptr || v_cache != nullptr;
+  if (store) {
+    FR_CHECK_ARG(k_cache && v_cache && v && loc && num_slots > 0 && aligned8(v) && v_t % 4 == 0 && v_h % 4 == 0);
+    FR_CHECK_ARG(aligned4(k_cache) && aligned4(v_cache) && ck_s % 4 == 0 && ck_h % 4 == 0 && cv_s % 4 == 0 &&
+                 cv_h % 4 == 0);
+  }
+  // without a cache the V heads have no work; loc is then never read for a slot that is used
+  RopeArgs a{static_cast<__nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k),
+             static_cast<const __nv_bfloat16*>(store ? v : k), q_t, q_h, k_t, k_h, store ? v_t : k_t,
+             store ? v_h : k_h, positions, store ? loc : positions, nullptr, nullptr, 0.f, cos_sin, max_pos,
+             static_cast<uint8_t*>(k_cache), static_cast<uint8_t*>(v_cache), ck_s, ck_h, cv_s, cv_h, T, n_q, n_kv,
+             store ? num_slots : 1, static_cast<__nv_bfloat16*>(k)};
+  return launch_rope<true, false>(a, D, stream);
 }
 
 extern "C" int fr_store_kv_fp8(const void* k, const void* v, int64_t k_t, int64_t k_h, int64_t v_t, int64_t v_h,
@@ -226,7 +272,7 @@ extern "C" int fr_store_kv_fp8(const void* k, const void* v, int64_t k_t, int64_
   FR_CHECK_ARG(aligned4(k_cache) && aligned4(v_cache) && ck_s % 4 == 0 && ck_h % 4 == 0 && cv_s % 4 == 0 && cv_h % 4 == 0);
   RopeArgs a{nullptr, static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), 0, 0, k_t, k_h, v_t,
              v_h, nullptr, loc, nullptr, nullptr, 0.f, nullptr, 1, static_cast<uint8_t*>(k_cache),
-             static_cast<uint8_t*>(v_cache), ck_s, ck_h, cv_s, cv_h, T, 0, n_kv, num_slots};
+             static_cast<uint8_t*>(v_cache), ck_s, ck_h, cv_s, cv_h, T, 0, n_kv, num_slots, nullptr};
   return launch_rope<false>(a, D, stream);
 }
 

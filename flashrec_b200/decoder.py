@@ -1,12 +1,13 @@
 """Host-side call order of one Qwen3 decode step on the FP8 path — a mirror of
 ``Qwen3Attention / Qwen3MLP / Qwen3DecoderLayer / Qwen3ForCausalLM``
-(models/qwen3.py:36-273) and of ``ForwardBatch`` (core.py:81-101). Every
+(models/qwen3.py:36-273); ``ForwardBatch`` (core.py:81-101) is re-exported from ``flashrec_b200.core``. Every
 arithmetic step is one call into the sm_100a library; this file only sequences
 them and owns the weights.
 """
 
 from __future__ import annotations
 
+import itertools
 from dataclasses import dataclass
 from typing import List, Optional
 
@@ -14,6 +15,7 @@ import torch
 
 from flashrec_b200._lib import call, ptr, stream_ptr
 from flashrec_b200.attention import AttentionBackend, TokenToKVPool
+from flashrec_b200.core import ForwardBatch
 from flashrec_b200.kernel.qk_rope_kv import fp8_qkv_mm_norm_rope_store, fused_qk_norm_rope_store_fp8
 from flashrec_b200.kernel.sglops import (fp8_scaled_mm_silu_mul, interleave_gate_up, per_token_quant_fp8,
                                          quant_known_amax_fp8)
@@ -33,32 +35,6 @@ class Qwen3Config:
     rope_theta: float = 1e6
     max_position_embeddings: int = 8192
     vocab_size: int = 151936 + 24576
-
-
-@dataclass
-class ForwardBatch:
-    """One forward; ``n_rows`` = total beam rows (decode) or prompts (prefill) (core.py:81-101).
-
-    Prefill (``is_prefill``): ``input_ids`` / ``positions`` / ``out_cache_loc`` hold one entry per
-    extend token, ``seq_lens`` / ``kv_indptr`` one per request; ``extend_seq_lens`` and
-    ``extend_prefix_lens`` are the reference's host lists, ``qo_indptr`` (int32, device,
-    ``[n_rows + 1]``) is the running sum of ``extend_seq_lens`` that the attention kernel reads."""
-
-    input_ids: torch.Tensor
-    req_pool_indices: Optional[torch.Tensor]
-    seq_lens: torch.Tensor
-    positions: torch.Tensor
-    out_cache_loc: torch.Tensor
-    is_prefill: bool = False
-    kv_indices: Optional[torch.Tensor] = None
-    kv_indptr: Optional[torch.Tensor] = None
-    extend_prefix_lens: Optional[List[int]] = None
-    extend_seq_lens: Optional[List[int]] = None
-    qo_indptr: Optional[torch.Tensor] = None
-
-    @property
-    def n_rows(self) -> int:
-        return int(self.seq_lens.numel())
 
 
 class Qwen3Attention:
@@ -228,10 +204,16 @@ class Qwen3ForCausalLM:
     def last_token_hidden(self, hidden: torch.Tensor, batch: ForwardBatch) -> torch.Tensor:
         """Rows of ``hidden`` that feed the head: all of them for a decode batch, each request's
         last extend token for a prefill batch (ModelEngine.last_token_hidden, engine/engine.py:286-303).
-        The offsets come from ``qo_indptr`` on the device; nothing is staged from the host."""
+        The offsets come from ``qo_indptr`` on the device when the batch has it (nothing is staged from
+        the host), else from the host list ``extend_seq_lens`` as in the reference."""
         if not batch.is_prefill or not batch.extend_seq_lens:
             return hidden
-        idx = (batch.qo_indptr[1:] - 1).to(torch.int64)
+        qo = getattr(batch, "qo_indptr", None)
+        if qo is not None:
+            idx = (qo[1:] - 1).to(torch.int64)
+        else:
+            offs = [o - 1 for o in itertools.accumulate(int(x) for x in batch.extend_seq_lens)]
+            idx = torch.tensor(offs, dtype=torch.int64).to(hidden.device, non_blocking=True)
         out = torch.empty((idx.numel(), hidden.shape[1]), dtype=torch.bfloat16, device=hidden.device)
         call("fr_embedding_bf16", ptr(hidden), ptr(idx), ptr(out), idx.numel(), int(hidden.shape[1]),
              int(hidden.shape[0]), stream_ptr(hidden.device))

@@ -195,6 +195,68 @@ def silu_and_mul(x: torch.Tensor) -> torch.Tensor:
     return out.view(*x.shape[:-1], d)
 
 
+def _rope_call(positions, query, key, value, loc, k_cache, v_cache, head_size, cos_sin_cache) -> None:
+    d = int(head_size)
+    t = int(query.shape[0])
+    if query.dtype != torch.bfloat16 or key.dtype != torch.bfloat16:
+        raise TypeError("rope: bfloat16 activations only")
+    if query.dim() != 2 or key.dim() != 2 or query.stride(1) != 1 or key.stride(1) != 1:
+        raise ValueError("rope: query / key must be [T, heads * head_size] with unit column stride")
+    n_q, n_kv = int(query.shape[1]) // d, int(key.shape[1]) // d
+    if int(cos_sin_cache.shape[-1]) != d:
+        raise ValueError("rope: cos_sin_cache width != head_size")
+    pos = positions.reshape(-1)[:t].to(dtype=torch.int64).contiguous()
+    cs = cos_sin_cache.to(device=query.device, dtype=torch.float32).contiguous()
+    args_v = (None, 0, 0)
+    loc64 = kc = vc = None
+    strides_c = (0, 0, 0, 0)
+    slots = 0
+    if k_cache is not None:
+        if k_cache.dtype != _FP8 or v_cache.dtype != _FP8:
+            raise TypeError("rope + store: only the float8_e4m3fn pool is supported")
+        v2 = value if value.stride(-1) == 1 else value.contiguous()
+        if v2.dim() != 2 or int(v2.shape[1]) != n_kv * d:
+            raise ValueError("rope + store: value must be [T, kv_heads * head_size]")
+        args_v = (v2, v2.stride(0), d)
+        loc64 = loc.reshape(-1)[:t].to(torch.int64).contiguous()
+        kc = k_cache.view(k_cache.shape[0], -1)
+        vc = v_cache.view(v_cache.shape[0], -1)
+        strides_c = (kc.stride(0), d, vc.stride(0), d)
+        slots = int(kc.shape[0])
+    call("fr_rope_neox_inplace", ptr(query), ptr(key), ptr(args_v[0]), query.stride(0), d, key.stride(0), d,
+         args_v[1], args_v[2], ptr(pos), ptr(loc64), ptr(cs), int(cs.shape[0]), ptr(kc), ptr(vc), *strides_c, t, n_q,
+         n_kv, d, slots, stream_ptr(query.device))
+
+
+def apply_rope_inplace(positions: torch.Tensor, query: torch.Tensor, key: torch.Tensor, head_size: int,
+                       cos_sin_cache: torch.Tensor) -> bool:
+    """NeoX rotation of ``query`` [T, Hq * D] and ``key`` [T, Hkv * D] in place (bf16), angles from
+    ``cos_sin_cache`` fp32 [max_pos, D] = [cos | sin]; fp32 arithmetic, one rounding to bf16
+    (kernel/sglops.py:65-82, which hands the same arguments to sgl-kernel's
+    ``apply_rope_with_cos_sin_cache_inplace``). Always returns True: there is no other branch."""
+    require_cuda(positions, query, key, cos_sin_cache)
+    if query.numel() == 0:
+        return True
+    _rope_call(positions, query, key, None, None, None, None, head_size, cos_sin_cache)
+    return True
+
+
+def apply_rope_and_store_kv(positions: torch.Tensor, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                            loc: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, head_size: int,
+                            cos_sin_cache: torch.Tensor) -> bool:
+    """``apply_rope_inplace`` plus the KV write of the same tokens in one launch: the rotated key
+    (its bf16 value) and ``value`` are converted to e4m3 and stored at ``k_cache[loc]`` /
+    ``v_cache[loc]`` (caches ``[slots, Hkv * D]``). The reference's function of this name
+    (kernel/sglops.py:155-205) declines an e4m3 pool with bf16 activations and leaves the store to
+    ``TokenToKVPool.store``; the bytes written here are the ones that store would write after the
+    rotation. Returns True (KV has been written)."""
+    require_cuda(positions, query, key, value, loc, k_cache, v_cache, cos_sin_cache)
+    if query.numel() == 0:
+        return True
+    _rope_call(positions, query, key, value, loc, k_cache, v_cache, head_size, cos_sin_cache)
+    return True
+
+
 def store_kv_cache(
     k_cache: torch.Tensor, v_cache: torch.Tensor, loc: torch.Tensor, k: torch.Tensor, v: torch.Tensor
 ) -> None:

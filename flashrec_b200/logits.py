@@ -65,7 +65,7 @@ class RestrictedLMHead:
     def bind(self, lm_weight: torch.Tensor) -> None:
         """Slice the SID rows out of the lm_head once and quantise them per channel.
 
-        ``lm_weight`` is [vocab, H] in bf16/fp32; the SID ids must be one contiguous range."""
+        ``lm_weight`` is [vocab, H] in bf16/fp32."""
         if lm_weight is None or not self.enabled:
             return
         ids = self.ids or []
@@ -73,10 +73,15 @@ class RestrictedLMHead:
         if (not ids) or min(ids) < 0 or max(ids) >= vocab:
             raise ValueError(f"sid_token_range out of range for vocab {vocab}")
         lo, hi = int(ids[0]), int(ids[-1])
-        if hi - lo != len(ids) - 1 or any(b - a != 1 for a, b in zip(ids, ids[1:])):
-            raise NotImplementedError("flashrec_b200 needs a contiguous SID token range")
-        self._token_ids = torch.arange(lo, hi + 1, dtype=torch.long, device=lm_weight.device)
-        q, s = quantize_weight_fp8(lm_weight.narrow(0, lo, len(ids)))
+        if hi - lo == len(ids) - 1 and all(b - a == 1 for a, b in zip(ids, ids[1:])):
+            # one contiguous range: a narrow() view, as the reference takes (logits.py:108-113)
+            self._token_ids = torch.arange(lo, hi + 1, dtype=torch.long, device=lm_weight.device)
+            rows = lm_weight.narrow(0, lo, len(ids))
+        else:
+            # scattered ids: gathered once with index_select, as the reference does (logits.py:114-115)
+            self._token_ids = torch.tensor(ids, dtype=torch.long, device=lm_weight.device)
+            rows = lm_weight.index_select(0, self._token_ids)
+        q, s = quantize_weight_fp8(rows)
         self._weight, self._scale = q, s
 
     def bind_quantized(self, weight_fp8: torch.Tensor, scale: torch.Tensor) -> None:

@@ -162,6 +162,19 @@ int fr_qk_norm_rope_kv_fp8(void* q, const void* k, const void* v, int64_t q_t, i
                            void* k_cache, void* v_cache, int64_t ck_s, int64_t ck_h, int64_t cv_s, int64_t cv_h, int T,
                            int n_q, int n_kv, int D, int num_slots, cudaStream_t stream);
 
+/* NeoX rotation only (no norm) of Q and K, both rewritten in place as bf16: x1' = x1 cos - x2 sin,
+ * x2' = x2 cos + x1 sin in fp32, one rounding. q, k, v, positions, cos_sin as in
+ * fr_qk_norm_rope_kv_fp8. With k_cache / v_cache given (both or neither), the rotated K (its
+ * bf16 value) and V are also converted to e4m3 and scattered to slot loc[t]; with both NULL,
+ * v and loc are not read.
+ * Reference: apply_rope_inplace and apply_rope_and_store_kv (kernel/sglops.py:65-82, 155-205:
+ * sgl-kernel's apply_rope_with_cos_sin_cache_inplace), RotaryEmbedding.forward
+ * (layers/rotary.py:43-71) followed by TokenToKVPool.store (kvcache/pool.py:121-139). */
+int fr_rope_neox_inplace(void* q, void* k, const void* v, int64_t q_t, int64_t q_h, int64_t k_t, int64_t k_h,
+                         int64_t v_t, int64_t v_h, const int64_t* positions, const int64_t* loc, const float* cos_sin,
+                         int max_pos, void* k_cache, void* v_cache, int64_t ck_s, int64_t ck_h, int64_t cv_s,
+                         int64_t cv_h, int T, int n_q, int n_kv, int D, int num_slots, cudaStream_t stream);
+
 /* bf16 K/V -> e4m3 scatter into the pool.
  * Reference: TokenToKVPool.store (kvcache/pool.py:121-139). */
 int fr_store_kv_fp8(const void* k, const void* v, int64_t k_t, int64_t k_h, int64_t v_t, int64_t v_h,
