@@ -84,7 +84,7 @@ _SIGNATURES = {
     "fr_qk_norm_rope_kv_fp8": [P, P, P, _L, _L, _L, _L, _L, _L, P, P, P, P, _F, P, _I, P, P, _L, _L, _L, _L, _I,
                                _I, _I, _I, _I, P],
     "fr_rope_neox_inplace": [P, P, P, _L, _L, _L, _L, _L, _L, P, P, P, _I, P, P, _L, _L, _L, _L, _I, _I, _I, _I, _I, P],
-    "fr_store_kv_fp8": [P, P, _L, _L, _L, _L, P, P, P, _L, _L, _L, _L, _I, _I, _I, _I, P],
+    "fr_store_kv_fp8": [P, P, _L, _L, _L, _L, P, P, P, _L, _L, _L, _L, _I, _I, _I, _I, _I, P],
     "fr_gather_kv_indices": [P, _L, P, P, P, P, _I, _I, P],
     "fr_kv_table_step": [P, _L, _I, _I, P, P, _I, P, P, P, P, P, P, _I, _I, P],
     "fr_kv_table_fanout": [P, _L, _I, P, P, _I, _I, _I, P],

@@ -354,12 +354,17 @@ class AttentionBackend:
             kv = kv.to(torch.int32)
         bufs = self._graph_bufs.get(self._graph_bs) if self._graph_bs is not None else None
         given = getattr(batch, "kv_indptr", None)
+        lens = None
+        if given is None:
+            lens = batch.seq_lens.view(-1)[:n]
+            if lens.dtype != torch.int32:
+                lens = lens.to(torch.int32)
         if bufs is not None:
             indptr, indices = bufs["indptr"], bufs["indices"]
             if given is not None:
                 indptr[: n + 1].copy_(given.view(-1)[: n + 1], non_blocking=True)
             else:
-                torch.cumsum(batch.seq_lens.view(-1)[:n], dim=0, out=indptr[1: n + 1])
+                torch.cumsum(lens, dim=0, out=indptr[1: n + 1])
             nidx = int(kv.numel())
             if nidx > 0 and kv.data_ptr() != indices.data_ptr():
                 indices[:nidx].copy_(kv, non_blocking=True)
@@ -368,7 +373,7 @@ class AttentionBackend:
             return given, kv
         if self._own_indptr is None or self._own_indptr.numel() < n + 1:
             self._own_indptr = torch.zeros(n + 1, dtype=torch.int32, device=kv.device)
-        torch.cumsum(batch.seq_lens.view(-1)[:n], dim=0, out=self._own_indptr[1: n + 1])
+        torch.cumsum(lens, dim=0, out=self._own_indptr[1: n + 1])
         return self._own_indptr, kv
 
     def _host_max_len(self, batch, n: int) -> int:

@@ -194,6 +194,31 @@ static int launch_rope(const RopeArgs& a, int D, cudaStream_t stream) {
   return launch_status();
 }
 
+// Scatter of rows that are e4m3 already: cache[loc[t], h, :] = src[t, h, :] as 16-byte pieces.
+__global__ void __launch_bounds__(256) kv_scatter_e4m3_kernel(const uint8_t* __restrict__ k, const uint8_t* __restrict__ v,
+                                                             int64_t k_t, int64_t k_h, int64_t v_t, int64_t v_h,
+                                                             const int64_t* __restrict__ loc, uint8_t* kc, uint8_t* vc,
+                                                             int64_t ck_s, int64_t ck_h, int64_t cv_s, int64_t cv_h, int T,
+                                                             int n_kv, int D, int num_slots) {
+  const int vec = D / 16;
+  const int64_t total = static_cast<int64_t>(T) * n_kv * vec * 2;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(i % vec);
+    const int h = static_cast<int>((i / vec) % n_kv);
+    const int which = static_cast<int>((i / (static_cast<int64_t>(vec) * n_kv)) & 1);
+    const int t = static_cast<int>(i / (static_cast<int64_t>(vec) * n_kv * 2));
+    const int64_t slot = loc[t];
+    if (slot < 0 || slot >= num_slots) continue;
+    if (which == 0)
+      *reinterpret_cast<uint4*>(kc + slot * ck_s + h * ck_h + 16 * c) =
+          *reinterpret_cast<const uint4*>(k + t * k_t + h * k_h + 16 * c);
+    else
+      *reinterpret_cast<uint4*>(vc + slot * cv_s + h * cv_h + 16 * c) =
+          *reinterpret_cast<const uint4*>(v + t * v_t + h * v_h + 16 * c);
+  }
+}
+
 __global__ void __launch_bounds__(256) embedding_kernel(const uint4* __restrict__ table, const int64_t* __restrict__ ids,
                                                        uint4* __restrict__ out, int T, int vec_per_row, int vocab) {
   const int64_t total = static_cast<int64_t>(T) * vec_per_row;
@@ -262,12 +287,26 @@ extern "C" int fr_rope_neox_inplace(void* q, void* k, const void* v, int64_t q_t
 
 extern "C" int fr_store_kv_fp8(const void* k, const void* v, int64_t k_t, int64_t k_h, int64_t v_t, int64_t v_h,
                                const int64_t* loc, void* k_cache, void* v_cache, int64_t ck_s, int64_t ck_h,
-                               int64_t cv_s, int64_t cv_h, int T, int n_kv, int D, int num_slots,
+                               int64_t cv_s, int64_t cv_h, int T, int n_kv, int D, int num_slots, int src_is_e4m3,
                                cudaStream_t stream) {
   FR_CHECK_ARG(T >= 0 && n_kv >= 0 && D > 0 && num_slots > 0);
   if (T == 0) return FR_OK;
   FR_CHECK_ARG(k && v && loc && k_cache && v_cache);
   FR_CHECK_SUPPORTED(D == 128 || D == 64);
+  if (src_is_e4m3) {
+    // rows converted by the caller (TokenToKVPool.store casts before it calls store_kv_cache): byte scatter
+    FR_CHECK_ARG(aligned16(k) && aligned16(v) && aligned16(k_cache) && aligned16(v_cache));
+    FR_CHECK_ARG(k_t % 16 == 0 && k_h % 16 == 0 && v_t % 16 == 0 && v_h % 16 == 0 && ck_s % 16 == 0 && ck_h % 16 == 0 &&
+                 cv_s % 16 == 0 && cv_h % 16 == 0);
+    const int64_t total = static_cast<int64_t>(T) * n_kv * (D / 16) * 2;
+    int grid = ceil_div(total, 256);
+    if (grid > 148 * 16) grid = 148 * 16;
+    kv_scatter_e4m3_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(k), static_cast<const uint8_t*>(v), k_t,
+                                                    k_h, v_t, v_h, loc, static_cast<uint8_t*>(k_cache),
+                                                    static_cast<uint8_t*>(v_cache), ck_s, ck_h, cv_s, cv_h, T, n_kv, D,
+                                                    num_slots);
+    return launch_status();
+  }
   FR_CHECK_ARG(aligned8(k) && aligned8(v) && k_t % 4 == 0 && k_h % 4 == 0 && v_t % 4 == 0 && v_h % 4 == 0);
   FR_CHECK_ARG(aligned4(k_cache) && aligned4(v_cache) && ck_s % 4 == 0 && ck_h % 4 == 0 && cv_s % 4 == 0 && cv_h % 4 == 0);
   RopeArgs a{nullptr, static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), 0, 0, k_t, k_h, v_t,

@@ -260,8 +260,9 @@ def apply_rope_and_store_kv(positions: torch.Tensor, query: torch.Tensor, key: t
 def store_kv_cache(
     k_cache: torch.Tensor, v_cache: torch.Tensor, loc: torch.Tensor, k: torch.Tensor, v: torch.Tensor
 ) -> None:
-    """k_cache[loc] = k; v_cache[loc] = v with bf16 -> e4m3 conversion.
-    Caches are [slots, H*D] (or [slots, H, D]) e4m3; k/v are [n, H*D] bf16 (kernel/sglops.py:207-222)."""
+    """k_cache[loc] = k; v_cache[loc] = v. Caches are [slots, H*D] (or [slots, H, D]) e4m3; k/v are
+    [n, H*D] bf16 (converted here) or e4m3 already, as ``TokenToKVPool.store`` hands them over
+    (kernel/sglops.py:207-222, kvcache/pool.py:121-139)."""
     require_cuda(k_cache, v_cache, loc, k, v)
     if k_cache.dtype != _FP8:
         raise TypeError("store_kv_cache: only the float8_e4m3fn pool is supported")
@@ -280,5 +281,8 @@ def store_kv_cache(
     loc64 = loc.reshape(-1).to(torch.int64).contiguous()
     kc = k_cache.view(k_cache.shape[0], -1)
     vc = v_cache.view(v_cache.shape[0], -1)
+    if k2.dtype not in (torch.bfloat16, _FP8) or v2.dtype != k2.dtype:
+        raise TypeError(f"store_kv_cache: k / v must both be bfloat16 or float8_e4m3fn, got {k2.dtype} / {v2.dtype}")
     call("fr_store_kv_fp8", ptr(k2), ptr(v2), k2.stride(0), k2.stride(1), v2.stride(0), v2.stride(1), ptr(loc64),
-         ptr(kc), ptr(vc), kc.stride(0), d, vc.stride(0), d, n, h, d, int(kc.shape[0]), stream_ptr(k.device))
+         ptr(kc), ptr(vc), kc.stride(0), d, vc.stride(0), d, n, h, d, int(kc.shape[0]), int(k2.dtype == _FP8),
+         stream_ptr(k.device))

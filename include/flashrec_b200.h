@@ -175,11 +175,14 @@ int fr_rope_neox_inplace(void* q, void* k, const void* v, int64_t q_t, int64_t q
                          int max_pos, void* k_cache, void* v_cache, int64_t ck_s, int64_t ck_h, int64_t cv_s,
                          int64_t cv_h, int T, int n_q, int n_kv, int D, int num_slots, cudaStream_t stream);
 
-/* bf16 K/V -> e4m3 scatter into the pool.
- * Reference: TokenToKVPool.store (kvcache/pool.py:121-139). */
+/* K/V scatter into the e4m3 pool: cache[loc[t], h, :] = e4m3(src[t, h, :]). src is bf16
+ * (src_is_e4m3 == 0; element strides, converted here) or e4m3 already (src_is_e4m3 != 0: byte
+ * strides, 16-byte aligned rows, a plain copy — TokenToKVPool.store casts before it calls
+ * store_kv_cache).
+ * Reference: TokenToKVPool.store (kvcache/pool.py:121-139), store_kv_cache (kernel/sglops.py:207-222). */
 int fr_store_kv_fp8(const void* k, const void* v, int64_t k_t, int64_t k_h, int64_t v_t, int64_t v_h,
                     const int64_t* loc, void* k_cache, void* v_cache, int64_t ck_s, int64_t ck_h, int64_t cv_s,
-                    int64_t cv_h, int T, int n_kv, int D, int num_slots, cudaStream_t stream);
+                    int64_t cv_h, int T, int n_kv, int D, int num_slots, int src_is_e4m3, cudaStream_t stream);
 
 /* indptr_out[0..n] = exclusive scan of seq_lens; out[indptr[i] + j] =
  * req_to_token[rows[i], j] for j < seq_lens[i]. req_to_token int32 with element

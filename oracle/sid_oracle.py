@@ -173,6 +173,27 @@ def qk_norm_rope_store_fp8(q, k, v, positions, loc, q_weight, k_weight, eps, cos
     return q_new
 
 
+def rope_neox(positions, query, key, head_size: int, cos_sin_cache):
+    """Rotation only (no norm) of ``query`` [T, Hq * D] and ``key`` [T, Hkv * D]: what
+    ``apply_rope_inplace`` asks of sgl-kernel's ``apply_rope_with_cos_sin_cache_inplace``
+    (kernel/sglops.py:65-82; third-party, ``sgl-kernel>=0.3.21,<0.4`` in the reference's
+    pyproject.toml:49) and what ``RotaryEmbedding.forward`` intends with its torch formula
+    ``q * cos + rotate_half(q) * sin`` (layers/rotary.py:55-71, which raises as written because it
+    multiplies 64-wide cos / sin into 128-wide heads): NeoX halves, float32 products and sums, one
+    rounding to the input dtype. The rotation arithmetic is the one of ``_norm_rope`` above (pinned by
+    the reference's Triton kernel under the interpreter) with the norm step left out. Returns new (q, k)."""
+    d = int(head_size)
+    cs = cos_sin_cache[positions.long()].float()
+    cos, sin = cs[:, None, : d // 2], cs[:, None, d // 2:]
+
+    def rot(x):
+        x3 = x.float().view(x.shape[0], -1, d)
+        x1, x2 = x3[..., : d // 2], x3[..., d // 2:]
+        return torch.cat((x1 * cos - x2 * sin, x2 * cos + x1 * sin), dim=-1).to(x.dtype).view(x.shape)
+
+    return rot(query), rot(key)
+
+
 def store_kv(k_cache, v_cache, loc, k, v):
     """kvcache/pool.py:121-139 + kernel/sglops.py:207-222 (index_put of converted rows)."""
     k_cache[loc.long()] = k.to(FP8)
@@ -307,6 +328,77 @@ def decoder_layer(x, residual, w, norms, positions, loc, cos_sin_cache, k_cache,
     out = fp8_scaled_mm(yq, w["down"][0], ys, w["down"][1])
     t["out"] = out
     return out, residual
+
+
+def model_forward(input_ids, embed, layers, final_norm, positions, loc, cos_sin_cache, k_caches, v_caches, kv_indptr,
+                  kv_indices, hq: int, hkv: int, d: int, eps: float = 1e-6) -> torch.Tensor:
+    """Qwen3ForCausalLM.forward on the FP8 branch (models/qwen3.py:262-273): embedding lookup, the
+    decoder layers chained through (hidden, residual), final fused add + RMSNorm. ``layers`` is a list of
+    (weights, norms) as ``decoder_layer`` takes them; ``k_caches`` / ``v_caches`` one e4m3 pool per layer
+    (written in place at ``loc``). Returns the normalised hidden states, bf16 [rows, hidden]."""
+    x = embed[input_ids.long()]
+    residual = None
+    for li, (w, norms) in enumerate(layers):
+        x, residual = decoder_layer(x, residual, w, norms, positions, loc, cos_sin_cache, k_caches[li], v_caches[li],
+                                    kv_indptr, kv_indices, hq, hkv, d, eps)
+    if residual is None:
+        return rmsnorm(x, final_norm, eps)
+    return fused_add_rmsnorm(x, residual, final_norm, eps)[0]
+
+
+def decode_wave(embed, layers, final_norm, head_w, head_s, sizes, token_base: int, trie, table, k_caches, v_caches,
+                prompt_lens, beam_width: int, slot_of_step, cos_sin_cache, hq: int, hkv: int, d: int,
+                first_token: int, eps: float = 1e-6, trace: Optional[list] = None):
+    """A whole wave of trie-constrained SID beam search, every stage from this module: the device
+    work of the reference's decode ticks (``BeamRecEngine._forward_decode`` / ``_expand_decode_body``,
+    scheduler/scheduler.py:1261-1456) for ``len(prompt_lens)`` requests x ``beam_width`` beams over
+    ``len(sizes)`` levels, with the whole level as candidate set. Per level: slot-table tick (window
+    remap by last level's parents, new slot, flat lists), model body, FP8 head of the level's rows
+    (``head_w`` e4m3 [sum(sizes), hidden], ``head_s`` f32) with the unmasked fp32 log-softmax, beam step.
+
+    ``table``: int32 [n * bw + n, max_seq] slot table whose last n rows are the requests' prompt rows;
+    ``slot_of_step[s]``: int64 [n * bw] KV slots the rows write at level s; step 0 starts from one live
+    beam per request at the trie root with input token ``first_token``. Returns dict(vals [n, bw] f32
+    sorted descending, tokens [n, bw, L] int64, nodes [n, bw]) — the ranking the scheduler returns for
+    length_penalty 0 (scheduler/scheduler.py:805-807: stable argsort of the cumulative score)."""
+    n, bw, L = len(prompt_lens), int(beam_width), len(sizes)
+    rows = n * bw
+    table = table.clone()
+    rows_idx = torch.arange(rows)
+    beam_rows = rows_idx.view(n, bw)
+    copy_prefill_to_beams_many(table, torch.arange(rows, rows + n), beam_rows, max(prompt_lens))
+    plen_rows = torch.tensor(prompt_lens, dtype=torch.int64).repeat_interleave(bw)
+    group_indptr = torch.arange(n + 1) * bw
+    cum = torch.full((n, bw), float("-inf"))
+    cum[:, 0] = 0.0
+    nodes = torch.zeros((n, bw), dtype=torch.int64)
+    toks = torch.zeros((n, bw, L), dtype=torch.int64)
+    input_ids = torch.full((rows,), int(first_token), dtype=torch.int64)
+    positions = plen_rows.clone()
+    seq_lens = (plen_rows + 1).to(torch.int32)
+    parents = None
+    off = 0
+    for s in range(L):
+        loc = slot_of_step[s].to(torch.int64)
+        indptr, flat = kv_table_step(table, rows_idx, group_indptr, seq_lens, new_slot=loc, parents_rel=parents,
+                                     prefix_len=plen_rows.to(torch.int32))
+        hidden = model_forward(input_ids, embed, layers, final_norm, positions, loc, cos_sin_cache, k_caches, v_caches,
+                               indptr, flat, hq, hkv, d, eps)
+        hq8, hs = per_token_quant_fp8(hidden)
+        logits = fp8_logits_f32(hq8, head_w[off: off + sizes[s]], hs, head_s[off: off + sizes[s]])
+        out = sid_beam_step(cum, logits, nodes, trie, token_base + off, bw, token_ids=toks, col=s)
+        if trace is not None:
+            trace.append(dict(hidden=hidden, logits=logits, vals=out["vals"].clone(), tokens=out["tokens"].clone(),
+                              parents=out["parents"].clone()))
+        cum = out["vals"]
+        toks = out["token_ids"][:, :bw]
+        nodes = out["node_ids"][:, :bw] if out["node_ids"] is not None else nodes
+        parents = out["parents"].reshape(-1)
+        input_ids = out["tokens"].reshape(-1)
+        positions = positions + 1
+        seq_lens = seq_lens + 1
+        off += sizes[s]
+    return dict(vals=cum, tokens=toks, nodes=nodes)
 
 
 # ---------------------------------------------------------------------------

@@ -276,3 +276,95 @@ def test_model_with_residual_adds_in_gemm_epilogues_equals_unfused_flow():
     for layer in range(cfg.num_hidden_layers):  # and the KV pools hold the same bytes
         assert torch.equal(pools[0].k[layer].view(torch.uint8), pools[1].k[layer].view(torch.uint8))
         assert torch.equal(pools[0].v[layer].view(torch.uint8), pools[1].v[layer].view(torch.uint8))
+
+
+def _oracle_model_of(eng):
+    """The engine's weights, KV pool and slot table as CPU tensors in the layout the oracle takes."""
+    layers = []
+    for layer in eng.model.layers:
+        a, m = layer.self_attn, layer.mlp
+        gu_w, gu_s = m._gu_w.cpu(), m._gu_s.cpu()  # rows regrouped per 256 as [128 gate | 128 up]: undo
+        d = gu_w.shape[0] // 2
+        idx = torch.arange(d).view(d // 128, 128)
+        perm = torch.cat((idx, idx + d), dim=1).reshape(-1)
+        gw = torch.empty_like(gu_w.view(torch.uint8))
+        gw[perm] = gu_w.view(torch.uint8)
+        gs = torch.empty_like(gu_s)
+        gs[perm] = gu_s
+        w = dict(qkv=(a.qkv_proj._fp8_weight.t().cpu().contiguous(), a.qkv_proj._fp8_scale.cpu()),
+                 o=(a.o_proj._fp8_weight.t().cpu().contiguous(), a.o_proj._fp8_scale.cpu()),
+                 gate_up=(gw.view(FP8), gs),
+                 down=(m.down_proj._fp8_weight.t().cpu().contiguous(), m.down_proj._fp8_scale.cpu()))
+        norms = dict(input=layer.input_layernorm.weight.cpu().bfloat16(), post=layer.post_attention_layernorm.weight.cpu().bfloat16(),
+                     q=a.q_norm.weight.cpu().bfloat16(), k=a.k_norm.weight.cpu().bfloat16())
+        layers.append((w, norms))
+    return layers
+
+
+def test_end_to_end_ranked_beams_match_the_oracle_wave():
+    """The whole wave — slot-table ticks, a 4-layer model body per level, the FP8 head, the beam steps —
+    run by the engine (eager and from CUDA graphs) against the same wave run stage by stage by the CPU
+    oracle on the same weights, KV bytes and slot table. Rule under test: the final ranked SID beams are
+    identical wherever the oracle's adjacent score gaps exceed 1e-3, and the scores agree within 2e-2
+    (the tolerance of the bf16 GEMM / attention outputs they are built from). Positions whose neighbours
+    lie within the gap may legitimately swap; their number is checked to be small and reported."""
+    from flashrec_b200.decoder import Qwen3Config
+    from flashrec_b200.sid_decode import SidDecodeEngine
+    from flashrec_b200.trie import build_trie_arrays, trie_to_device
+
+    cfg = Qwen3Config(hidden_size=512, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+                      intermediate_size=1024, num_hidden_layers=4, max_position_embeddings=128, vocab_size=1000 + 192)
+    rng = np.random.default_rng(21)
+    sizes, base, n, bw = [64, 64, 64], 1000, 3, 64
+    items = np.stack([rng.integers(0, 64, 6000) for _ in sizes], 1)
+    arrays = build_trie_arrays(items, sizes, base)
+    trie = trie_to_device(arrays, "csr", DEV)
+    prompts = [37, 52, 24]
+    eng = SidDecodeEngine(cfg, n, bw, prompts, sizes, base, trie, DEV, shared_prefix=8, seed=4)
+    eng.model.norm.weight.copy_((1 + 0.1 * torch.randn(cfg.hidden_size, generator=torch.Generator().manual_seed(1))).to(DEV))
+    # snapshot what the oracle needs BEFORE the wave writes decode K/V
+    layers = _oracle_model_of(eng)
+    k_caches = [k.cpu().clone() for k in eng.pool.k]
+    v_caches = [v.cpu().clone() for v in eng.pool.v]
+    table = eng.req_to_token.cpu().clone()
+    embed = eng.model.embed_tokens.cpu()
+    head_w, head_s = eng.head._weight.cpu(), eng.head._scale.cpu()
+    cs = eng.model.rotary.cos_sin_cache.cpu()
+    otr = O.OracleTrie(arrays.csr_keys, arrays.edge_child, arrays.vsz, base, arrays.invalid_node)
+    trace = []
+    ref = O.decode_wave(embed, layers, eng.model.norm.weight.cpu().bfloat16(), head_w, head_s, sizes, base, otr, table,
+                        k_caches, v_caches, prompts, bw, [eng.h_loc[s] for s in range(3)], cs,
+                        cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, first_token=base, trace=trace)
+    eng.run(host_io=False, _eager=True)
+    got_vals, got_tok = eng.cum.cpu().clone(), eng.final_tokens.cpu().clone()
+    eng.capture()
+    eng.run(host_io=True)
+    assert torch.equal(eng.h_vals, got_vals) and torch.equal(eng.h_tokens, got_tok)  # graphs == eager
+
+    gap = 1e-3
+    decided = under_gap = 0
+    for r in range(n):
+        rv, rt = ref["vals"][r].numpy(), ref["tokens"][r].numpy()
+        gv, gt = got_vals[r].numpy(), got_tok[r].numpy()
+        live = np.isfinite(rv)
+        assert (np.isfinite(gv) == live).all()
+        m = int(live.sum())
+        assert m >= bw // 2
+        # both lists rank the same set of SIDs, up to items whose score lies within the gap of the cut-off
+        ref_set, got_set = {tuple(t) for t in rt[:m]}, {tuple(t) for t in gt[:m]}
+        for t in ref_set ^ got_set:
+            where = rt[:m] if t in ref_set else gt[:m]
+            vals = rv if t in ref_set else gv
+            i = next(i for i in range(m) if tuple(where[i]) == t)
+            assert vals[i] - vals[m - 1] <= 2e-2, (r, t)
+        for i in range(m):
+            lo = rv[i - 1] - rv[i] if i > 0 else np.inf
+            hi = rv[i] - rv[i + 1] if i + 1 < m else np.inf
+            if min(lo, hi) > gap:
+                decided += 1
+                assert tuple(gt[i]) == tuple(rt[i]), (r, i, rv[max(i - 1, 0): i + 2], gv[max(i - 1, 0): i + 2])
+                assert abs(gv[i] - rv[i]) <= 2e-2
+            else:
+                under_gap += 1
+    print(f"ranked-beam parity: {decided} positions decided by a gap > {gap}, {under_gap} within the gap")
+    assert decided >= (n * bw) // 4  # the rule was exercised, not vacuous

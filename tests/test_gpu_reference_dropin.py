@@ -1,0 +1,171 @@
+"""Drop-in checks against the reference engine itself (installed unmodified under ``oracle/_ref``):
+
+1. the reference's own GPU tests for this path, run with this library's kernels swapped in at the
+   reference's function boundary (``tests/refshim.py``): in each of them the CUDA side is now this
+   library and the expected side is still the reference's own torch code;
+2. the reference's ``Qwen3ForCausalLM`` (its modules, its weight loading) with the kernels and the
+   attention backend swapped in, one decode step captured and replayed by the reference's own
+   ``DecodeGraphRunner`` at 2 x beam width rows, against this repository's ``decoder.py`` — bit for bit.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+import refshim
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not refshim.available(), reason="oracle/_ref not installed")]
+DEV = "cuda:0"
+FP8 = torch.float8_e4m3fn
+
+# (reference test file, class, test) — the CUDA-gated tests of the kernels on this path
+REFERENCE_TESTS = [
+    ("test_rms_fp8", "TestRmsFp8", "test_rmsnorm_quant_matches_sequential"),
+    ("test_rms_fp8", "TestRmsFp8", "test_fused_add_quant_matches_sequential"),
+    ("test_rms_fp8", "TestRmsFp8", "test_shared_qkv_quant_matches_three_linears"),
+    ("test_silu_fp8", "TestSiluFp8", "test_silu_quant_matches_sequential"),
+    ("test_qk_rope_kv", "TestQkRopeKv", "test_fused_matches_sequential_fp8_store"),
+    ("test_mlp", "TestSiluAndMul", "test_cuda_matches_cpu"),
+    ("test_kv_pool", "TestGatherAndPool", "test_gather_gpu_seq_lens_with_total"),
+    ("test_expand", "TestExpand", "test_genrec_cuda_matches_pytorch"),
+    ("test_expand", "TestExpand", "test_genrec_cuda_skips_masked_heads"),
+    ("test_expand", "TestExpand", "test_genrec_cuda_production_shape"),
+    ("test_expand", "TestExpand", "test_workspace_canonicalizes_cuda_device"),
+    ("test_expand", "TestExpand", "test_genrec_cuda_pingpong_flips_and_matches_cpu"),
+    ("test_graph_expand", "TestGraphExpand", "test_fill_topk_tokens_matches_advanced_index"),
+    ("test_graph_expand", "TestGraphExpand", "test_graph_replay_matches_eager_and_clone_survives"),
+    ("test_graph_expand", "TestGraphExpand", "test_graph_flip_kernel_matches_eager"),
+    ("test_graph_expand", "TestGraphExpand", "test_single_request_graph_replay_keeps_beam_diversity"),
+    ("test_trie_csr", "TestTrieCsrParity", "test_mask_candidates_matches_dense"),
+    ("test_trie_csr", "TestTrieCsrParity", "test_advance_matches_dense"),
+]
+
+
+@pytest.mark.parametrize("stem,cls,name", REFERENCE_TESTS, ids=[f"{s}::{n}" for s, _, n in REFERENCE_TESTS])
+def test_reference_own_test_passes_with_this_library_swapped_in(stem, cls, name):
+    mod = refshim.load_reference_test_module(stem)
+    obj = getattr(mod, cls)()
+    fn = getattr(obj, name)
+    if stem == "test_trie_csr":  # the module's pytest fixture, called by hand
+        fn(mod.trie_pair.__wrapped__() if hasattr(mod.trie_pair, "__wrapped__") else _trie_pair(mod))
+    else:
+        fn()
+    torch.cuda.synchronize()
+
+
+def _trie_pair(mod):
+    import random
+
+    rng = random.Random(7)
+    device = torch.device("cuda")
+    seqs = mod._random_sequences(rng, 120)
+    dense, csr = mod._build_pair(seqs, device)
+    return rng, device, seqs, dense, csr
+
+
+def test_reference_model_and_graph_runner_with_swapped_kernels_equal_this_decoder_bitwise():
+    """The reference's model classes + its CUDA-graph runner on top of this library, against decoder.py."""
+    refshim.install()
+    import flashrec.models.qwen3 as RQ
+    from flashrec.core import ForwardBatch as RefBatch
+    from flashrec.engine.graph import DecodeGraphRunner
+
+    from flashrec_b200.attention import AttentionBackend, TokenToKVPool
+    from flashrec_b200.core import ForwardBatch
+    from flashrec_b200.decoder import Qwen3Config, Qwen3ForCausalLM
+    from flashrec_b200.layers import quantize_weight_fp8
+
+    H, HQ, HKV, D, I, L, V = 512, 4, 2, 128, 1024, 2, 600
+    bw, rows, prompt, slots = 64, 128, 40, 2048
+    g = torch.Generator().manual_seed(9)
+    w = [dict(qkv=0.02 * torch.randn((HQ + 2 * HKV) * D, H, generator=g), o=0.02 * torch.randn(H, HQ * D, generator=g),
+              gate_up=0.02 * torch.randn(2 * I, H, generator=g), down=0.02 * torch.randn(H, I, generator=g),
+              ln1=1 + 0.1 * torch.randn(H, generator=g), ln2=1 + 0.1 * torch.randn(H, generator=g),
+              qn=1 + 0.1 * torch.randn(D, generator=g), kn=1 + 0.1 * torch.randn(D, generator=g)) for _ in range(L)]
+    embed = (0.02 * torch.randn(V, H, generator=g)).bfloat16()
+    final = 1 + 0.1 * torch.randn(H, generator=g)
+    kv0 = [(torch.randn(slots, HKV, D, generator=g).bfloat16().to(FP8), torch.randn(slots, HKV, D, generator=g).bfloat16().to(FP8))
+           for _ in range(L)]
+
+    def fresh_pool():
+        pool = TokenToKVPool(L, slots, HKV, D, FP8, torch.device(DEV))
+        for i, (k, v) in enumerate(kv0):
+            pool.k[i].copy_(k.to(DEV))
+            pool.v[i].copy_(v.to(DEV))
+        return pool
+
+    # two requests x 64 beams: each request's beams share its 40 prompt slots, one own slot per row
+    ids = torch.randint(0, V, (rows,), generator=g)
+    own = torch.arange(1000, 1000 + rows)
+    lists = torch.cat([torch.cat([torch.arange(1 + r * prompt, 1 + (r + 1) * prompt).repeat(bw, 1),
+                                  own[r * bw:(r + 1) * bw, None]], dim=1) for r in range(2)]).to(torch.int32)
+    positions = torch.full((rows,), prompt)
+
+    # ---- this repository's decoder -------------------------------------------------------------------
+    cfg = Qwen3Config(hidden_size=H, num_attention_heads=HQ, num_key_value_heads=HKV, head_dim=D, intermediate_size=I,
+                      num_hidden_layers=L, max_position_embeddings=256, vocab_size=V)
+    pool_a = fresh_pool()
+    attn_a = AttentionBackend(pool_a, HQ, HKV, D, beam_width=bw, max_shared_len=prompt + 1)
+    mine = Qwen3ForCausalLM(cfg, attn_a, DEV, fuse_residual=False, fuse_rope_gemm=False)
+    for layer, lw in zip(mine.layers, w):
+        layer.self_attn.qkv_proj.load(lw["qkv"].to(DEV), quantize_fp8=True)
+        layer.self_attn.o_proj.load(lw["o"].to(DEV), quantize_fp8=True)
+        layer.mlp.gate_up_proj.load(lw["gate_up"].to(DEV), quantize_fp8=True)
+        layer.mlp.down_proj.load(lw["down"].to(DEV), quantize_fp8=True)
+        layer.mlp.prepare_fused()
+        layer.input_layernorm.weight.copy_(lw["ln1"].to(DEV))
+        layer.post_attention_layernorm.weight.copy_(lw["ln2"].to(DEV))
+        layer.self_attn.q_norm.weight.copy_(lw["qn"].to(DEV))
+        layer.self_attn.k_norm.weight.copy_(lw["kn"].to(DEV))
+    mine.norm.weight.copy_(final.to(DEV))
+    mine.embed_tokens = embed.to(DEV)
+    batch_a = ForwardBatch(input_ids=ids.to(DEV), req_pool_indices=None,
+                           seq_lens=torch.full((rows,), prompt + 1, dtype=torch.int32, device=DEV),
+                           positions=positions.to(DEV), out_cache_loc=own.to(DEV), kv_indices=lists.reshape(-1).to(DEV),
+                           kv_indptr=(torch.arange(rows + 1, dtype=torch.int32) * (prompt + 1)).to(DEV))
+    attn_a.prepare(batch_a)
+    want = mine.forward(batch_a).clone()
+
+    # ---- the reference's model + graph runner, kernels and attention backend swapped in ---------------
+    rcfg = RQ.Qwen3Config(hidden_size=H, intermediate_size=I, num_hidden_layers=L, num_attention_heads=HQ,
+                          num_key_value_heads=HKV, head_dim=D, vocab_size=V, rms_norm_eps=1e-6, rope_theta=1e6,
+                          max_position_embeddings=256, tie_word_embeddings=True)
+    pool_b = fresh_pool()
+    attn_b = AttentionBackend(pool_b, HQ, HKV, D, backend="flashinfer", fi_backend="fa2", beam_width=bw)
+    theirs = RQ.Qwen3ForCausalLM(rcfg, attn_b, torch.device(DEV), torch.bfloat16)
+    for layer, lw in zip(theirs.layers, w):
+        for lin, key in ((layer.self_attn.qkv_proj, "qkv"), (layer.self_attn.o_proj, "o"),
+                         (layer.mlp.gate_up_proj, "gate_up"), (layer.mlp.down_proj, "down")):
+            q8, s8 = quantize_weight_fp8(lw[key].to(DEV))  # the same e4m3 bytes and scales as above
+            lin.load(q8, weight_scale=s8)
+        layer.input_layernorm.weight.data.copy_(lw["ln1"].bfloat16().to(DEV))
+        layer.post_attention_layernorm.weight.data.copy_(lw["ln2"].bfloat16().to(DEV))
+        layer.self_attn.q_norm.weight.data.copy_(lw["qn"].bfloat16().to(DEV))
+        layer.self_attn.k_norm.weight.data.copy_(lw["kn"].bfloat16().to(DEV))
+    theirs.norm.weight.data.copy_(final.bfloat16().to(DEV))
+    theirs.embed_tokens.weight.data = embed.to(DEV)
+    # the cos / sin table is an input of the kernels: give both sides the same one (the reference fills it
+    # with the device's cos / sin, this repository with the host's; the two differ in the last bit)
+    theirs.rotary.cos_sin_cache.copy_(mine.rotary.cos_sin_cache)
+    max_seq = 64
+    attn_b.init_graph_wrappers([rows], max_seq)
+    runner = DecodeGraphRunner(device=torch.device(DEV), max_bs=rows, max_seq_len=max_seq, capture_bs=[rows], attn=attn_b)
+    with torch.inference_mode():
+        runner.capture(lambda b: theirs(b), attn_b.prepare)
+        assert rows in runner.graphs, "the reference's runner captured no graph for this batch size"
+        seq_cpu = torch.full((rows,), prompt + 1, dtype=torch.int32)
+        batch_b = RefBatch(input_ids=ids.to(DEV), req_pool_indices=torch.zeros(rows, dtype=torch.int64, device=DEV),
+                           seq_lens=seq_cpu.to(DEV), seq_lens_cpu=seq_cpu, positions=positions.to(DEV),
+                           out_cache_loc=own.to(DEV), is_prefill=False, kv_indices=lists.reshape(-1).to(DEV))
+        got, fused = runner.replay(batch_b, attn_b.prepare)
+        got = got.clone()
+        # eager through the same objects (no graph) gives the same bits
+        attn_b.prepare(batch_b)
+        eager = theirs(batch_b).clone()
+    torch.cuda.synchronize()
+    assert fused is None
+    assert torch.equal(eager, want), float((eager.float() - want.float()).abs().max())
+    assert torch.equal(got, want), float((got.float() - want.float()).abs().max())
+    for i in range(L):  # and the KV pools hold the same bytes
+        assert torch.equal(pool_a.k[i].view(torch.uint8), pool_b.k[i].view(torch.uint8))
+        assert torch.equal(pool_a.v[i].view(torch.uint8), pool_b.v[i].view(torch.uint8))
