@@ -521,3 +521,76 @@ def test_decode_attention_prefix_reused_across_steps():
             assert torch.equal(a, b), (step, layer)
         ref = O.decode_attention(q, kc, vc, indptr, indices, hq // hkv).float()
         assert (a.float().cpu() - ref).abs().max() / ref.abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("t,hq,hkv,d", [(37, 16, 8, 128), (5, 3, 1, 64), (0, 4, 2, 128)])
+def test_rotation_only_rope_in_place_and_with_kv_store(t, hq, hkv, d):
+    """apply_rope_inplace / apply_rope_and_store_kv (rotation without norm, kernel/sglops.py:65-82, 155-205)
+    against the oracle: Q and K bits in place, and with the store the e4m3 bytes TokenToKVPool.store would
+    write for the rotated K and for V; untouched slots stay untouched."""
+    from flashrec_b200.kernel.sglops import apply_rope_and_store_kv, apply_rope_inplace
+
+    g = torch.Generator().manual_seed(t + d)
+    q = torch.randn(t, hq * d, generator=g).bfloat16()
+    k = torch.randn(t, hkv * d, generator=g).bfloat16()
+    v = torch.randn(t, hkv * d, generator=g).bfloat16()
+    cs = O.build_cos_sin_cache(d, 300, 1e6)
+    pos = torch.randint(0, 300, (t,), generator=g)
+    q_ref, k_ref = O.rope_neox(pos, q, k, d, cs)
+    qd, kd = q.to(DEV), k.to(DEV)
+    assert apply_rope_inplace(pos.to(DEV), qd, kd, d, cs.to(DEV)) is True
+    assert torch.equal(qd.cpu().view(torch.int16), q_ref.view(torch.int16))
+    assert torch.equal(kd.cpu().view(torch.int16), k_ref.view(torch.int16))
+    slots = 64
+    loc = torch.randperm(slots - 1, generator=g)[:t] + 1
+    kc = torch.full((slots, hkv * d), 0x11, dtype=torch.uint8).view(FP8)
+    vc = torch.full((slots, hkv * d), 0x22, dtype=torch.uint8).view(FP8)
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    O.store_kv(kc_ref, vc_ref, loc, k_ref, v)
+    qd, kd, kcd, vcd = q.to(DEV), k.to(DEV), kc.to(DEV), vc.to(DEV)
+    assert apply_rope_and_store_kv(pos.to(DEV), qd, kd, v.to(DEV), loc.to(DEV), kcd, vcd, d, cs.to(DEV)) is True
+    assert torch.equal(qd.cpu().view(torch.int16), q_ref.view(torch.int16))
+    assert torch.equal(kd.cpu().view(torch.int16), k_ref.view(torch.int16))
+    assert np.array_equal(bits8(kcd), bits8(kc_ref)) and np.array_equal(bits8(vcd), bits8(vc_ref))
+    # rows that are e4m3 already (the reference's pool casts before it calls store_kv_cache): a plain copy
+    from flashrec_b200.kernel.sglops import store_kv_cache
+
+    kcd2, vcd2 = kc.to(DEV), vc.to(DEV)
+    store_kv_cache(kcd2, vcd2, loc.to(DEV), k_ref.to(FP8).to(DEV), v.to(FP8).to(DEV))
+    assert np.array_equal(bits8(kcd2), bits8(kc_ref)) and np.array_equal(bits8(vcd2), bits8(vc_ref))
+
+
+def test_fused_step_accepts_sliced_and_narrow_typed_inputs():
+    """genrec_mask_topk_expand with a non-contiguous ``cum``, float64 log-probs and int32 tokens — inputs the
+    reference accepts — equals the call on their contiguous float32 / int64 copies and the oracle."""
+    from flashrec_b200.kernel.beam_trie import genrec_mask_topk_expand, trie_mask_candidates
+
+    g = torch.Generator().manual_seed(12)
+    n, bw, c = 3, 32, 24
+    allow = (torch.rand(9, 48, generator=g) > 0.3)
+    nxt = torch.randint(0, 9, (9, 48), generator=g)
+    cum_wide = torch.randn(n, 2 * bw, generator=g)
+    cum = cum_wide[:, ::2]                      # strided view
+    lp = torch.sort(torch.randn(n, bw, c, generator=g), dim=-1, descending=True).values
+    tok = torch.randint(10, 58, (n, bw, c), generator=g)
+    nodes = torch.randint(0, 9, (n, bw), generator=g)
+    tids = torch.randint(10, 58, (n, bw, 4), generator=g)
+    kw = dict(select_k=bw, allow_table=allow.to(DEV), token_base=10, col=2, next_node=nxt.to(DEV), invalid_node=0)
+    a = genrec_mask_topk_expand(cum_wide.to(DEV)[:, ::2], lp.double().to(DEV), tok.to(torch.int32).to(DEV),
+                                node_ids=nodes.to(torch.int32).to(DEV), token_ids=tids.to(DEV), **kw)
+    a = [x.clone() for x in a]
+    b = genrec_mask_topk_expand(cum.contiguous().to(DEV), lp.to(DEV), tok.to(DEV), node_ids=nodes.to(DEV),
+                                token_ids=tids.to(DEV), **kw)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+    otr_keys = (torch.arange(9)[:, None] * 48 + torch.arange(48)[None, :])[allow].numpy()
+    otr = O.OracleTrie(otr_keys, nxt[allow].numpy(), 48, 10, 0)
+    ref = O.mask_topk_expand(cum.contiguous(), lp, tok, bw, node_ids=nodes, trie=otr, token_ids=tids, col=2)
+    assert torch.equal(b.vals.cpu(), ref["vals"]) and torch.equal(b.tokens.cpu(), ref["tokens"])
+    assert torch.equal(b.token_ids.cpu(), ref["token_ids"]) and torch.equal(b.node_ids.cpu(), ref["node_ids"])
+    # the same for the element-wise mask
+    sc = torch.randn(bw, c, generator=g)
+    m1 = trie_mask_candidates(sc.to(DEV), tok[0].to(torch.int32).to(DEV), nodes[0].to(torch.int32).to(DEV),
+                              allow.to(DEV), 10)
+    m2 = trie_mask_candidates(sc.to(DEV), tok[0].to(DEV), nodes[0].to(DEV), allow.to(DEV), 10)
+    assert torch.equal(m1, m2)

@@ -2,7 +2,7 @@
 
 Config 1: RMSNorm -> FP8 then one W8A8 linear, 512 rows x 2048 -> 6144, seed-0 inputs.
 Config 3: trie-constrained SID head, 512 beams, 3 levels x 8192 codes, a catalog of uniform random
-3-tuples (200k here: the catalog size changes the trie, not the kernels), CSR and bitmap tries, three
+3-tuples (200k items, and the configuration's own 1M), CSR and bitmap tries, three
 decode steps: every step against the CPU oracle bit for bit, and the properties the step must have
 at any size (legal SIDs only, sorted scores, distinct beams, layouts agree).
 Config 2 at full size is the last case of tests/test_gpu_engine.py::test_decoder_layer_vs_oracle.
@@ -52,7 +52,7 @@ def test_config1_rmsnorm_fp8_linear_512x2048x6144():
         assert (o2.float().cpu() - out_ref).abs().max() / out_ref.abs().max() < 2e-2, hint
 
 
-@pytest.mark.parametrize("catalog", [200_000])
+@pytest.mark.parametrize("catalog", [200_000, 1_000_000])
 def test_config3_trie_constrained_head_three_steps(catalog):
     from flashrec_b200.logits import RestrictedLMHead
     from flashrec_b200.sid_decode import sid_beam_step
@@ -98,7 +98,7 @@ def test_config3_trie_constrained_head_three_steps(catalog):
             assert (v[:-1] >= v[1:]).all()  # sorted scores
             cum_d, nodes_d, toks_d = out.vals.clone(), node_out, tok_out
         live = torch.isfinite(cum_d[0]).cpu().numpy()
-        assert live.sum() == bw  # a 200k-item catalog keeps all 512 beams alive after three levels
+        assert live.sum() == bw  # catalogs of this size keep all 512 beams alive after three levels
         codes = (toks_d[0].cpu() - torch.tensor([base, base + kl, base + 2 * kl])).numpy()
         rows = [tuple(c) for c in codes[live]]
         assert all(r in legal for r in rows)  # illegal-SID rate 0
@@ -181,3 +181,76 @@ def test_config5_wide_beam_sharded_head_2048_beams_4x4096():
         rows = [tuple(c) for c in codes[r]]
         assert all(x in legal for x in rows) and len(set(rows)) == len(rows)
     assert (nodes == -1).all()
+
+
+def test_config4_full_size_wave_slot_lists_kv_bytes_and_legality():
+    """Config 4 at its stated size on one GPU: 28 layers, 32 requests x 512 beams = 16384 rows, prompts
+    U[128, 1024] sharing a 64-token prefix, 3 levels x 8192 codes, the 1M-item catalog (CSR), one wave from
+    CUDA graphs. Checked against the oracle: the slot table and the last flat slot list of all 16384 rows
+    (bit-exact integer bookkeeping, replayed with the parents the wave chose), the e4m3 K / V bytes the first
+    layer wrote at step 0 for a sample of rows (at most 2 % of the bytes differ, K by one e4m3 step at most:
+    they are conversions of the qkv GEMM's bf16 output, which itself is compared at 2e-2), and for
+    every request: only catalog items, distinct, scores sorted, complete SIDs."""
+    from flashrec_b200.decoder import Qwen3Config
+    from flashrec_b200.sid_decode import SidDecodeEngine
+    from flashrec_b200.trie import build_trie_device
+
+    n, bw, kl, base = 32, 512, 8192, 151_936
+    sizes = [kl] * 3
+    rng = np.random.default_rng(0)
+    items = np.stack([rng.integers(0, s, 1_000_000) for s in sizes], axis=1)
+    trie = build_trie_device(torch.from_numpy(items.astype(np.int32)).to(DEV), sizes, base, layout="csr")
+    prompts = [int(x) for x in np.random.default_rng(1000).integers(128, 1025, n)]
+    cfg = Qwen3Config(num_hidden_layers=28)
+    eng = SidDecodeEngine(cfg, n, bw, prompts, sizes, base, trie, DEV, shared_prefix=64, page_size=16, seed=0)
+    table0 = eng.req_to_token.cpu().clone()
+    eng.capture()
+    eng.run(host_io=True)
+    torch.cuda.synchronize()
+
+    # (1) slot table and last flat list: the reference's bookkeeping replayed on the host
+    exp = table0.clone()
+    O.copy_prefill_to_beams_many(exp, eng.prefill_rows.cpu(), eng.rows_idx.cpu().view(n, bw), max(prompts))
+    pre = eng.prefix_len_rows.cpu()
+    for s in range(eng.steps):
+        par = eng.outs[s - 1].parents.cpu().view(-1) if s else None
+        indptr, flat = O.kv_table_step(exp, eng.rows_idx.cpu(), eng.group_indptr.cpu(), pre + s + 1, eng.h_loc[s], par,
+                                       pre)
+    n_flat = int(indptr[-1])
+    assert torch.equal(eng.kv_indptr.cpu(), indptr) and torch.equal(eng.kv_indices.cpu()[:n_flat], flat)
+    tab = eng.req_to_token.cpu()
+    cols = torch.arange(tab.shape[1])[None, :]
+    reach = cols < (pre[:, None] + eng.steps)  # columns a reader can reach: [:seq_len]
+    assert torch.equal(torch.where(reach, tab[: eng.rows], 0), torch.where(reach, exp[: eng.rows], 0))
+
+    # (2) first layer's K / V bytes of step 0 for a sample of rows
+    layer = eng.model.layers[0]
+    a = layer.self_attn
+    sample = torch.tensor([0, 1, 511, 512, 7000, 16383])
+    x = eng.model.embed_tokens[base].cpu()[None, :].repeat(len(sample), 1)
+    q8, s8 = O.rmsnorm_quant_fp8(x, layer.input_layernorm.weight.cpu(), cfg.rms_norm_eps)
+    qkv = O.fp8_scaled_mm(q8, a.qkv_proj._fp8_weight.t().cpu().contiguous(), s8, a.qkv_proj._fp8_scale.cpu())
+    heads = qkv.view(len(sample), 32, 128)
+    kc = torch.zeros(len(sample) + 1, 8, 128, dtype=torch.uint8).view(FP8)
+    vc = torch.zeros(len(sample) + 1, 8, 128, dtype=torch.uint8).view(FP8)
+    pos = torch.tensor([prompts[int(r) // bw] for r in sample])
+    O.qk_norm_rope_store_fp8(heads[:, :16], heads[:, 16:24], heads[:, 24:], pos, torch.arange(1, len(sample) + 1),
+                             a.q_norm.weight.cpu(), a.k_norm.weight.cpu(), cfg.rms_norm_eps,
+                             eng.model.rotary.cos_sin_cache.cpu(), kc, vc)
+    slots = eng.h_loc[0][sample]
+    got_k, got_v = _bytes(eng.pool.k[0][slots.to(DEV)]), _bytes(eng.pool.v[0][slots.to(DEV)])
+    ref_k, ref_v = _bytes(kc[1:]), _bytes(vc[1:])
+    assert (got_v != ref_v).mean() <= 0.02 and (got_k != ref_k).mean() <= 0.02, ((got_v != ref_v).mean(),
+                                                                                  (got_k != ref_k).mean())
+    dk = np.abs(kc[1:].float().numpy() - eng.pool.k[0][slots.to(DEV)].float().cpu().numpy())
+    assert (dk <= 0.13 * np.maximum(np.abs(kc[1:].float().numpy()), 2.0 ** -6)).all()  # one e4m3 step at most
+
+    # (3) every request: catalog items only, distinct, sorted, complete
+    legal_keys = np.unique(items[:, 0].astype(np.int64) * kl * kl + items[:, 1] * kl + items[:, 2])
+    codes = (eng.h_tokens - torch.tensor([base, base + kl, base + 2 * kl])).numpy().astype(np.int64)
+    keys = codes[..., 0] * kl * kl + codes[..., 1] * kl + codes[..., 2]
+    assert np.isfinite(eng.h_vals.numpy()).all()
+    assert np.isin(keys, legal_keys).all()  # illegal-SID rate 0
+    assert all(len(np.unique(keys[r])) == bw for r in range(n))
+    assert (eng.h_vals[:, :-1] >= eng.h_vals[:, 1:]).all()
+    assert (eng.final_nodes == -1).all()
