@@ -93,7 +93,8 @@ __device__ __forceinline__ int64_t trie_transition(const Trie& tr, int64_t old, 
   const int64_t rel = tok - tr.token_base;
   if (rel < 0 || rel >= tr.vsz) return tr.invalid_node;
   if (tr.kind == FR_TRIE_DENSE) {
-    if (tr.n_rows <= 0) return tr.invalid_node;
+    // a dense trie given for masking only carries no transition table: no edge is known
+    if (tr.n_rows <= 0 || tr.next == nullptr) return tr.invalid_node;
     const int64_t safe = clamp64(old, 0, tr.n_rows - 1);
     return tr.next_is_i32 ? static_cast<int64_t>(__ldg(static_cast<const int32_t*>(tr.next) + safe * tr.vsz + rel))
                           : __ldg(static_cast<const int64_t*>(tr.next) + safe * tr.vsz + rel);

@@ -121,11 +121,38 @@ def fp8_gemm_acc(a_q: torch.Tensor, b_q_nk: torch.Tensor) -> torch.Tensor:
     return (a_q.float().double() @ b_q_nk.float().double().t()).float()
 
 
+# How fp8_scaled_mm rounds. "two_step" is the reference's torch branch, the one that runs on a CPU:
+# torch._scaled_mm with unit scales rounds the accumulator to the output dtype, the scales are applied in
+# fp32 and the result is rounded again (kernel/sglops.py:111-135). "one_step" is what the reference's GPU
+# branch asks of sgl-kernel's fp8_scaled_mm (kernel/sglops.py:109-110; third-party, sgl-kernel>=0.3.21,<0.4):
+# the scales are applied to the fp32 accumulator in the GEMM epilogue and the result is rounded once. The
+# CUDA kernels of this repository round once; the two differ by one bf16 ulp on about a third of the outputs.
+GEMM_ROUNDING = "two_step"
+
+
+class gemm_rounding:
+    """``with gemm_rounding("one_step"): ...`` switches fp8_scaled_mm for the duration of the block."""
+
+    def __init__(self, mode: str):
+        assert mode in ("two_step", "one_step")
+        self.mode = mode
+
+    def __enter__(self):
+        global GEMM_ROUNDING
+        self.prev, GEMM_ROUNDING = GEMM_ROUNDING, self.mode
+
+    def __exit__(self, *a):
+        global GEMM_ROUNDING
+        GEMM_ROUNDING = self.prev
+
+
 def fp8_scaled_mm(a_q, b_q_nk, scale_a, scale_b, out_dtype=torch.bfloat16, bias=None):
-    """kernel/sglops.py:99-140 (torch branch): _scaled_mm with unit scales -> out
-    dtype, then * scale_a * scale_b in fp32 -> out dtype (two roundings)."""
-    acc = fp8_gemm_acc(a_q, b_q_nk).to(out_dtype)
-    out = (acc.float() * scale_a.reshape(-1, 1).float() * scale_b.reshape(1, -1).float()).to(out_dtype)
+    """kernel/sglops.py:99-140. Default ("two_step", the torch branch): _scaled_mm with unit scales -> out
+    dtype, then * scale_a * scale_b in fp32 -> out dtype (two roundings). See GEMM_ROUNDING."""
+    acc = fp8_gemm_acc(a_q, b_q_nk)
+    if GEMM_ROUNDING == "two_step":
+        acc = acc.to(out_dtype).float()
+    out = (acc * scale_a.reshape(-1, 1).float() * scale_b.reshape(1, -1).float()).to(out_dtype)
     if bias is not None:
         out = out + bias.to(out_dtype)
     return out
@@ -187,7 +214,7 @@ def rope_neox(positions, query, key, head_size: int, cos_sin_cache):
     cos, sin = cs[:, None, : d // 2], cs[:, None, d // 2:]
 
     def rot(x):
-        x3 = x.float().view(x.shape[0], -1, d)
+        x3 = x.float().view(x.shape[0], x.shape[1] // d, d)
         x1, x2 = x3[..., : d // 2], x3[..., d // 2:]
         return torch.cat((x1 * cos - x2 * sin, x2 * cos + x1 * sin), dim=-1).to(x.dtype).view(x.shape)
 
@@ -293,12 +320,15 @@ def prefill_attention(q, k_cache, v_cache, qo_indptr, kv_indptr, kv_indices, n_r
 
 
 def decoder_layer(x, residual, w, norms, positions, loc, cos_sin_cache, k_cache, v_cache, kv_indptr, kv_indices,
-                  hq: int, hkv: int, d: int, eps: float = 1e-6, trace: Optional[dict] = None):
+                  hq: int, hkv: int, d: int, eps: float = 1e-6, trace: Optional[dict] = None, attn_out=None):
     """FP8 branch of Qwen3DecoderLayer.forward (models/qwen3.py:198-215) with
     Qwen3Attention.forward (:62-134) and Qwen3MLP.forward (:144-172) inlined.
     ``w`` maps qkv / o / gate_up / down to (e4m3 [N,K], scale [N]); ``norms`` maps
     input / post / q / k to bf16 weights. residual None = first layer. If ``trace``
-    is a dict, every intermediate tensor is stored in it."""
+    is a dict, every intermediate tensor is stored in it. ``attn_out`` (bf16 [rows, hq * d]), when given,
+    stands in for this module's attention result: attention is the one stage whose device arithmetic (fp16
+    probabilities, approximate exponentials) is only comparable within a tolerance, and a test that wants to
+    follow the rest of the chain exactly feeds the device's attention output in here."""
     t = trace if trace is not None else {}
     rows = x.shape[0]
     if residual is None:
@@ -313,7 +343,10 @@ def decoder_layer(x, residual, w, norms, positions, loc, cos_sin_cache, k_cache,
     qn = qk_norm_rope_store_fp8(qkv[:, :hq], qkv[:, hq:hq + hkv], qkv[:, hq + hkv:], positions, loc, norms["q"],
                                 norms["k"], eps, cos_sin_cache, k_cache, v_cache)
     t["qn"] = qn
-    a = decode_attention(qn, k_cache, v_cache, kv_indptr, kv_indices, hq // hkv).reshape(rows, -1)
+    if attn_out is None:
+        a = decode_attention(qn, k_cache, v_cache, kv_indptr, kv_indices, hq // hkv).reshape(rows, -1)
+    else:
+        a = attn_out.reshape(rows, -1).to(qn.dtype)
     t["attn"] = a
     aq, asc = per_token_quant_fp8(a)
     t.update(aq=aq, asc=asc)
@@ -331,16 +364,18 @@ def decoder_layer(x, residual, w, norms, positions, loc, cos_sin_cache, k_cache,
 
 
 def model_forward(input_ids, embed, layers, final_norm, positions, loc, cos_sin_cache, k_caches, v_caches, kv_indptr,
-                  kv_indices, hq: int, hkv: int, d: int, eps: float = 1e-6) -> torch.Tensor:
+                  kv_indices, hq: int, hkv: int, d: int, eps: float = 1e-6, attn_outs=None) -> torch.Tensor:
     """Qwen3ForCausalLM.forward on the FP8 branch (models/qwen3.py:262-273): embedding lookup, the
     decoder layers chained through (hidden, residual), final fused add + RMSNorm. ``layers`` is a list of
     (weights, norms) as ``decoder_layer`` takes them; ``k_caches`` / ``v_caches`` one e4m3 pool per layer
-    (written in place at ``loc``). Returns the normalised hidden states, bf16 [rows, hidden]."""
+    (written in place at ``loc``); ``attn_outs``: optional per-layer attention results to use instead of
+    this module's (see ``decoder_layer``). Returns the normalised hidden states, bf16 [rows, hidden]."""
     x = embed[input_ids.long()]
     residual = None
     for li, (w, norms) in enumerate(layers):
         x, residual = decoder_layer(x, residual, w, norms, positions, loc, cos_sin_cache, k_caches[li], v_caches[li],
-                                    kv_indptr, kv_indices, hq, hkv, d, eps)
+                                    kv_indptr, kv_indices, hq, hkv, d, eps,
+                                    attn_out=None if attn_outs is None else attn_outs[li])
     if residual is None:
         return rmsnorm(x, final_norm, eps)
     return fused_add_rmsnorm(x, residual, final_norm, eps)[0]
@@ -348,7 +383,7 @@ def model_forward(input_ids, embed, layers, final_norm, positions, loc, cos_sin_
 
 def decode_wave(embed, layers, final_norm, head_w, head_s, sizes, token_base: int, trie, table, k_caches, v_caches,
                 prompt_lens, beam_width: int, slot_of_step, cos_sin_cache, hq: int, hkv: int, d: int,
-                first_token: int, eps: float = 1e-6, trace: Optional[list] = None):
+                first_token: int, eps: float = 1e-6, trace: Optional[list] = None, attn_outs=None):
     """A whole wave of trie-constrained SID beam search, every stage from this module: the device
     work of the reference's decode ticks (``BeamRecEngine._forward_decode`` / ``_expand_decode_body``,
     scheduler/scheduler.py:1261-1456) for ``len(prompt_lens)`` requests x ``beam_width`` beams over
@@ -358,7 +393,8 @@ def decode_wave(embed, layers, final_norm, head_w, head_s, sizes, token_base: in
 
     ``table``: int32 [n * bw + n, max_seq] slot table whose last n rows are the requests' prompt rows;
     ``slot_of_step[s]``: int64 [n * bw] KV slots the rows write at level s; step 0 starts from one live
-    beam per request at the trie root with input token ``first_token``. Returns dict(vals [n, bw] f32
+    beam per request at the trie root with input token ``first_token``; ``attn_outs[s][layer]``: optional
+    attention results to use instead of this module's (see ``decoder_layer``). Returns dict(vals [n, bw] f32
     sorted descending, tokens [n, bw, L] int64, nodes [n, bw]) — the ranking the scheduler returns for
     length_penalty 0 (scheduler/scheduler.py:805-807: stable argsort of the cumulative score)."""
     n, bw, L = len(prompt_lens), int(beam_width), len(sizes)
@@ -383,7 +419,7 @@ def decode_wave(embed, layers, final_norm, head_w, head_s, sizes, token_base: in
         indptr, flat = kv_table_step(table, rows_idx, group_indptr, seq_lens, new_slot=loc, parents_rel=parents,
                                      prefix_len=plen_rows.to(torch.int32))
         hidden = model_forward(input_ids, embed, layers, final_norm, positions, loc, cos_sin_cache, k_caches, v_caches,
-                               indptr, flat, hq, hkv, d, eps)
+                               indptr, flat, hq, hkv, d, eps, attn_outs=None if attn_outs is None else attn_outs[s])
         hq8, hs = per_token_quant_fp8(hidden)
         logits = fp8_logits_f32(hq8, head_w[off: off + sizes[s]], hs, head_s[off: off + sizes[s]])
         out = sid_beam_step(cum, logits, nodes, trie, token_base + off, bw, token_ids=toks, col=s)
