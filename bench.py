@@ -11,7 +11,8 @@ Metric: beam rows decoded per second (rows x levels / time), whole job.
   e2e    same wave driven from pinned host buffers: per-step slot ids copied
          host->device, final beams (scores + SID tokens) copied device->host
   roofline      the gate_up FP8 GEMM with the SwiGLU epilogue (dominant kernel), timed alone
-  cpu_baseline  the CPU oracle port of the same ops on a bounded sample
+  cpu_baseline  the reference engine's own torch CPU path for the same step, a bounded sample
+                (also what --impl reference times)
 
 With --gpus N > 1 (launched by torch.distributed.run) every rank runs its own
 replica on its own requests (requests never interact): weak scaling, no
@@ -138,11 +139,148 @@ def prompt_lengths(n: int, seed: int):
 
 
 # ---------------------------------------------------------------------------
-# CPU baseline (oracle port) — also the --impl reference arm
+# CPU baseline = the --impl reference arm: the reference's own torch CPU path
 # ---------------------------------------------------------------------------
-def cpu_baseline(beam: int, sizes, items: int, layers: int, budget_rows: int = 64):
-    """Times the oracle's restatement of one decode step on the host cores for a
-    bounded sample: `budget_rows` beam rows of one request (prompt 256) through ONE
+REF_DIR = ROOT / "oracle" / "_ref"
+
+
+def bench_config(args, world: int, rows: int, catalog_items, decode_steps: int, value_per_gpu=None):
+    """The ``config`` object of the JSON line; both arms print the same keys."""
+    return dict(WORKLOAD, requests=args.requests, beam_width=args.beam, layers=args.layers,
+                catalog_items=catalog_items, trie=args.trie, parallelism=f"dp{world}", rows_per_gpu=rows,
+                value_per_gpu=value_per_gpu, decode_steps_per_wave=decode_steps)
+
+
+class ReferenceCpuStep:
+    """One decode step of the hot path through the UNMODIFIED reference engine on the host cores (its torch
+    branch: sgl-kernel is absent, so every ``flashrec.kernel.sglops`` wrapper computes in torch, and its
+    attention backend takes SDPA), installed under ``oracle/_ref`` by ``oracle/Makefile``:
+
+      body   ``Qwen3DecoderLayer.forward`` (models/qwen3.py:198-215) of ONE layer for ``rows_body`` beam rows of
+             one request over a 256-token prompt: ``RMSNorm.quant_fp8``, ``Linear.forward_fp8`` (torch._scaled_mm
+             on the CPU), the KV store into the e4m3 ``TokenToKVPool``, ``AttentionBackend._sdpa``,
+             ``silu_and_mul_per_token_quant_fp8``. One thing is substituted: ``RotaryEmbedding.forward``'s torch
+             formula raises on a CPU (it multiplies 64-wide cos / sin into 128-wide heads), so the rotation comes
+             from the oracle's restatement of the reference's Triton kernel.
+      head   ``RestrictedLMHead.compute_level`` (bf16, as the reference keeps the head) for a whole request of
+             ``beam`` rows, per-beam ``torch.topk`` of 2 x beam candidates and ``expand_step`` with the reference's
+             CSR ``BeamValidPathTrie`` (search/expand.py:240-372).
+
+    The step time of a request is extrapolated: body x layers x (beam / rows_body) + head. Falls back to the
+    oracle port of the same ops (``kind`` "port") when ``oracle/_ref`` is not there."""
+
+    def __init__(self, beam: int, sizes, items: int, layers: int, rows_body: int = 8):
+        import numpy as np
+        import torch
+
+        self.torch = torch
+        self.beam, self.layers, self.rows = int(beam), int(layers), int(rows_body)
+        self.cores = os.cpu_count() or 1
+        torch.set_num_threads(self.cores)
+        self.kind = "reference" if (REF_DIR / "flashrec" / "__init__.py").exists() else "port"
+        if self.kind == "port":
+            self._port = lambda: cpu_baseline_port(beam, sizes, items, layers)
+            return
+        if str(REF_DIR) not in sys.path:
+            sys.path.insert(0, str(REF_DIR))
+        from flashrec.attention.flashinfer import AttentionBackend
+        from flashrec.core import ForwardBatch
+        from flashrec.kvcache.pool import TokenToKVPool
+        from flashrec.layers import rotary as ref_rotary
+        from flashrec.logits import RestrictedLMHead
+        from flashrec.models.qwen3 import Qwen3Config, Qwen3DecoderLayer
+        from flashrec.search import trie as trie_mod
+        from flashrec.search.expand import expand_step, init_from_prefill_batch
+        from flashrec.search.trie import BeamValidPathTrie
+
+        from oracle import sid_oracle as O
+
+        def rope_forward(self_, positions, query, key):  # see the class text
+            return O.rope_neox(positions, query, key, self_.head_dim, self_.cos_sin_cache)
+
+        ref_rotary.RotaryEmbedding.forward = rope_forward
+        g = torch.Generator().manual_seed(0)
+        H, HQ, HKV, D, I = 2048, 16, 8, 128, 6144
+        rows, plen = self.rows, 256
+        cfg = Qwen3Config(hidden_size=H, intermediate_size=I, num_hidden_layers=1, num_attention_heads=HQ,
+                          num_key_value_heads=HKV, head_dim=D, vocab_size=32, rms_norm_eps=1e-6, rope_theta=1e6,
+                          max_position_embeddings=plen + 8, tie_word_embeddings=True)
+        dev = torch.device("cpu")
+        pool = TokenToKVPool(1, plen + rows + 1, HKV, D, torch.float8_e4m3fn, dev)
+        pool.k[0][1:plen + 1] = torch.randn(plen, HKV, D, generator=g).bfloat16().to(torch.float8_e4m3fn)
+        pool.v[0][1:plen + 1] = torch.randn(plen, HKV, D, generator=g).bfloat16().to(torch.float8_e4m3fn)
+        attn = AttentionBackend(pool, HQ, HKV, D, backend="flashinfer")
+        rot = ref_rotary.RotaryEmbedding(D, plen + 8, 1e6, device=dev)
+        layer = Qwen3DecoderLayer(cfg, 0, attn, rot)
+        for lin, (n_out, n_in) in ((layer.self_attn.qkv_proj, ((HQ + 2 * HKV) * D, H)), (layer.self_attn.o_proj, (H, HQ * D)),
+                                   (layer.mlp.gate_up_proj, (2 * I, H)), (layer.mlp.down_proj, (H, I))):
+            lin.load(0.02 * torch.randn(n_out, n_in, generator=g), quantize_fp8=True)
+        loc = torch.arange(plen + 1, plen + 1 + rows)
+        lists = torch.cat([torch.cat((torch.arange(1, plen + 1), loc[i:i + 1])) for i in range(rows)]).to(torch.int32)
+        seq = torch.full((rows,), plen + 1, dtype=torch.int64)
+        self._batch = ForwardBatch(input_ids=torch.zeros(rows, dtype=torch.int64), req_pool_indices=torch.zeros(rows, dtype=torch.int64),
+                                   seq_lens=seq, seq_lens_cpu=seq.clone(), positions=torch.full((rows,), plen),
+                                   out_cache_loc=loc, is_prefill=False, kv_indices=lists)
+        self._layer = layer
+        self._x = torch.randn(rows, H, generator=g).bfloat16()
+        # head of a whole request: bf16 SID rows, the reference's trie in its CSR layout
+        sid_total, base = int(sum(sizes)), 0
+        head = RestrictedLMHead(list(range(sid_total)))
+        head.bind((0.02 * torch.randn(sid_total, H, generator=g)).bfloat16())
+        head.bind_codebook(list(sizes))
+        cat = make_catalog(min(items, 200_000), sizes)
+        offs = np.concatenate([[0], np.cumsum(sizes)])
+        tr = BeamValidPathTrie(mode="trie")
+        tr.max_depth = len(sizes)
+        for it in cat.tolist():
+            toks = [int(base + offs[l] + it[l]) for l in range(len(sizes))]
+            for dd in range(len(sizes)):
+                tr.children.setdefault(tuple(toks[:dd]), set()).add(toks[dd])
+        tr.all_tokens = set(range(sid_total))
+        tr.finalize_index(token_base=base, vocab_size=sid_total)
+        saved = trie_mod._DENSE_MAX_CELLS
+        trie_mod._DENSE_MAX_CELLS = 0  # the CSR cache, as the 1M-item catalog takes
+        try:
+            tr._ensure_gpu_cache(dev)
+        finally:
+            trie_mod._DENSE_MAX_CELLS = saved
+        self._trie, self._head = tr, head
+        self._hidden = torch.randn(self.beam, H, generator=g).bfloat16()
+        lp0, ids0 = head.compute_level(self._hidden[:1], 0)
+        self._init = lambda: init_from_prefill_batch(lp0, self.beam, min(2 * self.beam, sizes[0]), len(sizes), [plen],
+                                                     valid_path=tr, candidate_token_ids=ids0)[0]
+        self._expand_step = expand_step
+        self.catalog_items = int(cat.shape[0])
+
+    def sample(self):
+        """(beam rows per second, description) of one extrapolated request step."""
+        if self.kind == "port":
+            v, _, desc = self._port()
+            return v, desc
+        torch = self.torch
+        with torch.inference_mode():
+            t0 = time.perf_counter()
+            self._layer(self._x, self._x.clone(), self._batch)
+            t_layer = time.perf_counter() - t0
+            bl = self._init()
+            t0 = time.perf_counter()
+            lp, ids = self._head.compute_level(self._hidden, 1)
+            c = min(2 * self.beam, int(lp.shape[1]))
+            vals, idx = torch.topk(lp, c, dim=-1, largest=True, sorted=True)
+            self._expand_step(bl, ids[idx], vals, self.beam, valid_path=self._trie)
+            t_head = time.perf_counter() - t0
+        per_request_step = t_layer * self.layers * (self.beam / self.rows) + t_head
+        desc = (f"reference engine (torch CPU branch, {self.cores} threads): Qwen3DecoderLayer.forward of 1 layer for "
+                f"{self.rows} beam rows over a 256-token prompt {t_layer:.2f}s, x {self.layers} layers x "
+                f"{self.beam}/{self.rows} rows (extrapolated); RestrictedLMHead.compute_level + top-{c} + expand_step "
+                f"with the CSR trie ({self.catalog_items} items) for one request of {self.beam} beams {t_head:.2f}s; "
+                "rotation from the oracle (the reference's torch RoPE raises on a CPU)")
+        return self.beam / per_request_step, desc
+
+
+def cpu_baseline_port(beam: int, sizes, items: int, layers: int, budget_rows: int = 64):
+    """The oracle's restatement of one decode step on the host cores, used when the reference install is
+    not there: `budget_rows` beam rows of one request (prompt 256) through ONE
     decoder layer, one SID head level and one beam step; the layer time is
     multiplied by the layer count. Returns (beam_rows_per_s, cores, description)."""
     import numpy as np
@@ -191,32 +329,63 @@ def cpu_baseline(beam: int, sizes, items: int, layers: int, budget_rows: int = 6
     head_and_step(h)
     t_head = time.perf_counter() - t0
     per_step = t_layer * layers + t_head
-    desc = (f"{rows} beam rows of one request (prompt 256): 1 decoder layer timed {t_layer:.3f}s x {layers} layers "
-            f"(extrapolated) + head level and beam step {t_head:.3f}s; float64-accumulating oracle port")
+    desc = (f"oracle port: {rows} beam rows of one request (prompt 256): 1 decoder layer timed {t_layer:.3f}s x {layers} "
+            f"layers (extrapolated) + head level and beam step {t_head:.3f}s")
     return rows / per_step, cores, desc
 
 
 def run_reference_arm(args):
+    """``--impl reference``: rank 0 alone times the reference's CPU implementation of the step; each step is
+    one bounded sample (see ReferenceCpuStep)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     sizes = [8192] * 3
-    vals = []
+    ref = ReferenceCpuStep(args.beam, sizes, args.items, args.layers)
+    for _ in range(max(0, min(args.warmup, 1))):
+        ref.sample()
+    vals, desc = [], ""
+    t0 = time.perf_counter()
     for _ in range(max(1, min(args.steps, 3))):
-        v, cores, desc = cpu_baseline(args.beam, sizes, args.items, args.layers)
+        v, desc = ref.sample()
         vals.append(v)
+    wall = time.perf_counter() - t0
     v = statistics.median(vals)
     line = {
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "fp8_e4m3 x fp8_e4m3 -> f32", "data": "synthetic", "config": WORKLOAD,
-        "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
+        "warmup": args.warmup, "ms_per_step": wall / len(vals) * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> bf16 on the host (torch)", "data": "synthetic",
+        "config": bench_config(args, max(args.gpus, 1), args.requests * args.beam, None, len(sizes)),
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": ref.cores, "kind": ref.kind, "sample": desc,
+                         "samples_timed": len(vals)},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
     }
     print(json.dumps(line))
 
 
 # ---------------------------------------------------------------------------
+def dram_traffic_of_dominant_kernel(rows: int):
+    """DRAM bytes per launch of the dominant kernel, from the text summary of its ncu capture (the
+    ``dram__bytes_read.sum`` / ``dram__bytes_write.sum`` rows of one launch at 16384 rows), scaled by the row
+    count. ``None`` when no capture summary is present: the number is never made up."""
+    import re
+
+    src = ROOT / "profiles" / "gate_up_gemm_dram_traffic.txt"
+    if not src.exists():
+        return None, "no ncu capture summary found"
+    vals = {}
+    for line in src.read_text().splitlines():
+        m = re.match(r"\s*(dram__bytes_(?:read|write)\.sum)\s+([0-9.eE+]+)\s*(\w*)", line)
+        if m:
+            mult = {"": 1.0, "byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}.get(m.group(3), 1.0)
+            vals[m.group(1)] = float(m.group(2)) * mult
+    if len(vals) != 2:
+        return None, "ncu capture summary unreadable"
+    return sum(vals.values()) * rows / 16384.0, ("ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at "
+                                                  "M=16384 (capture summary under profiles/), scaled to this row count")
+
+
 def time_gemms(torch, rows: int, iters: int = 10):
     """FP8 GEMM roofline figures, timed alone with CUDA events on the launch stream:
     (a) the dominant kernel of the wave, the gate_up GEMM with the SwiGLU epilogue, at the
@@ -627,9 +796,7 @@ def main():
         bf16_burst = float(peaks.get("bf16_tflops", 1590.0))
         peak_fp8 = 2.0 * bf16_burst
         achieved = fused_flops / fused_sec / 1e12
-        # DRAM bytes of one launch of this kernel at M = 16384 from the ncu capture summarised in
-        # profiles/gemm_fp8_gate_up_M16384.md (68.0 MB read + 166.7 MB written), scaled by the rows
-        traffic = (68.0e6 + 166.7e6) * eng.rows / 16384.0
+        traffic, traffic_src = dram_traffic_of_dominant_kernel(eng.rows)
         roof = {
             "bound": "tensor", "achieved": achieved, "peak": peak_fp8, "unit": "TFLOP/s",
             "frac": achieved / peak_fp8, "traffic": traffic,
@@ -638,25 +805,24 @@ def main():
             "us_per_launch": fused_sec * 1e6,
             "peak_source": ("2 x measured bf16 burst (MEASURED_PEAKS.json)" if peaks else "2 x fallback 1.59 PFLOP/s")
             + "; nominal dense FP8 4500",
-            "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch at M=16384 "
-                              "(profiles/gemm_fp8_gate_up_M16384.md), scaled to this row count",
+            "traffic_source": traffic_src,
             "layer_gemms_tflops": flops / gsec / 1e12,
             "layer_gemms": "plain qkv+o+gate_up+down at M=%d, 4 launches back to back" % eng.rows,
             "cublaslt_fp8_tflops_same_shapes": lib_tf,
         }
         cpu = None
-        if not args.no_cpu_baseline:
-            v, cores, desc = cpu_baseline(args.beam, sizes, args.items, args.layers)
-            cpu = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc}
+        if not args.no_cpu_baseline and world == 1:
+            # one bounded sample on the host cores; only in the single-process run, where nothing else loads them
+            ref = ReferenceCpuStep(args.beam, sizes, args.items, args.layers)
+            v, desc = ref.sample()
+            cpu = {"value": v, "unit": UNIT, "cores": ref.cores, "kind": ref.kind, "sample": desc}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": sec / args.steps * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> f32 (bf16 activations)",
             "data": "synthetic",
-            "config": dict(WORKLOAD, requests=args.requests, beam_width=args.beam, layers=args.layers,
-                           catalog_items=int(arrays.n_items), trie=args.trie, parallelism=f"dp{world}",
-                           rows_per_gpu=eng.rows, value_per_gpu=value / world,
-                           decode_steps_per_wave=eng.steps - eng.first_step),
+            "config": bench_config(args, world, eng.rows, int(arrays.n_items), eng.steps - eng.first_step,
+                                   value / world),
             "clocks": clk.summary(),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": sec_e2e / args.steps * 1e3},
