@@ -66,6 +66,10 @@ def parse():
     ap.add_argument("--attn-compare", action="store_true",
                     help="time one layer's decode attention on the bench's slot lists beside FlashInfer's paged "
                          "decode kernel (a library comparison) and exit")
+    ap.add_argument("--ref-kernels", type=int, default=0, metavar="ROWS",
+                    help="time the reference's own GPU kernels for this path (its Triton kernels and its beam_trie CUDA "
+                         "source JIT-built through tvm_ffi, from the install under oracle/_ref) beside this library's at "
+                         "ROWS rows and exit")
     ap.add_argument("--profile-prefill", action="store_true",
                     help="run one prefill pass between cudaProfilerStart/Stop and exit (for ncu --profile-from-start off)")
     ap.add_argument("--profile-wave", action="store_true",
@@ -549,6 +553,135 @@ def profile_kernels(rows: int):
     print(json.dumps({"profiled": "kernels", "rows": rows}))
 
 
+def ref_kernels_compare(rows: int):
+    """The reference's own GPU kernels for this path beside this library's, same inputs, same harness (20
+    launches per CUDA graph, two replays timed with CUDA events; outputs allocated inside the graph by both
+    sides, as their wrappers do). The reference comes unmodified from ``oracle/_ref``: its Triton kernels
+    (kernel/rms_fp8.py:29-61, silu_fp8.py:29-72, qk_rope_kv.py:28-155, attention/kv_indices.py:20-42), its torch
+    branch where it has no kernel of its own (``per_token_quant_fp8`` without sgl-kernel), and
+    ``kernel/csrc/beam_trie.cuh`` JIT-built through tvm_ffi. Prints one JSON line; an entry the box cannot run
+    is recorded as unavailable with the error."""
+    import numpy as np
+    import torch
+
+    if str(REF_DIR) not in sys.path:
+        sys.path.insert(0, str(REF_DIR))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    fp8 = torch.float8_e4m3fn
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def graph_us(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(20):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        g.replay()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / 40
+
+    out = {}
+
+    def compare(name, mine, theirs, nbytes):
+        rec = {"algorithmic_bytes": nbytes}
+        try:
+            rec["this_library_us"] = round(graph_us(mine), 2)
+            rec["this_library_GBps"] = round(nbytes / rec["this_library_us"] / 1e3, 1)
+        except Exception as exc:
+            rec["this_library_error"] = repr(exc)[:200]
+        try:
+            rec["reference_us"] = round(graph_us(theirs), 2)
+            rec["reference_GBps"] = round(nbytes / rec["reference_us"] / 1e3, 1)
+        except Exception as exc:
+            rec["reference_unavailable"] = "unavailable on this box: " + repr(exc)[:200]
+        out[name] = rec
+
+    import flashrec_b200.attention as b_att
+    import flashrec_b200.kernel.beam_trie as b_trie
+    import flashrec_b200.kernel.qk_rope_kv as b_rope
+    import flashrec_b200.kernel.rms_fp8 as b_rms
+    import flashrec_b200.kernel.sglops as b_sgl
+    import flashrec_b200.kernel.silu_fp8 as b_silu
+
+    try:
+        import flashrec.attention.kv_indices as r_kvi
+        import flashrec.kernel.beam_trie as r_trie
+        import flashrec.kernel.qk_rope_kv as r_rope
+        import flashrec.kernel.rms_fp8 as r_rms
+        import flashrec.kernel.sglops as r_sgl
+        import flashrec.kernel.silu_fp8 as r_silu
+    except Exception as exc:
+        print(json.dumps({"ref_kernels_rows": rows, "reference_unavailable": "unavailable on this box: " + repr(exc)[:300]}))
+        return
+
+    H, I, HQ, HKV, D = 2048, 6144, 16, 8, 128
+    x = torch.randn(rows, H, device=dev).bfloat16()
+    res = torch.randn(rows, H, device=dev).bfloat16()
+    w = torch.ones(H, device=dev).bfloat16()
+    compare("rmsnorm_per_token_quant_fp8", lambda: b_rms.rmsnorm_per_token_quant_fp8(x, w, 1e-6),
+            lambda: r_rms.rmsnorm_per_token_quant_fp8(x, w, 1e-6), rows * H * 3 + rows * 4)
+    compare("fused_add_rmsnorm_per_token_quant_fp8", lambda: b_rms.fused_add_rmsnorm_per_token_quant_fp8(x, res, w, 1e-6),
+            lambda: r_rms.fused_add_rmsnorm_per_token_quant_fp8(x, res, w, 1e-6), rows * H * 7 + rows * 4)
+    compare("per_token_quant_fp8", lambda: b_sgl.per_token_quant_fp8(x), lambda: r_sgl.per_token_quant_fp8(x),
+            rows * H * 3 + rows * 4)
+    gu = torch.randn(rows, 2 * I, device=dev).bfloat16()
+    compare("silu_and_mul_per_token_quant_fp8", lambda: b_silu.silu_and_mul_per_token_quant_fp8(gu),
+            lambda: r_silu.silu_and_mul_per_token_quant_fp8(gu), rows * (2 * I * 2 + I + 4))
+    qkv = torch.randn(rows, HQ + 2 * HKV, D, device=dev).bfloat16()
+    from flashrec_b200.layers import build_cos_sin_cache
+
+    cs = build_cos_sin_cache(D, 2048, 1e6, device=dev)
+    pos = torch.randint(0, 2048, (rows,), device=dev)
+    loc = torch.arange(1, rows + 1, device=dev)
+    kc = torch.zeros(rows + 16, HKV, D, dtype=torch.uint8, device=dev).view(fp8)
+    vc = torch.zeros_like(kc)
+    hw = torch.ones(D, device=dev).bfloat16()
+    rope_args = (qkv[:, :HQ], qkv[:, HQ:HQ + HKV], qkv[:, HQ + HKV:], pos, loc, hw, hw, 1e-6, cs, kc, vc)
+    compare("fused_qk_norm_rope_store_fp8", lambda: b_rope.fused_qk_norm_rope_store_fp8(*rope_args),
+            lambda: r_rope.fused_qk_norm_rope_store_fp8(*rope_args),
+            rows * ((HQ + 2 * HKV) * D * 2 + HQ * D * 2 + 2 * HKV * D + 16))
+    # slot-list gather: rows x ~600 slots
+    rng = np.random.default_rng(0)
+    lens = torch.from_numpy(rng.integers(128, 1025, max(rows // 512, 1)).repeat(min(rows, 512))[:rows].astype(np.int32)).to(dev)
+    table = torch.randint(1, 60000, (rows, 1040), dtype=torch.int32, device=dev)
+    ridx = torch.arange(rows, device=dev)
+    total = int(lens.sum().item())
+    buf = torch.empty(total, dtype=torch.int32, device=dev)
+    compare("gather_kv_indices", lambda: b_att.gather_kv_indices(table, ridx, lens, out=buf, total=total),
+            lambda: r_kvi.gather_kv_indices(table, ridx, lens, out=buf, total=total), total * 8 + rows * 16)
+    # fused mask + top-k + expand + advance on a dense trie (the reference kernel's limit: 512 beams)
+    n, bw, c, L, vsz, nodes_n = max(rows // 512, 1), min(rows, 512), 128, 3, 192, 4096
+    g = torch.Generator(device=dev).manual_seed(0)
+    allow = (torch.rand(nodes_n + 1, vsz, generator=g, device=dev) > 0.5)
+    nxt = torch.randint(0, nodes_n, (nodes_n + 1, vsz), generator=g, device=dev)
+    cum = torch.randn(n, bw, generator=g, device=dev)
+    lp = torch.sort(torch.randn(n, bw, c, generator=g, device=dev), dim=-1, descending=True).values.contiguous()
+    tok = torch.randint(1000, 1000 + vsz, (n, bw, c), generator=g, device=dev)
+    node = torch.randint(0, nodes_n, (n, bw), generator=g, device=dev)
+    tids = torch.randint(1000, 1000 + vsz, (n, bw, L), generator=g, device=dev)
+    kw = dict(select_k=bw, node_ids=node, allow_table=allow, token_base=1000, token_ids=tids, col=1, next_node=nxt,
+              invalid_node=nodes_n)
+    ws_b, ws_r = b_trie.GenrecFusedWorkspace(), r_trie.GenrecFusedWorkspace()
+    loaded = False
+    try:
+        loaded = bool(r_trie.try_load_beam_trie())
+    except Exception:
+        loaded = False
+    compare("genrec_mask_topk_expand", lambda: b_trie.genrec_mask_topk_expand(cum, lp, tok, workspace=ws_b, **kw),
+            (lambda: r_trie.genrec_mask_topk_expand(cum, lp, tok, workspace=ws_r, **kw)) if loaded else
+            (lambda: (_ for _ in ()).throw(RuntimeError("beam_trie.cuh did not build through tvm_ffi"))),
+            n * bw * c * (4 + 8) * 2)
+    out["genrec_mask_topk_expand"]["shape"] = f"N={n} BW={bw} C={c} dense trie {nodes_n} x {vsz}"
+    print(json.dumps({"ref_kernels_rows": rows, "kernels": out}))
+
+
 def attn_compare(requests: int, beam: int, iters: int = 10):
     """The decode attention of one layer on the bench's slot lists (requests x beam rows, prompts
     U[128,1024] shared by a request's beams, one own slot per row), timed between L2 flushes: this
@@ -642,6 +775,12 @@ def main():
 
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
         gemm_shapes(args.gemm_shapes)
+        return
+    if args.ref_kernels:
+        import torch
+
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        ref_kernels_compare(args.ref_kernels)
         return
     if args.profile_kernels:
         import torch
