@@ -63,6 +63,9 @@ def parse():
                     help="leave the prompt K/V as the synthetic fill instead of running the prefill pass")
     ap.add_argument("--no-fuse-rope-gemm", action="store_true",
                     help="run QK-norm + RoPE + KV write as their own kernel instead of in the qkv GEMM's epilogue")
+    ap.add_argument("--no-fused-head", action="store_true",
+                    help="run the SID head as GEMM -> row statistics -> beam step (fp32 logits in HBM) instead of the "
+                         "fused head call")
     ap.add_argument("--attn-compare", action="store_true",
                     help="time one layer's decode attention on the bench's slot lists beside FlashInfer's paged "
                          "decode kernel (a library comparison) and exit")
@@ -819,7 +822,7 @@ def main():
     arrays = trie.arrays
     eng = SidDecodeEngine(cfg, args.requests, args.beam, prompt_lengths(args.requests, rank), sizes, token_base, trie,
                           dev, shared_prefix=64, page_size=16, seed=rank, fuse_rope_gemm=not args.no_fuse_rope_gemm,
-                          level0_from_prefill=args.level0_from_prefill)
+                          level0_from_prefill=args.level0_from_prefill, fused_head=not args.no_fused_head)
     # Prefill of the prompts (eager, one extend batch): the decode waves below then read real K/V. Timed on
     # its own; it is not part of `value` (the metric is the decode step).
     prefill = None
@@ -865,6 +868,8 @@ def main():
     import flashrec_b200.sid_decode as m_sid
 
     mods = [m_att, m_dec, m_rope, m_rms, m_sgl, m_silu, m_log, m_sid]
+    # (the fused head call: row-mask pass for CSR tries + GEMM + statistics combine + beam step)
+    kernels_per_call["fr_sid_head_topk"] = 3 if args.trie == "bitmap" else 4
     for m in mods:
         m.call = counting_call
     eng.run(host_io=False, _eager=True)

@@ -23,6 +23,7 @@
 // replaces the reference's K serial block-wide arg-max rounds and has no 512
 // limit on beam width.
 #include "fr_common.cuh"
+#include "sid_head.cuh"
 #include "topk_select.cuh"
 
 namespace fr {
@@ -202,6 +203,10 @@ struct StepParams {
   int64_t level_tok_base;   // token id of code 0 of this level
   int64_t idx_base;         // added to c when forming the flat index (token-range shards)
   int64_t idx_width;        // C used in the flat index (whole level width)
+  // compact candidates written by the head GEMM's epilogue: {logit bits, flat index} per record
+  const uint2* cand;        // [N, cand_cap]
+  const int* cand_count;    // [N]
+  int cand_cap;
   Trie trie;
   int N, BW, C, K, L;
   int apply_mask, apply_expand, apply_advance;
@@ -214,10 +219,24 @@ using topk::SelectSmem;
 // Candidate enumeration. Calls f(composite) for every live candidate of request n.
 // `rng` (FULL + CSR trie): per beam the [first, last) positions of its node's edges in the sorted
 // key array, found once per launch; a negative first position means "no range, scan the level".
-template <bool FULL, class F>
+// MODE 0: explicit candidates (lp / tok); 1: every code of the level, read from the logits matrix;
+// 2: the compact candidate records the head GEMM's epilogue emitted (already trie-legal).
+template <int MODE, class F>
 __device__ __forceinline__ void for_each_candidate(const StepParams& p, int n, bool masked, const int64_t* rng,
                                                    F&& f) {
-  if constexpr (!FULL) {
+  constexpr bool FULL = MODE == 1;
+  if constexpr (MODE == 2) {
+    const uint2* cn = p.cand + static_cast<size_t>(n) * p.cand_cap;
+    const int cnt = min(p.cand_count[n], p.cand_cap);
+    const size_t row0 = static_cast<size_t>(n) * p.BW;
+    for (int i = threadIdx.x; i < cnt; i += kThreads) {
+      const uint2 rec = cn[i];
+      const uint32_t b = rec.y / static_cast<uint32_t>(p.idx_width);
+      const size_t row = row0 + b;
+      const float s = __fadd_rn(p.cum[row], __fsub_rn(__fsub_rn(__uint_as_float(rec.x), p.row_max[row]), p.row_logsum[row]));
+      if (s != p.neg_inf) f(compose(s, rec.y));
+    }
+  } else if constexpr (!FULL) {
     const uint32_t M = static_cast<uint32_t>(p.BW) * p.C;
     const float* cum_n = p.cum + static_cast<size_t>(n) * p.BW;
     if (masked) {
@@ -309,8 +328,9 @@ __device__ __forceinline__ void apply_winners(const StepParams& p, int n, const 
   }
 }
 
-template <bool FULL>
+template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1) beam_step_kernel(StepParams p) {
+  constexpr bool FULL = MODE != 0;  // the winners' tokens follow from the flat index over the level
   extern __shared__ __align__(16) uint8_t dyn[];
   __shared__ SelectSmem sm;
   const int n = blockIdx.x;
@@ -343,7 +363,7 @@ __global__ void __launch_bounds__(kThreads, 1) beam_step_kernel(StepParams p) {
     }
   }
 
-  if constexpr (FULL) {
+  if constexpr (MODE == 1) {
     if (p.trie.kind == FR_TRIE_CSR) {
       // every enumeration pass below walks the beams' edge lists: find each list once (one
       // binary-search pair per thread, all beams in parallel) instead of once per pass and warp
@@ -366,7 +386,7 @@ __global__ void __launch_bounds__(kThreads, 1) beam_step_kernel(StepParams p) {
 
   // ---- select + sort ---------------------------------------------------------
   const int nvalid = topk::radix_select_topk<kThreads>(
-      [&](auto&& f) { for_each_candidate<FULL>(p, n, masked, rng, f); }, p.K, win, kp2, sm);
+      [&](auto&& f) { for_each_candidate<MODE>(p, n, masked, rng, f); }, p.K, win, kp2, sm);
 
   // ---- outputs ---------------------------------------------------------------
   const int64_t* tok_n = FULL ? nullptr : p.tok + static_cast<size_t>(n) * M;
@@ -525,10 +545,10 @@ static size_t step_smem(int K, int BW, bool edge_ranges) {
   return b + 16;
 }
 
-template <bool FULL>
+template <int MODE>
 static int launch_step(const StepParams& p, cudaStream_t stream) {
-  const size_t smem = step_smem(p.K, p.BW, FULL && p.trie.kind == FR_TRIE_CSR);
-  auto kern = beam_step_kernel<FULL>;
+  const size_t smem = step_smem(p.K, p.BW, MODE == 1 && p.trie.kind == FR_TRIE_CSR);
+  auto kern = beam_step_kernel<MODE>;
   if (smem > 32 * 1024) {  // static shared memory counts towards the 48 KiB default limit
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
       return FR_ERR_CUDA;
@@ -622,7 +642,7 @@ extern "C" int fr_mask_topk_expand(float* out_vals, int64_t* out_parents, int64_
   if (st != FR_OK) return st;
   FR_CHECK_ARG(top_logprobs && top_tokens);
   if (p.apply_mask) FR_CHECK_ARG(scratch);
-  return launch_step<false>(p, stream);
+  return launch_step<0>(p, stream);
 }
 
 extern "C" int fr_sid_beam_step(float* out_vals, int64_t* out_parents, int64_t* out_tokens, int64_t* out_indices,
@@ -650,7 +670,7 @@ extern "C" int fr_sid_beam_step(float* out_vals, int64_t* out_parents, int64_t* 
   if (st != FR_OK) return st;
   FR_CHECK_ARG(logits && row_max && row_logsum && ld >= level_width);
   FR_CHECK_ARG(p.trie.kind == FR_TRIE_NONE || node_in);
-  return launch_step<true>(p, stream);
+  return launch_step<1>(p, stream);
 }
 
 extern "C" int fr_topk_merge_shards(float* out_vals, int64_t* out_parents, int64_t* out_tokens, int64_t* out_indices,
@@ -693,6 +713,166 @@ extern "C" int fr_topk_merge_shards(float* out_vals, int64_t* out_parents, int64
   }
   merge_shards_kernel<<<N, kThreads, smem, stream>>>(mp);
   return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Fused SID head: logits GEMM -> (tile statistics, legal candidates) -> top-K, without the logits matrix.
+// ---------------------------------------------------------------------------
+namespace fr {
+namespace beam {
+
+// Row masks over the codes of the level shard for tries whose layout the GEMM epilogue cannot index by node
+// (sorted-key CSR, the reference's dense byte table, a bitmap whose level is not word-aligned with the shard):
+// mask[row, c >> 5] bit (c & 31) = code c of the shard is a legal continuation of the row's node. One warp per
+// row; `mask` must be zero on entry. Dead rows (cum == -inf) stay zero.
+__global__ void __launch_bounds__(256) row_mask_kernel(uint32_t* __restrict__ mask, int words, const float* __restrict__ cum,
+                                                      const int64_t* __restrict__ node_in, Trie tr, int64_t first_tok,
+                                                      int C, int rows) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  if (cum[row] == -INFINITY) return;
+  const int64_t node = node_in ? node_in[row] : -1;
+  uint32_t* m = mask + static_cast<size_t>(row) * words;
+  if (tr.kind == FR_TRIE_CSR && node >= 0) {
+    if (tr.n_edges <= 0) return;
+    const int64_t k0 = node * tr.vsz + (first_tok - tr.token_base);
+    const int64_t e0 = lower_bound(tr.keys, tr.n_edges, k0);
+    const int64_t e1 = lower_bound(tr.keys, tr.n_edges, k0 + C);
+    for (int64_t e = e0 + lane; e < e1; e += 32) {
+      const int64_t c = __ldg(tr.keys + e) - k0;
+      atomicOr(m + (c >> 5), 1u << (c & 31));
+    }
+    return;
+  }
+  for (int c0 = 0; c0 < C; c0 += 32) {
+    const int c = c0 + lane;
+    const bool ok = c < C && trie_allowed(tr, node, first_tok + c);
+    const uint32_t w = __ballot_sync(0xffffffffu, ok);
+    if (lane == 0) m[c0 >> 5] = w;
+  }
+}
+
+__global__ void tile_stats_combine_kernel(const float* __restrict__ tmax, const float* __restrict__ tlog,
+                                          float* __restrict__ row_max, float* __restrict__ row_logsum, int tiles, int rows) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  float mx, ls;
+  lse_combine(tmax + r, tlog + r, tiles, rows, mx, ls);
+  row_max[r] = mx;
+  row_logsum[r] = ls;
+}
+
+struct HeadWorkspace {
+  float* tile_max;
+  float* tile_logsum;
+  float* row_max;
+  float* row_logsum;
+  int* cand_count;
+  uint2* cand;
+  uint32_t* row_mask;
+  int64_t bytes;
+};
+
+static int64_t align256(int64_t x) { return (x + 255) / 256 * 256; }
+
+// Carves the workspace; base may be null to compute the size only. needs_row_mask: every trie but an aligned bitmap.
+static HeadWorkspace head_workspace(void* base, int N, int BW, int level_width, int cand_cap, bool needs_row_mask) {
+  const int64_t rows = static_cast<int64_t>(N) * BW;
+  const int64_t tiles = (level_width + 255) / 256;
+  const int64_t words = (level_width + 31) / 32;
+  uint8_t* p = static_cast<uint8_t*>(base);
+  int64_t off = 0;
+  HeadWorkspace w{};
+  auto take = [&](int64_t bytes) { void* q = p ? p + off : nullptr; off += align256(bytes); return q; };
+  w.tile_max = static_cast<float*>(take(tiles * rows * 4));
+  w.tile_logsum = static_cast<float*>(take(tiles * rows * 4));
+  w.row_max = static_cast<float*>(take(rows * 4));
+  w.row_logsum = static_cast<float*>(take(rows * 4));
+  w.cand_count = static_cast<int*>(take(static_cast<int64_t>(N) * 4));
+  w.cand = static_cast<uint2*>(take(static_cast<int64_t>(N) * cand_cap * 8));
+  w.row_mask = needs_row_mask ? static_cast<uint32_t*>(take(rows * words * 4)) : nullptr;
+  w.bytes = off;
+  return w;
+}
+
+}  // namespace beam
+}  // namespace fr
+
+extern "C" int64_t fr_sid_head_topk_workspace_bytes(int N, int BW, int level_width, int cand_capacity) {
+  if (N < 0 || BW <= 0 || level_width <= 0 || cand_capacity < 0) return -1;
+  return head_workspace(nullptr, N, BW, level_width, cand_capacity, true).bytes;
+}
+
+extern "C" int fr_sid_head_topk(float* out_vals, int64_t* out_parents, int64_t* out_tokens, int64_t* out_indices,
+                                int64_t* out_child, const void* a, const float* scale_a, int64_t lda, const void* w,
+                                const float* scale_w, int64_t ldw, int K_dim, const float* cum, const int64_t* node_in,
+                                const int64_t* token_ids_in, int64_t* token_ids_out, int64_t* node_ids_out,
+                                const uint8_t* do_expand, const int32_t* col_n, const fr_trie* trie,
+                                int64_t level_tok_base, int64_t idx_base, int64_t idx_width, int N, int BW,
+                                int level_width, int K, int L, int apply_expand, int apply_advance, int phase,
+                                float* row_max, float* row_logsum, void* workspace, int64_t workspace_bytes,
+                                int cand_capacity, cudaStream_t stream) {
+  FR_CHECK_ARG(N >= 0 && BW > 0 && level_width > 0 && K > 0 && L >= 0 && K_dim > 0 && cand_capacity > 0);
+  FR_CHECK_ARG(phase >= 0 && phase <= 2);
+  if (N == 0) return FR_OK;
+  FR_CHECK_SUPPORTED(BW % 32 == 0 && idx_base % 32 == 0);
+  FR_CHECK_ARG(workspace && aligned16(workspace) && cum);
+  StepParams p{};
+  p.out_vals = out_vals; p.out_parents = out_parents; p.out_tokens = out_tokens; p.out_indices = out_indices;
+  p.out_child = out_child; p.token_ids_out = token_ids_out; p.node_ids_out = node_ids_out;
+  p.cum = cum; p.node_in = node_in; p.token_ids_in = token_ids_in; p.do_expand = do_expand; p.col_n = col_n;
+  p.level_tok_base = level_tok_base; p.idx_base = idx_base; p.idx_width = idx_width > 0 ? idx_width : level_width;
+  p.N = N; p.BW = BW; p.C = level_width; p.K = K; p.L = L;
+  p.apply_mask = 1; p.apply_expand = apply_expand; p.apply_advance = apply_advance && apply_expand;
+  p.neg_inf = -INFINITY;
+  int st = make_trie(trie, &p.trie);
+  if (st != FR_OK) return st;
+  FR_CHECK_ARG(p.trie.kind == FR_TRIE_NONE || node_in);
+  if (p.trie.kind == FR_TRIE_NONE) { p.trie.vsz = 1; p.trie.token_base = 0; }
+  const int64_t first_tok = level_tok_base + idx_base;
+  // a bitmap trie is read in place when its rows line up with the shard's 32-code words
+  const bool direct_bitmap = p.trie.kind == FR_TRIE_BITMAP && static_cast<int64_t>(p.trie.words) * 32 >= idx_base + level_width;
+  const HeadWorkspace ws = head_workspace(workspace, N, BW, level_width, cand_capacity, !direct_bitmap);
+  FR_CHECK_ARG(workspace_bytes >= ws.bytes);
+  const int rows = N * BW;
+  const int tiles = (level_width + 255) / 256;
+  const int words = (level_width + 31) / 32;
+  float* mx = row_max ? row_max : ws.row_max;
+  float* ls = row_logsum ? row_logsum : ws.row_logsum;
+  if (phase == 0 || phase == 1) {
+    FR_CHECK_ARG(a && scale_a && w && scale_w && aligned16(a) && aligned16(w));
+    FR_CHECK_ARG(lda >= K_dim && ldw >= K_dim && lda % 16 == 0 && ldw % 16 == 0 && K_dim % 16 == 0);
+    if (cudaMemsetAsync(ws.cand_count, 0, static_cast<size_t>(N) * 4, stream) != cudaSuccess) return FR_ERR_CUDA;
+    HeadEpi hp{};
+    hp.tile_max = ws.tile_max; hp.tile_logsum = ws.tile_logsum; hp.cum = cum;
+    hp.cand = ws.cand; hp.cand_count = ws.cand_count; hp.cand_cap = cand_capacity; hp.BW = BW;
+    hp.idx_base = idx_base; hp.idx_width = p.idx_width;
+    if (direct_bitmap) {
+      hp.mask = p.trie.bitmap; hp.mask_index = node_in; hp.level_off = p.trie.level_off;
+      hp.mask_stride = p.trie.words; hp.mask_rows = p.trie.n_rows; hp.mask_word0 = static_cast<int>(idx_base / 32);
+      hp.level_off_expected = static_cast<int>(level_tok_base - p.trie.token_base);
+    } else {
+      if (cudaMemsetAsync(ws.row_mask, 0, static_cast<size_t>(rows) * words * 4, stream) != cudaSuccess) return FR_ERR_CUDA;
+      row_mask_kernel<<<ceil_div(rows, 8), 256, 0, stream>>>(ws.row_mask, words, cum, p.trie.kind == FR_TRIE_NONE ? nullptr : node_in,
+                                                            p.trie, first_tok, level_width, rows);
+      if (launch_status() != FR_OK) return FR_ERR_CUDA;
+      hp.mask = ws.row_mask; hp.mask_index = nullptr; hp.level_off = nullptr;
+      hp.mask_stride = words; hp.mask_rows = rows; hp.mask_word0 = 0; hp.level_off_expected = 0;
+    }
+    st = launch_head_gemm(a, w, scale_a, scale_w, rows, level_width, K_dim, lda, ldw, hp, stream);
+    if (st != FR_OK) return st;
+    tile_stats_combine_kernel<<<ceil_div(rows, 256), 256, 0, stream>>>(ws.tile_max, ws.tile_logsum, mx, ls, tiles, rows);
+    if (launch_status() != FR_OK) return FR_ERR_CUDA;
+    if (phase == 1) return FR_OK;
+  } else {
+    FR_CHECK_ARG(row_max && row_logsum);  // the statistics of the whole row, combined by the caller
+  }
+  st = check_step_common(p);
+  if (st != FR_OK) return st;
+  p.row_max = mx; p.row_logsum = ls;
+  p.cand = ws.cand; p.cand_count = ws.cand_count; p.cand_cap = cand_capacity;
+  return launch_step<2>(p, stream);
 }
 
 // ---------------------------------------------------------------------------

@@ -24,6 +24,7 @@
 #include <stdlib.h>
 
 #include "fr_common.cuh"
+#include "sid_head.cuh"
 #include "sm100_ptx.cuh"
 
 namespace fr {
@@ -430,7 +431,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                      const __grid_constant__ CUtensorMap tmap_out, const float* __restrict__ scale_a,
                      const float* __restrict__ scale_b, const __nv_bfloat16* __restrict__ bias, int M, int N, int K,
                      unsigned int* __restrict__ row_amax, const uint16_t* __restrict__ silu_table, const QkvRope rp,
-                     int* status) {
+                     const HeadEpi hp, int* status) {
   using C = PairCfg<EPI>;
   constexpr int BLOCK_N = C::kBlockN;
   constexpr int kEpiThreads = EpiCfg<EPI>::kEpiThreads;
@@ -824,6 +825,104 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             }
           }
         }
+      } else if constexpr (EPI == 4) {
+        // SID head: row statistics of the tile + the allowed codes' logits; nothing else leaves the SM
+        const bool row_ok = row < M;
+        const int n_valid = N - n0;  // codes of this tile that exist (the last tile of a level may be short)
+        bool live = false;
+        int64_t midx = row;
+        if (row_ok) {
+          live = __ldg(hp.cum + row) != -INFINITY;
+          if (hp.mask_index != nullptr) midx = __ldg(hp.mask_index + row);
+        }
+        bool all_codes = false, no_codes = !live;
+        if (live && hp.mask_index != nullptr) {
+          if (midx < 0) all_codes = true;
+          else if (midx >= hp.mask_rows) no_codes = true;
+          else if (hp.level_off != nullptr && __ldg(hp.level_off + midx) != hp.level_off_expected) no_codes = true;
+        }
+        uint32_t mw[8];
+        int cnt = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint32_t wv = 0u;
+          const int64_t wi = static_cast<int64_t>(hp.mask_word0) + (n0 >> 5) + j;
+          if (all_codes) wv = 0xffffffffu;
+          else if (!no_codes && wi < hp.mask_stride) wv = __ldg(hp.mask + midx * hp.mask_stride + wi);
+          const int left = n_valid - 32 * j;  // valid codes in this word
+          if (left <= 0) wv = 0u;
+          else if (left < 32) wv &= (1u << left) - 1u;
+          mw[j] = wv;
+          cnt += __popc(wv);
+        }
+        // one cursor update per warp: its 32 rows belong to one request (BW is a multiple of 32)
+        int incl = cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int y = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += y;
+        }
+        const int total = __shfl_sync(0xffffffffu, incl, 31);
+        const int req = row_base / hp.BW;
+        int base_pos = 0;
+        if (total > 0) {
+          if (lane == 0) base_pos = atomicAdd(hp.cand_count + req, total);
+          base_pos = __shfl_sync(0xffffffffu, base_pos, 0);
+        }
+        int pos = base_pos + incl - cnt;
+        uint2* cand_req = hp.cand + static_cast<int64_t>(req) * hp.cand_cap;
+        const uint32_t flat0 = static_cast<uint32_t>(static_cast<int64_t>(row - req * hp.BW) * hp.idx_width + hp.idx_base + n0);
+        bool dropped = false;
+        float mx = -INFINITY, sum = 0.f;
+        constexpr float kLog2e = 1.4426950408889634f;
+#pragma unroll
+        for (int c = 0; c < BLOCK_N / 32; ++c) {  // unrolled: mw[] stays in registers
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(taddr_row + c * 32, r);
+          ptx::tmem_ld_wait();
+          if (c == BLOCK_N / 32 - 1) {  // last read of this accumulator buffer by this warp
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(tempty_remote);
+          }
+          const int left = n_valid - 32 * c;
+          float cm = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float t = __fmul_rn(__fmul_rn(__uint_as_float(r[j]), sa), sbs[c * 32 + j]);
+            if (j >= left) t = -INFINITY;
+            r[j] = __float_as_uint(t);
+            cm = fmaxf(cm, t);
+          }
+          if (cm > mx) {  // rescale the running sum to the new maximum
+            sum *= ex2_approx((mx - cm) * kLog2e);  // mx == -inf: sum is 0 and stays 0
+            mx = cm;
+          }
+          if (mx != -INFINITY) {
+            const float off = mx * kLog2e;
+            float part = 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) part += ex2_approx(__fmaf_rn(__uint_as_float(r[j]), kLog2e, -off));
+            sum += part;
+          }
+          const uint32_t bits = mw[c];
+          if (bits != 0u) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if ((bits >> j) & 1u) {
+                if (pos < hp.cand_cap) cand_req[pos] = make_uint2(r[j], flat0 + static_cast<uint32_t>(c * 32 + j));
+                else dropped = true;
+                ++pos;
+              }
+            }
+          }
+        }
+        if (row_ok) {
+          const int64_t o = static_cast<int64_t>(tc.nb) * M + row;
+          hp.tile_max[o] = mx;
+          hp.tile_logsum[o] = logf(sum);  // -inf for a tile without codes
+        }
+        if (dropped && atomicCAS(status, 0, FR_ERR_UNSUPPORTED) == 0) status[1] = 51;
       } else {
         // one 32-column chunk of y per warp and tile: 64-byte rows, 64-byte swizzle
         uint8_t* st = out_stage + ewarp * 2048;
@@ -1214,7 +1313,8 @@ static int launch(const void* a, const void* b, const float* sa, const float* sb
 template <typename OutT, int EPI>
 static int launch_pair(const void* a, const void* b, const float* sa, const float* sb, const void* bias, void* out,
                        int64_t ldo, int M, int N, int K, int64_t lda, int64_t ldb, cudaStream_t stream,
-                       unsigned int* row_amax = nullptr, const QkvRope& rp = QkvRope{}) {
+                       unsigned int* row_amax = nullptr, const QkvRope& rp = QkvRope{},
+                       const HeadEpi& hp = HeadEpi{}) {
   using C = PairCfg<EPI>;
   CUtensorMap ta, tb;
   int st = make_tmap_u8(&ta, a, M, K, lda, kBlockM);
@@ -1223,6 +1323,7 @@ static int launch_pair(const void* a, const void* b, const float* sa, const floa
   if (st != FR_OK) return st;
   CUtensorMap to;
   if (EPI == 1) st = make_tmap_out(&to, out, M, N / 2, ldo, 2, 32);
+  else if (EPI == 4) st = make_tmap_out(&to, hp.tile_max, 32, 32, 32, 4, 32);  // not used by this epilogue; a valid target
   else st = make_tmap_out(&to, out, M, EPI == 3 ? rp.n_q * 128 : N, ldo, static_cast<int>(sizeof(OutT)),
                           128 / static_cast<int>(sizeof(OutT)));
   if (st != FR_OK) return st;
@@ -1248,7 +1349,7 @@ static int launch_pair(const void* a, const void* b, const float* sa, const floa
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   if (cudaLaunchKernelEx(&cfg, kern, ta, tb, to, sa, sb, static_cast<const __nv_bfloat16*>(bias), M, N, K, row_amax,
-                         table, rp, status) != cudaSuccess) {
+                         table, rp, hp, status) != cudaSuccess) {
     cudaGetLastError();
     return FR_ERR_CUDA;
   }
@@ -1332,6 +1433,14 @@ static int launch_splitk(const void* a, const void* b, const float* sa, const fl
 }
 
 }  // namespace gemm
+
+// The head GEMM with the SID-head epilogue (sid_head.cuh); called by fr_sid_head_topk.
+int launch_head_gemm(const void* a, const void* b, const float* sa, const float* sb, int M, int N, int K, int64_t lda,
+                     int64_t ldb, const HeadEpi& hp, cudaStream_t stream) {
+  return gemm::launch_pair<float, 4>(a, b, sa, sb, nullptr, nullptr, 0, M, N, K, lda, ldb, stream, nullptr,
+                                     gemm::QkvRope{}, hp);
+}
+
 }  // namespace fr
 
 using namespace fr;

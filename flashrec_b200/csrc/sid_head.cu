@@ -14,6 +14,7 @@
 // log-prob convention everywhere: lp = (x - max) - log(sum exp(x - max)), the
 // order of operations of a fused CPU log_softmax.
 #include "fr_common.cuh"
+#include "sid_head.cuh"
 #include "topk_select.cuh"
 
 namespace fr {
@@ -92,15 +93,10 @@ __global__ void lse_combine_kernel(const float* __restrict__ smax, const float* 
                                    float* __restrict__ row_max, float* __restrict__ row_logsum, int S, int rows) {
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= rows) return;
-  float mx = -INFINITY;
-  for (int s = 0; s < S; ++s) mx = fmaxf(mx, smax[static_cast<size_t>(s) * rows + r]);
-  float sum = 0.f;
-  for (int s = 0; s < S; ++s) {
-    const size_t o = static_cast<size_t>(s) * rows + r;
-    sum += expf(slog[o] + (smax[o] - mx));  // shard sum rescaled to the global max
-  }
+  float mx, ls;
+  lse_combine(smax + r, slog + r, S, rows, mx, ls);
   row_max[r] = mx;
-  row_logsum[r] = logf(sum);
+  row_logsum[r] = ls;
 }
 
 }  // namespace head

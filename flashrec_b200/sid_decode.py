@@ -24,6 +24,7 @@ from flashrec_b200._lib import call, ptr, stream_ptr
 from flashrec_b200.attention import AttentionBackend, TokenToKVPool, copy_prefill_to_beams_many, kv_table_step
 from flashrec_b200.decoder import ForwardBatch, Qwen3Config, Qwen3ForCausalLM
 from flashrec_b200.kernel.beam_trie import GenrecFusedResult
+from flashrec_b200.kernel.sglops import per_token_quant_fp8
 from flashrec_b200.logits import RestrictedLMHead
 
 _FP8 = torch.float8_e4m3fn
@@ -85,6 +86,85 @@ def sid_beam_step(
     return out
 
 
+class SidHeadWorkspace:
+    """Grow-only device buffer for ``sid_head_topk`` (tile statistics, candidate lists, row masks)."""
+
+    def __init__(self):
+        self.buf: Optional[torch.Tensor] = None
+
+    def get(self, n: int, bw: int, level_width: int, cand_capacity: int, device) -> torch.Tensor:
+        from flashrec_b200._lib import load
+
+        need = int(load().fr_sid_head_topk_workspace_bytes(int(n), int(bw), int(level_width), int(cand_capacity)))
+        if need < 0:
+            raise ValueError("sid_head_topk: bad workspace dimensions")
+        if self.buf is None or self.buf.numel() < need or self.buf.device != torch.device(device):
+            self.buf = torch.empty(need, dtype=torch.uint8, device=device)
+        return self.buf
+
+
+def sid_head_topk(
+    cum: torch.Tensor,
+    hidden_fp8: torch.Tensor,
+    hidden_scale: torch.Tensor,
+    weight_fp8: torch.Tensor,
+    weight_scale: torch.Tensor,
+    node_ids: Optional[torch.Tensor],
+    trie,
+    level_tok_base: int,
+    select_k: int,
+    workspace: SidHeadWorkspace,
+    *,
+    cand_capacity: Optional[int] = None,
+    token_ids_in: Optional[torch.Tensor] = None,
+    token_ids_out: Optional[torch.Tensor] = None,
+    node_ids_out: Optional[torch.Tensor] = None,
+    col: Optional[torch.Tensor] = None,
+    out: Optional[BeamStepOut] = None,
+    idx_base: int = 0,
+    idx_width: int = 0,
+    level: Optional[int] = None,
+    phase: int = 0,
+    row_max: Optional[torch.Tensor] = None,
+    row_logsum: Optional[torch.Tensor] = None,
+) -> BeamStepOut:
+    """The level's head GEMM and the beam step in one call (``fr_sid_head_topk``): the fp32 logits are never
+    written, only per-row statistics and the trie-legal candidates leave the GEMM. ``hidden_fp8`` e4m3
+    ``[N*BW, H]`` with ``hidden_scale`` (``per_token_quant_fp8`` of the final hidden states), ``weight_fp8`` the
+    level's e4m3 head rows ``[K_l, H]`` with ``weight_scale``; the rest as ``sid_beam_step``. ``cand_capacity``:
+    candidate records per request; by default the trie's bound for ``level`` (or beams x level width)."""
+    n, bw = int(cum.shape[0]), int(cum.shape[1])
+    kl, h = int(weight_fp8.shape[0]), int(weight_fp8.shape[1])
+    k = int(select_k)
+    dev = cum.device
+    if cand_capacity is None:
+        if trie is not None and level is not None and hasattr(trie, "candidate_bound"):
+            cand_capacity = trie.candidate_bound(int(level), bw)
+        else:
+            cand_capacity = bw * kl
+    if out is None:
+        out = BeamStepOut(
+            vals=torch.empty((n, k), dtype=torch.float32, device=dev),
+            parents=torch.empty((n, k), dtype=torch.int64, device=dev),
+            tokens=torch.empty((n, k), dtype=torch.int64, device=dev),
+            indices=torch.empty((n, k), dtype=torch.int64, device=dev),
+            child=torch.empty((n, k), dtype=torch.int64, device=dev),
+        )
+    ws = workspace.get(n, bw, kl, cand_capacity, dev)
+    tr = trie.descriptor() if trie is not None else None
+    do_exp = token_ids_in is not None and token_ids_out is not None
+    do_adv = do_exp and node_ids is not None and node_ids_out is not None and trie is not None
+    sa = hidden_scale.reshape(-1)
+    sw = weight_scale.reshape(-1)
+    call("fr_sid_head_topk", ptr(out.vals), ptr(out.parents), ptr(out.tokens), ptr(out.indices), ptr(out.child),
+         ptr(hidden_fp8), ptr(sa), hidden_fp8.stride(0), ptr(weight_fp8), ptr(sw), weight_fp8.stride(0), h, ptr(cum),
+         ptr(node_ids), ptr(token_ids_in), ptr(token_ids_out), ptr(node_ids_out), None, ptr(col),
+         ctypes.byref(tr) if tr is not None else None, int(level_tok_base), int(idx_base), int(idx_width), n, bw, kl, k,
+         int(token_ids_in.shape[2]) if do_exp else 0, int(do_exp), int(do_adv), int(phase), ptr(row_max),
+         ptr(row_logsum), ptr(ws), int(ws.numel()), int(cand_capacity), stream_ptr(dev))
+    return out
+
+
 class SidDecodeEngine:
     """A wave of ``n_requests`` requests x ``beam_width`` beams decoding ``len(sizes)``
     SID levels with a Qwen3-shaped FP8 model. Weights are random (N(0, 0.02)), the
@@ -110,6 +190,7 @@ class SidDecodeEngine:
         keep_prefix: bool = True,
         fuse_rope_gemm: bool = True,
         level0_from_prefill: bool = False,
+        fused_head: bool = True,
     ):
         self.cfg = cfg
         self.device = torch.device(device)
@@ -210,6 +291,11 @@ class SidDecodeEngine:
         self._cum0 = torch.zeros((self.n, 1), dtype=torch.float32, device=dev)
         self._node0 = torch.zeros((self.n, 1), **i64)
         self._tok0 = torch.zeros((self.n, 1, self.steps), **i64)
+        # head GEMM + statistics + trie mask + top-K without the fp32 logits matrix (fr_sid_head_topk); the
+        # three-call flow (GEMM -> row statistics -> beam step) stays as the other branch
+        self.fused_head = bool(fused_head) and trie is not None and self.bw % 32 == 0
+        self.head_ws = SidHeadWorkspace()
+        self.cand_caps = [trie.candidate_bound(l, self.bw) for l in range(self.steps)] if self.fused_head else []
         self.graphs: List[Optional[torch.cuda.CUDAGraph]] = [None] * self.steps
         self.kernel_launches_per_step: List[int] = [0] * self.steps
         self.reset()
@@ -259,11 +345,19 @@ class SidDecodeEngine:
                              kv_indptr=self.kv_indptr)
         self.attn.prepare(batch, reuse_prefix=s > self.first_step)
         hidden = self.model.forward(batch)
-        logits, mx, ls, _ = self.head.logits_level(hidden, s)
         self.col.fill_(s)
-        out = sid_beam_step(self.cum, logits, mx, ls, self.node_planes[src], self.trie, self.level_tok_base[s],
-                            self.bw, token_ids_in=self.tok_planes[src], token_ids_out=self.tok_planes[dst],
-                            node_ids_out=self.node_planes[dst], col=self.col, out=self.outs[s])
+        if self.fused_head:
+            h8, h_scale = per_token_quant_fp8(hidden)
+            out = sid_head_topk(self.cum, h8, h_scale, self.head._level_weights[s], self.head._level_scales[s],
+                                self.node_planes[src], self.trie, self.level_tok_base[s], self.bw, self.head_ws,
+                                cand_capacity=self.cand_caps[s], token_ids_in=self.tok_planes[src],
+                                token_ids_out=self.tok_planes[dst], node_ids_out=self.node_planes[dst], col=self.col,
+                                out=self.outs[s])
+        else:
+            logits, mx, ls, _ = self.head.logits_level(hidden, s)
+            out = sid_beam_step(self.cum, logits, mx, ls, self.node_planes[src], self.trie, self.level_tok_base[s],
+                                self.bw, token_ids_in=self.tok_planes[src], token_ids_out=self.tok_planes[dst],
+                                node_ids_out=self.node_planes[dst], col=self.col, out=self.outs[s])
         # state of the next step (the window remap by out.parents is deferred to its table call, as
         # scheduler.py:1590-1610 defers it)
         self.cum.copy_(out.vals)

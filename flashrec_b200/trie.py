@@ -38,6 +38,7 @@ class TrieArrays:
     edge_rel: np.ndarray        # [E] int64 token - token_base
     edge_child: np.ndarray      # [E] int64 child node id, or -1 for leaves
     n_items: int
+    max_children: Optional[list] = None  # per level: the largest number of children of a node of that depth
 
     @property
     def invalid_node(self) -> int:
@@ -92,16 +93,20 @@ def build_trie_arrays(items: np.ndarray, sizes: Sequence[int], token_base: int) 
         else:
             childs.append(np.full(ck.shape[0], -1, dtype=np.int64))
     cat = lambda xs: np.concatenate(xs) if xs else np.zeros(0, dtype=np.int64)  # noqa: E731
+    edge_parent = cat(parents)
+    deg = np.bincount(edge_parent, minlength=max(n_nodes, 1))
+    max_children = [int(deg[level_start[d]: level_start[d + 1]].max(initial=0)) for d in range(L)]
     return TrieArrays(
         sizes=sizes,
         token_base=int(token_base),
         vsz=int(offs[-1]),
         n_nodes=n_nodes,
         level_start=level_start,
-        edge_parent=cat(parents),
+        edge_parent=edge_parent,
         edge_rel=cat(rels),
         edge_child=cat(childs),
         n_items=n_items,
+        max_children=max_children,
     )
 
 
@@ -156,6 +161,16 @@ class DeviceTrie:
 
     def nbytes(self) -> int:
         return sum(int(v.numel()) * v.element_size() for v in self.tensors.values())
+
+    def candidate_bound(self, level: int, beam_width: int) -> int:
+        """Upper bound on the legal continuations of ``beam_width`` beams at ``level`` (beams of a request sit on
+        distinct nodes): beam_width x the largest fan-out of that depth, never more than the nodes (items, at the
+        last level) one level down, nor than beam_width x the level's width."""
+        a = self.arrays
+        L = len(a.sizes)
+        below = int(a.level_start[level + 2] - a.level_start[level + 1]) if level + 1 < L else int(a.n_items)
+        fan = a.max_children[level] if a.max_children else a.sizes[level]
+        return max(1, min(int(beam_width) * int(fan), max(below, int(fan)), int(beam_width) * int(a.sizes[level])))
 
 
 def trie_to_device(arrays: TrieArrays, layout: str, device) -> DeviceTrie:
@@ -249,9 +264,16 @@ def build_trie_device(items: torch.Tensor, sizes: Sequence[int], token_base: int
     if n == 0:
         level_start[1:] = 1
     empty = np.zeros(0, dtype=np.int64)
+    # the largest fan-out per depth (sizes the candidate lists of the fused head): one more small host read
+    max_children = [0] * depth
+    if n_edges > 0:
+        deg = torch.bincount(keys[:n_edges] // int(sum(sizes)), minlength=max(int(c[1]), 1))
+        max_children = [int(deg[int(level_start[d]): int(level_start[d + 1])].max().item())
+                        if level_start[d + 1] > level_start[d] else 0 for d in range(depth)]
+        del deg
     arrays = TrieArrays(sizes=sizes, token_base=int(token_base), vsz=int(sum(sizes)), n_nodes=int(c[1]),
                         level_start=level_start, edge_parent=empty, edge_rel=empty, edge_child=empty,
-                        n_items=int(c[0]))
+                        n_items=int(c[0]), max_children=max_children)
     if layout == "bitmap":
         rows, words = arrays.n_nodes + 1, (max(sizes) + 31) // 32
         bitmap = torch.empty((rows, words), dtype=torch.int32, device=dev)

@@ -435,6 +435,34 @@ int fr_sid_beam_step(float* out_vals, int64_t* out_parents, int64_t* out_tokens,
                      const fr_trie* trie, int64_t level_tok_base, int64_t idx_base, int64_t idx_width, int N, int BW,
                      int level_width, int K, int L, int apply_expand, int apply_advance, cudaStream_t stream);
 
+/* The SID head of one level and the beam step in one call, without the [N*BW, level_width] fp32 logits
+ * matrix: the head GEMM (a: e4m3 hidden rows [N*BW, K_dim] with per-row scales, w: the level's e4m3 head
+ * rows [level_width, K_dim] with per-channel scales; the arithmetic of fr_gemm_fp8_w8a8 with fp32 output)
+ * keeps, in its epilogue, only (max, log-sum-exp) per row and 256-code tile and the logits of the codes the
+ * row's trie node allows (bitmap tries are indexed by node in the epilogue; for CSR / dense tries a per-row
+ * bit mask is built first); the tile statistics are combined per row (the unmasked normaliser over the whole
+ * level, as logits.py:136-137), and the beam step of fr_sid_beam_step runs over the compact candidate lists.
+ * Winners, scores, planes: bit-identical to fr_gemm_fp8_w8a8 (fp32 out, CTA pairs) -> fr_sid_beam_step given
+ * the same row statistics. BW % 32 == 0, idx_base % 32 == 0.
+ * phase 0: everything. phase 1: GEMM + candidates + row statistics only (row_max / row_logsum, f32 [N*BW],
+ * receive the statistics of this call's codes: a token-range shard exchanges them). phase 2: the beam step
+ * only, on the candidates phase 1 left in the workspace, with row_max / row_logsum given (the statistics of
+ * the whole row). In phase 0 row_max / row_logsum are optional outputs.
+ * workspace: fr_sid_head_topk_workspace_bytes(N, BW, level_width, cand_capacity) bytes, 16-byte aligned;
+ * cand_capacity = candidate records per request (an upper bound on the legal continuations of its live
+ * beams; records beyond it are dropped and the status word gets FR_ERR_UNSUPPORTED, site 51).
+ * Reference: RestrictedLMHead.compute_level (logits.py:118-138) + the expand step
+ * (search/expand.py:240-372, kernel/beam_trie.py:536-684), which materialise the [T, K] fp32 log-probs. */
+int64_t fr_sid_head_topk_workspace_bytes(int N, int BW, int level_width, int cand_capacity);
+int fr_sid_head_topk(float* out_vals, int64_t* out_parents, int64_t* out_tokens, int64_t* out_indices,
+                     int64_t* out_child, const void* a, const float* scale_a, int64_t lda, const void* w,
+                     const float* scale_w, int64_t ldw, int K_dim, const float* cum, const int64_t* node_in,
+                     const int64_t* token_ids_in, int64_t* token_ids_out, int64_t* node_ids_out,
+                     const uint8_t* do_expand, const int32_t* col_n, const fr_trie* trie, int64_t level_tok_base,
+                     int64_t idx_base, int64_t idx_width, int N, int BW, int level_width, int K, int L,
+                     int apply_expand, int apply_advance, int phase, float* row_max, float* row_logsum,
+                     void* workspace, int64_t workspace_bytes, int cand_capacity, cudaStream_t stream);
+
 /* Merge S per-shard sorted winner lists ([S, N, K] values / flat indices /
  * child nodes, e.g. after an all-gather) into the global sorted top-K, then
  * expand / advance as above. S * K <= 16384. trie (optional): with it, the slots

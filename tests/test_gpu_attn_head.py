@@ -594,3 +594,135 @@ def test_fused_step_accepts_sliced_and_narrow_typed_inputs():
                               allow.to(DEV), 10)
     m2 = trie_mask_candidates(sc.to(DEV), tok[0].to(DEV), nodes[0].to(DEV), allow.to(DEV), 10)
     assert torch.equal(m1, m2)
+
+
+def _fused_head_case(layout, seed=0, n=3, bw=64, hidden=256, sizes=(96, 320), n_items=2500):
+    from flashrec_b200.kernel.sglops import per_token_quant_fp8
+    from flashrec_b200.layers import quantize_weight_fp8
+    from flashrec_b200.trie import build_trie_arrays, trie_to_device
+
+    rng = np.random.default_rng(seed)
+    base = 5000
+    items = np.stack([rng.integers(0, s, n_items) for s in sizes], 1)
+    arrays = build_trie_arrays(items, list(sizes), base)
+    trie = None if layout == "none" else trie_to_device(arrays, layout, DEV)
+    g = torch.Generator().manual_seed(seed)
+    kl = sizes[1]
+    w = 0.05 * torch.randn(kl, hidden, generator=g)
+    wq, ws = quantize_weight_fp8(w.to(DEV))
+    h = torch.randn(n * bw, hidden, generator=g).bfloat16().to(DEV)
+    hq, hs = per_token_quant_fp8(h)
+    cum = torch.randn(n, bw, generator=g)
+    cum[:, -5:] = float("-inf")          # dead beams
+    cum[2, 3:] = float("-inf")           # a request with few live beams: fewer candidates than winners
+    n1 = int(arrays.level_start[2] - arrays.level_start[1])
+    nodes = torch.from_numpy(rng.integers(1, 1 + n1, (n, bw)))
+    nodes[0, 1] = -1                     # unconstrained beam: every code is legal
+    nodes[0, 2] = arrays.invalid_node    # no legal continuation
+    toks = torch.from_numpy(rng.integers(base, base + sizes[0], (n, bw, 2)))
+    return arrays, trie, wq, ws, hq, hs, cum.to(DEV), nodes.to(DEV), toks.to(DEV), base + sizes[0], kl
+
+
+@pytest.mark.parametrize("layout", ["csr", "bitmap", "dense", "none"])
+def test_fused_sid_head_equals_gemm_then_statistics_then_beam_step(layout):
+    """fr_sid_head_topk (logits never written: tile statistics + trie-legal candidates out of the GEMM epilogue)
+    against fr_gemm_fp8_w8a8 (fp32) -> fr_sid_beam_step on the same row statistics: every output bit for bit,
+    for every trie layout, with dead, unconstrained and invalid beams, a short last column tile and a request
+    that has fewer candidates than winners; the statistics against fr_logsumexp_rows within 2e-5."""
+    from flashrec_b200._lib import call, ptr, stream_ptr
+    from flashrec_b200.kernel.sglops import fp8_scaled_mm
+    from flashrec_b200.sid_decode import SidHeadWorkspace, sid_beam_step, sid_head_topk
+
+    arrays, trie, wq, ws, hq, hs, cum, nodes, toks, tok_base, kl = _fused_head_case(layout)
+    n, bw = cum.shape
+    k = bw
+    col = torch.full((n,), 1, dtype=torch.int32, device=DEV)
+    mx = torch.empty(n * bw, device=DEV)
+    ls = torch.empty(n * bw, device=DEV)
+    tok_out, node_out = torch.zeros_like(toks), torch.zeros_like(nodes)
+    wsp = SidHeadWorkspace()
+    cap = bw * kl if layout in ("none",) else None
+    fused = sid_head_topk(cum, hq, hs, wq, ws, nodes if trie is not None else None, trie, tok_base, k, wsp,
+                          token_ids_in=toks, token_ids_out=tok_out, node_ids_out=node_out, col=col, level=1,
+                          row_max=mx, row_logsum=ls, cand_capacity=cap if cap else bw * kl)
+    logits = fp8_scaled_mm(hq, wq.t(), hs, ws, torch.float32, block_n=512)
+    mx2, ls2 = torch.empty_like(mx), torch.empty_like(ls)
+    call("fr_logsumexp_rows", ptr(logits), logits.stride(0), ptr(mx2), ptr(ls2), None, 0, n * bw, kl, stream_ptr(DEV))
+    assert torch.equal(mx, mx2) and torch.allclose(ls, ls2, atol=2e-5, rtol=0)
+    tok_ref, node_ref = torch.zeros_like(toks), torch.zeros_like(nodes)
+    ref = sid_beam_step(cum, logits, mx, ls, nodes if trie is not None else None, trie, tok_base, k,
+                        token_ids_in=toks, token_ids_out=tok_ref, node_ids_out=node_ref, col=col)
+    for name in ("vals", "parents", "tokens", "indices", "child"):
+        assert torch.equal(getattr(fused, name), getattr(ref, name)), (layout, name)
+    assert torch.equal(tok_out, tok_ref)
+    if trie is not None:
+        assert torch.equal(node_out, node_ref)
+    assert torch.isfinite(fused.vals[0]).all() and not torch.isfinite(fused.vals[2]).all()
+    # the trie-sized candidate bound is enough (no record dropped: the status word stays clean)
+    if trie is not None:
+        from flashrec_b200 import device_status
+
+        nodes2 = nodes.clone()
+        nodes2[0, 1] = nodes2[0, 0]  # without the unconstrained beam the bound of the trie applies
+        a = sid_head_topk(cum, hq, hs, wq, ws, nodes2, trie, tok_base, k, SidHeadWorkspace(), level=1, row_max=mx,
+                          row_logsum=ls)
+        b = sid_beam_step(cum, logits, mx, ls, nodes2, trie, tok_base, k)
+        assert torch.equal(a.vals, b.vals) and torch.equal(a.indices, b.indices)
+        assert device_status() == (0, 0)
+
+
+def test_fused_sid_head_reports_a_candidate_list_that_is_too_short():
+    from flashrec_b200 import device_status
+    from flashrec_b200.sid_decode import SidHeadWorkspace, sid_head_topk
+
+    arrays, trie, wq, ws, hq, hs, cum, nodes, toks, tok_base, kl = _fused_head_case("csr")
+    assert device_status() == (0, 0)
+    sid_head_topk(cum, hq, hs, wq, ws, nodes, trie, tok_base, 8, SidHeadWorkspace(), cand_capacity=16)
+    assert device_status() == (-2, 51)
+
+
+def test_fused_sid_head_in_two_phases_over_token_range_shards():
+    """The sharded use of the fused head: phase 1 per shard (GEMM on the shard's codes, candidates, shard
+    statistics), statistics combined over the shards, phase 2 per shard with the whole row's statistics, merge —
+    against the unsharded step on the same combined statistics, bit for bit."""
+    import ctypes
+
+    from flashrec_b200._lib import call, ptr, stream_ptr
+    from flashrec_b200.kernel.sglops import fp8_scaled_mm
+    from flashrec_b200.sid_decode import BeamStepOut, SidHeadWorkspace, sid_beam_step, sid_head_topk
+
+    arrays, trie, wq, ws, hq, hs, cum, nodes, toks, tok_base, kl = _fused_head_case("csr", seed=3)
+    n, bw = cum.shape
+    S, wdt = 2, kl // 2
+    assert wdt % 32 == 0
+    smx, sls = torch.empty((S, n * bw), device=DEV), torch.empty((S, n * bw), device=DEV)
+    wss = [SidHeadWorkspace() for _ in range(S)]
+    for s in range(S):
+        sid_head_topk(cum, hq, hs, wq[s * wdt:(s + 1) * wdt], ws.reshape(-1)[s * wdt:(s + 1) * wdt], nodes, trie, tok_base, bw,
+                      wss[s], idx_base=s * wdt, idx_width=kl, phase=1, row_max=smx[s], row_logsum=sls[s],
+                      cand_capacity=bw * wdt)
+    gmx, gls = torch.empty(n * bw, device=DEV), torch.empty(n * bw, device=DEV)
+    call("fr_lse_combine_shards", ptr(smx), ptr(sls), ptr(gmx), ptr(gls), S, n * bw, stream_ptr(DEV))
+    vals = torch.empty((S, n, bw), device=DEV)
+    idx = torch.empty((S, n, bw), dtype=torch.int64, device=DEV)
+    child = torch.empty((S, n, bw), dtype=torch.int64, device=DEV)
+    for s in range(S):
+        o = sid_head_topk(cum, hq, hs, wq[s * wdt:(s + 1) * wdt], ws.reshape(-1)[s * wdt:(s + 1) * wdt], nodes, trie, tok_base,
+                          bw, wss[s], idx_base=s * wdt, idx_width=kl, phase=2, row_max=gmx, row_logsum=gls,
+                          cand_capacity=bw * wdt)
+        vals[s], idx[s], child[s] = o.vals, o.indices, o.child
+    col = torch.full((n,), 1, dtype=torch.int32, device=DEV)
+    m = BeamStepOut(*(torch.empty((n, bw), dtype=dt, device=DEV)
+                      for dt in (torch.float32, torch.int64, torch.int64, torch.int64, torch.int64)))
+    tok_out, node_out = torch.zeros_like(toks), torch.zeros_like(nodes)
+    tr_desc = trie.descriptor()
+    call("fr_topk_merge_shards", ptr(m.vals), ptr(m.parents), ptr(m.tokens), ptr(m.indices), ptr(m.child), ptr(vals),
+         ptr(idx), ptr(child), ptr(nodes), ptr(toks), ptr(tok_out), ptr(node_out), None, ptr(col), ctypes.byref(tr_desc),
+         tok_base, kl, S, n, bw, bw, 2, 1, 1, stream_ptr(DEV))
+    logits = fp8_scaled_mm(hq, wq.t(), hs, ws, torch.float32, block_n=512)
+    tok_ref, node_ref = torch.zeros_like(toks), torch.zeros_like(nodes)
+    full = sid_beam_step(cum, logits, gmx, gls, nodes, trie, tok_base, bw, token_ids_in=toks, token_ids_out=tok_ref,
+                         node_ids_out=node_ref, col=col)
+    for a, b in ((m.vals, full.vals), (m.parents, full.parents), (m.tokens, full.tokens), (m.indices, full.indices),
+                 (m.child, full.child), (tok_out, tok_ref), (node_out, node_ref)):
+        assert torch.equal(a, b)
