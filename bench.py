@@ -66,6 +66,9 @@ def parse():
     ap.add_argument("--no-fused-head", action="store_true",
                     help="run the SID head as GEMM -> row statistics -> beam step (fp32 logits in HBM) instead of the "
                          "fused head call")
+    ap.add_argument("--head-compare", action="store_true",
+                    help="time the SID head + beam step of every level at the bench's sizes, fused call against the "
+                         "three-call flow, CSR and bitmap tries, and exit")
     ap.add_argument("--attn-compare", action="store_true",
                     help="time one layer's decode attention on the bench's slot lists beside FlashInfer's paged "
                          "decode kernel (a library comparison) and exit")
@@ -685,6 +688,84 @@ def ref_kernels_compare(rows: int):
     print(json.dumps({"ref_kernels_rows": rows, "kernels": out}))
 
 
+def head_compare(requests: int, beam: int, items: int, iters: int = 10):
+    """SID head + beam step of each level at the bench's sizes (requests x beam rows, hidden 2048, 3 x 8192
+    codes, the bench's catalog), with the beam state the previous level left: the fused call
+    (``fr_sid_head_topk``: no logits matrix) beside the three-call flow (fp32 logits GEMM -> row statistics ->
+    beam step), for the CSR and the bitmap trie. CUDA events around each flow, a 256 MB buffer rewritten between
+    repetitions, median. Prints one JSON line."""
+    import numpy as np
+    import torch
+
+    from flashrec_b200.kernel.sglops import per_token_quant_fp8
+    from flashrec_b200.layers import quantize_weight_fp8
+    from flashrec_b200.logits import RestrictedLMHead
+    from flashrec_b200.sid_decode import SidHeadWorkspace, sid_beam_step, sid_head_topk
+    from flashrec_b200.trie import build_trie_device
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    sizes, base, hidden = [8192] * 3, 151_936, 2048
+    n, bw = requests, beam
+    cat = torch.from_numpy(np.ascontiguousarray(make_catalog(items, sizes), dtype=np.int32)).to(dev)
+    g = torch.Generator(device=dev).manual_seed(0)
+    wq, wsc = quantize_weight_fp8(torch.randn((sum(sizes), hidden), generator=g, device=dev) * 0.02)
+    head = RestrictedLMHead(list(range(base, base + sum(sizes))))
+    head.bind_quantized(wq, wsc)
+    head.bind_codebook(sizes)
+    hs = [torch.randn((n * bw, hidden), generator=g, device=dev).to(torch.bfloat16) for _ in sizes]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(fn):
+        for _ in range(3):
+            out = fn()
+        torch.cuda.synchronize()
+        ms = []
+        for _ in range(iters):
+            flush.zero_()
+            e0.record()
+            out = fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms.append(e0.elapsed_time(e1))
+        return out, statistics.median(ms) * 1e3
+
+    res = {"head_compare": True, "rows": n * bw, "requests": n, "beam_width": bw, "level_width": sizes[0],
+           "hidden": hidden, "layouts": {}}
+    for layout in ("csr", "bitmap"):
+        trie = build_trie_device(cat, sizes, base, layout=layout)
+        cum = torch.full((n, bw), float("-inf"), device=dev)
+        cum[:, 0] = 0.0
+        nodes = torch.zeros((n, bw), dtype=torch.int64, device=dev)
+        toks = torch.zeros((n, bw, 3), dtype=torch.int64, device=dev)
+        wsp = SidHeadWorkspace()
+        levels = []
+        for lv in range(3):
+            col = torch.full((n,), lv, dtype=torch.int32, device=dev)
+            tok_o, node_o = torch.zeros_like(toks), torch.zeros_like(nodes)
+
+            def unfused():
+                lg, mx, ls, _ = head.logits_level(hs[lv], lv)
+                return sid_beam_step(cum, lg, mx, ls, nodes, trie, base + lv * sizes[0], bw, token_ids_in=toks,
+                                     token_ids_out=tok_o, node_ids_out=node_o, col=col)
+
+            def fused():
+                q, sc = per_token_quant_fp8(hs[lv])
+                return sid_head_topk(cum, q, sc, head._level_weights[lv], head._level_scales[lv], nodes, trie,
+                                     base + lv * sizes[0], bw, wsp, level=lv, token_ids_in=toks, token_ids_out=tok_o,
+                                     node_ids_out=node_o, col=col)
+
+            _, us_u = timed(unfused)
+            out, us_f = timed(fused)
+            levels.append({"level": lv, "three_calls_us": round(us_u, 1), "fused_us": round(us_f, 1),
+                           "candidate_capacity_per_request": trie.candidate_bound(lv, bw),
+                           "live_beams": int(torch.isfinite(cum).sum().item())})
+            cum, nodes, toks = out.vals.clone(), node_o, tok_o
+        res["layouts"][layout] = levels
+        del trie
+    print(json.dumps(res))
+
+
 def attn_compare(requests: int, beam: int, iters: int = 10):
     """The decode attention of one layer on the bench's slot lists (requests x beam rows, prompts
     U[128,1024] shared by a request's beams, one own slot per row), timed between L2 flushes: this
@@ -772,6 +853,12 @@ def main():
 
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
         attn_compare(args.requests, args.beam)
+        return
+    if args.head_compare:
+        import torch
+
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        head_compare(args.requests, args.beam, args.items)
         return
     if args.gemm_shapes:
         import torch

@@ -614,7 +614,7 @@ def _fused_head_case(layout, seed=0, n=3, bw=64, hidden=256, sizes=(96, 320), n_
     hq, hs = per_token_quant_fp8(h)
     cum = torch.randn(n, bw, generator=g)
     cum[:, -5:] = float("-inf")          # dead beams
-    cum[2, 3:] = float("-inf")           # a request with few live beams: fewer candidates than winners
+    cum[2, 2:] = float("-inf")           # a request with few live beams: fewer candidates than winners
     n1 = int(arrays.level_start[2] - arrays.level_start[1])
     nodes = torch.from_numpy(rng.integers(1, 1 + n1, (n, bw)))
     nodes[0, 1] = -1                     # unconstrained beam: every code is legal
