@@ -779,7 +779,7 @@ static int64_t align256(int64_t x) { return (x + 255) / 256 * 256; }
 // Carves the workspace; base may be null to compute the size only. needs_row_mask: every trie but an aligned bitmap.
 static HeadWorkspace head_workspace(void* base, int N, int BW, int level_width, int cand_cap, bool needs_row_mask) {
   const int64_t rows = static_cast<int64_t>(N) * BW;
-  const int64_t tiles = (level_width + 255) / 256;
+  const int64_t tiles = (level_width + 255) / 256 * kHeadParts;  // statistics entries per row
   const int64_t words = (level_width + 31) / 32;
   uint8_t* p = static_cast<uint8_t*>(base);
   int64_t off = 0;
@@ -836,7 +836,7 @@ extern "C" int fr_sid_head_topk(float* out_vals, int64_t* out_parents, int64_t* 
   const HeadWorkspace ws = head_workspace(workspace, N, BW, level_width, cand_capacity, !direct_bitmap);
   FR_CHECK_ARG(workspace_bytes >= ws.bytes);
   const int rows = N * BW;
-  const int tiles = (level_width + 255) / 256;
+  const int tiles = (level_width + 255) / 256 * kHeadParts;
   const int words = (level_width + 31) / 32;
   float* mx = row_max ? row_max : ws.row_max;
   float* ls = row_logsum ? row_logsum : ws.row_logsum;

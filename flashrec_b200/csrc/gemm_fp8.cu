@@ -41,7 +41,7 @@ constexpr int kUmmaK = 32;
 // (each takes one 32-column chunk) so that it still hides under the main loop.
 template <int EPI>
 struct EpiCfg {
-  static constexpr int kWarps = (EPI == 1 || EPI == 3) ? 16 : 4;
+  static constexpr int kWarps = (EPI == 1 || EPI == 3 || EPI == 4) ? 16 : 4;
   static constexpr int kEpiThreads = kWarps * 32;
   static constexpr int kThreads = 64 + kEpiThreads;
 };
@@ -826,7 +826,11 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           }
         }
       } else if constexpr (EPI == 4) {
-        // SID head: row statistics of the tile + the allowed codes' logits; nothing else leaves the SM
+        // SID head: row statistics + the allowed codes' logits; nothing else leaves the SM. The four warps of
+        // a lane quadrant split the tile's 256 codes into four parts of 64 (kHeadParts), each with its own
+        // statistics entry and its own share of the candidate records, so no exchange between warps is needed.
+        constexpr int kChunks = (BLOCK_N / 32) / kSplit;  // 32-code chunks per warp and tile: 2
+        const int cbase = part * kChunks;
         const bool row_ok = row < M;
         const int n_valid = N - n0;  // codes of this tile that exist (the last tile of a level may be short)
         bool live = false;
@@ -841,15 +845,15 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           else if (midx >= hp.mask_rows) no_codes = true;
           else if (hp.level_off != nullptr && __ldg(hp.level_off + midx) != hp.level_off_expected) no_codes = true;
         }
-        uint32_t mw[8];
+        uint32_t mw[kChunks];
         int cnt = 0;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < kChunks; ++j) {
           uint32_t wv = 0u;
-          const int64_t wi = static_cast<int64_t>(hp.mask_word0) + (n0 >> 5) + j;
+          const int64_t wi = static_cast<int64_t>(hp.mask_word0) + (n0 >> 5) + cbase + j;
           if (all_codes) wv = 0xffffffffu;
           else if (!no_codes && wi < hp.mask_stride) wv = __ldg(hp.mask + midx * hp.mask_stride + wi);
-          const int left = n_valid - 32 * j;  // valid codes in this word
+          const int left = n_valid - 32 * (cbase + j);  // valid codes in this word
           if (left <= 0) wv = 0u;
           else if (left < 32) wv &= (1u << left) - 1u;
           mw[j] = wv;
@@ -871,41 +875,44 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         }
         int pos = base_pos + incl - cnt;
         uint2* cand_req = hp.cand + static_cast<int64_t>(req) * hp.cand_cap;
-        const uint32_t flat0 = static_cast<uint32_t>(static_cast<int64_t>(row - req * hp.BW) * hp.idx_width + hp.idx_base + n0);
+        const uint32_t flat0 =
+            static_cast<uint32_t>(static_cast<int64_t>(row - req * hp.BW) * hp.idx_width + hp.idx_base + n0);
         bool dropped = false;
         float mx = -INFINITY, sum = 0.f;
         constexpr float kLog2e = 1.4426950408889634f;
 #pragma unroll
-        for (int c = 0; c < BLOCK_N / 32; ++c) {  // unrolled: mw[] stays in registers
+        for (int cc = 0; cc < kChunks; ++cc) {
+          const int c = cbase + cc;
           uint32_t r[32];
           ptx::tmem_ld_32x32(taddr_row + c * 32, r);
           ptx::tmem_ld_wait();
-          if (c == BLOCK_N / 32 - 1) {  // last read of this accumulator buffer by this warp
+          if (cc == kChunks - 1) {  // last read of this accumulator buffer by this warp
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive_cluster(tempty_remote);
           }
           const int left = n_valid - 32 * c;
-          float cm = -INFINITY;
+          float cm4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             float t = __fmul_rn(__fmul_rn(__uint_as_float(r[j]), sa), sbs[c * 32 + j]);
             if (j >= left) t = -INFINITY;
             r[j] = __float_as_uint(t);
-            cm = fmaxf(cm, t);
+            cm4[j & 3] = fmaxf(cm4[j & 3], t);
           }
+          const float cm = fmaxf(fmaxf(cm4[0], cm4[1]), fmaxf(cm4[2], cm4[3]));
           if (cm > mx) {  // rescale the running sum to the new maximum
             sum *= ex2_approx((mx - cm) * kLog2e);  // mx == -inf: sum is 0 and stays 0
             mx = cm;
           }
           if (mx != -INFINITY) {
             const float off = mx * kLog2e;
-            float part = 0.f;
+            float p4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int j = 0; j < 32; ++j) part += ex2_approx(__fmaf_rn(__uint_as_float(r[j]), kLog2e, -off));
-            sum += part;
+            for (int j = 0; j < 32; ++j) p4[j & 3] += ex2_approx(__fmaf_rn(__uint_as_float(r[j]), kLog2e, -off));
+            sum += (p4[0] + p4[1]) + (p4[2] + p4[3]);
           }
-          const uint32_t bits = mw[c];
+          const uint32_t bits = mw[cc];
           if (bits != 0u) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
@@ -918,9 +925,9 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           }
         }
         if (row_ok) {
-          const int64_t o = static_cast<int64_t>(tc.nb) * M + row;
+          const int64_t o = (static_cast<int64_t>(tc.nb) * kSplit + part) * M + row;
           hp.tile_max[o] = mx;
-          hp.tile_logsum[o] = logf(sum);  // -inf for a tile without codes
+          hp.tile_logsum[o] = logf(sum);  // -inf for a part without codes
         }
         if (dropped && atomicCAS(status, 0, FR_ERR_UNSUPPORTED) == 0) status[1] = 51;
       } else {

@@ -6,7 +6,7 @@
 namespace fr {
 
 // Arguments of the SID-head epilogue (EPI == 4): the fp32 logits tile [rows, 256 codes of one level] is never
-// written. Per row and tile the epilogue keeps the pair (max, log-sum-exp) of the tile's codes and appends the
+// written. Per row and 64 codes the epilogue keeps the pair (max, log-sum-exp) of those codes and appends the
 // logits of the codes the row's trie node allows to the candidate list of the row's request.
 //   row r = beam r % BW of request r / BW; a row is live when cum[r] is not -inf
 //   mask word for codes [32 j, 32 j + 32) of the level shard: mask[idx * mask_stride + mask_word0 + j] with
@@ -16,9 +16,10 @@ namespace fr {
 //   candidate record = {logit bits, flat index beam * idx_width + idx_base + code}, appended at
 //   cand[request * cand_cap + atomicAdd(&cand_count[request], ...)]; records past cand_cap are dropped and the
 //   status word is set.
+constexpr int kHeadParts = 4;  // statistics entries per 256-code tile (one per epilogue warp of a lane quadrant)
 struct HeadEpi {
-  float* tile_max;          // [n_tiles_n, M]
-  float* tile_logsum;       // [n_tiles_n, M]
+  float* tile_max;          // [n_tiles_n * kHeadParts, M]
+  float* tile_logsum;       // [n_tiles_n * kHeadParts, M]
   const float* cum;         // [M]
   const uint32_t* mask;
   const int64_t* mask_index;   // [M] or null
