@@ -55,6 +55,61 @@ logsumexp_kernel(const float* __restrict__ x, int64_t ld, float* __restrict__ ro
   }
 }
 
+// The same statistics for rows that fit the CTA's registers (cols <= 1024 * VPT, cols and ld multiples of 4,
+// 16-byte aligned rows): one pass over HBM with 16-byte loads, the row kept in registers between the maximum,
+// the sum and the optional log-prob write. Same arithmetic per element as logsumexp_kernel; the sum's order
+// differs (it is only compared within a tolerance anywhere).
+template <int VPT>
+__global__ void __launch_bounds__(kThreads)
+logsumexp_vec_kernel(const float* __restrict__ x, int64_t ld, float* __restrict__ row_max, float* __restrict__ row_logsum,
+                     float* __restrict__ lp_out, int64_t ldo, int cols) {
+  __shared__ float red[kThreads / 32];
+  const int row = blockIdx.x;
+  const float4* xr = reinterpret_cast<const float4*>(x + static_cast<int64_t>(row) * ld);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nvec = cols >> 2;
+  float4 v[VPT];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * kThreads;
+    v[i] = idx < nvec ? __ldg(xr + idx) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    mx = fmaxf(mx, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+  }
+  mx = warp_max(mx);
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  mx = red[0];
+#pragma unroll
+  for (int i = 1; i < kThreads / 32; ++i) mx = fmaxf(mx, red[i]);
+  __syncthreads();
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i)
+    sum += (expf(v[i].x - mx) + expf(v[i].y - mx)) + (expf(v[i].z - mx) + expf(v[i].w - mx));  // exp(-inf) = 0
+  sum = warp_sum(sum);
+  if (lane == 0) red[warp] = sum;
+  __syncthreads();
+  sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < kThreads / 32; ++i) sum += red[i];
+  const float ls = logf(sum);
+  if (threadIdx.x == 0) {
+    row_max[row] = mx;
+    row_logsum[row] = ls;
+  }
+  if (lp_out) {
+    float4* o = reinterpret_cast<float4*>(lp_out + static_cast<int64_t>(row) * ldo);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * kThreads;
+      if (idx < nvec)
+        o[idx] = make_float4(__fsub_rn(__fsub_rn(v[i].x, mx), ls), __fsub_rn(__fsub_rn(v[i].y, mx), ls),
+                             __fsub_rn(__fsub_rn(v[i].z, mx), ls), __fsub_rn(__fsub_rn(v[i].w, mx), ls));
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kThreads)
 topk_rows_kernel(const float* __restrict__ x, int64_t ld, const float* __restrict__ row_max,
                  const float* __restrict__ row_logsum, float* __restrict__ vals, int64_t* __restrict__ idx, int cols,
@@ -109,6 +164,20 @@ extern "C" int fr_logsumexp_rows(const float* logits, int64_t ld, float* row_max
   FR_CHECK_ARG(rows >= 0 && cols > 0 && ld >= cols);
   if (rows == 0) return FR_OK;
   FR_CHECK_ARG(logits && row_max && row_logsum && (!logprobs_out || ldo >= cols));
+  const bool vec = cols % 4 == 0 && ld % 4 == 0 && aligned16(logits) && cols <= 8 * 1024 &&
+                   (!logprobs_out || (ldo % 4 == 0 && aligned16(logprobs_out)));
+  if (vec) {
+    const int vpt = ceil_div(cols, 4 * head::kThreads);
+#define FR_LSE_CASE(V)                                                                                              \
+  head::logsumexp_vec_kernel<V><<<rows, head::kThreads, 0, stream>>>(logits, ld, row_max, row_logsum, logprobs_out, \
+                                                                     ldo, cols)
+    if (vpt <= 1) FR_LSE_CASE(1);
+    else if (vpt <= 2) FR_LSE_CASE(2);
+    else if (vpt <= 4) FR_LSE_CASE(4);
+    else FR_LSE_CASE(8);
+#undef FR_LSE_CASE
+    return launch_status();
+  }
   head::logsumexp_kernel<<<rows, head::kThreads, 0, stream>>>(logits, ld, row_max, row_logsum, logprobs_out, ldo, cols);
   return launch_status();
 }

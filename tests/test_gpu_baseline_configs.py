@@ -243,8 +243,9 @@ def test_config4_full_size_wave_slot_lists_kv_bytes_and_legality():
     assert (got_v != ref_v).mean() <= 0.04 and (got_k != ref_k).mean() <= 0.04, ((got_v != ref_v).mean(),
                                                                                   (got_k != ref_k).mean())
     ref_kf, got_kf = kc[1:].float().numpy(), eng.pool.k[0][slots.to(DEV)].float().cpu().numpy()
-    # one e4m3 step at most (a step is up to 1/7 of the smaller neighbour)
-    assert (np.abs(ref_kf - got_kf) <= 0.15 * np.maximum(np.maximum(np.abs(ref_kf), np.abs(got_kf)), 2.0 ** -6)).all()
+    # one e4m3 step at most (a step is up to 1/7 of the smaller neighbour); where the rotation cancels two
+    # large terms into a small value, one bf16 ulp of either term (0.03 in absolute terms) is the bound instead
+    assert (np.abs(ref_kf - got_kf) <= np.maximum(0.15 * np.maximum(np.abs(ref_kf), np.abs(got_kf)), 0.03)).all()
 
     # (3) every request: catalog items only, distinct, sorted, complete
     legal_keys = np.unique(items[:, 0].astype(np.int64) * kl * kl + items[:, 1] * kl + items[:, 2])
