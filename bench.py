@@ -69,6 +69,10 @@ def parse():
     ap.add_argument("--head-compare", action="store_true",
                     help="time the SID head + beam step of every level at the bench's sizes, fused call against the "
                          "three-call flow, CSR and bitmap tries, and exit")
+    ap.add_argument("--config5", action="store_true",
+                    help="only run the token-range-sharded head step of the widest configuration (the `config5` object "
+                         "of the JSON line, which multi-GPU runs always carry) and print it")
+    ap.add_argument("--no-config5", action="store_true", help="leave the `config5` object out of a multi-GPU line")
     ap.add_argument("--attn-compare", action="store_true",
                     help="time one layer's decode attention on the bench's slot lists beside FlashInfer's paged "
                          "decode kernel (a library comparison) and exit")
@@ -766,6 +770,146 @@ def head_compare(requests: int, beam: int, items: int, iters: int = 10):
     print(json.dumps(res))
 
 
+def config5_head(dist, dev, rank: int, world: int, requests: int = 16, beam: int = 2048, levels: int = 4,
+                 width: int = 4096, items: int = 10_000_000, hidden: int = 2048, reps: int = 3):
+    """The one exchange step of the scope, at the widest baseline configuration's shape: 4 levels x 4096
+    codes, a Zipf-skewed 10M-item catalog (CSR trie built on every GPU), 2048 beams, ``requests`` requests
+    whose beam state every rank holds. The SID head is split by token range over the ``world`` ranks
+    (``flashrec_b200.sharded_head``: local fused head on the rank's codes, one all-gather of row statistics,
+    one of 16-byte winner records, merge) and timed per level beside the unsharded fused head on one GPU, with
+    and without the all-gather of the ranks' quantised hidden rows that a data-parallel model body needs
+    first. CUDA events, max over ranks. Also checks that every rank's merged result equals the unsharded
+    step on the same (combined) row statistics, bit for bit. Returns a dict for the JSON line."""
+    import numpy as np
+    import torch
+
+    from flashrec_b200.kernel.sglops import per_token_quant_fp8
+    from flashrec_b200.layers import quantize_weight_fp8
+    from flashrec_b200.sharded_head import ShardedSidHead, shard_range
+    from flashrec_b200.sid_decode import BeamStepOut, SidHeadWorkspace, sid_head_topk
+    from flashrec_b200.trie import build_trie_device
+
+    n, bw, L, kl, base = requests, beam, levels, width, 151_936
+    sizes = [kl] * L
+    rng = np.random.default_rng(0)  # the same catalog, weights and hidden states on every rank
+    cols = [np.minimum(rng.zipf(1.1, items) - 1, kl - 1) if l < 2 else rng.integers(0, kl, items) for l in range(L)]
+    trie = build_trie_device(torch.from_numpy(np.stack(cols, 1).astype(np.int32)).to(dev), sizes, base)
+    g = torch.Generator(device=dev).manual_seed(1)
+    wq, ws = quantize_weight_fp8(torch.randn((L * kl, hidden), generator=g, device=dev) * 0.02)
+    ws = ws.reshape(-1)
+    sharded = world > 1
+    head = ShardedSidHead() if sharded else None
+    lo, hi = shard_range(kl, rank, world)
+    rows = n * bw
+    my_rows = slice(rank * rows // world, (rank + 1) * rows // world)
+    i64 = dict(dtype=torch.int64, device=dev)
+
+    def planes():
+        cum = torch.full((n, bw), float("-inf"), device=dev)
+        cum[:, 0] = 0.0
+        return cum, torch.zeros((n, bw), **i64), torch.zeros((n, bw, L), **i64)
+
+    cum, node, tok = planes()
+    ws_full = SidHeadWorkspace()
+    ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+    t_un, t_sh, t_shx = [], [], []
+    equal = True
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for lv in range(L):
+        hid = torch.randn((rows, hidden), generator=g, device=dev).to(torch.bfloat16)
+        h8, hs = per_token_quant_fp8(hid)
+        wl, sl = wq[lv * kl:(lv + 1) * kl], ws[lv * kl:(lv + 1) * kl]
+        col = torch.full((n,), lv, dtype=torch.int32, device=dev)
+        tb = base + lv * kl
+        cap = trie.candidate_bound(lv, bw)
+        # unsharded fused head, everything on this GPU
+        for rep in range(reps + 1):
+            tok_u, node_u = torch.zeros_like(tok), torch.zeros_like(node)
+            barrier()
+            e0, e1 = ev(), ev()
+            e0.record()
+            out_u = sid_head_topk(cum, h8, hs.reshape(-1), wl, sl, node, trie, tb, bw, ws_full, cand_capacity=cap,
+                                  token_ids_in=tok, token_ids_out=tok_u, node_ids_out=node_u, col=col)
+            e1.record()
+            torch.cuda.synchronize()
+            if rep:
+                t_un.append((lv, e0.elapsed_time(e1)))
+        if sharded:
+            local = (h8, hs.reshape(-1), wl[lo:hi], sl[lo:hi])
+            for rep in range(reps + 1):
+                tok_s, node_s = torch.zeros_like(tok), torch.zeros_like(node)
+                barrier()
+                e0, e1 = ev(), ev()
+                e0.record()
+                out_s = head.step(cum, local, node, trie, tb, kl, bw, level=lv, token_ids_in=tok, token_ids_out=tok_s,
+                                  node_ids_out=node_s, col=col)
+                e1.record()
+                torch.cuda.synchronize()
+                if rep:
+                    t_sh.append((lv, e0.elapsed_time(e1)))
+            # the same with the hidden rows of a data-parallel body gathered first
+            h8_my, hs_my = h8[my_rows].contiguous(), hs.reshape(-1)[my_rows].contiguous()
+            for rep in range(reps + 1):
+                tok_x, node_x = torch.zeros_like(tok), torch.zeros_like(node)
+                barrier()
+                e0, e1 = ev(), ev()
+                e0.record()
+                gh, gs = head.gather_hidden(h8_my, hs_my)
+                out_x = head.step(cum, (gh, gs, wl[lo:hi], sl[lo:hi]), node, trie, tb, kl, bw, level=lv, token_ids_in=tok,
+                                  token_ids_out=tok_x, node_ids_out=node_x, col=col)
+                e1.record()
+                torch.cuda.synchronize()
+                if rep:
+                    t_shx.append((lv, e0.elapsed_time(e1)))
+            equal = equal and torch.equal(out_x.vals, out_s.vals) and torch.equal(tok_x, tok_s)
+            # bit-exact check: the unsharded step on the statistics the protocol combined
+            stats = head.ops.local_stats(cum, local, node, trie, tb, lo, kl, lv)
+            cmx, cls_ = head.ops.combine_stats(head._all_gather(stats))
+            tok_r, node_r = torch.zeros_like(tok), torch.zeros_like(node)
+            sid_head_topk(cum, h8, hs.reshape(-1), wl, sl, node, trie, tb, bw, ws_full, cand_capacity=cap, phase=1)
+            ref = sid_head_topk(cum, h8, hs.reshape(-1), wl, sl, node, trie, tb, bw, ws_full, cand_capacity=cap, phase=2,
+                                row_max=cmx, row_logsum=cls_, token_ids_in=tok, token_ids_out=tok_r, node_ids_out=node_r,
+                                col=col)
+            equal = equal and torch.equal(out_s.vals, ref.vals) and torch.equal(out_s.tokens, ref.tokens)
+            equal = equal and torch.equal(out_s.parents, ref.parents) and torch.equal(tok_s, tok_r)
+            equal = equal and torch.equal(node_s, node_r)
+            cum, node, tok = out_s.vals.clone(), node_s, tok_s
+        else:
+            cum, node, tok = out_u.vals.clone(), node_u, tok_u
+
+    def total_ms(ts):
+        if not ts:
+            return None
+        per_level = [sum(t for l, t in ts if l == lv) / reps for lv in range(L)]
+        t = torch.tensor(per_level, device=dev, dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [round(float(x), 4) for x in t.tolist()]
+
+    live = torch.isfinite(cum)
+    flags = torch.tensor([int(equal), int((node[live] == -1).all().item())], device=dev)
+    if dist is not None:
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    un, sh, shx = total_ms(t_un), total_ms(t_sh), total_ms(t_shx)
+    return {
+        "workload": "head step of the widest configuration: token-range-sharded SID head, NCCL all-gathers",
+        "requests": n, "beam_width": bw, "levels": L, "level_width": kl, "catalog_items": int(trie.arrays.n_items),
+        "trie_nodes": trie.n_nodes, "n_gpus": world,
+        "head_ms_per_level_unsharded_one_gpu": un, "head_ms_all_levels_unsharded_one_gpu": round(sum(un), 4),
+        "head_ms_per_level_sharded": sh, "head_ms_all_levels_sharded": round(sum(sh), 4) if sh else None,
+        "head_ms_all_levels_sharded_with_hidden_all_gather": round(sum(shx), 4) if shx else None,
+        "sharded_equals_unsharded_bitwise_on_shared_statistics": bool(flags[0].item()) if sharded else None,
+        "complete_sids_reached": bool(flags[1].item()),
+        "collectives_per_level": "1 x statistics [2, rows] f32 + 1 x winner records [N, K] x 16 B (+ 2 for the hidden "
+                                 "rows of a data-parallel body)",
+    }
+
+
 def attn_compare(requests: int, beam: int, iters: int = 10):
     """The decode attention of one layer on the bench's slot lists (requests x beam rows, prompts
     U[128,1024] shared by a request's beams, one own slot per row), timed between L2 flushes: this
@@ -899,6 +1043,14 @@ def main():
     from flashrec_b200.trie import build_trie_device
 
     _lib.load()  # fails loudly if the CUDA library is missing
+    if args.config5:
+        c5 = config5_head(dist, dev, rank, world)
+        if rank == 0:
+            print(json.dumps({"config5": c5}))
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     sizes = [8192] * 3
     token_base = 151_936
     cfg = Qwen3Config(num_hidden_layers=args.layers)
@@ -1064,6 +1216,15 @@ def main():
             "illegal_sid_beams": illegal,
             "device_status": [code, site],
         }
+    c5 = None
+    if world > 1 and not args.no_config5:
+        # the one path with a real exchange: all ranks take part, after the replicas' timed region
+        del eng
+        torch.cuda.empty_cache()
+        c5 = config5_head(dist, dev, rank, world)
+    if rank == 0:
+        if c5 is not None:
+            line["config5"] = c5
         print(json.dumps(line))
     if dist is not None:
         dist.barrier()

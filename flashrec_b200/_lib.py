@@ -102,7 +102,7 @@ _SIGNATURES = {
                                  _L, _I, P, P],
     "fr_logsumexp_rows": [P, _L, P, P, P, _L, _I, _I, P],
     "fr_topk_rows": [P, _L, P, P, P, P, _I, _I, _I, P],
-    "fr_lse_combine_shards": [P, P, P, P, _I, _I, P],
+    "fr_lse_combine_shards": [P, P, P, P, _I, _I, _L, P],
     "fr_trie_mask": [P, P, P, P, P, _F, _L, _L, P],
     "fr_trie_advance": [P, P, P, P, P, _I, _I, _I, P],
     "fr_beam_expand": [P, P, P, P, _I, _I, _I, _I, P],
@@ -110,8 +110,8 @@ _SIGNATURES = {
     "fr_mask_topk_expand_static": [P] * 15 + [_I] * 8 + [P],
     "fr_sid_beam_step": [P] * 7 + [_L] + [P] * 9 + [_L] * 3 + [_I] * 7 + [P],
     "fr_sid_head_topk_workspace_bytes": [_I, _I, _I, _I],
-    "fr_sid_head_topk": [P] * 5 + [P, P, _L, P, P, _L, _I] + [P] * 8 + [_L] * 3 + [_I] * 8 + [P, P, P, _L, _I, P],
-    "fr_topk_merge_shards": [P] * 15 + [_L] * 2 + [_I] * 7 + [P],
+    "fr_sid_head_topk": [P] * 6 + [P, P, _L, P, P, _L, _I] + [P] * 8 + [_L] * 3 + [_I] * 8 + [P, P, P, _L, _I, P],
+    "fr_topk_merge_shards": [P] * 16 + [_L] * 2 + [_I] * 7 + [P],
 }
 _RESTYPES = {"fr_version": c_char_p, "fr_decode_attn_scratch_bytes": c_int64,
              "fr_sid_head_topk_workspace_bytes": c_int64,

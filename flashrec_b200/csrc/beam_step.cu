@@ -184,6 +184,7 @@ struct StepParams {
   int64_t* out_tokens;     // [N, K]
   int64_t* out_indices;    // [N, K] flat index b * C + c
   int64_t* out_child;      // [N, K] node after the step, or null
+  uint4* out_records;      // [N, K] {score bits, flat index, child low, child high} for the shard exchange, or null
   int64_t* token_ids_out;  // [N, max(BW, K), L] or null
   int64_t* node_ids_out;   // [N, max(BW, K)] or null
   const float* cum;        // [N, BW]
@@ -413,6 +414,9 @@ __global__ void __launch_bounds__(kThreads, 1) beam_step_kernel(StepParams p) {
     p.out_tokens[o] = token;
     p.out_indices[o] = k < nvalid ? static_cast<int64_t>(idx) : 0;
     if (p.out_child) p.out_child[o] = child;
+    if (p.out_records)
+      p.out_records[o] = make_uint4(__float_as_uint(v), k < nvalid ? idx : 0u, static_cast<uint32_t>(child & 0xffffffffll),
+                                    static_cast<uint32_t>(static_cast<uint64_t>(child) >> 32));
     sel_parent[k] = static_cast<int32_t>(pc);
     sel_token[k] = token;
     sel_child[k] = child;
@@ -429,77 +433,101 @@ struct MergeParams {
   const float* vals;       // [S, N, K]
   const int64_t* indices;  // [S, N, K] flat index over the whole level
   const int64_t* child;    // [S, N, K]
+  const uint4* records;    // [S, N, K] {score bits, flat index, child low, child high}: replaces the three arrays
   int S;
   StepParams step;  // outputs + expand inputs; idx_width / level_tok_base / K / BW / L used
 };
 
+// Each shard's list is sorted like the output (score descending, then flat index ascending) and the flat
+// indices of different shards are disjoint, so the place of a record in the merged list is its own place
+// plus, for every other shard, the number of that shard's records that rank before it: one binary search
+// per (record, other shard) over composites held in shared memory. Records that land below K are written
+// straight to their place with the child node they carry; no sort, nothing looked up again.
 __global__ void __launch_bounds__(kThreads, 1) merge_shards_kernel(MergeParams mp) {
   extern __shared__ __align__(16) uint8_t dyn[];
+  __shared__ int live_total;
   const StepParams& p = mp.step;
   const int n = blockIdx.x;
-  const int total = mp.S * p.K;
-  int tp2 = 1;
-  while (tp2 < total) tp2 <<= 1;
-  uint64_t* win = reinterpret_cast<uint64_t*>(dyn);                    // [tp2]
-  int64_t* sel_token = reinterpret_cast<int64_t*>(win + tp2);          // [K]
-  int64_t* sel_child = sel_token + p.K;                                // [K]
-  int32_t* sel_parent = reinterpret_cast<int32_t*>(sel_child + p.K);   // [K]
-  for (int i = threadIdx.x; i < tp2; i += kThreads) {
-    uint64_t ck = 0;
-    if (i < total) {
-      const int s = i / p.K, k = i - s * p.K;
-      const size_t o = (static_cast<size_t>(s) * p.N + n) * p.K + k;
-      const float v = mp.vals[o];
-      if (v != p.neg_inf) ck = compose(v, static_cast<uint32_t>(mp.indices[o]));
-    }
-    win[i] = ck;
-  }
+  const int K = p.K;
+  const int total = mp.S * K;
+  uint64_t* comp = reinterpret_cast<uint64_t*>(dyn);                   // [S * K]
+  int64_t* sel_token = reinterpret_cast<int64_t*>(comp + total);       // [K]
+  int64_t* sel_child = sel_token + K;                                  // [K]
+  int32_t* sel_parent = reinterpret_cast<int32_t*>(sel_child + K);     // [K]
+  if (threadIdx.x == 0) live_total = 0;
   __syncthreads();
-  topk::bitonic_sort_desc<kThreads>(win, tp2);
-  for (int k = threadIdx.x; k < p.K; k += kThreads) {
-    const uint64_t ck = win[k];
-    const bool live = ck != 0;
-    float v = p.neg_inf;
-    uint32_t idx = 0;
-    if (live) {
-      v = topk::composite_score(ck);
-      idx = topk::composite_index(ck);
+  int live_mine = 0;
+  for (int i = threadIdx.x; i < total; i += kThreads) {
+    const int s = i / K, k = i - s * K;
+    const size_t o = (static_cast<size_t>(s) * p.N + n) * K + k;
+    float v;
+    uint32_t idx;
+    if (mp.records) {
+      const uint4 r = mp.records[o];
+      v = __uint_as_float(r.x);
+      idx = r.y;
+    } else {
+      v = mp.vals[o];
+      idx = static_cast<uint32_t>(mp.indices[o]);
     }
+    const uint64_t ck = v != p.neg_inf ? compose(v, idx) : 0;
+    comp[i] = ck;
+    live_mine += ck != 0;
+  }
+  if (live_mine) atomicAdd(&live_total, live_mine);
+  __syncthreads();
+  const int n_live = min(live_total, K);
+  for (int i = threadIdx.x; i < total; i += kThreads) {
+    const uint64_t ck = comp[i];
+    if (ck == 0) continue;
+    const int s = i / K;
+    int rank = i - s * K;
+    for (int t = 0; t < mp.S && rank < K; ++t) {
+      if (t == s) continue;
+      const uint64_t* lst = comp + t * K;  // descending; dead entries (0) at the end
+      int lo = 0, hi = K;
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (lst[mid] > ck) lo = mid + 1; else hi = mid;
+      }
+      rank += lo;
+    }
+    if (rank >= K) continue;
+    const size_t src = (static_cast<size_t>(s) * p.N + n) * K + (i - s * K);
+    int64_t child = 0;
+    if (mp.records) {
+      const uint4 r = mp.records[src];
+      child = static_cast<int64_t>((static_cast<uint64_t>(r.w) << 32) | r.z);
+    } else if (mp.child) {
+      child = mp.child[src];
+    }
+    const uint32_t idx = topk::composite_index(ck);
     const int64_t parent = static_cast<int64_t>(idx) / p.idx_width;
     const int64_t token = p.level_tok_base + static_cast<int64_t>(idx) % p.idx_width;
-    // find the record again in the shard lists to fetch its child node
-    int64_t child = 0;
-    if (live && mp.child) {
-      for (int s = 0; s < mp.S; ++s) {
-        const size_t base = (static_cast<size_t>(s) * p.N + n) * p.K;
-        // shard lists are sorted like the output: binary search on the composite
-        int lo = 0, hi = p.K;
-        while (lo < hi) {
-          const int mid = (lo + hi) >> 1;
-          const float mv = mp.vals[base + mid];
-          const uint64_t mk = mv != p.neg_inf ? compose(mv, static_cast<uint32_t>(mp.indices[base + mid])) : 0;
-          if (mk > ck) lo = mid + 1; else hi = mid;
-        }
-        if (lo < p.K && mp.vals[base + lo] != p.neg_inf &&
-            compose(mp.vals[base + lo], static_cast<uint32_t>(mp.indices[base + lo])) == ck) {
-          child = mp.child[base + lo];
-          break;
-        }
-      }
-    }
-    // a dead winner (fewer than K live candidates over all shards) is filled as the unsharded step
-    // fills it: parent 0, code 0 of the level, and the node that edge leads to
-    if (!live && p.node_in && p.trie.kind != FR_TRIE_NONE)
-      child = trie_transition(p.trie, p.node_in[static_cast<size_t>(n) * p.BW], p.level_tok_base);
-    const int64_t pc = clamp64(parent, 0, p.BW - 1);
-    const size_t o = static_cast<size_t>(n) * p.K + k;
-    p.out_vals[o] = v;
-    p.out_parents[o] = live ? parent : 0;
-    p.out_tokens[o] = live ? token : p.level_tok_base;
-    p.out_indices[o] = live ? static_cast<int64_t>(idx) : 0;
+    const size_t o = static_cast<size_t>(n) * K + rank;
+    p.out_vals[o] = topk::composite_score(ck);
+    p.out_parents[o] = parent;
+    p.out_tokens[o] = token;
+    p.out_indices[o] = static_cast<int64_t>(idx);
     if (p.out_child) p.out_child[o] = child;
-    sel_parent[k] = static_cast<int32_t>(live ? pc : 0);
-    sel_token[k] = live ? token : p.level_tok_base;
+    sel_parent[rank] = static_cast<int32_t>(clamp64(parent, 0, p.BW - 1));
+    sel_token[rank] = token;
+    sel_child[rank] = child;
+  }
+  // places past the last live winner (fewer than K live candidates over all shards) are filled as the
+  // unsharded step fills them: parent 0, code 0 of the level, and the node that edge leads to
+  for (int k = n_live + threadIdx.x; k < K; k += kThreads) {
+    int64_t child = 0;
+    if (p.node_in && p.trie.kind != FR_TRIE_NONE)
+      child = trie_transition(p.trie, p.node_in[static_cast<size_t>(n) * p.BW], p.level_tok_base);
+    const size_t o = static_cast<size_t>(n) * K + k;
+    p.out_vals[o] = p.neg_inf;
+    p.out_parents[o] = 0;
+    p.out_tokens[o] = p.level_tok_base;
+    p.out_indices[o] = 0;
+    if (p.out_child) p.out_child[o] = child;
+    sel_parent[k] = 0;
+    sel_token[k] = p.level_tok_base;
     sel_child[k] = child;
   }
   __syncthreads();
@@ -675,17 +703,20 @@ extern "C" int fr_sid_beam_step(float* out_vals, int64_t* out_parents, int64_t* 
 
 extern "C" int fr_topk_merge_shards(float* out_vals, int64_t* out_parents, int64_t* out_tokens, int64_t* out_indices,
                                     int64_t* out_child, const float* shard_vals, const int64_t* shard_indices,
-                                    const int64_t* shard_child, const int64_t* node_in, const int64_t* token_ids_in,
+                                    const int64_t* shard_child, const void* shard_records, const int64_t* node_in,
+                                    const int64_t* token_ids_in,
                                     int64_t* token_ids_out, int64_t* node_ids_out, const uint8_t* do_expand,
                                     const int32_t* col_n, const fr_trie* trie, int64_t level_tok_base,
                                     int64_t idx_width, int S, int N, int BW, int K, int L, int apply_expand,
                                     int apply_advance, cudaStream_t stream) {
   FR_CHECK_ARG(S > 0 && N >= 0 && BW > 0 && K > 0 && idx_width > 0);
   if (N == 0) return FR_OK;
-  FR_CHECK_ARG(out_vals && out_parents && out_tokens && out_indices && shard_vals && shard_indices);
+  FR_CHECK_ARG(out_vals && out_parents && out_tokens && out_indices);
+  FR_CHECK_ARG((shard_records && aligned16(shard_records)) || (shard_vals && shard_indices));
   FR_CHECK_SUPPORTED(K <= kMaxK && static_cast<int64_t>(S) * K <= 16384);
   MergeParams mp{};
   mp.vals = shard_vals; mp.indices = shard_indices; mp.child = shard_child; mp.S = S;
+  mp.records = static_cast<const uint4*>(shard_records);
   StepParams& p = mp.step;
   {
     const int st = make_trie(trie, &p.trie);
@@ -696,16 +727,15 @@ extern "C" int fr_topk_merge_shards(float* out_vals, int64_t* out_parents, int64
   p.node_in = node_in; p.token_ids_in = token_ids_in; p.do_expand = do_expand; p.col_n = col_n;
   p.level_tok_base = level_tok_base; p.idx_width = idx_width;
   p.N = N; p.BW = BW; p.C = 1; p.K = K; p.L = L;
-  p.apply_expand = apply_expand; p.apply_advance = apply_advance && apply_expand && shard_child != nullptr;
+  p.apply_expand = apply_expand;
+  p.apply_advance = apply_advance && apply_expand && (shard_child != nullptr || shard_records != nullptr);
   p.neg_inf = -INFINITY;
   if (apply_expand) {
     FR_CHECK_ARG(token_ids_in && token_ids_out && token_ids_in != token_ids_out && L > 0);
     FR_CHECK_SUPPORTED(K <= BW);
   }
   if (p.apply_advance) FR_CHECK_ARG(node_in && node_ids_out && node_in != node_ids_out);
-  int tp2 = 1;
-  while (tp2 < S * K) tp2 <<= 1;
-  const size_t smem = static_cast<size_t>(tp2) * 8 + static_cast<size_t>(K) * 20 + 16;
+  const size_t smem = static_cast<size_t>(S) * K * 8 + static_cast<size_t>(K) * 20 + 16;
   if (smem > 32 * 1024) {
     if (cudaFuncSetAttribute(merge_shards_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
@@ -805,7 +835,7 @@ extern "C" int64_t fr_sid_head_topk_workspace_bytes(int N, int BW, int level_wid
 }
 
 extern "C" int fr_sid_head_topk(float* out_vals, int64_t* out_parents, int64_t* out_tokens, int64_t* out_indices,
-                                int64_t* out_child, const void* a, const float* scale_a, int64_t lda, const void* w,
+                                int64_t* out_child, void* out_records, const void* a, const float* scale_a, int64_t lda, const void* w,
                                 const float* scale_w, int64_t ldw, int K_dim, const float* cum, const int64_t* node_in,
                                 const int64_t* token_ids_in, int64_t* token_ids_out, int64_t* node_ids_out,
                                 const uint8_t* do_expand, const int32_t* col_n, const fr_trie* trie,
@@ -821,6 +851,8 @@ extern "C" int fr_sid_head_topk(float* out_vals, int64_t* out_parents, int64_t* 
   StepParams p{};
   p.out_vals = out_vals; p.out_parents = out_parents; p.out_tokens = out_tokens; p.out_indices = out_indices;
   p.out_child = out_child; p.token_ids_out = token_ids_out; p.node_ids_out = node_ids_out;
+  p.out_records = static_cast<uint4*>(out_records);
+  FR_CHECK_ARG(out_records == nullptr || aligned16(out_records));
   p.cum = cum; p.node_in = node_in; p.token_ids_in = token_ids_in; p.do_expand = do_expand; p.col_n = col_n;
   p.level_tok_base = level_tok_base; p.idx_base = idx_base; p.idx_width = idx_width > 0 ? idx_width : level_width;
   p.N = N; p.BW = BW; p.C = level_width; p.K = K; p.L = L;

@@ -145,11 +145,12 @@ topk_rows_kernel(const float* __restrict__ x, int64_t ld, const float* __restric
 }
 
 __global__ void lse_combine_kernel(const float* __restrict__ smax, const float* __restrict__ slog,
-                                   float* __restrict__ row_max, float* __restrict__ row_logsum, int S, int rows) {
+                                   float* __restrict__ row_max, float* __restrict__ row_logsum, int S, int rows,
+                                   int64_t stride) {
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= rows) return;
   float mx, ls;
-  lse_combine(smax + r, slog + r, S, rows, mx, ls);
+  lse_combine(smax + r, slog + r, S, stride, mx, ls);
   row_max[r] = mx;
   row_logsum[r] = ls;
 }
@@ -203,11 +204,11 @@ extern "C" int fr_topk_rows(const float* x, int64_t ld, const float* row_max, co
 }
 
 extern "C" int fr_lse_combine_shards(const float* shard_max, const float* shard_logsum, float* row_max,
-                                     float* row_logsum, int S, int rows, cudaStream_t stream) {
-  FR_CHECK_ARG(S > 0 && rows >= 0);
+                                     float* row_logsum, int S, int rows, int64_t shard_stride, cudaStream_t stream) {
+  FR_CHECK_ARG(S > 0 && rows >= 0 && (shard_stride == 0 || shard_stride >= rows));
   if (rows == 0) return FR_OK;
   FR_CHECK_ARG(shard_max && shard_logsum && row_max && row_logsum);
   head::lse_combine_kernel<<<ceil_div(rows, 256), 256, 0, stream>>>(shard_max, shard_logsum, row_max, row_logsum, S,
-                                                                   rows);
+                                                                   rows, shard_stride > 0 ? shard_stride : rows);
   return launch_status();
 }

@@ -127,6 +127,7 @@ def sid_head_topk(
     phase: int = 0,
     row_max: Optional[torch.Tensor] = None,
     row_logsum: Optional[torch.Tensor] = None,
+    out_records: Optional[torch.Tensor] = None,
 ) -> BeamStepOut:
     """The level's head GEMM and the beam step in one call (``fr_sid_head_topk``): the fp32 logits are never
     written, only per-row statistics and the trie-legal candidates leave the GEMM. ``hidden_fp8`` e4m3
@@ -157,7 +158,7 @@ def sid_head_topk(
     sa = hidden_scale.reshape(-1)
     sw = weight_scale.reshape(-1)
     call("fr_sid_head_topk", ptr(out.vals), ptr(out.parents), ptr(out.tokens), ptr(out.indices), ptr(out.child),
-         ptr(hidden_fp8), ptr(sa), hidden_fp8.stride(0), ptr(weight_fp8), ptr(sw), weight_fp8.stride(0), h, ptr(cum),
+         ptr(out_records), ptr(hidden_fp8), ptr(sa), hidden_fp8.stride(0), ptr(weight_fp8), ptr(sw), weight_fp8.stride(0), h, ptr(cum),
          ptr(node_ids), ptr(token_ids_in), ptr(token_ids_out), ptr(node_ids_out), None, ptr(col),
          ctypes.byref(tr) if tr is not None else None, int(level_tok_base), int(idx_base), int(idx_width), n, bw, kl, k,
          int(token_ids_in.shape[2]) if do_exp else 0, int(do_exp), int(do_adv), int(phase), ptr(row_max),

@@ -448,6 +448,8 @@ int fr_sid_beam_step(float* out_vals, int64_t* out_parents, int64_t* out_tokens,
  * receive the statistics of this call's codes: a token-range shard exchanges them). phase 2: the beam step
  * only, on the candidates phase 1 left in the workspace, with row_max / row_logsum given (the statistics of
  * the whole row). In phase 0 row_max / row_logsum are optional outputs.
+ * out_records (optional, 16-byte aligned, 16 bytes x [N, K]): the winners once more as {score bits, flat
+ * index u32, child node as two 32-bit halves}, the record a token-range shard hands to fr_topk_merge_shards.
  * workspace: fr_sid_head_topk_workspace_bytes(N, BW, level_width, cand_capacity) bytes, 16-byte aligned;
  * cand_capacity = candidate records per request (an upper bound on the legal continuations of its live
  * beams; records beyond it are dropped and the status word gets FR_ERR_UNSUPPORTED, site 51).
@@ -455,7 +457,7 @@ int fr_sid_beam_step(float* out_vals, int64_t* out_parents, int64_t* out_tokens,
  * (search/expand.py:240-372, kernel/beam_trie.py:536-684), which materialise the [T, K] fp32 log-probs. */
 int64_t fr_sid_head_topk_workspace_bytes(int N, int BW, int level_width, int cand_capacity);
 int fr_sid_head_topk(float* out_vals, int64_t* out_parents, int64_t* out_tokens, int64_t* out_indices,
-                     int64_t* out_child, const void* a, const float* scale_a, int64_t lda, const void* w,
+                     int64_t* out_child, void* out_records, const void* a, const float* scale_a, int64_t lda, const void* w,
                      const float* scale_w, int64_t ldw, int K_dim, const float* cum, const int64_t* node_in,
                      const int64_t* token_ids_in, int64_t* token_ids_out, int64_t* node_ids_out,
                      const uint8_t* do_expand, const int32_t* col_n, const fr_trie* trie, int64_t level_tok_base,
@@ -464,7 +466,8 @@ int fr_sid_head_topk(float* out_vals, int64_t* out_parents, int64_t* out_tokens,
                      void* workspace, int64_t workspace_bytes, int cand_capacity, cudaStream_t stream);
 
 /* Merge S per-shard sorted winner lists ([S, N, K] values / flat indices /
- * child nodes, e.g. after an all-gather) into the global sorted top-K, then
+ * child nodes, or the same as 16-byte records in shard_records, e.g. after ONE
+ * all-gather; the three arrays may then be NULL) into the global sorted top-K, then
  * expand / advance as above. S * K <= 16384. trie (optional): with it, the slots
  * past the last live winner get the child node fr_sid_beam_step gives them (the
  * edge of code 0 from beam 0's node), so sharded and unsharded node planes agree
@@ -472,15 +475,18 @@ int fr_sid_head_topk(float* out_vals, int64_t* out_parents, int64_t* out_tokens,
  * multi-GPU path); the ordering rule is the one above. */
 int fr_topk_merge_shards(float* out_vals, int64_t* out_parents, int64_t* out_tokens, int64_t* out_indices,
                          int64_t* out_child, const float* shard_vals, const int64_t* shard_indices,
-                         const int64_t* shard_child, const int64_t* node_in, const int64_t* token_ids_in,
+                         const int64_t* shard_child, const void* shard_records, const int64_t* node_in,
+                         const int64_t* token_ids_in,
                          int64_t* token_ids_out, int64_t* node_ids_out, const uint8_t* do_expand, const int32_t* col_n,
                          const fr_trie* trie, int64_t level_tok_base, int64_t idx_width, int S, int N, int BW, int K,
                          int L, int apply_expand, int apply_advance, cudaStream_t stream);
 
-/* Combine per-shard row statistics [S, rows] (max, logsum) into the statistics
- * of the concatenated row. No counterpart in the reference. */
+/* Combine per-shard row statistics (max, logsum) into the statistics of the concatenated row.
+ * Shard s has its maxima at shard_max + s * shard_stride and its log-sums at shard_logsum +
+ * s * shard_stride (floats; shard_stride 0 = rows, i.e. two dense [S, rows] arrays; 2 * rows when each
+ * shard sent one [2, rows] block). No counterpart in the reference. */
 int fr_lse_combine_shards(const float* shard_max, const float* shard_logsum, float* row_max, float* row_logsum, int S,
-                          int rows, cudaStream_t stream);
+                          int rows, int64_t shard_stride, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -445,7 +445,7 @@ def test_merge_shards_equals_unsharded():
         call("fr_logsumexp_rows", ptr(part), part.stride(0), ptr(smx[s]), ptr(sls[s]), None, 0, n * bw, w,
              stream_ptr(logits.device))
     gmx, gls = torch.empty_like(mx), torch.empty_like(ls)
-    call("fr_lse_combine_shards", ptr(smx), ptr(sls), ptr(gmx), ptr(gls), S, n * bw, stream_ptr(logits.device))
+    call("fr_lse_combine_shards", ptr(smx), ptr(sls), ptr(gmx), ptr(gls), S, n * bw, 0, stream_ptr(logits.device))
     assert torch.allclose(gmx, mx) and torch.allclose(gls, ls, atol=1e-5)
     vals = torch.empty((S, n, bw), device=DEV)
     idx = torch.empty((S, n, bw), dtype=torch.int64, device=DEV)
@@ -459,7 +459,7 @@ def test_merge_shards_equals_unsharded():
     tok_out, node_out = torch.zeros_like(token_ids), torch.zeros_like(nodes)
     tr_desc = tr.descriptor()
     call("fr_topk_merge_shards", ptr(m.vals), ptr(m.parents), ptr(m.tokens), ptr(m.indices), ptr(m.child), ptr(vals),
-         ptr(idx), ptr(child), ptr(nodes), ptr(token_ids), ptr(tok_out), ptr(node_out), None, ptr(col),
+         ptr(idx), ptr(child), None, ptr(nodes), ptr(token_ids), ptr(tok_out), ptr(node_out), None, ptr(col),
          ctypes.byref(tr_desc), base + kl, kl, S, n, bw, bw, 2, 1, 1, stream_ptr(logits.device))
     for a, b in ((m.vals, full.vals), (m.parents, full.parents), (m.tokens, full.tokens), (m.indices, full.indices),
                  (m.child, full.child), (tok_out, tok_ref), (node_out, node_ref)):
@@ -704,7 +704,7 @@ def test_fused_sid_head_in_two_phases_over_token_range_shards():
                       wss[s], idx_base=s * wdt, idx_width=kl, phase=1, row_max=smx[s], row_logsum=sls[s],
                       cand_capacity=bw * wdt)
     gmx, gls = torch.empty(n * bw, device=DEV), torch.empty(n * bw, device=DEV)
-    call("fr_lse_combine_shards", ptr(smx), ptr(sls), ptr(gmx), ptr(gls), S, n * bw, stream_ptr(DEV))
+    call("fr_lse_combine_shards", ptr(smx), ptr(sls), ptr(gmx), ptr(gls), S, n * bw, 0, stream_ptr(DEV))
     vals = torch.empty((S, n, bw), device=DEV)
     idx = torch.empty((S, n, bw), dtype=torch.int64, device=DEV)
     child = torch.empty((S, n, bw), dtype=torch.int64, device=DEV)
@@ -719,7 +719,7 @@ def test_fused_sid_head_in_two_phases_over_token_range_shards():
     tok_out, node_out = torch.zeros_like(toks), torch.zeros_like(nodes)
     tr_desc = trie.descriptor()
     call("fr_topk_merge_shards", ptr(m.vals), ptr(m.parents), ptr(m.tokens), ptr(m.indices), ptr(m.child), ptr(vals),
-         ptr(idx), ptr(child), ptr(nodes), ptr(toks), ptr(tok_out), ptr(node_out), None, ptr(col), ctypes.byref(tr_desc),
+         ptr(idx), ptr(child), None, ptr(nodes), ptr(toks), ptr(tok_out), ptr(node_out), None, ptr(col), ctypes.byref(tr_desc),
          tok_base, kl, S, n, bw, bw, 2, 1, 1, stream_ptr(DEV))
     logits = fp8_scaled_mm(hq, wq.t(), hs, ws, torch.float32, block_n=512)
     tok_ref, node_ref = torch.zeros_like(toks), torch.zeros_like(nodes)

@@ -154,7 +154,7 @@ def test_config5_wide_beam_sharded_head_2048_beams_4x4096():
             call("fr_logsumexp_rows", ptr(part), part.stride(0), ptr(smx[s]), ptr(sls[s]), None, 0, n * bw, w,
                  stream_ptr(DEV))
         gmx, gls = torch.empty_like(mx), torch.empty_like(ls)
-        call("fr_lse_combine_shards", ptr(smx), ptr(sls), ptr(gmx), ptr(gls), S, n * bw, stream_ptr(DEV))
+        call("fr_lse_combine_shards", ptr(smx), ptr(sls), ptr(gmx), ptr(gls), S, n * bw, 0, stream_ptr(DEV))
         vals = torch.empty((S, n, bw), device=DEV)
         idx = torch.empty((S, n, bw), dtype=torch.int64, device=DEV)
         child = torch.empty((S, n, bw), dtype=torch.int64, device=DEV)
@@ -167,7 +167,7 @@ def test_config5_wide_beam_sharded_head_2048_beams_4x4096():
         tok_out, node_out = torch.zeros_like(toks), torch.zeros_like(nodes)
         trie_desc = trie.descriptor()
         call("fr_topk_merge_shards", ptr(m.vals), ptr(m.parents), ptr(m.tokens), ptr(m.indices), ptr(m.child),
-             ptr(vals), ptr(idx), ptr(child), ptr(nodes), ptr(toks), ptr(tok_out), ptr(node_out), None, ptr(col),
+             ptr(vals), ptr(idx), ptr(child), None, ptr(nodes), ptr(toks), ptr(tok_out), ptr(node_out), None, ptr(col),
              ctypes.byref(trie_desc), base + lv * kl, kl, S, n, bw, bw, L, 1, 1, stream_ptr(DEV))
         for a, b in ((m.vals, full.vals), (m.parents, full.parents), (m.tokens, full.tokens),
                      (m.indices, full.indices), (m.child, full.child), (tok_out, tok_ref), (node_out, node_ref)):

@@ -1,5 +1,6 @@
 """Host protocol of the token-range-sharded SID head on CPU ranks (gloo,
-world_size 2): statistics all-gather, local steps, winner all-gather, merge.
+world_size 2): one all-gather of the statistics, local steps, one all-gather of the 16-byte winner
+records, merge.
 The arithmetic is injected from the CPU oracle; the GPU kernels behind the same
 protocol are checked bit for bit against the unsharded step in
 tests/test_gpu_attn_head.py::test_merge_shards_equals_unsharded."""
@@ -16,13 +17,16 @@ from oracle import sid_oracle as O
 
 
 class OracleHeadOps:
+    """CPU stand-in for CudaHeadOps: ``local`` is the rank's slice of the level's fp32 logits."""
+
     def __init__(self, otr):
         self.otr = otr
 
-    def local_stats(self, logits):
-        return O.row_stats(logits)
+    def local_stats(self, cum, local, node_ids, trie, level_tok_base, lo, level_width, level):
+        return torch.stack(O.row_stats(local))  # [2, rows]
 
-    def combine_stats(self, all_mx, all_ls):
+    def combine_stats(self, all_stats):
+        all_mx, all_ls = all_stats[:, 0], all_stats[:, 1]
         mx = all_mx.amax(dim=0)
         return mx, torch.log(torch.exp(all_ls + (all_mx - mx)).sum(dim=0))
 
@@ -34,10 +38,19 @@ class OracleHeadOps:
         r = O.mask_topk_expand(cum, lp, toks, k, node_ids=node_ids, trie=self.otr, apply_expand=False)
         gidx = r["parents"] * idx_width + idx_base + (r["indices"] % w)
         gidx = torch.where(torch.isfinite(r["vals"]), gidx, torch.zeros_like(gidx))
-        return r["vals"], gidx, r["child"]
+        # the 16-byte record of the exchange: {score bits, flat index, child low, child high}
+        rec = torch.empty((n, k, 4), dtype=torch.int32)
+        rec[..., 0] = r["vals"].contiguous().view(torch.int32)
+        rec[..., 1] = gidx.to(torch.int32)
+        rec[..., 2] = (r["child"] & 0xffffffff).to(torch.int64).view(torch.int64).to(torch.int32)
+        rec[..., 3] = (r["child"] >> 32).to(torch.int32)
+        return rec
 
-    def merge(self, all_vals, all_idx, all_child, node_ids, tin, tout, nout, col, level_tok_base, idx_width, **_):
-        s, n, k = all_vals.shape
+    def merge(self, all_rec, node_ids, tin, tout, nout, col, level_tok_base, idx_width, trie, bw):
+        s, n, k, _ = all_rec.shape
+        all_vals = all_rec[..., 0].contiguous().view(torch.float32)
+        all_idx = all_rec[..., 1].to(torch.int64) & 0xffffffff
+        all_child = (all_rec[..., 3].to(torch.int64) << 32) | (all_rec[..., 2].to(torch.int64) & 0xffffffff)
         out = dict(vals=torch.empty(n, k), idx=torch.empty(n, k, dtype=torch.int64),
                    child=torch.empty(n, k, dtype=torch.int64))
         for i in range(n):
