@@ -580,6 +580,16 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           sbs[i] = n < N ? __ldg(scale_b + n) : 0.f;
           bss[i] = (bias != nullptr && n < N) ? __bfloat162float(bias[n]) : 0.f;
         }
+        if constexpr (EPI == 3) {
+          // The cos / sin row of the tile's first row, staged once per tile: the beams of a request decode at
+          // one position, so nearly every row of the tile reads this row (from shared memory instead of sixteen
+          // dependent 16-byte global loads per thread); a row at another position reads its own row as before.
+          if (epi_tid < 128) {
+            int64_t p0 = __ldg(rp.pos + min(m0, M - 1));
+            p0 = p0 < 0 ? 0 : (p0 >= rp.max_pos ? rp.max_pos - 1 : p0);
+            reinterpret_cast<float*>(out_stage + 16384)[buf * 128 + epi_tid] = __ldg(rp.cs + p0 * 128 + epi_tid);
+          }
+        }
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
       }
       int okw = 0;
@@ -730,7 +740,10 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         if (row_ok && (is_q || is_k)) ps = __ldg(rp.pos + row);
         if (row_ok && !is_q) slot = __ldg(rp.loc + row);
         ps = ps < 0 ? 0 : (ps >= rp.max_pos ? rp.max_pos - 1 : ps);
-        const float* cp = rp.cs + ps * 128 + 32 * sh;
+        int64_t ps0 = __ldg(rp.pos + min(m0, M - 1));  // the position whose row was staged for this tile
+        ps0 = ps0 < 0 ? 0 : (ps0 >= rp.max_pos ? rp.max_pos - 1 : ps0);
+        const float* cp = (ps == ps0 ? reinterpret_cast<const float*>(out_stage + 16384) + buf * 128
+                                     : rp.cs + ps * 128) + 32 * sh;
         ptx::tmem_ld_wait();
         {  // last read of this accumulator buffer by this warp
           ptx::tc_fence_before();
@@ -764,9 +777,9 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           for (int i0 = 0; i0 < 32; i0 += 8) {
             float cv[8], sv[8];
 #pragma unroll
-            for (int i = 0; i < 8; i += 4) {
-              const float4 c4 = __ldg(reinterpret_cast<const float4*>(cp + i0 + i));
-              const float4 s4 = __ldg(reinterpret_cast<const float4*>(cp + 64 + i0 + i));
+            for (int i = 0; i < 8; i += 4) {  // generic loads: cp points into shared or global memory
+              const float4 c4 = *reinterpret_cast<const float4*>(cp + i0 + i);
+              const float4 s4 = *reinterpret_cast<const float4*>(cp + 64 + i0 + i);
               cv[i] = c4.x; cv[i + 1] = c4.y; cv[i + 2] = c4.z; cv[i + 3] = c4.w;
               sv[i] = s4.x; sv[i + 1] = s4.y; sv[i + 2] = s4.z; sv[i + 3] = s4.w;
             }
