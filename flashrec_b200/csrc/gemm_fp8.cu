@@ -175,6 +175,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above touched only this CTA's shared / tensor memory: with a programmatic launch dependency it
+  // ran while the previous kernel of the stream was still finishing; global memory is touched from here on
+  ptx::griddep_wait();
+  ptx::griddep_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------ TMA producer ---------------------------
@@ -491,6 +495,8 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   ptx::cluster_wait();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  ptx::griddep_wait();  // see gemm_fp8_kernel
+  ptx::griddep_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------ TMA producer (both CTAs) ---------------
@@ -1066,6 +1072,8 @@ gemm_fp8_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  ptx::griddep_wait();  // see gemm_fp8_kernel
+  ptx::griddep_launch_dependents();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -1287,6 +1295,35 @@ static int make_tmap_out(CUtensorMap* map, const void* ptr, int64_t rows, int64_
 
 static int sm_count() { return device_sm_count(); }
 
+// Programmatic dependent launch for the decode step of few rows, where a GEMM's prologue (barrier set-up,
+// tensor-memory allocation, descriptor prefetch) and the launch gap are a large share of its few
+// microseconds: the kernel may then start while its predecessor in the stream is finishing and waits
+// (griddepcontrol.wait) before it touches global memory. FR_GEMM_PDL=0/1 overrides the row threshold.
+static bool use_pdl(int M) {
+  static int forced = []() {
+    const char* e = getenv("FR_GEMM_PDL");
+    return e ? (e[0] == '0' ? 0 : 1) : -1;
+  }();
+  if (forced >= 0) return forced == 1;
+  return M <= 2048;
+}
+static int fill_launch_attrs(cudaLaunchAttribute* attr, int cluster, bool pdl) {
+  int n = 0;
+  if (cluster > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (pdl) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  return n;
+}
+
 // Tile-width choice: whole waves of 128 x BLOCK_N tiles over the SMs, discounted
 // by how far a narrower tile falls below the tensor-pipe rate (a 128x64 tile
 // needs 192 B/clk of shared-memory operand reads against 128 B/clk available).
@@ -1325,9 +1362,20 @@ static int launch(const void* a, const void* b, const float* sa, const float* sb
   if (EPI == 1 && !table) return FR_ERR_CUDA;
   const int tiles = ceil_div(M, kBlockM) * ceil_div(N, BLOCK_N);
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, EpiCfg<EPI>::kThreads, C::kSmemBytes, stream>>>(ta, tb, static_cast<OutT*>(out), ldo, sa, sb,
-                                                  static_cast<const __nv_bfloat16*>(bias), M, N, K, row_amax, table, status);
-  return launch_status();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(EpiCfg<EPI>::kThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  cfg.attrs = attr;
+  cfg.numAttrs = fill_launch_attrs(attr, 1, use_pdl(M));
+  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, static_cast<OutT*>(out), ldo, sa, sb, static_cast<const __nv_bfloat16*>(bias),
+                         M, N, K, row_amax, table, status) != cudaSuccess) {
+    cudaGetLastError();
+    return FR_ERR_CUDA;
+  }
+  return FR_OK;
 }
 
 template <typename OutT, int EPI>
@@ -1361,13 +1409,9 @@ static int launch_pair(const void* a, const void* b, const float* sa, const floa
   cfg.blockDim = dim3(EpiCfg<EPI>::kThreads);
   cfg.dynamicSmemBytes = C::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
+  cudaLaunchAttribute attr[2];
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = fill_launch_attrs(attr, 2, use_pdl(M));
   if (cudaLaunchKernelEx(&cfg, kern, ta, tb, to, sa, sb, static_cast<const __nv_bfloat16*>(bias), M, N, K, row_amax,
                          table, rp, hp, status) != cudaSuccess) {
     cudaGetLastError();
@@ -1384,7 +1428,9 @@ static bool use_pair(int M, int N) {
   }();
   if (forced >= 0) return forced == 1;
   const int64_t tiles = static_cast<int64_t>(ceil_div(M, 2 * kBlockM)) * ceil_div(N, PairCfg<0>::kBlockN);
-  return tiles >= 3 * (sm_count() / 2);
+  // several waves of pair tiles, or — for the few rows of a one-request step — at least one pair tile per SM
+  // pair (measured at 512 rows: the gate_up shape, 96 pair tiles, 18.2 us against 20.4 us with 128 x 256 tiles)
+  return tiles >= 3 * (sm_count() / 2) || (M <= 1024 && M > kBlockM && tiles >= sm_count() / 2);
 }
 
 // Split-K over a cluster: the largest S in {8, 4, 2} that divides the k-blocks, leaves each CTA
@@ -1438,13 +1484,9 @@ static int launch_splitk(const void* a, const void* b, const float* sa, const fl
   cfg.blockDim = dim3(C::kThreads);
   cfg.dynamicSmemBytes = C::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = splits;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
+  cudaLaunchAttribute attr[2];
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = fill_launch_attrs(attr, splits, use_pdl(M));
   if (cudaLaunchKernelEx(&cfg, kern, ta, tb, static_cast<OutT*>(out), ldo, sa, sb, M, N, K, status) != cudaSuccess) {
     cudaGetLastError();
     return FR_ERR_CUDA;

@@ -77,6 +77,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return false;
 }
 
+// Programmatic dependent launch. `griddep_wait` returns once every grid this one was made dependent on has
+// completed and its writes are visible (at once when the launch carried no such dependency);
+// `griddep_launch_dependents` lets the grids that depend on this one be scheduled from here on (they still
+// block in their own griddep_wait until this grid has finished).
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // 2-D TMA tile load global -> shared, completion signalled on an mbarrier.
 // c0 is the innermost coordinate (elements); c0 * elemsize must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap* tmap, int c0, int c1, uint32_t bar) {
