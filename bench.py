@@ -467,7 +467,7 @@ def time_gemms(torch, rows: int, iters: int = 10):
     return fused_flops, fused_sec, flops, sec, lib
 
 
-def gemm_shapes(rows: int):
+def gemm_shapes(rows: int, emit: bool = True):
     """FP8 GEMM time of every linear-layer shape of the step at ``rows`` rows (512 = the decode
     step of a single request), this library and cuBLASLt (``torch._scaled_mm``) side by side:
     20 launches per CUDA graph, two replays timed with CUDA events (weights stay L2-resident)."""
@@ -510,7 +510,9 @@ def gemm_shapes(rows: int):
                                                 out_dtype=torch.bfloat16))
         out[name] = {"N": n, "K": k, "us": round(us, 2), "tflops": round(flops / us / 1e6, 1),
                      "cublaslt_us": round(lib, 2), "cublaslt_tflops": round(flops / lib / 1e6, 1)}
-    print(json.dumps({"gemm_shapes_rows": rows, "shapes": out}))
+    if emit:
+        print(json.dumps({"gemm_shapes_rows": rows, "shapes": out}))
+    return out
 
 
 def profile_kernels(rows: int):
@@ -518,7 +520,7 @@ def profile_kernels(rows: int):
     (about 1.5 GB resident, each kernel a fraction of a millisecond)."""
     import torch
 
-    from flashrec_b200.kernel.qk_rope_kv import fused_qk_norm_rope_store_fp8
+    from flashrec_b200.kernel.qk_rope_kv import fp8_qkv_mm_norm_rope_store, fused_qk_norm_rope_store_fp8
     from flashrec_b200.kernel.rms_fp8 import fused_add_rmsnorm_per_token_quant_fp8
     from flashrec_b200.kernel.sglops import (fp8_scaled_mm, fp8_scaled_mm_silu_mul, per_token_quant_fp8,
                                              quant_known_amax_fp8)
@@ -538,6 +540,7 @@ def profile_kernels(rows: int):
     qkv = torch.randn(rows, 32, 128, device=dev).bfloat16()
     cs = build_cos_sin_cache(128, 2048, 1e6, device=dev)
     pos = torch.randint(0, 2048, (rows,), device=dev)
+    pos_req = torch.randint(128, 1025, (max(rows // 512, 1),), device=dev).repeat_interleave(min(rows, 512))[:rows]
     loc = torch.arange(1, rows + 1, device=dev)
     kc = torch.zeros(rows + 16, 8, 128, dtype=torch.uint8, device=dev).view(fp8)
     vc = torch.zeros_like(kc)
@@ -552,6 +555,8 @@ def profile_kernels(rows: int):
         per_token_quant_fp8(h)
         silu_and_mul_per_token_quant_fp8(gu)                              # unfused SwiGLU quantiser
         fused_qk_norm_rope_store_fp8(qkv[:, :16], qkv[:, 16:24], qkv[:, 24:], pos, loc, hw, hw, 1e-6, cs, kc, vc)
+        # qkv GEMM with QK-norm + RoPE + KV write in its epilogue (rows of a request share a position)
+        fp8_qkv_mm_norm_rope_store(a, b[:4096].t(), sa, sb[:4096], pos_req, loc, hw, hw, 1e-6, cs, kc, vc, 16, 8)
 
     for _ in range(2):
         once()
@@ -1193,6 +1198,15 @@ def main():
             "layer_gemms": "plain qkv+o+gate_up+down at M=%d, 4 launches back to back" % eng.rows,
             "cublaslt_fp8_tflops_same_shapes": lib_tf,
         }
+        # the second baseline metric is quoted at 512 rows (one request): per-shape time, PFLOP/s and fraction of
+        # the same peak, with cuBLASLt's FP8 GEMM on the same shapes in the same run beside it
+        try:
+            m512 = gemm_shapes(512, emit=False)
+            roof["m512"] = {k: {"us": v["us"], "tflops": v["tflops"], "frac": round(v["tflops"] / peak_fp8, 4),
+                                "cublaslt_us": v["cublaslt_us"], "cublaslt_tflops": v["cublaslt_tflops"]}
+                            for k, v in m512.items()}
+        except Exception as exc:  # a library comparison must not take the bench line down
+            roof["m512"] = {"error": repr(exc)[:200]}
         cpu = None
         if not args.no_cpu_baseline and world == 1:
             # one bounded sample on the host cores; only in the single-process run, where nothing else loads them

@@ -22,10 +22,11 @@ namespace fr {
 int* device_status_ptr();  // capi.cu
 
 // indptr[0] = 0, indptr[i + 1] = sum of max(seq_lens[..i], 0). One CTA; each thread owns kScanItems
-// consecutive rows of a chunk, so 16384 rows take two rounds of the block-wide scan.
-constexpr int kScanItems = 8;
+// consecutive rows of a chunk (read with 16-byte loads when the array allows it), so up to 32768 rows take one
+// round of the block-wide scan: the kernel is a chain of a few latencies, not bandwidth.
 // `status` (optional): the library's sticky status word; it receives {FR_ERR_BAD_ARG, site 41} when the
 // list is longer than `capacity`, since the caller cannot see that without a host read.
+constexpr int kScanItems = 32;
 __global__ void __launch_bounds__(1024) seq_scan_kernel(const int32_t* __restrict__ seq_lens,
                                                        int32_t* __restrict__ indptr, int n, int capacity = 0,
                                                        int* status = nullptr) {
@@ -34,15 +35,23 @@ __global__ void __launch_bounds__(1024) seq_scan_kernel(const int32_t* __restric
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (threadIdx.x == 0) { carry_s = 0; indptr[0] = 0; }
   __syncthreads();
+  const bool vec_ok = (reinterpret_cast<uintptr_t>(seq_lens) & 15u) == 0;
   for (int base = 0; base < n; base += 1024 * kScanItems) {
     const int i0 = base + threadIdx.x * kScanItems;
     int32_t v[kScanItems];
+    if (vec_ok && i0 + kScanItems <= n) {
+#pragma unroll
+      for (int j = 0; j < kScanItems; j += 4) {
+        const int4 q = __ldg(reinterpret_cast<const int4*>(seq_lens + i0 + j));
+        v[j] = max(q.x, 0); v[j + 1] = max(q.y, 0); v[j + 2] = max(q.z, 0); v[j + 3] = max(q.w, 0);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < kScanItems; ++j) v[j] = i0 + j < n ? max(__ldg(seq_lens + i0 + j), 0) : 0;
+    }
     int32_t x = 0;
 #pragma unroll
-    for (int j = 0; j < kScanItems; ++j) {
-      v[j] = i0 + j < n ? max(seq_lens[i0 + j], 0) : 0;
-      x += v[j];
-    }
+    for (int j = 0; j < kScanItems; ++j) x += v[j];
     const int32_t mine = x;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
