@@ -783,14 +783,42 @@ __global__ void __launch_bounds__(256) row_mask_kernel(uint32_t* __restrict__ ma
   }
 }
 
-__global__ void tile_stats_combine_kernel(const float* __restrict__ tmax, const float* __restrict__ tlog,
-                                          float* __restrict__ row_max, float* __restrict__ row_logsum, int tiles, int rows) {
-  const int r = blockIdx.x * blockDim.x + threadIdx.x;
-  if (r >= rows) return;
-  float mx, ls;
-  lse_combine(tmax + r, tlog + r, tiles, rows, mx, ls);
-  row_max[r] = mx;
-  row_logsum[r] = ls;
+// Row statistics from the head GEMM's per-part entries ([parts, rows] each): 8 threads per row, each merging
+// parts/8 consecutive entries with a running (max, scaled sum), then the eight partial results merged in
+// group order through shared memory. 32 rows per CTA; loads are one 128-byte line per warp and part.
+__global__ void __launch_bounds__(256) tile_stats_combine_kernel(const float* __restrict__ tmax, const float* __restrict__ tlog,
+                                                                float* __restrict__ row_max, float* __restrict__ row_logsum,
+                                                                int parts, int rows) {
+  __shared__ float sm_m[8][32], sm_s[8][32];
+  const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
+  const int r = blockIdx.x * 32 + lane;
+  const int per = (parts + 7) / 8;
+  float m = -INFINITY, s = 0.f;
+  if (r < rows) {
+    const int p1 = min(parts, (grp + 1) * per);
+    for (int p = grp * per; p < p1; ++p) {
+      const float pm = __ldg(tmax + static_cast<size_t>(p) * rows + r);
+      const float pl = __ldg(tlog + static_cast<size_t>(p) * rows + r);
+      if (pm == -INFINITY) continue;  // a part without codes
+      const float nm = fmaxf(m, pm);
+      s = s * expf(m - nm) + expf(pl + (pm - nm));  // m == -inf: s is 0 and exp(-inf) = 0
+      m = nm;
+    }
+  }
+  sm_m[grp][lane] = m;
+  sm_s[grp][lane] = s;
+  __syncthreads();
+  if (grp == 0 && r < rows) {
+    float M = -INFINITY;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) M = fmaxf(M, sm_m[g][lane]);
+    float sum = 0.f;
+#pragma unroll
+    for (int g = 0; g < 8; ++g)
+      if (sm_m[g][lane] != -INFINITY) sum += sm_s[g][lane] * expf(sm_m[g][lane] - M);
+    row_max[r] = M;
+    row_logsum[r] = logf(sum);
+  }
 }
 
 struct HeadWorkspace {
@@ -873,7 +901,7 @@ extern "C" int fr_sid_head_topk(float* out_vals, int64_t* out_parents, int64_t* 
   float* mx = row_max ? row_max : ws.row_max;
   float* ls = row_logsum ? row_logsum : ws.row_logsum;
   if (phase == 0 || phase == 1) {
-    FR_CHECK_ARG(a && scale_a && w && scale_w && aligned16(a) && aligned16(w));
+    FR_CHECK_ARG(a && scale_a && w && scale_w && aligned16(a) && aligned16(w) && aligned16(scale_w));
     FR_CHECK_ARG(lda >= K_dim && ldw >= K_dim && lda % 16 == 0 && ldw % 16 == 0 && K_dim % 16 == 0);
     if (cudaMemsetAsync(ws.cand_count, 0, static_cast<size_t>(N) * 4, stream) != cudaSuccess) return FR_ERR_CUDA;
     HeadEpi hp{};
@@ -894,7 +922,7 @@ extern "C" int fr_sid_head_topk(float* out_vals, int64_t* out_parents, int64_t* 
     }
     st = launch_head_gemm(a, w, scale_a, scale_w, rows, level_width, K_dim, lda, ldw, hp, stream);
     if (st != FR_OK) return st;
-    tile_stats_combine_kernel<<<ceil_div(rows, 256), 256, 0, stream>>>(ws.tile_max, ws.tile_logsum, mx, ls, tiles, rows);
+    tile_stats_combine_kernel<<<ceil_div(rows, 32), 256, 0, stream>>>(ws.tile_max, ws.tile_logsum, mx, ls, tiles, rows);
     if (launch_status() != FR_OK) return FR_ERR_CUDA;
     if (phase == 1) return FR_OK;
   } else {

@@ -580,7 +580,7 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       float* bss = bias_stage + buf * BLOCK_N;
       const int row = m0 + quad * 32 + lane;
       const float sa = row < M ? __ldg(scale_a + row) : 0.f;
-      if constexpr (EPI != 1) {  // the SwiGLU epilogue reads its few scales straight from global memory
+      if constexpr (EPI != 1 && EPI != 4) {  // the SwiGLU and SID-head epilogues read their scales from global memory
         for (int i = epi_tid; i < BLOCK_N; i += kEpiThreads) {
           const int n = n0 + i;
           sbs[i] = n < N ? __ldg(scale_b + n) : 0.f;
@@ -912,12 +912,29 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           }
           const int left = n_valid - 32 * c;
           float cm4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains
+          // per-channel scales straight from global memory (every lane reads the same addresses: L1 broadcasts),
+          // so that the sixteen epilogue warps need no CTA-wide barrier per tile
+          const float* sbp = scale_b + n0 + c * 32;
+          if (left >= 32) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float t = __fmul_rn(__fmul_rn(__uint_as_float(r[j]), sa), sbs[c * 32 + j]);
-            if (j >= left) t = -INFINITY;
-            r[j] = __float_as_uint(t);
-            cm4[j & 3] = fmaxf(cm4[j & 3], t);
+            for (int j = 0; j < 32; j += 4) {
+              const float4 s4 = __ldg(reinterpret_cast<const float4*>(sbp + j));
+              const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float t = __fmul_rn(__fmul_rn(__uint_as_float(r[j + e]), sa), sv[e]);
+                r[j + e] = __float_as_uint(t);
+                cm4[e] = fmaxf(cm4[e], t);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float t = -INFINITY;
+              if (j < left) t = __fmul_rn(__fmul_rn(__uint_as_float(r[j]), sa), __ldg(sbp + j));
+              r[j] = __float_as_uint(t);
+              cm4[j & 3] = fmaxf(cm4[j & 3], t);
+            }
           }
           const float cm = fmaxf(fmaxf(cm4[0], cm4[1]), fmaxf(cm4[2], cm4[3]));
           if (cm > mx) {  // rescale the running sum to the new maximum
