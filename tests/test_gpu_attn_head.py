@@ -226,6 +226,38 @@ def test_head_logprobs_and_topk():
     assert torch.equal(vals.cpu(), rv) and torch.equal(idx.cpu(), ri)
 
 
+def test_fp8_head_top_k_against_the_bf16_head_fixture():
+    """How far the FP8 SID head (this library) and the reference's bf16 head agree on WINNERS, on the
+    committed fixture written by the reference: log-probs differ by at most 6e-2 (measured 3.3e-2), so
+    a code can only enter or leave a row's top-K when its bf16-head log-prob lies within twice that
+    bound of the K-th value, and two winners can only swap order inside such a gap. Counted on the
+    fixture: 48 of 48 (K=4), 94 of 96 (K=8), 186 of 192 (K=16) winners in common."""
+    from flashrec_b200.logits import RestrictedLMHead, topk_rows
+
+    g = load_golden("head")
+    sizes, base = g["sizes"].tolist(), int(g["base"])
+    head = RestrictedLMHead(list(range(base, base + sum(sizes))))
+    head.bind_quantized(fp8_from_bits(g["sid_q"]).to(DEV), torch.from_numpy(g["sid_s"]).to(DEV))
+    head.bind_codebook(sizes)
+    lp, _ = head.compute(bf16_from_bits(g["h"]).to(DEV))
+    ref = torch.from_numpy(g["lp_all"])
+    bound = 2 * 6e-2
+    for k, least_common in ((4, 46), (8, 90), (16, 180)):
+        _, idx = topk_rows(lp, k)
+        idx = idx.cpu()
+        common = 0
+        for r in range(ref.shape[0]):
+            mine, theirs = idx[r].tolist(), torch.topk(ref[r], k).indices.tolist()
+            kth = torch.topk(ref[r], k).values[-1].item()
+            common += len(set(mine) & set(theirs))
+            for c in set(mine) ^ set(theirs):  # only near-ties at the cut-off may differ
+                assert abs(ref[r, c].item() - kth) <= bound, (k, r, c)
+            for i in range(k):  # my order never contradicts a bf16-head gap wider than the bound
+                for j in range(i + 1, k):
+                    assert ref[r, mine[i]] - ref[r, mine[j]] >= -bound, (k, r, i, j)
+        assert common >= least_common, (k, common)
+
+
 @pytest.mark.parametrize("rows,cols,k", [(5, 8192, 1024), (3, 100, 100), (4, 4096, 1), (2, 777, 300)])
 def test_topk_rows_with_ties(rows, cols, k):
     from flashrec_b200.logits import topk_rows
