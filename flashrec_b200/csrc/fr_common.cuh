@@ -104,6 +104,59 @@ __device__ __forceinline__ double warp_sum(double v) {
   return v;
 }
 
+// ---------------------------------------------------------------------------
+// Sum of squares of bf16 values, exact, without fp64 arithmetic on the common path: for code whose
+// warps all square at the same time (the qkv GEMM's epilogue: sixteen warps per SM reach the phase
+// together and queue on the fp64 pipe, about 26 cycles per warp instruction). The row kernels keep
+// their fp64 FMAs: there the fp64 pipe works beside other warps' fp32 instructions, and the eight
+// fp32 instructions per element below were measured slower (RMSNorm -> e4m3 29.1 against 24.6 us).
+// The square of a bf16 value is exact in fp32 (8-bit significand); the running sum
+// is kept as an unevaluated pair s + e: Knuth's TwoSum makes s + p == t + err exactly, the errs
+// are added up in e with plain fp32 adds. For chains of at most 16 squares merged pairwise
+// (sq_merge, also across lanes) the pair differs from the exact sum by less than 2^-39 of it,
+// for up to 128 squares per thread and 32 threads per row. Callers turn the row total into
+// fp64, scale it by a power of two and round to fp32; sq_rounding_is_safe tells whether that
+// rounding is certain to equal the rounding of the exact sum (the bits dropped by the rounding
+// are further than the error bound from a rounding boundary). When it is not (about one row in
+// 8000), the caller recomputes the row in fp64 as before, so results never change.
+// ---------------------------------------------------------------------------
+struct SqSum {
+  float s, e;
+};
+
+__device__ __forceinline__ void sq_two_sum(float a, float b, float& t, float& err) {
+  t = __fadd_rn(a, b);
+  const float bb = __fsub_rn(t, a);
+  err = __fadd_rn(__fsub_rn(a, __fsub_rn(t, bb)), __fsub_rn(b, bb));
+}
+
+__device__ __forceinline__ void sq_add(SqSum& a, float x) {
+  float t, err;
+  sq_two_sum(a.s, __fmul_rn(x, x), t, err);
+  a.s = t;
+  a.e = __fadd_rn(a.e, err);
+}
+
+__device__ __forceinline__ void sq_merge(SqSum& a, const SqSum& b) {
+  float t, err;
+  sq_two_sum(a.s, b.s, t, err);
+  a.s = t;
+  a.e = __fadd_rn(__fadd_rn(a.e, b.e), err);
+}
+
+__device__ __forceinline__ double sq_value(const SqSum& a) { return static_cast<double>(a.s) + static_cast<double>(a.e); }
+
+// v = (row total from SqSum pairs) scaled by a power of two; true when static_cast<float>(v) is the
+// fp32 rounding of the exactly summed value as well. fp32 keeps 23 of the 52 fraction bits; the
+// error bound 2^-39 |v| is below 2^14 units of the last fp64 place, the window leaves a factor two.
+__device__ __forceinline__ bool sq_rounding_is_safe(double v) {
+  if (v == 0.0) return true;  // every square was zero
+  const int lo = __double2loint(v) & 0x1fffffff;
+  const int ex = (__double2hiint(v) >> 20) & 0x7ff;
+  const int dist = lo > (1 << 28) ? lo - (1 << 28) : (1 << 28) - lo;
+  return dist > (1 << 15) && ex > 1023 - 60 && ex < 1023 + 100;  // squares and the fp32 result stay normal
+}
+
 // bf16 <-> fp32 on raw bit patterns (a bf16 is the upper half of an fp32).
 __device__ __forceinline__ float bf16lo(uint32_t packed) { return __uint_as_float(packed << 16); }
 __device__ __forceinline__ float bf16hi(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }

@@ -396,6 +396,7 @@ struct QkvRope {
   int64_t ldq, ck_s, ck_h, cv_s, cv_h;
   float eps;
   int max_pos, num_slots, n_q, n_kv;
+  int wide;  // Q rows and cache rows are 32-byte aligned: 32-byte stores
 };
 
 // ---------------------------------------------------------------------------
@@ -570,6 +571,23 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         wn[i] = __bfloat162float(i < 128 ? rp.qw[i] : rp.kw[i - 128]);
       asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
     }
+    // EPI 3: the values staged per tile (weight scales of the tile's 256 columns, cos / sin row of its first
+    // row) are loaded one tile ahead into registers, so the barrier below never waits for global memory.
+    float pre_sb = 0.f, pre_cs = 0.f;
+    auto prefetch_tile = [&](int t) {
+      if (t >= num_tiles) return;
+      const TileCoord tn = tile_coord(t, m_blocks, n_blocks);
+      if (epi_tid < BLOCK_N) {
+        const int n = tn.nb * BLOCK_N + epi_tid;
+        pre_sb = n < N ? __ldg(scale_b + n) : 0.f;
+      } else if (epi_tid < BLOCK_N + 128) {
+        const int mrow = tn.mb * (2 * kBlockM) + static_cast<int>(rank) * kBlockM;
+        int64_t p0 = __ldg(rp.pos + min(mrow, M - 1));
+        p0 = p0 < 0 ? 0 : (p0 >= rp.max_pos ? rp.max_pos - 1 : p0);
+        pre_cs = __ldg(rp.cs + p0 * 128 + (epi_tid - BLOCK_N));
+      }
+    };
+    if constexpr (EPI == 3) prefetch_tile(pair);
     for (int tile = pair; tile < num_tiles && ok; tile += n_pairs, ++it) {
       const TileCoord tc = tile_coord(tile, m_blocks, n_blocks);
       const int m0 = tc.mb * (2 * kBlockM) + static_cast<int>(rank) * kBlockM;
@@ -580,21 +598,19 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       float* bss = bias_stage + buf * BLOCK_N;
       const int row = m0 + quad * 32 + lane;
       const float sa = row < M ? __ldg(scale_a + row) : 0.f;
-      if constexpr (EPI != 1 && EPI != 4) {  // the SwiGLU and SID-head epilogues read their scales from global memory
+      if constexpr (EPI == 3) {
+        // The cos / sin row of the tile's first row is staged once per tile: the beams of a request decode at
+        // one position, so nearly every row of the tile reads this row (from shared memory instead of sixteen
+        // dependent 16-byte global loads per thread); a row at another position reads its own row as before.
+        if (epi_tid < BLOCK_N) sbs[epi_tid] = pre_sb;
+        else if (epi_tid < BLOCK_N + 128) reinterpret_cast<float*>(out_stage + 16384)[buf * 128 + epi_tid - BLOCK_N] = pre_cs;
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+        prefetch_tile(tile + n_pairs);
+      } else if constexpr (EPI != 1 && EPI != 4) {  // the SwiGLU and SID-head epilogues read their scales from global memory
         for (int i = epi_tid; i < BLOCK_N; i += kEpiThreads) {
           const int n = n0 + i;
           sbs[i] = n < N ? __ldg(scale_b + n) : 0.f;
           bss[i] = (bias != nullptr && n < N) ? __bfloat162float(bias[n]) : 0.f;
-        }
-        if constexpr (EPI == 3) {
-          // The cos / sin row of the tile's first row, staged once per tile: the beams of a request decode at
-          // one position, so nearly every row of the tile reads this row (from shared memory instead of sixteen
-          // dependent 16-byte global loads per thread); a row at another position reads its own row as before.
-          if (epi_tid < 128) {
-            int64_t p0 = __ldg(rp.pos + min(m0, M - 1));
-            p0 = p0 < 0 ? 0 : (p0 >= rp.max_pos ? rp.max_pos - 1 : p0);
-            reinterpret_cast<float*>(out_stage + 16384)[buf * 128 + epi_tid] = __ldg(rp.cs + p0 * 128 + epi_tid);
-          }
         }
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
       }
@@ -754,28 +770,51 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         {  // last read of this accumulator buffer by this warp
           ptx::tc_fence_before();
           __syncwarp();
-          if (lane == 0) ptx::mbar_arrive_cluster(tempty_remote);
+          if (lane == 0) ptx::mbar_arrive_cluster_relaxed(tempty_remote);
         }
-        // the qkv GEMM's bf16 output values, in place
+        // the qkv GEMM's bf16 output values, in place (two values per conversion instruction)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          a1[i] = __float_as_uint(round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(a1[i]), sa), sbs[c0 + i])));
-          a2[i] = __float_as_uint(round_bf16(__fmul_rn(__fmul_rn(__uint_as_float(a2[i]), sa), sbs[c0 + 64 + i])));
+        for (int i = 0; i < 32; i += 2) {
+          const uint32_t p1 = pack_bf16(__fmul_rn(__fmul_rn(__uint_as_float(a1[i]), sa), sbs[c0 + i]),
+                                        __fmul_rn(__fmul_rn(__uint_as_float(a1[i + 1]), sa), sbs[c0 + i + 1]));
+          const uint32_t p2 = pack_bf16(__fmul_rn(__fmul_rn(__uint_as_float(a2[i]), sa), sbs[c0 + 64 + i]),
+                                        __fmul_rn(__fmul_rn(__uint_as_float(a2[i + 1]), sa), sbs[c0 + 64 + i + 1]));
+          a1[i] = p1 << 16; a1[i + 1] = p1 & 0xffff0000u;
+          a2[i] = p2 << 16; a2[i + 1] = p2 & 0xffff0000u;
         }
         if (is_q || is_k) {
-          double sq[4] = {0.0, 0.0, 0.0, 0.0};  // four independent chains
+          // this thread's 64 squares as fp32 pairs (four chains of 16, merged pairwise): see SqSum
+          SqSum sq[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const double l = static_cast<double>(__uint_as_float(a1[i])), hh = static_cast<double>(__uint_as_float(a2[i]));
-            sq[i & 3] = fma(l, l, sq[i & 3]);
-            sq[i & 3] = fma(hh, hh, sq[i & 3]);
+            sq_add(sq[i & 3], __uint_as_float(a1[i]));
+            sq_add(sq[i & 3], __uint_as_float(a2[i]));
           }
+          sq_merge(sq[0], sq[1]);
+          sq_merge(sq[2], sq[3]);
+          sq_merge(sq[0], sq[2]);
           double* xs = xss + ((xsel * 16 + quad * 4 + hd * 2) * 32);
           xsel ^= 1;  // alternate buffers per exchange: use n + 2 is separated from use n by barrier n + 1
-          xs[sh * 32 + lane] = (sq[0] + sq[1]) + (sq[2] + sq[3]);
+          xs[sh * 32 + lane] = sq_value(sq[0]);
           // the two warps of this (quadrant, head) meet; both take the same path through every tile
           asm volatile("bar.sync %0, 64;" ::"r"(2 + quad * 2 + hd) : "memory");
-          const double tot = xs[lane] + xs[32 + lane];
+          double tot = xs[lane] + xs[32 + lane];
+          // Both warps hold the same totals lane by lane, so they agree on whether some row needs the fp64 sum
+          // (a total whose fp32 rounding the pairs cannot decide: rare) and repeat the exchange together.
+          if (__any_sync(0xffffffffu, !sq_rounding_is_safe(tot))) {
+            double d4[4] = {0.0, 0.0, 0.0, 0.0};
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const double l = static_cast<double>(__uint_as_float(a1[i])), hh = static_cast<double>(__uint_as_float(a2[i]));
+              d4[i & 3] = fma(l, l, d4[i & 3]);
+              d4[i & 3] = fma(hh, hh, d4[i & 3]);
+            }
+            double* xs2 = xss + ((xsel * 16 + quad * 4 + hd * 2) * 32);
+            xsel ^= 1;
+            xs2[sh * 32 + lane] = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+            asm volatile("bar.sync %0, 64;" ::"r"(2 + quad * 2 + hd) : "memory");
+            tot = xs2[lane] + xs2[32 + lane];
+          }
           const float var = static_cast<float>(tot / 128.0);
           const float rstd = rsqrt_rn(__fadd_rn(var, rp.eps));
           const float* w = wn + (is_q ? 0 : 128) + 32 * sh;
@@ -801,46 +840,62 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         if (is_q) {
           if (row_ok) {
             __nv_bfloat16* dst = rp.q_out + static_cast<int64_t>(row) * rp.ldq + hg * 128 + 32 * sh;
-            uint4* d1 = reinterpret_cast<uint4*>(dst);
-            uint4* d2 = reinterpret_cast<uint4*>(dst + 64);
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              d1[v] = make_uint4(pack_bf16(__uint_as_float(a1[8 * v]), __uint_as_float(a1[8 * v + 1])),
-                                 pack_bf16(__uint_as_float(a1[8 * v + 2]), __uint_as_float(a1[8 * v + 3])),
-                                 pack_bf16(__uint_as_float(a1[8 * v + 4]), __uint_as_float(a1[8 * v + 5])),
-                                 pack_bf16(__uint_as_float(a1[8 * v + 6]), __uint_as_float(a1[8 * v + 7])));
-              d2[v] = make_uint4(pack_bf16(__uint_as_float(a2[8 * v]), __uint_as_float(a2[8 * v + 1])),
-                                 pack_bf16(__uint_as_float(a2[8 * v + 2]), __uint_as_float(a2[8 * v + 3])),
-                                 pack_bf16(__uint_as_float(a2[8 * v + 4]), __uint_as_float(a2[8 * v + 5])),
-                                 pack_bf16(__uint_as_float(a2[8 * v + 6]), __uint_as_float(a2[8 * v + 7])));
+            for (int i = 0; i < 16; ++i) {  // packed in place: words 0..15 of a1 / a2 hold the 32 bf16 values
+              a1[i] = pack_bf16(__uint_as_float(a1[2 * i]), __uint_as_float(a1[2 * i + 1]));
+              a2[i] = pack_bf16(__uint_as_float(a2[2 * i]), __uint_as_float(a2[2 * i + 1]));
+            }
+            if (rp.wide) {
+#pragma unroll
+              for (int v = 0; v < 2; ++v) {
+                const uint32_t w1[8] = {a1[8 * v], a1[8 * v + 1], a1[8 * v + 2], a1[8 * v + 3],
+                                        a1[8 * v + 4], a1[8 * v + 5], a1[8 * v + 6], a1[8 * v + 7]};
+                const uint32_t w2[8] = {a2[8 * v], a2[8 * v + 1], a2[8 * v + 2], a2[8 * v + 3],
+                                        a2[8 * v + 4], a2[8 * v + 5], a2[8 * v + 6], a2[8 * v + 7]};
+                ptx::st_global_v8(dst + 16 * v, w1);
+                ptx::st_global_v8(dst + 64 + 16 * v, w2);
+              }
+            } else {
+              uint4* d1 = reinterpret_cast<uint4*>(dst);
+              uint4* d2 = reinterpret_cast<uint4*>(dst + 64);
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                d1[v] = make_uint4(a1[4 * v], a1[4 * v + 1], a1[4 * v + 2], a1[4 * v + 3]);
+                d2[v] = make_uint4(a2[4 * v], a2[4 * v + 1], a2[4 * v + 2], a2[4 * v + 3]);
+              }
             }
           }
         } else {
           if (is_k) {  // K: round to bf16 first, as the reference does before the e4m3 cast
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              a1[i] = __float_as_uint(round_bf16(__uint_as_float(a1[i])));
-              a2[i] = __float_as_uint(round_bf16(__uint_as_float(a2[i])));
+            for (int i = 0; i < 32; i += 2) {
+              const uint32_t p1 = pack_bf16(__uint_as_float(a1[i]), __uint_as_float(a1[i + 1]));
+              const uint32_t p2 = pack_bf16(__uint_as_float(a2[i]), __uint_as_float(a2[i + 1]));
+              a1[i] = p1 << 16; a1[i + 1] = p1 & 0xffff0000u;
+              a2[i] = p2 << 16; a2[i + 1] = p2 & 0xffff0000u;
             }
           }
           if (row_ok && slot >= 0 && slot < rp.num_slots) {  // never write outside the pool
             uint8_t* dst = is_k ? (rp.kc + slot * rp.ck_s + (hg - rp.n_q) * rp.ck_h)
                                 : (rp.vc + slot * rp.cv_s + (hg - rp.n_q - rp.n_kv) * rp.cv_h);
-            uint4* d1 = reinterpret_cast<uint4*>(dst + 32 * sh);
-            uint4* d2 = reinterpret_cast<uint4*>(dst + 64 + 32 * sh);
+            uint32_t w1[8], w2[8];  // 32 e4m3 bytes of each rotary half: one full sector each
 #pragma unroll
-            for (int v = 0; v < 2; ++v) {
-              uint32_t w1[4], w2[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const int i = 16 * v + 4 * j;
-                w1[j] = pack_e4m3x4(__uint_as_float(a1[i]), __uint_as_float(a1[i + 1]), __uint_as_float(a1[i + 2]),
-                                    __uint_as_float(a1[i + 3]));
-                w2[j] = pack_e4m3x4(__uint_as_float(a2[i]), __uint_as_float(a2[i + 1]), __uint_as_float(a2[i + 2]),
-                                    __uint_as_float(a2[i + 3]));
-              }
-              d1[v] = make_uint4(w1[0], w1[1], w1[2], w1[3]);
-              d2[v] = make_uint4(w2[0], w2[1], w2[2], w2[3]);
+            for (int j = 0; j < 8; ++j) {
+              w1[j] = pack_e4m3x4(__uint_as_float(a1[4 * j]), __uint_as_float(a1[4 * j + 1]), __uint_as_float(a1[4 * j + 2]),
+                                  __uint_as_float(a1[4 * j + 3]));
+              w2[j] = pack_e4m3x4(__uint_as_float(a2[4 * j]), __uint_as_float(a2[4 * j + 1]), __uint_as_float(a2[4 * j + 2]),
+                                  __uint_as_float(a2[4 * j + 3]));
+            }
+            if (rp.wide) {
+              ptx::st_global_v8(dst + 32 * sh, w1);
+              ptx::st_global_v8(dst + 64 + 32 * sh, w2);
+            } else {
+              uint4* d1 = reinterpret_cast<uint4*>(dst + 32 * sh);
+              uint4* d2 = reinterpret_cast<uint4*>(dst + 64 + 32 * sh);
+              d1[0] = make_uint4(w1[0], w1[1], w1[2], w1[3]);
+              d1[1] = make_uint4(w1[4], w1[5], w1[6], w1[7]);
+              d2[0] = make_uint4(w2[0], w2[1], w2[2], w2[3]);
+              d2[1] = make_uint4(w2[4], w2[5], w2[6], w2[7]);
             }
           }
         }
@@ -1652,6 +1707,9 @@ extern "C" int fr_gemm_fp8_qkv_rope(const void* a, const void* b, const float* s
   rp.num_slots = num_slots;
   rp.n_q = n_q;
   rp.n_kv = n_kv;
+  rp.wide = (reinterpret_cast<uintptr_t>(q_out) % 32 == 0 && (ldq * 2) % 32 == 0 &&
+             reinterpret_cast<uintptr_t>(k_cache) % 32 == 0 && reinterpret_cast<uintptr_t>(v_cache) % 32 == 0 &&
+             ck_s % 32 == 0 && ck_h % 32 == 0 && cv_s % 32 == 0 && cv_h % 32 == 0) ? 1 : 0;
   // the output tensor map of the launcher is not used by this epilogue; q_out gives it a valid target
   return gemm::launch_pair<__nv_bfloat16, 3>(a, b, scale_a, scale_b, nullptr, q_out, ldq, M, N, K, lda, ldb, stream,
                                              nullptr, rp);

@@ -249,6 +249,19 @@ __device__ __forceinline__ void st_cluster_u32x4(uint32_t cluster_addr, uint32_t
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// The same arrive without release semantics, for handing a TMEM accumulator back: the reads it follows
+// are tcgen05.ld whose completion tcgen05.wait::ld has already awaited and tcgen05.fence::before_thread_sync
+// orders; a release would in addition wait for every earlier global store of the thread to be performed
+// (the previous tile's output), which costs the epilogue 1-2 thousand cycles per tile.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// 32-byte global store (one full sector per thread); the address must be 32-byte aligned.
+__device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&w)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+               "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
+}
 
 // TMA tile load into THIS CTA's shared memory whose completion bytes are credited to an
 // mbarrier that may live in the other CTA of the pair (`bar_cluster` is a shared::cluster address).
