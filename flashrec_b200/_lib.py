@@ -8,13 +8,16 @@ gets an exception.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p, POINTER
 from pathlib import Path
 from typing import Optional
 
 import torch
 
-_LIB_PATH = Path(__file__).resolve().parent / "libflashrec_b200.so"
+# FLASHREC_B200_LIB selects another build of the same library (e.g. to compare two builds in one process
+# launch each); by default the library built in-tree next to this file is loaded.
+_LIB_PATH = Path(os.environ.get("FLASHREC_B200_LIB") or Path(__file__).resolve().parent / "libflashrec_b200.so").resolve()
 _lib: Optional[ctypes.CDLL] = None
 
 FR_OK = 0
