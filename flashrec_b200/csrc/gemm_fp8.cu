@@ -963,7 +963,8 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           if (cc == kChunks - 1) {  // last read of this accumulator buffer by this warp
             ptx::tc_fence_before();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive_cluster(tempty_remote);
+            // relaxed: the records and statistics of the previous tile are plain global stores still in flight
+            if (lane == 0) ptx::mbar_arrive_cluster_relaxed(tempty_remote);
           }
           const int left = n_valid - 32 * c;
           float cm4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // independent chains

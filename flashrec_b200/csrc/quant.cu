@@ -58,18 +58,20 @@ row_warp_kernel(const uint4* __restrict__ x, uint4* __restrict__ resid, const ui
 
   float amax = 0.f;
   if constexpr (NORM) {
-    double ss = 0.0;
+    // four independent chains: a lane's 8 * VPL fp64 FMAs in one chain are the longest dependent
+    // sequence of the kernel when few rows are in flight (a decode step of one request)
+    double s4[4] = {0.0, 0.0, 0.0, 0.0};
 #pragma unroll
     for (int j = 0; j < VPL; ++j) {
       const uint32_t* xv = reinterpret_cast<const uint32_t*>(&v[j]);
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
         const double a = static_cast<double>(bf16lo(xv[t])), b = static_cast<double>(bf16hi(xv[t]));
-        ss = fma(a, a, ss);  // the squares are exact (8-bit significands)
-        ss = fma(b, b, ss);
+        s4[t] = fma(a, a, s4[t]);  // the squares are exact (8-bit significands)
+        s4[t] = fma(b, b, s4[t]);
       }
     }
-    ss = warp_sum(ss);
+    double ss = warp_sum((s4[0] + s4[1]) + (s4[2] + s4[3]));
     const float var = static_cast<float>(ss / static_cast<double>(VPL * 256));
     const float rstd = rsqrt_rn(__fadd_rn(var, eps));
 #pragma unroll
