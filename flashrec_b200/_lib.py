@@ -112,12 +112,15 @@ _SIGNATURES = {
     "fr_mask_topk_expand": [P] * 16 + [_I] * 8 + [P],
     "fr_mask_topk_expand_static": [P] * 15 + [_I] * 8 + [P],
     "fr_sid_beam_step": [P] * 7 + [_L] + [P] * 9 + [_L] * 3 + [_I] * 7 + [P],
+    "fr_joint_select_workspace_bytes": [_I, _I],
+    "fr_joint_select": [P] * 8 + [P, P, P, P, P, _I, P, _L, _I, _I, _I, _I, P],
+    "fr_select_final_topk": [P] * 4 + [P, P, P, P, _I, _I, _I, _I, P],
     "fr_sid_head_topk_workspace_bytes": [_I, _I, _I, _I],
     "fr_sid_head_topk": [P] * 6 + [P, P, _L, P, P, _L, _I] + [P] * 8 + [_L] * 3 + [_I] * 8 + [P, P, P, _L, _I, P],
     "fr_topk_merge_shards": [P] * 16 + [_L] * 2 + [_I] * 7 + [P],
 }
 _RESTYPES = {"fr_version": c_char_p, "fr_decode_attn_scratch_bytes": c_int64,
-             "fr_sid_head_topk_workspace_bytes": c_int64,
+             "fr_sid_head_topk_workspace_bytes": c_int64, "fr_joint_select_workspace_bytes": c_int64,
              "fr_trie_build_workspace_bytes": c_int64}
 
 

@@ -196,6 +196,7 @@ struct StepParams {
   const float* lp;     // [N, BW, C]
   const int64_t* tok;  // [N, BW, C]
   float* scratch;      // [N, BW * C] masked scores
+  const float* perturb;  // [N, BW, C] or null: added to the score for ranking only (unmasked explicit candidates)
   // full-width candidates straight from the level's logits
   const float* logits;  // [N * BW, ld]
   int64_t ld;
@@ -248,7 +249,13 @@ __device__ __forceinline__ void for_each_candidate(const StepParams& p, int n, b
       }
     } else {
       const float* lp_n = p.lp + static_cast<size_t>(n) * M;
-      for (uint32_t i = threadIdx.x; i < M; i += kThreads) f(compose(__fadd_rn(cum_n[i / p.C], lp_n[i]), i));
+      if (p.perturb != nullptr) {
+        const float* pt = p.perturb + static_cast<size_t>(n) * M;
+        for (uint32_t i = threadIdx.x; i < M; i += kThreads)
+          f(compose(__fadd_rn(__fadd_rn(cum_n[i / p.C], lp_n[i]), pt[i]), i));
+      } else {
+        for (uint32_t i = threadIdx.x; i < M; i += kThreads) f(compose(__fadd_rn(cum_n[i / p.C], lp_n[i]), i));
+      }
     }
   } else {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -400,6 +407,10 @@ __global__ void __launch_bounds__(kThreads, 1) beam_step_kernel(StepParams p) {
       const uint64_t ck = win[k];
       v = topk::composite_score(ck);
       idx = topk::composite_index(ck);
+      if constexpr (MODE == 0) {  // ranked with noise: the score that is reported carries none
+        if (p.perturb != nullptr && !p.apply_mask)
+          v = __fadd_rn(p.cum[static_cast<size_t>(n) * p.BW + idx / p.C], p.lp[static_cast<size_t>(n) * M + idx]);
+      }
     }
     const int64_t parent = k < nvalid ? static_cast<int64_t>(idx) / cdiv : 0;
     int64_t token;
@@ -585,6 +596,125 @@ static int launch_step(const StepParams& p, cudaStream_t stream) {
   return launch_status();
 }
 
+
+// ---------------------------------------------------------------------------
+// Stop-token walk over a group's ranked candidates (search/select.py:98-161): candidate i survives when
+// it is not a stop token and fewer than K non-stop candidates rank before it; a stop-token candidate is
+// finished when fewer than K survivors rank before it. Survivors are compacted into [K] slots in rank
+// order, finished candidates into [C] slots; unused slots read zero. One CTA per group.
+// ---------------------------------------------------------------------------
+struct JointParams {
+  const float* vals;        // [G, C] ranked scores (no noise)
+  const int64_t* parents;   // [G, C]
+  const int64_t* tokens;    // [G, C]
+  const int64_t* stop;      // [n_stop]
+  int n_stop;
+  int64_t* next_tokens;     // [G, K]
+  int64_t* parent_idx;      // [G, K]
+  float* new_cum;           // [G, K]
+  int64_t* num_survivors;   // [G]
+  int64_t* fin_tokens;      // [G, C]
+  int64_t* fin_parent;      // [G, C]
+  float* fin_cum;           // [G, C]
+  int64_t* num_finished;    // [G]
+  int C, K;
+};
+
+constexpr int kScanThreads = 256;
+
+// exclusive prefix of v over the CTA; total returned through `total`
+__device__ __forceinline__ int block_exclusive(int v, int* warp_sums, int& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int y = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += y;
+  }
+  __syncthreads();  // warp_sums may still be read from a previous call
+  if (lane == 31) warp_sums[warp] = inc;
+  __syncthreads();
+  int before = 0;
+  total = 0;
+#pragma unroll
+  for (int w = 0; w < kScanThreads / 32; ++w) {
+    const int t = warp_sums[w];
+    if (w < warp) before += t;
+    total += t;
+  }
+  return before + inc - v;
+}
+
+__global__ void __launch_bounds__(kScanThreads) joint_select_scan_kernel(JointParams p) {
+  __shared__ int warp_sums[kScanThreads / 32];
+  __shared__ int64_t stop_s[64];
+  const int g = blockIdx.x, tid = threadIdx.x;
+  const int C = p.C, K = p.K;
+  const float* vals = p.vals + static_cast<size_t>(g) * C;
+  const int64_t* par = p.parents + static_cast<size_t>(g) * C;
+  const int64_t* tok = p.tokens + static_cast<size_t>(g) * C;
+  for (int i = tid; i < min(p.n_stop, 64); i += kScanThreads) stop_s[i] = p.stop[i];
+  for (int i = tid; i < K; i += kScanThreads) {
+    p.next_tokens[static_cast<size_t>(g) * K + i] = 0;
+    p.parent_idx[static_cast<size_t>(g) * K + i] = 0;
+    p.new_cum[static_cast<size_t>(g) * K + i] = 0.f;
+  }
+  for (int i = tid; i < C; i += kScanThreads) {
+    p.fin_tokens[static_cast<size_t>(g) * C + i] = 0;
+    p.fin_parent[static_cast<size_t>(g) * C + i] = 0;
+    p.fin_cum[static_cast<size_t>(g) * C + i] = 0.f;
+  }
+  __syncthreads();
+  auto is_stop = [&](int64_t t) {
+    bool s = false;
+    for (int j = 0; j < p.n_stop; ++j) s |= (j < 64 ? stop_s[j] : p.stop[j]) == t;
+    return s;
+  };
+  const int per = (C + kScanThreads - 1) / kScanThreads;  // consecutive candidates per thread (<= 16)
+  const int i0 = min(C, tid * per), i1 = min(C, i0 + per);
+  uint32_t stop_bits = 0;
+  int non_stop = 0;
+  for (int i = i0; i < i1; ++i) {
+    const bool st = is_stop(tok[i]);
+    stop_bits |= (st ? 1u : 0u) << (i - i0);
+    non_stop += st ? 0 : 1;
+  }
+  int total_ns;
+  int rank = block_exclusive(non_stop, warp_sums, total_ns);  // non-stop candidates ranked before my first
+  int fin = 0;
+  {
+    int r = rank;
+    for (int i = i0; i < i1; ++i) {
+      if ((stop_bits >> (i - i0)) & 1u) fin += r < K ? 1 : 0;
+      else ++r;
+    }
+  }
+  int total_fin;
+  int fin_rank = block_exclusive(fin, warp_sums, total_fin);
+  for (int i = i0; i < i1; ++i) {
+    if ((stop_bits >> (i - i0)) & 1u) {
+      if (rank < K) {
+        const size_t o = static_cast<size_t>(g) * C + fin_rank++;
+        p.fin_tokens[o] = tok[i];
+        p.fin_parent[o] = par[i];
+        p.fin_cum[o] = vals[i];
+      }
+    } else {
+      if (rank < K) {
+        const size_t o = static_cast<size_t>(g) * K + rank;
+        p.next_tokens[o] = tok[i];
+        p.parent_idx[o] = par[i];
+        p.new_cum[o] = vals[i];
+      }
+      ++rank;
+    }
+  }
+  if (tid == 0) {
+    p.num_survivors[g] = min(total_ns, K);
+    p.num_finished[g] = total_fin;
+  }
+}
+
 static int grid_for(int64_t total, int threads) {
   int64_t g = (total + threads - 1) / threads;
   if (g > 148 * 8) g = 148 * 8;
@@ -671,6 +801,70 @@ extern "C" int fr_mask_topk_expand(float* out_vals, int64_t* out_parents, int64_
   FR_CHECK_ARG(top_logprobs && top_tokens);
   if (p.apply_mask) FR_CHECK_ARG(scratch);
   return launch_step<0>(p, stream);
+}
+
+
+// joint_select / select_final_topk of the reference (search/select.py:72-179) for G independent groups.
+extern "C" int64_t fr_joint_select_workspace_bytes(int G, int C) {
+  if (G < 0 || C <= 0) return -1;
+  return static_cast<int64_t>(G) * C * (4 + 3 * 8) + 64;
+}
+
+extern "C" int fr_joint_select(int64_t* next_tokens, int64_t* parent_idx, float* new_cum, int64_t* num_survivors,
+                               int64_t* fin_tokens, int64_t* fin_parent, float* fin_cum, int64_t* num_finished,
+                               const float* cum, const float* top_logprobs, const int64_t* top_tokens,
+                               const float* perturb, const int64_t* stop_ids, int n_stop, void* workspace,
+                               int64_t workspace_bytes, int G, int R, int C, int K, cudaStream_t stream) {
+  FR_CHECK_ARG(G >= 0 && R > 0 && C > 0 && K > 0 && n_stop >= 0);
+  if (G == 0) return FR_OK;
+  FR_CHECK_ARG(next_tokens && parent_idx && new_cum && num_survivors && fin_tokens && fin_parent && fin_cum && num_finished);
+  FR_CHECK_ARG(cum && top_logprobs && top_tokens && (n_stop == 0 || stop_ids));
+  FR_CHECK_SUPPORTED(C <= kMaxK && C <= kScanThreads * 16);
+  FR_CHECK_ARG(workspace && aligned16(workspace) && workspace_bytes >= fr_joint_select_workspace_bytes(G, C));
+  const size_t gc = static_cast<size_t>(G) * C;
+  uint8_t* w = static_cast<uint8_t*>(workspace);
+  int64_t* s_par = reinterpret_cast<int64_t*>(w);
+  int64_t* s_tok = s_par + gc;
+  int64_t* s_idx = s_tok + gc;
+  float* s_val = reinterpret_cast<float*>(s_idx + gc);
+  StepParams sp{};
+  sp.out_vals = s_val; sp.out_parents = s_par; sp.out_tokens = s_tok; sp.out_indices = s_idx;
+  sp.cum = cum; sp.lp = top_logprobs; sp.tok = top_tokens; sp.perturb = perturb;
+  sp.N = G; sp.BW = R; sp.C = C; sp.K = C; sp.L = 0;  // the walk looks at the C best of the R * C extensions
+  sp.neg_inf = -INFINITY;
+  sp.idx_width = C;
+  int st = make_trie(nullptr, &sp.trie);
+  if (st != FR_OK) return st;
+  st = check_step_common(sp);
+  if (st != FR_OK) return st;
+  st = launch_step<0>(sp, stream);
+  if (st != FR_OK) return st;
+  JointParams jp{};
+  jp.vals = s_val; jp.parents = s_par; jp.tokens = s_tok; jp.stop = stop_ids; jp.n_stop = n_stop;
+  jp.next_tokens = next_tokens; jp.parent_idx = parent_idx; jp.new_cum = new_cum; jp.num_survivors = num_survivors;
+  jp.fin_tokens = fin_tokens; jp.fin_parent = fin_parent; jp.fin_cum = fin_cum; jp.num_finished = num_finished;
+  jp.C = C; jp.K = K;
+  joint_select_scan_kernel<<<G, kScanThreads, 0, stream>>>(jp);
+  return launch_status();
+}
+
+extern "C" int fr_select_final_topk(int64_t* tokens, int64_t* parent_idx, float* cum_out, int64_t* indices_scratch,
+                                    const float* cum, const float* top_logprobs, const int64_t* top_tokens,
+                                    const float* perturb, int G, int R, int C, int K, cudaStream_t stream) {
+  FR_CHECK_ARG(G >= 0 && R > 0 && C > 0 && K > 0);
+  if (G == 0) return FR_OK;
+  FR_CHECK_ARG(tokens && parent_idx && cum_out && indices_scratch && cum && top_logprobs && top_tokens);
+  StepParams sp{};
+  sp.out_vals = cum_out; sp.out_parents = parent_idx; sp.out_tokens = tokens; sp.out_indices = indices_scratch;
+  sp.cum = cum; sp.lp = top_logprobs; sp.tok = top_tokens; sp.perturb = perturb;
+  sp.N = G; sp.BW = R; sp.C = C; sp.K = K; sp.L = 0;
+  sp.neg_inf = -INFINITY;
+  sp.idx_width = C;
+  int st = make_trie(nullptr, &sp.trie);
+  if (st != FR_OK) return st;
+  st = check_step_common(sp);
+  if (st != FR_OK) return st;
+  return launch_step<0>(sp, stream);
 }
 
 extern "C" int fr_sid_beam_step(float* out_vals, int64_t* out_parents, int64_t* out_tokens, int64_t* out_indices,

@@ -177,6 +177,7 @@ class Qwen3ForCausalLM:
             layer.self_attn.fuse_rope_gemm = bool(fuse_rope_gemm)
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, device=device)
         self.embed_tokens: Optional[torch.Tensor] = None  # bf16 [vocab, hidden]
+        self.lm_head_weight: Optional[torch.Tensor] = None  # bf16 [vocab, hidden]; the embedding when tied
         self.attn = attn
 
     def embed(self, input_ids: torch.Tensor) -> torch.Tensor:

@@ -419,6 +419,29 @@ int fr_mask_topk_expand_static(float* out_vals, int64_t* out_parents, int64_t* o
                                const int32_t* col_n, const fr_trie* trie, int N, int BW, int C, int K, int L,
                                int apply_mask, int apply_expand, int apply_advance, cudaStream_t stream);
 
+/* One beam expansion step with stop tokens, for G independent groups of R frontier rows with C candidates
+ * each: rank the R * C extensions by cum[r] + top_logprobs[r, c] (+ perturb[r, c] when given: rank noise,
+ * e.g. Gumbel(0, 1) for sampling without replacement; the reported scores never carry it), take the C best
+ * in order, and walk them: a candidate whose token is not a stop token survives while fewer than K survivors
+ * rank before it; a stop-token candidate is finished while fewer than K survivors rank before it. Survivors
+ * go to next_tokens / parent_idx / new_cum [G, K] in rank order, finished candidates to fin_* [G, C];
+ * unused slots are zero; num_survivors / num_finished [G] (int64) count them. Ties rank by lower flat index
+ * r * C + c. C <= 4096. workspace: fr_joint_select_workspace_bytes(G, C) bytes, 16-byte aligned.
+ * Reference: joint_select (search/select.py:98-161), one group per call there. */
+int64_t fr_joint_select_workspace_bytes(int G, int C);
+int fr_joint_select(int64_t* next_tokens, int64_t* parent_idx, float* new_cum, int64_t* num_survivors,
+                    int64_t* fin_tokens, int64_t* fin_parent, float* fin_cum, int64_t* num_finished,
+                    const float* cum, const float* top_logprobs, const int64_t* top_tokens, const float* perturb,
+                    const int64_t* stop_ids, int n_stop, void* workspace, int64_t workspace_bytes, int G, int R,
+                    int C, int K, cudaStream_t stream);
+
+/* The K best of the R * C extensions of each group, in order, all finished (the step that ends by length):
+ * tokens / parent_idx / cum_out [G, K]; indices_scratch int64 [G, K] receives the flat indices. perturb as above.
+ * Reference: select_final_topk (search/select.py:164-179). */
+int fr_select_final_topk(int64_t* tokens, int64_t* parent_idx, float* cum_out, int64_t* indices_scratch,
+                         const float* cum, const float* top_logprobs, const int64_t* top_tokens,
+                         const float* perturb, int G, int R, int C, int K, cudaStream_t stream);
+
 /* The same step with the candidates taken straight from the level's fp32
  * logits [N*BW, level_width] and their row statistics: every code of the level
  * is a candidate (score = cum + (logit - max) - logsum), so no legal SID is

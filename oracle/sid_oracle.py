@@ -595,3 +595,55 @@ def sid_beam_step(cum, logits, node_ids, trie: Optional[OracleTrie], level_tok_b
     toks = (level_tok_base + torch.arange(kl, dtype=torch.int64))[None, None, :].expand(n, bw, kl)
     return mask_topk_expand(cum, lp, toks, select_k, node_ids=node_ids, trie=trie, token_ids=token_ids, col=col,
                             apply_mask=True)
+
+
+# ---------------------------------------------------------------------------
+# Selection with stop tokens and rank noise (search/select.py, search/expand.py)
+# ---------------------------------------------------------------------------
+def ranked_candidates(cum, top_logprobs, top_tokens, num_out, perturb=None):
+    """_ranked_candidates (search/select.py:72-95): the ``num_out`` best of the rows x C extensions by
+    cum + log-prob (+ perturb for the ranking only), in order; ties by lower flat index.
+    Returns (scores without noise, parent rows, tokens)."""
+    c = int(top_logprobs.shape[1])
+    scores = (cum.float()[:, None] + top_logprobs.float()).reshape(-1).numpy()
+    key = scores if perturb is None else (torch.from_numpy(scores) + perturb.float().reshape(-1)).numpy()
+    order = np.lexsort((np.arange(key.shape[0]), -key.astype(np.float64)))[: int(num_out)]
+    idx = torch.from_numpy(order.copy())
+    return torch.from_numpy(scores)[idx], idx // c, top_tokens.reshape(-1)[idx]
+
+
+def joint_select(cum, top_logprobs, top_tokens, stop_token_ids, beam_width, perturb=None):
+    """joint_select (search/select.py:98-161) as a plain walk over the C best candidates: a stop-token
+    candidate is finished, any other survives, while fewer than ``beam_width`` survivors precede it.
+    Returns a dict with the reference's SelectResult field names (unused slots zero)."""
+    c, k = int(top_logprobs.shape[1]), int(beam_width)
+    scores, parent, tokens = ranked_candidates(cum, top_logprobs, top_tokens, c, perturb)
+    stops = set(int(t) for t in stop_token_ids.reshape(-1).tolist())
+    out = dict(next_tokens=torch.zeros(k, dtype=torch.int64), parent_idx=torch.zeros(k, dtype=torch.int64),
+               new_cum_logprobs=torch.zeros(k), fin_tokens=torch.zeros(c, dtype=torch.int64),
+               fin_parent_idx=torch.zeros(c, dtype=torch.int64), fin_cum_logprobs=torch.zeros(c))
+    surv = fin = 0
+    for i in range(c):
+        if surv >= k:
+            break  # nothing after the k-th survivor is examined
+        if int(tokens[i]) in stops:
+            out["fin_tokens"][fin], out["fin_parent_idx"][fin], out["fin_cum_logprobs"][fin] = tokens[i], parent[i], scores[i]
+            fin += 1
+        else:
+            out["next_tokens"][surv], out["parent_idx"][surv], out["new_cum_logprobs"][surv] = tokens[i], parent[i], scores[i]
+            surv += 1
+    out["num_survivors"], out["num_finished"] = torch.tensor(surv), torch.tensor(fin)
+    return out
+
+
+def select_final_topk(cum, top_logprobs, top_tokens, beam_width, perturb=None):
+    """select_final_topk (search/select.py:164-179)."""
+    scores, parent, tokens = ranked_candidates(cum, top_logprobs, top_tokens, beam_width, perturb)
+    return dict(tokens=tokens, parent_idx=parent, cum_logprobs=scores)
+
+
+def apply_temperature(logprobs, temperature):
+    """apply_temperature (search/expand.py:61-70)."""
+    if temperature is None or temperature <= 0.0 or abs(temperature - 1.0) < 1e-6:
+        return logprobs
+    return log_softmax_rows(logprobs.float() / float(temperature))

@@ -2,7 +2,7 @@
 
 Usage (only where the reference checkout is available):
 
-    python tests/golden/make_golden.py <reference>/python [--only kv_table | prefill_attention | rope_triton_interp]
+    python tests/golden/make_golden.py <reference>/python [--only kv_table | prefill_attention | select | rope_triton_interp]
 
 (``--only NAME`` writes just ``NAME.npz``, leaving the other files as they are; ``rope_triton_interp`` is only
 written that way, in a process of its own.)
@@ -32,6 +32,38 @@ def bits16(t: torch.Tensor) -> np.ndarray:
 
 def bits8(t: torch.Tensor) -> np.ndarray:
     return t.contiguous().view(torch.uint8).numpy().copy()
+
+
+def select_fixture() -> None:
+    """joint_select / select_final_topk / apply_temperature of the reference (search/select.py, search/expand.py)
+    on seeded inputs: with and without stop tokens, with rank noise, with more survivors than candidates allow."""
+    from flashrec.search.expand import apply_temperature
+    from flashrec.search.select import joint_select, select_final_topk
+
+    g = torch.Generator().manual_seed(11)
+    out = {}
+    cases = [(6, 8, 4, [3, 5]), (16, 32, 8, []), (5, 64, 40, [1, 2, 3, 4, 5, 6, 7, 8, 9, 10]), (3, 4, 16, [7])]
+    for i, (r, c, k, stops) in enumerate(cases):
+        cum = torch.randn(r, generator=g)
+        lp = torch.log_softmax(torch.randn(r, c, generator=g), dim=-1)
+        tok = torch.randint(0, 20 if stops else 1000, (r, c), generator=g)
+        pert = -torch.log(-torch.log(torch.rand(r, c, generator=g).clamp_min(1e-30)))
+        st = torch.tensor(stops, dtype=torch.int64)
+        for tag, pt in (("plain", None), ("noise", pert)):
+            res = joint_select(cum, lp, tok, st, k, perturb=pt)
+            for f in ("next_tokens", "parent_idx", "new_cum_logprobs", "num_survivors", "fin_tokens", "fin_parent_idx",
+                      "fin_cum_logprobs", "num_finished"):
+                out[f"c{i}_{tag}_{f}"] = getattr(res, f).numpy()
+            if k <= r * c:
+                fin = select_final_topk(cum, lp, tok, min(k, c), perturb=pt)
+                out[f"c{i}_{tag}_final_tokens"] = fin.tokens.numpy()
+                out[f"c{i}_{tag}_final_parent"] = fin.parent_idx.numpy()
+                out[f"c{i}_{tag}_final_cum"] = fin.cum_logprobs.numpy()
+        out[f"c{i}_cum"], out[f"c{i}_lp"], out[f"c{i}_tok"], out[f"c{i}_pert"] = cum.numpy(), lp.numpy(), tok.numpy(), pert.numpy()
+        out[f"c{i}_stop"], out[f"c{i}_k"] = st.numpy(), np.array(k)
+        out[f"c{i}_temp"] = apply_temperature(lp, 0.7).numpy()
+    out["n_cases"] = np.array(len(cases))
+    np.savez_compressed(HERE / "select.npz", **out)
 
 
 def kv_table_fixture() -> None:
@@ -298,6 +330,7 @@ def main() -> None:
                         token_ids_out=res.token_ids.numpy(), node_out=res.node_ids.numpy())
     kv_table_fixture()
     prefill_attention_fixture()
+    select_fixture()
     print("wrote", sorted(p.name for p in HERE.glob("*.npz")))
 
 
@@ -312,6 +345,8 @@ if __name__ == "__main__":
         kv_table_fixture()
     elif sys.argv[2:4] == ["--only", "prefill_attention"]:
         prefill_attention_fixture()
+    elif sys.argv[2:4] == ["--only", "select"]:
+        select_fixture()
     elif sys.argv[2:4] == ["--only", "rope_triton_interp"]:
         rope_triton_interp_fixture()
     else:

@@ -169,3 +169,110 @@ def test_reference_model_and_graph_runner_with_swapped_kernels_equal_this_decode
     for i in range(L):  # and the KV pools hold the same bytes (slot 0 is the dummy slot the runner's warm-up writes)
         assert torch.equal(pool_a.k[i][1:].view(torch.uint8), pool_b.k[i][1:].view(torch.uint8))
         assert torch.equal(pool_a.v[i][1:].view(torch.uint8), pool_b.v[i][1:].view(torch.uint8))
+
+
+def _write_checkpoint(path, cfg, seed, prequantised):
+    """A tiny Hugging Face style Qwen3 directory: split q / k / v and gate / up matrices, either bf16 or e4m3 with
+    a per-channel ``weight_scale`` (stored as [N, 1], [N] or [1]: every form the loaders accept)."""
+    import json
+
+    from safetensors.torch import save_file
+
+    from oracle import sid_oracle as O
+
+    g = torch.Generator().manual_seed(seed)
+    H, D, I = cfg["hidden_size"], cfg["head_dim"], cfg["intermediate_size"]
+    HQ, HKV, V = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["vocab_size"]
+    tensors = {"model.embed_tokens.weight": (0.02 * torch.randn(V, H, generator=g)).bfloat16(),
+               "model.norm.weight": (1 + 0.1 * torch.randn(H, generator=g)).bfloat16()}
+    for li in range(cfg["num_hidden_layers"]):
+        pre = f"model.layers.{li}."
+        mats = {"self_attn.q_proj": (HQ * D, H), "self_attn.k_proj": (HKV * D, H), "self_attn.v_proj": (HKV * D, H),
+                "self_attn.o_proj": (H, HQ * D), "mlp.gate_proj": (I, H), "mlp.up_proj": (I, H), "mlp.down_proj": (H, I)}
+        for j, (name, (n, k)) in enumerate(mats.items()):
+            w = 0.02 * torch.randn(n, k, generator=g)
+            if prequantised:
+                q8, s = O.quantize_weight_fp8(w)
+                tensors[pre + name + ".weight"] = q8
+                s = s.reshape(-1).float()
+                key = ".weight_scale_inv" if j % 3 == 2 else ".weight_scale"  # both spellings name the scale
+                tensors[pre + name + key] = s.reshape(-1, 1) if j % 2 == 0 else s
+            else:
+                tensors[pre + name + ".weight"] = w.bfloat16()
+        for name, n in (("input_layernorm", H), ("post_attention_layernorm", H), ("self_attn.q_norm", D), ("self_attn.k_norm", D)):
+            tensors[pre + name + ".weight"] = (1 + 0.1 * torch.randn(n, generator=g)).bfloat16()
+    path.mkdir(parents=True, exist_ok=True)
+    save_file({k: v.contiguous() for k, v in tensors.items()}, str(path / "model.safetensors"))
+    (path / "config.json").write_text(json.dumps(cfg))
+    return tensors
+
+
+@pytest.mark.parametrize("prequantised", [True, False])
+def test_checkpoint_loading_equals_the_reference_loader(tmp_path, prequantised):
+    """``flashrec_b200.weights.load_weights`` against the reference's ``load_weights`` (models/weight.py:116-263) on the
+    same checkpoint directory: merged qkv / gate_up matrices and their scales, o / down, norms, embedding — equal
+    byte for byte, for a pre-quantised e4m3 checkpoint (scales concatenated, nothing requantised) and for a bf16
+    checkpoint quantised at load; and the loaded model's decode step equals the reference model's.
+    The bf16 case loads the reference model on the CPU: that is the arithmetic this library reproduces (on a GPU
+    torch turns the reference's ``amax / 448`` into a multiplication by the rounded reciprocal, which moves one
+    scale in a few hundred by one ulp, so the reference's own GPU and CPU loads do not agree with each other)."""
+    refshim.install()
+    import flashrec.models.qwen3 as RQ
+    from flashrec.models.weight import load_hf_config as ref_config
+    from flashrec.models.weight import load_weights as ref_load
+
+    from flashrec_b200.attention import AttentionBackend, TokenToKVPool
+    from flashrec_b200.core import ForwardBatch
+    from flashrec_b200.decoder import Qwen3ForCausalLM
+    from flashrec_b200.weights import load_hf_config, load_weights
+
+    raw = dict(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=2,
+               num_key_value_heads=1, head_dim=128, vocab_size=300, rms_norm_eps=1e-6, rope_theta=1e6,
+               max_position_embeddings=128, tie_word_embeddings=True)
+    _write_checkpoint(tmp_path, raw, 21, prequantised)
+    cfg, rcfg = load_hf_config(str(tmp_path)), ref_config(str(tmp_path))
+    dev = torch.device(DEV)
+    slots, rows, prompt = 256, 64, 9
+    pools = [TokenToKVPool(cfg.num_hidden_layers, slots, cfg.num_key_value_heads, 128, FP8, dev) for _ in range(2)]
+    attn_a = AttentionBackend(pools[0], cfg.num_attention_heads, cfg.num_key_value_heads, 128, beam_width=rows)
+    attn_b = AttentionBackend(pools[1], cfg.num_attention_heads, cfg.num_key_value_heads, 128, beam_width=rows)
+    mine = Qwen3ForCausalLM(cfg, attn_a, dev, fuse_residual=False, fuse_rope_gemm=False)
+    ref_dev = dev if prequantised else torch.device("cpu")
+    theirs = RQ.Qwen3ForCausalLM(rcfg, attn_b, ref_dev, torch.bfloat16)
+    load_weights(mine, str(tmp_path), dev, torch.bfloat16, quantize_fp8=not prequantised)
+    ref_load(theirs, str(tmp_path), ref_dev, torch.bfloat16, quantize_fp8=not prequantised)
+    for a, b in zip(mine.layers, theirs.layers):
+        for x, y in ((a.self_attn.qkv_proj, b.self_attn.qkv_proj), (a.self_attn.o_proj, b.self_attn.o_proj),
+                     (a.mlp.gate_up_proj, b.mlp.gate_up_proj), (a.mlp.down_proj, b.mlp.down_proj)):
+            assert x._fp8_weight.shape == y._fp8_weight.shape
+            assert torch.equal(x._fp8_weight.contiguous().view(torch.uint8).cpu(), y._fp8_weight.contiguous().view(torch.uint8).cpu())
+            assert torch.equal(x._fp8_scale.reshape(-1).cpu(), y._fp8_scale.reshape(-1).float().cpu())
+        for x, y in ((a.input_layernorm, b.input_layernorm), (a.post_attention_layernorm, b.post_attention_layernorm),
+                     (a.self_attn.q_norm, b.self_attn.q_norm), (a.self_attn.k_norm, b.self_attn.k_norm)):
+            assert torch.equal(x.weight.cpu(), y.weight.data.cpu())
+    assert torch.equal(mine.norm.weight.cpu(), theirs.norm.weight.data.cpu())
+    assert torch.equal(mine.embed_tokens.cpu(), theirs.embed_tokens.weight.data.cpu())
+    assert mine.lm_head_weight is mine.embed_tokens  # tied: the checkpoint has no lm_head
+    if not prequantised:
+        return
+    # one decode step of both models on the same batch (each on its own, equally filled pool)
+    g = torch.Generator().manual_seed(4)
+    for p in pools:
+        for li in range(cfg.num_hidden_layers):
+            p.k[li][1:1 + prompt].copy_(torch.randn(prompt, 1, 128, generator=torch.Generator().manual_seed(li)).bfloat16().to(FP8))
+            p.v[li][1:1 + prompt].copy_(torch.randn(prompt, 1, 128, generator=torch.Generator().manual_seed(50 + li)).bfloat16().to(FP8))
+    ids = torch.randint(0, cfg.vocab_size, (rows,), generator=g).to(dev)
+    own = torch.arange(100, 100 + rows)
+    lists = torch.cat([torch.arange(1, 1 + prompt).repeat(rows, 1), own[:, None]], dim=1).to(torch.int32)
+    theirs.rotary.cos_sin_cache.copy_(mine.rotary.cos_sin_cache)
+    outs = []
+    for model, attn in ((mine, attn_a), (theirs, attn_b)):
+        batch = ForwardBatch(input_ids=ids, req_pool_indices=None,
+                             seq_lens=torch.full((rows,), prompt + 1, dtype=torch.int32, device=dev),
+                             positions=torch.full((rows,), prompt, device=dev), out_cache_loc=own.to(dev),
+                             kv_indices=lists.reshape(-1).to(dev),
+                             kv_indptr=(torch.arange(rows + 1, dtype=torch.int32) * (prompt + 1)).to(dev))
+        attn.prepare(batch)
+        with torch.inference_mode():
+            outs.append((model.forward(batch) if model is mine else model(batch)).clone())
+    assert torch.equal(outs[0], outs[1])

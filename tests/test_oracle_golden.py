@@ -204,3 +204,23 @@ def test_fused_qk_norm_rope_float32_arithmetic_matches_reference_triton_kernel()
     assert np.array_equal(truncated, g["q_out_truncated"])
     rounded = bits16(y.to(torch.bfloat16)).astype(np.int32)
     assert np.abs(rounded - g["q_out_truncated"].astype(np.int32)).max() <= 1
+
+
+def test_selection_with_stop_tokens_and_rank_noise_matches_reference():
+    """joint_select / select_final_topk / apply_temperature (search/select.py:72-179, search/expand.py:61-70):
+    the oracle's plain walk against the reference's cumsum / scatter formulation, every output slot."""
+    g = load_golden("select")
+    for i in range(int(g["n_cases"])):
+        cum, lp, tok, pert = (torch.from_numpy(g[f"c{i}_{n}"]) for n in ("cum", "lp", "tok", "pert"))
+        st, k = torch.from_numpy(g[f"c{i}_stop"]), int(g[f"c{i}_k"])
+        for tag, pt in (("plain", None), ("noise", pert)):
+            r = O.joint_select(cum, lp, tok, st, k, pt)
+            for f, v in r.items():
+                assert np.array_equal(np.asarray(v), g[f"c{i}_{tag}_{f}"]), (i, tag, f)
+            if f"c{i}_{tag}_final_tokens" in g.files:
+                kk = g[f"c{i}_{tag}_final_tokens"].shape[0]
+                fr = O.select_final_topk(cum, lp, tok, kk, pt)
+                assert np.array_equal(fr["tokens"].numpy(), g[f"c{i}_{tag}_final_tokens"])
+                assert np.array_equal(fr["parent_idx"].numpy(), g[f"c{i}_{tag}_final_parent"])
+                assert np.array_equal(fr["cum_logprobs"].numpy(), g[f"c{i}_{tag}_final_cum"])
+        assert np.allclose(O.apply_temperature(lp, 0.7).numpy(), g[f"c{i}_temp"], atol=1e-6)
