@@ -158,11 +158,12 @@ def prompt_lengths(n: int, seed: int):
 REF_DIR = ROOT / "oracle" / "_ref"
 
 
-def bench_config(args, world: int, rows: int, catalog_items, decode_steps: int, value_per_gpu=None):
-    """The ``config`` object of the JSON line; both arms print the same keys."""
+def bench_config(args, world: int, rows: int, decode_steps: int):
+    """The ``config`` object of the JSON line: the workload only, so that both arms print the same object
+    (measured quantities such as the per-GPU value or the number of distinct catalog items are top-level keys)."""
     return dict(WORKLOAD, requests=args.requests, beam_width=args.beam, layers=args.layers,
-                catalog_items=catalog_items, trie=args.trie, parallelism=f"dp{world}", rows_per_gpu=rows,
-                value_per_gpu=value_per_gpu, decode_steps_per_wave=decode_steps)
+                catalog_items=args.items, trie=args.trie, parallelism=f"dp{world}", rows_per_gpu=rows,
+                decode_steps_per_wave=decode_steps)
 
 
 class ReferenceCpuStep:
@@ -369,7 +370,7 @@ def run_reference_arm(args):
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": wall / len(vals) * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> bf16 on the host (torch)", "data": "synthetic",
-        "config": bench_config(args, max(args.gpus, 1), args.requests * args.beam, None, len(sizes)),
+        "config": bench_config(args, max(args.gpus, 1), args.requests * args.beam, len(sizes)),
         "cpu_baseline": {"value": v, "unit": UNIT, "cores": ref.cores, "kind": ref.kind, "sample": desc,
                          "samples_timed": len(vals)},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -1218,8 +1219,8 @@ def main():
             "warmup": max(args.warmup, 3), "ms_per_step": sec / args.steps * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> f32 (bf16 activations)",
             "data": "synthetic",
-            "config": bench_config(args, world, eng.rows, int(arrays.n_items), eng.steps - eng.first_step,
-                                   value / world),
+            "config": bench_config(args, world, eng.rows, eng.steps - eng.first_step),
+            "value_per_gpu": value / world, "catalog_items_distinct": int(arrays.n_items),
             "clocks": clk.summary(),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": sec_e2e / args.steps * 1e3},

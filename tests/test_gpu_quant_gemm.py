@@ -333,3 +333,42 @@ def test_qkv_gemm_with_norm_rope_kv_epilogue_equals_the_two_calls(t, n_q, n_kv, 
     assert q.shape == (t, n_q, d)
     assert np.array_equal(bits16(q), bits16(qkv[:, :n_q].contiguous()))
     assert np.array_equal(bits8(kc), bits8(kc_ref)) and np.array_equal(bits8(vc), bits8(vc_ref))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs in one process")
+def test_one_process_drives_a_second_gpu():
+    """Kernels that opt in to more than 48 KB of dynamic shared memory (every tcgen05 GEMM variant, the wide beam
+    step) launched on cuda:0 and then on cuda:1 from one process: the opt-in is per device, so a cache keyed by
+    process would leave the second device without it (launch failure). Same bits on both devices."""
+    from flashrec_b200 import device_status
+    from flashrec_b200.kernel.sglops import (fp8_scaled_mm, fp8_scaled_mm_add_, fp8_scaled_mm_silu_mul,
+                                             interleave_gate_up, per_token_quant_fp8)
+    from flashrec_b200.layers import quantize_weight_fp8
+    from flashrec_b200.sid_decode import sid_beam_step
+
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(1024, 512, generator=g).bfloat16()
+    w = 0.05 * torch.randn(1024, 512, generator=g)
+    res = torch.randn(1024, 1024, generator=g).bfloat16()
+    logits = torch.randn(2 * 64, 4096, generator=g)
+    outs = []
+    for dev in ("cuda:0", "cuda:1"):
+        with torch.cuda.device(dev):
+            q, s = per_token_quant_fp8(x.to(dev))
+            wq, ws = quantize_weight_fp8(w.to(dev))
+            y = fp8_scaled_mm(q, wq.t(), s, ws, torch.bfloat16)               # pair kernel (M = 1024)
+            y512 = fp8_scaled_mm(q[:512], wq.t(), s[:512], ws, torch.bfloat16)  # one CTA per tile
+            wi, si = interleave_gate_up(wq, ws)
+            ys, amax = fp8_scaled_mm_silu_mul(q, wi, s, si)
+            r = res.to(dev).clone()
+            fp8_scaled_mm_add_(q, wq.t(), s, ws, r)
+            lg = logits.to(dev)
+            mx = lg.amax(dim=-1)
+            ls = torch.log(torch.exp(lg - mx[:, None]).sum(-1))
+            cum = torch.zeros(2, 64, device=dev)
+            st = sid_beam_step(cum, lg, mx, ls, None, None, 0, 2048)           # K = 2048: wide shared memory
+            torch.cuda.synchronize()
+            assert device_status() == (0, 0)
+            outs.append([t.cpu() for t in (y, y512, ys, amax, r, st.vals, st.indices)])
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
