@@ -50,6 +50,11 @@ def parse():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="config4", choices=["config4", "config5"],
+                    help="config4 (default): 32 requests x 512 beams, 3 x 8192 codes, 1M items, prompts 128-1024. "
+                         "config5: the widest configuration as one replica per GPU: 2048 beams, 4 x 4096 codes, 10M "
+                         "Zipf items, prompts 1024-4096 (give --requests; 64 requests over the GPUs of a box is the "
+                         "stated concurrency)")
     ap.add_argument("--requests", type=int, default=32)
     ap.add_argument("--beam", type=int, default=512)
     ap.add_argument("--layers", type=int, default=28)
@@ -145,11 +150,21 @@ def make_catalog(items: int, sizes, seed=0):
     return np.stack([rng.integers(0, s, items) for s in sizes], axis=1)
 
 
-def prompt_lengths(n: int, seed: int):
+def prompt_lengths(n: int, seed: int, lo: int = 128, hi: int = 1024):
     import numpy as np
 
     rng = np.random.default_rng(1000 + seed)
-    return [int(x) for x in rng.integers(128, 1025, n)]
+    return [int(x) for x in rng.integers(lo, hi + 1, n)]
+
+
+def make_zipf_catalog(items: int, sizes, seed=0):
+    """Popular first and second codes (Zipf 1.1), uniform deeper codes: a few nodes with thousands of children."""
+    import numpy as np
+
+    rng = np.random.default_rng(seed)
+    cols = [np.minimum(rng.zipf(1.1, items) - 1, s - 1) if l < 2 else rng.integers(0, s, items)
+            for l, s in enumerate(sizes)]
+    return np.stack(cols, axis=1)
 
 
 # ---------------------------------------------------------------------------
@@ -1059,13 +1074,21 @@ def main():
         return
     sizes = [8192] * 3
     token_base = 151_936
+    p_lo, p_hi = 128, 1024
+    if args.workload == "config5":
+        sizes, p_lo, p_hi = [4096] * 4, 1024, 4096
+        args.beam = 2048 if args.beam == 512 else args.beam
+        args.items = 10_000_000 if args.items == 1_000_000 else args.items
+        WORKLOAD.update(workload="qwen3-1.7b-shaped 28-layer FP8 W8A8 decode, fp8 KV, 4-level SID (4x4096), 10M-item "
+                                 "Zipf catalog (CSR trie), one replica per GPU", levels=4,
+                        prompt_len="uniform[1024,4096]")
     cfg = Qwen3Config(num_hidden_layers=args.layers)
-    catalog = make_catalog(args.items, sizes)
+    catalog = make_zipf_catalog(args.items, sizes) if args.workload == "config5" else make_catalog(args.items, sizes)
     # sort-based build on the GPU, straight into the layout the beam step reads
     trie = build_trie_device(torch.from_numpy(np.ascontiguousarray(catalog, dtype=np.int32)).to(dev), sizes,
                              token_base, layout=args.trie)
     arrays = trie.arrays
-    eng = SidDecodeEngine(cfg, args.requests, args.beam, prompt_lengths(args.requests, rank), sizes, token_base, trie,
+    eng = SidDecodeEngine(cfg, args.requests, args.beam, prompt_lengths(args.requests, rank, p_lo, p_hi), sizes, token_base, trie,
                           dev, shared_prefix=64, page_size=16, seed=rank, fuse_rope_gemm=not args.no_fuse_rope_gemm,
                           level0_from_prefill=args.level0_from_prefill, fused_head=not args.no_fused_head)
     # Prefill of the prompts (eager, one extend batch): the decode waves below then read real K/V. Timed on
@@ -1081,7 +1104,7 @@ def main():
         torch.cuda.synchronize()
         pms = e0.elapsed_time(e1)
         prefill = {"tokens": eng.prefill_tokens, "ms": pms, "tokens_per_s": eng.prefill_tokens / pms * 1e3,
-                   "note": "prompts U[128,1024], 64-token shared prefix computed once (cached prefix for the rest)"}
+                   "note": f"prompts U[{p_lo},{p_hi}], 64-token shared prefix computed once (cached prefix for the rest)"}
     if args.profile_prefill:
         eng.prefill()
         torch.cuda.synchronize()
