@@ -372,3 +372,29 @@ def test_one_process_drives_a_second_gpu():
             outs.append([t.cpu() for t in (y, y512, ys, amax, r, st.vals, st.indices)])
     for a, b in zip(*outs):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("m,n,k", [(512, 4096, 2048), (512, 2048, 2048), (300, 4096, 256), (1000, 2048, 384), (129, 4096, 128)])
+def test_few_row_gemms_equal_across_tilings(m, n, k):
+    """A decode step of one request (a few hundred rows): whatever tiling the library picks, plain and
+    add-into-residual outputs must equal, bit for bit, the one-CTA-per-tile kernel (tile hint 128 / 64) and the
+    256 x 256 pair kernel (hint 512), with ragged last row blocks; and the oracle within the GEMM tolerance."""
+    from flashrec_b200.kernel.sglops import fp8_scaled_mm, fp8_scaled_mm_add_, per_token_quant_fp8
+    from flashrec_b200.layers import quantize_weight_fp8
+
+    g = torch.Generator().manual_seed(m + n + k)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    w = 0.05 * torch.randn(n, k, generator=g)
+    res = torch.randn(m, n, generator=g).bfloat16()
+    q, s = per_token_quant_fp8(x.to(DEV))
+    wq, ws = quantize_weight_fp8(w.to(DEV))
+    y = fp8_scaled_mm(q, wq.t(), s, ws, torch.bfloat16)
+    for hint in (64, 128, 512):
+        assert torch.equal(y, fp8_scaled_mm(q, wq.t(), s, ws, torch.bfloat16, block_n=hint)), hint
+    ref = O.fp8_scaled_mm(q.cpu(), wq.cpu(), s.cpu(), ws.cpu()).float()
+    assert ((y.float().cpu() - ref).abs().max() / ref.abs().max()) < 2e-2
+    want = (y.float() + res.to(DEV).float()).bfloat16()
+    for hint in (0, 64, 128, 512):
+        r = res.to(DEV).clone()
+        fp8_scaled_mm_add_(q, wq.t(), s, ws, r, block_n=hint)
+        assert torch.equal(r, want), hint
