@@ -1213,7 +1213,7 @@ def main():
             "bound": "tensor", "achieved": achieved, "peak": peak_fp8, "unit": "TFLOP/s",
             "frac": achieved / peak_fp8, "traffic": traffic,
             "kernel": "gemm_fp8_pair_kernel<bf16, EPI=1> (gate_up GEMM + SwiGLU epilogue, M=%d N=12288 K=2048; "
-                      "31 %% of the wave)" % eng.rows,
+                      "35 %% of the wave)" % eng.rows,
             "us_per_launch": fused_sec * 1e6,
             "peak_source": ("2 x measured bf16 burst (MEASURED_PEAKS.json)" if peaks else "2 x fallback 1.59 PFLOP/s")
             + "; nominal dense FP8 4500",
