@@ -34,6 +34,8 @@ _SWAPS = {
                                    "beam_expand_token_ids", "genrec_mask_topk_expand", "call_genrec_cuda",
                                    "try_load_beam_trie"]),
     "flashrec.attention.kv_indices": ("flashrec_b200.attention", ["gather_kv_indices"]),
+    "flashrec.search.select": ("flashrec_b200.search", ["joint_select", "select_final_topk"]),
+    "flashrec.search.expand": ("flashrec_b200.search", ["apply_temperature", "gumbel_like"]),
 }
 _installed = {}
 

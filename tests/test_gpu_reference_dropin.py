@@ -276,3 +276,51 @@ def test_checkpoint_loading_equals_the_reference_loader(tmp_path, prequantised):
         with torch.inference_mode():
             outs.append((model.forward(batch) if model is mine else model(batch)).clone())
     assert torch.equal(outs[0], outs[1])
+
+
+def test_reference_expand_step_with_stop_tokens_on_the_swapped_selection_kernels():
+    """The reference's own ``expand_step`` (search/expand.py:240-372) in its stop-token branch and its
+    end-by-length branch, on CUDA tensors with ``joint_select`` / ``select_final_topk`` swapped for this
+    library's (``fr_joint_select``, ``fr_select_final_topk``), against the same calls on the CPU with the
+    reference's own selection: beams, scores, token planes and finished sequences equal step by step; and
+    with a fixed Gumbel noise tensor (sampling without replacement) the two sides still agree."""
+    refshim.install()
+    import torch.nn.functional as F
+    import flashrec.search.expand as RE
+    from flashrec.search.expand import expand_step, init_from_prefill
+
+    g = torch.Generator().manual_seed(5)
+    vocab, bw, cand = 50, 8, 16
+    lp0 = F.log_softmax(torch.randn(vocab, generator=g), -1)
+    steps = [(torch.stack([torch.randperm(vocab, generator=g)[:cand] for _ in range(bw)]),
+              F.log_softmax(torch.randn(bw, cand, generator=g), -1)) for _ in range(3)]
+    noise = [-torch.log(-torch.log(torch.rand(bw, cand, generator=g).clamp_min(1e-20))) for _ in range(3)]
+    stops = [3, 7, 11, 19]
+
+    def run(device, temperature):
+        bl = init_from_prefill(lp0.to(device), beam_width=bw, beam_candidates=cand, max_new_tokens=4, prompt_len=1)
+        trace = []
+        for i, (tt, tl) in enumerate(steps):
+            if temperature > 0:  # the same noise on both sides instead of each device's own generator
+                fixed = noise[i].to(device)
+                RE.gumbel_like = lambda x, fixed=fixed: fixed
+            rows = int(bl.cum_logprobs.shape[0])
+            par = expand_step(bl, tt[:rows].to(device), tl[:rows].to(device), bw, stop_token_ids=stops, ignore_eos=False,
+                              will_finish=(i == 2), temperature=temperature)
+            trace.append((None if par is None else par.cpu(), bl.last_tokens.cpu(), bl.cum_logprobs.cpu(),
+                          bl.token_ids[: bl.last_tokens.shape[0]].cpu()))
+        return trace, [(tuple(s.tokens), round(s.cum_logprob, 5)) for s in bl.completed]
+
+    keep = RE.gumbel_like
+    try:
+        for temperature in (0.0, 1.0):
+            cpu_trace, cpu_done = run(torch.device("cpu"), temperature)
+            gpu_trace, gpu_done = run(torch.device(DEV), temperature)
+            assert cpu_done == gpu_done and len(cpu_done) > 0
+            for a, b in zip(cpu_trace, gpu_trace):
+                assert (a[0] is None) == (b[0] is None)
+                if a[0] is not None:
+                    assert torch.equal(a[0], b[0])
+                assert torch.equal(a[1], b[1]) and torch.equal(a[2], b[2]) and torch.equal(a[3], b[3])
+    finally:
+        RE.gumbel_like = keep
