@@ -710,6 +710,44 @@ def ref_kernels_compare(rows: int):
             (lambda: (_ for _ in ()).throw(RuntimeError("beam_trie.cuh did not build through tvm_ffi"))),
             n * bw * c * (4 + 8) * 2)
     out["genrec_mask_topk_expand"]["shape"] = f"N={n} BW={bw} C={c} dense trie {nodes_n} x {vsz}"
+    # selection with stop tokens and Gumbel rank noise: every request in one launch here, one call per request in
+    # the reference (torch ops: topk, isin, cumsum, scatter), as its expand_step calls it
+    import flashrec_b200.search as b_sel
+    try:
+        import flashrec.search.select as r_sel
+    except Exception:
+        r_sel = None
+    cj = 256
+    lpj = torch.log_softmax(torch.randn(n, bw, cj, generator=g, device=dev), dim=-1)
+    tkj = torch.randint(0, 4000, (n, bw, cj), generator=g, device=dev)
+    stop = torch.arange(0, 40, device=dev)
+    pert = b_sel.gumbel_like(lpj)
+
+    def ref_joint():
+        if r_sel is None:
+            raise RuntimeError("flashrec.search.select not importable")
+        for i in range(n):
+            r_sel.joint_select(cum[i], lpj[i], tkj[i], stop, bw, perturb=pert[i])
+
+    compare("joint_select", lambda: b_sel.joint_select(cum, lpj, tkj, stop, bw, perturb=pert), ref_joint,
+            n * bw * cj * (4 + 8 + 4))
+    if "reference_us" not in out["joint_select"]:
+        # the reference's version cannot be captured (torch.isin synchronises): time it eagerly, 20 calls between events
+        try:
+            for _ in range(3):
+                ref_joint()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(20):
+                ref_joint()
+            e1.record()
+            torch.cuda.synchronize()
+            out["joint_select"].pop("reference_unavailable", None)
+            out["joint_select"]["reference_us"] = round(e0.elapsed_time(e1) * 1e3 / 20, 2)
+            out["joint_select"]["reference_note"] = "eager launches (not capturable in a CUDA graph)"
+        except Exception as exc:
+            out["joint_select"]["reference_unavailable"] = "unavailable on this box: " + repr(exc)[:200]
+    out["joint_select"]["shape"] = f"{n} requests x {bw} rows x {cj} candidates, 40 stop tokens, rank noise"
     print(json.dumps({"ref_kernels_rows": rows, "kernels": out}))
 
 
