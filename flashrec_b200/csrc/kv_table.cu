@@ -99,16 +99,56 @@ __device__ __forceinline__ void warp_copy_words(const int32_t* __restrict__ src,
   for (; c < end; c += 32) dst[c] = __ldg(src + c);
 }
 
-__global__ void __launch_bounds__(256) gather_kv_kernel(const int32_t* __restrict__ table, int64_t stride,
-                                                       const int64_t* __restrict__ rows,
-                                                       const int32_t* __restrict__ seq_lens,
-                                                       const int32_t* __restrict__ indptr, int32_t* __restrict__ out,
-                                                       int n, int capacity) {
-  const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (r >= n) return;
-  const int lane = threadIdx.x & 31;
+// The offsets and the copy in one launch: a CTA owns 32 consecutive rows (one warp each) and finds the offset of
+// its first row itself, by summing every length before it (the lengths are a few KB that every CTA of an SM
+// reads from L1; 512 CTAs reading 8 K values on average is a fraction of the slot ids the copy moves), so there
+// is no scan kernel in front and no dependency between CTAs. indptr is written along the way.
+// (ROWS = 32 rows per CTA for long lists; 8 for a few hundred rows, where more, smaller CTAs start sooner.)
+template <int kFusedRows>
+__global__ void __launch_bounds__(kFusedRows * 32) gather_kv_fused_kernel(
+    const int32_t* __restrict__ table, int64_t stride, const int64_t* __restrict__ rows,
+    const int32_t* __restrict__ seq_lens, int32_t* __restrict__ indptr, int32_t* __restrict__ out, int n, int capacity) {
+  __shared__ int32_t warp_part[kFusedRows];
+  __shared__ int32_t row_off[32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int r0 = blockIdx.x * kFusedRows;
+  // sum of the lengths before row r0 (r0 is a multiple of 32: whole int4 groups when the array is aligned)
+  int32_t acc = 0;
+  if ((reinterpret_cast<uintptr_t>(seq_lens) & 15u) == 0) {
+    const int4* q = reinterpret_cast<const int4*>(seq_lens);
+    for (int i = threadIdx.x; i < r0 / 4; i += blockDim.x) {
+      const int4 v = __ldg(q + i);
+      acc += max(v.x, 0) + max(v.y, 0) + max(v.z, 0) + max(v.w, 0);
+    }
+  } else {
+    for (int i = threadIdx.x; i < r0; i += blockDim.x) acc += max(__ldg(seq_lens + i), 0);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) warp_part[warp] = acc;
+  __syncthreads();
+  if (warp == 0) {
+    int32_t base = lane < kFusedRows ? warp_part[lane] : 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) base += __shfl_xor_sync(0xffffffffu, base, o);
+    // exclusive offsets of this CTA's rows
+    const int r = r0 + lane;
+    const int32_t len = (r < n && lane < kFusedRows) ? max(__ldg(seq_lens + r), 0) : 0;
+    int32_t incl = len;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int32_t y = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += y;
+    }
+    row_off[lane] = base + incl - len;
+    if (r < n && lane < kFusedRows) indptr[r + 1] = base + incl;
+    if (r0 == 0 && lane == 0) indptr[0] = 0;
+  }
+  __syncthreads();
+  const int r = r0 + warp;
+  if (r >= n || capacity == 0) return;
   const int32_t sl = max(seq_lens[r], 0);
-  const int32_t off = indptr[r];
+  const int32_t off = row_off[warp];
   const int32_t* src = table + rows[r] * stride;
   warp_copy_words(src, out + off, 0, sl, capacity - off, lane);
 }
@@ -214,11 +254,12 @@ extern "C" int fr_gather_kv_indices(const int32_t* req_to_token, int64_t row_str
   FR_CHECK_ARG(n >= 0 && out_capacity >= 0);
   if (n == 0) return FR_OK;
   FR_CHECK_ARG(req_to_token && rows && seq_lens && indptr_out && (out || out_capacity == 0));
-  seq_scan_kernel<<<1, 1024, 0, stream>>>(seq_lens, indptr_out, n);
-  if (launch_status() != FR_OK) return FR_ERR_CUDA;
-  if (out_capacity == 0) return FR_OK;
-  gather_kv_kernel<<<ceil_div(n, 8), 256, 0, stream>>>(req_to_token, row_stride, rows, seq_lens, indptr_out, out, n,
-                                                      out_capacity);
+  if (n <= 4096)
+    gather_kv_fused_kernel<8><<<ceil_div(n, 8), 256, 0, stream>>>(req_to_token, row_stride, rows, seq_lens, indptr_out, out,
+                                                                 n, out_capacity);
+  else
+    gather_kv_fused_kernel<32><<<ceil_div(n, 32), 1024, 0, stream>>>(req_to_token, row_stride, rows, seq_lens, indptr_out,
+                                                                    out, n, out_capacity);
   return launch_status();
 }
 
