@@ -409,42 +409,65 @@ class SidDecodeEngine:
             self.h_tokens.copy_(self.tok_planes[last], non_blocking=True)
             torch.cuda.current_stream(self.device).synchronize()
 
-    def prefill(self) -> torch.Tensor:
+    def prefill(self, chunk_tokens: Optional[int] = None) -> torch.Tensor:
         """Run the model over the prompts (seeded random token ids) so that the pool holds their real
-        K/V instead of the synthetic fill, as one extend batch: request 0 computes the shared prefix,
-        the others take it as a cached prefix (a radix hit; ``extend_prefix_lens``, core.py:81-101) and
-        extend only their own tokens. Eager, like the reference's prefill. Returns the hidden state
-        of each request's last prompt token, ``[n_requests, hidden]`` (engine/engine.py:286-303)."""
+        K/V instead of the synthetic fill. Request 0 computes the shared prefix, the others take it as a
+        cached prefix (a radix hit; ``extend_prefix_lens``, core.py:81-101) and extend only their own tokens.
+        By default everything is one extend batch. With ``chunk_tokens`` every request extends at most that
+        many tokens per pass (chunked prefill, for prompts that do not fit one batch): each pass is an extend
+        batch over what the earlier passes left in the pool; the other requests join in the pass in which
+        request 0 completes the shared prefix (inside a layer K/V are written before attention reads them).
+        Eager, like the reference's prefill. Returns the hidden state of each request's last prompt token,
+        ``[n_requests, hidden]`` (engine/engine.py:286-303)."""
         dev = self.device
         sp = self.shared_prefix
         pre = [0 if r == 0 else min(sp, p) for r, p in enumerate(self.prompt_lens)]
-        ext = [p - q for p, q in zip(self.prompt_lens, pre)]
-        if min(ext) <= 0:
+        if min(p - q for p, q in zip(self.prompt_lens, pre)) <= 0:
             raise ValueError("every request needs at least one token of its own after the shared prefix")
         g = torch.Generator().manual_seed(self.seed + 17)
         shared_ids = torch.randint(0, self.token_base, (sp,), generator=g)
-        ids, pos = [], []
+        full_ids = []
         for r, plen in enumerate(self.prompt_lens):
             own = torch.randint(0, self.token_base, (plen - min(sp, plen),), generator=g)
-            full = torch.cat((shared_ids[: min(sp, plen)], own))
-            ids.append(full[pre[r]:])
-            pos.append(torch.arange(pre[r], plen))
-        seq = torch.tensor(self.prompt_lens, dtype=torch.int32, device=dev)
-        n_idx = sum(self.prompt_lens)
-        kv_indices = torch.empty(n_idx, dtype=torch.int32, device=dev)
-        kv_indptr = torch.empty(self.n + 1, dtype=torch.int32, device=dev)
-        kv_table_step(self.req_to_token, self.prefill_rows, seq, kv_indices, kv_indptr)  # plain gather
+            full_ids.append(torch.cat((shared_ids[: min(sp, plen)], own)))
         table = self.req_to_token[self.rows:].cpu()
-        loc = torch.cat([table[r, pre[r]: self.prompt_lens[r]] for r in range(self.n)]).to(torch.int64)
-        qo = torch.zeros(self.n + 1, dtype=torch.int32)
-        qo[1:] = torch.cumsum(torch.tensor(ext), 0)
-        batch = ForwardBatch(input_ids=torch.cat(ids).to(dev), req_pool_indices=self.prefill_rows, seq_lens=seq,
-                             positions=torch.cat(pos).to(dev), out_cache_loc=loc.to(dev), is_prefill=True,
-                             kv_indices=kv_indices, kv_indptr=kv_indptr, extend_prefix_lens=pre,
-                             extend_seq_lens=ext, qo_indptr=qo.to(dev))
-        hidden = self.model.forward(batch)
-        self.prefill_tokens = int(qo[-1])
-        self.prefill_hidden = self.model.last_token_hidden(hidden, batch)
+        chunk = int(chunk_tokens) if chunk_tokens else max(self.prompt_lens)
+        if chunk <= 0:
+            raise ValueError("chunk_tokens must be positive")
+        # the pass in which request 0 has the whole shared prefix in the pool: the others start there
+        first_pass = [0] + [max(0, -(-min(sp, self.prompt_lens[0]) // chunk) - 1)] * (self.n - 1)
+        done = list(pre)  # tokens of each request already in the pool
+        last_hidden = torch.empty((self.n, self.cfg.hidden_size), dtype=torch.bfloat16, device=dev)
+        self.prefill_tokens = 0
+        k = 0
+        while any(d < p for d, p in zip(done, self.prompt_lens)):
+            reqs = [r for r in range(self.n) if done[r] < self.prompt_lens[r] and k >= first_pass[r]]
+            ext = [min(chunk, self.prompt_lens[r] - done[r]) for r in reqs]
+            seq_l = [done[r] + e for r, e in zip(reqs, ext)]
+            rows = self.prefill_rows[torch.tensor(reqs, dtype=torch.int64, device=dev)]
+            seq = torch.tensor(seq_l, dtype=torch.int32, device=dev)
+            kv_indices = torch.empty(sum(seq_l), dtype=torch.int32, device=dev)
+            kv_indptr = torch.empty(len(reqs) + 1, dtype=torch.int32, device=dev)
+            kv_table_step(self.req_to_token, rows, seq, kv_indices, kv_indptr)  # plain gather
+            loc = torch.cat([table[r, done[r]: done[r] + e] for r, e in zip(reqs, ext)]).to(torch.int64)
+            qo = torch.zeros(len(reqs) + 1, dtype=torch.int32)
+            qo[1:] = torch.cumsum(torch.tensor(ext), 0)
+            batch = ForwardBatch(
+                input_ids=torch.cat([full_ids[r][done[r]: done[r] + e] for r, e in zip(reqs, ext)]).to(dev),
+                req_pool_indices=rows, seq_lens=seq,
+                positions=torch.cat([torch.arange(done[r], done[r] + e) for r, e in zip(reqs, ext)]).to(dev),
+                out_cache_loc=loc.to(dev), is_prefill=True, kv_indices=kv_indices, kv_indptr=kv_indptr,
+                extend_prefix_lens=[done[r] for r in reqs], extend_seq_lens=ext, qo_indptr=qo.to(dev))
+            hidden = self.model.forward(batch)
+            last = self.model.last_token_hidden(hidden, batch)
+            for i, (r, e) in enumerate(zip(reqs, ext)):
+                done[r] += e
+                if done[r] == self.prompt_lens[r]:
+                    last_hidden[r] = last[i]
+            self.prefill_tokens += int(qo[-1])
+            k += 1
+        self.prefill_passes = k
+        self.prefill_hidden = last_hidden
         return self.prefill_hidden
 
     # results of the last run (device tensors)

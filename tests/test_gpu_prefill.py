@@ -191,3 +191,47 @@ def test_prefill_attention_empty_request_and_unaligned_lengths():
     ref = O.prefill_attention(q, kc, vc, qo, kv, kvi, hq // hkv).float()
     assert (out.float().cpu() - ref).abs().max() / ref.abs().max() < 2e-2
     assert torch.isfinite(out.float()).all()
+
+
+@pytest.mark.parametrize("chunk", [64, 5, 1000])
+def test_chunked_prefill_leaves_the_same_pool_as_one_batch(chunk):
+    """``SidDecodeEngine.prefill(chunk_tokens=...)``: every request extends at most ``chunk`` tokens per pass over
+    what the earlier passes left in the pool (chunk 5 is shorter than the 16-token shared prefix: the other
+    requests wait for request 0 to finish it). Layer 0's K bytes depend on no attention and must equal the
+    one-batch prefill exactly; deeper layers and the last-token hidden states see attention computed over a
+    cached prefix instead of inside one batch (same arithmetic, other tile boundaries): nearly all e4m3 bytes
+    equal, hidden states within the attention tolerance. A chunk that covers every prompt is the one-batch run."""
+    from flashrec_b200.decoder import Qwen3Config
+    from flashrec_b200.sid_decode import SidDecodeEngine
+    from flashrec_b200.trie import build_trie_arrays, trie_to_device
+
+    cfg = Qwen3Config(hidden_size=256, num_attention_heads=2, num_key_value_heads=1, head_dim=128,
+                      intermediate_size=512, num_hidden_layers=3, max_position_embeddings=512, vocab_size=1000 + 64)
+    rng = np.random.default_rng(2)
+    sizes, base = [32, 32], 1000
+    trie = trie_to_device(build_trie_arrays(np.stack([rng.integers(0, 32, 300) for _ in sizes], 1), sizes, base), "csr", DEV)
+    prompts = [97, 30, 200]
+
+    def run(chunk_tokens):
+        eng = SidDecodeEngine(cfg, 3, 32, prompts, sizes, base, trie, DEV, shared_prefix=16, seed=3, use_graphs=False)
+        h = eng.prefill(chunk_tokens=chunk_tokens).clone()
+        table = eng.req_to_token[eng.rows:].cpu()
+        slots = torch.cat([table[r, :p] for r, p in enumerate(prompts)]).to(torch.int64).to(DEV)
+        kv = [(eng.pool.k[l][slots].view(torch.uint8).clone(), eng.pool.v[l][slots].view(torch.uint8).clone())
+              for l in range(cfg.num_hidden_layers)]
+        return h, kv, eng
+
+    h1, kv1, e1 = run(None)
+    h2, kv2, e2 = run(chunk)
+    assert e1.prefill_passes == 1 and e1.prefill_tokens == e2.prefill_tokens == 97 + (30 - 16) + (200 - 16)
+    if chunk >= max(prompts):
+        assert e2.prefill_passes == 1 and torch.equal(h1, h2)
+        assert all(torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) for a, b in zip(kv1, kv2))
+        return
+    assert e2.prefill_passes >= -(-(200 - 16) // chunk)  # the longest request extends 184 tokens of its own
+    assert torch.equal(kv1[0][0], kv2[0][0]) and torch.equal(kv1[0][1], kv2[0][1])
+    for l in range(1, cfg.num_hidden_layers):
+        for a, b in zip(kv1[l], kv2[l]):
+            assert (a != b).float().mean() < 0.05, l
+    d = (h1.float() - h2.float()).abs()
+    assert d.max() / h1.float().abs().max() < 0.15 and d.mean() / h1.float().abs().mean() < 2e-2
