@@ -547,6 +547,7 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       // ---- normalise and store ----------------------------------------------------
       const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
       __nv_bfloat16* op = p.out + row * p.o_t + head * kD;
+      const bool wide_out = (reinterpret_cast<uintptr_t>(p.out) & 31u) == 0 && (p.o_t & 15) == 0;  // CTA-uniform
 #pragma unroll 1
       for (int c = 0; c < kD / 32; ++c) {
         uint32_t o[32];
@@ -558,15 +559,20 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
           for (int i = 0; i < 32; ++i) o[i] = 0u;
         }
         if (live) {
-          uint4* dst = reinterpret_cast<uint4*>(op + c * 32);
+          uint32_t w[16];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint4 w;
-            w.x = pack_bf16(__uint_as_float(o[8 * i + 0]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
-            w.y = pack_bf16(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
-            w.z = pack_bf16(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
-            w.w = pack_bf16(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
-            dst[i] = w;
+          for (int i = 0; i < 16; ++i)
+            w[i] = pack_bf16(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
+          __nv_bfloat16* dst = op + c * 32;
+          if (wide_out) {  // 32-byte stores: one full sector per instruction (rows are 4 KB apart)
+            const uint32_t w0[8] = {w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]};
+            const uint32_t w1[8] = {w[8], w[9], w[10], w[11], w[12], w[13], w[14], w[15]};
+            ptx::st_global_v8(dst, w0);
+            ptx::st_global_v8(dst + 16, w1);
+          } else {
+            uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) d4[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
           }
         }
       }
