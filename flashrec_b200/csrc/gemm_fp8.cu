@@ -58,21 +58,27 @@ struct Cfg {
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kScaleBytes + kBarBytes;
 };
 
+// `wide`: dst is 32-byte aligned, so a thread's chunk leaves as whole 32-byte sectors (rows are far apart:
+// a 16-byte store fills half a sector per instruction).
 template <typename OutT>
-__device__ __forceinline__ void store_chunk32(OutT* dst, const float (&v)[32], int ncols_valid);
+__device__ __forceinline__ void store_chunk32(OutT* dst, const float (&v)[32], int ncols_valid, bool wide);
 
 template <>
-__device__ __forceinline__ void store_chunk32<__nv_bfloat16>(__nv_bfloat16* dst, const float (&v)[32], int nvalid) {
+__device__ __forceinline__ void store_chunk32<__nv_bfloat16>(__nv_bfloat16* dst, const float (&v)[32], int nvalid,
+                                                             bool wide) {
   if (nvalid >= 32) {
-    uint4* d4 = reinterpret_cast<uint4*>(dst);
+    uint32_t w[16];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      uint4 o;
-      o.x = pack_bf16(v[8 * i + 0], v[8 * i + 1]);
-      o.y = pack_bf16(v[8 * i + 2], v[8 * i + 3]);
-      o.z = pack_bf16(v[8 * i + 4], v[8 * i + 5]);
-      o.w = pack_bf16(v[8 * i + 6], v[8 * i + 7]);
-      d4[i] = o;
+    for (int i = 0; i < 16; ++i) w[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
+    if (wide) {
+      const uint32_t w0[8] = {w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]};
+      const uint32_t w1[8] = {w[8], w[9], w[10], w[11], w[12], w[13], w[14], w[15]};
+      ptx::st_global_v8(dst, w0);
+      ptx::st_global_v8(dst + 16, w1);
+    } else {
+      uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) d4[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
     }
   } else {
 #pragma unroll
@@ -82,11 +88,21 @@ __device__ __forceinline__ void store_chunk32<__nv_bfloat16>(__nv_bfloat16* dst,
 }
 
 template <>
-__device__ __forceinline__ void store_chunk32<float>(float* dst, const float (&v)[32], int nvalid) {
+__device__ __forceinline__ void store_chunk32<float>(float* dst, const float (&v)[32], int nvalid, bool wide) {
   if (nvalid >= 32) {
-    float4* d4 = reinterpret_cast<float4*>(dst);
+    if (wide) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) d4[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t w[8] = {__float_as_uint(v[8 * i]),     __float_as_uint(v[8 * i + 1]), __float_as_uint(v[8 * i + 2]),
+                               __float_as_uint(v[8 * i + 3]), __float_as_uint(v[8 * i + 4]), __float_as_uint(v[8 * i + 5]),
+                               __float_as_uint(v[8 * i + 6]), __float_as_uint(v[8 * i + 7])};
+        ptx::st_global_v8(dst + 8 * i, w);
+      }
+    } else {
+      float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) d4[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    }
   } else {
 #pragma unroll
     for (int i = 0; i < 32; ++i)
@@ -266,6 +282,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const uint32_t taddr_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BLOCK_N;
       if constexpr (EPI == 0 || EPI == 2) {
         OutT* out_row = out + static_cast<int64_t>(row) * ldo + n0;
+        const bool wide_out = (reinterpret_cast<uintptr_t>(out) & 31u) == 0 && (ldo * sizeof(OutT)) % 32 == 0;
 #pragma unroll 1
         for (int c = part; c < BLOCK_N / 32; c += kSplit) {
           uint32_t r[32];
@@ -289,7 +306,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                 if (j < nvalid) v[j] = __fadd_rn(round_bf16(v[j]), __bfloat162float(res[j]));
             }
           }
-          if (row < M && nvalid > 0) store_chunk32<OutT>(out_row + c * 32, v, nvalid);
+          if (row < M && nvalid > 0) store_chunk32<OutT>(out_row + c * 32, v, nvalid, wide_out);
         }
       } else {
         __nv_bfloat16* out_row = reinterpret_cast<__nv_bfloat16*>(out) + static_cast<int64_t>(row) * ldo + n0 / 2;
@@ -309,7 +326,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             v[j] = y;
             amax = fmaxf(amax, fabsf(y));
           }
-          if (row < M) store_chunk32<__nv_bfloat16>(out_row + c * 32, v, 32);
+          if (row < M) store_chunk32<__nv_bfloat16>(out_row + c * 32, v, 32, false);
         }
         if (row < M) atomicMax(row_amax + row, __float_as_uint(amax));
       }
