@@ -86,3 +86,20 @@ def test_joint_select_ties_rank_by_flat_index_and_graph_capture():
     for r in (got, got2):
         for f in FIELDS:
             assert torch.equal(getattr(r, f).cpu(), torch.as_tensor(ref[f])), f
+
+
+def test_joint_select_argument_limits():
+    """More candidates per row than the select supports is refused before any launch; zero groups is a no-op."""
+    from flashrec_b200 import FlashRecKernelError
+    from flashrec_b200.search import joint_select
+
+    cum = torch.zeros(1, 2, device=DEV)
+    lp = torch.zeros(1, 2, 4100, device=DEV)
+    tok = torch.zeros(1, 2, 4100, dtype=torch.int64, device=DEV)
+    with pytest.raises(FlashRecKernelError):
+        joint_select(cum, lp, tok, torch.empty(0, dtype=torch.int64, device=DEV), 2)
+    with pytest.raises(FlashRecKernelError):
+        joint_select(cum.cpu(), lp.cpu(), tok.cpu(), torch.empty(0, dtype=torch.int64), 2)  # no CPU path
+    out = joint_select(torch.zeros(0, 2, device=DEV), torch.zeros(0, 2, 8, device=DEV),
+                       torch.zeros(0, 2, 8, dtype=torch.int64, device=DEV), torch.empty(0, dtype=torch.int64, device=DEV), 2)
+    assert out.next_tokens.shape == (0, 2) and out.num_survivors.shape == (0,)

@@ -112,3 +112,29 @@ def test_item_matrix_from_a_catalog_file_builds_the_same_trie(tmp_path):
     a = build_trie_arrays(read_sid_catalog(tmp_path / "c.json", base=64), sizes, 1000)
     b = build_trie_arrays(items, sizes, 1000)
     assert np.array_equal(a.csr_keys, b.csr_keys) and np.array_equal(a.edge_child, b.edge_child)
+
+
+def test_iter_safetensors_reads_shards_through_the_index_and_filters_before_reading(tmp_path):
+    from safetensors.torch import save_file
+
+    from flashrec_b200.weights import iter_safetensors
+
+    a = {"model.norm.weight": torch.ones(4), "model.layers.0.mlp.down_proj.weight_scale": torch.rand(3)}
+    b = {"model.layers.0.mlp.down_proj.weight": torch.rand(3, 4), "lm_head.weight": torch.rand(5, 4)}
+    save_file(a, str(tmp_path / "model-00001-of-00002.safetensors"))
+    save_file(b, str(tmp_path / "model-00002-of-00002.safetensors"))
+    index = {"weight_map": {**{k: "model-00001-of-00002.safetensors" for k in a},
+                            **{k: "model-00002-of-00002.safetensors" for k in b}}}
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps(index))
+    got = dict(iter_safetensors(str(tmp_path)))
+    assert set(got) == set(a) | set(b) and all(torch.equal(got[k], {**a, **b}[k]) for k in got)
+    scales = dict(iter_safetensors(str(tmp_path), key_filter=lambda k: k.endswith(".weight_scale")))
+    assert list(scales) == ["model.layers.0.mlp.down_proj.weight_scale"]
+    # a directory without an index falls back to model.safetensors; an empty directory yields nothing
+    single = tmp_path / "single"
+    single.mkdir()
+    save_file(a, str(single / "model.safetensors"))
+    assert set(dict(iter_safetensors(str(single)))) == set(a)
+    empty = tmp_path / "empty"
+    empty.mkdir()
+    assert list(iter_safetensors(str(empty))) == []
