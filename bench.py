@@ -1272,9 +1272,13 @@ def main():
         cpu = None
         if not args.no_cpu_baseline and world == 1:
             # one bounded sample on the host cores; only in the single-process run, where nothing else loads them
-            ref = ReferenceCpuStep(args.beam, sizes, args.items, args.layers)
-            v, desc = ref.sample()
-            cpu = {"value": v, "unit": UNIT, "cores": ref.cores, "kind": ref.kind, "sample": desc}
+            try:
+                ref = ReferenceCpuStep(args.beam, sizes, args.items, args.layers)
+                v, desc = ref.sample()
+                cpu = {"value": v, "unit": UNIT, "cores": ref.cores, "kind": ref.kind, "sample": desc}
+            except Exception as exc:  # the host-side baseline must not take the GPU line down
+                cpu = {"value": None, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "reference",
+                       "sample": "failed: " + repr(exc)[:200]}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": sec / args.steps * 1e3, "higher_is_better": True,
@@ -1297,7 +1301,10 @@ def main():
         # the one path with a real exchange: all ranks take part, after the replicas' timed region
         del eng
         torch.cuda.empty_cache()
-        c5 = config5_head(dist, dev, rank, world)
+        try:
+            c5 = config5_head(dist, dev, rank, world)
+        except Exception as exc:  # keep the replicas' line even if the exchange path fails on this rank
+            c5 = {"error": repr(exc)[:300]}
     if rank == 0:
         if c5 is not None:
             line["config5"] = c5
