@@ -872,7 +872,29 @@ def config5_head(dist, dev, rank: int, world: int, requests: int = 16, beam: int
     ws_full = SidHeadWorkspace()
     ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
     t_un, t_sh, t_shx = [], [], []
+    t_un_g, t_sh_g = [], []  # the same steps replayed as CUDA graphs (kernels and NCCL collectives captured)
+    graph_note = None
     equal = True
+
+    def timed_graph(fn, sink, lv):
+        """Capture one call of ``fn`` and time ``reps`` replays; on any capture problem record why and go on."""
+        nonlocal graph_note
+        try:
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                fn()
+            for rep_i in range(reps + 1):
+                barrier()
+                e0, e1 = ev(), ev()
+                e0.record()
+                gr.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                if rep_i:
+                    sink.append((lv, e0.elapsed_time(e1)))
+        except Exception as exc:
+            graph_note = "graph capture unavailable: " + repr(exc)[:160]
 
     def barrier():
         if dist is not None:
@@ -898,6 +920,10 @@ def config5_head(dist, dev, rank: int, world: int, requests: int = 16, beam: int
             torch.cuda.synchronize()
             if rep:
                 t_un.append((lv, e0.elapsed_time(e1)))
+        tok_g, node_g = torch.zeros_like(tok), torch.zeros_like(node)
+        timed_graph(lambda: sid_head_topk(cum, h8, hs.reshape(-1), wl, sl, node, trie, tb, bw, ws_full, cand_capacity=cap,
+                                          token_ids_in=tok, token_ids_out=tok_g, node_ids_out=node_g, col=col),
+                    t_un_g, lv)
         if sharded:
             local = (h8, hs.reshape(-1), wl[lo:hi], sl[lo:hi])
             for rep in range(reps + 1):
@@ -911,6 +937,9 @@ def config5_head(dist, dev, rank: int, world: int, requests: int = 16, beam: int
                 torch.cuda.synchronize()
                 if rep:
                     t_sh.append((lv, e0.elapsed_time(e1)))
+            tok_sg, node_sg = torch.zeros_like(tok), torch.zeros_like(node)
+            timed_graph(lambda: head.step(cum, local, node, trie, tb, kl, bw, level=lv, token_ids_in=tok,
+                                          token_ids_out=tok_sg, node_ids_out=node_sg, col=col), t_sh_g, lv)
             # the same with the hidden rows of a data-parallel body gathered first
             h8_my, hs_my = h8[my_rows].contiguous(), hs.reshape(-1)[my_rows].contiguous()
             for rep in range(reps + 1):
@@ -955,6 +984,7 @@ def config5_head(dist, dev, rank: int, world: int, requests: int = 16, beam: int
     if dist is not None:
         dist.all_reduce(flags, op=dist.ReduceOp.MIN)
     un, sh, shx = total_ms(t_un), total_ms(t_sh), total_ms(t_shx)
+    un_g, sh_g = total_ms(t_un_g), total_ms(t_sh_g)
     return {
         "workload": "head step of the widest configuration: token-range-sharded SID head, NCCL all-gathers",
         "requests": n, "beam_width": bw, "levels": L, "level_width": kl, "catalog_items": int(trie.arrays.n_items),
@@ -962,6 +992,10 @@ def config5_head(dist, dev, rank: int, world: int, requests: int = 16, beam: int
         "head_ms_per_level_unsharded_one_gpu": un, "head_ms_all_levels_unsharded_one_gpu": round(sum(un), 4),
         "head_ms_per_level_sharded": sh, "head_ms_all_levels_sharded": round(sum(sh), 4) if sh else None,
         "head_ms_all_levels_sharded_with_hidden_all_gather": round(sum(shx), 4) if shx else None,
+        "graph_replay": {"head_ms_per_level_unsharded_one_gpu": un_g,
+                         "head_ms_all_levels_unsharded_one_gpu": round(sum(un_g), 4) if un_g else None,
+                         "head_ms_per_level_sharded": sh_g,
+                         "head_ms_all_levels_sharded": round(sum(sh_g), 4) if sh_g else None, "note": graph_note},
         "sharded_equals_unsharded_bitwise_on_shared_statistics": bool(flags[0].item()) if sharded else None,
         "complete_sids_reached": bool(flags[1].item()),
         "collectives_per_level": "1 x statistics [2, rows] f32 + 1 x winner records [N, K] x 16 B (+ 2 for the hidden "
