@@ -877,24 +877,35 @@ def config5_head(dist, dev, rank: int, world: int, requests: int = 16, beam: int
     equal = True
 
     def timed_graph(fn, sink, lv):
-        """Capture one call of ``fn`` and time ``reps`` replays; on any capture problem record why and go on."""
+        """Capture one call of ``fn`` and time ``reps`` replays; on any capture problem record why and go on.
+        The ranks agree on the outcome before anyone replays, so a rank whose capture failed leaves nobody
+        waiting in a collective."""
         nonlocal graph_note
+        if graph_note is not None:
+            return
+        gr, why = None, None
         try:
             torch.cuda.synchronize()
             gr = torch.cuda.CUDAGraph()
             with torch.cuda.graph(gr):
                 fn()
-            for rep_i in range(reps + 1):
-                barrier()
-                e0, e1 = ev(), ev()
-                e0.record()
-                gr.replay()
-                e1.record()
-                torch.cuda.synchronize()
-                if rep_i:
-                    sink.append((lv, e0.elapsed_time(e1)))
         except Exception as exc:
-            graph_note = "graph capture unavailable: " + repr(exc)[:160]
+            gr, why = None, repr(exc)[:160]
+        ok = torch.tensor([0 if gr is None else 1], dtype=torch.int32, device=dev)
+        if dist is not None:
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 0:
+            graph_note = "graph capture unavailable: " + (why or "failed on another rank")
+            return
+        for rep_i in range(reps + 1):
+            barrier()
+            e0, e1 = ev(), ev()
+            e0.record()
+            gr.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            if rep_i:
+                sink.append((lv, e0.elapsed_time(e1)))
 
     def barrier():
         if dist is not None:
