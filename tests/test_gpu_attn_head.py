@@ -68,18 +68,19 @@ def test_gather_kv_indices_golden_and_ragged():
     out = gather_kv_indices(table, torch.tensor([0, 1, 1], device=DEV), [3, 1, 4])
     assert out.cpu().tolist() == [0, 1, 2, 10, 10, 11, 12, 13]
     # many rows, zero-length rows, device seq_lens + preallocated outputs (no sync)
+    # (both CTA shapes of the kernel: up to 4096 rows, and more)
     rng = np.random.default_rng(0)
-    n = 3000
-    table = torch.from_numpy(rng.integers(0, 1 << 20, (64, 300)).astype(np.int32)).to(DEV)
-    rows = torch.from_numpy(rng.integers(0, 64, n)).to(DEV)
-    sl = rng.integers(0, 301, n).astype(np.int32)
-    indptr = torch.empty(n + 1, dtype=torch.int32, device=DEV)
-    buf = torch.full((int(sl.sum()) + 5,), -7, dtype=torch.int32, device=DEV)
-    gather_kv_indices(table, rows, torch.from_numpy(sl).to(DEV), out=buf, indptr_out=indptr)
-    ref = O.gather_kv_indices(table.cpu(), rows.cpu(), sl.tolist())
-    assert np.array_equal(buf[: ref.numel()].cpu().numpy(), ref.numpy())
-    assert buf[ref.numel():].eq(-7).all()
-    assert np.array_equal(indptr.cpu().numpy(), np.concatenate([[0], np.cumsum(sl)]))
+    for n in (3000, 9001):
+        table = torch.from_numpy(rng.integers(0, 1 << 20, (64, 300)).astype(np.int32)).to(DEV)
+        rows = torch.from_numpy(rng.integers(0, 64, n)).to(DEV)
+        sl = rng.integers(0, 301, n).astype(np.int32)
+        indptr = torch.empty(n + 1, dtype=torch.int32, device=DEV)
+        buf = torch.full((int(sl.sum()) + 5,), -7, dtype=torch.int32, device=DEV)
+        gather_kv_indices(table, rows, torch.from_numpy(sl).to(DEV), out=buf, indptr_out=indptr)
+        ref = O.gather_kv_indices(table.cpu(), rows.cpu(), sl.tolist())
+        assert np.array_equal(buf[: ref.numel()].cpu().numpy(), ref.numpy())
+        assert buf[ref.numel():].eq(-7).all()
+        assert np.array_equal(indptr.cpu().numpy(), np.concatenate([[0], np.cumsum(sl)]))
 
 
 # ---------------------------------------------------------------------------
