@@ -1102,25 +1102,29 @@ gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 // barrier.
 // EPI 0: out = scaled product (bf16 or f32). EPI 2: bf16 out += (in place, residual).
 // ---------------------------------------------------------------------------
+// TN = 256 or 128 columns per tile: the narrower tile halves the partial tile a CTA has to exchange, at the
+// price of more operand bytes per CTA; the host picks per shape (pick_split_plan).
+template <int TN>
 struct SplitCfg {
   static constexpr int kTileM = kBlockM;  // 128
-  static constexpr int kTileN = 256;
+  static constexpr int kTileN = TN;
   static constexpr int kStageA = kTileM * kBlockK;  // 16 KB
-  static constexpr int kStageB = kTileN * kBlockK;  // 32 KB
+  static constexpr int kStageB = kTileN * kBlockK;  // 32 / 16 KB
   static constexpr int kStageBytes = kStageA + kStageB;
-  static constexpr int kStages = 4;      // 192 KB; the first 128 KB double as the reduction buffer
-  static constexpr int kTmemCols = 256;  // one 128 x 256 fp32 accumulator
+  static constexpr int kStages = TN == 256 ? 4 : 6;  // 192 KB; the first 128 / 64 KB double as the reduction buffer
+  static constexpr int kTmemCols = TN;               // one 128 x TN fp32 accumulator
+  static constexpr int kRowBytes = TN * 4;           // one partial row in the reduction buffer
   static constexpr int kBarBytes = (2 * kStages + 1) * 8 + 16;
   static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kBarBytes;
   static constexpr int kThreads = 192;
 };
 
-template <typename OutT, int EPI, int S>
-__global__ void __launch_bounds__(SplitCfg::kThreads, 1)
+template <typename OutT, int EPI, int S, int TN>
+__global__ void __launch_bounds__(SplitCfg<TN>::kThreads, 1)
 gemm_fp8_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                        OutT* __restrict__ out, int64_t ldo, const float* __restrict__ scale_a,
                        const float* __restrict__ scale_b, int M, int N, int K, int* status) {
-  using C = SplitCfg;
+  using C = SplitCfg<TN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -1221,12 +1225,12 @@ gemm_fp8_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
   ptx::cluster_arrive();
   ptx::cluster_wait();
   if (epi) {
-    // accumulator row r -> owner CTA r / rows_per, slot `rank`, fp32 [rows_per][1024 bytes] per
+    // accumulator row r -> owner CTA r / rows_per, slot `rank`, fp32 [rows_per][4 TN bytes] per
     // slot, 16-byte pieces XOR-swizzled by (row & 7) (conflict-free for the stores and the loads)
     const int r = quad * 32 + lane;
     const int owner = r / rows_per;
     const int rl = r % rows_per;
-    const uint32_t dst_row = ptx::mapa(base + (rank * rows_per + rl) * 1024, owner);
+    const uint32_t dst_row = ptx::mapa(base + (rank * rows_per + rl) * C::kRowBytes, owner);
     const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
 #pragma unroll 1
     for (int c = 0; c < C::kTileN / 32; ++c) {
@@ -1272,11 +1276,11 @@ gemm_fp8_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         const int idx = (b0 + b) * 128 + epi_tid;
         const int rl = idx / (C::kTileN / 4);
         const int ch = idx % (C::kTileN / 4);
-        const uint8_t* src = smem + rl * 1024 + ((ch ^ (rl & 7)) << 4);
+        const uint8_t* src = smem + rl * C::kRowBytes + ((ch ^ (rl & 7)) << 4);
         float4 sum = *reinterpret_cast<const float4*>(src);
 #pragma unroll
         for (int pr = 1; pr < S; ++pr) {
-          const float4 v = *reinterpret_cast<const float4*>(src + pr * rows_per * 1024);
+          const float4 v = *reinterpret_cast<const float4*>(src + pr * rows_per * C::kRowBytes);
           sum.x = __fadd_rn(sum.x, v.x);
           sum.y = __fadd_rn(sum.y, v.y);
           sum.z = __fadd_rn(sum.z, v.z);
@@ -1523,32 +1527,68 @@ static bool use_pair(int M, int N) {
   return tiles >= 3 * (sm_count() / 2) || (M <= 1024 && M > kBlockM && tiles >= sm_count() / 2);
 }
 
-// Split-K over a cluster: the largest S in {8, 4, 2} that divides the k-blocks, leaves each CTA
-// at least two of them and keeps tiles x S within the SM count; 1 when no such S exists, 0 when
-// the shape has too many rows or tiles for this kernel.
-static int pick_splits(int M, int N, int K) {
-  const int64_t tiles = static_cast<int64_t>(ceil_div(M, SplitCfg::kTileM)) * ceil_div(N, SplitCfg::kTileN);
+// Split-K over a cluster. A plan is the number of CTAs S in {8, 4, 2} per tile (it divides the k-blocks,
+// leaves each CTA at least two of them, tiles x S fits the SM count) and the tile width (256 or 128
+// columns). Among the plans that fit, the cheapest by the two rates measured for a 512-row step wins: a CTA
+// pulls its operands at about 48 bytes per clock, and the partial tiles cross the cluster at about 11 bytes
+// per clock and SM whichever instruction moves them. splits = 1 (tile 256) when no S fits, 0 when the shape
+// has too many rows or tiles for this kernel. `force_tn` (128 / 256) restricts the width.
+struct SplitPlan {
+  int splits;
+  int tile_n;
+};
+static SplitPlan pick_split_plan(int M, int N, int K, int force_tn = 0) {
   const int num_kb = ceil_div(K, kBlockK);
-  if (M > 1024 || tiles > sm_count()) return 0;
-  for (int s = 8; s >= 2; s >>= 1)
-    if (num_kb % s == 0 && num_kb / s >= 2 && tiles * s <= sm_count()) return s;
-  return 1;
+  SplitPlan best{0, 256};
+  double best_cost = 0.0;
+  bool any_width = false;
+  for (int tn = 256; tn >= 128; tn >>= 1) {
+    if (force_tn != 0 && tn != force_tn) continue;
+    const int64_t tiles = static_cast<int64_t>(ceil_div(M, kBlockM)) * ceil_div(N, tn);
+    if (M > 1024 || tiles > sm_count()) continue;
+    any_width = true;
+    for (int s = 8; s >= 2; s >>= 1) {
+      if (num_kb % s != 0 || num_kb / s < 2 || tiles * s > sm_count()) continue;
+      const double feed = static_cast<double>(kBlockM + tn) * kBlockK * (num_kb / s) / 48.0;
+      const double exchange = static_cast<double>(kBlockM) * tn * 4.0 * (s - 1) / s / 11.0;
+      const double cost = feed + exchange;
+      if (best.splits == 0 || cost < best_cost) {
+        best = SplitPlan{s, tn};
+        best_cost = cost;
+      }
+    }
+  }
+  if (best.splits == 0 && any_width) best = SplitPlan{1, force_tn == 128 ? 128 : 256};
+  return best;
 }
 
 // Chosen by itself only for long reductions (K >= 4096: the down projection of a one-request
-// step), where the serial K loop of a lone CTA costs more than the exchange of partial tiles:
-// distributed shared memory moved only ~11 bytes per clock and SM in the measurements, so for
-// shorter K the kernels above are faster.
-static int auto_splits(int M, int N, int K) {
-  if (ceil_div(K, kBlockK) < 32) return 0;
-  const int s = pick_splits(M, N, K);
-  return s >= 2 ? s : 0;
+// step), where the serial K loop of a lone CTA costs more than the exchange of partial tiles;
+// for shorter K the kernels above are faster.
+static SplitPlan auto_split_plan(int M, int N, int K) {
+  if (ceil_div(K, kBlockK) < 32) return SplitPlan{0, 256};
+  const SplitPlan p = pick_split_plan(M, N, K);
+  return p.splits >= 2 ? p : SplitPlan{0, 256};
 }
 
-template <typename OutT, int EPI>
-static int launch_splitk(const void* a, const void* b, const float* sa, const float* sb, void* out, int64_t ldo, int M,
-                         int N, int K, int64_t lda, int64_t ldb, int splits, cudaStream_t stream) {
-  using C = SplitCfg;
+// block_n_hint of the GEMM entry points: 1024 = split-K, plan chosen; 1024 + 128 / 1024 + 256 = split-K with
+// that tile width; 0 = split-K only where auto_split_plan says so.
+static SplitPlan split_plan_for_hint(int block_n_hint, int M, int N, int K) {
+  if (block_n_hint == 0) return auto_split_plan(M, N, K);
+  SplitPlan p{0, 256};
+  if (block_n_hint == 1024) p = pick_split_plan(M, N, K);
+  else if (block_n_hint == 1024 + 128) p = pick_split_plan(M, N, K, 128);
+  else if (block_n_hint == 1024 + 256) p = pick_split_plan(M, N, K, 256);
+  else return p;
+  if (p.splits == 0) p.splits = 1;  // asked for by name: run it unsplit rather than refuse
+  return p;
+}
+static bool is_split_hint(int h) { return h == 1024 || h == 1024 + 128 || h == 1024 + 256; }
+
+template <typename OutT, int EPI, int TN>
+static int launch_splitk_tn(const void* a, const void* b, const float* sa, const float* sb, void* out, int64_t ldo,
+                            int M, int N, int K, int64_t lda, int64_t ldb, int splits, cudaStream_t stream) {
+  using C = SplitCfg<TN>;
   CUtensorMap ta, tb;
   int st = make_tmap_u8(&ta, a, M, K, lda, kBlockM);
   if (st != FR_OK) return st;
@@ -1558,13 +1598,13 @@ static int launch_splitk(const void* a, const void* b, const float* sa, const fl
                         int*);
   Kern kern = nullptr;
   switch (splits) {
-    case 1: kern = gemm_fp8_splitk_kernel<OutT, EPI, 1>; break;
-    case 2: kern = gemm_fp8_splitk_kernel<OutT, EPI, 2>; break;
-    case 4: kern = gemm_fp8_splitk_kernel<OutT, EPI, 4>; break;
-    case 8: kern = gemm_fp8_splitk_kernel<OutT, EPI, 8>; break;
+    case 1: kern = gemm_fp8_splitk_kernel<OutT, EPI, 1, TN>; break;
+    case 2: kern = gemm_fp8_splitk_kernel<OutT, EPI, 2, TN>; break;
+    case 4: kern = gemm_fp8_splitk_kernel<OutT, EPI, 4, TN>; break;
+    case 8: kern = gemm_fp8_splitk_kernel<OutT, EPI, 8, TN>; break;
     default: return FR_ERR_UNSUPPORTED;
   }
-  static PerDeviceFlag attr_done[9];  // per split count and device
+  static PerDeviceFlag attr_done[9];  // per split count and device (one array per OutT, EPI, TN)
   if (ensure_dyn_smem(attr_done[splits], kern, C::kSmemBytes) != FR_OK) return FR_ERR_CUDA;
   int* status = device_status_ptr();
   if (!status) return FR_ERR_CUDA;
@@ -1582,6 +1622,14 @@ static int launch_splitk(const void* a, const void* b, const float* sa, const fl
     return FR_ERR_CUDA;
   }
   return FR_OK;
+}
+
+template <typename OutT, int EPI>
+static int launch_splitk(const void* a, const void* b, const float* sa, const float* sb, void* out, int64_t ldo, int M,
+                         int N, int K, int64_t lda, int64_t ldb, SplitPlan plan, cudaStream_t stream) {
+  if (plan.tile_n == 128)
+    return launch_splitk_tn<OutT, EPI, 128>(a, b, sa, sb, out, ldo, M, N, K, lda, ldb, plan.splits, stream);
+  return launch_splitk_tn<OutT, EPI, 256>(a, b, sa, sb, out, ldo, M, N, K, lda, ldb, plan.splits, stream);
 }
 
 }  // namespace gemm
@@ -1609,14 +1657,13 @@ extern "C" int fr_gemm_fp8_w8a8(const void* a, const void* b, const float* scale
   FR_CHECK_ARG(out_is_f32 ? (ldo % 4 == 0) : (ldo % 8 == 0));
   FR_CHECK_ARG(K % 16 == 0);
   FR_CHECK_SUPPORTED(out_is_f32 ? (bias == nullptr) : true);
-  if (bias == nullptr && (block_n_hint == 1024 || block_n_hint == 0)) {
-    int splits = block_n_hint == 1024 ? gemm::pick_splits(M, N, K) : gemm::auto_splits(M, N, K);
-    if (block_n_hint == 1024 && splits == 0) splits = 1;
-    if (splits >= 1)
-      return out_is_f32 ? gemm::launch_splitk<float, 0>(a, b, scale_a, scale_b, out, ldo, M, N, K, lda, ldb, splits,
+  if (bias == nullptr && (gemm::is_split_hint(block_n_hint) || block_n_hint == 0)) {
+    const gemm::SplitPlan plan = gemm::split_plan_for_hint(block_n_hint, M, N, K);
+    if (plan.splits >= 1)
+      return out_is_f32 ? gemm::launch_splitk<float, 0>(a, b, scale_a, scale_b, out, ldo, M, N, K, lda, ldb, plan,
                                                         stream)
                         : gemm::launch_splitk<__nv_bfloat16, 0>(a, b, scale_a, scale_b, out, ldo, M, N, K, lda, ldb,
-                                                                splits, stream);
+                                                                plan, stream);
   }
   if (block_n_hint == 512 || (block_n_hint == 0 && gemm::use_pair(M, N))) {
     return out_is_f32 ? gemm::launch_pair<float, 0>(a, b, scale_a, scale_b, bias, out, ldo, M, N, K, lda, ldb, stream)
@@ -1663,11 +1710,10 @@ extern "C" int fr_gemm_fp8_w8a8_add(const void* a, const void* b, const float* s
   FR_CHECK_ARG(a && b && scale_a && scale_b && residual_inout);
   FR_CHECK_ARG(aligned16(a) && aligned16(b) && aligned16(residual_inout));
   FR_CHECK_ARG(lda >= K && ldb >= K && ldr >= N && lda % 16 == 0 && ldb % 16 == 0 && ldr % 8 == 0 && K % 16 == 0);
-  if (block_n_hint == 1024 || block_n_hint == 0) {
-    int splits = block_n_hint == 1024 ? gemm::pick_splits(M, N, K) : gemm::auto_splits(M, N, K);
-    if (block_n_hint == 1024 && splits == 0) splits = 1;
-    if (splits >= 1)
-      return gemm::launch_splitk<__nv_bfloat16, 2>(a, b, scale_a, scale_b, residual_inout, ldr, M, N, K, lda, ldb, splits,
+  if (gemm::is_split_hint(block_n_hint) || block_n_hint == 0) {
+    const gemm::SplitPlan plan = gemm::split_plan_for_hint(block_n_hint, M, N, K);
+    if (plan.splits >= 1)
+      return gemm::launch_splitk<__nv_bfloat16, 2>(a, b, scale_a, scale_b, residual_inout, ldr, M, N, K, lda, ldb, plan,
                                                    stream);
   }
   if (block_n_hint == 512 || (block_n_hint == 0 && gemm::use_pair(M, N)))

@@ -88,7 +88,8 @@ int fr_silu_mul_bf16(const void* x, void* y_out, int rows, int d, cudaStream_t s
  * (elements). K % 16 == 0; pitches in elements, multiples of 16 for a/b.
  * block_n_hint: 0 = choose, 64 / 128 / 256 = one CTA per 128 x block_n tile,
  * 512 = CTA pairs (cluster of 2, tcgen05 cta_group::2) on 256 x 256 tiles,
- * 1024 = split-K over a cluster of up to 8 CTAs per 128 x 256 tile (few rows, long K; no bias).
+ * 1024 = split-K over a cluster of up to 8 CTAs per 128 x 256 or 128 x 128 tile (few rows, long K; no bias;
+ * the tile width is chosen per shape, 1024 + 128 / 1024 + 256 name it).
  * Reports FR_ERR_TIMEOUT through fr_device_status if a pipeline wait gives up.
  * Reference: Linear.forward_fp8 -> fp8_scaled_mm (layers/linear.py:134-172,
  * kernel/sglops.py:99-140). */

@@ -133,6 +133,14 @@ GEMM_SHAPES = [
     (300, 328, 144, 1024),     # ragged everywhere, K tail, a single k-split
     (37, 200, 2048, 1024),     # N not a multiple of 4 pieces' row, one row block
     (1000, 768, 256, 1024),
+    # 1024 + 128 / 1024 + 256: split-K with the tile width named (128 x 128 or 128 x 256 per cluster)
+    (512, 2048, 6144, 1152),   # 2 CTAs per 128-wide tile
+    (256, 2048, 6144, 1152),   # 4 CTAs per tile
+    (128, 1024, 2048, 1152),   # 8 CTAs per tile
+    (300, 328, 144, 1152),     # ragged, a single k-split
+    (37, 200, 2048, 1152),
+    (512, 2048, 6144, 1280),
+    (256, 2048, 6144, 0),      # auto: the plan's cost model picks the narrow tile here
 ]
 
 
@@ -171,7 +179,7 @@ def test_gemm_exact_accumulation_small_integers():
     ref = a @ b.t()
     ones_m = torch.ones(m, 1, device=DEV)
     ones_n = torch.ones(n, device=DEV)
-    for bn in (64, 128, 256, 512, 1024):
+    for bn in (64, 128, 256, 512, 1024, 1152, 1280):
         out = fp8_scaled_mm(a.to(torch.float8_e4m3fn).to(DEV), b.to(torch.float8_e4m3fn).to(DEV).t(), ones_m, ones_n,
                             torch.float32, block_n=bn)
         assert torch.equal(out.cpu(), ref), f"block_n={bn}"
@@ -271,7 +279,8 @@ def test_gemm_silu_epilogue_corner_inputs(case):
 
 @pytest.mark.parametrize("m,n,k,block_n", [(300, 512, 256, 0), (37, 200, 128, 64), (128, 256, 2048, 256),
                                            (700, 1024, 384, 512), (513, 200, 512, 512), (4100, 2048, 256, 0),
-                                           (512, 2048, 6144, 1024), (300, 200, 384, 1024), (512, 2048, 2048, 0)])
+                                           (512, 2048, 6144, 1024), (300, 200, 384, 1024), (512, 2048, 2048, 0),
+                                           (512, 2048, 6144, 1152), (300, 200, 384, 1152), (256, 2048, 6144, 1280)])
 def test_gemm_add_into_residual_equals_gemm_then_bf16_add(m, n, k, block_n):
     """fr_gemm_fp8_w8a8_add == GEMM (bf16 out) followed by the bf16 add of fused_add_rmsnorm, bit for bit,
     through the single-CTA kernels (hint 64 / 256 / auto) and the CTA-pair kernel (hint 512, ragged edges)."""
