@@ -22,6 +22,7 @@ data-path collective; the time is the max over ranks.
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import statistics
@@ -78,6 +79,10 @@ def parse():
                     help="only run the token-range-sharded head step of the widest configuration (the `config5` object "
                          "of the JSON line, which multi-GPU runs always carry) and print it")
     ap.add_argument("--no-config5", action="store_true", help="leave the `config5` object out of a multi-GPU line")
+    ap.add_argument("--sharded-head", action="store_true",
+                    help="N > 1: one group of N x --requests requests; the model body data-parallel over the ranks' "
+                         "own requests, the SID head split by token range over the ranks (NCCL all-gathers of the "
+                         "hidden rows, the row statistics and the winners) instead of independent replicas")
     ap.add_argument("--attn-compare", action="store_true",
                     help="time one layer's decode attention on the bench's slot lists beside FlashInfer's paged "
                          "decode kernel (a library comparison) and exit")
@@ -177,7 +182,8 @@ def bench_config(args, world: int, rows: int, decode_steps: int):
     """The ``config`` object of the JSON line: the workload only, so that both arms print the same object
     (measured quantities such as the per-GPU value or the number of distinct catalog items are top-level keys)."""
     return dict(WORKLOAD, requests=args.requests, beam_width=args.beam, layers=args.layers,
-                catalog_items=args.items, trie=args.trie, parallelism=f"dp{world}", rows_per_gpu=rows,
+                catalog_items=args.items, trie=args.trie,
+                parallelism=WORKLOAD.get("parallelism", f"dp{world}"), rows_per_gpu=rows,
                 decode_steps_per_wave=decode_steps)
 
 
@@ -1171,9 +1177,20 @@ def main():
     trie = build_trie_device(torch.from_numpy(np.ascontiguousarray(catalog, dtype=np.int32)).to(dev), sizes,
                              token_base, layout=args.trie)
     arrays = trie.arrays
+    sharded = None
+    if args.sharded_head:
+        if dist is None:
+            raise SystemExit("--sharded-head needs more than one rank (torchrun)")
+        from flashrec_b200.sharded_head import ShardedSidHead
+
+        sharded = ShardedSidHead()
+        WORKLOAD.update(parallelism=f"dp{world} body + token-range-sharded SID head (NCCL)",
+                        requests_in_group=args.requests * world)
     eng = SidDecodeEngine(cfg, args.requests, args.beam, prompt_lengths(args.requests, rank, p_lo, p_hi), sizes, token_base, trie,
-                          dev, shared_prefix=64, page_size=16, seed=rank, fuse_rope_gemm=not args.no_fuse_rope_gemm,
-                          level0_from_prefill=args.level0_from_prefill, fused_head=not args.no_fused_head)
+                          dev, shared_prefix=64, page_size=16, seed=0 if sharded is not None else rank,
+                          fuse_rope_gemm=not args.no_fuse_rope_gemm, level0_from_prefill=args.level0_from_prefill,
+                          fused_head=not args.no_fused_head, sharded_head=sharded,
+                          data_seed=rank if sharded is not None else None)
     # Prefill of the prompts (eager, one extend batch): the decode waves below then read real K/V. Timed on
     # its own; it is not part of `value` (the metric is the decode step).
     prefill = None
@@ -1353,8 +1370,12 @@ def main():
     if rank == 0:
         if c5 is not None:
             line["config5"] = c5
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if dist is not None:
+        # captured graphs that hold NCCL work go before the communicator does
+        eng = None
+        gc.collect()
+        torch.cuda.synchronize()
         dist.barrier()
         dist.destroy_process_group()
 

@@ -82,14 +82,15 @@ class CudaHeadOps:
         return rec
 
     def merge(self, all_rec, node_ids, token_ids_in, token_ids_out, node_ids_out, col, level_tok_base, idx_width, trie,
-              bw):
+              bw, out=None):
         from flashrec_b200._lib import call, ptr, stream_ptr
         from flashrec_b200.sid_decode import BeamStepOut
 
         s, n, k, _ = all_rec.shape
         dev = all_rec.device
-        out = BeamStepOut(*(torch.empty((n, k), dtype=dt, device=dev)
-                            for dt in (torch.float32, torch.int64, torch.int64, torch.int64, torch.int64)))
+        if out is None:
+            out = BeamStepOut(*(torch.empty((n, k), dtype=dt, device=dev)
+                                for dt in (torch.float32, torch.int64, torch.int64, torch.int64, torch.int64)))
         tr = trie.descriptor() if trie is not None else None
         do_exp = token_ids_in is not None and token_ids_out is not None
         call("fr_topk_merge_shards", ptr(out.vals), ptr(out.parents), ptr(out.tokens), ptr(out.indices),
@@ -121,14 +122,18 @@ class ShardedSidHead:
         return h.view(-1, h.shape[-1]).view(hidden_fp8_local.dtype), s.view(-1)
 
     def step(self, cum, local, node_ids, trie, level_tok_base: int, level_width: int, select_k: int, *, level=None,
-             token_ids_in=None, token_ids_out=None, node_ids_out=None, col=None):
+             token_ids_in=None, token_ids_out=None, node_ids_out=None, col=None, out=None):
         """``local``: what this rank's ``ops`` compute from (:class:`CudaHeadOps`: the hidden rows of ALL
-        requests and the rank's head rows). Every rank must own shards of equal width."""
+        requests and the rank's head rows). Every rank must own shards of equal width. ``out``: a
+        ``BeamStepOut`` of ``[N, K]`` buffers to write the merged result into (CUDA ops only)."""
         if level_width % self.world != 0:
             raise ValueError("level width must be divisible by the world size")
         lo, hi = shard_range(level_width, self.rank, self.world)
         stats = self.ops.local_stats(cum, local, node_ids, trie, level_tok_base, lo, level_width, level)
         mx, ls = self.ops.combine_stats(self._all_gather(stats))
         rec = self.ops.local_step(cum, local, mx, ls, node_ids, trie, level_tok_base, select_k, lo, level_width)
+        if out is None:  # (stand-in ops of the CPU protocol test take no buffers)
+            return self.ops.merge(self._all_gather(rec), node_ids, token_ids_in, token_ids_out, node_ids_out, col,
+                                  level_tok_base, level_width, trie, int(cum.shape[1]))
         return self.ops.merge(self._all_gather(rec), node_ids, token_ids_in, token_ids_out, node_ids_out, col,
-                              level_tok_base, level_width, trie, int(cum.shape[1]))
+                              level_tok_base, level_width, trie, int(cum.shape[1]), out=out)

@@ -171,7 +171,14 @@ class SidDecodeEngine:
     SID levels with a Qwen3-shaped FP8 model. Weights are random (N(0, 0.02)), the
     prompt KV is synthetic e4m3 data laid out as a prefill would have left it:
     requests share the slots of a common prompt prefix (a radix-cache hit), every
-    beam of a request shares the request's prompt slots."""
+    beam of a request shares the request's prompt slots.
+
+    With ``sharded_head`` (a :class:`flashrec_b200.sharded_head.ShardedSidHead` over a process group of equal
+    engines) the model body stays data-parallel over the ranks' own requests and the SID head is split by
+    token range: every step all-gathers the ranks' quantised final hidden rows, runs the head on the rank's
+    code range for ALL requests, and merges the shards' winners, so every rank holds the beam state of all
+    requests and continues with its own. With a ``data_seed`` the weights come from ``seed`` alone (the same
+    on every rank) and prompts and KV fill from ``data_seed``."""
 
     def __init__(
         self,
@@ -192,6 +199,8 @@ class SidDecodeEngine:
         fuse_rope_gemm: bool = True,
         level0_from_prefill: bool = False,
         fused_head: bool = True,
+        sharded_head=None,
+        data_seed: Optional[int] = None,
     ):
         self.cfg = cfg
         self.device = torch.device(device)
@@ -207,13 +216,23 @@ class SidDecodeEngine:
         assert len(self.prompt_lens) == self.n
         self.shared_prefix = int(shared_prefix)
         self.seed = int(seed)
+        self.data_seed = self.seed if data_seed is None else int(data_seed)
+        self.sharded = sharded_head
+        self.world = int(sharded_head.world) if sharded_head is not None else 1
+        self.rank = int(sharded_head.rank) if sharded_head is not None else 0
+        self.n_total = self.n * self.world
+        if sharded_head is not None:
+            if level0_from_prefill or trie is None or not fused_head:
+                raise ValueError("the sharded head runs the fused, trie-constrained decode steps only")
+            if any(int(k) % self.world for k in sizes):
+                raise ValueError("every level width must be divisible by the number of head shards")
         # the reference's flow: level 0 is chosen from the prefill's last-token logits (one row per
         # request, init_from_prefill_batch, search/expand.py:168-237) and only levels 1.. are decode steps
         self.first_step = 1 if level0_from_prefill else 0
         self.prefill_hidden: Optional[torch.Tensor] = None
         dev = self.device
         g = torch.Generator(device=dev)
-        g.manual_seed(seed)
+        g.manual_seed(self.data_seed)
 
         # ---- KV pool: [page 0 dummy][shared prefix][per-request prompts][decode slots] ----
         uniq_prompt = shared_prefix + sum(max(p - shared_prefix, 0) for p in self.prompt_lens)
@@ -254,7 +273,11 @@ class SidDecodeEngine:
         self.model = Qwen3ForCausalLM(cfg, self.attn, dev, fuse_rope_gemm=fuse_rope_gemm)
         self.model.init_random(seed=seed + 1)
         sid_total = sum(self.sizes)
-        sid_w = torch.randn((sid_total, cfg.hidden_size), generator=g, device=dev, dtype=torch.float32) * 0.02
+        gw = g
+        if sharded_head is not None or data_seed is not None:  # the same head on every rank, whatever its prompts drew from g
+            gw = torch.Generator(device=dev)
+            gw.manual_seed(seed + 2)
+        sid_w = torch.randn((sid_total, cfg.hidden_size), generator=gw, device=dev, dtype=torch.float32) * 0.02
         self.head = RestrictedLMHead(list(range(self.token_base, self.token_base + sid_total)))
         from flashrec_b200.layers import quantize_weight_fp8
 
@@ -271,17 +294,27 @@ class SidDecodeEngine:
         total_idx = sum(self.prompt_lens) * self.bw + self.rows * self.steps
         self.kv_indices = torch.zeros(total_idx, dtype=torch.int32, device=dev)
         self.kv_indptr = torch.zeros(self.rows + 1, dtype=torch.int32, device=dev)
-        self.cum = torch.zeros((self.n, self.bw), dtype=torch.float32, device=dev)
-        self.node_planes = [torch.zeros((self.n, self.bw), **i64) for _ in range(2)]
-        self.tok_planes = [torch.zeros((self.n, self.bw, self.steps), **i64) for _ in range(2)]
-        self.col = torch.zeros(self.n, dtype=torch.int32, device=dev)
-        self.outs = [
+        # beam state of all requests of the group (n_total == n without a sharded head); this engine's own
+        # requests are the rows [rank * n, (rank + 1) * n) of it
+        nt = self.n_total
+        own = slice(self.rank * self.n, (self.rank + 1) * self.n)
+        self.g_cum = torch.zeros((nt, self.bw), dtype=torch.float32, device=dev)
+        self.g_node_planes = [torch.zeros((nt, self.bw), **i64) for _ in range(2)]
+        self.g_tok_planes = [torch.zeros((nt, self.bw, self.steps), **i64) for _ in range(2)]
+        self.g_col = torch.zeros(nt, dtype=torch.int32, device=dev)
+        self.g_outs = [
             BeamStepOut(
-                vals=torch.empty((self.n, self.bw), dtype=torch.float32, device=dev),
-                parents=torch.empty((self.n, self.bw), **i64), tokens=torch.empty((self.n, self.bw), **i64),
-                indices=torch.empty((self.n, self.bw), **i64), child=torch.empty((self.n, self.bw), **i64))
+                vals=torch.empty((nt, self.bw), dtype=torch.float32, device=dev),
+                parents=torch.empty((nt, self.bw), **i64), tokens=torch.empty((nt, self.bw), **i64),
+                indices=torch.empty((nt, self.bw), **i64), child=torch.empty((nt, self.bw), **i64))
             for _ in range(self.steps)
         ]
+        self.cum = self.g_cum[own]
+        self.node_planes = [t[own] for t in self.g_node_planes]
+        self.tok_planes = [t[own] for t in self.g_tok_planes]
+        self.col = self.g_col[own]
+        self.outs = [BeamStepOut(vals=o.vals[own], parents=o.parents[own], tokens=o.tokens[own],
+                                 indices=o.indices[own], child=o.child[own]) for o in self.g_outs]
         # pinned host staging for the per-step inputs and the final result
         self.h_loc = torch.empty((self.steps, self.rows), dtype=torch.int64).pin_memory()
         for s in range(self.steps):
@@ -307,10 +340,10 @@ class SidDecodeEngine:
         beam row holding its request's prompt slots (engine/engine.py:252-274)."""
         copy_prefill_to_beams_many(self.req_to_token, self.prefill_rows, self.rows_idx.view(self.n, self.bw),
                                    max(self.prompt_lens))
-        self.cum.fill_(float("-inf"))
-        self.cum[:, 0] = 0.0
-        self.node_planes[0].zero_()
-        self.tok_planes[0].zero_()
+        self.g_cum.fill_(float("-inf"))
+        self.g_cum[:, 0] = 0.0
+        self.g_node_planes[0].zero_()
+        self.g_tok_planes[0].zero_()
         self.input_ids.fill_(self.token_base)  # stand-in for the last prompt token
         self.positions.copy_(self.prompt_len_rows)
         self.seq_lens.copy_((self.prompt_len_rows + 1).to(torch.int32))
@@ -346,8 +379,22 @@ class SidDecodeEngine:
                              kv_indptr=self.kv_indptr)
         self.attn.prepare(batch, reuse_prefix=s > self.first_step)
         hidden = self.model.forward(batch)
-        self.col.fill_(s)
-        if self.fused_head:
+        self.g_col.fill_(s)
+        if self.sharded is not None:
+            # the ranks' hidden rows (e4m3 + scales) in rank order, then the head on this rank's codes of
+            # the level for every request of the group; the merged winners land in the group's state
+            h8, h_scale = per_token_quant_fp8(hidden)
+            gh, gs = self.sharded.gather_hidden(h8, h_scale.reshape(-1))
+            kl = self.sizes[s]
+            lo, hi = kl // self.world * self.rank, kl // self.world * (self.rank + 1)
+            local = (gh, gs, self.head._level_weights[s][lo:hi], self.head._level_scales[s][lo:hi])
+            self.sharded.step(self.g_cum, local, self.g_node_planes[src], self.trie, self.level_tok_base[s], kl,
+                              self.bw, level=s, token_ids_in=self.g_tok_planes[src],
+                              token_ids_out=self.g_tok_planes[dst], node_ids_out=self.g_node_planes[dst],
+                              col=self.g_col, out=self.g_outs[s])
+            out = self.outs[s]
+            self.g_cum.copy_(self.g_outs[s].vals)
+        elif self.fused_head:
             h8, h_scale = per_token_quant_fp8(hidden)
             out = sid_head_topk(self.cum, h8, h_scale, self.head._level_weights[s], self.head._level_scales[s],
                                 self.node_planes[src], self.trie, self.level_tok_base[s], self.bw, self.head_ws,
@@ -361,7 +408,8 @@ class SidDecodeEngine:
                                 node_ids_out=self.node_planes[dst], col=self.col, out=self.outs[s])
         # state of the next step (the window remap by out.parents is deferred to its table call, as
         # scheduler.py:1590-1610 defers it)
-        self.cum.copy_(out.vals)
+        if self.sharded is None:
+            self.cum.copy_(out.vals)
         if self.trie is None:
             self.node_planes[dst].fill_(-1)
         self.input_ids.copy_(out.tokens.reshape(-1))
@@ -424,7 +472,7 @@ class SidDecodeEngine:
         pre = [0 if r == 0 else min(sp, p) for r, p in enumerate(self.prompt_lens)]
         if min(p - q for p, q in zip(self.prompt_lens, pre)) <= 0:
             raise ValueError("every request needs at least one token of its own after the shared prefix")
-        g = torch.Generator().manual_seed(self.seed + 17)
+        g = torch.Generator().manual_seed(self.data_seed + 17)
         shared_ids = torch.randint(0, self.token_base, (sp,), generator=g)
         full_ids = []
         for r, plen in enumerate(self.prompt_lens):
