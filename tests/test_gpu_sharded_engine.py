@@ -32,47 +32,46 @@ def _worker(rank, world, port, q):
 
 
 def _body(rank, world, dev, dist, q):
-    if True:
-        from flashrec_b200 import device_status
-        from flashrec_b200.decoder import Qwen3Config
-        from flashrec_b200.sharded_head import ShardedSidHead
-        from flashrec_b200.sid_decode import SidDecodeEngine
-        from flashrec_b200.trie import build_trie_device
+    from flashrec_b200 import device_status
+    from flashrec_b200.decoder import Qwen3Config
+    from flashrec_b200.sharded_head import ShardedSidHead
+    from flashrec_b200.sid_decode import SidDecodeEngine
+    from flashrec_b200.trie import build_trie_device
 
-        rng = np.random.default_rng(3)
-        sizes, base = [256, 256, 256], 1000
-        items = np.unique(rng.integers(0, 256, (30000, 3)), axis=0).astype(np.int32)
-        trie = build_trie_device(torch.from_numpy(items).to(dev), sizes, base, layout="csr")
-        cfg = Qwen3Config(hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=4,
-                          num_key_value_heads=2, head_dim=128, max_position_embeddings=256, vocab_size=base + sum(sizes))
-        n, bw = 2, 64
-        plens = [40 + 7 * rank, 55 + 3 * rank]
-        kw = dict(shared_prefix=16, page_size=16, seed=0, data_seed=rank)
-        sh = SidDecodeEngine(cfg, n, bw, plens, sizes, base, trie, dev, sharded_head=ShardedSidHead(), **kw)
-        sh.prefill()
-        sh.run(host_io=False, _eager=True)
-        eager = (sh.cum.clone(), sh.tok_planes[sh.steps & 1].clone(), sh.g_cum.clone())
-        sh.capture()
-        sh.run(host_io=True)
-        torch.cuda.synchronize()
-        assert device_status() == (0, 0)
-        # graph replay == eager, and every rank holds the same state of the whole group
-        assert torch.equal(sh.cum, eager[0]) and torch.equal(sh.tok_planes[sh.steps & 1], eager[1])
-        both = [torch.empty_like(sh.g_cum) for _ in range(world)]
-        dist.all_gather(both, sh.g_cum.contiguous())
-        assert all(torch.equal(b, both[0]) for b in both)
-        nodes = sh.final_nodes
-        assert int(((nodes != -1) & torch.isfinite(sh.cum)).sum()) == 0  # complete, legal SIDs only
-        # the same requests through the unsharded engine with the same weights
-        un = SidDecodeEngine(cfg, n, bw, plens, sizes, base, trie, dev, **kw)
-        un.prefill()
-        un.run(host_io=False, _eager=True)
-        torch.cuda.synchronize()
-        q.put((rank, sh.cum.cpu().numpy(), sh.tok_planes[sh.steps & 1].cpu().numpy(), un.cum.cpu().numpy(),
-               un.tok_planes[un.steps & 1].cpu().numpy()))
-        sh.graphs = [None] * sh.steps  # captured NCCL work goes before the process group does
-        torch.cuda.synchronize()
-        dist.barrier()
+    rng = np.random.default_rng(3)
+    sizes, base = [256, 256, 256], 1000
+    items = np.unique(rng.integers(0, 256, (30000, 3)), axis=0).astype(np.int32)
+    trie = build_trie_device(torch.from_numpy(items).to(dev), sizes, base, layout="csr")
+    cfg = Qwen3Config(hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, head_dim=128, max_position_embeddings=256, vocab_size=base + sum(sizes))
+    n, bw = 2, 64
+    plens = [40 + 7 * rank, 55 + 3 * rank]
+    kw = dict(shared_prefix=16, page_size=16, seed=0, data_seed=rank)
+    sh = SidDecodeEngine(cfg, n, bw, plens, sizes, base, trie, dev, sharded_head=ShardedSidHead(), **kw)
+    sh.prefill()
+    sh.run(host_io=False, _eager=True)
+    eager = (sh.cum.clone(), sh.tok_planes[sh.steps & 1].clone(), sh.g_cum.clone())
+    sh.capture()
+    sh.run(host_io=True)
+    torch.cuda.synchronize()
+    assert device_status() == (0, 0)
+    # graph replay == eager, and every rank holds the same state of the whole group
+    assert torch.equal(sh.cum, eager[0]) and torch.equal(sh.tok_planes[sh.steps & 1], eager[1])
+    both = [torch.empty_like(sh.g_cum) for _ in range(world)]
+    dist.all_gather(both, sh.g_cum.contiguous())
+    assert all(torch.equal(b, both[0]) for b in both)
+    nodes = sh.final_nodes
+    assert int(((nodes != -1) & torch.isfinite(sh.cum)).sum()) == 0  # complete, legal SIDs only
+    # the same requests through the unsharded engine with the same weights
+    un = SidDecodeEngine(cfg, n, bw, plens, sizes, base, trie, dev, **kw)
+    un.prefill()
+    un.run(host_io=False, _eager=True)
+    torch.cuda.synchronize()
+    q.put((rank, sh.cum.cpu().numpy(), sh.tok_planes[sh.steps & 1].cpu().numpy(), un.cum.cpu().numpy(),
+           un.tok_planes[un.steps & 1].cpu().numpy()))
+    sh.graphs = [None] * sh.steps  # captured NCCL work goes before the process group does
+    torch.cuda.synchronize()
+    dist.barrier()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
